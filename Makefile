@@ -1,0 +1,74 @@
+# Builds the native parts: sm_100a kernels, the daemon (libmccs_daemon.so + mccsd),
+# the client shim (libmccs.so), the LD_PRELOAD allocator hook, the apps and the
+# host-side unit tests. Everything lands in mccs_b200/_native/.
+NVCC      ?= nvcc
+CXX       ?= g++
+OUT       := mccs_b200/_native
+OBJ       := build/obj
+ARCH      := -gencode arch=compute_100a,code=sm_100a
+CXXFLAGS  := -std=c++17 -O2 -g -fPIC -Wall -Wextra -Wno-unused-parameter -pthread -I/usr/local/cuda/include
+NVCCFLAGS := -std=c++17 -O3 -lineinfo $(ARCH) -Xcompiler -fPIC,-Wall,-Wno-unused-parameter -Xptxas -v
+LDLIBS    := -lpthread -ldl -lrt
+
+TYPES := i8:int8_t u8:uint8_t i32:int32_t u32:uint32_t i64:int64_t u64:uint64_t f16:__half f32:float f64:double bf16:__nv_bfloat16
+NVLS_TYPES := f16 f32 bf16
+TYPE_OBJS := $(foreach t,$(TYPES),$(OBJ)/inst_$(word 1,$(subst :, ,$(t))).o)
+
+HOST_SRCS := csrc/common/value.cc csrc/common/log.cc csrc/ipc/uds.cc csrc/device/host_backend.cc \
+             csrc/daemon/config.cc csrc/daemon/planner.cc csrc/daemon/qos.cc csrc/daemon/trace.cc \
+             csrc/daemon/runtime.cc csrc/daemon/daemon.cc csrc/daemon/proxy.cc csrc/daemon/admin.cc
+HOST_OBJS := $(patsubst csrc/%.cc,$(OBJ)/%.o,$(HOST_SRCS))
+CUDA_OBJS := $(OBJ)/device/cuda_backend.o $(OBJ)/kernels/launch.o $(OBJ)/kernels/untyped.o $(TYPE_OBJS)
+SHIM_SRCS := csrc/shim/libmccs.cc csrc/common/value.cc csrc/common/log.cc csrc/ipc/uds.cc
+SHIM_OBJS := $(patsubst csrc/%.cc,$(OBJ)/%.o,$(SHIM_SRCS))
+HDRS := $(wildcard csrc/*/*.h csrc/*/*.cuh)
+
+APPS := allreduce_bench allgather_bench allreduce_proto allgather_proto traffic_gen ring_config mccs_hello
+APP_BINS := $(addprefix $(OUT)/,$(APPS))
+
+all: $(OUT)/libmccs_daemon.so $(OUT)/libmccs.so $(OUT)/mccsd $(OUT)/libmccs_preload.so $(APP_BINS) $(OUT)/host_tests
+
+$(OBJ)/%.o: csrc/%.cc $(HDRS)
+	@mkdir -p $(dir $@)
+	$(CXX) $(CXXFLAGS) -c $< -o $@
+
+$(OBJ)/device/cuda_backend.o: csrc/device/cuda_backend.cu $(HDRS)
+	@mkdir -p $(dir $@)
+	$(NVCC) $(NVCCFLAGS) -c $< -o $@ 2> $@.log || (cat $@.log; false)
+
+$(OBJ)/kernels/%.o: csrc/kernels/%.cu $(HDRS)
+	@mkdir -p $(dir $@)
+	$(NVCC) $(NVCCFLAGS) -c $< -o $@ 2> $@.log || (cat $@.log; false)
+
+define TYPE_RULE
+$(OBJ)/inst_$(1).o: csrc/kernels/inst_dtype.cu $(HDRS)
+	@mkdir -p $$(dir $$@)
+	$(NVCC) $(NVCCFLAGS) -DMCCS_T=$(2) -DMCCS_TNAME=$(1) $(if $(filter $(1),$(NVLS_TYPES)),-DMCCS_NVLS=1) -c $$< -o $$@ 2> $$@.log || (cat $$@.log; false)
+endef
+$(foreach t,$(TYPES),$(eval $(call TYPE_RULE,$(word 1,$(subst :, ,$(t))),$(word 2,$(subst :, ,$(t))))))
+
+$(OUT)/libmccs_daemon.so: $(HOST_OBJS) $(CUDA_OBJS)
+	@mkdir -p $(OUT)
+	$(NVCC) $(ARCH) -shared -cudart static -o $@ $^ $(LDLIBS)
+
+$(OUT)/libmccs.so: $(SHIM_OBJS)
+	@mkdir -p $(OUT)
+	$(CXX) -shared -o $@ $^ $(LDLIBS)
+
+$(OUT)/libmccs_preload.so: $(OBJ)/shim/preload.o $(OUT)/libmccs.so
+	$(CXX) -shared -o $@ $(OBJ)/shim/preload.o -L$(OUT) -lmccs -Wl,-rpath,'$$ORIGIN' $(LDLIBS)
+
+$(OUT)/mccsd: $(OBJ)/daemon/main.o $(OUT)/libmccs_daemon.so
+	$(CXX) -o $@ $(OBJ)/daemon/main.o -L$(OUT) -lmccs_daemon -Wl,-rpath,'$$ORIGIN' $(LDLIBS)
+
+$(OUT)/%: $(OBJ)/apps/%.o $(OBJ)/apps/app_common.o $(OUT)/libmccs.so
+	$(CXX) -o $@ $(OBJ)/apps/$*.o $(OBJ)/apps/app_common.o -L$(OUT) -lmccs -Wl,-rpath,'$$ORIGIN' $(LDLIBS)
+
+$(OUT)/host_tests: $(OBJ)/tests/host_tests.o $(OUT)/libmccs_daemon.so
+	$(CXX) -o $@ $(OBJ)/tests/host_tests.o -L$(OUT) -lmccs_daemon -Wl,-rpath,'$$ORIGIN' $(LDLIBS)
+
+clean:
+	rm -rf build $(OUT)/*.so $(OUT)/mccsd $(APP_BINS) $(OUT)/host_tests
+
+.PHONY: all clean
+.SECONDARY:

@@ -1,0 +1,214 @@
+// Wire protocol between the client shim (libmccs) and the service daemon.
+//
+// Two channels per client, as in the reference (src/ipc/mccs/src/command.rs:88-112
+// for control, src/ipc/mccs/src/dp.rs:8-28 for the data path):
+//   * control: request/reply messages on a Unix SOCK_SEQPACKET connection. Fixed
+//     layout structs (no serialisation step); file descriptors travel as
+//     SCM_RIGHTS ancillary data.
+//   * data path: one pair of single-producer/single-consumer rings in shared memory
+//     per (communicator, rank): 128-byte work requests, 64-byte completions, the slot
+//     sizes the reference uses. The per-GPU proxy polls the request ring directly,
+//     so a collective crosses one thread boundary instead of the reference's two.
+#pragma once
+#include <stdint.h>
+
+namespace mccs {
+namespace proto {
+
+constexpr uint32_t kMagic = 0x5343434du;  // "MCCS"
+constexpr uint32_t kVersion = 3;
+constexpr uint32_t kWqDepth = 64;
+constexpr uint32_t kCqDepth = 64;
+constexpr uint32_t kWrBytes = 128;
+constexpr uint32_t kWcBytes = 64;
+constexpr uint32_t kIpcHandleBytes = 64;  // cudaIpcMemHandle_t / cudaIpcEventHandle_t
+
+enum MsgType : uint32_t {
+  kHello = 1, kWelcome = 2,
+  kMalloc = 3, kMallocReply = 4,
+  kFree = 5, kFreeReply = 6,
+  kCommInit = 7, kCommInitReply = 8,
+  kCommDestroy = 9, kCommDestroyReply = 10,
+  kRegisterStream = 11, kRegisterStreamReply = 12,
+  kCommQuery = 13, kCommQueryReply = 14,
+  kGoodbye = 15,
+};
+
+enum Status : int32_t {
+  kOk = 0,
+  kErrInvalidArgument = -1,
+  kErrOutOfMemory = -2,
+  kErrDevice = -3,          // a CUDA call failed
+  kErrProtocol = -4,
+  kErrNotFound = -5,
+  kErrTimeout = -6,         // a bounded device-side or host-side wait ran out
+  kErrAborted = -7,
+  kErrMismatch = -8,        // ranks disagreed on a collective's parameters
+  kErrUnsupported = -9,
+  kErrPeerLost = -10,       // another rank of the communicator went away
+  kErrInternal = -11,
+};
+
+enum Backend : uint32_t { kBackendHost = 0, kBackendCuda = 1 };
+
+// How the client maps an allocation the daemon made for it.
+enum ShareKind : uint32_t {
+  kShareHostFd = 0,     // memfd: mmap (host backend)
+  kShareVmmFd = 1,      // CUDA VMM allocation exported as POSIX fd
+  kShareCudaIpc = 2,    // cudaIpcMemHandle_t (cudaMalloc'ed memory)
+  kShareSameProcess = 3 // daemon runs inside the client process: use daemon_va
+};
+
+struct Header {
+  uint32_t magic;
+  uint32_t type;     // MsgType
+  uint32_t req_id;   // echoed in the reply
+  int32_t status;    // Status (replies)
+};
+
+struct Hello {
+  Header h;
+  uint32_t version;
+  int32_t pid;
+  int32_t device_affinity;  // -1: none
+  uint32_t reserved;
+  char app_name[64];
+};
+
+struct Welcome {
+  Header h;
+  uint32_t version;
+  int32_t daemon_pid;
+  uint32_t backend;       // Backend
+  uint32_t num_devices;
+  uint64_t session_id;
+  uint32_t sync_mode;     // 0: IPC events
+  uint32_t reserved;
+};
+
+struct MallocReq {
+  Header h;
+  int32_t device;
+  uint32_t flags;
+  uint64_t size;
+};
+
+struct MallocReply {
+  Header h;
+  uint64_t mem_id;
+  uint64_t size;          // mapped size (>= requested, rounded to the granularity)
+  uint64_t daemon_va;
+  uint32_t share_kind;    // ShareKind
+  int32_t device;
+  uint8_t ipc_handle[kIpcHandleBytes];
+};
+
+struct FreeReq { Header h; uint64_t mem_id; };
+struct FreeReply { Header h; };
+
+struct CommInitReq {
+  Header h;
+  uint32_t comm_id;       // user-chosen id: also the tenant key for QoS and overrides
+  int32_t rank;
+  int32_t nranks;
+  int32_t device;
+  char root_addr[64];     // accepted for API parity; rendezvous is in-daemon
+};
+
+struct CommInitReply {
+  Header h;
+  uint64_t comm_handle;   // (comm_id << 32) + rank, as the reference composes it
+  uint8_t event_handle[kIpcHandleBytes];  // backend event (IPC) ...
+  uint64_t event_raw;                     // ... or its in-process handle
+  uint32_t dp_bytes;      // size of the data-path segment passed as fd
+  uint32_t reserved;
+};
+
+struct CommDestroyReq { Header h; uint64_t comm_handle; };
+struct CommDestroyReply { Header h; };
+
+struct RegisterStreamReq {
+  Header h;
+  int32_t device;
+  uint32_t reserved;
+  uint64_t stream;        // client-side stream handle, used only as a key
+  uint8_t event_handle[kIpcHandleBytes];
+  uint64_t event_raw;
+};
+struct RegisterStreamReply { Header h; uint64_t stream_id; };
+
+struct CommQueryReq { Header h; uint64_t comm_handle; };
+struct CommQueryReply {
+  Header h;
+  int32_t async_error;     // Status, sticky
+  uint32_t device_error;   // DevStatus reported by a kernel
+  uint64_t launched;       // collectives launched so far
+  uint64_t completed;
+  uint32_t last_variant;
+  uint32_t last_ctas;
+  uint64_t config_epoch;   // bumps on every applied reconfiguration
+};
+
+union AnyMsg {
+  Header h;
+  Hello hello; Welcome welcome;
+  MallocReq malloc_req; MallocReply malloc_reply;
+  FreeReq free_req; FreeReply free_reply;
+  CommInitReq comm_init; CommInitReply comm_init_reply;
+  CommDestroyReq comm_destroy; CommDestroyReply comm_destroy_reply;
+  RegisterStreamReq reg_stream; RegisterStreamReply reg_stream_reply;
+  CommQueryReq comm_query; CommQueryReply comm_query_reply;
+  uint8_t raw[256];
+};
+
+// ---------------------------------------------------------------------------
+// Data path
+// ---------------------------------------------------------------------------
+enum WrFlags : uint32_t {
+  kWrGroupMore = 1u << 0,   // further requests of the same group follow
+};
+
+struct alignas(64) WorkRequest {
+  uint32_t kind;        // CollKind
+  uint32_t dtype;       // DataType (AllReduce)
+  uint32_t op;          // RedOp (AllReduce)
+  uint32_t flags;       // WrFlags
+  uint64_t comm_handle;
+  uint64_t send_mem, send_off;
+  uint64_t recv_mem, recv_off;
+  uint64_t count;       // AllReduce: elements; AllGather: bytes per rank
+  uint64_t stream_id;   // from RegisterStream
+  uint64_t user_seq;    // client-side counter, echoed in the completion
+  float scale;          // PreMulSum / SumPostDiv argument
+  uint32_t variant;     // Variant requested by the caller (0 = planner decides)
+  uint64_t reserved[5];
+};
+static_assert(sizeof(WorkRequest) == kWrBytes, "work request must fill one 128-byte slot");
+
+struct alignas(64) WorkCompletion {
+  uint32_t kind;
+  int32_t status;       // Status
+  uint64_t user_seq;
+  uint32_t variant;     // what the planner launched
+  uint32_t ctas;
+  uint64_t comm_seq;    // sequence number of the collective within the communicator
+  uint64_t reserved[4];
+};
+static_assert(sizeof(WorkCompletion) == kWcBytes, "completion must fill one 64-byte slot");
+
+inline uint64_t make_comm_handle(uint32_t comm_id, int rank) { return ((uint64_t)comm_id << 32) + (uint32_t)rank; }
+inline uint32_t handle_comm_id(uint64_t h) { return (uint32_t)(h >> 32); }
+inline int handle_rank(uint64_t h) { return (int)(uint32_t)h; }
+
+// ---------------------------------------------------------------------------
+// Admin channel (TCP), same framing as the reference's exchange engine
+// (src/mccs/src/exchange/engine.rs:33,44-76): u64 magic, u8 type, u32 length, body.
+// Type 1 carries a reconfiguration command; the body here is JSON text.
+// ---------------------------------------------------------------------------
+constexpr uint64_t kAdminMagic = 0x424ab9f2fc4b9d6eull;
+enum AdminType : uint8_t { kAdminProxy = 0, kAdminReconfig = 1, kAdminQuery = 2 };
+
+const char* status_string(int32_t s);
+
+}  // namespace proto
+}  // namespace mccs

@@ -1,0 +1,135 @@
+#include "config.h"
+
+#include <set>
+#include <stdexcept>
+
+namespace mccs {
+
+std::string Config::control_socket_path() const {
+  std::string prefix = expand_env(control_prefix);
+  if (!prefix.empty() && prefix.back() == '/') prefix.pop_back();
+  return prefix + "/" + expand_env(control_path);
+}
+
+const CommPattern* Config::find_override(uint32_t comm_id) const {
+  for (const auto& p : overrides)
+    if (p.communicator_id == comm_id) return &p;
+  return nullptr;
+}
+
+CommPattern Config::parse_pattern(const Value& v) {
+  CommPattern p;
+  if (!v.has("communicator_id")) throw std::runtime_error("comm pattern without communicator_id");
+  p.communicator_id = (uint32_t)v["communicator_id"].as_int();
+  for (const Value& c : v["channels"].items()) {
+    ChannelPattern ch;
+    ch.channel_id = (int)c["channel_id"].as_int();
+    for (const Value& r : c["ring"].items()) ch.ring.push_back((int)r.as_int());
+    for (const Value& t : c["udp_sport"].items()) {
+      std::vector<int> triple;
+      for (const Value& x : t.items()) triple.push_back((int)x.as_int());
+      ch.udp_sport.push_back(triple);
+    }
+    ch.net_dev = c["net_dev"].as_string();
+    p.channels.push_back(ch);
+  }
+  if (v.has("ib_traffic_class")) p.ib_traffic_class = (int)v["ib_traffic_class"].as_int();
+  p.allreduce_algo = v["allreduce_algo"].as_string();
+  p.allgather_algo = v["allgather_algo"].as_string();
+  p.ctas = (int)v["ctas"].as_int(0);
+  return p;
+}
+
+static void check_keys(const Value& table, const std::set<std::string>& allowed, const char* where) {
+  for (const auto& kv : table.fields())
+    if (!allowed.count(kv.first))
+      throw std::runtime_error(std::string("unknown key '") + kv.first + "' in " + where);
+}
+
+Config Config::from_value(const Value& root) {
+  Config c;
+  // The reference rejects unknown top-level fields (serde deny_unknown_fields,
+  // src/mccs/src/config.rs:74-76); so does this loader.
+  check_keys(root,
+             {"control", "comm_default_config", "comm_global_config", "addrs", "listen_port",
+              "mccs_daemon_basename", "mccs_daemon_prefix", "qos_schedule", "qos",
+              "comm_patterns_override", "b200"},
+             "the top level");
+  if (root.has("control")) {
+    const Value& t = root["control"];
+    c.control_prefix = t["prefix"].as_string(c.control_prefix);
+    c.control_path = t["path"].as_string(c.control_path);
+  }
+  c.daemon_prefix = root["mccs_daemon_prefix"].as_string(c.daemon_prefix);
+  c.daemon_basename = root["mccs_daemon_basename"].as_string(c.daemon_basename);
+  for (const Value& a : root["addrs"].items()) c.addrs.push_back(a.as_string());
+  c.listen_port = (int)root["listen_port"].as_int(c.listen_port);
+  if (root.has("comm_default_config")) {
+    const Value& t = root["comm_default_config"];
+    if (t.has("buffer_sizes")) {
+      c.buffer_sizes.clear();
+      for (const Value& b : t["buffer_sizes"].items()) c.buffer_sizes.push_back((uint64_t)b.as_int());
+      if (c.buffer_sizes.empty()) throw std::runtime_error("buffer_sizes must not be empty");
+    }
+    c.channel_count = (int)t["channel_count"].as_int(c.channel_count);
+    if (c.channel_count < 1 || c.channel_count > 32) throw std::runtime_error("channel_count out of range 1..32");
+  }
+  c.comm_global_config = root["comm_global_config"];
+  if (root.has("qos_schedule")) {
+    const Value& q = root["qos_schedule"];
+    c.qos_epoch_us = (uint64_t)q["epoch_microsecs"].as_int();
+    for (const auto& kv : q["schedule"].fields()) {
+      QosIntervalConfig qi;
+      for (const Value& iv : kv.second["intervals"].items()) {
+        if (iv.size() != 2) throw std::runtime_error("qos interval must be [start, end]");
+        qi.intervals.push_back({(uint64_t)iv.at(0).as_int(), (uint64_t)iv.at(1).as_int()});
+      }
+      std::string mode = kv.second["mode"].as_string("Allow");
+      if (mode != "Allow" && mode != "Deny") throw std::runtime_error("qos mode must be Allow or Deny");
+      qi.allow = mode == "Allow";
+      qi.enforce_step = (int)kv.second["enforce_step"].as_int(0);
+      c.qos_schedule[(uint32_t)std::stoul(kv.first)] = qi;
+    }
+  }
+  if (root.has("qos")) {
+    const Value& q = root["qos"];
+    c.qos_cta_budget = (int)q["cta_budget"].as_int(c.qos_cta_budget);
+    c.qos_max_outstanding_bytes = (uint64_t)q["max_outstanding_bytes"].as_int((int64_t)c.qos_max_outstanding_bytes);
+    for (const auto& kv : q["tenants"].fields()) {
+      QosTenantConfig t;
+      t.weight = kv.second["weight"].as_double(1.0);
+      t.priority = (int)kv.second["priority"].as_int(0);
+      t.cta_quota = (int)kv.second["cta_quota"].as_int(0);
+      if (t.weight <= 0) throw std::runtime_error("tenant weight must be positive");
+      c.qos_tenants[(uint32_t)std::stoul(kv.first)] = t;
+    }
+  }
+  for (const Value& p : root["comm_patterns_override"].items()) c.overrides.push_back(parse_pattern(p));
+  if (root.has("b200")) {
+    const Value& b = root["b200"];
+    check_keys(b,
+               {"transport", "nvls", "vmm", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
+                "host_devices", "force_host_backend", "idle_sleep_us", "pin_threads", "init_timeout_ms"},
+               "[b200]");
+    c.transport = b["transport"].as_string(c.transport);
+    if (c.transport != "auto" && c.transport != "nvlink" && c.transport != "host_staged")
+      throw std::runtime_error("b200.transport must be auto, nvlink or host_staged");
+    c.nvls = b["nvls"].as_bool(c.nvls);
+    c.vmm = b["vmm"].as_bool(c.vmm);
+    c.wait_timeout_ms = (uint64_t)b["wait_timeout_ms"].as_int((int64_t)c.wait_timeout_ms);
+    c.tuning_file = b["tuning_file"].as_string();
+    c.trace = b["trace"].as_bool(c.trace);
+    c.trace_file = b["trace_file"].as_string();
+    c.host_devices = (int)b["host_devices"].as_int(c.host_devices);
+    c.force_host_backend = b["force_host_backend"].as_bool(c.force_host_backend);
+    c.idle_sleep_us = (int)b["idle_sleep_us"].as_int(c.idle_sleep_us);
+    c.pin_threads = b["pin_threads"].as_bool(c.pin_threads);
+    c.init_timeout_ms = (uint64_t)b["init_timeout_ms"].as_int((int64_t)c.init_timeout_ms);
+  }
+  return c;
+}
+
+Config Config::from_string(const std::string& toml) { return from_value(parse_toml(toml)); }
+Config Config::from_file(const std::string& path) { return from_string(read_text_file(path)); }
+
+}  // namespace mccs

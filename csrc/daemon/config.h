@@ -1,0 +1,95 @@
+// Daemon configuration. The file keeps the reference's TOML schema
+// (src/mccs/src/config.rs:14-89 and the shipped mccs.toml) so an existing mccs.toml
+// loads unchanged: [control], [comm_default_config], [comm_global_config.*], addrs,
+// listen_port, [qos_schedule] and [[comm_patterns_override]]. The RDMA/NIC keys are
+// accepted and kept but have no effect inside one NVSwitch box. A new [b200] table
+// and [qos.tenants.<id>] tables carry what the NVLink re-target adds: transport
+// selection, NVLS on/off, device wait bound, tuning table, tenant weights.
+#pragma once
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../common/value.h"
+
+namespace mccs {
+
+struct ChannelPattern {
+  int channel_id = 0;
+  std::vector<int> ring;                      // user ranks in ring order
+  std::vector<std::vector<int>> udp_sport;    // kept for schema parity, unused
+  std::string net_dev;                        // kept for schema parity, unused
+};
+
+struct CommPattern {
+  uint32_t communicator_id = 0;
+  std::vector<ChannelPattern> channels;
+  int ib_traffic_class = -1;
+  // Extensions for the NVLink box (all optional).
+  std::string allreduce_algo;   // "", "auto", or a variant name
+  std::string allgather_algo;
+  int ctas = 0;                 // 0: planner decides ("channel count" of the new kernels)
+};
+
+struct QosIntervalConfig {
+  std::vector<std::pair<uint64_t, uint64_t>> intervals;  // [start,end) in µs within the epoch
+  bool allow = true;            // mode = "Allow" | "Deny"
+  int enforce_step = 0;         // 0: every collective; N: only when round % N == 0
+};
+
+struct QosTenantConfig {
+  double weight = 1.0;
+  int priority = 0;             // > 0: high-priority stream
+  int cta_quota = 0;            // 0: derived from the weight
+};
+
+struct Config {
+  // [control]
+  std::string control_prefix = "/tmp/mccs-${USER}";
+  std::string control_path = "control.sock";
+  std::string daemon_prefix = "/tmp/mccs-${USER}";
+  std::string daemon_basename = "mccs-deamon";
+  std::vector<std::string> addrs;
+  int listen_port = 5000;       // admin/exchange TCP port; 0 disables, -1 picks a free port
+  // [comm_default_config]
+  std::vector<uint64_t> buffer_sizes{4u << 20};   // ring FIFO bytes per channel
+  int channel_count = 1;
+  // [comm_global_config.*] kept verbatim
+  Value comm_global_config;
+  // [qos_schedule]
+  uint64_t qos_epoch_us = 0;
+  std::map<uint32_t, QosIntervalConfig> qos_schedule;
+  // [qos.tenants.<id>]
+  std::map<uint32_t, QosTenantConfig> qos_tenants;
+  int qos_cta_budget = 64;       // CTAs shared by contending tenants on one GPU
+  uint64_t qos_max_outstanding_bytes = 64ull << 20;  // per tenant, only under contention
+  // [[comm_patterns_override]]
+  std::vector<CommPattern> overrides;
+  // [b200]
+  std::string transport = "auto";   // auto | nvlink | host_staged
+  bool nvls = true;
+  bool vmm = true;
+  uint64_t wait_timeout_ms = 10000; // bound of every device-side wait
+  std::string tuning_file;
+  bool trace = false;
+  std::string trace_file;
+  int host_devices = 8;
+  bool force_host_backend = false;
+  int idle_sleep_us = 50;           // proxy back-off after a stretch of idle polls
+  bool pin_threads = true;
+  uint64_t init_timeout_ms = 60000; // how long a communicator waits for all its ranks
+
+  std::string control_socket_path() const;   // expanded prefix/path
+  const CommPattern* find_override(uint32_t comm_id) const;
+
+  static Config from_value(const Value& root);       // throws std::runtime_error
+  static Config from_file(const std::string& path);  // throws
+  static Config from_string(const std::string& toml);
+  // Parses one override / reconfiguration entry (TOML or JSON tree).
+  static CommPattern parse_pattern(const Value& v);
+};
+
+}  // namespace mccs

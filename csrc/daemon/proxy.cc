@@ -1,0 +1,554 @@
+// Data path of the daemon: the per-GPU proxy engine.
+//
+// For every rank that lives on its device the proxy (1) takes work requests from
+// the client's shared-memory ring, (2) posts them into the communicator's
+// rendezvous slot for that collective, (3) once every rank has posted, one proxy
+// plans the collective for all ranks (variant, CTAs, slices, barrier epochs, NVLS
+// mappings), (4) asks the QoS arbiter for admission, slice by slice, (5) launches
+// the kernel on the rank's backend stream between the client's "submitted" event
+// and the backend's "done" event, and (6) completes the request.
+//
+// Reference counterparts: check_daemon_command / schedule_all_reduce /
+// launch_scheduled_and_record (src/mccs/src/proxy/engine.rs:926-1066,1170-1275) and
+// the planner in src/mccs/src/proxy/plan.rs. The reference's per-rank proxies never
+// meet on the host: each uploads work to its kernel's FIFO and the kernels find each
+// other through connection FIFOs set up at communicator creation. Here the host-side
+// meeting is what lets one plan (and one reconfiguration point) hold for all ranks.
+#include <string.h>
+
+#include <algorithm>
+
+#include "../common/log.h"
+#include "daemon.h"
+
+namespace mccs {
+
+void ProxyEngine::on_start() {
+  daemon_->backend()->set_device(device_);
+  started_.store(true);
+}
+
+void ProxyEngine::add_rank(RankState* rs) {
+  std::lock_guard<std::mutex> g(mu_);
+  ranks_.push_back(rs);
+  version_.fetch_add(1);
+}
+
+void ProxyEngine::remove_rank(RankState* rs) {
+  uint64_t v;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    ranks_.erase(std::remove(ranks_.begin(), ranks_.end(), rs), ranks_.end());
+    v = version_.fetch_add(1) + 1;
+  }
+  // Wait until the proxy thread has adopted the new list (it may be mid-iteration).
+  if (!started_.load()) return;
+  for (int i = 0; i < 20000 && seen_version_.load(std::memory_order_acquire) < v; i++) {
+    struct timespec ts = {0, 100000};
+    nanosleep(&ts, nullptr);
+  }
+}
+
+Progress ProxyEngine::progress() {
+  if (seen_version_.load(std::memory_order_relaxed) != version_.load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> g(mu_);
+    local_ = ranks_;
+    seen_version_.store(version_.load(), std::memory_order_release);
+  }
+  bool any = false;
+  spins_++;
+  for (RankState* rs : local_) {
+    if (rs->gone.load(std::memory_order_relaxed)) continue;
+    any |= intake(*rs);
+    any |= advance(*rs);
+    if ((spins_ & 0x3f) == 0 || any) housekeeping(*rs);
+  }
+  return any ? Progress::kProgressed : Progress::kIdle;
+}
+
+// ---------------------------------------------------------------------------
+// (1)+(2): request intake and posting
+// ---------------------------------------------------------------------------
+bool ProxyEngine::intake(RankState& rs) {
+  bool any = false;
+  if (rs.have_pending_wc) {
+    if (!rs.cq.try_push(&rs.pending_wc)) return false;
+    rs.have_pending_wc = false;
+    any = true;
+  }
+  // The reference drains at most 32 requests per visit (daemon/engine.rs:274-435).
+  for (int i = 0; i < 32; i++) {
+    if (!rs.have_pending_wr) {
+      if (!rs.wq.try_pop(&rs.pending_wr)) break;
+      rs.have_pending_wr = true;
+    }
+    if (rs.comm->state.load(std::memory_order_acquire) == kCommError) {
+      // A failed communicator takes no new work: answer in order, after whatever
+      // was posted before the failure has been completed by advance().
+      if (rs.next_launch_seq != rs.next_post_seq || rs.have_pending_wc) break;
+      proto::WorkCompletion wc;
+      memset(&wc, 0, sizeof wc);
+      wc.kind = rs.pending_wr.kind;
+      int err = rs.comm->async_error.load();
+      wc.status = err ? err : proto::kErrAborted;
+      wc.user_seq = rs.pending_wr.user_seq;
+      if (!rs.cq.try_push(&wc)) { rs.pending_wc = wc; rs.have_pending_wc = true; }
+      rs.have_pending_wr = false;
+      any = true;
+      continue;
+    }
+    if (!post(rs, rs.pending_wr)) break;
+    rs.have_pending_wr = false;
+    any = true;
+  }
+  return any;
+}
+
+bool ProxyEngine::post(RankState& rs, const proto::WorkRequest& wr) {
+  Communicator& c = *rs.comm;
+  const uint64_t seq = rs.next_post_seq;
+  CollSlot& s = c.slot(seq);
+  if (s.seq.load(std::memory_order_acquire) != seq) return false;   // slot still busy with seq - kCollSlots
+
+  CollOp& op = s.ops[rs.rank];
+  op = CollOp();
+  op.kind = (int)wr.kind;
+  op.dtype = (int)wr.dtype;
+  op.op = (int)wr.op;
+  op.count = wr.count;
+  op.scale = wr.scale;
+  op.variant_req = (int)wr.variant;
+  op.user_seq = wr.user_seq;
+  op.send_mem = wr.send_mem; op.send_off = wr.send_off;
+  op.recv_mem = wr.recv_mem; op.recv_off = wr.recv_off;
+  op.t_post_us = monotonic_us();
+  int status = proto::kOk;
+  if (op.kind != kAllReduce && op.kind != kAllGather) status = proto::kErrInvalidArgument;
+  else if (op.kind == kAllReduce && (op.dtype < 0 || op.dtype >= kNumDataTypes || op.op < 0 || op.op >= kNumRedOps))
+    status = proto::kErrInvalidArgument;
+  else if (op.variant_req < 0 || op.variant_req >= kNumVariants) status = proto::kErrInvalidArgument;
+  if (status == proto::kOk) {
+    const uint64_t esz = op.kind == kAllReduce ? (uint64_t)dtype_size(op.dtype) : 1;
+    const uint64_t send_bytes = op.count * esz;
+    const uint64_t recv_bytes = op.kind == kAllReduce ? send_bytes : send_bytes * (uint64_t)c.nranks;
+    int sdev = -1, rdev = -1;
+    if (!daemon_->translate(op.send_mem, op.send_off, send_bytes, &op.send_va, &sdev) ||
+        !daemon_->translate(op.recv_mem, op.recv_off, recv_bytes, &op.recv_va, &rdev))
+      status = proto::kErrNotFound;
+    else if (sdev != rs.device || rdev != rs.device)
+      status = proto::kErrInvalidArgument;
+  }
+  op.user_event = daemon_->lookup_stream_event(rs.session_id, wr.stream_id);
+  op.status = status;
+  op.valid = status == proto::kOk;
+  rs.next_post_seq++;
+  if (s.arrived.fetch_add(1, std::memory_order_acq_rel) + 1 == c.nranks)
+    s.state.store(kSlotCollected, std::memory_order_release);
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// (3): planning, done by whichever proxy first sees the slot complete
+// ---------------------------------------------------------------------------
+int ProxyEngine::ensure_mc(Communicator& c, CollSlot& s, bool for_recv, uint64_t* out_va) {
+  std::vector<uint64_t> key;
+  for (int r = 0; r < c.nranks; r++) key.push_back(for_recv ? s.ops[r].recv_mem : s.ops[r].send_mem);
+  const uint64_t off = for_recv ? s.ops[0].recv_off : s.ops[0].send_off;
+  const uint64_t esz = s.ops[0].kind == kAllReduce ? (uint64_t)dtype_size(s.ops[0].dtype) : 1;
+  uint64_t bytes = s.ops[0].count * esz;
+  if (for_recv && s.ops[0].kind == kAllGather) bytes *= (uint64_t)c.nranks;
+  std::lock_guard<std::mutex> g(c.mc_mu);
+  auto it = c.mc_cache.find(key);
+  if (it == c.mc_cache.end()) {
+    std::shared_lock<std::shared_mutex> al(daemon_->alloc_mutex());
+    std::vector<const Allocation*> allocs;
+    for (uint64_t id : key) {
+      const Allocation* a = daemon_->find_alloc_locked(id);
+      if (!a) return proto::kErrNotFound;
+      allocs.push_back(a);
+    }
+    McRegion reg;
+    int rc = daemon_->backend()->mc_create(allocs, &reg);
+    if (rc != proto::kOk) {
+      // Remember the failure so that it is not retried on every collective.
+      McRegion none;
+      c.mc_cache[key] = none;
+      return rc;
+    }
+    LOG_INFO("comm %u: multicast region of %zu bytes bound for %d ranks", c.id, reg.size, c.nranks);
+    it = c.mc_cache.emplace(key, reg).first;
+  }
+  const McRegion& reg = it->second;
+  if (!reg.handle) return proto::kErrUnsupported;
+  if (off + bytes > reg.size) return proto::kErrUnsupported;
+  for (int r = 0; r < c.nranks; r++) out_va[r] = reg.va[r];
+  return proto::kOk;
+}
+
+bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
+  auto fail = [&](int status) {
+    s.status = status;
+    s.state.store(kSlotFailed, std::memory_order_release);
+    return false;
+  };
+  const CollOp& o0 = s.ops[0];
+  for (int r = 0; r < c.nranks; r++)
+    if (!s.ops[r].valid) return fail(s.ops[r].status ? s.ops[r].status : proto::kErrInvalidArgument);
+  for (int r = 1; r < c.nranks; r++) {
+    const CollOp& o = s.ops[r];
+    if (o.kind != o0.kind || o.count != o0.count || (o0.kind == kAllReduce && (o.dtype != o0.dtype || o.op != o0.op)))
+      return fail(proto::kErrMismatch);
+  }
+  Backend* be = daemon_->backend();
+  const bool host_backend = be->kind() == proto::kBackendHost;
+  PlanInput in;
+  in.kind = o0.kind;
+  in.nranks = c.nranks;
+  in.count = o0.count;
+  in.dtype = o0.kind == kAllReduce ? o0.dtype : kUint8;
+  in.op = o0.kind == kAllReduce ? o0.op : kSum;
+  in.emulated = c.emulated;
+  in.host_staged = c.host_staged;
+  in.fifo_slot_bytes = c.fifo_slot_bytes;
+  uint64_t bits = o0.kind == kAllGather ? o0.count : 0;
+  bool same_off = true, all_vmm = !host_backend;
+  int req = o0.variant_req;
+  for (int r = 0; r < c.nranks; r++) {
+    const CollOp& o = s.ops[r];
+    bits |= o.send_va | o.recv_va;
+    if (o0.kind == kAllReduce) in.in_place |= o.send_va == o.recv_va;
+    else in.in_place |= o.send_va == o.recv_va + (uint64_t)r * o.count;
+    same_off &= o.send_off == o0.send_off && o.recv_off == o0.recv_off;
+    if (o.variant_req != req) req = kAuto;
+  }
+  in.aligned16 = (bits & 15u) == 0;
+  in.p2p_possible = true;
+  for (int a = 0; a < c.nranks && in.p2p_possible; a++)
+    for (int b = 0; b < c.nranks; b++)
+      if (!be->peer_access(c.devices[a], c.devices[b])) { in.p2p_possible = false; break; }
+  in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged &&
+                     all_vmm && same_off && c.nranks >= 2;
+  {
+    std::lock_guard<std::mutex> g(c.cfg_mu);
+    const int cfg_variant = o0.kind == kAllReduce ? c.ar_variant : c.ag_variant;
+    in.requested_variant = req != kAuto ? req : cfg_variant;
+    in.requested_ctas = c.ctas_override;
+    in.ring_channels = c.channel_count;
+    // The ring order is frozen here, once for all ranks, so that a reconfiguration
+    // arriving between two ranks' launches cannot split the collective.
+    for (int ch = 0; ch < kMaxRingChannels; ch++) {
+      const std::vector<int>& ring = c.rings[(size_t)ch % c.rings.size()];
+      for (int i = 0; i < c.nranks; i++) s.ring[ch][i] = (int8_t)ring[(size_t)i];
+    }
+  }
+  const uint64_t now = monotonic_us();
+  in.cta_cap = daemon_->qos().cta_cap(c.id, now);
+
+  Plan plan = daemon_->planner().plan(in);
+  for (int attempt = 0; attempt < 3 && plan.status == proto::kOk; attempt++) {
+    bool redo = false;
+    if (plan.needs_mc_send && ensure_mc(c, s, false, s.mc_send) != proto::kOk) redo = true;
+    if (!redo && plan.needs_mc_recv && ensure_mc(c, s, true, s.mc_recv) != proto::kOk) redo = true;
+    if (redo) {
+      in.nvls_possible = false;
+      plan = daemon_->planner().plan(in);
+      continue;
+    }
+    if (!be->variant_supported(plan.variant, in.dtype, in.op)) {
+      if (in.requested_variant == plan.variant) in.requested_variant = kAuto;
+      in.nvls_possible = false;
+      Plan alt = daemon_->planner().plan(in);
+      if (alt.variant == plan.variant) { plan.status = proto::kErrUnsupported; break; }
+      plan = alt;
+      continue;
+    }
+    break;
+  }
+  if (plan.status != proto::kOk) return fail(plan.status);
+  if (!plan.note.empty()) LOG_DEBUG("comm %u seq %llu: %s", c.id, (unsigned long long)seq, plan.note.c_str());
+
+  // Ring variants are limited by the FIFO space that exists per rank.
+  if (variant_is_ring(plan.variant)) {
+    const int fifo_channels = (int)(c.ranks[0]->fifo_bytes / (c.fifo_slot_bytes * kRingSlots));
+    if (fifo_channels < 1) return fail(proto::kErrUnsupported);
+    plan.dims.ctas = std::min(plan.dims.ctas, fifo_channels);
+  }
+  if (c.emulated && !host_backend) {
+    int fit = be->max_group_ctas(plan.variant, in.dtype, in.op, plan.dims.threads, c.nranks);
+    if (fit < 1) return fail(proto::kErrUnsupported);
+    plan.dims.ctas = std::min(plan.dims.ctas, fit);
+  }
+
+  // Time slices (all-reduce through non-ring variants only: each slice is an
+  // independent collective over a sub-range).
+  s.nslices = 1;
+  s.slice_count = o0.count;
+  const uint64_t slice_bytes = daemon_->qos().slice_bytes(c.id, now);
+  if (slice_bytes && o0.kind == kAllReduce && !variant_is_ring(plan.variant) && plan.bytes > slice_bytes &&
+      plan.variant != kLocalCopy) {
+    const uint64_t esz = (uint64_t)dtype_size(o0.dtype);
+    uint64_t n = std::min<uint64_t>((plan.bytes + slice_bytes - 1) / slice_bytes, 64);
+    uint64_t per = (o0.count + n - 1) / n;
+    const uint64_t quantum = 256 / esz;   // keeps every slice start 256-byte aligned
+    per = (per + quantum - 1) / quantum * quantum;
+    s.slice_count = per;
+    s.nslices = (int)((o0.count + per - 1) / per);
+  }
+  s.epoch_base = c.barrier_epoch;
+  c.barrier_epoch += 2u * (uint32_t)s.nslices;
+  s.ticket_base = c.ticket + 1;
+  c.ticket += (uint64_t)s.nslices;
+  if (variant_is_ring(plan.variant)) {
+    const int esz = o0.kind == kAllReduce ? dtype_size(o0.dtype) : 1;
+    const uint64_t steps = ring_steps_per_channel(o0.kind, o0.count, esz, c.nranks, plan.dims.ctas, c.fifo_slot_bytes);
+    for (int ch = 0; ch < kMaxRingChannels; ch++) s.ring_step_base[ch] = c.ring_steps[ch];
+    for (int ch = 0; ch < plan.dims.ctas; ch++) c.ring_steps[ch] += steps;
+  }
+  s.plan = plan;
+  s.status = proto::kOk;
+  s.t_ready_us = now;
+  s.admitted_slices.store(0, std::memory_order_relaxed);
+  s.group_launch.store(0, std::memory_order_relaxed);
+  c.planned.fetch_add(1);
+  c.last_variant.store((uint32_t)plan.variant);
+  c.last_ctas.store((uint32_t)plan.dims.ctas);
+  daemon_->qos().note_waiting(c.id, now);
+  s.state.store(kSlotPlanned, std::memory_order_release);
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// (4): admission
+// ---------------------------------------------------------------------------
+bool ProxyEngine::admit_slice(Communicator& c, CollSlot& s, int slice) {
+  if (s.admitted_slices.load(std::memory_order_acquire) > slice) return true;
+  std::lock_guard<std::mutex> g(c.admit_mu);
+  if (s.admitted_slices.load(std::memory_order_acquire) > slice) return true;
+  const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
+  QosDecision d = daemon_->qos().admit(c.id, bytes, monotonic_us(), wall_us());
+  if (d != kQosAdmit) return false;
+  s.admitted_slices.store(slice + 1, std::memory_order_release);
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// (5): launch
+// ---------------------------------------------------------------------------
+void ProxyEngine::fill_args(Communicator& c, CollSlot& s, int rank, int slice, CollArgs* out) {
+  CollArgs& a = *out;
+  memset(&a, 0, sizeof a);
+  const CollOp& o0 = s.ops[0];
+  const bool group = c.emulated || daemon_->backend()->kind() == proto::kBackendHost;
+  a.rank = rank;
+  a.nranks = c.nranks;
+  a.emulated = group ? 1 : 0;
+  a.dtype = o0.kind == kAllReduce ? o0.dtype : kUint8;
+  a.op = o0.kind == kAllReduce ? o0.op : kSum;
+  a.variant = s.plan.variant;
+  const uint64_t esz = o0.kind == kAllReduce ? (uint64_t)dtype_size(o0.dtype) : 1;
+  uint64_t first = 0, count = o0.count;
+  if (s.nslices > 1) {
+    first = (uint64_t)slice * s.slice_count;
+    count = std::min<uint64_t>(s.slice_count, o0.count - first);
+  }
+  const uint64_t off = first * esz;
+  a.count = count;
+  a.seq = s.ticket_base + (uint64_t)slice;
+  a.scale = o0.op == kSumPostDiv ? 1.0f / (float)c.nranks : o0.scale;
+  a.epoch = s.epoch_base + 2u * (uint32_t)slice;
+  a.timeout_ns = daemon_->timeout_ns();
+  a.trace = daemon_->tracer().enabled() ? 1 : 0;
+  for (int r = 0; r < c.nranks; r++) {
+    a.send[r] = (const void*)(s.ops[r].send_va + off);
+    a.recv[r] = (void*)(s.ops[r].recv_va + off);
+    a.pad[r] = c.ranks[(size_t)r]->pad;
+    a.status[r] = c.ranks[(size_t)r]->status;
+    a.fifo[r] = c.ranks[(size_t)r]->fifo;
+  }
+  if (s.plan.needs_mc_send) a.mc_send = (const void*)(s.mc_send[rank] + s.ops[rank].send_off + off);
+  if (s.plan.needs_mc_recv) a.mc_recv = (void*)(s.mc_recv[rank] + s.ops[rank].recv_off + off);
+  a.fifo_slot_bytes = c.fifo_slot_bytes;
+  memcpy(a.ring, s.ring, sizeof a.ring);
+  for (int ch = 0; ch < kMaxRingChannels; ch++) a.ring_step_base[ch] = s.ring_step_base[ch];
+}
+
+bool ProxyEngine::launch_slices(RankState& rs, CollSlot& s, uint64_t seq) {
+  Communicator& c = *rs.comm;
+  Backend* be = daemon_->backend();
+  const CollOp& op = s.ops[rs.rank];
+  while (rs.next_slice < s.nslices) {
+    if (!admit_slice(c, s, rs.next_slice)) return false;
+    if (rs.next_slice == 0 && op.user_event) be->stream_wait_event(rs.device, rs.stream, op.user_event);
+    CollArgs a;
+    fill_args(c, s, rs.rank, rs.next_slice, &a);
+    int rc = be->launch(rs.device, op.kind, a, s.plan.dims, rs.stream);
+    if (rc != proto::kOk) {
+      c.async_error.store(rc);
+      c.state.store(kCommError);
+      return true;   // the request completes with the communicator's error
+    }
+    if (rs.rank == 0) {
+      const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
+      rs.inflight.push_back({a.seq, bytes});
+    }
+    rs.next_slice++;
+  }
+  be->event_record(rs.device, rs.backend_event, rs.stream);
+  (void)seq;
+  return true;
+}
+
+// Emulated communicators (all ranks on one GPU) and the host backend run every rank
+// in one launch. Rank 0's proxy issues it; the other ranks wait for it.
+bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
+  (void)seq;
+  RankState& r0 = *c.ranks[0];
+  Backend* be = daemon_->backend();
+  while (r0.next_slice < s.nslices) {
+    if (!admit_slice(c, s, r0.next_slice)) return false;
+    if (r0.next_slice == 0) {
+      for (int r = 0; r < c.nranks; r++)
+        if (s.ops[r].user_event) be->stream_wait_event(r0.device, c.group_stream, s.ops[r].user_event);
+    }
+    CollArgs a;
+    fill_args(c, s, 0, r0.next_slice, &a);
+    int rc = be->launch(r0.device, s.ops[0].kind, a, s.plan.dims, c.group_stream);
+    if (rc != proto::kOk) {
+      c.async_error.store(rc);
+      c.state.store(kCommError);
+      break;
+    }
+    const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
+    r0.inflight.push_back({a.seq, bytes});
+    r0.next_slice++;
+  }
+  for (int r = 0; r < c.nranks; r++)
+    be->event_record(c.ranks[(size_t)r]->device, c.ranks[(size_t)r]->backend_event, c.group_stream);
+  s.group_launch.store(2, std::memory_order_release);
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// (6): completion
+// ---------------------------------------------------------------------------
+bool ProxyEngine::complete_request(RankState& rs, CollSlot& s, uint64_t seq, int status) {
+  proto::WorkCompletion wc;
+  memset(&wc, 0, sizeof wc);
+  wc.kind = (uint32_t)s.ops[rs.rank].kind;
+  wc.status = status;
+  wc.user_seq = s.ops[rs.rank].user_seq;
+  wc.variant = (uint32_t)s.plan.variant;
+  wc.ctas = (uint32_t)s.plan.dims.ctas;
+  wc.comm_seq = seq;
+  if (!rs.cq.try_push(&wc)) {
+    rs.pending_wc = wc;
+    rs.have_pending_wc = true;
+  }
+  return true;
+}
+
+void ProxyEngine::finish_slot(Communicator& c, CollSlot& s, uint64_t seq) {
+  if (s.finished.fetch_add(1, std::memory_order_acq_rel) + 1 == c.nranks) {
+    s.arrived.store(0, std::memory_order_relaxed);
+    s.finished.store(0, std::memory_order_relaxed);
+    s.admitted_slices.store(0, std::memory_order_relaxed);
+    s.group_launch.store(0, std::memory_order_relaxed);
+    s.state.store(kSlotCollecting, std::memory_order_relaxed);
+    s.seq.store(seq + kCollSlots, std::memory_order_release);
+  }
+}
+
+bool ProxyEngine::advance(RankState& rs) {
+  Communicator& c = *rs.comm;
+  Backend* be = daemon_->backend();
+  const bool group = c.emulated || be->kind() == proto::kBackendHost;
+  bool any = false;
+  while (rs.next_launch_seq < rs.next_post_seq) {
+    if (rs.have_pending_wc) {
+      if (!rs.cq.try_push(&rs.pending_wc)) break;
+      rs.have_pending_wc = false;
+    }
+    const uint64_t seq = rs.next_launch_seq;
+    CollSlot& s = c.slot(seq);
+    if (c.state.load(std::memory_order_acquire) == kCommError) {
+      // A failed communicator never launches again; what was posted completes in error.
+      int err = c.async_error.load();
+      complete_request(rs, s, seq, err ? err : proto::kErrAborted);
+      rs.next_launch_seq++;
+      rs.next_slice = 0;
+      any = true;
+      continue;
+    }
+    int st = s.state.load(std::memory_order_acquire);
+    if (st == kSlotCollecting) break;
+    if (st == kSlotCollected) {
+      if (c.paused.load(std::memory_order_acquire)) break;
+      int expect = kSlotCollected;
+      if (!s.state.compare_exchange_strong(expect, kSlotPlanning, std::memory_order_acq_rel)) break;
+      plan_slot(c, s, seq);
+      st = s.state.load(std::memory_order_acquire);
+      any = true;
+    }
+    if (st == kSlotPlanning) break;
+    int status = proto::kOk;
+    if (st == kSlotFailed) {
+      status = s.status;
+    } else if (group) {
+      if (s.group_launch.load(std::memory_order_acquire) != 2) {
+        if (rs.rank != 0) break;
+        if (!launch_group(c, s, seq)) break;
+      }
+      if (c.state.load() == kCommError) status = c.async_error.load();
+    } else {
+      if (!launch_slices(rs, s, seq)) break;
+      if (c.state.load() == kCommError) status = c.async_error.load();
+    }
+    if (daemon_->tracer().enabled() && st == kSlotPlanned) {
+      TraceEvent ev;
+      ev.comm_id = c.id; ev.rank = rs.rank; ev.device = rs.device; ev.seq = seq;
+      ev.kind = s.ops[rs.rank].kind; ev.variant = s.plan.variant; ev.ctas = s.plan.dims.ctas;
+      ev.slices = s.nslices; ev.bytes = s.plan.bytes;
+      ev.t_post_us = s.ops[rs.rank].t_post_us; ev.t_ready_us = s.t_ready_us; ev.t_launch_us = monotonic_us();
+      // Device stamps belong to the most recent finished kernel of this rank.
+      if (rs.status) { ev.dev_start_ns = rs.status->start_ns; ev.dev_end_ns = rs.status->end_ns; }
+      daemon_->tracer().record(ev);
+    }
+    complete_request(rs, s, seq, status);
+    finish_slot(c, s, seq);
+    rs.next_launch_seq++;
+    rs.next_slice = 0;
+    any = true;
+  }
+  return any;
+}
+
+// Completion accounting for QoS and device error pick-up.
+void ProxyEngine::housekeeping(RankState& rs) {
+  Communicator& c = *rs.comm;
+  if (!rs.status) return;
+  if (rs.rank == 0) {
+    const uint64_t done = *(volatile uint64_t*)&rs.status->done_seq;
+    while (!rs.inflight.empty() && rs.inflight.front().ticket <= done) {
+      daemon_->qos().complete(c.id, rs.inflight.front().bytes);
+      c.completed.fetch_add(1);
+      rs.inflight.pop_front();
+    }
+  }
+  const uint32_t err = *(volatile uint32_t*)&rs.status->error;
+  if (err != kDevOk && c.device_error.load() == kDevOk) {
+    c.device_error.store(err);
+    c.async_error.store(err == kDevAborted ? proto::kErrAborted : proto::kErrTimeout);
+    c.state.store(kCommError);
+    LOG_ERROR("comm %u rank %d: kernel reported %s (detail %u)", c.id, rs.rank,
+              err == kDevAborted ? "abort" : "a wait that ran out", rs.status->error_peer);
+    // Let the other ranks' kernels give up at once instead of waiting out their bound.
+    for (auto& r : c.ranks)
+      if (r && r->status) r->status->abort = 1;
+    // Nothing is in flight for QoS purposes any more.
+    if (rs.rank == 0) {
+      while (!rs.inflight.empty()) { daemon_->qos().complete(c.id, rs.inflight.front().bytes); rs.inflight.pop_front(); }
+    }
+  }
+}
+
+}  // namespace mccs

@@ -1,0 +1,150 @@
+/* libmccs: client API of the managed collective communication service.
+ *
+ * An application links against (or dlopens) libmccs.so and talks to the per-host
+ * daemon `mccsd`. The daemon owns the GPUs' communication: it allocates the device
+ * buffers (the application maps them), keeps the communicators, and launches the
+ * collective kernels on its own streams. Ordering against the application's CUDA
+ * streams is done with two interprocess events per (stream, communicator): the
+ * library records "submitted" on the caller's stream before it posts the request,
+ * and makes the caller's stream wait for the daemon's "done" event afterwards, so a
+ * collective call never blocks the GPU timeline of the host thread.
+ *
+ * This is the C form of the reference's Rust API (src/libmccs/src/lib.rs:23-27):
+ *   cuda_malloc            -> mccsMalloc          (src/libmccs/src/memory.rs:12)
+ *   init_communicator_rank -> mccsCommInitRank    (src/libmccs/src/communicator.rs:15)
+ *   register_stream        -> mccsRegisterStream  (src/libmccs/src/communicator.rs:47)
+ *   all_gather             -> mccsAllGather       (src/libmccs/src/collectives.rs:15)
+ *   all_reduce             -> mccsAllReduce       (src/libmccs/src/collectives.rs:75)
+ * plus what the reference leaves out: mccsFree (its cuda_free is unimplemented),
+ * communicator destruction, grouped submission, error queries, a C ABI.
+ *
+ * Environment: MCCS_CONTROL (path of the daemon's control socket, overrides
+ * MCCS_PREFIX + "/control.sock"), MCCS_PREFIX (default /tmp/mccs-$USER),
+ * MCCS_DEVICE_AFFINITY (advertised to the daemon), MCCS_WC_TIMEOUT_MS.
+ *
+ * Threading: one communicator (and one CUDA stream used with it) belongs to one
+ * host thread at a time, as in the reference (src/ipc/mccs/src/command.rs:96-98).
+ */
+#ifndef MCCS_H_
+#define MCCS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mccsComm* mccsComm_t;
+typedef void* mccsStream_t; /* a cudaStream_t / CUstream (NULL = legacy default stream) */
+
+typedef enum {
+  mccsSuccess = 0,
+  mccsInvalidArgument = -1,
+  mccsOutOfMemory = -2,
+  mccsDeviceError = -3,
+  mccsProtocolError = -4,
+  mccsNotFound = -5,
+  mccsTimeout = -6,
+  mccsAborted = -7,
+  mccsMismatch = -8,
+  mccsUnsupported = -9,
+  mccsPeerLost = -10,
+  mccsInternalError = -11,
+  mccsNotConnected = -12
+} mccsResult_t;
+
+/* Same numbering as the kernels' element types. The reference API exposes only
+ * Float16 and Int32 (src/ipc/mccs/src/command.rs:26-31). */
+typedef enum {
+  mccsInt8 = 0, mccsUint8 = 1, mccsInt32 = 2, mccsUint32 = 3, mccsInt64 = 4, mccsUint64 = 5,
+  mccsFloat16 = 6, mccsFloat32 = 7, mccsFloat64 = 8, mccsBfloat16 = 9
+} mccsDataType_t;
+
+/* src/ipc/mccs/src/command.rs:33-42. mccsSumPostDiv divides by the communicator
+ * size (an average); mccsPreMulSum multiplies every input by `scale` first. */
+typedef enum {
+  mccsSum = 0, mccsProd = 1, mccsMax = 2, mccsMin = 3, mccsPreMulSum = 4, mccsSumPostDiv = 5
+} mccsRedOp_t;
+
+/* Kernel variant request (0 lets the service decide). */
+typedef enum {
+  mccsAlgoAuto = 0, mccsAlgoArOneShot = 1, mccsAlgoArTwoShot = 2, mccsAlgoArNvlsOneShot = 3,
+  mccsAlgoArNvlsTwoShot = 4, mccsAlgoArRing = 5, mccsAlgoAgPull = 6, mccsAlgoAgPush = 7,
+  mccsAlgoAgNvls = 8, mccsAlgoAgRing = 9
+} mccsAlgo_t;
+
+/* Connects to the daemon. Optional: every other call connects on first use with
+ * the path from the environment. */
+mccsResult_t mccsInit(const char* control_socket_path);
+mccsResult_t mccsFinalize(void);
+/* 0: host backend (no GPU, buffers are host shared memory), 1: CUDA. */
+int mccsBackendKind(void);
+int mccsDeviceCount(void);
+
+/* Device memory owned by the daemon and mapped here. Only such memory can be
+ * passed to collectives. */
+mccsResult_t mccsMalloc(void** ptr, int device, size_t size);
+mccsResult_t mccsFree(void* ptr);
+/* Which allocation a pointer belongs to (any address inside it). */
+mccsResult_t mccsMemInfo(const void* ptr, uint64_t* mem_id, uint64_t* offset, uint64_t* alloc_size);
+
+/* Blocks until all `nranks` ranks of `unique_id` have joined. `root_addr` is accepted
+ * for source compatibility with the reference and ignored inside one box. */
+mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, int nranks, int device,
+                              const char* root_addr);
+mccsResult_t mccsCommDestroy(mccsComm_t comm);
+mccsResult_t mccsCommRank(mccsComm_t comm, int* rank);
+mccsResult_t mccsCommSize(mccsComm_t comm, int* nranks);
+uint64_t mccsCommHandle(mccsComm_t comm); /* (unique_id << 32) + rank */
+
+/* Optional: streams are registered on first use. */
+mccsResult_t mccsRegisterStream(int device, mccsStream_t stream);
+
+/* count: elements. In-place when send == recv. */
+mccsResult_t mccsAllReduce(mccsComm_t comm, const void* send, void* recv, size_t count,
+                           mccsDataType_t dtype, mccsRedOp_t op, mccsStream_t stream);
+mccsResult_t mccsAllReduceEx(mccsComm_t comm, const void* send, void* recv, size_t count,
+                             mccsDataType_t dtype, mccsRedOp_t op, float scale, mccsAlgo_t algo,
+                             mccsStream_t stream);
+/* bytes: per rank. recv holds nranks*bytes; in-place when send == recv + rank*bytes. */
+mccsResult_t mccsAllGather(mccsComm_t comm, const void* send, void* recv, size_t bytes,
+                           mccsStream_t stream);
+mccsResult_t mccsAllGatherEx(mccsComm_t comm, const void* send, void* recv, size_t bytes,
+                             mccsAlgo_t algo, mccsStream_t stream);
+
+/* Calls between GroupStart and GroupEnd are submitted back to back and completed
+ * together at GroupEnd (the protocol's GroupCall, src/ipc/mccs/src/command.rs:93-95). */
+mccsResult_t mccsGroupStart(void);
+mccsResult_t mccsGroupEnd(void);
+
+typedef struct {
+  int32_t async_error;     /* mccsResult_t, sticky */
+  uint32_t device_error;   /* kernel-reported status, 0 = none */
+  uint64_t launched;
+  uint64_t completed;
+  uint32_t last_variant;   /* mccsAlgo_t the service chose for the last collective */
+  uint32_t last_ctas;
+  uint64_t config_epoch;   /* number of live reconfigurations applied */
+} mccsCommInfo_t;
+mccsResult_t mccsCommQuery(mccsComm_t comm, mccsCommInfo_t* info);
+mccsResult_t mccsCommGetAsyncError(mccsComm_t comm, mccsResult_t* async_error);
+/* Variant and CTA count reported with the last completed request of this rank. */
+mccsResult_t mccsCommLastPlan(mccsComm_t comm, uint32_t* variant, uint32_t* ctas);
+
+const char* mccsGetErrorString(mccsResult_t r);
+const char* mccsAlgoName(int algo);
+
+/* Admin client: sends one framed request (type 1 = reconfiguration, 2 = query) with a
+ * JSON body to a daemon's admin port and copies the JSON reply into `reply`. */
+mccsResult_t mccsAdminRequest(const char* host, int port, int type, const char* json_body, char* reply,
+                              size_t reply_cap);
+
+/* Hooks for torch.cuda.memory.CUDAPluggableAllocator. */
+void* mccs_torch_malloc(size_t size, int device, void* stream);
+void mccs_torch_free(void* ptr, size_t size, int device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MCCS_H_ */

@@ -1,0 +1,868 @@
+// libmccs: the client shim. See csrc/include/mccs.h for the API and its map to the
+// reference's Rust crate (src/libmccs/src/{lib,memory,communicator,collectives}.rs).
+//
+// The library uses the CUDA *driver* API only, loaded with dlopen at first need, so
+// it has no link-time CUDA dependency, loads on machines without a GPU (the daemon's
+// host backend) and never creates a second CUDA runtime inside a PyTorch process.
+#include "../include/mccs.h"
+
+#include <arpa/inet.h>
+#include <cuda.h>
+#include <dlfcn.h>
+#include <errno.h>
+#include <netdb.h>
+#include <poll.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/socket.h>
+#include <time.h>
+#include <unistd.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../common/log.h"
+#include "../common/protocol.h"
+#include "../common/value.h"
+#include "../ipc/shm_ring.h"
+#include "../ipc/uds.h"
+#include "../kernels/dev_types.h"
+
+using namespace mccs;
+
+namespace {
+
+// ------------------------------------------------------------------ driver API
+#define DRV_FN(name) decltype(&name) name##_ = nullptr
+struct Driver {
+  void* lib = nullptr;
+  bool tried = false, ok = false;
+  DRV_FN(cuInit);
+  DRV_FN(cuDeviceGet);
+  DRV_FN(cuCtxGetCurrent);
+  DRV_FN(cuCtxSetCurrent);
+  DRV_FN(cuCtxGetDevice);
+  DRV_FN(cuDevicePrimaryCtxRetain);
+  DRV_FN(cuEventCreate);
+  DRV_FN(cuEventDestroy);
+  DRV_FN(cuEventRecord);
+  DRV_FN(cuStreamWaitEvent);
+  DRV_FN(cuIpcGetEventHandle);
+  DRV_FN(cuIpcOpenEventHandle);
+  DRV_FN(cuIpcOpenMemHandle);
+  DRV_FN(cuIpcCloseMemHandle);
+  DRV_FN(cuMemImportFromShareableHandle);
+  DRV_FN(cuMemAddressReserve);
+  DRV_FN(cuMemAddressFree);
+  DRV_FN(cuMemMap);
+  DRV_FN(cuMemUnmap);
+  DRV_FN(cuMemSetAccess);
+  DRV_FN(cuMemRelease);
+  DRV_FN(cuGetErrorString);
+};
+Driver g_drv;
+
+template <typename Fn> bool sym(void* lib, const char* name, Fn* out) {
+  void* p = dlsym(lib, name);
+  if (!p) return false;
+  *out = reinterpret_cast<Fn>(p);
+  return true;
+}
+
+bool load_driver() {
+  if (g_drv.tried) return g_drv.ok;
+  g_drv.tried = true;
+  g_drv.lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+  if (!g_drv.lib) return false;
+  void* l = g_drv.lib;
+  // Versioned names are what cuda.h's macros map the plain names to.
+  g_drv.ok = sym(l, "cuInit", &g_drv.cuInit_) && sym(l, "cuDeviceGet", &g_drv.cuDeviceGet_) &&
+             sym(l, "cuCtxGetCurrent", &g_drv.cuCtxGetCurrent_) && sym(l, "cuCtxSetCurrent", &g_drv.cuCtxSetCurrent_) &&
+             sym(l, "cuCtxGetDevice", &g_drv.cuCtxGetDevice_) &&
+             sym(l, "cuDevicePrimaryCtxRetain", &g_drv.cuDevicePrimaryCtxRetain_) &&
+             sym(l, "cuEventCreate", &g_drv.cuEventCreate_) && sym(l, "cuEventDestroy_v2", &g_drv.cuEventDestroy_) &&
+             sym(l, "cuEventRecord", &g_drv.cuEventRecord_) && sym(l, "cuStreamWaitEvent", &g_drv.cuStreamWaitEvent_) &&
+             sym(l, "cuIpcGetEventHandle", &g_drv.cuIpcGetEventHandle_) &&
+             sym(l, "cuIpcOpenEventHandle", &g_drv.cuIpcOpenEventHandle_) &&
+             sym(l, "cuIpcOpenMemHandle_v2", &g_drv.cuIpcOpenMemHandle_) &&
+             sym(l, "cuIpcCloseMemHandle", &g_drv.cuIpcCloseMemHandle_) &&
+             sym(l, "cuMemImportFromShareableHandle", &g_drv.cuMemImportFromShareableHandle_) &&
+             sym(l, "cuMemAddressReserve", &g_drv.cuMemAddressReserve_) &&
+             sym(l, "cuMemAddressFree", &g_drv.cuMemAddressFree_) && sym(l, "cuMemMap", &g_drv.cuMemMap_) &&
+             sym(l, "cuMemUnmap", &g_drv.cuMemUnmap_) && sym(l, "cuMemSetAccess", &g_drv.cuMemSetAccess_) &&
+             sym(l, "cuMemRelease", &g_drv.cuMemRelease_) && sym(l, "cuGetErrorString", &g_drv.cuGetErrorString_);
+  if (g_drv.ok && g_drv.cuInit_(0) != CUDA_SUCCESS) g_drv.ok = false;
+  return g_drv.ok;
+}
+
+const char* cu_err(CUresult r) {
+  const char* s = nullptr;
+  if (g_drv.cuGetErrorString_) g_drv.cuGetErrorString_(r, &s);
+  return s ? s : "unknown CUDA error";
+}
+
+// Makes the primary context of `device` current for the scope (and restores what
+// was current), so that the shim works from threads that have not touched CUDA yet
+// and never disturbs the caller's current device.
+struct CtxScope {
+  CUcontext saved = nullptr;
+  bool switched = false;
+  bool ok = false;
+  explicit CtxScope(int device) {
+    if (!load_driver()) return;
+    CUcontext cur = nullptr;
+    g_drv.cuCtxGetCurrent_(&cur);
+    if (cur) {
+      CUdevice d;
+      if (g_drv.cuCtxGetDevice_(&d) == CUDA_SUCCESS && (int)d == device) { ok = true; return; }
+    }
+    CUdevice dev;
+    if (g_drv.cuDeviceGet_(&dev, device) != CUDA_SUCCESS) return;
+    CUcontext primary = nullptr;
+    if (g_drv.cuDevicePrimaryCtxRetain_(&primary, dev) != CUDA_SUCCESS) return;
+    saved = cur;
+    if (g_drv.cuCtxSetCurrent_(primary) != CUDA_SUCCESS) return;
+    switched = true;
+    ok = true;
+  }
+  ~CtxScope() { if (switched) g_drv.cuCtxSetCurrent_(saved); }
+};
+
+// ------------------------------------------------------------------ state
+struct MemRec {
+  uint64_t mem_id = 0;
+  uint64_t base = 0;
+  size_t size = 0;
+  int device = 0;
+  uint32_t share_kind = 0;
+  uint64_t vmm_handle = 0;
+};
+
+struct StreamRec {
+  uint64_t stream_id = 0;
+  CUevent event = nullptr;   // "submitted" marker recorded on the user's stream
+  int device = 0;
+};
+
+struct Context {
+  std::mutex mu;
+  int fd = -1;
+  bool connected = false;
+  uint32_t backend = 0;
+  int daemon_pid = 0;
+  bool same_process = false;
+  int num_devices = 0;
+  uint64_t session_id = 0;
+  uint32_t next_req = 1;
+  std::map<uint64_t, MemRec> mem;                       // base -> record
+  std::map<std::pair<int, uint64_t>, StreamRec> streams;   // (device, stream) -> record
+  uint64_t wc_timeout_ms = 300000;
+};
+Context g_ctx;
+
+thread_local int g_group_depth = 0;
+struct GroupItem { struct mccsComm* comm; mccsStream_t stream; };
+thread_local std::vector<GroupItem> g_group_items;
+
+}  // namespace
+
+struct mccsComm {
+  uint64_t handle = 0;
+  uint32_t id = 0;
+  int rank = 0, nranks = 0, device = 0;
+  void* dp_mem = nullptr;
+  size_t dp_bytes = 0;
+  ipc::Ring wq, cq;
+  CUevent backend_event = nullptr;
+  bool event_owned = false;
+  uint64_t next_user_seq = 1;
+  uint64_t outstanding = 0;      // requests posted whose completion was not read yet
+  uint32_t last_variant = 0, last_ctas = 0;
+  int sticky_error = 0;
+};
+
+namespace {
+
+std::string default_control_path() {
+  const char* direct = getenv("MCCS_CONTROL");
+  if (direct && direct[0] == '/') return direct;
+  const char* prefix = getenv("MCCS_PREFIX");
+  std::string p = prefix ? prefix : "/tmp/mccs-${USER}";
+  p = expand_env(p);
+  if (!p.empty() && p.back() == '/') p.pop_back();
+  return p + "/" + (direct ? direct : "control.sock");
+}
+
+// Request/reply on the control connection. Caller holds g_ctx.mu.
+mccsResult_t roundtrip(proto::AnyMsg& m, size_t len, uint32_t expect_type, std::vector<int>* fds, int timeout_ms) {
+  Context& c = g_ctx;
+  m.h.magic = proto::kMagic;
+  m.h.req_id = c.next_req++;
+  const uint32_t req = m.h.req_id;
+  ssize_t n = ipc::uds_send(c.fd, &m, len);
+  if (n < 0) return mccsProtocolError;
+  for (;;) {
+    int rc = ipc::wait_readable(c.fd, timeout_ms);
+    if (rc == 0) return mccsTimeout;
+    if (rc < 0) return mccsProtocolError;
+    proto::AnyMsg r;
+    n = ipc::uds_recv(c.fd, &r, sizeof r, fds);
+    if (n <= 0) { c.connected = false; return mccsNotConnected; }
+    if ((size_t)n < sizeof(proto::Header) || r.h.magic != proto::kMagic) return mccsProtocolError;
+    if (r.h.req_id != req || r.h.type != expect_type) continue;   // stale reply of an abandoned request
+    m = r;
+    return (mccsResult_t)r.h.status;
+  }
+}
+
+mccsResult_t ensure_connected_locked(const char* path) {
+  Context& c = g_ctx;
+  if (c.connected) return mccsSuccess;
+  std::string p = path && path[0] ? path : default_control_path();
+  int fd = -1;
+  // The daemon may still be starting: retry briefly.
+  for (int i = 0; i < 100; i++) {
+    fd = ipc::uds_connect(p);
+    if (fd >= 0) break;
+    usleep(50000);
+  }
+  if (fd < 0) {
+    LOG_ERROR("cannot connect to the mccs daemon at %s: %s", p.c_str(), strerror(-fd));
+    return mccsNotConnected;
+  }
+  c.fd = fd;
+  proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
+  m.h.type = proto::kHello;
+  m.hello.version = proto::kVersion;
+  m.hello.pid = (int)getpid();
+  const char* aff = getenv("MCCS_DEVICE_AFFINITY");
+  m.hello.device_affinity = aff ? atoi(aff) : -1;
+  const char* app = getenv("MCCS_APP_NAME");
+  snprintf(m.hello.app_name, sizeof m.hello.app_name, "%s", app ? app : program_invocation_short_name);
+  mccsResult_t r = roundtrip(m, sizeof(proto::Hello), proto::kWelcome, nullptr, 10000);
+  if (r != mccsSuccess) { close(fd); c.fd = -1; return r; }
+  c.backend = m.welcome.backend;
+  c.daemon_pid = m.welcome.daemon_pid;
+  c.same_process = c.daemon_pid == (int)getpid();
+  c.num_devices = (int)m.welcome.num_devices;
+  c.session_id = m.welcome.session_id;
+  const char* to = getenv("MCCS_WC_TIMEOUT_MS");
+  if (to) c.wc_timeout_ms = strtoull(to, nullptr, 10);
+  c.connected = true;
+  if (c.backend == proto::kBackendCuda && !load_driver()) {
+    LOG_ERROR("the daemon runs on CUDA but libcuda.so.1 cannot be loaded here");
+    return mccsDeviceError;
+  }
+  return mccsSuccess;
+}
+
+const MemRec* find_mem_locked(const void* ptr) {
+  const uint64_t a = (uint64_t)ptr;
+  auto it = g_ctx.mem.upper_bound(a);
+  if (it == g_ctx.mem.begin()) return nullptr;
+  --it;
+  if (a >= it->second.base + it->second.size) return nullptr;
+  return &it->second;
+}
+
+mccsResult_t register_stream_locked(int device, mccsStream_t stream, StreamRec** out) {
+  Context& c = g_ctx;
+  auto key = std::make_pair(device, (uint64_t)stream);
+  auto it = c.streams.find(key);
+  if (it != c.streams.end()) { *out = &it->second; return mccsSuccess; }
+  StreamRec rec;
+  rec.device = device;
+  proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
+  m.h.type = proto::kRegisterStream;
+  m.reg_stream.device = device;
+  m.reg_stream.stream = (uint64_t)stream;
+  if (c.backend == proto::kBackendCuda) {
+    CtxScope scope(device);
+    if (!scope.ok) return mccsDeviceError;
+    unsigned flags = CU_EVENT_DISABLE_TIMING | (c.same_process ? 0u : (unsigned)CU_EVENT_INTERPROCESS);
+    CUresult r = g_drv.cuEventCreate_(&rec.event, flags);
+    if (r != CUDA_SUCCESS) { LOG_ERROR("cuEventCreate: %s", cu_err(r)); return mccsDeviceError; }
+    if (c.same_process) {
+      m.reg_stream.event_raw = (uint64_t)rec.event;
+    } else {
+      CUipcEventHandle h;
+      r = g_drv.cuIpcGetEventHandle_(&h, rec.event);
+      if (r != CUDA_SUCCESS) { LOG_ERROR("cuIpcGetEventHandle: %s", cu_err(r)); return mccsDeviceError; }
+      static_assert(sizeof h == proto::kIpcHandleBytes, "IPC event handle size");
+      memcpy(m.reg_stream.event_handle, &h, sizeof h);
+    }
+  }
+  mccsResult_t r = roundtrip(m, sizeof(proto::RegisterStreamReq), proto::kRegisterStreamReply, nullptr, 30000);
+  if (r != mccsSuccess) return r;
+  rec.stream_id = m.reg_stream_reply.stream_id;
+  auto ins = c.streams.emplace(key, rec);
+  *out = &ins.first->second;
+  return mccsSuccess;
+}
+
+// Spins for the completion of the oldest outstanding request of `comm`.
+mccsResult_t wait_completion(mccsComm* comm, proto::WorkCompletion* wc) {
+  struct timespec t0;
+  clock_gettime(CLOCK_MONOTONIC, &t0);
+  uint64_t spins = 0;
+  while (!comm->cq.try_pop(wc)) {
+    if ((++spins & 0xfff) == 0) {
+      struct timespec t1;
+      clock_gettime(CLOCK_MONOTONIC, &t1);
+      uint64_t ms = (uint64_t)(t1.tv_sec - t0.tv_sec) * 1000 + (uint64_t)((t1.tv_nsec - t0.tv_nsec) / 1000000);
+      if (ms > g_ctx.wc_timeout_ms) return mccsTimeout;
+      // A dead daemon never completes anything: notice the closed control connection.
+      struct pollfd pf = {g_ctx.fd, 0, 0};
+      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+      if (spins > (1u << 22)) usleep(50);
+    }
+  }
+  comm->outstanding--;
+  comm->last_variant = wc->variant;
+  comm->last_ctas = wc->ctas;
+  if (wc->status != 0 && comm->sticky_error == 0) comm->sticky_error = wc->status;
+  return (mccsResult_t)wc->status;
+}
+
+mccsResult_t finish_on_stream(mccsComm* comm, mccsStream_t stream) {
+  if (g_ctx.backend != proto::kBackendCuda || !comm->backend_event) return mccsSuccess;
+  CtxScope scope(comm->device);
+  if (!scope.ok) return mccsDeviceError;
+  CUresult r = g_drv.cuStreamWaitEvent_((CUstream)stream, comm->backend_event, 0);
+  if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitEvent: %s", cu_err(r)); return mccsDeviceError; }
+  return mccsSuccess;
+}
+
+mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, void* recv, uint64_t send_bytes,
+                    uint64_t recv_bytes, mccsStream_t stream) {
+  if (!comm) return mccsInvalidArgument;
+  StreamRec* srec = nullptr;
+  {
+    std::lock_guard<std::mutex> g(g_ctx.mu);
+    if (!g_ctx.connected) return mccsNotConnected;
+    const MemRec* sm = find_mem_locked(send);
+    const MemRec* rm = find_mem_locked(recv);
+    if (!sm || !rm) {
+      LOG_ERROR("collective buffers must come from mccsMalloc (send %p, recv %p)", send, recv);
+      return mccsInvalidArgument;
+    }
+    wr.send_mem = sm->mem_id; wr.send_off = (uint64_t)send - sm->base;
+    wr.recv_mem = rm->mem_id; wr.recv_off = (uint64_t)recv - rm->base;
+    if (wr.send_off + send_bytes > sm->size || wr.recv_off + recv_bytes > rm->size) return mccsInvalidArgument;
+    mccsResult_t r = register_stream_locked(comm->device, stream, &srec);
+    if (r != mccsSuccess) return r;
+  }
+  wr.comm_handle = comm->handle;
+  wr.stream_id = srec->stream_id;
+  wr.user_seq = comm->next_user_seq++;
+  if (g_group_depth > 0) wr.flags |= proto::kWrGroupMore;
+  if (g_ctx.backend == proto::kBackendCuda) {
+    CtxScope scope(comm->device);
+    if (!scope.ok) return mccsDeviceError;
+    CUresult r = g_drv.cuEventRecord_(srec->event, (CUstream)stream);
+    if (r != CUDA_SUCCESS) { LOG_ERROR("cuEventRecord: %s", cu_err(r)); return mccsDeviceError; }
+  }
+  // Post. A full ring means completions are waiting to be read (grouped calls).
+  while (!comm->wq.try_push(&wr)) {
+    proto::WorkCompletion wc;
+    if (comm->outstanding > 0 && comm->cq.try_pop(&wc)) {
+      comm->outstanding--;
+      if (wc.status != 0 && comm->sticky_error == 0) comm->sticky_error = wc.status;
+    }
+  }
+  comm->outstanding++;
+  if (g_group_depth > 0) {
+    g_group_items.push_back({comm, stream});
+    return mccsSuccess;
+  }
+  proto::WorkCompletion wc;
+  mccsResult_t r = mccsSuccess;
+  while (comm->outstanding > 0) {
+    mccsResult_t one = wait_completion(comm, &wc);
+    if (one == mccsTimeout || one == mccsNotConnected) return one;
+    if (one != mccsSuccess) r = one;
+  }
+  if (r != mccsSuccess) return r;
+  return finish_on_stream(comm, stream);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Public API
+// ---------------------------------------------------------------------------
+extern "C" {
+
+mccsResult_t mccsInit(const char* control_socket_path) {
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  return ensure_connected_locked(control_socket_path);
+}
+
+mccsResult_t mccsFinalize(void) {
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  Context& c = g_ctx;
+  if (!c.connected) return mccsSuccess;
+  proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
+  m.h.magic = proto::kMagic;
+  m.h.type = proto::kGoodbye;
+  ipc::uds_send(c.fd, &m, sizeof(proto::Header));
+  close(c.fd);
+  c.fd = -1;
+  c.connected = false;
+  for (auto& kv : c.mem) {
+    const MemRec& r = kv.second;
+    if (r.share_kind == proto::kShareHostFd) munmap((void*)r.base, r.size);
+    else if (r.share_kind == proto::kShareVmmFd && g_drv.ok) {
+      CtxScope scope(r.device);
+      g_drv.cuMemUnmap_((CUdeviceptr)r.base, r.size);
+      g_drv.cuMemAddressFree_((CUdeviceptr)r.base, r.size);
+      g_drv.cuMemRelease_((CUmemGenericAllocationHandle)r.vmm_handle);
+    } else if (r.share_kind == proto::kShareCudaIpc && g_drv.ok) {
+      CtxScope scope(r.device);
+      g_drv.cuIpcCloseMemHandle_((CUdeviceptr)r.base);
+    }
+  }
+  c.mem.clear();
+  if (g_drv.ok)
+    for (auto& kv : c.streams)
+      if (kv.second.event) { CtxScope scope(kv.second.device); g_drv.cuEventDestroy_(kv.second.event); }
+  c.streams.clear();
+  return mccsSuccess;
+}
+
+int mccsBackendKind(void) {
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  if (ensure_connected_locked(nullptr) != mccsSuccess) return -1;
+  return (int)g_ctx.backend;
+}
+
+int mccsDeviceCount(void) {
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  if (ensure_connected_locked(nullptr) != mccsSuccess) return -1;
+  return g_ctx.num_devices;
+}
+
+mccsResult_t mccsMalloc(void** ptr, int device, size_t size) {
+  if (!ptr || size == 0) return mccsInvalidArgument;
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  mccsResult_t r = ensure_connected_locked(nullptr);
+  if (r != mccsSuccess) return r;
+  proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
+  m.h.type = proto::kMalloc;
+  m.malloc_req.device = device;
+  m.malloc_req.size = size;
+  std::vector<int> fds;
+  r = roundtrip(m, sizeof(proto::MallocReq), proto::kMallocReply, &fds, 60000);
+  auto close_fds = [&]() { for (int f : fds) close(f); };
+  if (r != mccsSuccess) { close_fds(); return r; }
+  MemRec rec;
+  rec.mem_id = m.malloc_reply.mem_id;
+  rec.size = m.malloc_reply.size;
+  rec.device = m.malloc_reply.device;
+  rec.share_kind = m.malloc_reply.share_kind;
+  mccsResult_t fail = mccsSuccess;
+  switch (rec.share_kind) {
+    case proto::kShareSameProcess:
+      rec.base = m.malloc_reply.daemon_va;
+      break;
+    case proto::kShareHostFd: {
+      if (fds.empty()) { fail = mccsProtocolError; break; }
+      void* p = mmap(nullptr, rec.size, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
+      if (p == MAP_FAILED) { fail = mccsOutOfMemory; break; }
+      rec.base = (uint64_t)p;
+      break;
+    }
+    case proto::kShareVmmFd: {
+      if (fds.empty()) { fail = mccsProtocolError; break; }
+      CtxScope scope(device);
+      if (!scope.ok) { fail = mccsDeviceError; break; }
+      CUmemGenericAllocationHandle h = 0;
+      CUresult cr = g_drv.cuMemImportFromShareableHandle_(&h, (void*)(uintptr_t)fds[0],
+                                                          CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+      if (cr != CUDA_SUCCESS) { LOG_ERROR("cuMemImportFromShareableHandle: %s", cu_err(cr)); fail = mccsDeviceError; break; }
+      CUdeviceptr va = 0;
+      cr = g_drv.cuMemAddressReserve_(&va, rec.size, 0, 0, 0);
+      if (cr != CUDA_SUCCESS) { g_drv.cuMemRelease_(h); fail = mccsOutOfMemory; break; }
+      cr = g_drv.cuMemMap_(va, rec.size, 0, h, 0);
+      if (cr != CUDA_SUCCESS) {
+        LOG_ERROR("cuMemMap: %s", cu_err(cr));
+        g_drv.cuMemAddressFree_(va, rec.size);
+        g_drv.cuMemRelease_(h);
+        fail = mccsDeviceError;
+        break;
+      }
+      CUmemAccessDesc desc;
+      memset(&desc, 0, sizeof desc);
+      desc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+      desc.location.id = device;
+      desc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+      cr = g_drv.cuMemSetAccess_(va, rec.size, &desc, 1);
+      if (cr != CUDA_SUCCESS) {
+        LOG_ERROR("cuMemSetAccess: %s", cu_err(cr));
+        g_drv.cuMemUnmap_(va, rec.size);
+        g_drv.cuMemAddressFree_(va, rec.size);
+        g_drv.cuMemRelease_(h);
+        fail = mccsDeviceError;
+        break;
+      }
+      rec.base = (uint64_t)va;
+      rec.vmm_handle = (uint64_t)h;
+      break;
+    }
+    case proto::kShareCudaIpc: {
+      CtxScope scope(device);
+      if (!scope.ok) { fail = mccsDeviceError; break; }
+      CUipcMemHandle h;
+      memcpy(&h, m.malloc_reply.ipc_handle, sizeof h);
+      CUdeviceptr p = 0;
+      CUresult cr = g_drv.cuIpcOpenMemHandle_(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS);
+      if (cr != CUDA_SUCCESS) { LOG_ERROR("cuIpcOpenMemHandle: %s", cu_err(cr)); fail = mccsDeviceError; break; }
+      rec.base = (uint64_t)p;
+      break;
+    }
+    default: fail = mccsProtocolError;
+  }
+  close_fds();
+  if (fail != mccsSuccess) {
+    proto::AnyMsg f;
+    memset(&f, 0, sizeof f);
+    f.h.type = proto::kFree;
+    f.free_req.mem_id = rec.mem_id;
+    roundtrip(f, sizeof(proto::FreeReq), proto::kFreeReply, nullptr, 30000);
+    return fail;
+  }
+  g_ctx.mem[rec.base] = rec;
+  *ptr = (void*)rec.base;
+  return mccsSuccess;
+}
+
+mccsResult_t mccsFree(void* ptr) {
+  if (!ptr) return mccsSuccess;
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  auto it = g_ctx.mem.find((uint64_t)ptr);
+  if (it == g_ctx.mem.end()) return mccsNotFound;
+  MemRec rec = it->second;
+  // Unmap here first, then let the daemon release the memory.
+  if (rec.share_kind == proto::kShareHostFd) {
+    munmap((void*)rec.base, rec.size);
+  } else if (rec.share_kind == proto::kShareVmmFd) {
+    CtxScope scope(rec.device);
+    g_drv.cuMemUnmap_((CUdeviceptr)rec.base, rec.size);
+    g_drv.cuMemAddressFree_((CUdeviceptr)rec.base, rec.size);
+    g_drv.cuMemRelease_((CUmemGenericAllocationHandle)rec.vmm_handle);
+  } else if (rec.share_kind == proto::kShareCudaIpc) {
+    CtxScope scope(rec.device);
+    g_drv.cuIpcCloseMemHandle_((CUdeviceptr)rec.base);
+  }
+  g_ctx.mem.erase(it);
+  if (!g_ctx.connected) return mccsSuccess;
+  proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
+  m.h.type = proto::kFree;
+  m.free_req.mem_id = rec.mem_id;
+  return roundtrip(m, sizeof(proto::FreeReq), proto::kFreeReply, nullptr, 60000);
+}
+
+mccsResult_t mccsMemInfo(const void* ptr, uint64_t* mem_id, uint64_t* offset, uint64_t* alloc_size) {
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  const MemRec* r = find_mem_locked(ptr);
+  if (!r) return mccsNotFound;
+  if (mem_id) *mem_id = r->mem_id;
+  if (offset) *offset = (uint64_t)ptr - r->base;
+  if (alloc_size) *alloc_size = r->size;
+  return mccsSuccess;
+}
+
+mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, int nranks, int device,
+                              const char* root_addr) {
+  if (!comm) return mccsInvalidArgument;
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  mccsResult_t r = ensure_connected_locked(nullptr);
+  if (r != mccsSuccess) return r;
+  proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
+  m.h.type = proto::kCommInit;
+  m.comm_init.comm_id = unique_id;
+  m.comm_init.rank = rank;
+  m.comm_init.nranks = nranks;
+  m.comm_init.device = device;
+  if (root_addr) snprintf(m.comm_init.root_addr, sizeof m.comm_init.root_addr, "%s", root_addr);
+  std::vector<int> fds;
+  // Blocks until every rank has joined (the daemon bounds the wait).
+  r = roundtrip(m, sizeof(proto::CommInitReq), proto::kCommInitReply, &fds, 600000);
+  if (r != mccsSuccess) { for (int f : fds) close(f); return r; }
+  if (fds.empty()) return mccsProtocolError;
+  mccsComm* c = new mccsComm();
+  c->handle = m.comm_init_reply.comm_handle;
+  c->id = unique_id;
+  c->rank = rank;
+  c->nranks = nranks;
+  c->device = device;
+  c->dp_bytes = m.comm_init_reply.dp_bytes;
+  c->dp_mem = mmap(nullptr, c->dp_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
+  for (int f : fds) close(f);
+  if (c->dp_mem == MAP_FAILED) { delete c; return mccsOutOfMemory; }
+  const size_t wq_bytes = (ipc::Ring::bytes_needed(proto::kWqDepth, proto::kWrBytes) + 63) / 64 * 64;
+  c->wq.attach(c->dp_mem);
+  c->cq.attach((char*)c->dp_mem + wq_bytes);
+  if (g_ctx.backend == proto::kBackendCuda) {
+    if (g_ctx.same_process) {
+      c->backend_event = (CUevent)m.comm_init_reply.event_raw;
+    } else {
+      CtxScope scope(device);
+      if (!scope.ok) { munmap(c->dp_mem, c->dp_bytes); delete c; return mccsDeviceError; }
+      CUipcEventHandle h;
+      memcpy(&h, m.comm_init_reply.event_handle, sizeof h);
+      CUresult cr = g_drv.cuIpcOpenEventHandle_(&c->backend_event, h);
+      if (cr != CUDA_SUCCESS) {
+        LOG_ERROR("cuIpcOpenEventHandle: %s", cu_err(cr));
+        munmap(c->dp_mem, c->dp_bytes);
+        delete c;
+        return mccsDeviceError;
+      }
+      c->event_owned = true;
+    }
+  }
+  *comm = c;
+  return mccsSuccess;
+}
+
+mccsResult_t mccsCommDestroy(mccsComm_t comm) {
+  if (!comm) return mccsSuccess;
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  mccsResult_t r = mccsSuccess;
+  if (g_ctx.connected) {
+    proto::AnyMsg m;
+    memset(&m, 0, sizeof m);
+    m.h.type = proto::kCommDestroy;
+    m.comm_destroy.comm_handle = comm->handle;
+    r = roundtrip(m, sizeof(proto::CommDestroyReq), proto::kCommDestroyReply, nullptr, 60000);
+  }
+  if (comm->event_owned && comm->backend_event && g_drv.ok) {
+    CtxScope scope(comm->device);
+    g_drv.cuEventDestroy_(comm->backend_event);
+  }
+  if (comm->dp_mem) munmap(comm->dp_mem, comm->dp_bytes);
+  delete comm;
+  return r;
+}
+
+mccsResult_t mccsCommRank(mccsComm_t comm, int* rank) { if (!comm || !rank) return mccsInvalidArgument; *rank = comm->rank; return mccsSuccess; }
+mccsResult_t mccsCommSize(mccsComm_t comm, int* n) { if (!comm || !n) return mccsInvalidArgument; *n = comm->nranks; return mccsSuccess; }
+uint64_t mccsCommHandle(mccsComm_t comm) { return comm ? comm->handle : 0; }
+
+mccsResult_t mccsRegisterStream(int device, mccsStream_t stream) {
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  mccsResult_t r = ensure_connected_locked(nullptr);
+  if (r != mccsSuccess) return r;
+  StreamRec* rec = nullptr;
+  return register_stream_locked(device, stream, &rec);
+}
+
+mccsResult_t mccsAllReduceEx(mccsComm_t comm, const void* send, void* recv, size_t count, mccsDataType_t dtype,
+                             mccsRedOp_t op, float scale, mccsAlgo_t algo, mccsStream_t stream) {
+  if (!comm || (int)dtype < 0 || (int)dtype >= kNumDataTypes || (int)op < 0 || (int)op >= kNumRedOps)
+    return mccsInvalidArgument;
+  proto::WorkRequest wr;
+  memset(&wr, 0, sizeof wr);
+  wr.kind = kAllReduce;
+  wr.dtype = (uint32_t)dtype;
+  wr.op = (uint32_t)op;
+  wr.count = count;
+  wr.scale = scale;
+  wr.variant = (uint32_t)algo;
+  const uint64_t bytes = (uint64_t)count * (uint64_t)dtype_size((int)dtype);
+  return submit(comm, wr, send, recv, bytes, bytes, stream);
+}
+
+mccsResult_t mccsAllReduce(mccsComm_t comm, const void* send, void* recv, size_t count, mccsDataType_t dtype,
+                           mccsRedOp_t op, mccsStream_t stream) {
+  return mccsAllReduceEx(comm, send, recv, count, dtype, op, 1.0f, mccsAlgoAuto, stream);
+}
+
+mccsResult_t mccsAllGatherEx(mccsComm_t comm, const void* send, void* recv, size_t bytes, mccsAlgo_t algo,
+                             mccsStream_t stream) {
+  if (!comm) return mccsInvalidArgument;
+  proto::WorkRequest wr;
+  memset(&wr, 0, sizeof wr);
+  wr.kind = kAllGather;
+  wr.dtype = kUint8;
+  wr.count = bytes;
+  wr.scale = 1.0f;
+  wr.variant = (uint32_t)algo;
+  return submit(comm, wr, send, recv, bytes, (uint64_t)bytes * (uint64_t)comm->nranks, stream);
+}
+
+mccsResult_t mccsAllGather(mccsComm_t comm, const void* send, void* recv, size_t bytes, mccsStream_t stream) {
+  return mccsAllGatherEx(comm, send, recv, bytes, mccsAlgoAuto, stream);
+}
+
+mccsResult_t mccsGroupStart(void) { g_group_depth++; return mccsSuccess; }
+
+mccsResult_t mccsGroupEnd(void) {
+  if (g_group_depth <= 0) return mccsInvalidArgument;
+  if (--g_group_depth > 0) return mccsSuccess;
+  mccsResult_t result = mccsSuccess;
+  std::vector<GroupItem> items;
+  items.swap(g_group_items);
+  // Collect every completion, then order each (communicator, stream) pair once.
+  for (const GroupItem& it : items) {
+    proto::WorkCompletion wc;
+    while (it.comm->outstanding > 0) {
+      mccsResult_t r = wait_completion(it.comm, &wc);
+      if (r == mccsTimeout || r == mccsNotConnected) return r;
+      if (r != mccsSuccess) result = r;
+    }
+  }
+  std::vector<GroupItem> seen;
+  for (const GroupItem& it : items) {
+    bool dup = false;
+    for (const GroupItem& s : seen) dup |= s.comm == it.comm && s.stream == it.stream;
+    if (dup) continue;
+    seen.push_back(it);
+    if (it.comm->sticky_error && result == mccsSuccess) result = (mccsResult_t)it.comm->sticky_error;
+    mccsResult_t r = finish_on_stream(it.comm, it.stream);
+    if (r != mccsSuccess) result = r;
+  }
+  return result;
+}
+
+mccsResult_t mccsCommQuery(mccsComm_t comm, mccsCommInfo_t* info) {
+  if (!comm || !info) return mccsInvalidArgument;
+  std::lock_guard<std::mutex> g(g_ctx.mu);
+  if (!g_ctx.connected) return mccsNotConnected;
+  proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
+  m.h.type = proto::kCommQuery;
+  m.comm_query.comm_handle = comm->handle;
+  mccsResult_t r = roundtrip(m, sizeof(proto::CommQueryReq), proto::kCommQueryReply, nullptr, 30000);
+  if (r != mccsSuccess) return r;
+  info->async_error = m.comm_query_reply.async_error;
+  info->device_error = m.comm_query_reply.device_error;
+  info->launched = m.comm_query_reply.launched;
+  info->completed = m.comm_query_reply.completed;
+  info->last_variant = m.comm_query_reply.last_variant;
+  info->last_ctas = m.comm_query_reply.last_ctas;
+  info->config_epoch = m.comm_query_reply.config_epoch;
+  return mccsSuccess;
+}
+
+mccsResult_t mccsCommGetAsyncError(mccsComm_t comm, mccsResult_t* async_error) {
+  mccsCommInfo_t info;
+  mccsResult_t r = mccsCommQuery(comm, &info);
+  if (r != mccsSuccess) return r;
+  if (async_error) *async_error = (mccsResult_t)info.async_error;
+  return mccsSuccess;
+}
+
+mccsResult_t mccsCommLastPlan(mccsComm_t comm, uint32_t* variant, uint32_t* ctas) {
+  if (!comm) return mccsInvalidArgument;
+  if (variant) *variant = comm->last_variant;
+  if (ctas) *ctas = comm->last_ctas;
+  return mccsSuccess;
+}
+
+const char* mccsGetErrorString(mccsResult_t r) {
+  switch (r) {
+    case mccsSuccess: return "success";
+    case mccsInvalidArgument: return "invalid argument";
+    case mccsOutOfMemory: return "out of memory";
+    case mccsDeviceError: return "a CUDA call failed";
+    case mccsProtocolError: return "protocol error";
+    case mccsNotFound: return "not found";
+    case mccsTimeout: return "timed out";
+    case mccsAborted: return "aborted";
+    case mccsMismatch: return "ranks disagree on the collective";
+    case mccsUnsupported: return "unsupported";
+    case mccsPeerLost: return "a peer rank went away";
+    case mccsInternalError: return "internal error";
+    case mccsNotConnected: return "not connected to the daemon";
+  }
+  return "unknown error";
+}
+
+const char* mccsAlgoName(int algo) { return variant_name(algo); }
+
+mccsResult_t mccsAdminRequest(const char* host, int port, int type, const char* json_body, char* reply,
+                              size_t reply_cap) {
+  if (!host || port <= 0) return mccsInvalidArgument;
+  struct addrinfo hints, *res = nullptr;
+  memset(&hints, 0, sizeof hints);
+  hints.ai_family = AF_INET;
+  hints.ai_socktype = SOCK_STREAM;
+  char portstr[16];
+  snprintf(portstr, sizeof portstr, "%d", port);
+  if (getaddrinfo(host, portstr, &hints, &res) != 0 || !res) return mccsNotConnected;
+  int fd = socket(res->ai_family, res->ai_socktype | SOCK_CLOEXEC, res->ai_protocol);
+  if (fd < 0) { freeaddrinfo(res); return mccsNotConnected; }
+  if (connect(fd, res->ai_addr, res->ai_addrlen) < 0) { freeaddrinfo(res); close(fd); return mccsNotConnected; }
+  freeaddrinfo(res);
+  const std::string body = json_body ? json_body : "{}";
+  uint8_t hdr[13];
+  memcpy(hdr, &proto::kAdminMagic, 8);
+  hdr[8] = (uint8_t)type;
+  uint32_t len = (uint32_t)body.size();
+  memcpy(hdr + 9, &len, 4);
+  auto write_all = [&](const void* p, size_t n) {
+    const char* c = (const char*)p;
+    while (n) { ssize_t k = send(fd, c, n, MSG_NOSIGNAL); if (k <= 0) return false; c += k; n -= (size_t)k; }
+    return true;
+  };
+  auto read_all = [&](void* p, size_t n) {
+    char* c = (char*)p;
+    while (n) {
+      struct pollfd pf = {fd, POLLIN, 0};
+      if (poll(&pf, 1, 30000) <= 0) return false;
+      ssize_t k = read(fd, c, n);
+      if (k <= 0) return false;
+      c += k; n -= (size_t)k;
+    }
+    return true;
+  };
+  mccsResult_t result = mccsProtocolError;
+  if (write_all(hdr, sizeof hdr) && write_all(body.data(), body.size()) && read_all(hdr, sizeof hdr)) {
+    uint64_t magic;
+    memcpy(&magic, hdr, 8);
+    memcpy(&len, hdr + 9, 4);
+    if (magic == proto::kAdminMagic && len < (64u << 20)) {
+      std::string out(len, '\0');
+      if (!len || read_all(&out[0], len)) {
+        if (reply && reply_cap) {
+          size_t n = out.size() < reply_cap - 1 ? out.size() : reply_cap - 1;
+          memcpy(reply, out.data(), n);
+          reply[n] = 0;
+        }
+        result = mccsSuccess;
+      }
+    }
+  }
+  close(fd);
+  return result;
+}
+
+void* mccs_torch_malloc(size_t size, int device, void* stream) {
+  (void)stream;
+  void* p = nullptr;
+  if (size == 0) size = 1;
+  mccsResult_t r = mccsMalloc(&p, device, size);
+  if (r != mccsSuccess) {
+    LOG_ERROR("mccs_torch_malloc(%zu bytes, device %d): %s", size, device, mccsGetErrorString(r));
+    return nullptr;
+  }
+  return p;
+}
+
+void mccs_torch_free(void* ptr, size_t size, int device, void* stream) {
+  (void)size; (void)device; (void)stream;
+  mccsFree(ptr);
+}
+
+}  // extern "C"
