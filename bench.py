@@ -1,0 +1,302 @@
+#!/usr/bin/env python
+"""Headline benchmark: AllReduce algorithm bandwidth of a 512 MiB 16-bit message
+through the managed service, the configuration of the reference's single-app figure
+(``eval/plot/single_app/allreduce_8gpu.csv``: fp16, 512 MiB, 8 GPUs, MCCS algBW
+5.99 GB/s on 4x2 RTX 3090 over 50 Gb/s RoCE).
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+One step = one AllReduce(sum) of ``--size-mb`` MiB of bf16 per rank, out of place,
+issued through the public client API (libmccs -> daemon -> sm_100a kernel). The local
+rank 0 hosts the daemon inside its process; every rank is a client. Timing: CUDA
+events on the launching stream around exactly K steps, barrier + synchronise on both
+sides, MAX over ranks. The message (512 MiB) is larger than the 126 MB L2, so no
+flush is needed between iterations. The ``e2e`` figure adds, every step, the
+host->device copy of the input from pinned memory and a device->host read of the head
+of the result.
+
+``--impl reference`` runs the reference's own NCCL baseline harness
+(``nccl-tests-mccs`` built unmodified into ``baseline/_ref``) for the same message.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import re
+import subprocess
+import sys
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+BASELINE_ALGBW_GBPS = 5.99   # MCCS, AllReduce fp16 512 MiB, 8 GPUs
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="mccs", choices=["mccs", "reference"])
+    p.add_argument("--size-mb", type=float, default=512.0)
+    p.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
+    p.add_argument("--coll", default="allreduce", choices=["allreduce", "allgather"])
+    p.add_argument("--algo", default="auto")
+    p.add_argument("--no-nccl", action="store_true", help="skip the same-harness NCCL measurement")
+    return p.parse_args()
+
+
+def reference_arm(args, rank: int) -> int:
+    """The reference's NCCL baseline harness, unmodified, single process, -g N."""
+    if rank != 0:
+        return 0
+    exe = os.path.join(REPO, "baseline", "_ref", "nccl-tests-mccs", "build",
+                       "all_reduce_perf" if args.coll == "allreduce" else "all_gather_perf")
+    out = {"impl": "reference"}
+    if not os.path.exists(exe):
+        out["unavailable"] = ("the reference is a Rust workspace (no setup.py/pyproject; needs cargo, libibverbs, "
+                              "gdrcopy) and its nccl-tests-mccs harness is not built in baseline/_ref")
+        print(json.dumps(out))
+        return 0
+    size = int(args.size_mb * 1024 * 1024)
+    dt = {"bf16": "bfloat16", "fp16": "half", "fp32": "float"}[args.dtype]
+    env = dict(os.environ)
+    import glob
+    libs = glob.glob(os.path.join(sys.prefix, "lib", "python*", "site-packages", "nvidia", "nccl", "lib"))
+    env["LD_LIBRARY_PATH"] = ":".join(libs + [env.get("LD_LIBRARY_PATH", "")])
+    cmd = [exe, "-g", str(args.gpus), "-b", str(size), "-e", str(size), "-d", dt, "-n", str(args.steps),
+           "-w", str(max(args.warmup, 3)), "-c", "0"]
+    try:
+        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    except Exception as e:  # noqa: BLE001
+        out["unavailable"] = f"nccl-tests-mccs failed to run: {e}"
+        print(json.dumps(out))
+        return 0
+    alg = None
+    for line in res.stdout.splitlines():
+        f = line.split()
+        # size count type redop root  time algbw busbw #wrong  time algbw busbw #wrong
+        if len(f) >= 8 and f[0].isdigit() and int(f[0]) == size:
+            try:
+                nums = [float(x) for x in f if re.fullmatch(r"[-+0-9.eE]+", x)]
+                # out-of-place columns come first: time(us) algbw busbw
+                t_us, alg = nums[-8], nums[-7]
+                out.update({"ms_per_step": t_us / 1000.0})
+            except (ValueError, IndexError):
+                pass
+    if alg is None:
+        out["unavailable"] = "nccl-tests-mccs produced no result row: " + (res.stderr.strip()[-200:] or res.stdout.strip()[-200:])
+        print(json.dumps(out))
+        return 0
+    out.update({
+        "metric": f"{args.coll}_algbw_GBps", "value": alg, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": alg / BASELINE_ALGBW_GBPS, "dtype": args.dtype, "data": "synthetic",
+        "config": {"model": f"{args.coll} {args.size_mb:g} MiB {args.dtype}, NCCL via the reference's nccl-tests-mccs "
+                            "(host-timed by that harness, single process -g N)",
+                   "global_batch": size, "seq_len": 1, "parallelism": f"dp{args.gpus}"},
+    })
+    print(json.dumps(out))
+    return 0
+
+
+def main() -> int:
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        return reference_arm(args, rank)
+
+    import torch
+    import torch.distributed as dist
+
+    import mccs_b200 as M
+    from mccs_b200.utils.timing import ClockSampler, bus_factor
+
+    n = world
+    if n != args.gpus and rank == 0:
+        print(f"bench.py: WORLD_SIZE={world} differs from --gpus {args.gpus}; using {world}", file=sys.stderr)
+    have_cuda = torch.cuda.is_available()
+    if have_cuda:
+        torch.cuda.set_device(local_rank)
+    if n > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if have_cuda:
+            dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+        else:
+            dist.init_process_group("gloo")
+
+    def barrier():
+        if n > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if n == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=f"cuda:{local_rank}" if have_cuda else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    port = os.environ.get("MASTER_PORT", "0")
+    prefix = f"/tmp/mccs-bench-{os.getuid()}-{port}-{os.environ.get('TORCHELASTIC_RUN_ID', os.getppid() if n > 1 else os.getpid())}"
+    control = prefix + "/control.sock"
+    if local_rank == 0:
+        M.daemon.start_embedded(prefix=prefix, channel_count=2, host_devices=max(n, 1), listen_port=-1)
+    barrier()
+    M.init(control)
+    backend = M.backend()
+    dev = local_rank
+
+    tdtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    esz = torch.empty((), dtype=tdtype).element_size()
+    nbytes = int(args.size_mb * 1024 * 1024)
+    if backend == "host":
+        nbytes = min(nbytes, 8 << 20)   # CPU dry run of the script only
+    count = nbytes // esz
+    is_ar = args.coll == "allreduce"
+    send_buf = M.Buffer(nbytes, dev)
+    recv_buf = M.Buffer(nbytes if is_ar else nbytes * n, dev)
+    send = send_buf.tensor(tdtype, count)
+    recv = recv_buf.tensor(tdtype, count if is_ar else count * n)
+    gen = torch.Generator(device="cpu").manual_seed(rank)
+    pinned = torch.empty(count, dtype=tdtype, pin_memory=have_cuda)
+    chunk = 1 << 24
+    for off in range(0, count, chunk):   # U(-1, 1), seed = rank
+        m = min(chunk, count - off)
+        pinned[off:off + m] = (torch.rand(m, generator=gen) * 2 - 1).to(tdtype)
+    send.copy_(pinned)
+    comm = M.Communicator(0xB200, rank, n, device=dev)
+
+    def step():
+        if is_ar:
+            comm.all_reduce(send, recv, algo=args.algo)
+        else:
+            comm.all_gather(send, recv, algo=args.algo)
+
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+    for _ in range(warmup):
+        step()
+    if have_cuda:
+        torch.cuda.synchronize()
+
+    # Correctness of what is about to be timed: compare a slice against a plain fp32 sum.
+    check_n = min(count, 1 << 16)
+    ok = True
+    if n > 1 and is_ar and have_cuda:
+        mine = send[:check_n].float()
+        gathered = [torch.empty_like(mine) for _ in range(n)]
+        dist.all_gather(gathered, mine)
+        want = torch.stack(gathered).sum(0)
+        got = recv[:check_n].float()
+        tol = 1e-5 if tdtype == torch.float32 else 2e-2
+        ok = bool(torch.allclose(got, want, rtol=tol, atol=tol * n))
+    elif is_ar:
+        ok = bool(torch.equal(recv[:check_n], send[:check_n])) if n == 1 else True
+
+    sampler = ClockSampler(dev) if (have_cuda and local_rank == 0) else None
+
+    def timed(fn) -> float:
+        if not have_cuda:
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                fn()
+            dt = (time.perf_counter() - t0) * 1000 / steps
+            barrier()
+            return max_over_ranks(dt)
+        stream = torch.cuda.current_stream()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    if sampler:
+        sampler.start()
+    ms = timed(step)
+    variant, ctas = comm.last_plan()
+
+    # End to end: input arrives from pinned host memory and the result is read back, every step.
+    d2h_elems = min(count, 32768)
+    result_host = torch.empty(d2h_elems, dtype=tdtype, pin_memory=have_cuda)
+
+    def e2e_step():
+        send.copy_(pinned, non_blocking=True)
+        step()
+        result_host.copy_(recv[:d2h_elems], non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step)
+    clocks = sampler.stop() if sampler else None
+
+    # Same harness, NCCL (the baseline the service has to match on this box).
+    nccl = None
+    if n > 1 and have_cuda and not args.no_nccl:
+        src = torch.empty(count, dtype=tdtype, device=f"cuda:{dev}").copy_(send)
+        if is_ar:
+            def nccl_step():
+                dist.all_reduce(src)
+        else:
+            dst = torch.empty(count * n, dtype=tdtype, device=f"cuda:{dev}")
+
+            def nccl_step():
+                dist.all_gather_into_tensor(dst, src)
+        for _ in range(warmup):
+            nccl_step()
+        ms_nccl = timed(nccl_step)
+        total = nbytes if is_ar else nbytes * n
+        nccl = {"ms_per_step": ms_nccl, "algbw_GBps": total / ms_nccl / 1e6,
+                "busbw_GBps": total / ms_nccl / 1e6 * bus_factor(args.coll, n)}
+
+    total_bytes = nbytes if is_ar else nbytes * n
+    alg = total_bytes / ms / 1e6          # GB/s
+    alg_e2e = total_bytes / ms_e2e / 1e6
+    comm.destroy()
+    send_buf.free()
+    recv_buf.free()
+    M.finalize()
+    barrier()
+    if local_rank == 0:
+        M.daemon.stop_embedded()
+    if rank == 0:
+        out = {
+            "metric": f"{args.coll}_algbw_GBps", "value": alg, "unit": "GB/s", "n_gpus": n, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": alg / BASELINE_ALGBW_GBPS, "dtype": args.dtype, "data": "synthetic",
+            "impl": "mccs",
+            "busbw_GBps": alg * bus_factor(args.coll, n),
+            "config": {
+                "model": f"{args.coll} sum, {nbytes / 2**20:g} MiB per rank, out of place, through libmccs + daemon",
+                "global_batch": nbytes * n, "seq_len": 1, "parallelism": f"dp{n}",
+                "variant": variant, "ctas": ctas, "backend": backend,
+                "l2": "inputs larger than L2 (no flush)", "timing": "CUDA events, max over ranks",
+                "verified": ok,
+            },
+            "clocks": clocks,
+            "e2e": {"value": alg_e2e, "unit": "GB/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": d2h_elems * esz},
+            # one collective kernel per rank and step, launched by the daemon threads in local rank 0
+            "gpu_launches": steps * n,
+            "nccl_same_harness": nccl,
+        }
+        print(json.dumps(out))
+    if n > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

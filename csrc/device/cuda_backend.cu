@@ -601,3 +601,67 @@ Backend* make_cuda_backend(const BackendOptions& opt, std::string* why) {
 }
 
 }  // namespace mccs
+
+// Self-test of the bounded device-side waits: launches rank 0 of a two-rank
+// all-reduce whose peer is never launched, so the start barrier waits for a flag that
+// nothing sets, gives up after `timeout_ms`, reports through the status block and
+// returns. The context stays usable. Returns 0 when the launch and the
+// synchronisation succeeded; *error_out receives the DevStatus the kernel reported.
+extern "C" int mccs_selftest_bounded_wait(int device, int timeout_ms, unsigned* error_out, double* elapsed_ms) {
+  using namespace mccs;
+  if (cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); return -1; }
+  SignalPad* pads[2] = {nullptr, nullptr};
+  StatusBlock* status[2] = {nullptr, nullptr};
+  float* data = nullptr;
+  int rc = -1;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  do {
+    if (cudaMalloc(&data, 4 * 4096) != cudaSuccess) break;
+    if (cudaMemset(data, 0, 4 * 4096) != cudaSuccess) break;
+    bool ok = true;
+    for (int r = 0; r < 2 && ok; r++) {
+      ok = cudaMalloc(&pads[r], sizeof(SignalPad)) == cudaSuccess &&
+           cudaMemset(pads[r], 0, sizeof(SignalPad)) == cudaSuccess &&
+           cudaHostAlloc(&status[r], sizeof(StatusBlock), cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess;
+      if (ok) memset(status[r], 0, sizeof(StatusBlock));
+    }
+    if (!ok) break;
+    CollArgs a;
+    memset(&a, 0, sizeof a);
+    a.rank = 0;
+    a.nranks = 2;
+    a.dtype = kFloat32;
+    a.op = kSum;
+    a.variant = kArTwoShot;
+    a.count = 1024;
+    a.seq = 1;
+    a.scale = 1.0f;
+    a.epoch = 1;
+    a.timeout_ns = (uint64_t)timeout_ms * 1000000ull;
+    for (int r = 0; r < 2; r++) {
+      a.send[r] = data + r * 1024;
+      a.recv[r] = data + 2048 + r * 1024;
+      a.pad[r] = pads[r];
+      a.status[r] = status[r];
+    }
+    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
+    cudaEventRecord(e0, 0);
+    if (launch_collective(kAllReduce, a, LaunchDims{1, 128}, nullptr) != cudaSuccess) break;
+    cudaEventRecord(e1, 0);
+    if (cudaDeviceSynchronize() != cudaSuccess) break;
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (elapsed_ms) *elapsed_ms = ms;
+    if (error_out) *error_out = status[0]->error;
+    rc = 0;
+  } while (0);
+  cudaGetLastError();
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  for (int r = 0; r < 2; r++) {
+    if (pads[r]) cudaFree(pads[r]);
+    if (status[r]) cudaFreeHost(status[r]);
+  }
+  if (data) cudaFree(data);
+  return rc;
+}

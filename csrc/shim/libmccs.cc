@@ -20,6 +20,8 @@
 #include <time.h>
 #include <unistd.h>
 
+#include <chrono>
+#include <condition_variable>
 #include <map>
 #include <mutex>
 #include <string>
@@ -148,6 +150,11 @@ struct StreamRec {
   int device = 0;
 };
 
+struct Reply {
+  proto::AnyMsg msg;
+  std::vector<int> fds;
+};
+
 struct Context {
   std::mutex mu;
   int fd = -1;
@@ -161,6 +168,10 @@ struct Context {
   std::map<uint64_t, MemRec> mem;                       // base -> record
   std::map<std::pair<int, uint64_t>, StreamRec> streams;   // (device, stream) -> record
   uint64_t wc_timeout_ms = 300000;
+  // reply demultiplexing (see roundtrip)
+  bool reader_active = false;
+  std::condition_variable reply_cv;
+  std::map<uint32_t, struct Reply> replies;
 };
 Context g_ctx;
 
@@ -197,29 +208,62 @@ std::string default_control_path() {
   return p + "/" + (direct ? direct : "control.sock");
 }
 
-// Request/reply on the control connection. Caller holds g_ctx.mu.
-mccsResult_t roundtrip(proto::AnyMsg& m, size_t len, uint32_t expect_type, std::vector<int>* fds, int timeout_ms) {
+// Request/reply on the control connection. The caller holds g_ctx.mu through `lk`;
+// the lock is released while waiting so that several threads can have requests in
+// flight (communicator creation blocks until all ranks have joined, and those ranks
+// may be threads of this very process). Whichever waiting thread finds the socket
+// free reads it and files replies by request id for the others.
+mccsResult_t roundtrip(std::unique_lock<std::mutex>& lk, proto::AnyMsg& m, size_t len, uint32_t expect_type,
+                       std::vector<int>* fds, int timeout_ms) {
   Context& c = g_ctx;
   m.h.magic = proto::kMagic;
   m.h.req_id = c.next_req++;
   const uint32_t req = m.h.req_id;
   ssize_t n = ipc::uds_send(c.fd, &m, len);
   if (n < 0) return mccsProtocolError;
+  struct timespec t0;
+  clock_gettime(CLOCK_MONOTONIC, &t0);
   for (;;) {
-    int rc = ipc::wait_readable(c.fd, timeout_ms);
-    if (rc == 0) return mccsTimeout;
-    if (rc < 0) return mccsProtocolError;
-    proto::AnyMsg r;
-    n = ipc::uds_recv(c.fd, &r, sizeof r, fds);
-    if (n <= 0) { c.connected = false; return mccsNotConnected; }
-    if ((size_t)n < sizeof(proto::Header) || r.h.magic != proto::kMagic) return mccsProtocolError;
-    if (r.h.req_id != req || r.h.type != expect_type) continue;   // stale reply of an abandoned request
-    m = r;
-    return (mccsResult_t)r.h.status;
+    auto it = c.replies.find(req);
+    if (it != c.replies.end()) {
+      m = it->second.msg;
+      if (fds) *fds = it->second.fds;
+      else for (int f : it->second.fds) close(f);
+      c.replies.erase(it);
+      if (m.h.type != expect_type) return mccsProtocolError;
+      return (mccsResult_t)m.h.status;
+    }
+    if (!c.connected && c.session_id != 0) return mccsNotConnected;
+    struct timespec t1;
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    int64_t ms = (int64_t)(t1.tv_sec - t0.tv_sec) * 1000 + (t1.tv_nsec - t0.tv_nsec) / 1000000;
+    if (ms > timeout_ms) return mccsTimeout;
+    if (c.reader_active) {
+      c.reply_cv.wait_for(lk, std::chrono::milliseconds(20));
+      continue;
+    }
+    c.reader_active = true;
+    const int fd = c.fd;
+    lk.unlock();
+    Reply rep;
+    ssize_t got = -EAGAIN;
+    int rc = ipc::wait_readable(fd, 20);
+    if (rc > 0) got = ipc::uds_recv(fd, &rep.msg, sizeof rep.msg, &rep.fds);
+    lk.lock();
+    c.reader_active = false;
+    if (rc > 0) {
+      if (got <= 0 && got != -EAGAIN) { c.connected = false; c.reply_cv.notify_all(); return mccsNotConnected; }
+      if (got >= (ssize_t)sizeof(proto::Header) && rep.msg.h.magic == proto::kMagic)
+        c.replies[rep.msg.h.req_id] = rep;
+    } else if (rc < 0) {
+      c.reply_cv.notify_all();
+      return mccsProtocolError;
+    }
+    c.reply_cv.notify_all();
   }
 }
 
-mccsResult_t ensure_connected_locked(const char* path) {
+mccsResult_t ensure_connected_locked(std::unique_lock<std::mutex>& lk, const char* path) {
   Context& c = g_ctx;
   if (c.connected) return mccsSuccess;
   std::string p = path && path[0] ? path : default_control_path();
@@ -244,7 +288,7 @@ mccsResult_t ensure_connected_locked(const char* path) {
   m.hello.device_affinity = aff ? atoi(aff) : -1;
   const char* app = getenv("MCCS_APP_NAME");
   snprintf(m.hello.app_name, sizeof m.hello.app_name, "%s", app ? app : program_invocation_short_name);
-  mccsResult_t r = roundtrip(m, sizeof(proto::Hello), proto::kWelcome, nullptr, 10000);
+  mccsResult_t r = roundtrip(lk, m, sizeof(proto::Hello), proto::kWelcome, nullptr, 10000);
   if (r != mccsSuccess) { close(fd); c.fd = -1; return r; }
   c.backend = m.welcome.backend;
   c.daemon_pid = m.welcome.daemon_pid;
@@ -270,7 +314,7 @@ const MemRec* find_mem_locked(const void* ptr) {
   return &it->second;
 }
 
-mccsResult_t register_stream_locked(int device, mccsStream_t stream, StreamRec** out) {
+mccsResult_t register_stream_locked(std::unique_lock<std::mutex>& lk, int device, mccsStream_t stream, StreamRec** out) {
   Context& c = g_ctx;
   auto key = std::make_pair(device, (uint64_t)stream);
   auto it = c.streams.find(key);
@@ -298,7 +342,7 @@ mccsResult_t register_stream_locked(int device, mccsStream_t stream, StreamRec**
       memcpy(m.reg_stream.event_handle, &h, sizeof h);
     }
   }
-  mccsResult_t r = roundtrip(m, sizeof(proto::RegisterStreamReq), proto::kRegisterStreamReply, nullptr, 30000);
+  mccsResult_t r = roundtrip(lk, m, sizeof(proto::RegisterStreamReq), proto::kRegisterStreamReply, nullptr, 30000);
   if (r != mccsSuccess) return r;
   rec.stream_id = m.reg_stream_reply.stream_id;
   auto ins = c.streams.emplace(key, rec);
@@ -344,7 +388,7 @@ mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, vo
   if (!comm) return mccsInvalidArgument;
   StreamRec* srec = nullptr;
   {
-    std::lock_guard<std::mutex> g(g_ctx.mu);
+    std::unique_lock<std::mutex> g(g_ctx.mu);
     if (!g_ctx.connected) return mccsNotConnected;
     const MemRec* sm = find_mem_locked(send);
     const MemRec* rm = find_mem_locked(recv);
@@ -355,7 +399,7 @@ mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, vo
     wr.send_mem = sm->mem_id; wr.send_off = (uint64_t)send - sm->base;
     wr.recv_mem = rm->mem_id; wr.recv_off = (uint64_t)recv - rm->base;
     if (wr.send_off + send_bytes > sm->size || wr.recv_off + recv_bytes > rm->size) return mccsInvalidArgument;
-    mccsResult_t r = register_stream_locked(comm->device, stream, &srec);
+    mccsResult_t r = register_stream_locked(g, comm->device, stream, &srec);
     if (r != mccsSuccess) return r;
   }
   wr.comm_handle = comm->handle;
@@ -400,12 +444,12 @@ mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, vo
 extern "C" {
 
 mccsResult_t mccsInit(const char* control_socket_path) {
-  std::lock_guard<std::mutex> g(g_ctx.mu);
-  return ensure_connected_locked(control_socket_path);
+  std::unique_lock<std::mutex> g(g_ctx.mu);
+  return ensure_connected_locked(g, control_socket_path);
 }
 
 mccsResult_t mccsFinalize(void) {
-  std::lock_guard<std::mutex> g(g_ctx.mu);
+  std::unique_lock<std::mutex> g(g_ctx.mu);
   Context& c = g_ctx;
   if (!c.connected) return mccsSuccess;
   proto::AnyMsg m;
@@ -438,21 +482,21 @@ mccsResult_t mccsFinalize(void) {
 }
 
 int mccsBackendKind(void) {
-  std::lock_guard<std::mutex> g(g_ctx.mu);
-  if (ensure_connected_locked(nullptr) != mccsSuccess) return -1;
+  std::unique_lock<std::mutex> g(g_ctx.mu);
+  if (ensure_connected_locked(g, nullptr) != mccsSuccess) return -1;
   return (int)g_ctx.backend;
 }
 
 int mccsDeviceCount(void) {
-  std::lock_guard<std::mutex> g(g_ctx.mu);
-  if (ensure_connected_locked(nullptr) != mccsSuccess) return -1;
+  std::unique_lock<std::mutex> g(g_ctx.mu);
+  if (ensure_connected_locked(g, nullptr) != mccsSuccess) return -1;
   return g_ctx.num_devices;
 }
 
 mccsResult_t mccsMalloc(void** ptr, int device, size_t size) {
   if (!ptr || size == 0) return mccsInvalidArgument;
-  std::lock_guard<std::mutex> g(g_ctx.mu);
-  mccsResult_t r = ensure_connected_locked(nullptr);
+  std::unique_lock<std::mutex> g(g_ctx.mu);
+  mccsResult_t r = ensure_connected_locked(g, nullptr);
   if (r != mccsSuccess) return r;
   proto::AnyMsg m;
   memset(&m, 0, sizeof m);
@@ -460,7 +504,7 @@ mccsResult_t mccsMalloc(void** ptr, int device, size_t size) {
   m.malloc_req.device = device;
   m.malloc_req.size = size;
   std::vector<int> fds;
-  r = roundtrip(m, sizeof(proto::MallocReq), proto::kMallocReply, &fds, 60000);
+  r = roundtrip(g, m, sizeof(proto::MallocReq), proto::kMallocReply, &fds, 60000);
   auto close_fds = [&]() { for (int f : fds) close(f); };
   if (r != mccsSuccess) { close_fds(); return r; }
   MemRec rec;
@@ -536,7 +580,7 @@ mccsResult_t mccsMalloc(void** ptr, int device, size_t size) {
     memset(&f, 0, sizeof f);
     f.h.type = proto::kFree;
     f.free_req.mem_id = rec.mem_id;
-    roundtrip(f, sizeof(proto::FreeReq), proto::kFreeReply, nullptr, 30000);
+    roundtrip(g, f, sizeof(proto::FreeReq), proto::kFreeReply, nullptr, 30000);
     return fail;
   }
   g_ctx.mem[rec.base] = rec;
@@ -546,7 +590,7 @@ mccsResult_t mccsMalloc(void** ptr, int device, size_t size) {
 
 mccsResult_t mccsFree(void* ptr) {
   if (!ptr) return mccsSuccess;
-  std::lock_guard<std::mutex> g(g_ctx.mu);
+  std::unique_lock<std::mutex> g(g_ctx.mu);
   auto it = g_ctx.mem.find((uint64_t)ptr);
   if (it == g_ctx.mem.end()) return mccsNotFound;
   MemRec rec = it->second;
@@ -568,11 +612,11 @@ mccsResult_t mccsFree(void* ptr) {
   memset(&m, 0, sizeof m);
   m.h.type = proto::kFree;
   m.free_req.mem_id = rec.mem_id;
-  return roundtrip(m, sizeof(proto::FreeReq), proto::kFreeReply, nullptr, 60000);
+  return roundtrip(g, m, sizeof(proto::FreeReq), proto::kFreeReply, nullptr, 60000);
 }
 
 mccsResult_t mccsMemInfo(const void* ptr, uint64_t* mem_id, uint64_t* offset, uint64_t* alloc_size) {
-  std::lock_guard<std::mutex> g(g_ctx.mu);
+  std::unique_lock<std::mutex> g(g_ctx.mu);
   const MemRec* r = find_mem_locked(ptr);
   if (!r) return mccsNotFound;
   if (mem_id) *mem_id = r->mem_id;
@@ -584,8 +628,8 @@ mccsResult_t mccsMemInfo(const void* ptr, uint64_t* mem_id, uint64_t* offset, ui
 mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, int nranks, int device,
                               const char* root_addr) {
   if (!comm) return mccsInvalidArgument;
-  std::lock_guard<std::mutex> g(g_ctx.mu);
-  mccsResult_t r = ensure_connected_locked(nullptr);
+  std::unique_lock<std::mutex> g(g_ctx.mu);
+  mccsResult_t r = ensure_connected_locked(g, nullptr);
   if (r != mccsSuccess) return r;
   proto::AnyMsg m;
   memset(&m, 0, sizeof m);
@@ -597,7 +641,7 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
   if (root_addr) snprintf(m.comm_init.root_addr, sizeof m.comm_init.root_addr, "%s", root_addr);
   std::vector<int> fds;
   // Blocks until every rank has joined (the daemon bounds the wait).
-  r = roundtrip(m, sizeof(proto::CommInitReq), proto::kCommInitReply, &fds, 600000);
+  r = roundtrip(g, m, sizeof(proto::CommInitReq), proto::kCommInitReply, &fds, 600000);
   if (r != mccsSuccess) { for (int f : fds) close(f); return r; }
   if (fds.empty()) return mccsProtocolError;
   mccsComm* c = new mccsComm();
@@ -637,14 +681,14 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
 
 mccsResult_t mccsCommDestroy(mccsComm_t comm) {
   if (!comm) return mccsSuccess;
-  std::lock_guard<std::mutex> g(g_ctx.mu);
+  std::unique_lock<std::mutex> g(g_ctx.mu);
   mccsResult_t r = mccsSuccess;
   if (g_ctx.connected) {
     proto::AnyMsg m;
     memset(&m, 0, sizeof m);
     m.h.type = proto::kCommDestroy;
     m.comm_destroy.comm_handle = comm->handle;
-    r = roundtrip(m, sizeof(proto::CommDestroyReq), proto::kCommDestroyReply, nullptr, 60000);
+    r = roundtrip(g, m, sizeof(proto::CommDestroyReq), proto::kCommDestroyReply, nullptr, 60000);
   }
   if (comm->event_owned && comm->backend_event && g_drv.ok) {
     CtxScope scope(comm->device);
@@ -660,11 +704,11 @@ mccsResult_t mccsCommSize(mccsComm_t comm, int* n) { if (!comm || !n) return mcc
 uint64_t mccsCommHandle(mccsComm_t comm) { return comm ? comm->handle : 0; }
 
 mccsResult_t mccsRegisterStream(int device, mccsStream_t stream) {
-  std::lock_guard<std::mutex> g(g_ctx.mu);
-  mccsResult_t r = ensure_connected_locked(nullptr);
+  std::unique_lock<std::mutex> g(g_ctx.mu);
+  mccsResult_t r = ensure_connected_locked(g, nullptr);
   if (r != mccsSuccess) return r;
   StreamRec* rec = nullptr;
-  return register_stream_locked(device, stream, &rec);
+  return register_stream_locked(g, device, stream, &rec);
 }
 
 mccsResult_t mccsAllReduceEx(mccsComm_t comm, const void* send, void* recv, size_t count, mccsDataType_t dtype,
@@ -737,13 +781,13 @@ mccsResult_t mccsGroupEnd(void) {
 
 mccsResult_t mccsCommQuery(mccsComm_t comm, mccsCommInfo_t* info) {
   if (!comm || !info) return mccsInvalidArgument;
-  std::lock_guard<std::mutex> g(g_ctx.mu);
+  std::unique_lock<std::mutex> g(g_ctx.mu);
   if (!g_ctx.connected) return mccsNotConnected;
   proto::AnyMsg m;
   memset(&m, 0, sizeof m);
   m.h.type = proto::kCommQuery;
   m.comm_query.comm_handle = comm->handle;
-  mccsResult_t r = roundtrip(m, sizeof(proto::CommQueryReq), proto::kCommQueryReply, nullptr, 30000);
+  mccsResult_t r = roundtrip(g, m, sizeof(proto::CommQueryReq), proto::kCommQueryReply, nullptr, 30000);
   if (r != mccsSuccess) return r;
   info->async_error = m.comm_query_reply.async_error;
   info->device_error = m.comm_query_reply.device_error;

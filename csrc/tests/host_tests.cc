@@ -1,0 +1,348 @@
+// Host-side unit tests of the native code (no GPU needed): IPC rings, fd passing,
+// TOML/JSON, configuration schema, planner rules, ring step accounting, the QoS
+// arbiter on a simulated clock, CPU list parsing. The reference has unit tests only
+// for its in-process channel (src/ipc/core/src/channel/flavors/sequential.rs:85-108).
+// Run by tests/test_native_host.py; exit code = number of failed checks.
+#include <stdio.h>
+#include <string.h>
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <thread>
+
+#include "../common/protocol.h"
+#include "../common/value.h"
+#include "../daemon/config.h"
+#include "../daemon/planner.h"
+#include "../daemon/qos.h"
+#include "../daemon/runtime.h"
+#include "../ipc/shm_ring.h"
+#include "../ipc/uds.h"
+#include "../kernels/dev_types.h"
+
+using namespace mccs;
+
+static int g_failed = 0, g_checks = 0;
+#define CHECK(cond)                                                      \
+  do {                                                                   \
+    g_checks++;                                                          \
+    if (!(cond)) { g_failed++; printf("FAIL %s:%d: %s\n", __FILE__, __LINE__, #cond); } \
+  } while (0)
+
+static void test_ring() {
+  const size_t bytes = ipc::Ring::bytes_needed(8, 64);
+  std::vector<uint8_t> mem(bytes + 64);
+  void* base = (void*)(((uintptr_t)mem.data() + 63) & ~(uintptr_t)63);
+  ipc::Ring prod, cons;
+  prod.init(base, 8, 64);
+  cons.attach(base);
+  uint8_t item[64], out[64];
+  CHECK(cons.empty());
+  CHECK(!cons.try_pop(out));
+  for (int i = 0; i < 8; i++) { memset(item, i, 64); CHECK(prod.try_push(item)); }
+  CHECK(!prod.try_push(item));   // full
+  CHECK(cons.size() == 8);
+  for (int i = 0; i < 8; i++) { CHECK(cons.try_pop(out)); CHECK(out[0] == i && out[63] == i); }
+  // wrap-around under concurrency
+  const int total = 200000;
+  std::thread t([&] {
+    uint8_t it[64];
+    for (int i = 0; i < total;) { memcpy(it, &i, 4); if (prod.try_push(it)) i++; }
+  });
+  int expect = 0, bad = 0;
+  while (expect < total) {
+    if (cons.try_pop(out)) { int v; memcpy(&v, out, 4); bad += v != expect; expect++; }
+  }
+  t.join();
+  CHECK(bad == 0);
+}
+
+static void test_uds_fd_passing() {
+  char path[64];
+  snprintf(path, sizeof path, "/tmp/mccs-ut-%d.sock", (int)getpid());
+  int lfd = ipc::uds_listen(path);
+  CHECK(lfd >= 0);
+  pid_t pid = fork();
+  if (pid == 0) {
+    int fd = ipc::uds_connect(path);
+    int mfd = ipc::memfd_make("ut", 4096);
+    char* p = (char*)ipc::map_shared(mfd, 4096);
+    strcpy(p, "through the fd");
+    const char msg[] = "hello";
+    ipc::uds_send(fd, msg, sizeof msg, &mfd, 1);
+    char ack[8];
+    ipc::wait_readable(fd, 2000);
+    ipc::uds_recv(fd, ack, sizeof ack);
+    _exit(0);
+  }
+  int cfd = -1;
+  for (int i = 0; i < 200 && cfd < 0; i++) { cfd = ipc::uds_accept(lfd); if (cfd < 0) usleep(5000); }
+  CHECK(cfd >= 0);
+  ipc::PeerCred cred{};
+  CHECK(ipc::uds_peer_cred(cfd, &cred) == 0);
+  CHECK(cred.pid == pid);
+  char buf[32];
+  std::vector<int> fds;
+  CHECK(ipc::wait_readable(cfd, 2000) == 1);
+  ssize_t n = ipc::uds_recv(cfd, buf, sizeof buf, &fds);
+  CHECK(n == 6 && !strcmp(buf, "hello"));
+  CHECK(fds.size() == 1);
+  if (!fds.empty()) {
+    char* p = (char*)ipc::map_shared(fds[0], 4096);
+    CHECK(p && !strcmp(p, "through the fd"));
+    close(fds[0]);
+  }
+  ipc::uds_send(cfd, "ok", 3);
+  int st = 0;
+  waitpid(pid, &st, 0);
+  // Peer death shows as end of stream.
+  CHECK(ipc::wait_readable(cfd, 1000) == 1);
+  CHECK(ipc::uds_recv(cfd, buf, sizeof buf) == 0);
+  close(cfd);
+  close(lfd);
+  unlink(path);
+}
+
+static void test_toml_json() {
+  const char* text =
+      "a = 1\nname = \"x y\" # comment\nf = 2.5\nflag = true\narr = [1, 2,\n 3]\n"
+      "[t.sub]\nk = 'lit'\n[[items]]\nid = 1\nring = [0,1]\n[[items]]\nid = 2\n"
+      "inline = { p = 1, q = [ [1,2,3], [4,5,6] ], s = \"z\" }\n[qos_schedule.schedule.99]\nmode = \"Allow\"\n";
+  Value v = parse_toml(text);
+  CHECK(v["a"].as_int() == 1);
+  CHECK(v["name"].as_string() == "x y");
+  CHECK(v["f"].as_double() == 2.5);
+  CHECK(v["flag"].as_bool());
+  CHECK(v["arr"].size() == 3 && v["arr"].at(2).as_int() == 3);
+  CHECK(v["t"]["sub"]["k"].as_string() == "lit");
+  CHECK(v["items"].size() == 2 && v["items"].at(1)["id"].as_int() == 2);
+  CHECK(v["items"].at(1)["inline"]["q"].at(1).at(2).as_int() == 6);
+  CHECK(v["qos_schedule"]["schedule"]["99"]["mode"].as_string() == "Allow");
+  Value back = parse_json(v.to_json());
+  CHECK(back.to_json() == v.to_json());
+  bool threw = false;
+  try { parse_toml("a = \n"); } catch (const ParseError&) { threw = true; }
+  CHECK(threw);
+  threw = false;
+  try { parse_toml("a = 1\na = 2\n"); } catch (const ParseError&) { threw = true; }
+  CHECK(threw);
+  CHECK(parse_json("{\"k\": [1, 2.5, \"s\\n\", null, true]}")["k"].at(2).as_string() == "s\n");
+}
+
+static void test_config() {
+  // The reference's shipped file must load unchanged.
+  Config c = Config::from_string(
+      "mccs_daemon_basename = \"mccs-deamon\"\nmccs_daemon_prefix = \"/tmp/mccs-${USER}\"\n"
+      "addrs = [\"0.0.0.0\", \"192.168.211.2\"]\nlisten_port = 5000\n"
+      "[control]\nprefix = \"/tmp/mccs-${USER}\"\npath = \"control.sock\"\n"
+      "[comm_default_config]\nbuffer_sizes = [4194304]\nchannel_count = 2\n"
+      "[comm_global_config]\n[comm_global_config.net_rdma]\ngid_index = 3\n[comm_global_config.shm]\nlocality = \"Sender\"\n"
+      "[qos_schedule]\nepoch_microsecs = 85000\n[qos_schedule.schedule.99]\nintervals = [[0, 35000]]\nmode = \"Allow\"\n"
+      "[qos_schedule.schedule.100]\nintervals = [[35000, 69000]]\nmode = \"Deny\"\nenforce_step = 2\n"
+      "[[comm_patterns_override]]\ncommunicator_id = 138\n"
+      "channels = [ { channel_id = 0, ring = [0,1,2,3], udp_sport = [[3,4,49200]], net_dev = \"mlx5_0\" },\n"
+      "             { channel_id = 1, ring = [3,2,1,0] } ]\nib_traffic_class = 106\n");
+  CHECK(c.channel_count == 2);
+  CHECK(c.buffer_sizes[0] == 4194304);
+  CHECK(c.qos_epoch_us == 85000);
+  CHECK(c.qos_schedule.size() == 2);
+  CHECK(c.qos_schedule[99].allow && c.qos_schedule[99].intervals[0].second == 35000);
+  CHECK(!c.qos_schedule[100].allow && c.qos_schedule[100].enforce_step == 2);
+  CHECK(c.overrides.size() == 1);
+  CHECK(c.find_override(138) && c.find_override(138)->channels[1].ring[0] == 3);
+  CHECK(c.find_override(138)->ib_traffic_class == 106);
+  CHECK(!c.find_override(7));
+  CHECK(c.control_socket_path().find("${") == std::string::npos);
+  CHECK(c.control_socket_path().rfind("/control.sock") != std::string::npos);
+  bool threw = false;
+  try { Config::from_string("bogus_key = 1\n"); } catch (const std::exception&) { threw = true; }
+  CHECK(threw);   // unknown top-level keys are rejected
+  Config d = Config::from_string("[b200]\ntransport = \"host_staged\"\nwait_timeout_ms = 500\n[qos.tenants.7]\nweight = 2.0\npriority = 1\n");
+  CHECK(d.transport == "host_staged" && d.wait_timeout_ms == 500);
+  CHECK(d.qos_tenants[7].weight == 2.0 && d.qos_tenants[7].priority == 1);
+}
+
+static void test_planner() {
+  Planner p;
+  p.load_defaults(true);
+  PlanInput in;
+  in.kind = kAllReduce; in.nranks = 8; in.dtype = kBfloat16; in.op = kSum;
+  in.count = 256u << 20; in.nvls_possible = true;
+  Plan pl = p.plan(in);
+  CHECK(pl.status == 0 && pl.variant == kArNvlsTwo && pl.needs_mc_send && pl.needs_mc_recv);
+  in.nvls_possible = false;
+  pl = p.plan(in);
+  CHECK(pl.variant == kArTwoShot);
+  // small + out of place: one-shot family; in place forbids it
+  in.count = 4096; in.nvls_possible = true;
+  CHECK(p.plan(in).variant == kArNvlsOne);
+  in.in_place = true;
+  CHECK(p.plan(in).variant != kArNvlsOne && p.plan(in).variant != kArOneShot);
+  in.in_place = false;
+  // integer types and max never go to NVLS
+  in.dtype = kInt32; in.count = 1 << 24;
+  CHECK(!variant_is_nvls(p.plan(in).variant));
+  in.dtype = kFloat32; in.op = kMax;
+  CHECK(!variant_is_nvls(p.plan(in).variant));
+  in.op = kSum;
+  // host-staged transport: ring only, channel count from the configuration
+  in.host_staged = true; in.ring_channels = 2;
+  pl = p.plan(in);
+  CHECK(pl.variant == kArRing && pl.dims.ctas == 2);
+  in.count = 1024;   // tiny: one channel, small CTA (plan.rs:602-635)
+  pl = p.plan(in);
+  CHECK(pl.variant == kArRing && pl.dims.ctas == 1 && pl.dims.threads >= 64);
+  in.host_staged = false;
+  // requested variant honoured when feasible, replaced (with a note) when not
+  in.count = 1 << 20; in.requested_variant = kArRing;
+  CHECK(p.plan(in).variant == kArRing);
+  in.requested_variant = kAgPull;
+  pl = p.plan(in);
+  CHECK(pl.variant != kAgPull && !pl.note.empty());
+  in.requested_variant = kAuto;
+  // QoS cap and override
+  in.count = 256u << 20; in.cta_cap = 5;
+  CHECK(p.plan(in).dims.ctas == 5);
+  in.cta_cap = 0; in.requested_ctas = 24;
+  CHECK(p.plan(in).dims.ctas == 24);
+  in.requested_ctas = 0;
+  // single rank
+  in.nranks = 1;
+  CHECK(p.plan(in).variant == kLocalCopy);
+  // all-gather
+  PlanInput g;
+  g.kind = kAllGather; g.nranks = 4; g.count = 64 << 20; g.nvls_possible = true;
+  CHECK(p.plan(g).variant == kAgNvls);
+  g.aligned16 = false;
+  CHECK(p.plan(g).variant != kAgNvls);
+  // tuning table round trip and override
+  std::string err;
+  Value t = parse_json("{\"allreduce\": {\"8\": [[65536, \"ar_oneshot\", 4, 256], [-1, \"ar_twoshot\", 48, 512]]}}");
+  CHECK(p.load_json(t, &err));
+  PlanInput q;
+  q.kind = kAllReduce; q.nranks = 8; q.dtype = kFloat32; q.count = 1 << 24;
+  pl = p.plan(q);
+  CHECK(pl.variant == kArTwoShot && pl.dims.ctas == 48);
+  q.count = 1024;
+  pl = p.plan(q);
+  CHECK(pl.variant == kArOneShot && pl.dims.threads == 256);
+  CHECK(!p.load_json(parse_json("{\"allreduce\": {\"8\": [[1, \"nope\", 4]]}}"), &err));
+  Planner p2;
+  CHECK(p2.load_json(p.to_json(), &err));
+  CHECK(p2.to_json().to_json() == p.to_json().to_json());
+}
+
+static void test_ring_steps() {
+  // 8 ranks, 1 channel, 512 KiB slots: a 16 MiB fp32 all-reduce needs
+  // ceil(4Mi elems / (131072*8)) = 4 loops of 2*(8-1) steps.
+  CHECK(ring_loops(kAllReduce, 4u << 20, 4, 8, 1, 512 << 10) == 4);
+  CHECK(ring_steps_per_channel(kAllReduce, 4u << 20, 4, 8, 1, 512 << 10) == 4 * 14);
+  CHECK(ring_steps_per_channel(kAllReduce, 4u << 20, 4, 8, 2, 512 << 10) == 2 * 14);
+  CHECK(ring_steps_per_channel(kAllGather, 1 << 20, 1, 4, 2, 512 << 10) == 1 * 3);
+  CHECK(ring_steps_per_channel(kAllReduce, 0, 4, 8, 1, 512 << 10) == 0);
+  CHECK(ring_steps_per_channel(kAllReduce, 1, 2, 2, 1, 512 << 10) == 2);
+}
+
+static void test_qos() {
+  // Windows: the reference's Allow/Deny semantics on now % epoch.
+  QosIntervalConfig allow;
+  allow.intervals = {{0, 35000}};
+  CHECK(QosArbiter::window_allows(allow, 85000, 10, 0));
+  CHECK(!QosArbiter::window_allows(allow, 85000, 40000, 0));
+  CHECK(QosArbiter::window_allows(allow, 85000, 85000 + 34999, 0));
+  QosIntervalConfig deny = allow;
+  deny.allow = false;
+  CHECK(!QosArbiter::window_allows(deny, 85000, 10, 0));
+  CHECK(QosArbiter::window_allows(deny, 85000, 40000, 0));
+  allow.enforce_step = 2;
+  CHECK(QosArbiter::window_allows(allow, 85000, 40000, 1));    // odd rounds are not gated
+  CHECK(!QosArbiter::window_allows(allow, 85000, 40000, 2));
+
+  Config cfg;
+  cfg.qos_tenants[1].weight = 2.0;
+  cfg.qos_tenants[2].weight = 1.0;
+  cfg.qos_cta_budget = 60;
+  cfg.qos_max_outstanding_bytes = 32u << 20;
+  QosArbiter q;
+  q.configure(cfg);
+  q.tenant_register(1, {0, 1});
+  q.tenant_register(2, {1, 2});
+  q.tenant_register(3, {5});
+  uint64_t now = 1000;
+  // Alone: no cap, always admitted.
+  CHECK(q.cta_cap(1, now) == 0);
+  CHECK(q.admit(1, 8 << 20, now, 0) == kQosAdmit);
+  q.complete(1, 8 << 20);
+  // Contention: tenants 1 and 2 share device 1; tenant 3 does not take part.
+  q.note_waiting(2, now);
+  CHECK(q.contenders(1, now) == 1);
+  CHECK(q.contenders(3, now) == 0);
+  CHECK(q.cta_cap(1, now) == 40);   // 60 * 2/3
+  CHECK(q.cta_cap(2, now) == 20);
+  CHECK(q.cta_cap(3, now) == 0);
+  CHECK(q.slice_bytes(1, now) > 0 && q.slice_bytes(3, now) == 0);
+  // Weighted fair queueing: with both always backlogged, admitted bytes approach 2:1.
+  uint64_t b1 = 0, b2 = 0;
+  const uint64_t sz = 8 << 20;
+  for (int round = 0; round < 300; round++) {
+    now += 100;
+    q.note_waiting(1, now);
+    q.note_waiting(2, now);
+    if (q.admit(1, sz, now, 0) == kQosAdmit) { b1 += sz; q.complete(1, sz); }
+    q.note_waiting(1, now);
+    if (q.admit(2, sz, now, 0) == kQosAdmit) { b2 += sz; q.complete(2, sz); }
+  }
+  const double ratio = (double)b1 / (double)b2;
+  CHECK(ratio > 1.7 && ratio < 2.3);
+  // Backlog bound: outstanding bytes of a contended tenant are limited.
+  QosArbiter r;
+  r.configure(cfg);
+  r.tenant_register(1, {0});
+  r.tenant_register(2, {0});
+  r.note_waiting(2, 10);
+  int admitted = 0;
+  for (int i = 0; i < 10; i++) admitted += r.admit(1, 16u << 20, 10, 0) == kQosAdmit;
+  CHECK(admitted == 2);   // 32 MiB outstanding allowed
+  r.complete(1, 16u << 20);
+  CHECK(r.admit(1, 16u << 20, 11, 0) != kQosDeferBacklog);
+  // Window schedule applied at admission.
+  std::map<uint32_t, QosIntervalConfig> sched;
+  sched[1].intervals = {{0, 1000}};
+  r.set_schedule(10000, sched);
+  r.complete(1, 64u << 20);
+  // Tenant 2 was waiting all along and is behind in virtual time: it goes first.
+  CHECK(r.admit(1, 1024, 12, 500) == kQosDeferFairness);
+  CHECK(r.admit(2, 48u << 20, 12, 500) == kQosAdmit);
+  r.complete(2, 48u << 20);
+  CHECK(r.admit(1, 1024, 12, 5000) == kQosDeferWindow);
+  CHECK(r.admit(1, 1024, 12, 10500) == kQosAdmit);
+  r.set_enabled(false);
+  CHECK(r.admit(1, 1024, 12, 5000) == kQosAdmit);
+  CHECK(r.stats()["tenants"]["1"]["deferred_window"].as_int() == 1);
+}
+
+static void test_misc() {
+  std::vector<int> c = parse_cpu_list("0-3,8,10-11");
+  CHECK(c.size() == 7 && c[4] == 8 && c[6] == 11);
+  CHECK(parse_cpu_list("").empty());
+  CHECK(sizeof(proto::WorkRequest) == 128 && sizeof(proto::WorkCompletion) == 64);
+  CHECK(proto::handle_comm_id(proto::make_comm_handle(138, 5)) == 138);
+  CHECK(proto::handle_rank(proto::make_comm_handle(138, 5)) == 5);
+  CHECK(sizeof(StatusBlock) == 64);
+  CHECK(sizeof(CollArgs) < 4000);   // must fit the kernel parameter space
+  CHECK(Planner::variant_from_name("ar_nvls_twoshot") == kArNvlsTwo);
+  CHECK(Planner::variant_from_name("whatever") == -1);
+}
+
+int main() {
+  test_ring();
+  test_uds_fd_passing();
+  test_toml_json();
+  test_config();
+  test_planner();
+  test_ring_steps();
+  test_qos();
+  test_misc();
+  printf("%d checks, %d failed\n", g_checks, g_failed);
+  return g_failed;
+}

@@ -1,0 +1,142 @@
+"""Starting and stopping the service daemon from Python.
+
+Two ways, both ending with a control socket that clients connect to:
+
+* :func:`start_embedded` runs the daemon as native threads inside the calling
+  process (``libmccs_daemon.so``). The launcher rank of a ``torchrun`` job does this
+  so that no separate service has to be started by hand; the kernels are then
+  launched from this process.
+* :func:`spawn` starts the stand-alone ``mccsd`` binary the way the reference is
+  run (``mccs --host <idx> --config mccs.toml``, ``src/mccs/src/main.rs:16-24``).
+
+The configuration is the reference's ``mccs.toml`` schema plus a ``[b200]`` table;
+see ``csrc/daemon/config.h``.
+"""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import time
+from typing import Optional
+
+from . import _lib
+
+_embedded_path: Optional[str] = None
+
+
+def default_config(prefix: str, *, transport: str = "auto", nvls: bool = True, channel_count: int = 2,
+                   wait_timeout_ms: int = 10000, host_devices: int = 8, force_host: bool = False,
+                   listen_port: int = -1, trace: bool = False, extra: str = "") -> str:
+    """TOML text of a daemon configuration with its sockets under ``prefix``."""
+    return f"""
+listen_port = {listen_port}
+mccs_daemon_prefix = "{prefix}"
+[control]
+prefix = "{prefix}"
+path = "control.sock"
+[comm_default_config]
+buffer_sizes = [4194304]
+channel_count = {channel_count}
+[b200]
+transport = "{transport}"
+nvls = {"true" if nvls else "false"}
+wait_timeout_ms = {wait_timeout_ms}
+host_devices = {host_devices}
+force_host_backend = {"true" if force_host else "false"}
+trace = {"true" if trace else "false"}
+{extra}
+"""
+
+
+def start_embedded(config_toml: Optional[str] = None, *, prefix: Optional[str] = None, **kw) -> str:
+    """Start the in-process daemon (idempotent) and return its control socket path.
+
+    Also points this process's client shim at it through ``MCCS_CONTROL``.
+    """
+    global _embedded_path
+    lib = _lib.daemon_lib()
+    if config_toml is None:
+        prefix = prefix or f"/tmp/mccs-{os.getuid()}-{os.getpid()}"
+        config_toml = default_config(prefix, **kw)
+    rc = lib.mccsd_start(config_toml.encode())
+    if rc != 0:
+        raise RuntimeError(f"embedded mccs daemon failed to start (status {rc})")
+    _embedded_path = lib.mccsd_control_path().decode()
+    os.environ["MCCS_CONTROL"] = _embedded_path
+    return _embedded_path
+
+
+def stop_embedded() -> None:
+    global _embedded_path
+    if _embedded_path is not None:
+        _lib.daemon_lib().mccsd_stop()
+        _embedded_path = None
+
+
+def embedded_admin(body: dict, type_: int = 2) -> dict:
+    """Admin request to the in-process daemon without going through TCP."""
+    out = _lib.daemon_lib().mccsd_admin(type_, json.dumps(body).encode())
+    return json.loads(out.decode())
+
+
+def embedded_admin_port() -> int:
+    return int(_lib.daemon_lib().mccsd_admin_port())
+
+
+def embedded_backend() -> str:
+    k = _lib.daemon_lib().mccsd_backend_kind()
+    return {0: "host", 1: "cuda"}.get(k, "none")
+
+
+def describe_embedded() -> str:
+    return _lib.daemon_lib().mccsd_describe().decode()
+
+
+class SpawnedDaemon:
+    """A stand-alone ``mccsd`` child process."""
+
+    def __init__(self, proc: subprocess.Popen, control: str, admin_port: int, backend: str):
+        self.proc = proc
+        self.control = control
+        self.admin_port = admin_port
+        self.backend = backend
+
+    def stop(self, timeout: float = 10.0) -> int:
+        if self.proc.poll() is None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+                self.proc.wait()
+        return self.proc.returncode
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.stop()
+
+
+def spawn(config_path: str, *, env: Optional[dict] = None, timeout: float = 120.0) -> SpawnedDaemon:
+    """Start ``mccsd --config config_path`` and wait until it accepts clients."""
+    exe = os.path.join(_lib.NATIVE_DIR, "mccsd")
+    if not os.path.exists(exe):
+        raise FileNotFoundError(f"{exe} is missing: run `make -j` at the repository root")
+    e = dict(os.environ)
+    if env:
+        e.update(env)
+    proc = subprocess.Popen([exe, "--config", config_path], stdout=subprocess.PIPE, env=e, text=True)
+    deadline = time.time() + timeout
+    while time.time() < deadline:
+        line = proc.stdout.readline()
+        if not line:
+            if proc.poll() is not None:
+                raise RuntimeError(f"mccsd exited with {proc.returncode} before it was ready")
+            continue
+        if line.startswith("MCCSD_READY"):
+            fields = dict(f.split("=", 1) for f in line.split()[1:])
+            return SpawnedDaemon(proc, fields["control"], int(fields["admin_port"]), fields["backend"])
+    proc.kill()
+    raise TimeoutError("mccsd did not become ready")

@@ -1,0 +1,200 @@
+"""End-to-end tests of the service on the host backend (no GPU): client shim ->
+control socket -> daemon -> per-device proxies -> rendezvous -> planner -> QoS
+admission -> CPU collectives. Ranks are threads of the test process; every rank
+owns a communicator handle and its own request/completion rings, like separate
+applications would."""
+import torch
+import pytest
+
+from helpers import fresh_comm_id, run_ranks
+
+FLOAT_TYPES = [torch.float32, torch.float64, torch.float16, torch.bfloat16]
+INT_TYPES = [torch.int32, torch.int64, torch.int8, torch.uint8]
+
+
+def _make(dtype, count, seed):
+    g = torch.Generator().manual_seed(seed)
+    if dtype.is_floating_point:
+        return (torch.rand(count, generator=g) * 2 - 1).to(dtype)
+    hi = 5 if dtype in (torch.int8, torch.uint8) else 1000
+    lo = 0 if dtype == torch.uint8 else -hi
+    return torch.randint(lo, hi, (count,), generator=g).to(dtype)
+
+
+@pytest.mark.parametrize("nranks", [1, 2, 4, 8])
+@pytest.mark.parametrize("dtype", FLOAT_TYPES + INT_TYPES)
+def test_allreduce_sum(service, nranks, dtype):
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    cid, count = fresh_comm_id(), 3001
+
+    def rank_fn(r):
+        buf, out = M.Buffer(count * 8, r), M.Buffer(count * 8, r)
+        x = _make(dtype, count, r)
+        s, d = buf.tensor(dtype, count), out.tensor(dtype, count)
+        s.copy_(x)
+        c = M.Communicator(cid, r, nranks, device=r)
+        c.all_reduce(s, d)
+        res = d.clone()
+        c.all_reduce(s)   # in place
+        inplace = s.clone()
+        c.destroy()
+        return x, res, inplace
+
+    outs = run_ranks(nranks, rank_fn)
+    if dtype.is_floating_point:
+        want = sum(o[0].double() for o in outs)
+        tol = {torch.float32: 1e-5, torch.float64: 1e-12}.get(dtype, 2e-2)
+        for _, res, inplace in outs:
+            assert torch.allclose(res.double(), want, rtol=tol, atol=tol * nranks)
+            assert torch.equal(res, inplace)
+    else:
+        want = sum(o[0].to(torch.int64) for o in outs).to(dtype)
+        for _, res, inplace in outs:
+            assert torch.equal(res, want)
+            assert torch.equal(inplace, want)
+
+
+@pytest.mark.parametrize("op", ["prod", "max", "min", "avg", "premulsum"])
+def test_allreduce_ops(service, op):
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    n, count, cid = 4, 777, fresh_comm_id()
+
+    def rank_fn(r):
+        buf = M.Buffer(count * 4, r)
+        x = _make(torch.float32, count, 10 + r) + 1.5
+        s = buf.tensor(torch.float32, count)
+        s.copy_(x)
+        c = M.Communicator(cid, r, n, device=r)
+        c.all_reduce(s, op=op, scale=0.5)
+        c.destroy()
+        return x, s.clone()
+
+    outs = run_ranks(n, rank_fn)
+    xs = torch.stack([o[0] for o in outs])
+    want = {"prod": xs.prod(0), "max": xs.max(0).values, "min": xs.min(0).values, "avg": xs.sum(0) / n,
+            "premulsum": (xs * 0.5).sum(0)}[op]
+    for _, got in outs:
+        assert torch.allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 8])
+def test_allgather(service, nranks):
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    cid, per = fresh_comm_id(), 1000
+
+    def rank_fn(r):
+        out = M.Buffer(per * 4 * nranks, r)
+        full = out.tensor(torch.float32, per * nranks)
+        full.zero_()
+        mine = full[r * per:(r + 1) * per]
+        mine.copy_(torch.arange(per, dtype=torch.float32) + r * 1e6)   # values of BASELINE config 1
+        c = M.Communicator(cid, r, nranks, device=r)
+        c.all_gather(mine, full)        # in place: send = recv + rank*bytes
+        c.destroy()
+        return full.clone()
+
+    outs = run_ranks(nranks, rank_fn)
+    want = torch.cat([torch.arange(per, dtype=torch.float32) + r * 1e6 for r in range(nranks)])
+    for got in outs:
+        assert torch.equal(got, want)
+
+
+def test_config1_two_rank_reference_shapes(service):
+    """BASELINE configuration 1: 2 ranks, AllReduce sum fp32 count=262144 of N(0,1)
+    (seed 0) and AllGather fp32 of 65536 per rank with rank*1e6+index."""
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    cid = fresh_comm_id()
+    g = torch.Generator().manual_seed(0)
+    data = [torch.randn(262144, generator=g) for _ in range(2)]
+
+    def rank_fn(r):
+        a, b = M.Buffer(262144 * 4, r), M.Buffer(65536 * 4 * 2, r)
+        s = a.tensor(torch.float32, 262144)
+        s.copy_(data[r])
+        c = M.Communicator(cid, r, 2, device=r)
+        c.all_reduce(s, algo="ar_ring")
+        full = b.tensor(torch.float32, 65536 * 2)
+        full[r * 65536:(r + 1) * 65536] = torch.arange(65536, dtype=torch.float32) + r * 1e6
+        c.all_gather(full[r * 65536:(r + 1) * 65536], full, algo="ag_ring")
+        plan = c.last_plan()
+        c.destroy()
+        return s.clone(), full.clone(), plan
+
+    outs = run_ranks(2, rank_fn)
+    want = (data[0].double() + data[1].double()).float()
+    for s, full, plan in outs:
+        assert torch.allclose(s, want, rtol=1e-5, atol=1e-6)
+        assert torch.equal(full, torch.cat([torch.arange(65536, dtype=torch.float32) + r * 1e6 for r in range(2)]))
+        assert plan[0] == "ag_ring"
+
+
+def test_back_to_back_and_group(service):
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    n, cid, count = 4, fresh_comm_id(), 512
+    import threading
+    done = threading.Barrier(n)
+
+    def rank_fn(r):
+        bufs = [M.Buffer(count * 4, r) for _ in range(16)]
+        ts = [b.tensor(torch.float32, count) for b in bufs]
+        for i, t in enumerate(ts):
+            t.fill_(float(r + i))
+        c = M.Communicator(cid, r, n, device=r)
+        with M.group():                       # 16 back-to-back all-reduces, one completion wait
+            for t in ts:
+                c.all_reduce(t)
+        for _ in range(200):                  # more than the ring depth and the slot count
+            c.all_reduce(ts[0])
+        q = c.query()
+        done.wait()     # a communicator whose peers have left reports that as an error
+        c.destroy()
+        return [t.clone() for t in ts], q
+
+    outs = run_ranks(n, rank_fn)
+    for ts, q in outs:
+        for i in range(1, 16):
+            assert torch.all(ts[i] == sum(r + i for r in range(n)))
+        assert q["launched"] == 216 and q["async_error"] == 0
+
+
+def test_mismatch_is_an_error_not_a_hang(service):
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    cid = fresh_comm_id()
+
+    def rank_fn(r):
+        buf = M.Buffer(4096, r)
+        t = buf.tensor(torch.float32, 1024)
+        c = M.Communicator(cid, r, 2, device=r)
+        try:
+            c.all_reduce(t, count=1024 if r == 0 else 512)
+            return None
+        except M.client._lib.MccsError as e:
+            return e.code
+        finally:
+            c.destroy()
+
+    codes = run_ranks(2, rank_fn)
+    assert codes == [-8, -8]      # mccsMismatch on both ranks
+
+
+def test_buffer_must_come_from_the_service(service):
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    c = M.Communicator(fresh_comm_id(), 0, 1, device=0)
+    t = torch.zeros(16)
+    with pytest.raises(M.client._lib.MccsError):
+        c.all_reduce(t)
+    c.destroy()
