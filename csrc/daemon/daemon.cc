@@ -733,10 +733,9 @@ void Daemon::on_comm_destroy(Session& s, const proto::CommDestroyReq& m) {
     detach_rank(*c, rank, proto::kOk);
     last = true;
     for (auto& rr : c->ranks) if (rr && !rr->gone.load()) last = false;
-    if (!last && c->state.load() == kCommActive) {
-      c->async_error.store(proto::kErrPeerLost);
-      c->state.store(kCommError);
-    }
+    // No error is recorded: the communicator just stops taking work. A rank that
+    // still submits afterwards gets "peer lost" for that request.
+    if (!last && c->state.load() == kCommActive) c->state.store(kCommError);
   }
   if (last) destroy_communicator(id);
   reply(s, r, sizeof(proto::CommDestroyReply));

@@ -90,7 +90,7 @@ bool ProxyEngine::intake(RankState& rs) {
       memset(&wc, 0, sizeof wc);
       wc.kind = rs.pending_wr.kind;
       int err = rs.comm->async_error.load();
-      wc.status = err ? err : proto::kErrAborted;
+      wc.status = err ? err : proto::kErrPeerLost;
       wc.user_seq = rs.pending_wr.user_seq;
       if (!rs.cq.try_push(&wc)) { rs.pending_wc = wc; rs.have_pending_wc = true; }
       rs.have_pending_wr = false;
@@ -473,7 +473,7 @@ bool ProxyEngine::advance(RankState& rs) {
     if (c.state.load(std::memory_order_acquire) == kCommError) {
       // A failed communicator never launches again; what was posted completes in error.
       int err = c.async_error.load();
-      complete_request(rs, s, seq, err ? err : proto::kErrAborted);
+      complete_request(rs, s, seq, err ? err : proto::kErrPeerLost);
       rs.next_launch_seq++;
       rs.next_slice = 0;
       any = true;
