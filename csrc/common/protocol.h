@@ -16,7 +16,7 @@ namespace mccs {
 namespace proto {
 
 constexpr uint32_t kMagic = 0x5343434du;  // "MCCS"
-constexpr uint32_t kVersion = 3;
+constexpr uint32_t kVersion = 4;
 constexpr uint32_t kWqDepth = 64;
 constexpr uint32_t kCqDepth = 64;
 constexpr uint32_t kWrBytes = 128;
@@ -51,6 +51,21 @@ enum Status : int32_t {
 
 enum Backend : uint32_t { kBackendHost = 0, kBackendCuda = 1 };
 
+// How a collective is ordered against the caller's CUDA stream.
+//  kSyncEvents: two interprocess events per request, as the reference does
+//    (src/libmccs/src/collectives.rs:23-25,68-70): the caller records "submitted",
+//    waits for the daemon's completion message, then makes its stream wait for the
+//    daemon's "done" event. One blocking round trip per collective.
+//  kSyncMemOps: two 64-bit semaphores in device memory shared by caller and daemon,
+//    driven by stream memory operations. The caller enqueues "write submitted" and
+//    "wait done" on its stream and returns at once; the daemon enqueues "wait
+//    submitted", the kernel and "write done" on its stream. No round trip.
+enum SyncMode : uint32_t { kSyncEvents = 0, kSyncMemOps = 1 };
+constexpr uint32_t kSyncDoneSlot = 0;        // u64 index of the "done" semaphore in the sync page
+constexpr uint32_t kSyncFirstStreamSlot = 8; // first "submitted" semaphore
+constexpr uint32_t kSyncMaxStreams = 56;
+constexpr uint32_t kSyncPageBytes = 4096;
+
 // How the client maps an allocation the daemon made for it.
 enum ShareKind : uint32_t {
   kShareHostFd = 0,     // memfd: mmap (host backend)
@@ -82,7 +97,7 @@ struct Welcome {
   uint32_t backend;       // Backend
   uint32_t num_devices;
   uint64_t session_id;
-  uint32_t sync_mode;     // 0: IPC events
+  uint32_t sync_mode;     // SyncMode
   uint32_t reserved;
 };
 
@@ -121,7 +136,10 @@ struct CommInitReply {
   uint8_t event_handle[kIpcHandleBytes];  // backend event (IPC) ...
   uint64_t event_raw;                     // ... or its in-process handle
   uint32_t dp_bytes;      // size of the data-path segment passed as fd
-  uint32_t reserved;
+  uint32_t sync_share_kind;               // ShareKind of the sync page (mem-op mode)
+  uint64_t sync_size;                     // 0: no sync page, events are used
+  uint64_t sync_daemon_va;
+  uint8_t sync_ipc_handle[kIpcHandleBytes];
 };
 
 struct CommDestroyReq { Header h; uint64_t comm_handle; };
@@ -181,7 +199,9 @@ struct alignas(64) WorkRequest {
   uint64_t user_seq;    // client-side counter, echoed in the completion
   float scale;          // PreMulSum / SumPostDiv argument
   uint32_t variant;     // Variant requested by the caller (0 = planner decides)
-  uint64_t reserved[5];
+  uint64_t sync_slot;   // mem-op mode: 1 + index of the "submitted" semaphore, 0 = events
+  uint64_t sync_value;  // value the caller's stream writes there before this request
+  uint64_t reserved[3];
 };
 static_assert(sizeof(WorkRequest) == kWrBytes, "work request must fill one 128-byte slot");
 

@@ -108,14 +108,17 @@ Config Config::from_value(const Value& root) {
   if (root.has("b200")) {
     const Value& b = root["b200"];
     check_keys(b,
-               {"transport", "nvls", "vmm", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
-                "host_devices", "force_host_backend", "idle_sleep_us", "pin_threads", "init_timeout_ms"},
+               {"transport", "nvls", "vmm", "sync", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
+                "host_devices", "force_host_backend", "idle_sleep_us", "idle_spin_us", "pin_threads", "init_timeout_ms"},
                "[b200]");
     c.transport = b["transport"].as_string(c.transport);
     if (c.transport != "auto" && c.transport != "nvlink" && c.transport != "host_staged")
       throw std::runtime_error("b200.transport must be auto, nvlink or host_staged");
     c.nvls = b["nvls"].as_bool(c.nvls);
     c.vmm = b["vmm"].as_bool(c.vmm);
+    c.sync = b["sync"].as_string(c.sync);
+    if (c.sync != "auto" && c.sync != "events" && c.sync != "memops")
+      throw std::runtime_error("b200.sync must be auto, events or memops");
     c.wait_timeout_ms = (uint64_t)b["wait_timeout_ms"].as_int((int64_t)c.wait_timeout_ms);
     c.tuning_file = b["tuning_file"].as_string();
     c.trace = b["trace"].as_bool(c.trace);
@@ -123,6 +126,7 @@ Config Config::from_value(const Value& root) {
     c.host_devices = (int)b["host_devices"].as_int(c.host_devices);
     c.force_host_backend = b["force_host_backend"].as_bool(c.force_host_backend);
     c.idle_sleep_us = (int)b["idle_sleep_us"].as_int(c.idle_sleep_us);
+    c.idle_spin_us = (int)b["idle_spin_us"].as_int(c.idle_spin_us);
     c.pin_threads = b["pin_threads"].as_bool(c.pin_threads);
     c.init_timeout_ms = (uint64_t)b["init_timeout_ms"].as_int((int64_t)c.init_timeout_ms);
   }

@@ -72,13 +72,15 @@ struct Config {
   std::string transport = "auto";   // auto | nvlink | host_staged
   bool nvls = true;
   bool vmm = true;
+  std::string sync = "auto";        // auto | events | memops (see proto::SyncMode)
   uint64_t wait_timeout_ms = 10000; // bound of every device-side wait
   std::string tuning_file;
   bool trace = false;
   std::string trace_file;
   int host_devices = 8;
   bool force_host_backend = false;
-  int idle_sleep_us = 50;           // proxy back-off after a stretch of idle polls
+  int idle_sleep_us = 50;           // sleep between polls once a proxy has been idle for idle_spin_us
+  int idle_spin_us = 200000;        // how long an idle proxy keeps busy-polling
   bool pin_threads = true;
   uint64_t init_timeout_ms = 60000; // how long a communicator waits for all its ranks
 

@@ -47,9 +47,12 @@ int Daemon::start(const Config& cfg, std::string* err) {
   bo.allow_vmm = cfg.vmm;
   bo.allow_nvls = cfg.nvls;
   bo.force_host = cfg.force_host_backend;
+  bo.allow_memops = cfg.sync != "events";
   backend_.reset(make_backend(bo));
   if (!backend_) { if (err) *err = "no backend"; return proto::kErrInternal; }
   LOG_INFO("daemon backend: %s", backend_->describe().c_str());
+  memops_ = backend_->memops_supported() && cfg.sync != "events";
+  if (cfg.sync == "memops" && !memops_) LOG_WARN("b200.sync=memops requested but stream memory operations are unavailable; using events");
 
   planner_.load_defaults(backend_->nvls_supported() && cfg.nvls);
   if (!cfg.tuning_file.empty()) {
@@ -81,7 +84,7 @@ int Daemon::start(const Config& cfg, std::string* err) {
     }
   }
 
-  runtimes_.reset(new RuntimeManager(cfg.idle_sleep_us, cfg.pin_threads));
+  runtimes_.reset(new RuntimeManager(cfg.idle_sleep_us, cfg.idle_spin_us, cfg.pin_threads));
   for (int d = 0; d < backend_->device_count(); d++) {
     auto p = std::make_shared<ProxyEngine>(this, d);
     proxies_.push_back(p);
@@ -198,6 +201,7 @@ void Daemon::accept_clients() {
     r.welcome.daemon_pid = (int)getpid();
     r.welcome.backend = backend_->kind();
     r.welcome.num_devices = (uint32_t)backend_->device_count();
+    r.welcome.sync_mode = memops_ ? proto::kSyncMemOps : proto::kSyncEvents;
     LOG_INFO("client %llu attached: pid=%d app=%s%s", (unsigned long long)s->id, s->pid, s->app.c_str(),
              s->same_process ? " (same process)" : "");
     ipc::uds_send(fd, &r, sizeof(proto::Welcome));
@@ -509,7 +513,16 @@ void Daemon::on_comm_init(Session& s, const proto::CommInitReq& m) {
       memcpy(r.comm_init_reply.event_handle, rs.event_handle, sizeof rs.event_handle);
       r.comm_init_reply.event_raw = ps->same_process ? (uint64_t)rs.backend_event : 0;
       r.comm_init_reply.dp_bytes = (uint32_t)rs.dp_bytes;
-      reply(*ps, r, sizeof(proto::CommInitReply), &rs.dp_fd, 1);
+      int fds[2] = {rs.dp_fd, -1};
+      int nfds = 1;
+      if (rs.sync_alloc.va) {
+        r.comm_init_reply.sync_size = rs.sync_alloc.size;
+        r.comm_init_reply.sync_daemon_va = rs.sync_alloc.va;
+        r.comm_init_reply.sync_share_kind = ps->same_process ? proto::kShareSameProcess : rs.sync_alloc.share_kind;
+        memcpy(r.comm_init_reply.sync_ipc_handle, rs.sync_alloc.ipc_handle, sizeof rs.sync_alloc.ipc_handle);
+        if (!ps->same_process && rs.sync_alloc.share_fd >= 0) fds[nfds++] = rs.sync_alloc.share_fd;
+      }
+      reply(*ps, r, sizeof(proto::CommInitReply), fds, nfds);
     } else {
       reply(*ps, r, sizeof(proto::CommInitReply));
     }
@@ -578,6 +591,10 @@ int Daemon::finalize_communicator(Communicator& c) {
     }
     if ((rc = backend_->hostmem_alloc(sizeof(StatusBlock), &p)) != proto::kOk) return rc;
     rs.status = (StatusBlock*)p;
+    if (memops_) {
+      if ((rc = backend_->alloc(rs.device, proto::kSyncPageBytes, &rs.sync_alloc)) != proto::kOk) return rc;
+      if ((rc = backend_->zero_memory(rs.device, rs.sync_alloc.va, proto::kSyncPageBytes)) != proto::kOk) return rc;
+    }
     if ((rc = backend_->stream_create(rs.device, prio, &rs.stream)) != proto::kOk) return rc;
     if ((rc = backend_->event_create(rs.device, &rs.backend_event, rs.event_handle)) != proto::kOk) return rc;
     // Data-path segment: request ring followed by completion ring.
@@ -699,6 +716,7 @@ void Daemon::destroy_communicator(uint32_t comm_id) {
     if (r->pad) backend_->scratch_free(r->device, r->pad, sizeof(SignalPad), c->host_staged);
     if (r->fifo) backend_->scratch_free(r->device, r->fifo, r->fifo_bytes, c->host_staged);
     if (r->status) backend_->hostmem_free(r->status);
+    if (r->sync_alloc.va) backend_->release(&r->sync_alloc);
     if (r->dp_mem) ipc::unmap_shared(r->dp_mem, r->dp_bytes);
     if (r->dp_fd >= 0) close(r->dp_fd);
   }

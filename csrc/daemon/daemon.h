@@ -75,6 +75,7 @@ struct CollOp {
   uint64_t send_va = 0, recv_va = 0;
   uint64_t send_mem = 0, recv_mem = 0, send_off = 0, recv_off = 0;
   void* user_event = nullptr;
+  uint64_t sync_slot = 0, sync_value = 0;   // mem-op mode (see proto::SyncMode)
   uint64_t user_seq = 0;
   uint64_t t_post_us = 0;
 };
@@ -121,6 +122,7 @@ struct RankState {
   StatusBlock* status = nullptr;
   char* fifo = nullptr;
   size_t fifo_bytes = 0;
+  Allocation sync_alloc;               // semaphore page shared with the client (mem-op mode)
   // proxy-owned progress state
   uint64_t next_post_seq = 0;
   uint64_t next_launch_seq = 0;
@@ -202,6 +204,8 @@ class ProxyEngine : public Engine {
   bool admit_slice(Communicator& c, CollSlot& s, int slice);
   void fill_args(Communicator& c, CollSlot& s, int rank, int slice, CollArgs* a);
   bool complete_request(RankState& rs, CollSlot& s, uint64_t seq, int status);
+  void signal_done(RankState& rs, uint64_t user_seq);
+  void order_after_client(RankState& rs, const CollOp& op, void* stream);
   void finish_slot(Communicator& c, CollSlot& s, uint64_t seq);
   void housekeeping(RankState& rs);
   int ensure_mc(Communicator& c, CollSlot& s, bool for_recv, uint64_t* out_va);
@@ -246,6 +250,7 @@ class Daemon {
   std::string control_path() const { return control_path_; }
   int admin_port() const { return admin_port_; }
   uint64_t timeout_ns() const { return cfg_.wait_timeout_ms * 1000000ull; }
+  bool memops() const { return memops_; }
 
   // Allocation lookup for the data path (shared lock).
   bool translate(uint64_t mem_id, uint64_t off, uint64_t bytes, uint64_t* va, int* device);
@@ -297,6 +302,7 @@ class Daemon {
   std::thread control_thread_;
   std::thread admin_thread_;
   std::atomic<bool> running_{false};
+  bool memops_ = false;
   std::atomic<bool> stop_{false};
 
   std::mutex mu_;   // sessions_, comms_, pending_inits_

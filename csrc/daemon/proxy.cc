@@ -92,6 +92,7 @@ bool ProxyEngine::intake(RankState& rs) {
       int err = rs.comm->async_error.load();
       wc.status = err ? err : proto::kErrPeerLost;
       wc.user_seq = rs.pending_wr.user_seq;
+      if (rs.pending_wr.sync_slot) signal_done(rs, rs.pending_wr.user_seq);
       if (!rs.cq.try_push(&wc)) { rs.pending_wc = wc; rs.have_pending_wc = true; }
       rs.have_pending_wr = false;
       any = true;
@@ -119,6 +120,8 @@ bool ProxyEngine::post(RankState& rs, const proto::WorkRequest& wr) {
   op.scale = wr.scale;
   op.variant_req = (int)wr.variant;
   op.user_seq = wr.user_seq;
+  op.sync_slot = wr.sync_slot;
+  op.sync_value = wr.sync_value;
   op.send_mem = wr.send_mem; op.send_off = wr.send_off;
   op.recv_mem = wr.recv_mem; op.recv_off = wr.recv_off;
   op.t_post_us = monotonic_us();
@@ -211,14 +214,15 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   in.host_staged = c.host_staged;
   in.fifo_slot_bytes = c.fifo_slot_bytes;
   uint64_t bits = o0.kind == kAllGather ? o0.count : 0;
-  bool same_off = true, all_vmm = !host_backend;
+  bool same_send_off = true, same_recv_off = true, all_vmm = !host_backend;
   int req = o0.variant_req;
   for (int r = 0; r < c.nranks; r++) {
     const CollOp& o = s.ops[r];
     bits |= o.send_va | o.recv_va;
     if (o0.kind == kAllReduce) in.in_place |= o.send_va == o.recv_va;
     else in.in_place |= o.send_va == o.recv_va + (uint64_t)r * o.count;
-    same_off &= o.send_off == o0.send_off && o.recv_off == o0.recv_off;
+    same_send_off &= o.send_off == o0.send_off;
+    same_recv_off &= o.recv_off == o0.recv_off;
     if (o.variant_req != req) req = kAuto;
   }
   in.aligned16 = (bits & 15u) == 0;
@@ -227,7 +231,7 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
     for (int b = 0; b < c.nranks; b++)
       if (!be->peer_access(c.devices[a], c.devices[b])) { in.p2p_possible = false; break; }
   in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged &&
-                     all_vmm && same_off && c.nranks >= 2;
+                     all_vmm && same_recv_off && (same_send_off || o0.kind == kAllGather) && c.nranks >= 2;
   {
     std::lock_guard<std::mutex> g(c.cfg_mu);
     const int cfg_variant = o0.kind == kAllReduce ? c.ar_variant : c.ag_variant;
@@ -378,14 +382,14 @@ bool ProxyEngine::launch_slices(RankState& rs, CollSlot& s, uint64_t seq) {
   const CollOp& op = s.ops[rs.rank];
   while (rs.next_slice < s.nslices) {
     if (!admit_slice(c, s, rs.next_slice)) return false;
-    if (rs.next_slice == 0 && op.user_event) be->stream_wait_event(rs.device, rs.stream, op.user_event);
+    if (rs.next_slice == 0) order_after_client(rs, op, rs.stream);
     CollArgs a;
     fill_args(c, s, rs.rank, rs.next_slice, &a);
     int rc = be->launch(rs.device, op.kind, a, s.plan.dims, rs.stream);
     if (rc != proto::kOk) {
       c.async_error.store(rc);
       c.state.store(kCommError);
-      return true;   // the request completes with the communicator's error
+      break;   // the request completes with the communicator's error; the client's stream is still released below
     }
     if (rs.rank == 0) {
       const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
@@ -393,9 +397,32 @@ bool ProxyEngine::launch_slices(RankState& rs, CollSlot& s, uint64_t seq) {
     }
     rs.next_slice++;
   }
-  be->event_record(rs.device, rs.backend_event, rs.stream);
+  if (rs.sync_alloc.va && op.sync_slot)
+    be->stream_write_value64(rs.device, rs.stream, rs.sync_alloc.va + 8 * proto::kSyncDoneSlot, op.user_seq);
+  else
+    be->event_record(rs.device, rs.backend_event, rs.stream);
   (void)seq;
   return true;
+}
+
+// Makes `stream` wait for the work the client had queued before this request.
+void ProxyEngine::order_after_client(RankState& rs, const CollOp& op, void* stream) {
+  Backend* be = daemon_->backend();
+  if (rs.sync_alloc.va && op.sync_slot) {
+    const uint64_t addr = rs.sync_alloc.va + 8 * (proto::kSyncFirstStreamSlot + (op.sync_slot - 1) % proto::kSyncMaxStreams);
+    be->stream_wait_value64(rs.device, stream, addr, op.sync_value);
+  } else if (op.user_event) {
+    be->stream_wait_event(rs.device, stream, op.user_event);
+  }
+}
+
+// A request that ends without a launch must still release the client's stream, which
+// (in mem-op mode) already waits for this request's "done" value.
+void ProxyEngine::signal_done(RankState& rs, uint64_t user_seq) {
+  if (!rs.sync_alloc.va) return;
+  Communicator& c = *rs.comm;
+  void* stream = c.group_stream ? c.group_stream : rs.stream;
+  daemon_->backend()->stream_write_value64(rs.device, stream, rs.sync_alloc.va + 8 * proto::kSyncDoneSlot, user_seq);
 }
 
 // Emulated communicators (all ranks on one GPU) and the host backend run every rank
@@ -407,8 +434,7 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
   while (r0.next_slice < s.nslices) {
     if (!admit_slice(c, s, r0.next_slice)) return false;
     if (r0.next_slice == 0) {
-      for (int r = 0; r < c.nranks; r++)
-        if (s.ops[r].user_event) be->stream_wait_event(r0.device, c.group_stream, s.ops[r].user_event);
+      for (int r = 0; r < c.nranks; r++) order_after_client(*c.ranks[(size_t)r], s.ops[r], c.group_stream);
     }
     CollArgs a;
     fill_args(c, s, 0, r0.next_slice, &a);
@@ -422,8 +448,13 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
     r0.inflight.push_back({a.seq, bytes});
     r0.next_slice++;
   }
-  for (int r = 0; r < c.nranks; r++)
-    be->event_record(c.ranks[(size_t)r]->device, c.ranks[(size_t)r]->backend_event, c.group_stream);
+  for (int r = 0; r < c.nranks; r++) {
+    RankState& rr = *c.ranks[(size_t)r];
+    if (rr.sync_alloc.va && s.ops[r].sync_slot)
+      be->stream_write_value64(rr.device, c.group_stream, rr.sync_alloc.va + 8 * proto::kSyncDoneSlot, s.ops[r].user_seq);
+    else
+      be->event_record(rr.device, rr.backend_event, c.group_stream);
+  }
   s.group_launch.store(2, std::memory_order_release);
   return true;
 }
@@ -470,16 +501,21 @@ bool ProxyEngine::advance(RankState& rs) {
     }
     const uint64_t seq = rs.next_launch_seq;
     CollSlot& s = c.slot(seq);
+    int st = s.state.load(std::memory_order_acquire);
     if (c.state.load(std::memory_order_acquire) == kCommError) {
       // A failed communicator never launches again; what was posted completes in error.
-      int err = c.async_error.load();
-      complete_request(rs, s, seq, err ? err : proto::kErrPeerLost);
-      rs.next_launch_seq++;
-      rs.next_slice = 0;
-      any = true;
-      continue;
+      // A communicator that is merely being closed (a peer destroyed its handle, no
+      // error recorded) still finishes collectives every rank had already joined.
+      const int err = c.async_error.load();
+      if (err != 0 || st == kSlotCollecting) {
+        if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq);
+        complete_request(rs, s, seq, err ? err : proto::kErrPeerLost);
+        rs.next_launch_seq++;
+        rs.next_slice = 0;
+        any = true;
+        continue;
+      }
     }
-    int st = s.state.load(std::memory_order_acquire);
     if (st == kSlotCollecting) break;
     if (st == kSlotCollected) {
       if (c.paused.load(std::memory_order_acquire)) break;
@@ -493,6 +529,7 @@ bool ProxyEngine::advance(RankState& rs) {
     int status = proto::kOk;
     if (st == kSlotFailed) {
       status = s.status;
+      if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq);
     } else if (group) {
       if (s.group_launch.load(std::memory_order_acquire) != 2) {
         if (rs.rank != 0) break;

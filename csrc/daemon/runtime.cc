@@ -3,6 +3,7 @@
 #include <pthread.h>
 #include <sched.h>
 #include <stdlib.h>
+#include <time.h>
 #include <unistd.h>
 
 #include "../common/log.h"
@@ -26,8 +27,8 @@ std::vector<int> parse_cpu_list(const std::string& s) {
   return out;
 }
 
-Runtime::Runtime(std::string name, std::string cpu_list, int idle_sleep_us)
-    : name_(std::move(name)), cpu_list_(std::move(cpu_list)), idle_sleep_us_(idle_sleep_us) {}
+Runtime::Runtime(std::string name, std::string cpu_list, int idle_sleep_us, int idle_spin_us)
+    : name_(std::move(name)), cpu_list_(std::move(cpu_list)), idle_sleep_us_(idle_sleep_us), idle_spin_us_(idle_spin_us) {}
 
 Runtime::~Runtime() { stop(); }
 
@@ -59,6 +60,12 @@ void Runtime::mainloop() {
   }
   std::vector<std::shared_ptr<Engine>> engines;
   unsigned idle_rounds = 0;
+  uint64_t idle_since_ns = 0;
+  auto now_ns = [] {
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return (uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec;
+  };
   while (!stop_.load(std::memory_order_relaxed)) {
     if (has_pending_.load(std::memory_order_acquire)) {
       std::vector<std::shared_ptr<Engine>> fresh;
@@ -83,10 +90,20 @@ void Runtime::mainloop() {
     }
     if (any) {
       idle_rounds = 0;
-    } else if (++idle_rounds > 2000 && idle_sleep_us_ > 0) {
-      usleep((useconds_t)idle_sleep_us_);
+      idle_since_ns = 0;
     } else if (engines.empty()) {
       usleep(1000);
+    } else {
+      // Busy-poll through short gaps (the time a kernel runs, the time between two
+      // requests of a training step); only a runtime that has seen nothing for
+      // `idle_spin_us` starts to sleep between polls. A sleeping poller costs every
+      // request a timer wake-up, which is more than a small collective takes.
+      __builtin_ia32_pause();
+      if ((++idle_rounds & 0xff) == 0 && idle_sleep_us_ > 0) {
+        const uint64_t t = now_ns();
+        if (!idle_since_ns) idle_since_ns = t;
+        else if (t - idle_since_ns > (uint64_t)idle_spin_us_ * 1000ull) usleep((useconds_t)idle_sleep_us_);
+      }
     }
   }
 }
@@ -95,7 +112,7 @@ void RuntimeManager::submit(std::shared_ptr<Engine> e, const std::string& cpu_li
   std::lock_guard<std::mutex> g(mu_);
   if (e->scheduling_hint() == SchedulingHint::kCompact) {
     if (!compact_) {
-      runtimes_.emplace_back(new Runtime("mccs-compact", "", idle_sleep_us_ > 0 ? idle_sleep_us_ : 100));
+      runtimes_.emplace_back(new Runtime("mccs-compact", "", idle_sleep_us_ > 0 ? idle_sleep_us_ : 100, 1000));
       compact_ = runtimes_.back().get();
       compact_->start();
     }
@@ -103,7 +120,7 @@ void RuntimeManager::submit(std::shared_ptr<Engine> e, const std::string& cpu_li
     return;
   }
   std::string name = std::string("mccs-") + e->name();
-  runtimes_.emplace_back(new Runtime(name, pin_ ? cpu_list : "", idle_sleep_us_));
+  runtimes_.emplace_back(new Runtime(name, pin_ ? cpu_list : "", idle_sleep_us_, idle_spin_us_));
   runtimes_.back()->add(std::move(e));
   runtimes_.back()->start();
 }

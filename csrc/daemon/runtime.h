@@ -30,7 +30,7 @@ class Engine {
 
 class Runtime {
  public:
-  Runtime(std::string name, std::string cpu_list, int idle_sleep_us);
+  Runtime(std::string name, std::string cpu_list, int idle_sleep_us, int idle_spin_us);
   ~Runtime();
   void add(std::shared_ptr<Engine> e);
   void start();
@@ -42,6 +42,7 @@ class Runtime {
   std::string name_;
   std::string cpu_list_;
   int idle_sleep_us_;
+  int idle_spin_us_;
   std::mutex mu_;
   std::vector<std::shared_ptr<Engine>> pending_;
   std::atomic<bool> has_pending_{false};
@@ -52,7 +53,8 @@ class Runtime {
 
 class RuntimeManager {
  public:
-  explicit RuntimeManager(int idle_sleep_us, bool pin) : idle_sleep_us_(idle_sleep_us), pin_(pin) {}
+  RuntimeManager(int idle_sleep_us, int idle_spin_us, bool pin)
+      : idle_sleep_us_(idle_sleep_us), idle_spin_us_(idle_spin_us), pin_(pin) {}
   ~RuntimeManager() { stop_all(); }
   // cpu_list: "0-3,8" style list for thread affinity ("" = no pinning).
   void submit(std::shared_ptr<Engine> e, const std::string& cpu_list);
@@ -61,6 +63,7 @@ class RuntimeManager {
 
  private:
   int idle_sleep_us_;
+  int idle_spin_us_;
   bool pin_;
   std::mutex mu_;
   std::vector<std::unique_ptr<Runtime>> runtimes_;

@@ -48,6 +48,7 @@ struct BackendOptions {
   bool allow_vmm = true;
   bool allow_nvls = true;
   bool force_host = false;
+  bool allow_memops = true;
 };
 
 class Backend {
@@ -87,6 +88,12 @@ class Backend {
   virtual int event_destroy(int dev, void* ev) = 0;
   virtual int stream_wait_event(int dev, void* stream, void* ev) = 0;
   virtual int event_record(int dev, void* ev, void* stream) = 0;
+
+  // Stream memory operations on 64-bit words in device memory (mem-op sync mode).
+  virtual bool memops_supported() const = 0;
+  virtual int stream_wait_value64(int dev, void* stream, uint64_t addr, uint64_t value) = 0;   // waits *addr >= value
+  virtual int stream_write_value64(int dev, void* stream, uint64_t addr, uint64_t value) = 0;
+  virtual int zero_memory(int dev, uint64_t addr, size_t bytes) = 0;
 
   virtual int mc_create(const std::vector<const Allocation*>& per_rank, McRegion* out) = 0;
   virtual int mc_destroy(McRegion* r) = 0;

@@ -44,6 +44,9 @@ struct Driver {
   DRV_FN(cuMulticastBindMem);
   DRV_FN(cuMulticastUnbind);
   DRV_FN(cuMulticastGetGranularity);
+  DRV_FN(cuStreamWaitValue64);
+  DRV_FN(cuStreamWriteValue64);
+  bool memops_ok = false;
   bool ok = false;
   bool mc_ok = false;
 };
@@ -70,6 +73,7 @@ void load_driver(Driver& d) {
          LOAD(cuMemUnmap) && LOAD(cuMemSetAccess) && LOAD(cuMemExportToShareableHandle);
   d.mc_ok = d.ok && LOAD(cuMulticastCreate) && LOAD(cuMulticastAddDevice) &&
             LOAD(cuMulticastBindMem) && LOAD(cuMulticastUnbind) && LOAD(cuMulticastGetGranularity);
+  d.memops_ok = d.ok && LOAD(cuStreamWaitValue64) && LOAD(cuStreamWriteValue64);
 }
 
 #define RT_CHECK(expr, status)                                                          \
@@ -119,6 +123,14 @@ class CudaBackend : public Backend {
     vmm_ = opt.allow_vmm && drv_.ok && probe_vmm();
     if (!vmm_) enable_runtime_peer_access();
     nvls_ = vmm_ && opt.allow_nvls && drv_.mc_ok && ndev_ >= 2 && probe_multicast();
+    memops_ = drv_.memops_ok && opt.allow_memops;
+    for (int d = 0; d < ndev_ && memops_; d++) {
+      CUdevice dev;
+      int ok64 = 0;
+      if (drv_.cuDeviceGet_(&dev, d) != CUDA_SUCCESS) { memops_ = false; break; }
+      drv_.cuDeviceGetAttribute_(&ok64, CU_DEVICE_ATTRIBUTE_CAN_USE_64_BIT_STREAM_MEM_OPS, dev);
+      if (!ok64) memops_ = false;
+    }
     cudaSetDevice(0);
     LOG_INFO("%s", describe().c_str());
     return true;
@@ -132,8 +144,8 @@ class CudaBackend : public Backend {
   }
   std::string describe() const override {
     char buf[256];
-    snprintf(buf, sizeof buf, "cuda backend: %d device(s), alloc=%s, nvls=%s, gran=%zu", ndev_,
-             vmm_ ? "vmm+fd" : "cudaMalloc+ipc", nvls_ ? "on" : "off", gran_);
+    snprintf(buf, sizeof buf, "cuda backend: %d device(s), alloc=%s, nvls=%s, sync=%s, gran=%zu", ndev_,
+             vmm_ ? "vmm+fd" : "cudaMalloc+ipc", nvls_ ? "on" : "off", memops_ ? "memops" : "events", gran_);
     return buf;
   }
   std::string cpu_affinity(int dev) const override {
@@ -342,6 +354,25 @@ class CudaBackend : public Backend {
   }
   int event_record(int, void* ev, void* stream) override {
     RT_CHECK(cudaEventRecord((cudaEvent_t)ev, (cudaStream_t)stream), proto::kErrDevice);
+    return proto::kOk;
+  }
+
+  bool memops_supported() const override { return memops_; }
+  int stream_wait_value64(int, void* stream, uint64_t addr, uint64_t value) override {
+    CUresult r = drv_.cuStreamWaitValue64_((CUstream)stream, (CUdeviceptr)addr, value, CU_STREAM_WAIT_VALUE_GEQ);
+    if (r != CUDA_SUCCESS) { log_cu("cuStreamWaitValue64", r); return proto::kErrDevice; }
+    return proto::kOk;
+  }
+  int stream_write_value64(int, void* stream, uint64_t addr, uint64_t value) override {
+    CUresult r = drv_.cuStreamWriteValue64_((CUstream)stream, (CUdeviceptr)addr, value, CU_STREAM_WRITE_VALUE_DEFAULT);
+    if (r != CUDA_SUCCESS) { log_cu("cuStreamWriteValue64", r); return proto::kErrDevice; }
+    return proto::kOk;
+  }
+  int zero_memory(int dev, uint64_t addr, size_t bytes) override {
+    DeviceGuard guard;
+    RT_CHECK(cudaSetDevice(dev), proto::kErrDevice);
+    RT_CHECK(cudaMemset((void*)addr, 0, bytes), proto::kErrDevice);
+    RT_CHECK(cudaDeviceSynchronize(), proto::kErrDevice);
     return proto::kOk;
   }
 
@@ -585,6 +616,7 @@ class CudaBackend : public Backend {
   int ndev_ = 0;
   bool vmm_ = false;
   bool nvls_ = false;
+  bool memops_ = false;
   size_t gran_ = 2u << 20;
   bool peer_[kMaxRanks][kMaxRanks] = {{false}};
   Driver drv_;

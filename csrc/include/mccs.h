@@ -129,6 +129,12 @@ typedef struct {
 } mccsCommInfo_t;
 mccsResult_t mccsCommQuery(mccsComm_t comm, mccsCommInfo_t* info);
 mccsResult_t mccsCommGetAsyncError(mccsComm_t comm, mccsResult_t* async_error);
+/* Waits (on the host) until the daemon has taken and launched every request posted on
+ * this communicator so far, and returns the first error any of them reported. With
+ * stream-memory-operation synchronisation collective calls return before the daemon
+ * has seen them; this is the point where their errors become visible. It does not
+ * wait for the GPU work (synchronise the stream for that). */
+mccsResult_t mccsCommFlush(mccsComm_t comm);
 /* Variant and CTA count reported with the last completed request of this rank. */
 mccsResult_t mccsCommLastPlan(mccsComm_t comm, uint32_t* variant, uint32_t* ctas);
 

@@ -12,6 +12,7 @@
 #include <errno.h>
 #include <netdb.h>
 #include <poll.h>
+#include <pthread.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -65,6 +66,9 @@ struct Driver {
   DRV_FN(cuMemSetAccess);
   DRV_FN(cuMemRelease);
   DRV_FN(cuGetErrorString);
+  DRV_FN(cuStreamWaitValue64);
+  DRV_FN(cuStreamWriteValue64);
+  bool memops = false;
 };
 Driver g_drv;
 
@@ -97,6 +101,8 @@ bool load_driver() {
              sym(l, "cuMemAddressFree", &g_drv.cuMemAddressFree_) && sym(l, "cuMemMap", &g_drv.cuMemMap_) &&
              sym(l, "cuMemUnmap", &g_drv.cuMemUnmap_) && sym(l, "cuMemSetAccess", &g_drv.cuMemSetAccess_) &&
              sym(l, "cuMemRelease", &g_drv.cuMemRelease_) && sym(l, "cuGetErrorString", &g_drv.cuGetErrorString_);
+  g_drv.memops = sym(l, "cuStreamWaitValue64_v2", &g_drv.cuStreamWaitValue64_) &&
+                 sym(l, "cuStreamWriteValue64_v2", &g_drv.cuStreamWriteValue64_);
   if (g_drv.ok && g_drv.cuInit_(0) != CUDA_SUCCESS) g_drv.ok = false;
   return g_drv.ok;
 }
@@ -164,6 +170,7 @@ struct Context {
   bool same_process = false;
   int num_devices = 0;
   uint64_t session_id = 0;
+  uint32_t sync_mode = 0;
   uint32_t next_req = 1;
   std::map<uint64_t, MemRec> mem;                       // base -> record
   std::map<std::pair<int, uint64_t>, StreamRec> streams;   // (device, stream) -> record
@@ -172,6 +179,7 @@ struct Context {
   bool reader_active = false;
   std::condition_variable reply_cv;
   std::map<uint32_t, struct Reply> replies;
+  std::vector<struct mccsComm*> comms;   // live communicators (flushed before memory is freed)
 };
 Context g_ctx;
 
@@ -194,6 +202,12 @@ struct mccsComm {
   uint64_t outstanding = 0;      // requests posted whose completion was not read yet
   uint32_t last_variant = 0, last_ctas = 0;
   int sticky_error = 0;
+  pthread_t owner = pthread_self();   // the thread that created (and uses) the communicator
+  // mem-op synchronisation (proto::kSyncMemOps): semaphore page shared with the daemon
+  MemRec sync_rec;
+  uint64_t sync_base = 0;
+  std::map<uint64_t, uint32_t> stream_slot;            // stream handle -> semaphore index
+  uint64_t slot_value[proto::kSyncMaxStreams] = {0};   // last value written per semaphore
 };
 
 namespace {
@@ -295,6 +309,7 @@ mccsResult_t ensure_connected_locked(std::unique_lock<std::mutex>& lk, const cha
   c.same_process = c.daemon_pid == (int)getpid();
   c.num_devices = (int)m.welcome.num_devices;
   c.session_id = m.welcome.session_id;
+  c.sync_mode = m.welcome.sync_mode;
   const char* to = getenv("MCCS_WC_TIMEOUT_MS");
   if (to) c.wc_timeout_ms = strtoull(to, nullptr, 10);
   c.connected = true;
@@ -350,6 +365,84 @@ mccsResult_t register_stream_locked(std::unique_lock<std::mutex>& lk, int device
   return mccsSuccess;
 }
 
+// Maps an allocation the daemon made (rec.share_kind/size/device filled in) into
+// this process; `fd` is the descriptor that came with the reply (-1 if none).
+mccsResult_t map_allocation(MemRec& rec, int fd, const uint8_t* ipc_handle, uint64_t daemon_va) {
+  switch (rec.share_kind) {
+    case proto::kShareSameProcess:
+      rec.base = daemon_va;
+      return mccsSuccess;
+    case proto::kShareHostFd: {
+      if (fd < 0) return mccsProtocolError;
+      void* p = mmap(nullptr, rec.size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+      if (p == MAP_FAILED) return mccsOutOfMemory;
+      rec.base = (uint64_t)p;
+      return mccsSuccess;
+    }
+    case proto::kShareVmmFd: {
+      if (fd < 0) return mccsProtocolError;
+      CtxScope scope(rec.device);
+      if (!scope.ok) return mccsDeviceError;
+      CUmemGenericAllocationHandle h = 0;
+      CUresult cr = g_drv.cuMemImportFromShareableHandle_(&h, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+      if (cr != CUDA_SUCCESS) { LOG_ERROR("cuMemImportFromShareableHandle: %s", cu_err(cr)); return mccsDeviceError; }
+      CUdeviceptr va = 0;
+      cr = g_drv.cuMemAddressReserve_(&va, rec.size, 0, 0, 0);
+      if (cr != CUDA_SUCCESS) { g_drv.cuMemRelease_(h); return mccsOutOfMemory; }
+      cr = g_drv.cuMemMap_(va, rec.size, 0, h, 0);
+      if (cr != CUDA_SUCCESS) {
+        LOG_ERROR("cuMemMap: %s", cu_err(cr));
+        g_drv.cuMemAddressFree_(va, rec.size);
+        g_drv.cuMemRelease_(h);
+        return mccsDeviceError;
+      }
+      CUmemAccessDesc desc;
+      memset(&desc, 0, sizeof desc);
+      desc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+      desc.location.id = rec.device;
+      desc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+      cr = g_drv.cuMemSetAccess_(va, rec.size, &desc, 1);
+      if (cr != CUDA_SUCCESS) {
+        LOG_ERROR("cuMemSetAccess: %s", cu_err(cr));
+        g_drv.cuMemUnmap_(va, rec.size);
+        g_drv.cuMemAddressFree_(va, rec.size);
+        g_drv.cuMemRelease_(h);
+        return mccsDeviceError;
+      }
+      rec.base = (uint64_t)va;
+      rec.vmm_handle = (uint64_t)h;
+      return mccsSuccess;
+    }
+    case proto::kShareCudaIpc: {
+      CtxScope scope(rec.device);
+      if (!scope.ok) return mccsDeviceError;
+      CUipcMemHandle h;
+      memcpy(&h, ipc_handle, sizeof h);
+      CUdeviceptr p = 0;
+      CUresult cr = g_drv.cuIpcOpenMemHandle_(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS);
+      if (cr != CUDA_SUCCESS) { LOG_ERROR("cuIpcOpenMemHandle: %s", cu_err(cr)); return mccsDeviceError; }
+      rec.base = (uint64_t)p;
+      return mccsSuccess;
+    }
+  }
+  return mccsProtocolError;
+}
+
+void unmap_allocation(const MemRec& rec) {
+  if (!rec.base) return;
+  if (rec.share_kind == proto::kShareHostFd) {
+    munmap((void*)rec.base, rec.size);
+  } else if (rec.share_kind == proto::kShareVmmFd && g_drv.ok) {
+    CtxScope scope(rec.device);
+    g_drv.cuMemUnmap_((CUdeviceptr)rec.base, rec.size);
+    g_drv.cuMemAddressFree_((CUdeviceptr)rec.base, rec.size);
+    g_drv.cuMemRelease_((CUmemGenericAllocationHandle)rec.vmm_handle);
+  } else if (rec.share_kind == proto::kShareCudaIpc && g_drv.ok) {
+    CtxScope scope(rec.device);
+    g_drv.cuIpcCloseMemHandle_((CUdeviceptr)rec.base);
+  }
+}
+
 // Spins for the completion of the oldest outstanding request of `comm`.
 mccsResult_t wait_completion(mccsComm* comm, proto::WorkCompletion* wc) {
   struct timespec t0;
@@ -383,6 +476,56 @@ mccsResult_t finish_on_stream(mccsComm* comm, mccsStream_t stream) {
   return mccsSuccess;
 }
 
+// Takes whatever completions have arrived, without waiting.
+void reap_completions(mccsComm* comm) {
+  proto::WorkCompletion wc;
+  while (comm->outstanding > 0 && comm->cq.try_pop(&wc)) {
+    comm->outstanding--;
+    comm->last_variant = wc.variant;
+    comm->last_ctas = wc.ctas;
+    if (wc.status != 0 && comm->sticky_error == 0) comm->sticky_error = wc.status;
+  }
+}
+
+// Mem-op mode: nothing blocks. The caller's stream publishes "submitted", the request
+// is posted, and the stream is told to wait for the request's "done" value, which the
+// daemon's stream writes after the kernel. Errors surface on a later call.
+mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t stream) {
+  reap_completions(comm);
+  if (comm->sticky_error) return (mccsResult_t)comm->sticky_error;
+  uint32_t slot;
+  auto it = comm->stream_slot.find((uint64_t)stream);
+  if (it == comm->stream_slot.end()) {
+    slot = (uint32_t)comm->stream_slot.size();
+    if (slot >= proto::kSyncMaxStreams) return mccsUnsupported;
+    comm->stream_slot[(uint64_t)stream] = slot;
+  } else {
+    slot = it->second;
+  }
+  wr.comm_handle = comm->handle;
+  wr.user_seq = comm->next_user_seq++;
+  wr.sync_slot = slot + 1;
+  wr.sync_value = ++comm->slot_value[slot];
+  CtxScope scope(comm->device);
+  if (!scope.ok) return mccsDeviceError;
+  CUresult r = g_drv.cuStreamWriteValue64_((CUstream)stream, (CUdeviceptr)(comm->sync_base + 8 * (proto::kSyncFirstStreamSlot + slot)),
+                                           wr.sync_value, CU_STREAM_WRITE_VALUE_DEFAULT);
+  if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWriteValue64: %s", cu_err(r)); return mccsDeviceError; }
+  uint64_t spins = 0;
+  while (!comm->wq.try_push(&wr)) {
+    reap_completions(comm);
+    if ((++spins & 0xffff) == 0) {
+      struct pollfd pf = {g_ctx.fd, 0, 0};
+      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+    }
+  }
+  comm->outstanding++;
+  r = g_drv.cuStreamWaitValue64_((CUstream)stream, (CUdeviceptr)(comm->sync_base + 8 * proto::kSyncDoneSlot), wr.user_seq,
+                                 CU_STREAM_WAIT_VALUE_GEQ);
+  if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitValue64: %s", cu_err(r)); return mccsDeviceError; }
+  return mccsSuccess;
+}
+
 mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, void* recv, uint64_t send_bytes,
                     uint64_t recv_bytes, mccsStream_t stream) {
   if (!comm) return mccsInvalidArgument;
@@ -399,9 +542,12 @@ mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, vo
     wr.send_mem = sm->mem_id; wr.send_off = (uint64_t)send - sm->base;
     wr.recv_mem = rm->mem_id; wr.recv_off = (uint64_t)recv - rm->base;
     if (wr.send_off + send_bytes > sm->size || wr.recv_off + recv_bytes > rm->size) return mccsInvalidArgument;
-    mccsResult_t r = register_stream_locked(g, comm->device, stream, &srec);
-    if (r != mccsSuccess) return r;
+    if (!comm->sync_base) {
+      mccsResult_t r = register_stream_locked(g, comm->device, stream, &srec);
+      if (r != mccsSuccess) return r;
+    }
   }
+  if (comm->sync_base) return submit_memops(comm, wr, stream);
   wr.comm_handle = comm->handle;
   wr.stream_id = srec->stream_id;
   wr.user_seq = comm->next_user_seq++;
@@ -460,19 +606,7 @@ mccsResult_t mccsFinalize(void) {
   close(c.fd);
   c.fd = -1;
   c.connected = false;
-  for (auto& kv : c.mem) {
-    const MemRec& r = kv.second;
-    if (r.share_kind == proto::kShareHostFd) munmap((void*)r.base, r.size);
-    else if (r.share_kind == proto::kShareVmmFd && g_drv.ok) {
-      CtxScope scope(r.device);
-      g_drv.cuMemUnmap_((CUdeviceptr)r.base, r.size);
-      g_drv.cuMemAddressFree_((CUdeviceptr)r.base, r.size);
-      g_drv.cuMemRelease_((CUmemGenericAllocationHandle)r.vmm_handle);
-    } else if (r.share_kind == proto::kShareCudaIpc && g_drv.ok) {
-      CtxScope scope(r.device);
-      g_drv.cuIpcCloseMemHandle_((CUdeviceptr)r.base);
-    }
-  }
+  for (auto& kv : c.mem) unmap_allocation(kv.second);
   c.mem.clear();
   if (g_drv.ok)
     for (auto& kv : c.streams)
@@ -512,68 +646,7 @@ mccsResult_t mccsMalloc(void** ptr, int device, size_t size) {
   rec.size = m.malloc_reply.size;
   rec.device = m.malloc_reply.device;
   rec.share_kind = m.malloc_reply.share_kind;
-  mccsResult_t fail = mccsSuccess;
-  switch (rec.share_kind) {
-    case proto::kShareSameProcess:
-      rec.base = m.malloc_reply.daemon_va;
-      break;
-    case proto::kShareHostFd: {
-      if (fds.empty()) { fail = mccsProtocolError; break; }
-      void* p = mmap(nullptr, rec.size, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
-      if (p == MAP_FAILED) { fail = mccsOutOfMemory; break; }
-      rec.base = (uint64_t)p;
-      break;
-    }
-    case proto::kShareVmmFd: {
-      if (fds.empty()) { fail = mccsProtocolError; break; }
-      CtxScope scope(device);
-      if (!scope.ok) { fail = mccsDeviceError; break; }
-      CUmemGenericAllocationHandle h = 0;
-      CUresult cr = g_drv.cuMemImportFromShareableHandle_(&h, (void*)(uintptr_t)fds[0],
-                                                          CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
-      if (cr != CUDA_SUCCESS) { LOG_ERROR("cuMemImportFromShareableHandle: %s", cu_err(cr)); fail = mccsDeviceError; break; }
-      CUdeviceptr va = 0;
-      cr = g_drv.cuMemAddressReserve_(&va, rec.size, 0, 0, 0);
-      if (cr != CUDA_SUCCESS) { g_drv.cuMemRelease_(h); fail = mccsOutOfMemory; break; }
-      cr = g_drv.cuMemMap_(va, rec.size, 0, h, 0);
-      if (cr != CUDA_SUCCESS) {
-        LOG_ERROR("cuMemMap: %s", cu_err(cr));
-        g_drv.cuMemAddressFree_(va, rec.size);
-        g_drv.cuMemRelease_(h);
-        fail = mccsDeviceError;
-        break;
-      }
-      CUmemAccessDesc desc;
-      memset(&desc, 0, sizeof desc);
-      desc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
-      desc.location.id = device;
-      desc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
-      cr = g_drv.cuMemSetAccess_(va, rec.size, &desc, 1);
-      if (cr != CUDA_SUCCESS) {
-        LOG_ERROR("cuMemSetAccess: %s", cu_err(cr));
-        g_drv.cuMemUnmap_(va, rec.size);
-        g_drv.cuMemAddressFree_(va, rec.size);
-        g_drv.cuMemRelease_(h);
-        fail = mccsDeviceError;
-        break;
-      }
-      rec.base = (uint64_t)va;
-      rec.vmm_handle = (uint64_t)h;
-      break;
-    }
-    case proto::kShareCudaIpc: {
-      CtxScope scope(device);
-      if (!scope.ok) { fail = mccsDeviceError; break; }
-      CUipcMemHandle h;
-      memcpy(&h, m.malloc_reply.ipc_handle, sizeof h);
-      CUdeviceptr p = 0;
-      CUresult cr = g_drv.cuIpcOpenMemHandle_(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS);
-      if (cr != CUDA_SUCCESS) { LOG_ERROR("cuIpcOpenMemHandle: %s", cu_err(cr)); fail = mccsDeviceError; break; }
-      rec.base = (uint64_t)p;
-      break;
-    }
-    default: fail = mccsProtocolError;
-  }
+  mccsResult_t fail = map_allocation(rec, fds.empty() ? -1 : fds[0], m.malloc_reply.ipc_handle, m.malloc_reply.daemon_va);
   close_fds();
   if (fail != mccsSuccess) {
     proto::AnyMsg f;
@@ -590,22 +663,23 @@ mccsResult_t mccsMalloc(void** ptr, int device, size_t size) {
 
 mccsResult_t mccsFree(void* ptr) {
   if (!ptr) return mccsSuccess;
+  {
+    // Requests that name this memory may still sit in a request ring (calls return
+    // before the daemon takes them): let the daemon take them first.
+    std::vector<mccsComm*> comms;
+    { std::unique_lock<std::mutex> g(g_ctx.mu); comms = g_ctx.comms; }
+    // Only this thread's communicators: completions of another thread's requests are
+    // that thread's to read.
+    if (g_ctx.connected)
+      for (mccsComm* c : comms)
+        if (pthread_equal(c->owner, pthread_self()) && c->outstanding) mccsCommFlush(c);
+  }
   std::unique_lock<std::mutex> g(g_ctx.mu);
   auto it = g_ctx.mem.find((uint64_t)ptr);
   if (it == g_ctx.mem.end()) return mccsNotFound;
   MemRec rec = it->second;
   // Unmap here first, then let the daemon release the memory.
-  if (rec.share_kind == proto::kShareHostFd) {
-    munmap((void*)rec.base, rec.size);
-  } else if (rec.share_kind == proto::kShareVmmFd) {
-    CtxScope scope(rec.device);
-    g_drv.cuMemUnmap_((CUdeviceptr)rec.base, rec.size);
-    g_drv.cuMemAddressFree_((CUdeviceptr)rec.base, rec.size);
-    g_drv.cuMemRelease_((CUmemGenericAllocationHandle)rec.vmm_handle);
-  } else if (rec.share_kind == proto::kShareCudaIpc) {
-    CtxScope scope(rec.device);
-    g_drv.cuIpcCloseMemHandle_((CUdeviceptr)rec.base);
-  }
+  unmap_allocation(rec);
   g_ctx.mem.erase(it);
   if (!g_ctx.connected) return mccsSuccess;
   proto::AnyMsg m;
@@ -652,11 +726,21 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
   c->device = device;
   c->dp_bytes = m.comm_init_reply.dp_bytes;
   c->dp_mem = mmap(nullptr, c->dp_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
-  for (int f : fds) close(f);
-  if (c->dp_mem == MAP_FAILED) { delete c; return mccsOutOfMemory; }
+  if (c->dp_mem == MAP_FAILED) { for (int f : fds) close(f); delete c; return mccsOutOfMemory; }
   const size_t wq_bytes = (ipc::Ring::bytes_needed(proto::kWqDepth, proto::kWrBytes) + 63) / 64 * 64;
   c->wq.attach(c->dp_mem);
   c->cq.attach((char*)c->dp_mem + wq_bytes);
+  if (g_ctx.backend == proto::kBackendCuda && m.comm_init_reply.sync_size && g_drv.memops) {
+    c->sync_rec.size = m.comm_init_reply.sync_size;
+    c->sync_rec.device = device;
+    c->sync_rec.share_kind = m.comm_init_reply.sync_share_kind;
+    mccsResult_t mr = map_allocation(c->sync_rec, fds.size() > 1 ? fds[1] : -1, m.comm_init_reply.sync_ipc_handle,
+                                     m.comm_init_reply.sync_daemon_va);
+    if (mr == mccsSuccess) c->sync_base = c->sync_rec.base;
+    else LOG_WARN("cannot map the semaphore page (%s); falling back to event synchronisation", mccsGetErrorString(mr));
+  }
+  for (int f : fds) close(f);
+  fds.clear();
   if (g_ctx.backend == proto::kBackendCuda) {
     if (g_ctx.same_process) {
       c->backend_event = (CUevent)m.comm_init_reply.event_raw;
@@ -675,12 +759,24 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
       c->event_owned = true;
     }
   }
+  g_ctx.comms.push_back(c);
   *comm = c;
   return mccsSuccess;
 }
 
+mccsResult_t mccsCommFlush(mccsComm_t comm) {
+  if (!comm) return mccsInvalidArgument;
+  proto::WorkCompletion wc;
+  while (comm->outstanding > 0) {
+    mccsResult_t r = wait_completion(comm, &wc);
+    if (r == mccsTimeout || r == mccsNotConnected) return r;
+  }
+  return (mccsResult_t)comm->sticky_error;
+}
+
 mccsResult_t mccsCommDestroy(mccsComm_t comm) {
   if (!comm) return mccsSuccess;
+  if (g_ctx.connected) mccsCommFlush(comm);   // every posted request has been taken by the daemon
   std::unique_lock<std::mutex> g(g_ctx.mu);
   mccsResult_t r = mccsSuccess;
   if (g_ctx.connected) {
@@ -694,7 +790,10 @@ mccsResult_t mccsCommDestroy(mccsComm_t comm) {
     CtxScope scope(comm->device);
     g_drv.cuEventDestroy_(comm->backend_event);
   }
+  for (size_t i = 0; i < g_ctx.comms.size(); i++)
+    if (g_ctx.comms[i] == comm) { g_ctx.comms.erase(g_ctx.comms.begin() + (long)i); break; }
   if (comm->dp_mem) munmap(comm->dp_mem, comm->dp_bytes);
+  if (comm->sync_base) unmap_allocation(comm->sync_rec);
   delete comm;
   return r;
 }
@@ -809,6 +908,7 @@ mccsResult_t mccsCommGetAsyncError(mccsComm_t comm, mccsResult_t* async_error) {
 
 mccsResult_t mccsCommLastPlan(mccsComm_t comm, uint32_t* variant, uint32_t* ctas) {
   if (!comm) return mccsInvalidArgument;
+  mccsCommFlush(comm);
   if (variant) *variant = comm->last_variant;
   if (ctas) *ctas = comm->last_ctas;
   return mccsSuccess;

@@ -72,6 +72,8 @@ def shim() -> ctypes.CDLL:
     lib.mccsGroupEnd.restype = c_int
     lib.mccsCommQuery.argtypes = [c_void_p, POINTER(CommInfo)]
     lib.mccsCommQuery.restype = c_int
+    lib.mccsCommFlush.argtypes = [c_void_p]
+    lib.mccsCommFlush.restype = c_int
     lib.mccsCommLastPlan.argtypes = [c_void_p, POINTER(c_uint32), POINTER(c_uint32)]
     lib.mccsCommLastPlan.restype = c_int
     lib.mccsGetErrorString.argtypes = [c_int]

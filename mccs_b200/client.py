@@ -174,7 +174,14 @@ class Communicator:
         check(_lib.shim().mccsAllGatherEx(self._h, c_void_p(_ptr(send)), c_void_p(_ptr(recv)), int(nbytes),
                                           ALGOS[algo], c_void_p(self._stream(stream))), "mccsAllGather")
 
+    def flush(self) -> None:
+        """Wait until the daemon has launched everything posted so far; raise the first
+        error a request reported (collective calls may return before the daemon has
+        even seen them)."""
+        check(_lib.shim().mccsCommFlush(self._h), "mccsCommFlush")
+
     def query(self) -> dict:
+        _lib.shim().mccsCommFlush(self._h)
         info = _lib.CommInfo()
         check(_lib.shim().mccsCommQuery(self._h, byref(info)), "mccsCommQuery")
         return {f: getattr(info, f) for f, _ in info._fields_}

@@ -1,0 +1,31 @@
+"""Model zoo of the data-parallel training drivers: the three networks the build's
+training configurations name. ResNet-50 and VGG-16 come from torchvision (random
+init, no weights are downloaded); GPT-2-medium is defined here."""
+from __future__ import annotations
+
+import torch
+
+from .gpt2 import GPT2, GPT2Config, gpt2_medium, gpt2_tiny
+
+
+def build(name: str) -> torch.nn.Module:
+    name = name.lower()
+    if name in ("gpt2-medium", "gpt2_medium", "gpt2"):
+        return gpt2_medium()
+    if name in ("gpt2-tiny", "gpt2_tiny"):
+        return gpt2_tiny()
+    import torchvision
+    if name == "resnet50":
+        return torchvision.models.resnet50(weights=None)
+    if name == "vgg16":
+        return torchvision.models.vgg16(weights=None)
+    if name == "resnet18":
+        return torchvision.models.resnet18(weights=None)
+    raise ValueError(f"unknown model '{name}'")
+
+
+def is_language_model(name: str) -> bool:
+    return name.lower().startswith("gpt2")
+
+
+__all__ = ["build", "is_language_model", "GPT2", "GPT2Config", "gpt2_medium", "gpt2_tiny"]

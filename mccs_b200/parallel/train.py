@@ -1,0 +1,164 @@
+"""Data-parallel training driver with synthetic data: ResNet-50 / VGG-16 (fp32, batch
+64 per GPU, 224x224x3 images ~N(0,1), labels uniform over 1000 classes) and
+GPT-2-medium (bf16 autocast, batch 8 per GPU, sequence 1024, token ids uniform over
+the vocabulary), random init, SGD. One rank per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 4 --master-addr 127.0.0.1 \
+        -m mccs_b200.parallel.train --model resnet50 --comm-id 300 --steps 30
+
+``--backend mccs`` sends the 25 MB gradient buckets through the service (the job is a
+tenant: ``--comm-id`` is its QoS identity), overlapped with backward; ``--backend nccl``
+is torch's DistributedDataParallel over NCCL with the same bucket size, the baseline.
+The daemon must already run (``MCCS_CONTROL``), or ``--start-daemon`` lets local rank 0
+host it. Prints one JSON line with images/s or tokens/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="resnet50")
+    ap.add_argument("--backend", default="mccs", choices=["mccs", "nccl", "none"])
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--bucket-mb", type=float, default=25.0)
+    ap.add_argument("--comm-id", type=int, default=300)
+    ap.add_argument("--start-daemon", action="store_true")
+    ap.add_argument("--control", default="")
+    ap.add_argument("--devices", default="", help="comma separated GPU index per rank (default: local rank)")
+    ap.add_argument("--name", default="")
+    ap.add_argument("--lr", type=float, default=0.01)
+    args = ap.parse_args()
+
+    from mccs_b200 import models
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    cuda = torch.cuda.is_available()
+    dev_index = int(args.devices.split(",")[rank]) if args.devices else local_rank
+    device = torch.device(f"cuda:{dev_index}" if cuda else "cpu")
+    if cuda:
+        torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl" if cuda else "gloo", device_id=device if cuda else None)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    lm = models.is_language_model(args.model)
+    batch = args.batch or (8 if lm else 64)
+    torch.manual_seed(1234)          # identical initial weights on every rank
+    model = models.build(args.model).to(device)
+    if cuda and not lm:
+        model.to(memory_format=torch.channels_last)   # before gradient buckets are laid out
+    model.train()
+    opt = torch.optim.SGD(model.parameters(), lr=args.lr, momentum=0.9)
+
+    M = None
+    ddp = None
+    if args.backend == "mccs":
+        import mccs_b200 as M
+        prefix = args.control or f"/tmp/mccs-train-{os.getuid()}-{os.environ.get('MASTER_PORT', '0')}"
+        if args.start_daemon and local_rank == 0:
+            M.daemon.start_embedded(prefix=prefix, listen_port=-1)
+        barrier()
+        if args.start_daemon or args.control:
+            M.init(prefix + "/control.sock" if not prefix.endswith(".sock") else prefix)
+        comm = M.Communicator(args.comm_id, rank, world, device=dev_index if cuda else rank)
+        from mccs_b200.parallel import DataParallel
+        ddp = DataParallel(model, comm, bucket_mb=args.bucket_mb, broadcast_parameters=world > 1)
+        fwd = model
+    elif args.backend == "nccl" and world > 1:
+        fwd = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev_index] if cuda else None,
+                                                        bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
+    else:
+        fwd = model
+
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    if lm:
+        vocab = model.cfg.vocab_size
+        seq = min(args.seq, model.cfg.max_seq)
+        ids = torch.randint(0, vocab, (batch, seq + 1), generator=g).to(device)
+        inputs, targets = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+        units = batch * seq
+    else:
+        inputs = torch.randn(batch, 3, 224, 224, generator=g).to(device)
+        targets = torch.randint(0, 1000, (batch,), generator=g).to(device)
+        units = batch
+        if cuda:
+            inputs = inputs.contiguous(memory_format=torch.channels_last)
+
+    def step() -> torch.Tensor:
+        if ddp is not None:
+            ddp.zero_grad()
+        else:
+            opt.zero_grad(set_to_none=False)
+        if lm:
+            with torch.autocast(device_type=device.type, dtype=torch.bfloat16, enabled=cuda):
+                loss = fwd(inputs, targets)
+        else:
+            loss = torch.nn.functional.cross_entropy(fwd(inputs), targets)
+        loss.backward()
+        if ddp is not None:
+            ddp.finish()
+        opt.step()
+        return loss
+
+    losses = []
+    for _ in range(args.warmup):
+        losses.append(float(step()))
+    if cuda:
+        torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    if cuda:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    if cuda:
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+    else:
+        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    losses.append(float(loss))
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        out = {"name": args.name or args.model, "model": args.model, "backend": args.backend, "n_gpus": world,
+               "batch_per_gpu": batch, "ms_per_step": ms,
+               ("tokens_per_s" if lm else "images_per_s"): units * world / ms * 1e3,
+               "first_loss": losses[0] if losses else None, "last_loss": losses[-1],
+               "grad_bytes": ddp.gradient_bytes() if ddp is not None else sum(p.numel() * p.element_size() for p in model.parameters()),
+               "buckets": len(ddp.buckets) if ddp is not None else None}
+        print(json.dumps(out), flush=True)
+    barrier()
+    if ddp is not None:
+        ddp.release()
+        comm.destroy()
+        M.finalize()
+        barrier()
+        if args.start_daemon and local_rank == 0:
+            M.daemon.stop_embedded()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

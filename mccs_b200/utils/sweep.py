@@ -47,8 +47,8 @@ def parse_size(s: str) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--lo", default="32K", help="smallest message")
-    ap.add_argument("--hi", default="1G", help="largest message")
+    ap.add_argument("--min-bytes", default="32K", help="smallest message")
+    ap.add_argument("--max-bytes", default="1G", help="largest message")
     ap.add_argument("--colls", default="allreduce,allgather")
     ap.add_argument("--dtypes", default="bf16,fp32")
     ap.add_argument("--mode", default="tune", choices=["tune", "final"])
@@ -99,7 +99,7 @@ def main() -> int:
         dist.broadcast(flag, 0)
         nvls = bool(flag.item())
 
-    lo, hi = parse_size(args.lo), parse_size(args.hi)
+    lo, hi = parse_size(args.min_bytes), parse_size(args.max_bytes)
     sizes = []
     s = lo
     while s <= hi:

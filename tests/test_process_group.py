@@ -1,0 +1,128 @@
+"""The torch.distributed backend and the data-parallel driver, as separate client
+processes of a stand-alone ``mccsd`` (host backend): the full IPC path — control
+socket, fd passing for allocations and the request/completion rings."""
+import os
+import socket
+import subprocess
+import sys
+import tempfile
+
+import pytest
+
+from helpers import REPO, write_config
+
+WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+import mccs_b200.process_group as mpg
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"])
+dist.init_process_group("mccs", init_method=f"tcp://127.0.0.1:{os.environ['PORT']}", rank=rank, world_size=n)
+t = torch.arange(10, dtype=torch.float32) + rank
+dist.all_reduce(t)
+assert torch.equal(t, sum(torch.arange(10, dtype=torch.float32) + r for r in range(n))), t
+h = (torch.arange(7) + rank).to(torch.bfloat16); dist.all_reduce(h, op=dist.ReduceOp.AVG)
+assert torch.allclose(h.float(), torch.arange(7).float() + (n - 1) / 2, atol=0.1)
+b = torch.full((5,), float(rank)); dist.broadcast(b, src=1); assert torch.all(b == 1)
+outs = [torch.empty(3, dtype=torch.int64) for _ in range(n)]
+dist.all_gather(outs, torch.full((3,), rank, dtype=torch.int64))
+assert all(torch.all(o == r) for r, o in enumerate(outs))
+big = torch.empty(n * 4); dist.all_gather_into_tensor(big, torch.full((4,), float(rank)))
+assert torch.equal(big, torch.arange(n).repeat_interleave(4).float())
+m = torch.tensor([float(rank)]); dist.all_reduce(m, op=dist.ReduceOp.MAX); assert m.item() == n - 1
+rs = torch.empty(2); dist.reduce_scatter_tensor(rs, torch.arange(2 * n).float())
+assert torch.equal(rs, torch.arange(2 * n).float().reshape(n, 2)[rank] * n)
+# a tensor in service memory is reduced in place, without staging
+z, keep = mpg.empty(1000, torch.float32, device=rank)
+z.fill_(rank + 1.0); assert mpg.in_service_memory(z)
+dist.all_reduce(z); assert torch.all(z == n * (n + 1) / 2)
+dist.barrier()
+# torch's own DistributedDataParallel on top of the backend
+torch.manual_seed(0)
+model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 2))
+ddp = torch.nn.parallel.DistributedDataParallel(model)
+x = torch.randn(4, 8, generator=torch.Generator().manual_seed(rank))
+ddp(x).sum().backward()
+flat = torch.cat([p.grad.reshape(-1) for p in model.parameters()])
+ref = flat.clone(); dist.all_reduce(ref)
+assert torch.allclose(ref / n, flat, atol=1e-6)
+print(f"rank {rank} ok", flush=True)
+dist.destroy_process_group()
+"""
+
+TRAIN_WORKER = r"""
+import os, sys, torch
+import mccs_b200 as M
+from mccs_b200 import models
+from mccs_b200.parallel import DataParallel
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"])
+torch.manual_seed(0)
+m = models.build("gpt2-tiny")
+comm = M.Communicator(77, rank, n, device=rank)
+ddp = DataParallel(m, comm, bucket_mb=0.05)
+opt = torch.optim.SGD(m.parameters(), lr=0.1)
+ids = torch.randint(0, 512, (4, 33), generator=torch.Generator().manual_seed(rank))
+for it in range(3):
+    ddp.zero_grad()
+    loss = m(ids[:, :-1], ids[:, 1:])
+    loss.backward()
+    ddp.finish()
+    opt.step()
+torch.save([p.detach() for p in m.parameters()], os.environ["OUT"] + f".{rank}")
+assert len(ddp.buckets) > 3
+ddp.release(); comm.destroy(); M.finalize()
+print("ok", flush=True)
+"""
+
+
+def _free_port() -> int:
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.fixture()
+def standalone_daemon():
+    from mccs_b200 import daemon
+    d = tempfile.mkdtemp(prefix="mccs-pg-")
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=0,
+                       force_host=True)
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    yield sp
+    sp.stop()
+
+
+def _run_workers(code: str, n: int, control: str, extra_env=None):
+    env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=control, WORLD_SIZE=str(n), PORT=str(_free_port()),
+               MCCS_LOG="warn")
+    env.update(extra_env or {})
+    procs = [subprocess.Popen([sys.executable, "-c", code], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True) for r in range(n)]
+    outs = [p.communicate(timeout=180) for p in procs]
+    for p, (o, e) in zip(procs, outs):
+        assert p.returncode == 0, o + e
+    return outs
+
+
+def test_process_group_two_processes(standalone_daemon):
+    _run_workers(WORKER, 2, standalone_daemon.control)
+
+
+def test_data_parallel_matches_single_process(standalone_daemon, tmp_path):
+    import torch
+    from mccs_b200 import models
+    out = str(tmp_path / "params")
+    n = 2
+    _run_workers(TRAIN_WORKER, n, standalone_daemon.control, {"OUT": out})
+    torch.manual_seed(0)
+    m = models.build("gpt2-tiny")
+    opt = torch.optim.SGD(m.parameters(), lr=0.1)
+    batches = [torch.randint(0, 512, (4, 33), generator=torch.Generator().manual_seed(r)) for r in range(n)]
+    for _ in range(3):
+        opt.zero_grad()
+        (sum(m(b[:, :-1], b[:, 1:]) for b in batches) / n).backward()
+        opt.step()
+    for r in range(n):
+        got = torch.load(out + f".{r}")
+        for a, b in zip(got, m.parameters()):
+            assert torch.allclose(a, b.detach(), rtol=1e-4, atol=1e-5)

@@ -1,0 +1,335 @@
+"""Service behaviour beyond plain collectives, all on the host backend (no GPU):
+live reconfiguration, pause/resume with queued work, QoS windows, tracing, the admin
+endpoint, and the failure paths — every failure is made on the host (a client that
+exits, a rank that never joins), never by faulting a device."""
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import pytest
+import torch
+
+from helpers import NATIVE, REPO, fresh_comm_id, run_ranks, write_config
+
+
+def _host(M):
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+
+
+def test_live_reconfiguration_mid_run(service):
+    """Four ranks run batches of 16 back-to-back all-reduces; at iteration 5 the ring
+    order, the channel count and the algorithm are replaced while the job runs.
+    Results before and after are identical and no rank restarts anything."""
+    M = service
+    _host(M)
+    n, cid, count, iters = 4, fresh_comm_id(), 2048, 10
+    port = M.daemon.embedded_admin_port()
+    sync = threading.Barrier(n)
+
+    def rank_fn(r):
+        bufs = [M.Buffer(count * 4, r) for _ in range(16)]
+        ts = [b.tensor(torch.float32, count) for b in bufs]
+        c = M.Communicator(cid, r, n, device=r)
+        plans, sums = [], []
+        for it in range(iters):
+            for i, t in enumerate(ts):
+                t.fill_(float(r + i + it))
+            if it == 5:
+                sync.wait()
+                if r == 0:
+                    rep = M.reconfigure(port, [{"communicator_id": cid, "allreduce_algo": "ar_ring", "ctas": 3,
+                                                "channels": [{"channel_id": 0, "ring": [3, 2, 1, 0]},
+                                                             {"channel_id": 1, "ring": [0, 2, 1, 3]},
+                                                             {"channel_id": 2, "ring": [1, 3, 0, 2]}]}])
+                    assert rep["status"] == "ok", rep
+                sync.wait()
+            with M.group():
+                for t in ts:
+                    c.all_reduce(t)
+            plans.append(c.last_plan())
+            sums.append([float(t[0]) for t in ts])
+        q = c.query()
+        sync.wait()
+        c.destroy()
+        return plans, sums, q
+
+    outs = run_ranks(n, rank_fn)
+    for plans, sums, q in outs:
+        for it in range(iters):
+            assert sums[it] == [float(sum(r + i + it for r in range(n))) for i in range(16)]
+        assert plans[4][0] != "ar_ring"
+        assert plans[5] == ("ar_ring", 1) or plans[5][0] == "ar_ring"   # small messages use one channel
+        assert q["config_epoch"] == 1 and q["async_error"] == 0
+    stats = M.daemon.embedded_admin({"cmd": "stats"})["stats"]
+    assert str(cid) not in stats["communicators"]          # destroyed
+
+
+def test_reconfiguration_is_validated(service):
+    M = service
+    _host(M)
+    cid = fresh_comm_id()
+
+    def rank_fn(r):
+        c = M.Communicator(cid, r, 2, device=r)
+        if r == 0:
+            bad = M.daemon.embedded_admin({"comm_patterns_reconfig": [
+                {"communicator_id": cid, "channels": [{"channel_id": 0, "ring": [0, 0]}]}]}, type_=1)
+            unknown = M.daemon.embedded_admin({"comm_patterns_reconfig": [{"communicator_id": 999999, "ctas": 2}]}, type_=1)
+            algo = M.daemon.embedded_admin({"comm_patterns_reconfig": [{"communicator_id": cid, "allreduce_algo": "nope"}]}, type_=1)
+            res = (bad, unknown, algo)
+        else:
+            res = None
+        time.sleep(0.2)
+        q = c.query()
+        c.destroy()
+        return res, q
+
+    outs = run_ranks(2, rank_fn)
+    bad, unknown, algo = outs[0][0]
+    assert bad["status"] == "error" and "permutation" in bad["error"]
+    assert unknown["status"] == "error"
+    assert algo["status"] == "error"
+    assert outs[0][1]["config_epoch"] == 0
+
+
+def test_pause_queues_and_resume_replays(service):
+    """While a communicator is paused its collectives are queued, not failed
+    (the reference queues all-reduces that arrive during a reconfiguration,
+    src/mccs/src/proxy/engine.rs:1045-1047), and run in order after resume."""
+    M = service
+    _host(M)
+    n, cid = 2, fresh_comm_id()
+    done = [0] * n
+    gate = threading.Barrier(n + 1)
+
+    def rank_fn(r):
+        buf = M.Buffer(4096, r)
+        t = buf.tensor(torch.float32, 1024)
+        t.fill_(1.0)
+        c = M.Communicator(cid, r, n, device=r)
+        gate.wait()          # main thread pauses the communicator here
+        gate.wait()
+        for _ in range(3):
+            c.all_reduce(t)
+            done[r] += 1
+        c.destroy()
+        return float(t[0])
+
+    results = {}
+    th = threading.Thread(target=lambda: results.update(out=run_ranks(n, rank_fn)))
+    th.start()
+    gate.wait()
+    assert M.daemon.embedded_admin({"cmd": "pause", "communicator_id": cid})["status"] == "ok"
+    gate.wait()
+    time.sleep(0.4)
+    assert done == [0, 0]                       # queued behind the pause
+    assert M.daemon.embedded_admin({"cmd": "resume", "communicator_id": cid})["status"] == "ok"
+    th.join(30)
+    assert done == [3, 3]
+    assert results["out"] == [8.0, 8.0]         # 1 -> 2 -> 4 -> 8
+
+
+def test_qos_window_schedule_gates_a_tenant(service):
+    """The reference's Allow-window schedule (qos_schedule in mccs.toml): a tenant that
+    may only send during the first 10 ms of every 60 ms epoch needs several epochs for
+    a burst that otherwise takes microseconds."""
+    M = service
+    _host(M)
+    n, cid = 2, fresh_comm_id()
+    rep = M.daemon.embedded_admin({"cmd": "qos_set", "epoch_microsecs": 60000,
+                                   "schedule": {str(cid): {"intervals": [[0, 10000]], "mode": "Allow"}}})
+    assert rep["status"] == "ok"
+
+    def rank_fn(r):
+        buf = M.Buffer(4096, r)
+        t = buf.tensor(torch.float32, 1024)
+        t.fill_(1.0)
+        c = M.Communicator(cid, r, n, device=r)
+        t0 = time.time()
+        stamps = []
+        for _ in range(6):
+            c.all_reduce(t)
+            stamps.append((time.time() * 1e6) % 60000)
+        c.destroy()
+        return stamps, time.time() - t0, float(t[0])
+
+    try:
+        outs = run_ranks(n, rank_fn)
+        stats = M.daemon.embedded_admin({"cmd": "stats"})["stats"]["qos"]["tenants"][str(cid)]
+    finally:
+        M.daemon.embedded_admin({"cmd": "qos_set", "epoch_microsecs": 0, "schedule": {}})
+    for stamps, _, val in outs:
+        assert val == 64.0
+        # every completion falls inside (or just after) the allowed window
+        assert all(s < 25000 for s in stamps), stamps
+    assert stats["admitted"] == 6
+
+
+def test_trace_records_collectives(service):
+    M = service
+    _host(M)
+    assert M.daemon.embedded_admin({"cmd": "trace", "enabled": True, "clear": True})["status"] == "ok"
+    cid = fresh_comm_id()
+
+    def rank_fn(r):
+        buf = M.Buffer(1 << 16, r)
+        c = M.Communicator(cid, r, 2, device=r)
+        for _ in range(5):
+            c.all_reduce(buf.tensor(torch.float32, 1000))
+        c.destroy()
+
+    run_ranks(2, rank_fn)
+    rep = M.daemon.embedded_admin({"cmd": "trace", "enabled": False, "inline": True})
+    events = rep["trace"]["traceEvents"]
+    mine = [e for e in events if e["pid"] == cid]
+    assert len(mine) >= 10 and all(e["ph"] == "X" and e["dur"] >= 0 for e in mine)
+    assert any("rendezvous" in e["name"] for e in mine)
+
+
+def test_admin_over_tcp(service):
+    M = service
+    _host(M)
+    port = M.daemon.embedded_admin_port()
+    assert port > 0
+    rep = M.admin_request(port, {"cmd": "stats"})
+    assert rep["status"] == "ok" and "qos" in rep["stats"] and rep["stats"]["clients"] >= 1
+    assert M.admin_request(port, {"cmd": "no-such-command"})["status"] == "error"
+    table = M.admin_request(port, {"cmd": "tuning_get"})["tuning"]
+    assert "allreduce" in table and "8" in table["allreduce"]
+    assert M.admin_request(port, {"cmd": "tuning_set", "tuning": {"allreduce": {"2": [[-1, "ar_twoshot", 7, 256]]}}})["status"] == "ok"
+    cid = fresh_comm_id()
+
+    def rank_fn(r):
+        buf = M.Buffer(1 << 20, r)
+        c = M.Communicator(cid, r, 2, device=r)
+        c.all_reduce(buf.tensor(torch.float32, 1 << 18))
+        plan = c.last_plan()
+        c.destroy()
+        return plan
+
+    try:
+        assert run_ranks(2, rank_fn) == [("ar_twoshot", 7)] * 2
+    finally:
+        M.admin_request(port, {"cmd": "tuning_set", "tuning": table})
+
+
+# ---------------------------------------------------------------------------------------------
+# failure paths, each in its own daemon so that nothing leaks into other tests
+# ---------------------------------------------------------------------------------------------
+@pytest.fixture()
+def private_daemon():
+    from mccs_b200 import daemon
+    d = tempfile.mkdtemp(prefix="mccs-ft-")
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=-1,
+                       force_host=True, extra="init_timeout_ms = 1500")
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    yield sp
+    sp.stop()
+
+
+CLIENT = r"""
+import os, sys, time, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"]); mode = os.environ["MODE"]
+buf = M.Buffer(4096, rank)
+t = buf.tensor(torch.float32, 1024); t.fill_(1.0)
+try:
+    c = M.Communicator(4242, rank, n, device=rank)
+except Exception as e:
+    print("INIT_ERROR", getattr(e, "code", None), flush=True); sys.exit(0)
+c.all_reduce(t)
+print("FIRST_OK", float(t[0]), flush=True)
+if mode == "die" and rank == 1:
+    os._exit(17)                      # no goodbye, no destroy: the daemon only sees the socket close
+time.sleep(0.5)
+t0 = time.time()
+try:
+    c.all_reduce(t)
+    c.flush()
+    print("SECOND_OK", flush=True)
+except Exception as e:
+    print("SECOND_ERROR", getattr(e, "code", None), round(time.time() - t0, 2), flush=True)
+"""
+
+
+def _spawn_clients(control, n, mode, ranks=None):
+    env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=control, WORLD_SIZE=str(n), MODE=mode, MCCS_LOG="error",
+               MCCS_WC_TIMEOUT_MS="20000")
+    return [subprocess.Popen([sys.executable, "-c", CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                             stderr=subprocess.PIPE, text=True) for r in (ranks if ranks is not None else range(n))]
+
+
+def test_client_death_turns_into_an_error_for_its_peers(private_daemon):
+    procs = _spawn_clients(private_daemon.control, 2, "die")
+    outs = [p.communicate(timeout=60) for p in procs]
+    assert procs[1].returncode == 17
+    assert "FIRST_OK 2.0" in outs[0][0]
+    # the survivor is told that its peer is gone (-10), well inside the completion timeout
+    line = [l for l in outs[0][0].splitlines() if l.startswith("SECOND_")][0]
+    assert line.startswith("SECOND_ERROR -10"), outs[0]
+    assert float(line.split()[2]) < 10
+    # and the daemon keeps serving new communicators
+    procs = _spawn_clients(private_daemon.control, 2, "ok")
+    outs = [p.communicate(timeout=60) for p in procs]
+    assert all("SECOND_OK" in o[0] for o in outs), outs
+
+
+def test_rank_that_never_joins_times_out(private_daemon):
+    procs = _spawn_clients(private_daemon.control, 2, "ok", ranks=[0])
+    out, err = procs[0].communicate(timeout=60)
+    assert "INIT_ERROR -6" in out, out + err       # mccsTimeout after init_timeout_ms
+
+
+def test_example_apps_end_to_end(private_daemon, tmp_path):
+    """The C++ apps against a stand-alone daemon: hello, the two correctness probes,
+    both benchmarks, the trace replayer and the reconfiguration tool."""
+    env = dict(os.environ, MCCS_CONTROL=private_daemon.control, MCCS_LOG="error")
+
+    def run(args, **kw):
+        return subprocess.run(args, env=env, capture_output=True, text=True, timeout=120, **kw)
+
+    def run_ranks_app(name, n, extra):
+        procs = [subprocess.Popen([os.path.join(NATIVE, name), "--rank", str(r), "--num-ranks", str(n),
+                                   "--cuda-device-idx", str(r)] + extra, env=env, stdout=subprocess.PIPE,
+                                  stderr=subprocess.PIPE, text=True) for r in range(n)]
+        outs = [p.communicate(timeout=120) for p in procs]
+        for p, o in zip(procs, outs):
+            assert p.returncode == 0, o
+        return outs
+
+    r = run([os.path.join(NATIVE, "mccs_hello")])
+    assert r.returncode == 0 and "round trip ok" in r.stdout
+    outs = run_ranks_app("allreduce_proto", 4, ["--size", "65536", "--communicator", "42"])
+    assert all("passed" in o[0] for o in outs)
+    outs = run_ranks_app("allgather_proto", 3, ["--size", "65536", "--communicator", "43"])
+    assert all("passed" in o[0] for o in outs)
+    outs = run_ranks_app("allreduce_bench", 2, ["--size", "262144", "--communicator", "44", "--round", "5", "--epoch", "2"])
+    assert outs[0][0].count("Algorithm bandwidth") == 2 and "Bus bandwidth" in outs[0][0]
+    outs = run_ranks_app("allgather_bench", 2, ["--size", "65536", "--communicator", "45", "--round", "5"])
+    assert "Algorithm bandwidth" in outs[0][0]
+
+    trace = tmp_path / "trace.toml"
+    trace.write_text('communicator_id = 200\ncuda_devices = [0, 1]\n[[traces]]\nsize = 65536\ntype = "all_reduce"\n'
+                     'compute_interval = 500\n[[traces]]\nsize = 4096\ntype = "all_gather"\ncompute_interval = 100\n')
+    csv = tmp_path / "times.csv"
+    procs = [subprocess.Popen([os.path.join(NATIVE, "traffic_gen"), "--rank", str(rk), "--config", str(trace), "--iters", "30",
+                               "--save-path", str(csv), "--name", "vgg"], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True) for rk in range(2)]
+    outs = [p.communicate(timeout=120) for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert "[vgg] Rank 0: run time:" in outs[0][0]
+    assert len(csv.read_text().splitlines()) == 1 + 9      # header + iterations after the first 21 are dropped
+
+    patch = tmp_path / "patch.toml"
+    patch.write_text(f'mccs_addrs = ["127.0.0.1"]\nmccs_port = {private_daemon.admin_port}\n'
+                     '[[comm_patterns_reconfig]]\ncommunicator_id = 600\n'
+                     'channels = [ { channel_id = 0, ring = [1, 0] } ]\n')
+    r = run([os.path.join(NATIVE, "ring_config"), "--config", str(patch)])
+    assert "no communicator 600" in r.stdout          # reached the daemon, which rejected the unknown id
+    r = run([os.path.join(NATIVE, "ring_config"), "--stats", "--port", str(private_daemon.admin_port)])
+    assert r.returncode == 0 and json.loads(r.stdout.split(": ", 1)[1])["status"] == "ok"
