@@ -25,7 +25,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import re
 import subprocess
 import sys
 import time
@@ -66,7 +65,8 @@ def reference_arm(args, rank: int) -> int:
     dt = {"bf16": "bfloat16", "fp16": "half", "fp32": "float"}[args.dtype]
     env = dict(os.environ)
     import glob
-    libs = glob.glob(os.path.join(sys.prefix, "lib", "python*", "site-packages", "nvidia", "nccl", "lib"))
+    libs = glob.glob(os.path.join(sys.prefix, "lib", "python*", "site-packages", "nvidia", "*", "lib"))
+    libs.append("/usr/local/cuda/lib64")
     env["LD_LIBRARY_PATH"] = ":".join(libs + [env.get("LD_LIBRARY_PATH", "")])
     cmd = [exe, "-g", str(args.gpus), "-b", str(size), "-e", str(size), "-d", dt, "-n", str(args.steps),
            "-w", str(max(args.warmup, 3)), "-c", "0"]
@@ -82,14 +82,14 @@ def reference_arm(args, rank: int) -> int:
         # size count type redop root  time algbw busbw #wrong  time algbw busbw #wrong
         if len(f) >= 8 and f[0].isdigit() and int(f[0]) == size:
             try:
-                nums = [float(x) for x in f if re.fullmatch(r"[-+0-9.eE]+", x)]
-                # out-of-place columns come first: time(us) algbw busbw
-                t_us, alg = nums[-8], nums[-7]
+                # ... time algbw busbw #wrong | time algbw busbw #wrong (out of place, then in place)
+                t_us, alg = float(f[-8]), float(f[-7])
                 out.update({"ms_per_step": t_us / 1000.0})
             except (ValueError, IndexError):
                 pass
     if alg is None:
-        out["unavailable"] = "nccl-tests-mccs produced no result row: " + (res.stderr.strip()[-200:] or res.stdout.strip()[-200:])
+        tail = (res.stderr.strip() or res.stdout.strip())[-200:].replace("\n", " | ")
+        out["unavailable"] = "nccl-tests-mccs produced no result row: " + tail
         print(json.dumps(out))
         return 0
     out.update({
