@@ -496,6 +496,15 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
   uint32_t slot;
   auto it = comm->stream_slot.find((uint64_t)stream);
   if (it == comm->stream_slot.end()) {
+    // Two ranks of one communicator on the same stream can never finish: the second
+    // rank's "submitted" mark would sit behind the first rank's "wait until done".
+    std::unique_lock<std::mutex> g(g_ctx.mu);   // stream tables are only changed under this lock
+    for (mccsComm* other : g_ctx.comms)
+      if (other != comm && other->id == comm->id && other->stream_slot.count((uint64_t)stream)) {
+        LOG_ERROR("communicator %u: ranks %d and %d of this process use the same CUDA stream; give each rank "
+                  "its own stream (or run the daemon with [b200] sync = \"events\")", comm->id, other->rank, comm->rank);
+        return mccsInvalidArgument;
+      }
     slot = (uint32_t)comm->stream_slot.size();
     if (slot >= proto::kSyncMaxStreams) return mccsUnsupported;
     comm->stream_slot[(uint64_t)stream] = slot;

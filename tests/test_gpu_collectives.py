@@ -28,6 +28,15 @@ def svc(service):
     return service
 
 
+def _own_stream(dev):
+    """Each rank thread works on a stream of its own. With stream-memory-operation
+    synchronisation a collective call queues "wait until done" on the caller's stream
+    right away, so two ranks of one communicator must not share a stream (the second
+    rank's "submitted" mark would queue behind the first rank's wait)."""
+    torch.cuda.set_device(dev)
+    torch.cuda.set_stream(torch.cuda.Stream(device=dev))
+
+
 def _make(dtype, count, seed):
     g = torch.Generator().manual_seed(seed)
     if dtype.is_floating_point:
@@ -41,7 +50,7 @@ def _allreduce_case(M, n, dtype, count, algo, devices, op="sum", in_place=False,
 
     def rank_fn(r):
         dev = devices[r]
-        torch.cuda.set_device(dev)
+        _own_stream(dev)
         nbytes = (count + offset) * esz + 64
         a, b = M.Buffer(nbytes, dev), M.Buffer(nbytes, dev)
         x = _make(dtype, count, 100 + r)
@@ -120,7 +129,7 @@ def _allgather_case(M, n, nbytes, algo, devices, in_place):
 
     def rank_fn(r):
         dev = devices[r]
-        torch.cuda.set_device(dev)
+        _own_stream(dev)
         out = M.Buffer(nbytes * n + 64, dev)
         full = out.tensor(torch.uint8, nbytes * n)
         full.zero_()
@@ -173,7 +182,7 @@ def test_ring_many_loops_and_reorder(svc):
     sync = threading.Barrier(n)
 
     def rank_fn(r):
-        torch.cuda.set_device(0)
+        _own_stream(0)
         a = M.Buffer(count * 4, 0)
         b = M.Buffer(count * 4, 0)
         x = _make(torch.float32, count, 300 + r)
