@@ -36,6 +36,7 @@ int Planner::variant_from_name(const std::string& name) {
 }
 
 void Planner::load_defaults(bool nvls) {
+  std::unique_lock<std::shared_mutex> g(mu_);
   constexpr uint64_t KB = 1024, MB = 1024 * 1024;
   constexpr uint64_t kInf = ~0ull;
   for (int n = 1; n <= kMaxRanks; n++) {
@@ -88,6 +89,7 @@ bool Planner::load_json(const Value& root, std::string* err) {
         entries.push_back(e);
       }
       if (entries.empty()) continue;
+      std::unique_lock<std::shared_mutex> g(mu_);
       std::sort(entries.begin(), entries.end(),
                 [](const TuneEntry& a, const TuneEntry& b) { return a.max_bytes < b.max_bytes; });
       entries.back().max_bytes = ~0ull;
@@ -107,6 +109,7 @@ bool Planner::load_file(const std::string& path, std::string* err) {
 }
 
 Value Planner::to_json() const {
+  std::shared_lock<std::shared_mutex> g(mu_);
   static const char* kind_names[kNumCollKinds] = {"allreduce", "allgather"};
   Value root = Value::object();
   for (int k = 0; k < kNumCollKinds; k++) {
@@ -165,6 +168,7 @@ Plan Planner::plan(const PlanInput& in) const {
   p.bytes = message_bytes(in);
   if (in.nranks < 1 || in.nranks > kMaxRanks) { p.status = proto::kErrInvalidArgument; return p; }
   const bool is_ar = in.kind == kAllReduce;
+  std::shared_lock<std::shared_mutex> g(mu_);
   const TuneTable* t = find_table(in.kind, in.nranks);
   const TuneEntry* e = t ? t->lookup(p.bytes) : nullptr;
 

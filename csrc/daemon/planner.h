@@ -7,6 +7,8 @@
 #pragma once
 #include <stdint.h>
 
+#include <mutex>
+#include <shared_mutex>
 #include <string>
 #include <vector>
 
@@ -76,6 +78,7 @@ class Planner {
   TuneTable& table(int kind, int nranks);
   const TuneTable* find_table(int kind, int nranks) const;
   TuneTable tables_[kNumCollKinds][kMaxRanks + 1];
+  mutable std::shared_mutex mu_;   // tables can be replaced at run time (admin tuning_set) while proxies plan
 };
 
 }  // namespace mccs

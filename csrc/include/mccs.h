@@ -3,11 +3,18 @@
  * An application links against (or dlopens) libmccs.so and talks to the per-host
  * daemon `mccsd`. The daemon owns the GPUs' communication: it allocates the device
  * buffers (the application maps them), keeps the communicators, and launches the
- * collective kernels on its own streams. Ordering against the application's CUDA
- * streams is done with two interprocess events per (stream, communicator): the
- * library records "submitted" on the caller's stream before it posts the request,
- * and makes the caller's stream wait for the daemon's "done" event afterwards, so a
- * collective call never blocks the GPU timeline of the host thread.
+ * collective kernels on its own streams. A collective call is stream ordered like a
+ * kernel launch: it returns once the work is queued and the caller's stream will not
+ * run anything issued later until the collective has finished. Two mechanisms, chosen
+ * by the daemon ([b200] sync in its configuration):
+ *   - stream memory operations (default on GPUs that support them): the library
+ *     queues "write submitted" and "wait done" on the caller's stream, on two 64-bit
+ *     semaphores in device memory it shares with the daemon, and returns at once;
+ *     errors of a request show up on a later call or in mccsCommFlush. One stream may
+ *     carry only one rank of a given communicator.
+ *   - interprocess events (the reference's scheme): the library records "submitted",
+ *     waits for the daemon's completion message, then makes the stream wait for the
+ *     daemon's "done" event; the call blocks for one round trip and reports errors.
  *
  * This is the C form of the reference's Rust API (src/libmccs/src/lib.rs:23-27):
  *   cuda_malloc            -> mccsMalloc          (src/libmccs/src/memory.rs:12)

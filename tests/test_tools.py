@@ -1,0 +1,53 @@
+"""Tooling: the benchmark launcher (dependency order, weak services, output files,
+teardown) and the QoS interval planner."""
+import os
+import subprocess
+import sys
+
+from helpers import REPO
+
+
+def test_qos_interval_planner_matches_reference_algorithm():
+    from mccs_b200.utils.qos_intervals import calculate_intervals, to_toml
+    prem, vic, epoch = calculate_intervals(premium_comp=300, premium_comm=100, victim_comp=150, victim_comm=50)
+    assert epoch == 400                                    # lcm(400, 200)
+    assert prem == [(0, 100)]
+    assert vic == [(100, 150), (300, 350)]                 # first fit into the gap [100, 400)
+    # windows never overlap
+    for a, b in prem:
+        for c, d in vic:
+            assert b <= c or d <= a
+    text = to_toml(epoch, {7: prem, 8: vic})
+    sys.path.insert(0, REPO)
+    import tomllib
+    parsed = tomllib.loads(text)
+    assert parsed["qos_schedule"]["epoch_microsecs"] == 400
+    assert parsed["qos_schedule"]["schedule"]["8"]["intervals"] == [[100, 150], [300, 350]]
+
+
+def test_launcher_runs_workers_in_dependency_order(tmp_path):
+    marker = tmp_path / "order.txt"
+    spec = tmp_path / "bench.toml"
+    spec.write_text(f'''
+name = "unit"
+[[worker]]
+bin = "python"
+args = "-c \\"import time; open(r'{marker}', 'a').write('service\\\\n'); time.sleep(60)\\""
+weak = true
+dependencies = []
+[[worker]]
+bin = "python"
+args = "-c \\"open(r'{marker}', 'a').write('job1\\\\n'); print('hello from job1')\\""
+dependencies = [0]
+delay = 0.3
+[[worker]]
+bin = "python"
+args = "-c \\"open(r'{marker}', 'a').write('job2\\\\n')\\""
+dependencies = [1]
+''')
+    out = tmp_path / "out"
+    res = subprocess.run([sys.executable, "-m", "mccs_b200.utils.launcher", "--benchmark", str(spec), "--output-dir", str(out),
+                          "--timeout", "30"], env=dict(os.environ, PYTHONPATH=REPO), capture_output=True, text=True, timeout=60)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert marker.read_text().split() == ["service", "job1", "job2"]
+    assert "hello from job1" in (out / "unit" / "1_python.stdout").read_text()
