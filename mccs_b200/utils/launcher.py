@@ -90,7 +90,12 @@ def main() -> int:
                 if procs[i] is None and ready(i):
                     cmd = resolve_bin(w["bin"]) + shlex.split(w.get("args", ""))
                     env = dict(os.environ, PYTHONPATH=REPO + os.pathsep + os.environ.get("PYTHONPATH", ""))
-                    env.update({k: str(v) for k, v in w.get("env", {}).items()})
+                    env.setdefault("USER", os.environ.get("LOGNAME", "user"))   # what the daemon assumes when unset
+                    for k, v in w.get("env", {}).items():
+                        v = str(v)
+                        for name, val in env.items():
+                            v = v.replace("${" + name + "}", val)
+                        env[k] = v
                     tag = f"{i}_{os.path.basename(w['bin'])}"
                     so = open(os.path.join(out_dir, tag + ".stdout"), "w")
                     se = open(os.path.join(out_dir, tag + ".stderr"), "w")
