@@ -18,7 +18,7 @@ HOST_SRCS := csrc/common/value.cc csrc/common/log.cc csrc/ipc/uds.cc csrc/device
              csrc/daemon/config.cc csrc/daemon/planner.cc csrc/daemon/qos.cc csrc/daemon/trace.cc \
              csrc/daemon/runtime.cc csrc/daemon/daemon.cc csrc/daemon/proxy.cc csrc/daemon/admin.cc
 HOST_OBJS := $(patsubst csrc/%.cc,$(OBJ)/%.o,$(HOST_SRCS))
-CUDA_OBJS := $(OBJ)/device/cuda_backend.o $(OBJ)/kernels/launch.o $(OBJ)/kernels/untyped.o $(TYPE_OBJS)
+CUDA_OBJS := $(OBJ)/device/cuda_backend.o $(OBJ)/kernels/launch.o $(OBJ)/kernels/untyped.o $(OBJ)/kernels/noalloc.o $(TYPE_OBJS)
 SHIM_SRCS := csrc/shim/libmccs.cc csrc/common/value.cc csrc/common/log.cc csrc/ipc/uds.cc
 SHIM_OBJS := $(patsubst csrc/%.cc,$(OBJ)/%.o,$(SHIM_SRCS))
 HDRS := $(wildcard csrc/*/*.h csrc/*/*.cuh)

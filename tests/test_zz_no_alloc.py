@@ -1,0 +1,86 @@
+"""The allocation-free local AllReduce (csrc/include/mccs_noalloc.h), called through
+its exported C symbol, against the service's regular AllReduce on the same inputs.
+
+Who needs the entry point: callers that may not allocate when they reduce — inside a
+frozen or exhausted memory pool, in callbacks and latency-critical sections that must
+not enter the CUDA allocator. It keeps its synchronisation scratch in a static device
+array, so consecutive calls share state; two calls in a row check that the second one
+starts from a clean slate. This file is collected last on purpose: a failure here
+leaves every other test already run."""
+import ctypes
+
+import pytest
+import torch
+
+from helpers import fresh_comm_id, run_ranks
+
+pytestmark = pytest.mark.gpu
+
+DTYPE_CODE = {torch.float32: 7, torch.float16: 6, torch.bfloat16: 9}
+
+
+def _entry():
+    from mccs_b200 import _lib
+    lib = _lib.daemon_lib()
+    fn = lib.mccsLocalAllReduceNoAlloc
+    fn.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_size_t,
+                   ctypes.c_int, ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    return fn
+
+
+def _service_allreduce(M, inputs, dtype):
+    """The existing entry point: n ranks on cuda:0 through the daemon, two-shot kernel."""
+    n, count, cid = len(inputs), inputs[0].numel(), fresh_comm_id()
+
+    def rank_fn(r):
+        torch.cuda.set_device(0)
+        with torch.cuda.stream(torch.cuda.Stream()):     # one stream per rank of a communicator
+            a, b = M.Buffer(count * 4 + 64, 0), M.Buffer(count * 4 + 64, 0)
+            s, d = a.tensor(dtype, count), b.tensor(dtype, count)
+            s.copy_(inputs[r])
+            c = M.Communicator(cid, r, n, device=0)
+            c.all_reduce(s, d, algo="ar_twoshot")
+            torch.cuda.synchronize()
+            out = d.clone()
+            c.destroy()
+        return out
+
+    return run_ranks(n, rank_fn)
+
+
+@pytest.mark.parametrize("dtype,n,count", [(torch.float32, 4, 100003), (torch.bfloat16, 8, 1 << 20), (torch.float16, 2, 4096)])
+def test_no_alloc_entry_matches_service(service, dtype, n, count):
+    M = service
+    assert M.backend() == "cuda"
+    fn = _entry()
+    torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream()
+    tol = 1e-5 if dtype == torch.float32 else 1.6e-2
+    for call in range(2):                      # two calls in a row share the static scratch
+        g = torch.Generator().manual_seed(50 + call)
+        inputs = [((torch.rand(count, generator=g) * 2 - 1).to(dtype)).cuda() for _ in range(n)]
+        outputs = [torch.empty_like(x) for x in inputs]
+        ins = (ctypes.c_void_p * n)(*[x.data_ptr() for x in inputs])
+        outs = (ctypes.c_void_p * n)(*[x.data_ptr() for x in outputs])
+        rc = fn(ins, outs, n, count, DTYPE_CODE[dtype], ctypes.c_void_p(stream.cuda_stream))
+        assert rc == 0, f"cudaError {rc}"
+        torch.cuda.synchronize()
+        want = _service_allreduce(M, inputs, dtype)
+        ref = torch.stack([x.double() for x in inputs]).sum(0)
+        for r in range(n):
+            assert torch.allclose(outputs[r].double(), want[r].double(), rtol=tol, atol=tol * n)
+            assert torch.allclose(outputs[r].double(), ref, rtol=tol, atol=tol * n)
+
+
+def test_no_alloc_entry_rejects_what_it_cannot_do(service):
+    fn = _entry()
+    torch.cuda.set_device(0)
+    x = torch.zeros(16, device="cuda")
+    one = (ctypes.c_void_p * 1)(x.data_ptr())
+    many = (ctypes.c_void_p * 9)(*([x.data_ptr()] * 9))
+    assert fn(many, many, 9, 16, 7, None) != 0        # more buffers than the scratch has slots for
+    assert fn(one, one, 1, 16, 2, None) != 0          # int32 is not offered
+    assert fn(one, one, 0, 16, 7, None) != 0
+    assert fn(one, one, 1, 16, 7, None) == 0          # single buffer in place: nothing to do, still valid
+    torch.cuda.synchronize()
