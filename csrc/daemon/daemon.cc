@@ -591,7 +591,13 @@ int Daemon::finalize_communicator(Communicator& c) {
     }
     if ((rc = backend_->hostmem_alloc(sizeof(StatusBlock), &p)) != proto::kOk) return rc;
     rs.status = (StatusBlock*)p;
-    if (memops_) {
+    // Stream-memory-operation ordering only for clients in other processes. A client
+    // that lives in the daemon's own process has its stream in the same CUDA context
+    // as the backend streams; streams of one context can share a hardware queue, and a
+    // "wait for done" blocking the client's stream could then hold up the very backend
+    // stream that has to produce "done". Such clients use ordinary events, which are
+    // cheap inside one process.
+    if (memops_ && !rs.same_process) {
       if ((rc = backend_->alloc(rs.device, proto::kSyncPageBytes, &rs.sync_alloc)) != proto::kOk) return rc;
       if ((rc = backend_->zero_memory(rs.device, rs.sync_alloc.va, proto::kSyncPageBytes)) != proto::kOk) return rc;
     }

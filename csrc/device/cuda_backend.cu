@@ -11,6 +11,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <unistd.h>
 
@@ -97,6 +98,9 @@ struct DeviceGuard {
 class CudaBackend : public Backend {
  public:
   bool init(const BackendOptions& opt, std::string* why) {
+    // One hardware queue per stream as far as the GPU allows: a backend stream that waits
+    // for one tenant's "submitted" mark must not hold up another tenant's stream.
+    setenv("CUDA_DEVICE_MAX_CONNECTIONS", "32", 0);
     int n = 0;
     cudaError_t e = cudaGetDeviceCount(&n);
     if (e != cudaSuccess || n <= 0) {

@@ -25,10 +25,23 @@ from . import _lib
 _embedded_path: Optional[str] = None
 
 
+TUNING_FILE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "tuning_b200.json")
+
+
 def default_config(prefix: str, *, transport: str = "auto", nvls: bool = True, channel_count: int = 2,
                    wait_timeout_ms: int = 10000, host_devices: int = 8, force_host: bool = False,
-                   listen_port: int = -1, trace: bool = False, extra: str = "") -> str:
-    """TOML text of a daemon configuration with its sockets under ``prefix``."""
+                   listen_port: int = -1, trace: bool = False, sync: str = "auto", tuning_file: Optional[str] = None,
+                   extra: str = "") -> str:
+    """TOML text of a daemon configuration with its sockets under ``prefix``.
+
+    The size -> (variant, CTAs) table measured on B200 (``configs/tuning_b200.json``,
+    written by ``python -m mccs_b200.utils.sweep --tuning``) is loaded when present;
+    pass ``tuning_file=""`` for the built-in defaults.
+    """
+    if tuning_file is None:
+        tuning_file = TUNING_FILE if os.path.exists(TUNING_FILE) else ""
+    wait_timeout_ms = int(os.environ.get("MCCS_WAIT_TIMEOUT_MS", wait_timeout_ms))
+    tuning_line = f'tuning_file = "{tuning_file}"' if tuning_file else ""
     return f"""
 listen_port = {listen_port}
 mccs_daemon_prefix = "{prefix}"
@@ -45,6 +58,8 @@ wait_timeout_ms = {wait_timeout_ms}
 host_devices = {host_devices}
 force_host_backend = {"true" if force_host else "false"}
 trace = {"true" if trace else "false"}
+sync = "{sync}"
+{tuning_line}
 {extra}
 """
 

@@ -60,6 +60,8 @@ def main() -> int:
     ap.add_argument("--tuning", default="")
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--in-place", action="store_true")
+    ap.add_argument("--sync", default="auto", choices=["auto", "memops", "events"])
+    ap.add_argument("--merge-into", default="", help="also merge the new tuning rows into this JSON file")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -84,7 +86,9 @@ def main() -> int:
     prefix = f"/tmp/mccs-sweep-{os.getuid()}-{os.environ.get('MASTER_PORT', '0')}"
     port_file = prefix + "/admin_port"
     if local_rank == 0:
-        M.daemon.start_embedded(prefix=prefix, listen_port=-1)
+        # a tuning pass starts from the built-in table, a final pass uses the measured one
+        M.daemon.start_embedded(prefix=prefix, listen_port=-1, sync=args.sync,
+                                tuning_file="" if args.mode == "tune" else None)
         with open(port_file, "w") as f:
             f.write(str(M.daemon.embedded_admin_port()))
     barrier()
@@ -240,6 +244,15 @@ def main() -> int:
                     table[coll][str(n)][-1][0] = -1
             with open(args.tuning, "w") as f:
                 json.dump(table, f, indent=1)
+            if args.merge_into:
+                merged = {"allreduce": {}, "allgather": {}}
+                if os.path.exists(args.merge_into):
+                    with open(args.merge_into) as f:
+                        merged.update(json.load(f))
+                for coll in table:
+                    merged.setdefault(coll, {}).update({k: v for k, v in table[coll].items() if v})
+                with open(args.merge_into, "w") as f:
+                    json.dump(merged, f, indent=1)
     comm.destroy()
     send_buf.free()
     recv_buf.free()
