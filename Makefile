@@ -47,16 +47,16 @@ $(OBJ)/inst_$(1).o: csrc/kernels/inst_dtype.cu $(HDRS)
 endef
 $(foreach t,$(TYPES),$(eval $(call TYPE_RULE,$(word 1,$(subst :, ,$(t))),$(word 2,$(subst :, ,$(t))))))
 
-$(OUT)/libmccs_daemon.so: $(HOST_OBJS) $(CUDA_OBJS)
+$(OUT)/libmccs_daemon.so: $(HOST_OBJS) $(CUDA_OBJS) csrc/exports.map
 	@mkdir -p $(OUT)
-	$(NVCC) $(ARCH) -shared -cudart static -o $@ $^ $(LDLIBS)
+	$(NVCC) $(ARCH) -shared -cudart static -Xlinker --version-script=csrc/exports.map -o $@ $(HOST_OBJS) $(CUDA_OBJS) $(LDLIBS)
 
-$(OUT)/libmccs.so: $(SHIM_OBJS)
+$(OUT)/libmccs.so: $(SHIM_OBJS) csrc/exports.map
 	@mkdir -p $(OUT)
-	$(CXX) -shared -o $@ $^ $(LDLIBS)
+	$(CXX) -shared -Wl,--version-script=csrc/exports.map -o $@ $(SHIM_OBJS) $(LDLIBS)
 
 $(OUT)/libmccs_preload.so: $(OBJ)/shim/preload.o $(OUT)/libmccs.so
-	$(CXX) -shared -o $@ $(OBJ)/shim/preload.o -L$(OUT) -lmccs -Wl,-rpath,'$$ORIGIN' $(LDLIBS)
+	$(CXX) -shared -Wl,--version-script=csrc/exports_preload.map -o $@ $(OBJ)/shim/preload.o -L$(OUT) -lmccs -Wl,-rpath,'$$ORIGIN' $(LDLIBS)
 
 $(OUT)/mccsd: $(OBJ)/daemon/main.o $(OUT)/libmccs_daemon.so
 	$(CXX) -o $@ $(OBJ)/daemon/main.o -L$(OUT) -lmccs_daemon -Wl,-rpath,'$$ORIGIN' $(LDLIBS)

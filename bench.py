@@ -181,6 +181,10 @@ def main() -> int:
 
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
+    # clocks are sampled from before the warm-up to after the last timed step
+    sampler = ClockSampler(dev, period_ms=100) if (have_cuda and local_rank == 0) else None
+    if sampler:
+        sampler.start()
     for _ in range(warmup):
         step()
     if have_cuda:
@@ -199,8 +203,6 @@ def main() -> int:
         ok = bool(torch.allclose(got, want, rtol=tol, atol=tol * n))
     elif is_ar:
         ok = bool(torch.equal(recv[:check_n], send[:check_n])) if n == 1 else True
-
-    sampler = ClockSampler(dev) if (have_cuda and local_rank == 0) else None
 
     def timed(fn) -> float:
         if not have_cuda:
@@ -223,8 +225,6 @@ def main() -> int:
         barrier()
         return max_over_ranks(e0.elapsed_time(e1) / steps)
 
-    if sampler:
-        sampler.start()
     ms = timed(step)
     variant, ctas = comm.last_plan()
 

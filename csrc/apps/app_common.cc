@@ -66,7 +66,7 @@ bool load() {
   static bool tried = false;
   if (tried) return g.ok;
   tried = true;
-  void* lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+  void* lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_LOCAL);
   if (!lib) return false;
   g.ok = sym(lib, "cuInit", &g.init) && sym(lib, "cuDeviceGet", &g.device_get) &&
          sym(lib, "cuDevicePrimaryCtxRetain", &g.retain) && sym(lib, "cuCtxSetCurrent", &g.set_current) &&

@@ -41,6 +41,7 @@
 namespace mccs {
 
 constexpr int kCollSlots = 128;   // in-flight rendezvous slots per communicator
+constexpr uint64_t kMaxGpuQueue = 48;   // collectives (slices) a rank may have launched but not finished
 
 class Daemon;
 class Communicator;
@@ -134,6 +135,7 @@ struct RankState {
   struct Inflight { uint64_t ticket; uint64_t bytes; };
   std::deque<Inflight> inflight;       // rank 0 only: admitted, not yet seen finished
   uint64_t traced_ticket = 0;
+  uint64_t last_ticket = 0;            // ticket of the newest kernel launched for this rank
   std::atomic<bool> joined{false};
   std::atomic<bool> gone{false};       // its client went away
 };

@@ -395,6 +395,7 @@ bool ProxyEngine::launch_slices(RankState& rs, CollSlot& s, uint64_t seq) {
       const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
       rs.inflight.push_back({a.seq, bytes});
     }
+    rs.last_ticket = a.seq;
     rs.next_slice++;
   }
   if (rs.sync_alloc.va && op.sync_slot)
@@ -446,6 +447,7 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
     }
     const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
     r0.inflight.push_back({a.seq, bytes});
+    r0.last_ticket = a.seq;
     r0.next_slice++;
   }
   for (int r = 0; r < c.nranks; r++) {
@@ -526,6 +528,15 @@ bool ProxyEngine::advance(RankState& rs) {
       any = true;
     }
     if (st == kSlotPlanning) break;
+    // Bound the work queued on the GPU per rank. Clients can post far ahead of the GPU
+    // (calls return before anything runs); without a bound the backend streams fill up,
+    // a launch call then blocks this proxy thread, and since a blocked kernel at the head
+    // of that stream waits for a peer kernel that another (equally blocked) proxy has to
+    // launch, the proxies could wait on each other forever.
+    if (st == kSlotPlanned) {
+      RankState& gate = group ? *c.ranks[0] : rs;
+      if (gate.status && gate.last_ticket > *(volatile uint64_t*)&gate.status->done_seq + kMaxGpuQueue) break;
+    }
     int status = proto::kOk;
     if (st == kSlotFailed) {
       status = s.status;

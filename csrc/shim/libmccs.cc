@@ -10,6 +10,8 @@
 #include <cuda.h>
 #include <dlfcn.h>
 #include <errno.h>
+#include <execinfo.h>
+#include <signal.h>
 #include <netdb.h>
 #include <poll.h>
 #include <pthread.h>
@@ -82,7 +84,7 @@ template <typename Fn> bool sym(void* lib, const char* name, Fn* out) {
 bool load_driver() {
   if (g_drv.tried) return g_drv.ok;
   g_drv.tried = true;
-  g_drv.lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+  g_drv.lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_LOCAL);
   if (!g_drv.lib) return false;
   void* l = g_drv.lib;
   // Versioned names are what cuda.h's macros map the plain names to.
@@ -591,6 +593,36 @@ mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, vo
   return finish_on_stream(comm, stream);
 }
 
+}  // namespace
+
+// Optional native backtrace on a crash (MCCS_BACKTRACE=1): prints the C/C++ frames to
+// stderr, then hands over to whatever handler was installed before (Python's
+// faulthandler, the default action).
+namespace {
+struct sigaction g_prev_segv;
+void on_segv(int sig, siginfo_t* info, void* uctx) {
+  void* frames[64];
+  int n = backtrace(frames, 64);
+  const char msg[] = "\n[libmccs] fatal signal, native backtrace:\n";
+  if (write(2, msg, sizeof msg - 1) < 0) {}
+  backtrace_symbols_fd(frames, n, 2);
+  if (g_prev_segv.sa_flags & SA_SIGINFO) {
+    if (g_prev_segv.sa_sigaction) g_prev_segv.sa_sigaction(sig, info, uctx);
+  } else if (g_prev_segv.sa_handler && g_prev_segv.sa_handler != SIG_DFL && g_prev_segv.sa_handler != SIG_IGN) {
+    g_prev_segv.sa_handler(sig);
+  }
+  signal(sig, SIG_DFL);
+  raise(sig);
+}
+__attribute__((constructor)) void install_backtrace_handler() {
+  const char* e = getenv("MCCS_BACKTRACE");
+  if (!e || e[0] == '0') return;
+  struct sigaction sa;
+  memset(&sa, 0, sizeof sa);
+  sa.sa_sigaction = on_segv;
+  sa.sa_flags = SA_SIGINFO | SA_ONSTACK;
+  sigaction(SIGSEGV, &sa, &g_prev_segv);
+}
 }  // namespace
 
 // ---------------------------------------------------------------------------

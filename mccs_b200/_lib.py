@@ -26,7 +26,8 @@ def _load(name: str) -> ctypes.CDLL:
         raise ImportError(
             f"{path} is missing: build the native code with `make -j` at the repository root "
             "(or `python -c 'import __graft_entry__ as g; g.build()'`)")
-    return ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+    # RTLD_LOCAL: nothing else in the process should resolve symbols against these libraries
+    return ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
 
 
 class CommInfo(Structure):

@@ -144,7 +144,7 @@ def orchestrate(a) -> int:
         tenants = "\n".join(f"[qos.tenants.{x['comm_id']}]\nweight = {x['weight']}" for x in apps)
         extra = "" if a.no_qos else ""
         prefix = f"/tmp/mccs-mt-{os.getuid()}-{os.getpid()}"
-        cfg = M.daemon.default_config(prefix, listen_port=-1, host_devices=8, extra=extra) + ("" if a.no_qos else tenants + "\n")
+        cfg = M.daemon.default_config(prefix, listen_port=-1, host_devices=8, sync=a.sync, extra=extra) + ("" if a.no_qos else tenants + "\n")
         M.daemon.start_embedded(cfg)
         admin_port = M.daemon.embedded_admin_port()
         env["MCCS_CONTROL"] = prefix + "/control.sock"
@@ -212,6 +212,7 @@ def main() -> int:
     ap.add_argument("--reconfig-app", default="C")
     ap.add_argument("--apps", default="", help="JSON list of {name, comm_id, devices, weight}")
     ap.add_argument("--no-qos", action="store_true")
+    ap.add_argument("--sync", default="auto", choices=["auto", "memops", "events"])
     ap.add_argument("--host-devices", type=int, default=4)
     ap.add_argument("--timeout", type=float, default=900.0)
     # worker-only

@@ -61,6 +61,8 @@ def main() -> int:
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--in-place", action="store_true")
     ap.add_argument("--sync", default="auto", choices=["auto", "memops", "events"])
+    ap.add_argument("--daemon", default="standalone", choices=["standalone", "embedded"],
+                    help="stand-alone mccsd (every rank an outside client) or hosted by local rank 0")
     ap.add_argument("--merge-into", default="", help="also merge the new tuning rows into this JSON file")
     args = ap.parse_args()
 
@@ -85,19 +87,31 @@ def main() -> int:
 
     prefix = f"/tmp/mccs-sweep-{os.getuid()}-{os.environ.get('MASTER_PORT', '0')}"
     port_file = prefix + "/admin_port"
+    spawned = None
+    describe = ""
     if local_rank == 0:
+        os.makedirs(prefix, exist_ok=True)
         # a tuning pass starts from the built-in table, a final pass uses the measured one
-        M.daemon.start_embedded(prefix=prefix, listen_port=-1, sync=args.sync,
-                                tuning_file="" if args.mode == "tune" else None)
+        tuning = "" if args.mode == "tune" else None
+        if args.daemon == "embedded":
+            M.daemon.start_embedded(prefix=prefix, listen_port=-1, sync=args.sync, tuning_file=tuning)
+            port, describe = M.daemon.embedded_admin_port(), M.daemon.describe_embedded()
+        else:
+            # the deployment shape: a stand-alone mccsd, every rank an outside client
+            with open(prefix + "/mccs.toml", "w") as f:
+                f.write(M.daemon.default_config(prefix, listen_port=-1, sync=args.sync, tuning_file=tuning))
+            spawned = M.daemon.spawn(prefix + "/mccs.toml")
+            port, describe = spawned.admin_port, f"stand-alone mccsd ({spawned.backend})"
         with open(port_file, "w") as f:
-            f.write(str(M.daemon.embedded_admin_port()))
+            f.write(str(port))
     barrier()
     M.init(prefix + "/control.sock")
     admin_port = int(open(port_file).read())
     nvls = True
     if rank == 0:
-        nvls = "nvls=on" in M.daemon.describe_embedded()
-        print(f"# {M.daemon.describe_embedded()}", flush=True)
+        stats = M.admin_request(admin_port, {"cmd": "stats"})["stats"]
+        nvls = "nvls=on" in stats["backend"]
+        print(f"# {describe}: {stats['backend']}", flush=True)
     if n > 1:
         flag = torch.tensor([1 if nvls else 0], device=f"cuda:{dev}")
         dist.broadcast(flag, 0)
@@ -259,7 +273,10 @@ def main() -> int:
     M.finalize()
     barrier()
     if local_rank == 0:
-        M.daemon.stop_embedded()
+        if spawned is not None:
+            spawned.stop()
+        else:
+            M.daemon.stop_embedded()
     if n > 1:
         dist.destroy_process_group()
     return 0
