@@ -10,13 +10,14 @@
 //     sizes the reference uses. The per-GPU proxy polls the request ring directly,
 //     so a collective crosses one thread boundary instead of the reference's two.
 #pragma once
+#include <stddef.h>
 #include <stdint.h>
 
 namespace mccs {
 namespace proto {
 
 constexpr uint32_t kMagic = 0x5343434du;  // "MCCS"
-constexpr uint32_t kVersion = 4;
+constexpr uint32_t kVersion = 5;
 constexpr uint32_t kWqDepth = 64;
 constexpr uint32_t kCqDepth = 64;
 constexpr uint32_t kWrBytes = 128;
@@ -215,6 +216,24 @@ struct alignas(64) WorkCompletion {
   uint64_t reserved[4];
 };
 static_assert(sizeof(WorkCompletion) == kWcBytes, "completion must fill one 64-byte slot");
+
+// Completion state of requests submitted in mem-op mode, at the end of the data-path
+// segment. Such requests are not answered one by one (the caller does not wait for
+// them, so a completion ring could fill up while the caller sits in a CUDA
+// synchronisation that only ends once the daemon has launched more work); the daemon
+// counts them here and keeps the first error.
+struct alignas(64) DpStatus {
+  uint64_t completed;      // mem-op requests the daemon has finished handling (launched or failed)
+  int32_t first_error;     // Status of the first failed request, 0 = none
+  uint32_t last_variant;
+  uint32_t last_ctas;
+  uint32_t pad_[11];
+};
+static_assert(sizeof(DpStatus) == 64, "DpStatus layout is part of the ABI");
+
+inline size_t dp_wq_bytes() { return ((sizeof(uint64_t) * 24 + (size_t)kWqDepth * kWrBytes) + 63) / 64 * 64; }
+inline size_t dp_cq_bytes() { return ((sizeof(uint64_t) * 24 + (size_t)kCqDepth * kWcBytes) + 63) / 64 * 64; }
+inline size_t dp_segment_bytes() { return dp_wq_bytes() + dp_cq_bytes() + sizeof(DpStatus); }
 
 inline uint64_t make_comm_handle(uint32_t comm_id, int rank) { return ((uint64_t)comm_id << 32) + (uint32_t)rank; }
 inline uint32_t handle_comm_id(uint64_t h) { return (uint32_t)(h >> 32); }

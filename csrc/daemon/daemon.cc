@@ -515,12 +515,10 @@ void Daemon::on_comm_init(Session& s, const proto::CommInitReq& m) {
       r.comm_init_reply.dp_bytes = (uint32_t)rs.dp_bytes;
       int fds[2] = {rs.dp_fd, -1};
       int nfds = 1;
-      if (rs.sync_alloc.va) {
-        r.comm_init_reply.sync_size = rs.sync_alloc.size;
-        r.comm_init_reply.sync_daemon_va = rs.sync_alloc.va;
-        r.comm_init_reply.sync_share_kind = ps->same_process ? proto::kShareSameProcess : rs.sync_alloc.share_kind;
-        memcpy(r.comm_init_reply.sync_ipc_handle, rs.sync_alloc.ipc_handle, sizeof rs.sync_alloc.ipc_handle);
-        if (!ps->same_process && rs.sync_alloc.share_fd >= 0) fds[nfds++] = rs.sync_alloc.share_fd;
+      if (rs.sync.host) {
+        r.comm_init_reply.sync_size = rs.sync.bytes;
+        r.comm_init_reply.sync_share_kind = proto::kShareHostFd;
+        fds[nfds++] = rs.sync.fd;
       }
       reply(*ps, r, sizeof(proto::CommInitReply), fds, nfds);
     } else {
@@ -598,19 +596,19 @@ int Daemon::finalize_communicator(Communicator& c) {
     // stream that has to produce "done". Such clients use ordinary events, which are
     // cheap inside one process.
     if (memops_ && !rs.same_process) {
-      if ((rc = backend_->alloc(rs.device, proto::kSyncPageBytes, &rs.sync_alloc)) != proto::kOk) return rc;
-      if ((rc = backend_->zero_memory(rs.device, rs.sync_alloc.va, proto::kSyncPageBytes)) != proto::kOk) return rc;
+      if ((rc = backend_->sync_page_create(rs.device, &rs.sync)) != proto::kOk) return rc;
     }
     if ((rc = backend_->stream_create(rs.device, prio, &rs.stream)) != proto::kOk) return rc;
     if ((rc = backend_->event_create(rs.device, &rs.backend_event, rs.event_handle)) != proto::kOk) return rc;
     // Data-path segment: request ring followed by completion ring.
-    const size_t wq_bytes = (ipc::Ring::bytes_needed(proto::kWqDepth, proto::kWrBytes) + 63) / 64 * 64;
-    const size_t cq_bytes = (ipc::Ring::bytes_needed(proto::kCqDepth, proto::kWcBytes) + 63) / 64 * 64;
-    rs.dp_bytes = wq_bytes + cq_bytes;
+    const size_t wq_bytes = proto::dp_wq_bytes();
+    rs.dp_bytes = proto::dp_segment_bytes();
     rs.dp_fd = ipc::memfd_make("mccs-dp", rs.dp_bytes);
     if (rs.dp_fd < 0) return proto::kErrOutOfMemory;
     rs.dp_mem = ipc::map_shared(rs.dp_fd, rs.dp_bytes);
     if (!rs.dp_mem) return proto::kErrOutOfMemory;
+    rs.dp_status = (proto::DpStatus*)((char*)rs.dp_mem + wq_bytes + proto::dp_cq_bytes());
+    memset(rs.dp_status, 0, sizeof(proto::DpStatus));
     rs.wq.init(rs.dp_mem, proto::kWqDepth, proto::kWrBytes);
     rs.cq.init((char*)rs.dp_mem + wq_bytes, proto::kCqDepth, proto::kWcBytes);
   }
@@ -722,7 +720,7 @@ void Daemon::destroy_communicator(uint32_t comm_id) {
     if (r->pad) backend_->scratch_free(r->device, r->pad, sizeof(SignalPad), c->host_staged);
     if (r->fifo) backend_->scratch_free(r->device, r->fifo, r->fifo_bytes, c->host_staged);
     if (r->status) backend_->hostmem_free(r->status);
-    if (r->sync_alloc.va) backend_->release(&r->sync_alloc);
+    if (r->sync.host) backend_->sync_page_destroy(r->device, &r->sync);
     if (r->dp_mem) ipc::unmap_shared(r->dp_mem, r->dp_bytes);
     if (r->dp_fd >= 0) close(r->dp_fd);
   }

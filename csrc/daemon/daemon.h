@@ -115,6 +115,7 @@ struct RankState {
   void* dp_mem = nullptr;
   size_t dp_bytes = 0;
   ipc::Ring wq, cq;
+  proto::DpStatus* dp_status = nullptr;
   // device resources
   void* stream = nullptr;
   void* backend_event = nullptr;
@@ -123,7 +124,7 @@ struct RankState {
   StatusBlock* status = nullptr;
   char* fifo = nullptr;
   size_t fifo_bytes = 0;
-  Allocation sync_alloc;               // semaphore page shared with the client (mem-op mode)
+  SyncPage sync;                       // semaphore page shared with the client (mem-op mode)
   // proxy-owned progress state
   uint64_t next_post_seq = 0;
   uint64_t next_launch_seq = 0;
@@ -208,6 +209,7 @@ class ProxyEngine : public Engine {
   bool complete_request(RankState& rs, CollSlot& s, uint64_t seq, int status);
   void signal_done(RankState& rs, uint64_t user_seq);
   void order_after_client(RankState& rs, const CollOp& op, void* stream);
+  bool clients_ready(Communicator& c, CollSlot& s, int self_rank);
   void finish_slot(Communicator& c, CollSlot& s, uint64_t seq);
   void housekeeping(RankState& rs);
   int ensure_mc(Communicator& c, CollSlot& s, bool for_recv, uint64_t* out_va);

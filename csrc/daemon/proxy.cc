@@ -92,8 +92,11 @@ bool ProxyEngine::intake(RankState& rs) {
       int err = rs.comm->async_error.load();
       wc.status = err ? err : proto::kErrPeerLost;
       wc.user_seq = rs.pending_wr.user_seq;
-      if (rs.pending_wr.sync_slot) signal_done(rs, rs.pending_wr.user_seq);
-      if (!rs.cq.try_push(&wc)) { rs.pending_wc = wc; rs.have_pending_wc = true; }
+      if (rs.pending_wr.sync_slot && rs.dp_status) {
+        signal_done(rs, rs.pending_wr.user_seq);
+        if (rs.dp_status->first_error == 0) rs.dp_status->first_error = wc.status;
+        __atomic_store_n(&rs.dp_status->completed, rs.dp_status->completed + 1, __ATOMIC_RELEASE);
+      } else if (!rs.cq.try_push(&wc)) { rs.pending_wc = wc; rs.have_pending_wc = true; }
       rs.have_pending_wr = false;
       any = true;
       continue;
@@ -398,20 +401,41 @@ bool ProxyEngine::launch_slices(RankState& rs, CollSlot& s, uint64_t seq) {
     rs.last_ticket = a.seq;
     rs.next_slice++;
   }
-  if (rs.sync_alloc.va && op.sync_slot)
-    be->stream_write_value64(rs.device, rs.stream, rs.sync_alloc.va + 8 * proto::kSyncDoneSlot, op.user_seq);
+  if (rs.sync.host && op.sync_slot)
+    be->stream_write_value64(rs.device, rs.stream, rs.sync.dev_addr + 8 * proto::kSyncDoneSlot, op.user_seq);
   else
     be->event_record(rs.device, rs.backend_event, rs.stream);
   (void)seq;
   return true;
 }
 
+// Mem-op mode: has every rank's stream reached this collective? Each client's stream
+// writes a "submitted" value into its semaphore page (host memory) when the work queued
+// before the collective is done; the proxies read those words with plain loads. Kernels
+// are launched only once all inputs exist, so no kernel sits on SMs waiting for a peer
+// whose application is still computing, and no backend stream ever blocks.
+bool ProxyEngine::clients_ready(Communicator& c, CollSlot& s, int self_rank) {
+  // An event-ordered rank (a client inside the daemon's process) blocks on the host until
+  // its kernel is queued, so it is launched at once, as before; its kernel then waits
+  // for the others on the device, within the usual bound.
+  if (self_rank >= 0 && !(c.ranks[(size_t)self_rank]->sync.host && s.ops[self_rank].sync_slot)) return true;
+  for (int r = 0; r < c.nranks; r++) {
+    const CollOp& op = s.ops[r];
+    const RankState& rr = *c.ranks[(size_t)r];
+    if (!rr.sync.host || !op.sync_slot) continue;   // event-ordered client: the stream wait covers it
+    const volatile uint64_t* sem = (const volatile uint64_t*)rr.sync.host + proto::kSyncFirstStreamSlot +
+                                   (op.sync_slot - 1) % proto::kSyncMaxStreams;
+    if ((int64_t)(*sem - op.sync_value) < 0) return false;
+  }
+  std::atomic_thread_fence(std::memory_order_acquire);
+  return true;
+}
+
 // Makes `stream` wait for the work the client had queued before this request.
 void ProxyEngine::order_after_client(RankState& rs, const CollOp& op, void* stream) {
   Backend* be = daemon_->backend();
-  if (rs.sync_alloc.va && op.sync_slot) {
-    const uint64_t addr = rs.sync_alloc.va + 8 * (proto::kSyncFirstStreamSlot + (op.sync_slot - 1) % proto::kSyncMaxStreams);
-    be->stream_wait_value64(rs.device, stream, addr, op.sync_value);
+  if (rs.sync.host && op.sync_slot) {
+    // nothing to queue: clients_ready() has seen the "submitted" value already
   } else if (op.user_event) {
     be->stream_wait_event(rs.device, stream, op.user_event);
   }
@@ -420,10 +444,10 @@ void ProxyEngine::order_after_client(RankState& rs, const CollOp& op, void* stre
 // A request that ends without a launch must still release the client's stream, which
 // (in mem-op mode) already waits for this request's "done" value.
 void ProxyEngine::signal_done(RankState& rs, uint64_t user_seq) {
-  if (!rs.sync_alloc.va) return;
+  if (!rs.sync.host) return;
   Communicator& c = *rs.comm;
   void* stream = c.group_stream ? c.group_stream : rs.stream;
-  daemon_->backend()->stream_write_value64(rs.device, stream, rs.sync_alloc.va + 8 * proto::kSyncDoneSlot, user_seq);
+  daemon_->backend()->stream_write_value64(rs.device, stream, rs.sync.dev_addr + 8 * proto::kSyncDoneSlot, user_seq);
 }
 
 // Emulated communicators (all ranks on one GPU) and the host backend run every rank
@@ -452,8 +476,8 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
   }
   for (int r = 0; r < c.nranks; r++) {
     RankState& rr = *c.ranks[(size_t)r];
-    if (rr.sync_alloc.va && s.ops[r].sync_slot)
-      be->stream_write_value64(rr.device, c.group_stream, rr.sync_alloc.va + 8 * proto::kSyncDoneSlot, s.ops[r].user_seq);
+    if (rr.sync.host && s.ops[r].sync_slot)
+      be->stream_write_value64(rr.device, c.group_stream, rr.sync.dev_addr + 8 * proto::kSyncDoneSlot, s.ops[r].user_seq);
     else
       be->event_record(rr.device, rr.backend_event, c.group_stream);
   }
@@ -465,11 +489,22 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
 // (6): completion
 // ---------------------------------------------------------------------------
 bool ProxyEngine::complete_request(RankState& rs, CollSlot& s, uint64_t seq, int status) {
+  const CollOp& op = s.ops[rs.rank];
+  if (op.sync_slot && rs.dp_status) {
+    // Mem-op request: counted, not answered (see proto::DpStatus).
+    proto::DpStatus* d = rs.dp_status;
+    if (status != proto::kOk && d->first_error == 0) d->first_error = status;
+    d->last_variant = (uint32_t)s.plan.variant;
+    d->last_ctas = (uint32_t)s.plan.dims.ctas;
+    std::atomic_thread_fence(std::memory_order_release);
+    __atomic_store_n(&d->completed, d->completed + 1, __ATOMIC_RELEASE);
+    return true;
+  }
   proto::WorkCompletion wc;
   memset(&wc, 0, sizeof wc);
-  wc.kind = (uint32_t)s.ops[rs.rank].kind;
+  wc.kind = (uint32_t)op.kind;
   wc.status = status;
-  wc.user_seq = s.ops[rs.rank].user_seq;
+  wc.user_seq = op.user_seq;
   wc.variant = (uint32_t)s.plan.variant;
   wc.ctas = (uint32_t)s.plan.dims.ctas;
   wc.comm_seq = seq;
@@ -536,6 +571,7 @@ bool ProxyEngine::advance(RankState& rs) {
     if (st == kSlotPlanned) {
       RankState& gate = group ? *c.ranks[0] : rs;
       if (gate.status && gate.last_ticket > *(volatile uint64_t*)&gate.status->done_seq + kMaxGpuQueue) break;
+      if (rs.next_slice == 0 && !(group && s.group_launch.load(std::memory_order_acquire) == 2) && !clients_ready(c, s, group ? -1 : rs.rank)) break;
     }
     int status = proto::kOk;
     if (st == kSlotFailed) {

@@ -43,6 +43,16 @@ struct McRegion {
   uint64_t bound[kMaxRanks] = {0};  // allocation handle bound per rank (for unbinding)
 };
 
+// A small page of 64-bit semaphores that the daemon (CPU and GPU), the client's CPU
+// and the client's GPU streams can all address: shared host memory (memfd), registered
+// with CUDA on both sides so that stream memory operations can target it.
+struct SyncPage {
+  int fd = -1;
+  void* host = nullptr;      // CPU address in the daemon
+  uint64_t dev_addr = 0;     // address for stream memory operations issued by the daemon
+  size_t bytes = 0;
+};
+
 struct BackendOptions {
   int host_devices = 8;        // device count the host backend pretends to have
   bool allow_vmm = true;
@@ -94,6 +104,8 @@ class Backend {
   virtual int stream_wait_value64(int dev, void* stream, uint64_t addr, uint64_t value) = 0;   // waits *addr >= value
   virtual int stream_write_value64(int dev, void* stream, uint64_t addr, uint64_t value) = 0;
   virtual int zero_memory(int dev, uint64_t addr, size_t bytes) = 0;
+  virtual int sync_page_create(int dev, SyncPage* out) = 0;
+  virtual int sync_page_destroy(int dev, SyncPage* p) = 0;
 
   virtual int mc_create(const std::vector<const Allocation*>& per_rank, McRegion* out) = 0;
   virtual int mc_destroy(McRegion* r) = 0;

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "../common/log.h"
+#include "../ipc/uds.h"
 #include "../kernels/launch.h"
 #include "backend.h"
 
@@ -377,6 +378,43 @@ class CudaBackend : public Backend {
     RT_CHECK(cudaSetDevice(dev), proto::kErrDevice);
     RT_CHECK(cudaMemset((void*)addr, 0, bytes), proto::kErrDevice);
     RT_CHECK(cudaDeviceSynchronize(), proto::kErrDevice);
+    return proto::kOk;
+  }
+
+  int sync_page_create(int dev, SyncPage* out) override {
+    DeviceGuard guard;
+    RT_CHECK(cudaSetDevice(dev), proto::kErrDevice);
+    const size_t bytes = 4096;
+    int fd = ipc::memfd_make("mccs-sync", bytes);
+    if (fd < 0) return proto::kErrOutOfMemory;
+    void* p = ipc::map_shared(fd, bytes);
+    if (!p) { close(fd); return proto::kErrOutOfMemory; }
+    memset(p, 0, bytes);
+    cudaError_t e = cudaHostRegister(p, bytes, cudaHostRegisterPortable | cudaHostRegisterMapped);
+    void* d = nullptr;
+    if (e == cudaSuccess) e = cudaHostGetDevicePointer(&d, p, 0);
+    if (e != cudaSuccess) {
+      LOG_ERROR("registering the semaphore page failed: %s", cudaGetErrorString(e));
+      cudaGetLastError();
+      ipc::unmap_shared(p, bytes);
+      close(fd);
+      return proto::kErrDevice;
+    }
+    out->fd = fd;
+    out->host = p;
+    out->dev_addr = (uint64_t)d;
+    out->bytes = bytes;
+    return proto::kOk;
+  }
+  int sync_page_destroy(int dev, SyncPage* p) override {
+    if (!p->host) return proto::kOk;
+    DeviceGuard guard;
+    cudaSetDevice(dev);
+    cudaHostUnregister(p->host);
+    cudaGetLastError();
+    ipc::unmap_shared(p->host, p->bytes);
+    if (p->fd >= 0) close(p->fd);
+    *p = SyncPage();
     return proto::kOk;
   }
 

@@ -212,6 +212,8 @@ class HostBackend : public Backend {
   int stream_wait_value64(int, void*, uint64_t, uint64_t) override { return proto::kOk; }
   int stream_write_value64(int, void*, uint64_t, uint64_t) override { return proto::kOk; }
   int zero_memory(int, uint64_t addr, size_t bytes) override { memset((void*)addr, 0, bytes); return proto::kOk; }
+  int sync_page_create(int, SyncPage*) override { return proto::kErrUnsupported; }
+  int sync_page_destroy(int, SyncPage*) override { return proto::kOk; }
   int mc_create(const std::vector<const Allocation*>&, McRegion*) override { return proto::kErrUnsupported; }
   int mc_destroy(McRegion*) override { return proto::kOk; }
 

@@ -70,6 +70,9 @@ struct Driver {
   DRV_FN(cuGetErrorString);
   DRV_FN(cuStreamWaitValue64);
   DRV_FN(cuStreamWriteValue64);
+  DRV_FN(cuMemHostRegister);
+  DRV_FN(cuMemHostUnregister);
+  DRV_FN(cuMemHostGetDevicePointer);
   bool memops = false;
 };
 Driver g_drv;
@@ -104,7 +107,10 @@ bool load_driver() {
              sym(l, "cuMemUnmap", &g_drv.cuMemUnmap_) && sym(l, "cuMemSetAccess", &g_drv.cuMemSetAccess_) &&
              sym(l, "cuMemRelease", &g_drv.cuMemRelease_) && sym(l, "cuGetErrorString", &g_drv.cuGetErrorString_);
   g_drv.memops = sym(l, "cuStreamWaitValue64_v2", &g_drv.cuStreamWaitValue64_) &&
-                 sym(l, "cuStreamWriteValue64_v2", &g_drv.cuStreamWriteValue64_);
+                 sym(l, "cuStreamWriteValue64_v2", &g_drv.cuStreamWriteValue64_) &&
+                 sym(l, "cuMemHostRegister_v2", &g_drv.cuMemHostRegister_) &&
+                 sym(l, "cuMemHostUnregister", &g_drv.cuMemHostUnregister_) &&
+                 sym(l, "cuMemHostGetDevicePointer_v2", &g_drv.cuMemHostGetDevicePointer_);
   if (g_drv.ok && g_drv.cuInit_(0) != CUDA_SUCCESS) g_drv.ok = false;
   return g_drv.ok;
 }
@@ -198,6 +204,8 @@ struct mccsComm {
   void* dp_mem = nullptr;
   size_t dp_bytes = 0;
   ipc::Ring wq, cq;
+  proto::DpStatus* dp_status = nullptr;
+  uint64_t memop_posted = 0;     // mem-op requests posted (their completions are counted, not queued)
   CUevent backend_event = nullptr;
   bool event_owned = false;
   uint64_t next_user_seq = 1;
@@ -206,8 +214,10 @@ struct mccsComm {
   int sticky_error = 0;
   pthread_t owner = pthread_self();   // the thread that created (and uses) the communicator
   // mem-op synchronisation (proto::kSyncMemOps): semaphore page shared with the daemon
-  MemRec sync_rec;
-  uint64_t sync_base = 0;
+  // (host memory mapped here and registered for device access)
+  void* sync_host = nullptr;
+  size_t sync_bytes = 0;
+  uint64_t sync_base = 0;     // device address of the page for stream memory operations
   std::map<uint64_t, uint32_t> stream_slot;            // stream handle -> semaphore index
   uint64_t slot_value[proto::kSyncMaxStreams] = {0};   // last value written per semaphore
 };
@@ -480,6 +490,14 @@ mccsResult_t finish_on_stream(mccsComm* comm, mccsStream_t stream) {
 
 // Takes whatever completions have arrived, without waiting.
 void reap_completions(mccsComm* comm) {
+  if (comm->dp_status && comm->memop_posted) {
+    const uint64_t done = __atomic_load_n(&comm->dp_status->completed, __ATOMIC_ACQUIRE);
+    if (done) {
+      comm->last_variant = comm->dp_status->last_variant;
+      comm->last_ctas = comm->dp_status->last_ctas;
+    }
+    if (comm->dp_status->first_error != 0 && comm->sticky_error == 0) comm->sticky_error = comm->dp_status->first_error;
+  }
   proto::WorkCompletion wc;
   while (comm->outstanding > 0 && comm->cq.try_pop(&wc)) {
     comm->outstanding--;
@@ -530,7 +548,7 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
       if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
     }
   }
-  comm->outstanding++;
+  comm->memop_posted++;
   r = g_drv.cuStreamWaitValue64_((CUstream)stream, (CUdeviceptr)(comm->sync_base + 8 * proto::kSyncDoneSlot), wr.user_seq,
                                  CU_STREAM_WAIT_VALUE_GEQ);
   if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitValue64: %s", cu_err(r)); return mccsDeviceError; }
@@ -713,7 +731,7 @@ mccsResult_t mccsFree(void* ptr) {
     // that thread's to read.
     if (g_ctx.connected)
       for (mccsComm* c : comms)
-        if (pthread_equal(c->owner, pthread_self()) && c->outstanding) mccsCommFlush(c);
+        if (pthread_equal(c->owner, pthread_self()) && (c->outstanding || c->memop_posted)) mccsCommFlush(c);
   }
   std::unique_lock<std::mutex> g(g_ctx.mu);
   auto it = g_ctx.mem.find((uint64_t)ptr);
@@ -768,17 +786,28 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
   c->dp_bytes = m.comm_init_reply.dp_bytes;
   c->dp_mem = mmap(nullptr, c->dp_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
   if (c->dp_mem == MAP_FAILED) { for (int f : fds) close(f); delete c; return mccsOutOfMemory; }
-  const size_t wq_bytes = (ipc::Ring::bytes_needed(proto::kWqDepth, proto::kWrBytes) + 63) / 64 * 64;
+  const size_t wq_bytes = proto::dp_wq_bytes();
   c->wq.attach(c->dp_mem);
   c->cq.attach((char*)c->dp_mem + wq_bytes);
-  if (g_ctx.backend == proto::kBackendCuda && m.comm_init_reply.sync_size && g_drv.memops) {
-    c->sync_rec.size = m.comm_init_reply.sync_size;
-    c->sync_rec.device = device;
-    c->sync_rec.share_kind = m.comm_init_reply.sync_share_kind;
-    mccsResult_t mr = map_allocation(c->sync_rec, fds.size() > 1 ? fds[1] : -1, m.comm_init_reply.sync_ipc_handle,
-                                     m.comm_init_reply.sync_daemon_va);
-    if (mr == mccsSuccess) c->sync_base = c->sync_rec.base;
-    else LOG_WARN("cannot map the semaphore page (%s); falling back to event synchronisation", mccsGetErrorString(mr));
+  if (c->dp_bytes >= proto::dp_segment_bytes())
+    c->dp_status = (proto::DpStatus*)((char*)c->dp_mem + wq_bytes + proto::dp_cq_bytes());
+  if (g_ctx.backend == proto::kBackendCuda && m.comm_init_reply.sync_size && g_drv.memops && fds.size() > 1) {
+    CtxScope scope(device);
+    const size_t bytes = m.comm_init_reply.sync_size;
+    void* p = scope.ok ? mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[1], 0) : MAP_FAILED;
+    if (p != MAP_FAILED) {
+      CUdeviceptr d = 0;
+      CUresult cr = g_drv.cuMemHostRegister_(p, bytes, CU_MEMHOSTREGISTER_PORTABLE | CU_MEMHOSTREGISTER_DEVICEMAP);
+      if (cr == CUDA_SUCCESS) cr = g_drv.cuMemHostGetDevicePointer_(&d, p, 0);
+      if (cr == CUDA_SUCCESS) {
+        c->sync_host = p;
+        c->sync_bytes = bytes;
+        c->sync_base = (uint64_t)d;
+      } else {
+        LOG_WARN("cannot register the semaphore page (%s); falling back to event synchronisation", cu_err(cr));
+        munmap(p, bytes);
+      }
+    }
   }
   for (int f : fds) close(f);
   fds.clear();
@@ -812,6 +841,23 @@ mccsResult_t mccsCommFlush(mccsComm_t comm) {
     mccsResult_t r = wait_completion(comm, &wc);
     if (r == mccsTimeout || r == mccsNotConnected) return r;
   }
+  if (comm->dp_status && comm->memop_posted) {
+    struct timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    uint64_t spins = 0;
+    while (__atomic_load_n(&comm->dp_status->completed, __ATOMIC_ACQUIRE) < comm->memop_posted) {
+      if ((++spins & 0xfff) == 0) {
+        struct timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        uint64_t ms = (uint64_t)(t1.tv_sec - t0.tv_sec) * 1000 + (uint64_t)((t1.tv_nsec - t0.tv_nsec) / 1000000);
+        if (ms > g_ctx.wc_timeout_ms) return mccsTimeout;
+        struct pollfd pf = {g_ctx.fd, 0, 0};
+        if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+        if (spins > (1u << 20)) usleep(50);
+      }
+    }
+    reap_completions(comm);
+  }
   return (mccsResult_t)comm->sticky_error;
 }
 
@@ -834,7 +880,11 @@ mccsResult_t mccsCommDestroy(mccsComm_t comm) {
   for (size_t i = 0; i < g_ctx.comms.size(); i++)
     if (g_ctx.comms[i] == comm) { g_ctx.comms.erase(g_ctx.comms.begin() + (long)i); break; }
   if (comm->dp_mem) munmap(comm->dp_mem, comm->dp_bytes);
-  if (comm->sync_base) unmap_allocation(comm->sync_rec);
+  if (comm->sync_host) {
+    CtxScope scope(comm->device);
+    if (scope.ok) g_drv.cuMemHostUnregister_(comm->sync_host);
+    munmap(comm->sync_host, comm->sync_bytes);
+  }
   delete comm;
   return r;
 }

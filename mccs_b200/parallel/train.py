@@ -71,8 +71,13 @@ def main() -> int:
     if args.backend == "mccs":
         import mccs_b200 as M
         prefix = args.control or f"/tmp/mccs-train-{os.getuid()}-{os.environ.get('MASTER_PORT', '0')}"
+        spawned = None
         if args.start_daemon and local_rank == 0:
-            M.daemon.start_embedded(prefix=prefix, listen_port=-1)
+            # a stand-alone daemon: every rank is an outside client, nobody blocks on the host
+            os.makedirs(prefix, exist_ok=True)
+            with open(prefix + "/mccs.toml", "w") as f:
+                f.write(M.daemon.default_config(prefix, listen_port=-1))
+            spawned = M.daemon.spawn(prefix + "/mccs.toml")
         barrier()
         if args.start_daemon or args.control:
             M.init(prefix + "/control.sock" if not prefix.endswith(".sock") else prefix)
@@ -153,8 +158,8 @@ def main() -> int:
         comm.destroy()
         M.finalize()
         barrier()
-        if args.start_daemon and local_rank == 0:
-            M.daemon.stop_embedded()
+        if spawned is not None:
+            spawned.stop()
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -62,7 +62,7 @@ def worker(a) -> int:
         def one_iteration():
             with M.group():
                 for t in ts:
-                    comm.all_reduce(t)
+                    comm.all_reduce(t, op="avg")     # averages keep the values bounded over thousands of rounds
     else:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(a.group_port)
@@ -72,7 +72,7 @@ def worker(a) -> int:
 
         def one_iteration():
             for t in ts:
-                dist.all_reduce(t)
+                dist.all_reduce(t, op=dist.ReduceOp.AVG)
     g = torch.Generator().manual_seed(a.rank)
     for t in ts:
         t.copy_(torch.rand(count, generator=g) * 2 - 1)

@@ -59,6 +59,7 @@ def main() -> int:
     ap.add_argument("--out", default="sweep.csv")
     ap.add_argument("--tuning", default="")
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--auto-only", action="store_true", help="final mode: measure only the service's own choice (and NCCL)")
     ap.add_argument("--in-place", action="store_true")
     ap.add_argument("--sync", default="auto", choices=["auto", "memops", "events"])
     ap.add_argument("--daemon", default="standalone", choices=["standalone", "embedded"],
@@ -162,7 +163,7 @@ def main() -> int:
         if args.algos:
             algos = [a for a in algos if a in args.algos.split(",")]
         if args.mode == "final":
-            algos = ["auto"] + algos
+            algos = ["auto"] + ([] if args.auto_only else algos)
         if n == 1:
             algos = ["auto"]
         for dname in (args.dtypes.split(",") if is_ar else ["bytes"]):
