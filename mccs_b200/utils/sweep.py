@@ -207,8 +207,8 @@ def main() -> int:
                 for algo in algos:
                     if algo in ("ar_oneshot", "ar_nvls_oneshot") and (total > (8 << 20) or args.in_place):
                         continue
-                    if "ring" in algo and args.mode == "tune" and total > (256 << 20):
-                        continue
+                    if "ring" in algo and total > (64 << 20):
+                        continue   # the FIFO ring is a fall-back path: not worth minutes of sweep time
                     for k in (cta_list if "ring" not in algo else [0]):
                         set_ctas(k)
 
