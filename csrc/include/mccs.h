@@ -120,6 +120,14 @@ mccsResult_t mccsAllGather(mccsComm_t comm, const void* send, void* recv, size_t
 mccsResult_t mccsAllGatherEx(mccsComm_t comm, const void* send, void* recv, size_t bytes,
                              mccsAlgo_t algo, mccsStream_t stream);
 
+/* Deferred waiting. By default every collective call also makes the caller's stream wait
+ * for the collective (stream order, like a kernel launch). A caller that issues many
+ * collectives from a side stream and only needs the results later (gradient buckets
+ * during backward) can switch that off for a communicator and place one wait itself:
+ * mccsCommWait makes `stream` wait for every collective submitted on `comm` so far. */
+mccsResult_t mccsCommSetDeferredWait(mccsComm_t comm, int on);
+mccsResult_t mccsCommWait(mccsComm_t comm, mccsStream_t stream);
+
 /* Calls between GroupStart and GroupEnd are submitted back to back and completed
  * together at GroupEnd (the protocol's GroupCall, src/ipc/mccs/src/command.rs:93-95). */
 mccsResult_t mccsGroupStart(void);

@@ -212,6 +212,8 @@ struct mccsComm {
   uint64_t outstanding = 0;      // requests posted whose completion was not read yet
   uint32_t last_variant = 0, last_ctas = 0;
   int sticky_error = 0;
+  bool deferred_wait = false;         // collectives do not queue "wait done"; mccsCommWait does
+  uint64_t last_posted_seq = 0;       // user_seq of the newest request posted
   pthread_t owner = pthread_self();   // the thread that created (and uses) the communicator
   // mem-op synchronisation (proto::kSyncMemOps): semaphore page shared with the daemon
   // (host memory mapped here and registered for device access)
@@ -549,6 +551,8 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
     }
   }
   comm->memop_posted++;
+  comm->last_posted_seq = wr.user_seq;
+  if (comm->deferred_wait) return mccsSuccess;
   r = g_drv.cuStreamWaitValue64_((CUstream)stream, (CUdeviceptr)(comm->sync_base + 8 * proto::kSyncDoneSlot), wr.user_seq,
                                  CU_STREAM_WAIT_VALUE_GEQ);
   if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitValue64: %s", cu_err(r)); return mccsDeviceError; }
@@ -608,6 +612,7 @@ mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, vo
     if (one != mccsSuccess) r = one;
   }
   if (r != mccsSuccess) return r;
+  if (comm->deferred_wait) return mccsSuccess;
   return finish_on_stream(comm, stream);
 }
 
@@ -937,6 +942,28 @@ mccsResult_t mccsAllGatherEx(mccsComm_t comm, const void* send, void* recv, size
 
 mccsResult_t mccsAllGather(mccsComm_t comm, const void* send, void* recv, size_t bytes, mccsStream_t stream) {
   return mccsAllGatherEx(comm, send, recv, bytes, mccsAlgoAuto, stream);
+}
+
+mccsResult_t mccsCommSetDeferredWait(mccsComm_t comm, int on) {
+  if (!comm) return mccsInvalidArgument;
+  comm->deferred_wait = on != 0;
+  return mccsSuccess;
+}
+
+mccsResult_t mccsCommWait(mccsComm_t comm, mccsStream_t stream) {
+  if (!comm) return mccsInvalidArgument;
+  if (g_ctx.backend != proto::kBackendCuda) return mccsSuccess;
+  if (comm->sync_base) {
+    if (!comm->last_posted_seq) return mccsSuccess;
+    CtxScope scope(comm->device);
+    if (!scope.ok) return mccsDeviceError;
+    // "done" only grows and is written in submission order: the newest value covers all.
+    CUresult r = g_drv.cuStreamWaitValue64_((CUstream)stream, (CUdeviceptr)(comm->sync_base + 8 * proto::kSyncDoneSlot),
+                                            comm->last_posted_seq, CU_STREAM_WAIT_VALUE_GEQ);
+    if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitValue64: %s", cu_err(r)); return mccsDeviceError; }
+    return mccsSuccess;
+  }
+  return finish_on_stream(comm, stream);
 }
 
 mccsResult_t mccsGroupStart(void) { g_group_depth++; return mccsSuccess; }

@@ -73,6 +73,10 @@ def shim() -> ctypes.CDLL:
     lib.mccsGroupEnd.restype = c_int
     lib.mccsCommQuery.argtypes = [c_void_p, POINTER(CommInfo)]
     lib.mccsCommQuery.restype = c_int
+    lib.mccsCommSetDeferredWait.argtypes = [c_void_p, c_int]
+    lib.mccsCommSetDeferredWait.restype = c_int
+    lib.mccsCommWait.argtypes = [c_void_p, c_void_p]
+    lib.mccsCommWait.restype = c_int
     lib.mccsCommFlush.argtypes = [c_void_p]
     lib.mccsCommFlush.restype = c_int
     lib.mccsCommLastPlan.argtypes = [c_void_p, POINTER(c_uint32), POINTER(c_uint32)]

@@ -174,6 +174,16 @@ class Communicator:
         check(_lib.shim().mccsAllGatherEx(self._h, c_void_p(_ptr(send)), c_void_p(_ptr(recv)), int(nbytes),
                                           ALGOS[algo], c_void_p(self._stream(stream))), "mccsAllGather")
 
+    def set_deferred_wait(self, on: bool) -> None:
+        """With deferred waiting a collective call does not make the caller's stream wait
+        for it; :meth:`wait` places that wait where the results are needed."""
+        check(_lib.shim().mccsCommSetDeferredWait(self._h, 1 if on else 0), "mccsCommSetDeferredWait")
+
+    def wait(self, stream=None) -> None:
+        """Make ``stream`` (default: the current stream) wait for every collective
+        submitted on this communicator so far."""
+        check(_lib.shim().mccsCommWait(self._h, c_void_p(self._stream(stream))), "mccsCommWait")
+
     def flush(self) -> None:
         """Wait until the daemon has launched everything posted so far; raise the first
         error a request reported (collective calls may return before the daemon has

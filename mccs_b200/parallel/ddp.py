@@ -75,6 +75,9 @@ class DataParallel:
         if cur:
             self.buckets.append(_Bucket(cur, cur_dtype, self._device, self._cuda))
         self._launched = 0
+        # Bucket reductions are issued from a side stream and only their sum total is
+        # awaited, once, at the end of backward: no per-bucket wait is queued anywhere.
+        self.comm.set_deferred_wait(True)
         for b in self.buckets:
             for p, off in zip(b.params, b.offsets):
                 # same strides as the parameter (channels-last weights keep that layout)
@@ -125,8 +128,8 @@ class DataParallel:
                 # forward pass): reduce it now so that all ranks issue the same collectives.
                 self._reduce(b)
             b.pending = len(b.params)
-        if self._cuda:
-            torch.cuda.current_stream(self._device).wait_stream(self._stream)
+        if self.comm.nranks > 1:
+            self.comm.wait()          # the compute stream waits for all bucket reductions of this step
         self._launched = 0
 
     def zero_grad(self) -> None:
@@ -141,6 +144,7 @@ class DataParallel:
         return sum(b.numel * b.flat.element_size() for b in self.buckets)
 
     def release(self) -> None:
+        self.comm.set_deferred_wait(False)
         for b in self.buckets:
             for p in b.params:
                 p.grad = None

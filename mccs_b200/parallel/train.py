@@ -20,6 +20,10 @@ import os
 import sys
 import time
 
+# One hardware queue per CUDA stream where possible, so that a stream that waits for a
+# collective cannot hold up the compute stream (must be set before CUDA initialises).
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 import torch
 import torch.distributed as dist
 
