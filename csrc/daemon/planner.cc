@@ -49,17 +49,25 @@ void Planner::load_defaults(bool nvls) {
       ag.entries = ar.entries;
       continue;
     }
-    if (nvls) {
-      ar.entries = {{64 * KB, kArNvlsOne, 4, 512},   {512 * KB, kArNvlsTwo, 8, 512},
-                    {4 * MB, kArNvlsTwo, 16, 512},   {32 * MB, kArNvlsTwo, 32, 512},
-                    {kInf, kArNvlsTwo, 64, 512}};
-      ag.entries = {{256 * KB, kAgPull, 8, 512},     {4 * MB, kAgPush, 16, 512},
-                    {64 * MB, kAgNvls, 32, 512},     {kInf, kAgNvls, 64, 512}};
+    // Rows measured on B200: eight ranks behind an NVSwitch for n >= 4, two ranks for
+    // n <= 3, where the in-switch reduction moves no fewer bytes than a direct exchange
+    // and measured slower. A tuning file replaces them per rank count.
+    if (n <= 3) {
+      ar.entries = {{2 * MB, kArOneShot, 32, 512},   {32 * MB, kArTwoShot, 64, 512},
+                    {kInf, kArTwoShot, 128, 512}};
+      ag.entries = {{128 * KB, kAgPull, 8, 512},     {2 * MB, kAgPush, 16, 512},
+                    {64 * MB, kAgPush, 64, 512},     {kInf, kAgPush, 128, 512}};
+    } else if (nvls) {
+      ar.entries = {{256 * KB, kArNvlsOne, 4, 512},  {32 * MB, kArNvlsTwo, 8, 512},
+                    {kInf, kArNvlsTwo, 16, 512}};
+      ag.entries = {{128 * KB, kAgNvls, 2, 512},     {2 * MB, kAgPull, 32, 512},
+                    {16 * MB, kAgPull, 64, 512},     {64 * MB, kAgPush, 32, 512},
+                    {kInf, kAgPush, 128, 512}};
     } else {
-      ar.entries = {{128 * KB, kArOneShot, 8, 512},  {1 * MB, kArTwoShot, 16, 512},
-                    {16 * MB, kArTwoShot, 32, 512},  {kInf, kArTwoShot, 64, 512}};
-      ag.entries = {{256 * KB, kAgPull, 8, 512},     {8 * MB, kAgPush, 16, 512},
-                    {kInf, kAgPush, 64, 512}};
+      ar.entries = {{128 * KB, kArOneShot, 8, 512},  {4 * MB, kArTwoShot, 16, 512},
+                    {64 * MB, kArTwoShot, 32, 512},  {kInf, kArTwoShot, 64, 512}};
+      ag.entries = {{2 * MB, kAgPull, 32, 512},      {16 * MB, kAgPull, 64, 512},
+                    {64 * MB, kAgPush, 32, 512},     {kInf, kAgPush, 128, 512}};
     }
   }
 }

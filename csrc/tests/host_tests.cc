@@ -211,7 +211,7 @@ static void test_planner() {
   CHECK(p.plan(in).variant == kLocalCopy);
   // all-gather
   PlanInput g;
-  g.kind = kAllGather; g.nranks = 4; g.count = 64 << 20; g.nvls_possible = true;
+  g.kind = kAllGather; g.nranks = 4; g.count = 16 << 10; g.nvls_possible = true;
   CHECK(p.plan(g).variant == kAgNvls);
   g.aligned16 = false;
   CHECK(p.plan(g).variant != kAgNvls);

@@ -333,3 +333,23 @@ def test_example_apps_end_to_end(private_daemon, tmp_path):
     assert "no communicator 600" in r.stdout          # reached the daemon, which rejected the unknown id
     r = run([os.path.join(NATIVE, "ring_config"), "--stats", "--port", str(private_daemon.admin_port)])
     assert r.returncode == 0 and json.loads(r.stdout.split(": ", 1)[1])["status"] == "ok"
+
+
+def test_committed_tuning_table_is_accepted(service):
+    """The measured size -> (variant, CTAs) table that ships with the package loads into
+    the planner unchanged (every variant name known, every launch shape in range)."""
+    import json
+    M = service
+    port = M.daemon.embedded_admin_port()
+    with open(M.daemon.TUNING_FILE) as f:
+        shipped = json.load(f)
+    before = M.admin_request(port, {"cmd": "tuning_get"})["tuning"]
+    try:
+        assert M.admin_request(port, {"cmd": "tuning_set", "tuning": shipped})["status"] == "ok"
+        after = M.admin_request(port, {"cmd": "tuning_get"})["tuning"]
+        for kind in ("allreduce", "allgather"):
+            for n, rows in shipped[kind].items():
+                assert [r[1:3] for r in after[kind][n]] == [r[1:3] for r in rows]
+                assert after[kind][n][-1][0] == -1
+    finally:
+        M.admin_request(port, {"cmd": "tuning_set", "tuning": before})
