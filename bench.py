@@ -32,7 +32,7 @@ import time
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
-BASELINE_ALGBW_GBPS = 5.99   # MCCS, AllReduce fp16 512 MiB, 8 GPUs
+BASELINE_ALGBW_GBPS = 5.99   # MCCS, AllReduce fp16 512 MiB, 8 GPUs, as published by the reference (RTX 3090 testbed)
 
 
 def parse_args():

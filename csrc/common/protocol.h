@@ -57,10 +57,12 @@ enum Backend : uint32_t { kBackendHost = 0, kBackendCuda = 1 };
 //    (src/libmccs/src/collectives.rs:23-25,68-70): the caller records "submitted",
 //    waits for the daemon's completion message, then makes its stream wait for the
 //    daemon's "done" event. One blocking round trip per collective.
-//  kSyncMemOps: two 64-bit semaphores in device memory shared by caller and daemon,
-//    driven by stream memory operations. The caller enqueues "write submitted" and
-//    "wait done" on its stream and returns at once; the daemon enqueues "wait
-//    submitted", the kernel and "write done" on its stream. No round trip.
+//  kSyncMemOps: 64-bit semaphores in a pinned host page shared by caller and daemon.
+//    The caller enqueues "write submitted" and "wait done" on its stream (stream memory
+//    operations) and returns at once; the daemon's proxy polls the "submitted" words
+//    from the CPU, launches the kernel once every rank's caller has got there, and
+//    enqueues "write done" behind it. No round trip, no blocking wait on the daemon's
+//    streams.
 enum SyncMode : uint32_t { kSyncEvents = 0, kSyncMemOps = 1 };
 constexpr uint32_t kSyncDoneSlot = 0;        // u64 index of the "done" semaphore in the sync page
 constexpr uint32_t kSyncFirstStreamSlot = 8; // first "submitted" semaphore

@@ -9,7 +9,8 @@
  * by the daemon ([b200] sync in its configuration):
  *   - stream memory operations (default on GPUs that support them): the library
  *     queues "write submitted" and "wait done" on the caller's stream, on two 64-bit
- *     semaphores in device memory it shares with the daemon, and returns at once;
+ *     semaphores in a pinned host page it shares with the daemon, and returns at
+ *     once; the daemon polls "submitted" and launches when every rank got there;
  *     errors of a request show up on a later call or in mccsCommFlush. One stream may
  *     carry only one rank of a given communicator.
  *   - interprocess events (the reference's scheme): the library records "submitted",

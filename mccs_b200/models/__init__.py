@@ -1,5 +1,5 @@
-"""Model zoo of the data-parallel training drivers: the three networks the build's
-training configurations name. ResNet-50 and VGG-16 come from torchvision (random
+"""Model zoo of the data-parallel training drivers: ResNet-50, VGG-16 (the networks of the
+reference's workload traces) and GPT-2-medium. ResNet-50 and VGG-16 come from torchvision (random
 init, no weights are downloaded); GPT-2-medium is defined here."""
 from __future__ import annotations
 

@@ -5,7 +5,7 @@ The reference evaluates "real workloads" as traces of one monolithic AllReduce p
 iteration with a sleep for the compute phase and a stream synchronise after every
 operation (``workloads/setup-4_vgg.toml``, ``src/mccs_examples/traffic_gen/src/main.rs:171-204``).
 This module runs the real thing: gradients live in flat buckets of ``bucket_mb`` MB
-(25 MB as in the build's training configurations) that are allocated in service
+(25 MB, torch DDP's default) that are allocated in service
 memory, each parameter's ``.grad`` is a view into its bucket, and as soon as the last
 gradient of a bucket has been accumulated the bucket is all-reduced in place on a
 side stream while backward continues on the compute stream. The averaging is fused

@@ -2,7 +2,7 @@
 batches of back-to-back AllReduces, under QoS weights, with a live reconfiguration in
 the middle of the run.
 
-Default scenario (the build's third configuration; the reference's counterpart is
+Default scenario (the reference's counterpart is
 ``eval/multi-app`` settings 1-4 plus ``eval/dynamic-config``): four applications —
 A and B on two GPUs each, C and D on four GPUs each, overlapping A's and B's GPUs —
 each iteration = 16 back-to-back fp32 AllReduces of 8 MB, weights 2:1:1:1, and at
@@ -142,9 +142,8 @@ def orchestrate(a) -> int:
     if a.backend == "mccs":
         import mccs_b200 as M
         tenants = "\n".join(f"[qos.tenants.{x['comm_id']}]\nweight = {x['weight']}" for x in apps)
-        extra = "" if a.no_qos else ""
         prefix = f"/tmp/mccs-mt-{os.getuid()}-{os.getpid()}"
-        cfg = M.daemon.default_config(prefix, listen_port=-1, host_devices=8, sync=a.sync, extra=extra) + ("" if a.no_qos else tenants + "\n")
+        cfg = M.daemon.default_config(prefix, listen_port=-1, host_devices=8, sync=a.sync) + ("" if a.no_qos else tenants + "\n")
         M.daemon.start_embedded(cfg)
         admin_port = M.daemon.embedded_admin_port()
         env["MCCS_CONTROL"] = prefix + "/control.sock"

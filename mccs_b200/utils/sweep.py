@@ -7,8 +7,8 @@ with the same timing (CUDA events on the launching stream, max over ranks).
 
 It is the counterpart of the reference's single-app evaluation
 (``eval/single-app/gen_config.py:141-147`` sizes, ``collect.py`` CSV) and of its NCCL
-baseline runs (``nccl-tests-mccs/microbenchmark/run_nccl_once.sh``), with the protocol
-of the build's second configuration: sizes 32 KiB to 1 GiB in powers of two, 20 warm-up
+baseline runs (``nccl-tests-mccs/microbenchmark/run_nccl_once.sh``), with the
+nccl-tests protocol: sizes 32 KiB to 1 GiB in powers of two, 20 warm-up
 and 100 timed iterations for the final numbers (``--mode final``), fewer for the tuning
 pass (``--mode tune``) whose result is a tuning table the daemon loads
 (``[b200] tuning_file``).
