@@ -5,6 +5,7 @@
 // listed. Entries may also carry `allreduce_algo`, `allgather_algo` and `ctas`.
 //   ring_config --config patch.toml [--port P] [--addr A]
 //   ring_config --stats [--port P]            (prints the daemon's statistics)
+//   ring_config --hwinfo [--port P]           (devices, CPU affinity, peer access, NVLS)
 #include <stdio.h>
 #include <stdlib.h>
 
@@ -15,16 +16,16 @@
 #include "app_common.h"
 
 int main(int argc, char** argv) {
-  app::Options o(argc, argv, {"stats"});
+  app::Options o(argc, argv, {"stats", "hwinfo"});
   std::vector<std::string> addrs;
   int port = (int)o.num("port", 5000);
   mccs::Value body = mccs::Value::object();
   int type = 1;
-  if (o.flag("stats")) {
-    body.set("cmd", "stats");
+  if (o.flag("stats") || o.flag("hwinfo")) {
+    body.set("cmd", o.flag("stats") ? "stats" : "hwinfo");
     type = 2;
   } else {
-    if (!o.has("config")) { fprintf(stderr, "usage: ring_config --config patch.toml [--port P] [--addr A] | --stats\n"); return 2; }
+    if (!o.has("config")) { fprintf(stderr, "usage: ring_config --config patch.toml [--port P] [--addr A] | --stats | --hwinfo\n"); return 2; }
     mccs::Value cfg;
     try {
       cfg = mccs::parse_toml(mccs::read_text_file(o.str("config")));

@@ -285,6 +285,31 @@ Value Daemon::admin_request(int type, const Value& body) {
     if (!planner_.load_json(body["tuning"], &err)) return bad(err);
     return ok();
   }
+  if (cmd == "hwinfo") {
+    // What the daemon sees of the box: devices, the CPUs local to each (where its proxy
+    // thread is pinned), the peer-access matrix and in-switch multicast support. The
+    // reference's get_hwinfo example prints the NVML affinity part of this
+    // (src/experimental/examples/get_hwinfo.rs).
+    Value hw = Value::object();
+    hw.set("backend", backend_->kind() == proto::kBackendCuda ? "cuda" : "host");
+    hw.set("describe", backend_->describe());
+    hw.set("nvls", backend_->nvls_supported());
+    hw.set("memops", backend_->memops_supported());
+    Value devs = Value::array();
+    const int n = backend_->device_count();
+    for (int d = 0; d < n; d++) {
+      Value dv = Value::object();
+      dv.set("index", d);
+      dv.set("cpu_affinity", backend_->cpu_affinity(d));
+      Value peers = Value::array();
+      for (int e = 0; e < n; e++) peers.push(d == e || backend_->peer_access(d, e));
+      dv.set("peer_access", peers);
+      devs.push(dv);
+    }
+    hw.set("devices", devs);
+    reply.set("hwinfo", hw);
+    return ok();
+  }
   if (cmd == "shutdown") {
     stop_.store(true);
     return ok();

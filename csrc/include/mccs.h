@@ -130,7 +130,10 @@ mccsResult_t mccsCommSetDeferredWait(mccsComm_t comm, int on);
 mccsResult_t mccsCommWait(mccsComm_t comm, mccsStream_t stream);
 
 /* Calls between GroupStart and GroupEnd are submitted back to back and completed
- * together at GroupEnd (the protocol's GroupCall, src/ipc/mccs/src/command.rs:93-95). */
+ * together at GroupEnd (the protocol's GroupCall, src/ipc/mccs/src/command.rs:93-95):
+ * the caller's stream is ordered after the whole group, not after each member, so the
+ * daemon can queue the members' kernels without a gap. Results of a member are defined
+ * for work queued after GroupEnd. */
 mccsResult_t mccsGroupStart(void);
 mccsResult_t mccsGroupEnd(void);
 

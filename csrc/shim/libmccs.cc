@@ -553,6 +553,13 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
   comm->memop_posted++;
   comm->last_posted_seq = wr.user_seq;
   if (comm->deferred_wait) return mccsSuccess;
+  if (g_group_depth > 0) {
+    // Inside a group the stream is not made to wait after every collective: the daemon
+    // sees all of them submitted at once and queues their kernels back to back;
+    // mccsGroupEnd orders the stream after the last one.
+    g_group_items.push_back({comm, stream});
+    return mccsSuccess;
+  }
   r = g_drv.cuStreamWaitValue64_((CUstream)stream, (CUdeviceptr)(comm->sync_base + 8 * proto::kSyncDoneSlot), wr.user_seq,
                                  CU_STREAM_WAIT_VALUE_GEQ);
   if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitValue64: %s", cu_err(r)); return mccsDeviceError; }
@@ -990,7 +997,10 @@ mccsResult_t mccsGroupEnd(void) {
     if (dup) continue;
     seen.push_back(it);
     if (it.comm->sticky_error && result == mccsSuccess) result = (mccsResult_t)it.comm->sticky_error;
-    mccsResult_t r = finish_on_stream(it.comm, it.stream);
+    // Event mode: wait for the daemon's "done" event. Mem-op mode: wait for the "done"
+    // value of the newest request (values grow in submission order).
+    mccsResult_t r = it.comm->sync_base ? (it.comm->deferred_wait ? mccsSuccess : mccsCommWait(it.comm, it.stream))
+                                        : finish_on_stream(it.comm, it.stream);
     if (r != mccsSuccess) result = r;
   }
   return result;

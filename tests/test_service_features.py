@@ -353,3 +353,12 @@ def test_committed_tuning_table_is_accepted(service):
                 assert after[kind][n][-1][0] == -1
     finally:
         M.admin_request(port, {"cmd": "tuning_set", "tuning": before})
+
+
+def test_hwinfo_reports_devices_and_peer_matrix(service):
+    M = service
+    hw = M.admin_request(M.daemon.embedded_admin_port(), {"cmd": "hwinfo"})["hwinfo"]
+    n = len(hw["devices"])
+    assert n >= 1 and hw["backend"] in ("host", "cuda")
+    for d in hw["devices"]:
+        assert len(d["peer_access"]) == n and d["peer_access"][d["index"]] is True
