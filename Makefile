@@ -67,8 +67,28 @@ $(OUT)/%: $(OBJ)/apps/%.o $(OBJ)/apps/app_common.o $(OUT)/libmccs.so
 $(OUT)/host_tests: $(OBJ)/tests/host_tests.o $(OUT)/libmccs_daemon.so
 	$(CXX) -o $@ $(OBJ)/tests/host_tests.o -L$(OUT) -lmccs_daemon -Wl,-rpath,'$$ORIGIN' $(LDLIBS)
 
+# Host-only builds of daemon + client library + a multi-tenant stress run in one process,
+# under ThreadSanitizer / AddressSanitizer+UBSan (no GPU, no CUDA toolkit needed at run time).
+SAN_SRCS := $(sort $(HOST_SRCS) $(SHIM_SRCS)) csrc/tests/no_cuda_backend.cc csrc/tests/stress_host.cc
+SAN_CXX ?= /usr/bin/g++
+SAN_FLAGS := -std=c++17 -O1 -g -fno-omit-frame-pointer -Wall -Wextra -Wno-unused-parameter -pthread -I/usr/local/cuda/include
+
+build/san/stress_tsan: $(SAN_SRCS) $(HDRS)
+	@mkdir -p build/san
+	$(SAN_CXX) $(SAN_FLAGS) -fsanitize=thread -o $@ $(SAN_SRCS) $(LDLIBS)
+
+build/san/stress_asan: $(SAN_SRCS) $(HDRS)
+	@mkdir -p build/san
+	$(SAN_CXX) $(SAN_FLAGS) -fsanitize=address,undefined -fno-sanitize-recover=undefined -o $@ $(SAN_SRCS) $(LDLIBS)
+
+tsan: build/san/stress_tsan
+	TSAN_OPTIONS="halt_on_error=0 second_deadlock_stack=1 suppressions=csrc/tests/tsan.supp" build/san/stress_tsan 40
+
+asan: build/san/stress_asan
+	ASAN_OPTIONS="detect_leaks=1" build/san/stress_asan 40
+
 clean:
 	rm -rf build $(OUT)/*.so $(OUT)/mccsd $(APP_BINS) $(OUT)/host_tests
 
-.PHONY: all clean
+.PHONY: all clean tsan asan
 .SECONDARY:

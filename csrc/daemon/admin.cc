@@ -129,6 +129,10 @@ int Daemon::apply_reconfig(const CommPattern& p, std::string* err) {
     return proto::kErrNotFound;
   }
   Communicator& c = *it->second;
+  if (c.state.load(std::memory_order_acquire) == kCommInit) {
+    if (err) *err = "communicator " + std::to_string(p.communicator_id) + " is still waiting for ranks";
+    return proto::kErrNotFound;
+  }
   if (p.channels.size() > (size_t)kMaxRingChannels) {
     if (err) *err = "too many channels";
     return proto::kErrInvalidArgument;
@@ -171,8 +175,11 @@ Value Daemon::stats() {
       v.set("completed", (int64_t)c.completed.load());
       v.set("last_variant", variant_name((int)c.last_variant.load()));
       v.set("last_ctas", (int64_t)c.last_ctas.load());
-      v.set("emulated", c.emulated);
-      v.set("host_staged", c.host_staged);
+      // Placement fields are written while the communicator is being set up, outside
+      // the registry lock; they are final once its state has left "init".
+      const bool ready = c.state.load(std::memory_order_acquire) != kCommInit;
+      v.set("emulated", ready && c.emulated);
+      v.set("host_staged", ready && c.host_staged);
       v.set("paused", c.paused.load());
       Value devs = Value::array();
       for (int d : c.devices) devs.push(d);

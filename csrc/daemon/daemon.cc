@@ -680,7 +680,7 @@ void Daemon::detach_rank(Communicator& c, int rank, int status) {
   // Make any kernel of this communicator that still waits give up now.
   if (status != proto::kOk)
     for (auto& r : c.ranks)
-      if (r && r->status) r->status->abort = 1;
+      if (r && r->status) __atomic_store_n(&r->status->abort, 1u, __ATOMIC_RELEASE);
   if (c.state.load() != kCommInit) proxies_[(size_t)rs->device]->remove_rank(rs);
   rs->gone.store(true);
   if (rs->stream) backend_->stream_sync(rs->device, rs->stream);

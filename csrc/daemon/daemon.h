@@ -136,7 +136,7 @@ struct RankState {
   struct Inflight { uint64_t ticket; uint64_t bytes; };
   std::deque<Inflight> inflight;       // rank 0 only: admitted, not yet seen finished
   uint64_t traced_ticket = 0;
-  uint64_t last_ticket = 0;            // ticket of the newest kernel launched for this rank
+  std::atomic<uint64_t> last_ticket{0};  // ticket of the newest kernel launched for this rank (rank 0's is read by every proxy of a one-launch group)
   std::atomic<bool> joined{false};
   std::atomic<bool> gone{false};       // its client went away
 };

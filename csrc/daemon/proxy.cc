@@ -398,7 +398,7 @@ bool ProxyEngine::launch_slices(RankState& rs, CollSlot& s, uint64_t seq) {
       const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
       rs.inflight.push_back({a.seq, bytes});
     }
-    rs.last_ticket = a.seq;
+    rs.last_ticket.store(a.seq, std::memory_order_relaxed);
     rs.next_slice++;
   }
   if (rs.sync.host && op.sync_slot)
@@ -471,7 +471,7 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
     }
     const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
     r0.inflight.push_back({a.seq, bytes});
-    r0.last_ticket = a.seq;
+    r0.last_ticket.store(a.seq, std::memory_order_relaxed);
     r0.next_slice++;
   }
   for (int r = 0; r < c.nranks; r++) {
@@ -570,7 +570,8 @@ bool ProxyEngine::advance(RankState& rs) {
     // launch, the proxies could wait on each other forever.
     if (st == kSlotPlanned) {
       RankState& gate = group ? *c.ranks[0] : rs;
-      if (gate.status && gate.last_ticket > *(volatile uint64_t*)&gate.status->done_seq + kMaxGpuQueue) break;
+      if (gate.status && gate.last_ticket.load(std::memory_order_relaxed) >
+                             __atomic_load_n(&gate.status->done_seq, __ATOMIC_ACQUIRE) + kMaxGpuQueue) break;
       if (rs.next_slice == 0 && !(group && s.group_launch.load(std::memory_order_acquire) == 2) && !clients_ready(c, s, group ? -1 : rs.rank)) break;
     }
     int status = proto::kOk;
@@ -594,7 +595,10 @@ bool ProxyEngine::advance(RankState& rs) {
       ev.slices = s.nslices; ev.bytes = s.plan.bytes;
       ev.t_post_us = s.ops[rs.rank].t_post_us; ev.t_ready_us = s.t_ready_us; ev.t_launch_us = monotonic_us();
       // Device stamps belong to the most recent finished kernel of this rank.
-      if (rs.status) { ev.dev_start_ns = rs.status->start_ns; ev.dev_end_ns = rs.status->end_ns; }
+      if (rs.status) {
+        ev.dev_start_ns = __atomic_load_n(&rs.status->start_ns, __ATOMIC_RELAXED);
+        ev.dev_end_ns = __atomic_load_n(&rs.status->end_ns, __ATOMIC_RELAXED);
+      }
       daemon_->tracer().record(ev);
     }
     complete_request(rs, s, seq, status);
@@ -611,14 +615,14 @@ void ProxyEngine::housekeeping(RankState& rs) {
   Communicator& c = *rs.comm;
   if (!rs.status) return;
   if (rs.rank == 0) {
-    const uint64_t done = *(volatile uint64_t*)&rs.status->done_seq;
+    const uint64_t done = __atomic_load_n(&rs.status->done_seq, __ATOMIC_ACQUIRE);
     while (!rs.inflight.empty() && rs.inflight.front().ticket <= done) {
       daemon_->qos().complete(c.id, rs.inflight.front().bytes);
       c.completed.fetch_add(1);
       rs.inflight.pop_front();
     }
   }
-  const uint32_t err = *(volatile uint32_t*)&rs.status->error;
+  const uint32_t err = __atomic_load_n(&rs.status->error, __ATOMIC_ACQUIRE);
   if (err != kDevOk && c.device_error.load() == kDevOk) {
     c.device_error.store(err);
     c.async_error.store(err == kDevAborted ? proto::kErrAborted : proto::kErrTimeout);
@@ -627,7 +631,7 @@ void ProxyEngine::housekeeping(RankState& rs) {
               err == kDevAborted ? "abort" : "a wait that ran out", rs.status->error_peer);
     // Let the other ranks' kernels give up at once instead of waiting out their bound.
     for (auto& r : c.ranks)
-      if (r && r->status) r->status->abort = 1;
+      if (r && r->status) __atomic_store_n(&r->status->abort, 1u, __ATOMIC_RELEASE);
     // Nothing is in flight for QoS purposes any more.
     if (rs.rank == 0) {
       while (!rs.inflight.empty()) { daemon_->qos().complete(c.id, rs.inflight.front().bytes); rs.inflight.pop_front(); }

@@ -21,7 +21,7 @@ uint64_t wall_us() {
 }
 
 void Tracer::record(const TraceEvent& e) {
-  if (!enabled_) return;
+  if (!enabled()) return;
   std::lock_guard<std::mutex> g(mu_);
   if (buf_.size() < cap_) buf_.push_back(e);
   else buf_[next_ % cap_] = e;

@@ -5,6 +5,7 @@
 #pragma once
 #include <stdint.h>
 
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -33,8 +34,8 @@ struct TraceEvent {
 class Tracer {
  public:
   explicit Tracer(size_t capacity = 1 << 16) : cap_(capacity) {}
-  void set_enabled(bool on) { enabled_ = on; }
-  bool enabled() const { return enabled_; }
+  void set_enabled(bool on) { enabled_.store(on, std::memory_order_relaxed); }
+  bool enabled() const { return enabled_.load(std::memory_order_relaxed); }
   void record(const TraceEvent& e);
   std::vector<TraceEvent> snapshot();
   Value to_chrome_json();
@@ -43,7 +44,7 @@ class Tracer {
 
  private:
   std::mutex mu_;
-  bool enabled_ = false;
+  std::atomic<bool> enabled_{false};
   size_t cap_;
   size_t next_ = 0;
   std::vector<TraceEvent> buf_;

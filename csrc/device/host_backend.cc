@@ -222,8 +222,8 @@ class HostBackend : public Backend {
 
   int launch(int, int kind, const CollArgs& a, LaunchDims, void*) override {
     if (!a.emulated && a.nranks > 1) return proto::kErrUnsupported;
-    if (a.status[0] && a.status[0]->abort) {
-      for (int r = 0; r < a.nranks; r++) if (a.status[r]) a.status[r]->error = kDevAborted;
+    if (a.status[0] && __atomic_load_n(&a.status[0]->abort, __ATOMIC_ACQUIRE)) {
+      for (int r = 0; r < a.nranks; r++) if (a.status[r]) __atomic_store_n(&a.status[r]->error, (uint32_t)kDevAborted, __ATOMIC_RELEASE);
       return proto::kOk;
     }
     if (kind == kAllGather) {
@@ -244,7 +244,7 @@ class HostBackend : public Backend {
       }
     }
     for (int r = 0; r < a.nranks; r++)
-      if (a.status[r]) a.status[r]->done_seq = a.seq;
+      if (a.status[r]) __atomic_store_n(&a.status[r]->done_seq, a.seq, __ATOMIC_RELEASE);
     return proto::kOk;
   }
 

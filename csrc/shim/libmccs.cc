@@ -737,13 +737,18 @@ mccsResult_t mccsFree(void* ptr) {
   {
     // Requests that name this memory may still sit in a request ring (calls return
     // before the daemon takes them): let the daemon take them first.
-    std::vector<mccsComm*> comms;
-    { std::unique_lock<std::mutex> g(g_ctx.mu); comms = g_ctx.comms; }
     // Only this thread's communicators: completions of another thread's requests are
-    // that thread's to read.
+    // that thread's to read, and another thread may destroy its communicator at any
+    // time, so those are looked at under the lock only.
+    std::vector<mccsComm*> mine;
+    {
+      std::unique_lock<std::mutex> g(g_ctx.mu);
+      for (mccsComm* c : g_ctx.comms)
+        if (pthread_equal(c->owner, pthread_self())) mine.push_back(c);
+    }
     if (g_ctx.connected)
-      for (mccsComm* c : comms)
-        if (pthread_equal(c->owner, pthread_self()) && (c->outstanding || c->memop_posted)) mccsCommFlush(c);
+      for (mccsComm* c : mine)
+        if (c->outstanding || c->memop_posted) mccsCommFlush(c);
   }
   std::unique_lock<std::mutex> g(g_ctx.mu);
   auto it = g_ctx.mem.find((uint64_t)ptr);
