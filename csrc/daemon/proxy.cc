@@ -18,10 +18,21 @@
 
 #include <algorithm>
 
+#include <nvtx3/nvToolsExt.h>   // header-only; ranges cost a pointer check unless a profiler is attached
+
 #include "../common/log.h"
 #include "daemon.h"
 
 namespace mccs {
+
+namespace {
+// NVTX range for a timeline profiler: planning and every launch show up on the proxy
+// thread's row, named after the kernel variant.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
+}  // namespace
 
 void ProxyEngine::on_start() {
   daemon_->backend()->set_device(device_);
@@ -558,7 +569,10 @@ bool ProxyEngine::advance(RankState& rs) {
       if (c.paused.load(std::memory_order_acquire)) break;
       int expect = kSlotCollected;
       if (!s.state.compare_exchange_strong(expect, kSlotPlanning, std::memory_order_acq_rel)) break;
-      plan_slot(c, s, seq);
+      {
+        NvtxRange range("mccs plan");
+        plan_slot(c, s, seq);
+      }
       st = s.state.load(std::memory_order_acquire);
       any = true;
     }
@@ -581,11 +595,15 @@ bool ProxyEngine::advance(RankState& rs) {
     } else if (group) {
       if (s.group_launch.load(std::memory_order_acquire) != 2) {
         if (rs.rank != 0) break;
+        NvtxRange range(variant_name(s.plan.variant));
         if (!launch_group(c, s, seq)) break;
       }
       if (c.state.load() == kCommError) status = c.async_error.load();
     } else {
-      if (!launch_slices(rs, s, seq)) break;
+      {
+        NvtxRange range(variant_name(s.plan.variant));
+        if (!launch_slices(rs, s, seq)) break;
+      }
       if (c.state.load() == kCommError) status = c.async_error.load();
     }
     if (daemon_->tracer().enabled() && st == kSlotPlanned) {

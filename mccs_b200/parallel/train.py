@@ -10,7 +10,8 @@ the vocabulary), random init, SGD. One rank per GPU:
 tenant: ``--comm-id`` is its QoS identity), overlapped with backward; ``--backend nccl``
 is torch's DistributedDataParallel over NCCL with the same bucket size, the baseline.
 The daemon must already run (``MCCS_CONTROL``), or ``--start-daemon`` lets local rank 0
-host it. Prints one JSON line with images/s or tokens/s.
+host it. Prints one JSON line with images/s or tokens/s. ``--save`` / ``--resume`` write and
+read a plain ``torch.save`` checkpoint of model and optimizer.
 """
 from __future__ import annotations
 
@@ -43,6 +44,8 @@ def main() -> int:
     ap.add_argument("--devices", default="", help="comma separated GPU index per rank (default: local rank)")
     ap.add_argument("--name", default="")
     ap.add_argument("--lr", type=float, default=0.01)
+    ap.add_argument("--save", default="", help="after the run rank 0 writes model + optimizer state here (torch.save)")
+    ap.add_argument("--resume", default="", help="load model + optimizer state written by --save before training")
     args = ap.parse_args()
 
     from mccs_b200 import models
@@ -69,6 +72,15 @@ def main() -> int:
         model.to(memory_format=torch.channels_last)   # before gradient buckets are laid out
     model.train()
     opt = torch.optim.SGD(model.parameters(), lr=args.lr, momentum=0.9)
+    start_step = 0
+    if args.resume:
+        # The service keeps no state of its own (neither does the reference's): a job's
+        # checkpoint is its model and optimizer, restored before the gradient buckets
+        # are laid out over the parameters.
+        ck = torch.load(args.resume, map_location=device)
+        model.load_state_dict(ck["model"])
+        opt.load_state_dict(ck["optimizer"])
+        start_step = int(ck.get("step", 0))
 
     M = None
     ddp = None
@@ -154,7 +166,10 @@ def main() -> int:
                ("tokens_per_s" if lm else "images_per_s"): units * world / ms * 1e3,
                "first_loss": losses[0] if losses else None, "last_loss": losses[-1],
                "grad_bytes": ddp.gradient_bytes() if ddp is not None else sum(p.numel() * p.element_size() for p in model.parameters()),
-               "buckets": len(ddp.buckets) if ddp is not None else None}
+               "buckets": len(ddp.buckets) if ddp is not None else None,
+               "step": start_step + args.warmup + args.steps}
+        if args.save:
+            torch.save({"model": model.state_dict(), "optimizer": opt.state_dict(), "step": out["step"]}, args.save)
         print(json.dumps(out), flush=True)
     barrier()
     if ddp is not None:
