@@ -12,7 +12,7 @@ LDLIBS    := -lpthread -ldl -lrt
 
 TYPES := i8:int8_t u8:uint8_t i32:int32_t u32:uint32_t i64:int64_t u64:uint64_t f16:__half f32:float f64:double bf16:__nv_bfloat16
 NVLS_TYPES := f16 f32 bf16
-TYPE_OBJS := $(foreach t,$(TYPES),$(OBJ)/inst_$(word 1,$(subst :, ,$(t))).o)
+TYPE_OBJS := $(foreach t,$(TYPES),$(OBJ)/inst_$(word 1,$(subst :, ,$(t))).o) $(foreach t,$(TYPES),$(OBJ)/batch_$(word 1,$(subst :, ,$(t))).o)
 
 HOST_SRCS := csrc/common/value.cc csrc/common/log.cc csrc/ipc/uds.cc csrc/device/host_backend.cc \
              csrc/daemon/config.cc csrc/daemon/planner.cc csrc/daemon/qos.cc csrc/daemon/trace.cc \
@@ -42,6 +42,9 @@ $(OBJ)/kernels/%.o: csrc/kernels/%.cu $(HDRS)
 
 define TYPE_RULE
 $(OBJ)/inst_$(1).o: csrc/kernels/inst_dtype.cu $(HDRS)
+	@mkdir -p $$(dir $$@)
+	$(NVCC) $(NVCCFLAGS) -DMCCS_T=$(2) -DMCCS_TNAME=$(1) $(if $(filter $(1),$(NVLS_TYPES)),-DMCCS_NVLS=1) -c $$< -o $$@ 2> $$@.log || (cat $$@.log; false)
+$(OBJ)/batch_$(1).o: csrc/kernels/inst_batch.cu $(HDRS)
 	@mkdir -p $$(dir $$@)
 	$(NVCC) $(NVCCFLAGS) -DMCCS_T=$(2) -DMCCS_TNAME=$(1) $(if $(filter $(1),$(NVLS_TYPES)),-DMCCS_NVLS=1) -c $$< -o $$@ 2> $$@.log || (cat $$@.log; false)
 endef

@@ -173,6 +173,8 @@ Value Daemon::stats() {
       v.set("device_error", (int64_t)c.device_error.load());
       v.set("planned", (int64_t)c.planned.load());
       v.set("completed", (int64_t)c.completed.load());
+      v.set("fused_launches", (int64_t)c.fused_launches.load());
+      v.set("fused_members", (int64_t)c.fused_members.load());
       v.set("last_variant", variant_name((int)c.last_variant.load()));
       v.set("last_ctas", (int64_t)c.last_ctas.load());
       // Placement fields are written while the communicator is being set up, outside

@@ -83,6 +83,9 @@ struct Config {
   int idle_spin_us = 200000;        // how long an idle proxy keeps busy-polling
   bool pin_threads = true;
   uint64_t init_timeout_ms = 60000; // how long a communicator waits for all its ranks
+  // Fused launches: up to this many consecutive AllReduces of a communicator (same type and
+  // operator, all queued when the first is planned) share one kernel; 1 = off.
+  int fuse_allreduce = 1;
 
   std::string control_socket_path() const;   // expanded prefix/path
   const CommPattern* find_override(uint32_t comm_id) const;

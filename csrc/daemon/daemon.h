@@ -102,6 +102,11 @@ struct CollSlot {
   uint64_t mc_recv[kMaxRanks];
   int8_t ring[kMaxRingChannels][kMaxRanks];   // ring order per channel, fixed at plan time
   uint64_t t_ready_us = 0;
+  // Fused launches. A head slot carries `batch_len` collectives (itself and the next
+  // batch_len - 1 slots) in one kernel; a follower slot has batch_len == 0 and launches
+  // nothing of its own. Written by the planning proxy before the slot becomes "planned".
+  int batch_len = 1;
+  uint64_t batch_bytes = 0;            // head: bytes of all members together (admission)
 };
 
 struct RankState {
@@ -155,6 +160,7 @@ class Communicator {
   std::atomic<int> async_error{0};
   std::atomic<uint32_t> device_error{0};
   std::atomic<uint64_t> planned{0}, completed{0};
+  std::atomic<uint64_t> fused_launches{0}, fused_members{0};
   std::atomic<uint32_t> last_variant{0}, last_ctas{0};
   std::atomic<bool> paused{false};
   uint64_t created_us = 0;
@@ -202,6 +208,11 @@ class ProxyEngine : public Engine {
   bool post(RankState& rs, const proto::WorkRequest& wr);
   bool advance(RankState& rs);
   bool plan_slot(Communicator& c, CollSlot& s, uint64_t seq);
+  void extend_batch(Communicator& c, CollSlot& head, uint64_t seq, const PlanInput& head_in, uint64_t now);
+  bool plan_member(Communicator& c, CollSlot& head, CollSlot& m, const PlanInput& head_in, Plan* out);
+  void fill_batch_args(Communicator& c, CollSlot& head, uint64_t seq, int rank, BatchArgs* b);
+  bool batch_clients_ready(Communicator& c, CollSlot& head, uint64_t seq, int self_rank);
+  uint64_t last_member_user_seq(Communicator& c, CollSlot& head, uint64_t seq, int rank);
   bool launch_group(Communicator& c, CollSlot& s, uint64_t seq);
   bool launch_slices(RankState& rs, CollSlot& s, uint64_t seq);
   bool admit_slice(Communicator& c, CollSlot& s, int slice);

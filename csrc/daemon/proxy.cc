@@ -203,6 +203,8 @@ int ProxyEngine::ensure_mc(Communicator& c, CollSlot& s, bool for_recv, uint64_t
 }
 
 bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
+  s.batch_len = 1;
+  s.batch_bytes = 0;
   auto fail = [&](int status) {
     s.status = status;
     s.state.store(kSlotFailed, std::memory_order_release);
@@ -331,8 +333,158 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   c.last_variant.store((uint32_t)plan.variant);
   c.last_ctas.store((uint32_t)plan.dims.ctas);
   daemon_->qos().note_waiting(c.id, now);
+  s.batch_bytes = plan.bytes;
+  extend_batch(c, s, seq, in, now);
   s.state.store(kSlotPlanned, std::memory_order_release);
   return true;
+}
+
+// ---------------------------------------------------------------------------
+// (3b): fused launches. The reference chains consecutive queued AllReduce tasks with
+// equal type and operator into one kernel (src/mccs/src/proxy/plan.rs:122-141). Here the
+// proxy that plans a collective looks at the slots right behind it: every one that all
+// ranks have already posted, that is an AllReduce of the same type and operator, and
+// for which the planner picks the same two-shot variant becomes a follower of this
+// slot. The decision is taken once, by one thread, before the head becomes visible as
+// planned, so every rank launches the same batch.
+// ---------------------------------------------------------------------------
+// Do two byte ranges of the same allocation overlap?
+static bool ranges_overlap(uint64_t mem_a, uint64_t off_a, uint64_t len_a, uint64_t mem_b, uint64_t off_b, uint64_t len_b) {
+  return mem_a == mem_b && off_a < off_b + len_b && off_b < off_a + len_a;
+}
+
+// Members of a fused launch run between ONE pair of barriers, so a member must not
+// depend on an earlier one: its buffers may share nothing with an earlier member's
+// output, and its output nothing with an earlier member's input.
+static bool independent_of(const CollSlot& earlier, const CollSlot& m, int nranks) {
+  for (int r = 0; r < nranks; r++) {
+    const CollOp& e = earlier.ops[r];
+    const CollOp& o = m.ops[r];
+    const uint64_t eb = e.count * (uint64_t)dtype_size(e.dtype), ob = o.count * (uint64_t)dtype_size(o.dtype);
+    if (ranges_overlap(e.recv_mem, e.recv_off, eb, o.send_mem, o.send_off, ob) ||
+        ranges_overlap(e.recv_mem, e.recv_off, eb, o.recv_mem, o.recv_off, ob) ||
+        ranges_overlap(e.send_mem, e.send_off, eb, o.recv_mem, o.recv_off, ob))
+      return false;
+  }
+  return true;
+}
+
+bool ProxyEngine::plan_member(Communicator& c, CollSlot& head, CollSlot& m, const PlanInput& head_in, Plan* out) {
+  const CollOp& h0 = head.ops[0];
+  const CollOp& o0 = m.ops[0];
+  Backend* be = daemon_->backend();
+  PlanInput in = head_in;
+  in.count = o0.count;
+  in.in_place = false;
+  uint64_t bits = 0;
+  bool same_send_off = true, same_recv_off = true;
+  int req = o0.variant_req;
+  for (int r = 0; r < c.nranks; r++) {
+    const CollOp& o = m.ops[r];
+    if (!o.valid || o.kind != kAllReduce || o.count != o0.count || o.dtype != h0.dtype || o.op != h0.op ||
+        o.scale != h0.scale)
+      return false;   // left to the ordinary path, which also reports mismatches
+    bits |= o.send_va | o.recv_va;
+    in.in_place |= o.send_va == o.recv_va;
+    same_send_off &= o.send_off == o0.send_off;
+    same_recv_off &= o.recv_off == o0.recv_off;
+    if (o.variant_req != req) req = kAuto;
+  }
+  in.aligned16 = (bits & 15u) == 0;
+  in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged &&
+                     be->kind() != proto::kBackendHost && same_recv_off && same_send_off && c.nranks >= 2;
+  {
+    std::lock_guard<std::mutex> g(c.cfg_mu);
+    in.requested_variant = req != kAuto ? req : c.ar_variant;
+    in.requested_ctas = c.ctas_override;
+  }
+  Plan p = daemon_->planner().plan(in);
+  if (p.status != proto::kOk || p.variant != head.plan.variant) return false;
+  if (p.needs_mc_send && ensure_mc(c, m, false, m.mc_send) != proto::kOk) return false;
+  if (p.needs_mc_recv && ensure_mc(c, m, true, m.mc_recv) != proto::kOk) return false;
+  *out = p;
+  return true;
+}
+
+void ProxyEngine::extend_batch(Communicator& c, CollSlot& head, uint64_t seq, const PlanInput& head_in, uint64_t now) {
+  const int limit = std::min(daemon_->config().fuse_allreduce, kMaxBatch);
+  if (limit <= 1) return;
+  Backend* be = daemon_->backend();
+  const CollOp& h0 = head.ops[0];
+  if (h0.kind != kAllReduce || head.nslices != 1) return;
+  if (head.plan.variant != kArTwoShot && head.plan.variant != kArNvlsTwo) return;
+  if (!be->batch_supported(head.plan.variant, h0.dtype, h0.op)) return;
+  int fit = kMaxCtas;
+  if (c.emulated && be->kind() != proto::kBackendHost) {
+    fit = be->max_group_batch_ctas(head.plan.variant, h0.dtype, h0.op, head.plan.dims.threads, c.nranks);
+    if (fit < 1) return;
+  }
+  const uint64_t slice_bytes = daemon_->qos().slice_bytes(c.id, now);
+  int len = 1;
+  int ctas = head.plan.dims.ctas;
+  uint64_t bytes = head.plan.bytes;
+  while (len < limit) {
+    const uint64_t mseq = seq + (uint64_t)len;
+    CollSlot& m = c.slot(mseq);
+    if (m.seq.load(std::memory_order_acquire) != mseq) break;
+    int expect = kSlotCollected;
+    if (!m.state.compare_exchange_strong(expect, kSlotPlanning, std::memory_order_acq_rel)) break;
+    Plan mp;
+    bool independent = true;
+    for (int e = 0; e < len && independent; e++)
+      independent = independent_of(e == 0 ? head : c.slot(seq + (uint64_t)e), m, c.nranks);
+    if (!independent || !plan_member(c, head, m, head_in, &mp) || (slice_bytes && mp.bytes > slice_bytes)) {
+      m.state.store(kSlotCollected, std::memory_order_release);   // planned on its own later
+      break;
+    }
+    m.plan = mp;
+    m.status = proto::kOk;
+    m.nslices = 1;
+    m.slice_count = m.ops[0].count;
+    m.batch_len = 0;
+    m.batch_bytes = 0;
+    m.t_ready_us = now;
+    m.admitted_slices.store(0, std::memory_order_relaxed);
+    m.group_launch.store(0, std::memory_order_relaxed);
+    ctas = std::max(ctas, mp.dims.ctas);
+    bytes += mp.bytes;
+    c.planned.fetch_add(1);
+    m.state.store(kSlotPlanned, std::memory_order_release);
+    len++;
+  }
+  if (len == 1) return;
+  head.plan.dims.ctas = std::min(ctas, fit);
+  head.batch_len = len;
+  head.batch_bytes = bytes;
+  c.fused_launches.fetch_add(1);
+  c.fused_members.fetch_add((uint64_t)len);
+}
+
+void ProxyEngine::fill_batch_args(Communicator& c, CollSlot& head, uint64_t seq, int rank, BatchArgs* out) {
+  BatchArgs& b = *out;
+  memset(&b, 0, sizeof b);
+  fill_args(c, head, rank, 0, &b.base);
+  b.nops = head.batch_len;
+  for (int k = 0; k < head.batch_len; k++) {
+    CollSlot& m = k == 0 ? head : c.slot(seq + (uint64_t)k);
+    b.count[k] = m.ops[0].count;
+    for (int r = 0; r < c.nranks; r++) {
+      b.send[k][r] = (const void*)m.ops[r].send_va;
+      b.recv[k][r] = (void*)m.ops[r].recv_va;
+    }
+    if (head.plan.needs_mc_send) b.mc_send[k] = (const void*)(m.mc_send[rank] + m.ops[rank].send_off);
+    if (head.plan.needs_mc_recv) b.mc_recv[k] = (void*)(m.mc_recv[rank] + m.ops[rank].recv_off);
+  }
+}
+
+bool ProxyEngine::batch_clients_ready(Communicator& c, CollSlot& head, uint64_t seq, int self_rank) {
+  for (int k = 0; k < head.batch_len; k++)
+    if (!clients_ready(c, k == 0 ? head : c.slot(seq + (uint64_t)k), self_rank)) return false;
+  return true;
+}
+
+uint64_t ProxyEngine::last_member_user_seq(Communicator& c, CollSlot& head, uint64_t seq, int rank) {
+  return c.slot(seq + (uint64_t)head.batch_len - 1).ops[rank].user_seq;
 }
 
 // ---------------------------------------------------------------------------
@@ -342,7 +494,7 @@ bool ProxyEngine::admit_slice(Communicator& c, CollSlot& s, int slice) {
   if (s.admitted_slices.load(std::memory_order_acquire) > slice) return true;
   std::lock_guard<std::mutex> g(c.admit_mu);
   if (s.admitted_slices.load(std::memory_order_acquire) > slice) return true;
-  const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
+  const uint64_t bytes = s.batch_len > 1 ? s.batch_bytes : s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
   QosDecision d = daemon_->qos().admit(c.id, bytes, monotonic_us(), wall_us());
   if (d != kQosAdmit) return false;
   s.admitted_slices.store(slice + 1, std::memory_order_release);
@@ -394,6 +546,30 @@ bool ProxyEngine::launch_slices(RankState& rs, CollSlot& s, uint64_t seq) {
   Communicator& c = *rs.comm;
   Backend* be = daemon_->backend();
   const CollOp& op = s.ops[rs.rank];
+  if (s.batch_len > 1) {
+    // One kernel for this slot and its followers.
+    if (!admit_slice(c, s, 0)) return false;
+    for (int k = 0; k < s.batch_len; k++)
+      order_after_client(rs, (k == 0 ? s : c.slot(seq + (uint64_t)k)).ops[rs.rank], rs.stream);
+    BatchArgs b;
+    fill_batch_args(c, s, seq, rs.rank, &b);
+    int rc = be->launch_batch(rs.device, b, s.plan.dims, rs.stream);
+    if (rc != proto::kOk) {
+      c.async_error.store(rc);
+      c.state.store(kCommError);
+    } else {
+      if (rs.rank == 0) rs.inflight.push_back({b.base.seq, s.batch_bytes});
+      rs.last_ticket.store(b.base.seq, std::memory_order_relaxed);
+    }
+    rs.next_slice = 1;
+    // "done" values grow in submission order: the last member's covers the whole batch.
+    if (rs.sync.host && op.sync_slot)
+      be->stream_write_value64(rs.device, rs.stream, rs.sync.dev_addr + 8 * proto::kSyncDoneSlot,
+                               last_member_user_seq(c, s, seq, rs.rank));
+    else
+      be->event_record(rs.device, rs.backend_event, rs.stream);
+    return true;
+  }
   while (rs.next_slice < s.nslices) {
     if (!admit_slice(c, s, rs.next_slice)) return false;
     if (rs.next_slice == 0) order_after_client(rs, op, rs.stream);
@@ -467,6 +643,34 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
   (void)seq;
   RankState& r0 = *c.ranks[0];
   Backend* be = daemon_->backend();
+  if (s.batch_len > 1) {
+    if (!admit_slice(c, s, 0)) return false;
+    for (int k = 0; k < s.batch_len; k++) {
+      CollSlot& m = k == 0 ? s : c.slot(seq + (uint64_t)k);
+      for (int r = 0; r < c.nranks; r++) order_after_client(*c.ranks[(size_t)r], m.ops[r], c.group_stream);
+    }
+    BatchArgs b;
+    fill_batch_args(c, s, seq, 0, &b);
+    int rc = be->launch_batch(r0.device, b, s.plan.dims, c.group_stream);
+    if (rc != proto::kOk) {
+      c.async_error.store(rc);
+      c.state.store(kCommError);
+    } else {
+      r0.inflight.push_back({b.base.seq, s.batch_bytes});
+      r0.last_ticket.store(b.base.seq, std::memory_order_relaxed);
+    }
+    r0.next_slice = 1;
+    for (int r = 0; r < c.nranks; r++) {
+      RankState& rr = *c.ranks[(size_t)r];
+      if (rr.sync.host && s.ops[r].sync_slot)
+        be->stream_write_value64(rr.device, c.group_stream, rr.sync.dev_addr + 8 * proto::kSyncDoneSlot,
+                                 last_member_user_seq(c, s, seq, r));
+      else
+        be->event_record(rr.device, rr.backend_event, c.group_stream);
+    }
+    s.group_launch.store(2, std::memory_order_release);
+    return true;
+  }
   while (r0.next_slice < s.nslices) {
     if (!admit_slice(c, s, r0.next_slice)) return false;
     if (r0.next_slice == 0) {
@@ -582,16 +786,21 @@ bool ProxyEngine::advance(RankState& rs) {
     // a launch call then blocks this proxy thread, and since a blocked kernel at the head
     // of that stream waits for a peer kernel that another (equally blocked) proxy has to
     // launch, the proxies could wait on each other forever.
-    if (st == kSlotPlanned) {
+    const bool follower = st == kSlotPlanned && s.batch_len == 0;   // went out with its head's launch
+    if (st == kSlotPlanned && !follower) {
       RankState& gate = group ? *c.ranks[0] : rs;
       if (gate.status && gate.last_ticket.load(std::memory_order_relaxed) >
                              __atomic_load_n(&gate.status->done_seq, __ATOMIC_ACQUIRE) + kMaxGpuQueue) break;
-      if (rs.next_slice == 0 && !(group && s.group_launch.load(std::memory_order_acquire) == 2) && !clients_ready(c, s, group ? -1 : rs.rank)) break;
+      if (rs.next_slice == 0 && !(group && s.group_launch.load(std::memory_order_acquire) == 2) &&
+          !(s.batch_len > 1 ? batch_clients_ready(c, s, seq, group ? -1 : rs.rank) : clients_ready(c, s, group ? -1 : rs.rank)))
+        break;
     }
     int status = proto::kOk;
     if (st == kSlotFailed) {
       status = s.status;
       if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq);
+    } else if (follower) {
+      if (c.state.load() == kCommError) status = c.async_error.load();
     } else if (group) {
       if (s.group_launch.load(std::memory_order_acquire) != 2) {
         if (rs.rank != 0) break;

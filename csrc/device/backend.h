@@ -116,6 +116,12 @@ class Backend {
   virtual bool variant_supported(int variant, int dtype, int op) const = 0;
   // CTAs per rank that fit when one cooperative launch carries all `nranks` ranks.
   virtual int max_group_ctas(int variant, int dtype, int op, int threads, int nranks) const = 0;
+
+  // Fused AllReduce: several consecutive collectives of one communicator in one launch
+  // (kernels/batch.cuh; the reference's fused work elements, src/mccs/src/proxy/plan.rs:122-141).
+  virtual bool batch_supported(int variant, int dtype, int op) const = 0;
+  virtual int max_group_batch_ctas(int variant, int dtype, int op, int threads, int nranks) const = 0;
+  virtual int launch_batch(int dev, const BatchArgs& b, LaunchDims dims, void* stream) = 0;
 };
 
 // Returns nullptr (and a reason) when no usable CUDA device exists.

@@ -516,6 +516,24 @@ class CudaBackend : public Backend {
     return max_cooperative_ctas(variant, dtype, op, threads, nranks);
   }
 
+  bool batch_supported(int variant, int dtype, int op) const override {
+    if (variant_is_nvls(variant) && !nvls_) return false;
+    return batch_kernel_function(variant, dtype, op) != nullptr;
+  }
+  int max_group_batch_ctas(int variant, int dtype, int op, int threads, int nranks) const override {
+    return max_cooperative_batch_ctas(variant, dtype, op, threads, nranks);
+  }
+  int launch_batch(int dev, const BatchArgs& b, LaunchDims dims, void* stream) override {
+    (void)dev;
+    cudaError_t e = mccs::launch_batch(b, dims, stream);
+    if (e != cudaSuccess) {
+      LOG_ERROR("fused launch of %d x %s failed: %s", b.nops, variant_name(b.base.variant), cudaGetErrorString(e));
+      cudaGetLastError();
+      return proto::kErrDevice;
+    }
+    return proto::kOk;
+  }
+
   int launch(int dev, int kind, const CollArgs& a, LaunchDims dims, void* stream) override {
     (void)dev;
     cudaError_t e = launch_collective(kind, a, dims, stream);

@@ -220,6 +220,20 @@ class HostBackend : public Backend {
   bool variant_supported(int variant, int, int) const override { return !variant_is_nvls(variant); }
   int max_group_ctas(int, int, int, int, int) const override { return kMaxCtas; }
 
+  bool batch_supported(int variant, int, int) const override { return variant == kArTwoShot; }
+  int max_group_batch_ctas(int, int, int, int, int) const override { return kMaxCtas; }
+  int launch_batch(int dev, const BatchArgs& b, LaunchDims dims, void* stream) override {
+    if (b.nops < 1 || b.nops > kMaxBatch) return proto::kErrInvalidArgument;
+    for (int k = 0; k < b.nops; k++) {
+      CollArgs a = b.base;
+      a.count = b.count[k];
+      for (int r = 0; r < a.nranks; r++) { a.send[r] = b.send[k][r]; a.recv[r] = b.recv[k][r]; }
+      int rc = launch(dev, kAllReduce, a, dims, stream);
+      if (rc != proto::kOk) return rc;
+    }
+    return proto::kOk;
+  }
+
   int launch(int, int kind, const CollArgs& a, LaunchDims, void*) override {
     if (!a.emulated && a.nranks > 1) return proto::kErrUnsupported;
     if (a.status[0] && __atomic_load_n(&a.status[0]->abort, __ATOMIC_ACQUIRE)) {

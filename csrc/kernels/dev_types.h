@@ -117,6 +117,24 @@ struct CollArgs {
   uint64_t ring_step_base[kMaxRingChannels];  // cumulative steps already used per channel
 };
 
+// Several consecutive AllReduces of one communicator with the same element type and
+// operator, carried by ONE launch: one barrier before the first and one after the last
+// instead of two per collective. The reference fuses the same way, up to 10 work
+// elements per work item (src/mccs/src/proxy/plan.rs:122-141,
+// src/collectives/include/devcomm.h:66,103-104). `base` gives everything that is per
+// launch (identity, op, epoch, pads, status); its own send/recv/count are unused.
+constexpr int kMaxBatch = 8;
+struct BatchArgs {
+  CollArgs base;
+  int32_t nops;
+  int32_t pad0_;
+  uint64_t count[kMaxBatch];                 // elements of each member
+  const void* send[kMaxBatch][kMaxRanks];
+  void* recv[kMaxBatch][kMaxRanks];
+  const void* mc_send[kMaxBatch];            // NVLS members only
+  void* mc_recv[kMaxBatch];
+};
+
 struct LaunchDims {
   int32_t ctas;      // grid.x (per rank)
   int32_t threads;   // block.x

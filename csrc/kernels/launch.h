@@ -15,4 +15,10 @@ cudaError_t launch_collective(int kind, const CollArgs& args, LaunchDims dims, v
 // Largest CTA count per rank that keeps an emulated (cooperative) launch resident.
 int max_cooperative_ctas(int variant, int dtype, int op, int threads, int nranks);
 
+// Fused AllReduce (several members in one launch, see batch.cuh). Only the two-shot
+// variants have a fused form; returns null / cudaErrorInvalidDeviceFunction otherwise.
+const void* batch_kernel_function(int variant, int dtype, int op);
+cudaError_t launch_batch(const BatchArgs& args, LaunchDims dims, void* stream);
+int max_cooperative_batch_ctas(int variant, int dtype, int op, int threads, int nranks);
+
 }  // namespace mccs

@@ -50,6 +50,8 @@ void run_rank(const App& app, int rank) {
   EXPECT(mccsMalloc((void**)&recv, dev, count * sizeof(float)) == mccsSuccess);
   EXPECT(mccsMalloc((void**)&gath, dev, 1024 * (size_t)n) == mccsSuccess);
   if (!send || !recv || !gath) return;
+  float* multi[4] = {nullptr, nullptr, nullptr, nullptr};   // independent buffers: these may share one fused launch
+  for (int k = 0; k < 4; k++) EXPECT(mccsMalloc((void**)&multi[k], dev, (64 + 16 * (size_t)k) * sizeof(float)) == mccsSuccess);
   // Several lives of the communicator: creation and teardown race with the operator's
   // statistics and reconfiguration requests and with the other tenants' traffic.
   for (int life = 0; life < 3; life++) {
@@ -67,6 +69,16 @@ void run_rank(const App& app, int rank) {
       EXPECT(mccsGroupEnd() == mccsSuccess);
       float want = (float)n + (float)it;   // max over ranks of (rank+1) + 0 + it at i == 0
       EXPECT(recv[0] == want);
+      for (int k = 0; k < 4; k++)
+        for (int i = 0; i < 64 + 16 * k; i++) multi[k][i] = (float)(rank + k + i % 3);
+      EXPECT(mccsGroupStart() == mccsSuccess);
+      for (int k = 0; k < 4; k++)
+        EXPECT(mccsAllReduce(comm, multi[k], multi[k], 64 + 16 * (size_t)k, mccsFloat32, mccsSum, nullptr) == mccsSuccess);
+      EXPECT(mccsGroupEnd() == mccsSuccess);
+      for (int k = 0; k < 4; k++) {
+        const int last = 64 + 16 * k - 1;
+        EXPECT(multi[k][last] == (float)(n * (n - 1) / 2) + (float)n * (float)(k + last % 3));
+      }
       continue;
     }
     EXPECT(mccsAllReduce(comm, send, recv, count, mccsFloat32, mccsSum, nullptr) == mccsSuccess);
@@ -85,6 +97,7 @@ void run_rank(const App& app, int rank) {
   EXPECT(mccsFree(send) == mccsSuccess);
   EXPECT(mccsFree(recv) == mccsSuccess);
   EXPECT(mccsFree(gath) == mccsSuccess);
+  for (int k = 0; k < 4; k++) EXPECT(mccsFree(multi[k]) == mccsSuccess);
 }
 
 void operator_thread(const std::vector<App>& apps, std::atomic<bool>* stop) {
@@ -121,7 +134,7 @@ int main(int argc, char** argv) {
   const std::string cfg =
       "listen_port = -1\nmccs_daemon_prefix = \"" + prefix + "\"\n[control]\nprefix = \"" + prefix +
       "\"\npath = \"control.sock\"\n[comm_default_config]\nbuffer_sizes = [65536]\nchannel_count = 2\n"
-      "[b200]\nforce_host_backend = true\nhost_devices = 4\nwait_timeout_ms = 20000\n"
+      "[b200]\nforce_host_backend = true\nhost_devices = 4\nwait_timeout_ms = 20000\nfuse_allreduce = 4\n"
       "[qos.tenants.7001]\nweight = 2.0\n[qos.tenants.7002]\nweight = 1.0\n";
   if (mccs::mccsd_start(cfg.c_str()) != 0) {
     fprintf(stderr, "daemon did not start\n");

@@ -7,7 +7,10 @@ collectives of one variant, then exit.
         python -m mccs_b200.utils.profile_case --algo ar_twoshot --ranks 4 --mb 256
 
 The buffers are larger than the L2 (126 MB) by default, so DRAM counters mean
-something, and stay within a few GB in total.
+something, and stay within a few GB in total. ``--fuse K`` splits the message into K
+independent AllReduces issued as one group with fused launches switched on, which is
+how the fused kernels (``ar_twoshot_batch``) are reached. Rank 0 checks the last result
+against a plain fp32 sum (or the concatenation) of the ranks' inputs.
 """
 from __future__ import annotations
 
@@ -29,9 +32,11 @@ def main() -> int:
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--ctas", type=int, default=0)
+    ap.add_argument("--fuse", type=int, default=1, help="members per fused launch (AllReduce only)")
     a = ap.parse_args()
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
-    M.daemon.start_embedded(prefix=f"/tmp/mccs-prof-{os.getpid()}", listen_port=-1)
+    M.daemon.start_embedded(prefix=f"/tmp/mccs-prof-{os.getpid()}", listen_port=-1,
+                            extra=f"fuse_allreduce = {a.fuse}" if a.fuse > 1 else "")
     if M.backend() != "cuda":
         print("profile_case needs a GPU", file=sys.stderr)
         return 1
@@ -42,6 +47,9 @@ def main() -> int:
     count = nbytes // esz
     errors = []
     ready = threading.Barrier(n)
+    inputs = [None] * n
+    parts = max(a.fuse, 1) if is_ar else 1
+    part = count // parts // 64 * 64      # elements per member, 128-byte multiples
 
     def rank_fn(r: int) -> None:
         try:
@@ -51,18 +59,37 @@ def main() -> int:
             recv = M.Buffer(nbytes if is_ar else nbytes * n, 0)
             s = send.tensor(dtype, count)
             s.copy_(((torch.rand(min(count, 1 << 20)) * 2 - 1).to(dtype)).repeat((count + (1 << 20) - 1) // (1 << 20))[:count])
+            inputs[r] = s
+            r_all = recv.tensor(dtype, count if is_ar else count * n)
             comm = M.Communicator(77, r, n, device=0)
             if a.ctas and r == 0:
                 M.reconfigure(M.daemon.embedded_admin_port(), [{"communicator_id": 77, "ctas": a.ctas}])
             ready.wait()
             for _ in range(a.iters):
-                if is_ar:
-                    comm.all_reduce(s, recv.tensor(dtype, count), algo=a.algo)
+                if is_ar and parts > 1:
+                    with M.group():
+                        for k in range(parts):
+                            comm.all_reduce(s[k * part:(k + 1) * part], r_all[k * part:(k + 1) * part], algo=a.algo)
+                elif is_ar:
+                    comm.all_reduce(s, r_all, algo=a.algo)
                 else:
-                    comm.all_gather(s, recv.tensor(dtype, count * n), algo=a.algo)
+                    comm.all_gather(s, r_all, algo=a.algo)
             torch.cuda.synchronize()
+            ready.wait()
             if r == 0:
                 print("plan:", comm.last_plan(), flush=True)
+                m = min(part * parts if is_ar else count, 1 << 22)   # compare the head of the buffers
+                if is_ar:
+                    want = torch.stack([x[:m].float() for x in inputs]).sum(0)
+                    tol = 1e-5 if dtype == torch.float32 else 2e-2
+                    good = bool(torch.allclose(r_all[:m].float(), want, rtol=tol, atol=tol * n))
+                else:
+                    good = all(bool(torch.equal(r_all[q * count:q * count + m], inputs[q][:m])) for q in range(n))
+                st = M.daemon.embedded_admin({"cmd": "stats"})["stats"]["communicators"]["77"]
+                print(f"check: {'ok' if good else 'MISMATCH'}  fused_launches={st['fused_launches']} "
+                      f"fused_members={st['fused_members']}", flush=True)
+                if not good:
+                    errors.append(RuntimeError("result mismatch"))
             ready.wait()
             comm.destroy()
         except Exception as e:  # noqa: BLE001

@@ -362,3 +362,79 @@ def test_hwinfo_reports_devices_and_peer_matrix(service):
     assert n >= 1 and hw["backend"] in ("host", "cuda")
     for d in hw["devices"]:
         assert len(d["peer_access"]) == n and d["peer_access"][d["index"]] is True
+
+
+# ---------------------------------------------------------------------------------------------
+# fused launches: consecutive queued AllReduces of one communicator in one kernel
+# ---------------------------------------------------------------------------------------------
+FUSION_CLIENT = r"""
+import os, sys, json, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"])
+sizes = [1, 7, 256, 1000, 4096, 65539, 300, 12, 2048, 5, 33, 100000, 64, 8, 77, 1024]
+bufs = [M.Buffer(max(s, 4) * 4, rank) for s in sizes]
+c = M.Communicator(5151, rank, n, device=rank)
+ok = True
+for rnd in range(3):
+    ts = [b.tensor(torch.float32, s) for b, s in zip(bufs, sizes)]
+    for i, t in enumerate(ts):
+        t.copy_(torch.arange(t.numel(), dtype=torch.float32) % 13 + rank + i + rnd)
+    with M.group():
+        for i, t in enumerate(ts):
+            if i == 9:
+                # a different operator in the middle: ends one batch, starts another
+                c.all_reduce(t, op="max")
+            else:
+                c.all_reduce(t)
+    for i, (t, s) in enumerate(zip(ts, sizes)):
+        base = torch.arange(s, dtype=torch.float32) % 13 + i + rnd
+        want = base + (n - 1) if i == 9 else base * n + sum(range(n))
+        ok &= bool(torch.equal(t, want))
+    # the same buffers again, one by one (nothing to fuse with)
+    c.all_reduce(ts[2])
+    ok &= bool(torch.equal(ts[2], (torch.arange(256, dtype=torch.float32) % 13 + 2 + rnd) * n * n + sum(range(n)) * n))
+# members that depend on each other (the same buffer four times) must not share a launch
+dep = bufs[4].tensor(torch.float32, 4096)
+dep.fill_(1.0)
+with M.group():
+    for _ in range(4):
+        c.all_reduce(dep)
+ok &= bool(torch.all(dep == float(n) ** 4))
+q = c.query()
+st = M.admin_request(int(os.environ["ADMIN_PORT"]), {"cmd": "stats"})["stats"]["communicators"]["5151"]
+c.destroy()
+print("RESULT", json.dumps({"ok": ok, "launched": q["launched"], "async_error": q["async_error"],
+                            "fused_launches": st["fused_launches"], "fused_members": st["fused_members"]}), flush=True)
+"""
+
+
+def test_consecutive_allreduces_share_one_launch(tmp_path):
+    """With `fuse_allreduce = 8` a burst of queued AllReduces with the same type and
+    operator goes out as fused launches (the reference's plan.rs:122-141), results are
+    those of the separate collectives, and a change of operator splits the batch."""
+    import json
+    from mccs_b200 import daemon
+    import mccs_b200 as M
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=-1,
+                       force_host=True, extra="fuse_allreduce = 8")
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        n = 4
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), MCCS_LOG="error",
+                   ADMIN_PORT=str(sp.admin_port))
+        procs = [subprocess.Popen([sys.executable, "-c", FUSION_CLIENT], env=dict(env, RANK=str(r)),
+                                  stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(n)]
+        outs = [p.communicate(timeout=120) for p in procs]
+        fused = []
+        for p, (out, err) in zip(procs, outs):
+            assert p.returncode == 0, err[-2000:]
+            res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+            assert res["ok"] and res["async_error"] == 0
+            assert res["launched"] == 3 * 17 + 4
+            fused.append((res["fused_launches"], res["fused_members"]))
+        # every fused launch carries 2..8 members, and the bursts did get fused
+        launches, members = max(fused)
+        assert launches >= 1 and 2 * launches <= members <= 8 * launches, fused
+    finally:
+        sp.stop()
