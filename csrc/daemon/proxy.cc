@@ -796,6 +796,7 @@ bool ProxyEngine::advance(RankState& rs) {
         break;
     }
     int status = proto::kOk;
+    const uint64_t t_go_us = daemon_->tracer().enabled() ? monotonic_us() : 0;
     if (st == kSlotFailed) {
       status = s.status;
       if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq);
@@ -821,6 +822,7 @@ bool ProxyEngine::advance(RankState& rs) {
       ev.kind = s.ops[rs.rank].kind; ev.variant = s.plan.variant; ev.ctas = s.plan.dims.ctas;
       ev.slices = s.nslices; ev.bytes = s.plan.bytes;
       ev.t_post_us = s.ops[rs.rank].t_post_us; ev.t_ready_us = s.t_ready_us; ev.t_launch_us = monotonic_us();
+      ev.t_go_us = t_go_us;
       // Device stamps belong to the most recent finished kernel of this rank.
       if (rs.status) {
         ev.dev_start_ns = __atomic_load_n(&rs.status->start_ns, __ATOMIC_RELAXED);

@@ -65,7 +65,12 @@ Value Tracer::to_chrome_json() {
       events.push(ev);
     };
     span("rendezvous", e.t_post_us, e.t_ready_us);
-    span("admit+launch", e.t_ready_us, e.t_launch_us);
+    if (e.t_go_us >= e.t_ready_us && e.t_go_us <= e.t_launch_us) {
+      span("wait for clients", e.t_ready_us, e.t_go_us);
+      span("admit+launch", e.t_go_us, e.t_launch_us);
+    } else {
+      span("admit+launch", e.t_ready_us, e.t_launch_us);
+    }
     if (e.dev_start_ns && e.dev_end_ns >= e.dev_start_ns) {
       Value ev = Value::object();
       ev.set("name", std::string("device ") + variant_name(e.variant));

@@ -26,6 +26,7 @@ struct TraceEvent {
   uint64_t bytes = 0;
   uint64_t t_post_us = 0;     // work request taken from the client's ring
   uint64_t t_ready_us = 0;    // all ranks arrived and the plan exists
+  uint64_t t_go_us = 0;       // every gate passed (queue bound, all clients' streams arrived, admission may still defer)
   uint64_t t_launch_us = 0;   // last slice enqueued on the backend stream
   uint64_t dev_start_ns = 0;  // previous collective's device stamps (read back lazily)
   uint64_t dev_end_ns = 0;

@@ -51,3 +51,25 @@ dependencies = [1]
     assert res.returncode == 0, res.stdout + res.stderr
     assert marker.read_text().split() == ["service", "job1", "job2"]
     assert "hello from job1" in (out / "unit" / "1_python.stdout").read_text()
+
+
+def test_latency_breakdown_tool_on_host_backend():
+    """The per-stage latency report runs end to end (two gloo ranks, host backend) and
+    its host-side stages add up to less than the measured period."""
+    import json
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, PYTHONPATH=REPO, MCCS_LOG="warn")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "mccs_b200.utils.latency",
+                          "--bytes", "4K", "--iters", "100", "--warmup", "10", "--json"],
+                         env=env, capture_output=True, text=True, timeout=300, cwd=REPO)
+    assert res.returncode == 0, res.stderr[-3000:]
+    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
+    out = json.loads(line)
+    assert out["n"] == 2 and out["backend"] == "host" and out["period_us"] > 0
+    st = out["stages"]
+    assert st["rendezvous"]["n"] == 200 and st["launch"]["n"] == 200
+    assert st["rendezvous"]["median_us"] + st["launch"]["median_us"] < 5 * out["period_us"] + 50
