@@ -84,6 +84,16 @@ build/san/stress_asan: $(SAN_SRCS) $(HDRS)
 	@mkdir -p build/san
 	$(SAN_CXX) $(SAN_FLAGS) -fsanitize=address,undefined -fno-sanitize-recover=undefined -o $@ $(SAN_SRCS) $(LDLIBS)
 
+# The stand-alone daemon (host backend only) under a sanitizer, for the failure-path tests:
+#   make build/san/mccsd_asan && MCCSD=build/san/mccsd_asan python -m pytest tests/test_service_features.py
+SAN_DAEMON_SRCS := $(HOST_SRCS) csrc/tests/no_cuda_backend.cc csrc/daemon/main.cc
+build/san/mccsd_asan: $(SAN_DAEMON_SRCS) $(HDRS)
+	@mkdir -p build/san
+	$(SAN_CXX) $(SAN_FLAGS) -fsanitize=address,undefined -fno-sanitize-recover=undefined -o $@ $(SAN_DAEMON_SRCS) $(LDLIBS)
+build/san/mccsd_tsan: $(SAN_DAEMON_SRCS) $(HDRS)
+	@mkdir -p build/san
+	$(SAN_CXX) $(SAN_FLAGS) -fsanitize=thread -o $@ $(SAN_DAEMON_SRCS) $(LDLIBS)
+
 tsan: build/san/stress_tsan
 	TSAN_OPTIONS="halt_on_error=0 second_deadlock_stack=1 suppressions=csrc/tests/tsan.supp" build/san/stress_tsan 40
 

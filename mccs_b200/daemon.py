@@ -136,7 +136,7 @@ class SpawnedDaemon:
 
 def spawn(config_path: str, *, env: Optional[dict] = None, timeout: float = 120.0) -> SpawnedDaemon:
     """Start ``mccsd --config config_path`` and wait until it accepts clients."""
-    exe = os.path.join(_lib.NATIVE_DIR, "mccsd")
+    exe = os.environ.get("MCCSD") or os.path.join(_lib.NATIVE_DIR, "mccsd")   # MCCSD: another build, e.g. a sanitizer one
     if not os.path.exists(exe):
         raise FileNotFoundError(f"{exe} is missing: run `make -j` at the repository root")
     e = dict(os.environ)
