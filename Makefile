@@ -97,8 +97,13 @@ build/san/mccsd_tsan: $(SAN_DAEMON_SRCS) $(HDRS)
 tsan: build/san/stress_tsan
 	TSAN_OPTIONS="halt_on_error=0 second_deadlock_stack=1 suppressions=csrc/tests/tsan.supp" build/san/stress_tsan 40
 
-asan: build/san/stress_asan
+build/san/fuzz_value: csrc/tests/fuzz_value.cc csrc/common/value.cc csrc/common/log.cc csrc/daemon/config.cc $(HDRS)
+	@mkdir -p build/san
+	$(SAN_CXX) $(SAN_FLAGS) -fsanitize=address,undefined -fno-sanitize-recover=undefined -o $@ csrc/tests/fuzz_value.cc csrc/common/value.cc csrc/common/log.cc csrc/daemon/config.cc $(LDLIBS)
+
+asan: build/san/stress_asan build/san/fuzz_value
 	ASAN_OPTIONS="detect_leaks=1" build/san/stress_asan 40
+	build/san/fuzz_value 40000
 
 clean:
 	rm -rf build $(OUT)/*.so $(OUT)/mccsd $(APP_BINS) $(OUT)/host_tests

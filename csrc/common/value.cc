@@ -97,6 +97,16 @@ struct Scanner {
     throw ParseError("line " + std::to_string(line) + ": " + m);
   }
   void expect(char c) { if (peek() != c) fail(std::string("expected '") + c + "'"); get(); }
+  // Nesting of arrays and tables is bounded: the parsers recurse, and some of their
+  // input (the admin endpoint's JSON) comes from the network.
+  int depth = 0;
+  static constexpr int kMaxDepth = 64;
+};
+
+struct Nested {
+  Scanner& sc;
+  explicit Nested(Scanner& s) : sc(s) { if (++sc.depth > Scanner::kMaxDepth) sc.fail("nested too deeply"); }
+  ~Nested() { sc.depth--; }
 };
 
 void append_utf8(std::string& out, unsigned cp) {
@@ -194,6 +204,7 @@ void json_ws(Scanner& sc) {
 }
 
 Value json_value(Scanner& sc) {
+  Nested guard(sc);
   json_ws(sc);
   char c = sc.peek();
   if (c == '{') {
@@ -308,6 +319,7 @@ Value toml_inline_table(Scanner& sc) {  // after '{'
 }
 
 Value toml_value(Scanner& sc) {
+  Nested guard(sc);
   toml_ws(sc);
   char c = sc.peek();
   if (c == '"') {

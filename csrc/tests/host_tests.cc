@@ -227,6 +227,16 @@ static void test_planner() {
   pl = p.plan(q);
   CHECK(pl.variant == kArOneShot && pl.dims.threads == 256);
   CHECK(!p.load_json(parse_json("{\"allreduce\": {\"8\": [[1, \"nope\", 4]]}}"), &err));
+  {
+    // parsers refuse absurd nesting instead of recursing until the stack runs out
+    std::string deep(100000, '[');
+    bool threw = false;
+    try { parse_json(deep); } catch (const std::exception&) { threw = true; }
+    CHECK(threw);
+    threw = false;
+    try { parse_toml("a = " + deep); } catch (const std::exception&) { threw = true; }
+    CHECK(threw);
+  }
   Planner p2;
   CHECK(p2.load_json(p.to_json(), &err));
   CHECK(p2.to_json().to_json() == p.to_json().to_json());

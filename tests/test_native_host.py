@@ -29,6 +29,8 @@ def _sanitizer_run(target):
     assert res.returncode == 0, out[-4000:]
     assert "stress_host: 0 failure(s)" in out
     assert "WARNING: ThreadSanitizer" not in out and "ERROR: AddressSanitizer" not in out and "runtime error" not in out
+    if target == "asan":
+        assert "no crash" in out      # the parser fuzzing ran to its end
 
 
 def test_thread_sanitizer_stress():
