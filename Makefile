@@ -101,9 +101,15 @@ build/san/fuzz_value: csrc/tests/fuzz_value.cc csrc/common/value.cc csrc/common/
 	@mkdir -p build/san
 	$(SAN_CXX) $(SAN_FLAGS) -fsanitize=address,undefined -fno-sanitize-recover=undefined -o $@ csrc/tests/fuzz_value.cc csrc/common/value.cc csrc/common/log.cc csrc/daemon/config.cc $(LDLIBS)
 
-asan: build/san/stress_asan build/san/fuzz_value
+SAN_FUZZP_SRCS := $(sort $(HOST_SRCS) $(SHIM_SRCS)) csrc/tests/no_cuda_backend.cc csrc/tests/fuzz_protocol.cc
+build/san/fuzz_protocol: $(SAN_FUZZP_SRCS) $(HDRS)
+	@mkdir -p build/san
+	$(SAN_CXX) $(SAN_FLAGS) -fsanitize=address,undefined -fno-sanitize-recover=undefined -o $@ $(SAN_FUZZP_SRCS) $(LDLIBS)
+
+asan: build/san/stress_asan build/san/fuzz_value build/san/fuzz_protocol
 	ASAN_OPTIONS="detect_leaks=1" build/san/stress_asan 40
 	build/san/fuzz_value 40000
+	ASAN_OPTIONS="detect_leaks=1" build/san/fuzz_protocol 3000
 
 clean:
 	rm -rf build $(OUT)/*.so $(OUT)/mccsd $(APP_BINS) $(OUT)/host_tests

@@ -84,6 +84,8 @@ int Daemon::start(const Config& cfg, std::string* err) {
     }
   }
 
+  extern void proxy_tracing_init();
+  proxy_tracing_init();
   runtimes_.reset(new RuntimeManager(cfg.idle_sleep_us, cfg.idle_spin_us, cfg.pin_threads));
   for (int d = 0; d < backend_->device_count(); d++) {
     auto p = std::make_shared<ProxyEngine>(this, d);
@@ -218,6 +220,7 @@ void Daemon::reply(Session& s, proto::AnyMsg& m, size_t len, const int* fds, int
 
 void Daemon::handle_session(Session& s) {
   proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
   ssize_t n = ipc::uds_recv(s.fd, &m, sizeof m);
   if (n == -EAGAIN) return;
   if (n <= 0) { drop_session(s.id, n == 0 ? "client closed the connection" : "receive error"); return; }
@@ -225,6 +228,19 @@ void Daemon::handle_session(Session& s) {
     drop_session(s.id, "malformed message");
     return;
   }
+  // A request shorter than its type's layout is answered as a protocol error (the
+  // missing fields were zeroed above, nothing reads past what arrived).
+  size_t need = sizeof(proto::Header);
+  switch (m.h.type) {
+    case proto::kMalloc: need = sizeof(proto::MallocReq); break;
+    case proto::kFree: need = sizeof(proto::FreeReq); break;
+    case proto::kCommInit: need = sizeof(proto::CommInitReq); break;
+    case proto::kCommDestroy: need = sizeof(proto::CommDestroyReq); break;
+    case proto::kRegisterStream: need = sizeof(proto::RegisterStreamReq); break;
+    case proto::kCommQuery: need = sizeof(proto::CommQueryReq); break;
+    default: break;
+  }
+  if ((size_t)n < need) m.h.type = 0;   // falls into the protocol-error reply below
   switch (m.h.type) {
     case proto::kMalloc: on_malloc(s, m.malloc_req); break;
     case proto::kFree: on_free(s, m.free_req); break;

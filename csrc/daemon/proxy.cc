@@ -34,6 +34,14 @@ struct NvtxRange {
 };
 }  // namespace
 
+// NVTX fills its function table on first use, from whichever thread gets there first and
+// without synchronisation; doing it once before the proxy threads exist keeps that
+// initialisation single-threaded.
+void proxy_tracing_init() {
+  nvtxRangePushA("mccs init");
+  nvtxRangePop();
+}
+
 void ProxyEngine::on_start() {
   daemon_->backend()->set_device(device_);
   started_.store(true);
@@ -144,6 +152,8 @@ bool ProxyEngine::post(RankState& rs, const proto::WorkRequest& wr) {
   else if (op.kind == kAllReduce && (op.dtype < 0 || op.dtype >= kNumDataTypes || op.op < 0 || op.op >= kNumRedOps))
     status = proto::kErrInvalidArgument;
   else if (op.variant_req < 0 || op.variant_req >= kNumVariants) status = proto::kErrInvalidArgument;
+  // Sizes come from another process: keep count * element size * ranks far from wrapping.
+  else if (op.count > (1ull << 44)) status = proto::kErrInvalidArgument;
   if (status == proto::kOk) {
     const uint64_t esz = op.kind == kAllReduce ? (uint64_t)dtype_size(op.dtype) : 1;
     const uint64_t send_bytes = op.count * esz;
@@ -153,6 +163,10 @@ bool ProxyEngine::post(RankState& rs, const proto::WorkRequest& wr) {
         !daemon_->translate(op.recv_mem, op.recv_off, recv_bytes, &op.recv_va, &rdev))
       status = proto::kErrNotFound;
     else if (sdev != rs.device || rdev != rs.device)
+      status = proto::kErrInvalidArgument;
+    // Elements must be naturally aligned: the kernels load and store whole elements, and
+    // a misaligned access is a device fault, not an error code.
+    else if (((op.send_va | op.recv_va) & (esz - 1)) != 0)
       status = proto::kErrInvalidArgument;
   }
   op.user_event = daemon_->lookup_stream_event(rs.session_id, wr.stream_id);

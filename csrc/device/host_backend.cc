@@ -113,6 +113,7 @@ void cpu_allreduce(const CollArgs& a) {
   using Acc = typename C::Acc;
   constexpr bool is_float = std::is_floating_point<Acc>::value;
   const int n = a.nranks;
+  if (a.count == 0) return;
   // Results go through a temporary so that in-place calls (recv aliasing send) work.
   std::vector<uint8_t> tmp((size_t)a.count * ESZ);
   long long imul = llrintf(a.scale);
@@ -145,6 +146,7 @@ void cpu_allreduce(const CollArgs& a) {
 
 void cpu_allgather(const CollArgs& a) {
   const int n = a.nranks;
+  if (a.count == 0) return;
   std::vector<uint8_t> tmp((size_t)a.count * n);
   for (int r = 0; r < n; r++) memcpy(tmp.data() + (size_t)r * a.count, a.send[r], a.count);
   for (int r = 0; r < n; r++) memcpy(a.recv[r], tmp.data(), tmp.size());

@@ -922,6 +922,12 @@ mccsResult_t mccsAllReduceEx(mccsComm_t comm, const void* send, void* recv, size
                              mccsRedOp_t op, float scale, mccsAlgo_t algo, mccsStream_t stream) {
   if (!comm || (int)dtype < 0 || (int)dtype >= kNumDataTypes || (int)op < 0 || (int)op >= kNumRedOps)
     return mccsInvalidArgument;
+  const uint64_t esz = (uint64_t)dtype_size((int)dtype);
+  if ((((uint64_t)send | (uint64_t)recv) & (esz - 1)) != 0 || count > (1ull << 44)) {
+    LOG_ERROR("all-reduce buffers must be aligned to the element size (send %p, recv %p, %llu-byte elements)", send, recv,
+              (unsigned long long)esz);
+    return mccsInvalidArgument;
+  }
   proto::WorkRequest wr;
   memset(&wr, 0, sizeof wr);
   wr.kind = kAllReduce;
@@ -930,7 +936,7 @@ mccsResult_t mccsAllReduceEx(mccsComm_t comm, const void* send, void* recv, size
   wr.count = count;
   wr.scale = scale;
   wr.variant = (uint32_t)algo;
-  const uint64_t bytes = (uint64_t)count * (uint64_t)dtype_size((int)dtype);
+  const uint64_t bytes = (uint64_t)count * esz;
   return submit(comm, wr, send, recv, bytes, bytes, stream);
 }
 

@@ -1,0 +1,210 @@
+// A hostile tenant: speaks the control protocol and the shared-memory request ring with
+// random, truncated and out-of-range contents against an in-process daemon (host
+// backend), under AddressSanitizer (`make asan`). A tenant is another user's process, so
+// nothing it sends may crash the daemon, make it touch memory outside the tenant's own
+// allocations, or disturb a well-behaved tenant, which is checked at the end.
+//
+// The reference trusts its clients: most of its error paths are unwrap()/panic!
+// (src/mccs/src/daemon/engine.rs:86-99,263).
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <unistd.h>
+
+#include <random>
+#include <string>
+#include <vector>
+
+#include "../common/protocol.h"
+#include "../daemon/daemon.h"
+#include "../include/mccs.h"
+#include "../ipc/shm_ring.h"
+#include "../ipc/uds.h"
+
+using namespace mccs;
+
+namespace {
+
+std::mt19937_64 rng(987654321);
+
+int connect_and_hello(const std::string& path) {
+  int fd = ipc::uds_connect(path);
+  if (fd < 0) return fd;
+  proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
+  m.h.magic = proto::kMagic;
+  m.h.type = proto::kHello;
+  m.hello.version = proto::kVersion;
+  m.hello.pid = 1;   // claims to be someone else: the daemon goes by the socket's credentials
+  m.hello.device_affinity = -1;
+  snprintf(m.hello.app_name, sizeof m.hello.app_name, "fuzzer");
+  ipc::uds_send(fd, &m, sizeof(proto::Hello));
+  if (ipc::wait_readable(fd, 2000) <= 0) { close(fd); return -1; }
+  ipc::uds_recv(fd, &m, sizeof m);
+  return fd;
+}
+
+// Drains whatever the daemon answered; closes passed descriptors.
+void drain(int fd, std::vector<int>* keep_fds = nullptr, proto::AnyMsg* last = nullptr) {
+  while (ipc::wait_readable(fd, 3) > 0) {
+    proto::AnyMsg r;
+    std::vector<int> fds;
+    ssize_t n = ipc::uds_recv(fd, &r, sizeof r, &fds);
+    if (n <= 0) break;
+    if (last) *last = r;
+    for (int f : fds) {
+      if (keep_fds) keep_fds->push_back(f);
+      else close(f);
+    }
+  }
+}
+
+uint64_t wild_u64() {
+  switch (rng() % 6) {
+    case 0: return 0;
+    case 1: return ~0ull;
+    case 2: return 1ull << 63;
+    case 3: return rng() % 64;
+    case 4: return (1ull << (rng() % 64)) - (rng() % 3);
+    default: return rng();
+  }
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  const int rounds = argc > 1 ? atoi(argv[1]) : 3000;
+  const std::string prefix = "/tmp/mccs-fuzz-" + std::to_string((long)getpid());
+  const std::string cfg = "listen_port = 0\nmccs_daemon_prefix = \"" + prefix + "\"\n[control]\nprefix = \"" + prefix +
+                          "\"\npath = \"control.sock\"\n[comm_default_config]\nbuffer_sizes = [65536]\nchannel_count = 2\n"
+                          "[b200]\nforce_host_backend = true\nhost_devices = 2\nwait_timeout_ms = 2000\ninit_timeout_ms = 300\n";
+  setenv("MCCS_LOG", "error", 0);
+  if (mccsd_start(cfg.c_str()) != 0) { fprintf(stderr, "daemon did not start\n"); return 2; }
+  const std::string path = mccsd_control_path();
+
+  // 1. control messages: every type, random length, random fields
+  int fd = connect_and_hello(path);
+  if (fd < 0) { fprintf(stderr, "cannot connect\n"); return 2; }
+  for (int i = 0; i < rounds; i++) {
+    proto::AnyMsg m;
+    for (size_t k = 0; k < sizeof m.raw; k++) m.raw[k] = (uint8_t)rng();
+    m.h.magic = (rng() % 50 == 0) ? (uint32_t)rng() : proto::kMagic;
+    m.h.type = (rng() % 10 == 0) ? (uint32_t)rng() : (uint32_t)(rng() % 24);
+    switch (m.h.type) {
+      case proto::kMalloc: m.malloc_req.device = (int32_t)(rng() % 5) - 1; m.malloc_req.size = (rng() % 3) ? 4096 * (1 + rng() % 4) : wild_u64(); break;
+      case proto::kFree: m.free_req.mem_id = rng() % 40; break;
+      case proto::kCommInit:
+        m.comm_init.comm_id = 9000 + (uint32_t)(rng() % 4);
+        m.comm_init.nranks = (int32_t)(rng() % 12) - 1;
+        m.comm_init.rank = (int32_t)(rng() % 12) - 1;
+        m.comm_init.device = (int32_t)(rng() % 5) - 1;
+        break;
+      case proto::kCommDestroy: m.comm_destroy.comm_handle = ((uint64_t)(9000 + rng() % 4) << 32) + rng() % 3; break;
+      case proto::kCommQuery: m.comm_query.comm_handle = (rng() % 2) ? wild_u64() : ((uint64_t)(9000 + rng() % 4) << 32) + rng() % 3; break;
+      default: break;
+    }
+    const size_t len = (rng() % 4 == 0) ? rng() % (sizeof m + 1) : sizeof m;
+    if (ipc::uds_send(fd, &m, len) < 0) {
+      // the daemon hung up on us (malformed frame): that is its right; come back
+      close(fd);
+      fd = connect_and_hello(path);
+      if (fd < 0) { fprintf(stderr, "daemon no longer accepts connections\n"); return 1; }
+      continue;
+    }
+    drain(fd);
+  }
+  close(fd);
+
+  // 2. data path: a real single-rank communicator, then garbage in its request ring
+  fd = connect_and_hello(path);
+  proto::AnyMsg m;
+  memset(&m, 0, sizeof m);
+  m.h.magic = proto::kMagic;
+  m.h.type = proto::kMalloc;
+  m.malloc_req.device = 0;
+  m.malloc_req.size = 65536;
+  ipc::uds_send(fd, &m, sizeof(proto::MallocReq));
+  proto::AnyMsg rep;
+  memset(&rep, 0, sizeof rep);
+  std::vector<int> fds;
+  ipc::wait_readable(fd, 2000);
+  ipc::uds_recv(fd, &rep, sizeof rep, &fds);
+  const uint64_t mem_id = rep.malloc_reply.mem_id;
+  for (int f : fds) close(f);
+  fds.clear();
+  memset(&m, 0, sizeof m);
+  m.h.magic = proto::kMagic;
+  m.h.type = proto::kCommInit;
+  m.comm_init.comm_id = 9100;
+  m.comm_init.nranks = 1;
+  m.comm_init.rank = 0;
+  m.comm_init.device = 0;
+  ipc::uds_send(fd, &m, sizeof(proto::CommInitReq));
+  ipc::wait_readable(fd, 2000);
+  ipc::uds_recv(fd, &rep, sizeof rep, &fds);
+  if (rep.h.status != 0 || fds.empty()) { fprintf(stderr, "single-rank communicator refused (%d)\n", rep.h.status); return 1; }
+  const size_t dp_bytes = rep.comm_init_reply.dp_bytes;
+  void* dp = mmap(nullptr, dp_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
+  for (int f : fds) close(f);
+  if (dp == MAP_FAILED) { fprintf(stderr, "cannot map the data-path segment\n"); return 1; }
+  ipc::Ring wq, cq;
+  wq.attach(dp);
+  cq.attach((char*)dp + proto::dp_wq_bytes());
+  long posted = 0, answered = 0;
+  for (int i = 0; i < rounds; i++) {
+    proto::WorkRequest wr;
+    uint8_t* raw = (uint8_t*)&wr;
+    for (size_t k = 0; k < sizeof wr; k++) raw[k] = (uint8_t)rng();
+    wr.kind = (uint32_t)(rng() % 4);
+    wr.dtype = (uint32_t)(rng() % 12);
+    wr.op = (uint32_t)(rng() % 8);
+    wr.variant = (uint32_t)(rng() % 14);
+    wr.comm_handle = rep.comm_init_reply.comm_handle;
+    wr.send_mem = (rng() % 4) ? mem_id : wild_u64();
+    wr.recv_mem = (rng() % 4) ? mem_id : wild_u64();
+    wr.send_off = (rng() % 2) ? rng() % 70000 : wild_u64();
+    wr.recv_off = (rng() % 2) ? rng() % 70000 : wild_u64();
+    wr.count = (rng() % 2) ? rng() % 20000 : wild_u64();
+    wr.sync_slot = 0;   // the host backend has no semaphore page; events are not used either
+    wr.stream_id = rng() % 3;
+    wr.user_seq = (uint64_t)i;
+    while (!wq.try_push(&wr)) {
+      proto::WorkCompletion wc;
+      while (cq.try_pop(&wc)) answered++;
+      usleep(50);
+    }
+    posted++;
+    proto::WorkCompletion wc;
+    while (cq.try_pop(&wc)) answered++;
+  }
+  for (int spin = 0; spin < 20000 && answered < posted; spin++) {
+    proto::WorkCompletion wc;
+    while (cq.try_pop(&wc)) answered++;
+    usleep(100);
+  }
+  munmap(dp, dp_bytes);
+  close(fd);   // no goodbye: the daemon cleans up after us
+  if (answered != posted) { fprintf(stderr, "only %ld of %ld requests were answered\n", answered, posted); return 1; }
+
+  // 3. a well-behaved tenant still gets service
+  setenv("MCCS_CONTROL", path.c_str(), 1);
+  int bad = 0;
+  float* buf = nullptr;
+  mccsComm_t comm = nullptr;
+  bad += mccsInit(nullptr) != mccsSuccess;
+  bad += mccsMalloc((void**)&buf, 0, 4096) != mccsSuccess;
+  bad += mccsCommInitRank(&comm, 9200, 0, 1, 0, nullptr) != mccsSuccess;
+  if (buf && comm) {
+    for (int i = 0; i < 1024; i++) buf[i] = (float)i;
+    bad += mccsAllReduce(comm, buf, buf, 1024, mccsFloat32, mccsSum, nullptr) != mccsSuccess;
+    bad += buf[1023] != 1023.0f;
+    bad += mccsCommDestroy(comm) != mccsSuccess;
+    bad += mccsFree(buf) != mccsSuccess;
+  }
+  mccsFinalize();
+  mccsd_stop();
+  printf("fuzz_protocol: %d control frames, %ld ring requests answered, good tenant %s\n", rounds, answered,
+         bad ? "FAILED" : "served");
+  return bad ? 1 : 0;
+}
