@@ -111,8 +111,43 @@ asan: build/san/stress_asan build/san/fuzz_value build/san/fuzz_protocol
 	build/san/fuzz_value 40000
 	ASAN_OPTIONS="detect_leaks=1" build/san/fuzz_protocol 3000
 
+# ---------------------------------------------------------------------------------------
+# Evaluation recipes, one per figure of the reference's justfile (its `four_gpu_*`,
+# `batched-allreduce-multi-final`, `run-dynamic` / `reconfig-ring`, `collect-setup4-*`
+# recipes). They need the GPUs of one box; OUT collects the results.
+# ---------------------------------------------------------------------------------------
+NGPU ?= 8
+OUT_DIR ?= out
+PY ?= python
+TORCHRUN = $(PY) -m torch.distributed.run --nnodes=1 --nproc-per-node $(NGPU) --master-addr 127.0.0.1
+
+eval-single: all        # bandwidth vs. size for every variant, next to NCCL; table with roofline fractions
+	@mkdir -p $(OUT_DIR)
+	$(TORCHRUN) --master-port 29601 -m mccs_b200.utils.sweep --mode final --out $(OUT_DIR)/sweep_$(NGPU).csv
+	$(PY) -m mccs_b200.utils.report $(OUT_DIR)/sweep_$(NGPU).csv > $(OUT_DIR)/sweep_$(NGPU).md
+
+eval-tune: all          # measures a tuning table and merges it into configs/tuning_b200.json
+	@mkdir -p $(OUT_DIR)
+	$(TORCHRUN) --master-port 29602 -m mccs_b200.utils.sweep --mode tune --dtypes bf16 --out $(OUT_DIR)/tune_$(NGPU).csv \
+	    --tuning $(OUT_DIR)/tuning_$(NGPU).json --merge-into configs/tuning_b200.json
+
+eval-multi: all         # four co-located tenants under QoS weights, then the same as independent NCCL groups
+	@mkdir -p $(OUT_DIR)
+	$(PY) -m mccs_b200.utils.multi_tenant --iters 1000 > $(OUT_DIR)/multi_mccs.json
+	$(PY) -m mccs_b200.utils.multi_tenant --iters 1000 --backend nccl > $(OUT_DIR)/multi_nccl.json
+
+eval-dynamic: all       # a running job whose ring is reversed by the admin tool
+	$(PY) -m mccs_b200.utils.launcher --benchmark configs/launch/reconfig.toml --output-dir $(OUT_DIR)
+
+eval-colocate: all      # ResNet-50 and VGG-16 data-parallel jobs side by side; GPT-2-medium with a ResNet-50 neighbour
+	$(PY) -m mccs_b200.utils.launcher --benchmark configs/launch/colocate_cnn.toml --output-dir $(OUT_DIR)
+	$(PY) -m mccs_b200.utils.launcher --benchmark configs/launch/gpt2_with_resnet.toml --output-dir $(OUT_DIR)
+
+eval-latency: all       # where the time of a small collective goes
+	$(TORCHRUN) --master-port 29603 -m mccs_b200.utils.latency --bytes 64K
+
 clean:
 	rm -rf build $(OUT)/*.so $(OUT)/mccsd $(APP_BINS) $(OUT)/host_tests
 
-.PHONY: all clean tsan asan
+.PHONY: all clean tsan asan eval-single eval-tune eval-multi eval-dynamic eval-colocate eval-latency
 .SECONDARY:
