@@ -438,3 +438,56 @@ def test_consecutive_allreduces_share_one_launch(tmp_path):
         assert launches >= 1 and 2 * launches <= members <= 8 * launches, fused
     finally:
         sp.stop()
+
+
+# ---------------------------------------------------------------------------------------------
+# LD_PRELOAD allocation hook, against a stand-in CUDA runtime (no GPU needed)
+# ---------------------------------------------------------------------------------------------
+FAKE_CUDART = r"""
+#include <stdlib.h>
+int cudaMalloc(void** p, size_t n) { *p = malloc(n); return *p ? 0 : 2; }
+int cudaFree(void* p) { free(p); return 0; }
+int cudaGetDevice(int* d) { *d = 1; return 0; }
+"""
+
+PRELOAD_APP = r"""
+#include <dlfcn.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+int cudaMalloc(void**, size_t);
+int cudaFree(void*);
+typedef int (*meminfo_fn)(const void*, uint64_t*, uint64_t*, uint64_t*);
+int main(void) {
+  void *big = 0, *small = 0;
+  if (cudaMalloc(&big, 2u << 20) || cudaMalloc(&small, 1024)) return 2;
+  memset(big, 7, 2u << 20);                      /* service memory is ordinary shared memory on the host backend */
+  meminfo_fn info = (meminfo_fn)dlsym(RTLD_DEFAULT, "mccsMemInfo");
+  if (!info) return 3;
+  uint64_t id = 0, off = 0, size = 0;
+  int big_ours = info(big, &id, &off, &size) == 0;
+  int small_ours = info(small, 0, 0, 0) == 0;
+  printf("big_ours=%d size=%llu small_ours=%d\n", big_ours, (unsigned long long)size, small_ours);
+  if (cudaFree(big) || cudaFree(small)) return 4;
+  printf("big_after_free=%d\n", info(big, 0, 0, 0) == 0);
+  return 0;
+}
+"""
+
+
+def test_preload_hook_routes_large_allocations_to_the_service(private_daemon, tmp_path):
+    from helpers import NATIVE
+    (tmp_path / "fake_cudart.c").write_text(FAKE_CUDART)
+    (tmp_path / "app.c").write_text(PRELOAD_APP)
+    subprocess.run(["gcc", "-shared", "-fPIC", "-o", str(tmp_path / "libfakecudart.so"), str(tmp_path / "fake_cudart.c")],
+                   check=True)
+    subprocess.run(["gcc", "-o", str(tmp_path / "app"), str(tmp_path / "app.c"), "-L" + str(tmp_path), "-lfakecudart",
+                    "-ldl", "-Wl,-rpath," + str(tmp_path)], check=True)
+    env = dict(os.environ, LD_PRELOAD=os.path.join(NATIVE, "libmccs_preload.so"), MCCS_CONTROL=private_daemon.control,
+               MCCS_PRELOAD_MIN_BYTES=str(1 << 20), MCCS_LOG="error")
+    res = subprocess.run([str(tmp_path / "app")], env=env, capture_output=True, text=True, timeout=60)
+    assert res.returncode == 0, res.stdout + res.stderr
+    # the 2 MiB request came from the service (device 1, as the runtime reported), the 1 KiB one did not
+    assert "big_ours=1" in res.stdout and "small_ours=0" in res.stdout and "big_after_free=0" in res.stdout
+    size = int(res.stdout.split("size=")[1].split()[0])
+    assert size >= 2 << 20
