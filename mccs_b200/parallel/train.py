@@ -44,6 +44,10 @@ def main() -> int:
     ap.add_argument("--devices", default="", help="comma separated GPU index per rank (default: local rank)")
     ap.add_argument("--name", default="")
     ap.add_argument("--lr", type=float, default=0.01)
+    ap.add_argument("--comm-ctas", type=int, default=0,
+                    help="cap the CTAs of this job's collective kernels (a QoS quota set through the admin "
+                         "endpoint), leaving the other SMs to backward; 0 = the planner's choice")
+    ap.add_argument("--admin-port", type=int, default=0, help="admin port of a daemon that is already running")
     ap.add_argument("--save", default="", help="after the run rank 0 writes model + optimizer state here (torch.save)")
     ap.add_argument("--resume", default="", help="load model + optimizer state written by --save before training")
     args = ap.parse_args()
@@ -94,6 +98,12 @@ def main() -> int:
             with open(prefix + "/mccs.toml", "w") as f:
                 f.write(M.daemon.default_config(prefix, listen_port=-1))
             spawned = M.daemon.spawn(prefix + "/mccs.toml")
+        admin_port = spawned.admin_port if spawned is not None else args.admin_port
+        if args.comm_ctas > 0 and local_rank == 0:
+            if not admin_port:
+                raise SystemExit("--comm-ctas needs --start-daemon or --admin-port")
+            rep = M.admin_request(admin_port, {"cmd": "qos_set", "tenants": {str(args.comm_id): {"weight": 1.0, "cta_quota": args.comm_ctas}}})
+            assert rep.get("status") == "ok", rep
         barrier()
         if args.start_daemon or args.control:
             M.init(prefix + "/control.sock" if not prefix.endswith(".sock") else prefix)
