@@ -183,9 +183,21 @@ int main(int argc, char** argv) {
     while (cq.try_pop(&wc)) answered++;
     usleep(100);
   }
+  const bool all_answered = answered == posted;
+  // The segment is writable by the tenant: scribble over the ring headers (geometry and
+  // both indices) while the proxy keeps polling them. Whatever it makes of the contents,
+  // it must stay inside the segment.
+  for (int i = 0; i < 200; i++) {
+    ipc::RingHeader* h = (ipc::RingHeader*)((rng() % 2) ? dp : (void*)((char*)dp + proto::dp_wq_bytes()));
+    h->depth = (uint32_t)wild_u64();
+    h->slot_bytes = (uint32_t)wild_u64();
+    h->tail.store(wild_u64());
+    if (rng() % 3 == 0) h->head.store(wild_u64());
+    usleep(200);
+  }
   munmap(dp, dp_bytes);
   close(fd);   // no goodbye: the daemon cleans up after us
-  if (answered != posted) { fprintf(stderr, "only %ld of %ld requests were answered\n", answered, posted); return 1; }
+  if (!all_answered) { fprintf(stderr, "only %ld of %ld requests were answered\n", answered, posted); return 1; }
 
   // 3. a well-behaved tenant still gets service
   setenv("MCCS_CONTROL", path.c_str(), 1);
