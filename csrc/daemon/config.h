@@ -86,6 +86,11 @@ struct Config {
   // Fused launches: up to this many consecutive AllReduces of a communicator (same type and
   // operator, all queued when the first is planned) share one kernel; 1 = off.
   int fuse_allreduce = 1;
+  // Experiments on the per-call floor; they act on launches that go through the fused
+  // kernels only (kernels/batch.cuh) and are all off by default.
+  bool single_through_fused = false;  // a lone two-shot AllReduce also uses the fused kernel (one member)
+  bool skip_start_barrier = false;    // no barrier before the first load when the host has gated every rank
+  bool kernel_writes_done = false;    // the kernel's last CTA releases the caller's stream itself
 
   std::string control_socket_path() const;   // expanded prefix/path
   const CommPattern* find_override(uint32_t comm_id) const;

@@ -106,6 +106,7 @@ struct CollSlot {
   // batch_len - 1 slots) in one kernel; a follower slot has batch_len == 0 and launches
   // nothing of its own. Written by the planning proxy before the slot becomes "planned".
   int batch_len = 1;
+  bool fused_kernel = false;           // head: launched through the fused kernel (always when batch_len > 1)
   uint64_t batch_bytes = 0;            // head: bytes of all members together (admission)
 };
 

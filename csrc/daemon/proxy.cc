@@ -218,6 +218,7 @@ int ProxyEngine::ensure_mc(Communicator& c, CollSlot& s, bool for_recv, uint64_t
 
 bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   s.batch_len = 1;
+  s.fused_kernel = false;
   s.batch_bytes = 0;
   auto fail = [&](int status) {
     s.status = status;
@@ -422,7 +423,8 @@ bool ProxyEngine::plan_member(Communicator& c, CollSlot& head, CollSlot& m, cons
 
 void ProxyEngine::extend_batch(Communicator& c, CollSlot& head, uint64_t seq, const PlanInput& head_in, uint64_t now) {
   const int limit = std::min(daemon_->config().fuse_allreduce, kMaxBatch);
-  if (limit <= 1) return;
+  const bool single = daemon_->config().single_through_fused;
+  if (limit <= 1 && !single) return;
   Backend* be = daemon_->backend();
   const CollOp& h0 = head.ops[0];
   if (h0.kind != kAllReduce || head.nslices != 1) return;
@@ -466,9 +468,10 @@ void ProxyEngine::extend_batch(Communicator& c, CollSlot& head, uint64_t seq, co
     m.state.store(kSlotPlanned, std::memory_order_release);
     len++;
   }
-  if (len == 1) return;
+  if (len == 1 && !single) return;
   head.plan.dims.ctas = std::min(ctas, fit);
   head.batch_len = len;
+  head.fused_kernel = true;
   head.batch_bytes = bytes;
   c.fused_launches.fetch_add(1);
   c.fused_members.fetch_add((uint64_t)len);
@@ -488,6 +491,26 @@ void ProxyEngine::fill_batch_args(Communicator& c, CollSlot& head, uint64_t seq,
     }
     if (head.plan.needs_mc_send) b.mc_send[k] = (const void*)(m.mc_send[rank] + m.ops[rank].send_off);
     if (head.plan.needs_mc_recv) b.mc_recv[k] = (void*)(m.mc_recv[rank] + m.ops[rank].recv_off);
+  }
+  const Config& cfg = daemon_->config();
+  // Is every rank's launch held back by the host until all clients have arrived? Only
+  // then do all inputs exist (and may all outputs be overwritten) when a kernel starts.
+  bool all_gated = true;
+  for (int k = 0; k < head.batch_len; k++) {
+    CollSlot& m = k == 0 ? head : c.slot(seq + (uint64_t)k);
+    for (int r = 0; r < c.nranks; r++) all_gated &= c.ranks[(size_t)r]->sync.host != nullptr && m.ops[r].sync_slot != 0;
+  }
+  if (cfg.skip_start_barrier && all_gated) b.flags |= kBatchSkipStartBarrier;
+  if (cfg.kernel_writes_done && !c.host_staged) {
+    const bool group = c.emulated || daemon_->backend()->kind() == proto::kBackendHost;
+    for (int r = 0; r < c.nranks; r++) {
+      if (!group && r != rank) continue;
+      RankState& rr = *c.ranks[(size_t)r];
+      if (!rr.sync.host || !head.ops[r].sync_slot || !rr.pad) continue;
+      b.done_ptr[r] = (uint64_t*)(rr.sync.dev_addr + 8 * proto::kSyncDoneSlot);
+      b.done_value[r] = last_member_user_seq(c, head, seq, r);
+      b.done_counter[r] = &rr.pad->pad_[0];
+    }
   }
 }
 
@@ -560,7 +583,7 @@ bool ProxyEngine::launch_slices(RankState& rs, CollSlot& s, uint64_t seq) {
   Communicator& c = *rs.comm;
   Backend* be = daemon_->backend();
   const CollOp& op = s.ops[rs.rank];
-  if (s.batch_len > 1) {
+  if (s.fused_kernel) {
     // One kernel for this slot and its followers.
     if (!admit_slice(c, s, 0)) return false;
     for (int k = 0; k < s.batch_len; k++)
@@ -657,7 +680,7 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
   (void)seq;
   RankState& r0 = *c.ranks[0];
   Backend* be = daemon_->backend();
-  if (s.batch_len > 1) {
+  if (s.fused_kernel) {
     if (!admit_slice(c, s, 0)) return false;
     for (int k = 0; k < s.batch_len; k++) {
       CollSlot& m = k == 0 ? s : c.slot(seq + (uint64_t)k);

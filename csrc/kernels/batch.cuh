@@ -18,6 +18,27 @@
 namespace mccs {
 namespace dev {
 
+// Start of a fused launch: the cross-rank barrier, unless the host vouches for it.
+__device__ __forceinline__ bool batch_begin(const BatchArgs& b, int rank) {
+  trace_begin(b.base, rank);
+  if (b.flags & kBatchSkipStartBarrier) return true;
+  return rank_barrier<false>(b.base, rank, b.base.epoch, kDevTimeoutStart);
+}
+
+// End of a fused launch, after this CTA's closing barrier: bookkeeping for the daemon,
+// and, if asked for, the caller's completion word once ALL CTAs of this rank are through
+// (every CTA's barrier only covers the CTAs with its own index on the peers).
+__device__ __forceinline__ void batch_end(const BatchArgs& b, int rank) {
+  finish(b.base, rank);
+  if (b.done_ptr[rank] == nullptr) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fence_sys();
+    const unsigned last = gridDim.x - 1;
+    if (atomicInc(b.done_counter[rank], last) == last) st_release_sys_u64(b.done_ptr[rank], b.done_value[rank]);
+  }
+}
+
 __device__ __forceinline__ bool batch_aligned16(const BatchArgs& b, int k) {
   uint64_t bits = 0;
   for (int r = 0; r < b.base.nranks; r++) bits |= (uint64_t)b.send[k][r] | (uint64_t)b.recv[k][r];
@@ -51,8 +72,7 @@ __global__ void __launch_bounds__(kMaxThreads) ar_twoshot_batch_kernel(const __g
   const int rank = a.emulated ? (int)blockIdx.y : a.rank;
   __shared__ const char* s_src[kMaxRanks];
   __shared__ char* s_dst[kMaxRanks];
-  trace_begin(a, rank);
-  if (!rank_barrier<false>(a, rank, a.epoch, kDevTimeoutStart)) return;
+  if (!batch_begin(b, rank)) return;
 
 #pragma unroll 1
   for (int k = 0; k < b.nops; k++) {
@@ -64,8 +84,8 @@ __global__ void __launch_bounds__(kMaxThreads) ar_twoshot_batch_kernel(const __g
     __syncthreads();
     twoshot_member<T, Op>(s_src, s_dst, b.count[k], batch_aligned16(b, k), rank, a.nranks, a.op, a.scale);
   }
-  rank_barrier<true>(a, rank, a.epoch + 1, kDevTimeoutEnd);
-  finish(a, rank);
+  if (!rank_barrier<true>(a, rank, a.epoch + 1, kDevTimeoutEnd)) return;
+  batch_end(b, rank);
 }
 
 // Same, with the sum done by the switch (`multimem.ld_reduce`) and the broadcast by
@@ -79,8 +99,7 @@ __global__ void __launch_bounds__(kMaxThreads) ar_nvls_batch_kernel(const __grid
   using Acc = typename P::Acc;
   __shared__ const char* s_src[kMaxRanks];
   __shared__ char* s_dst[kMaxRanks];
-  trace_begin(a, rank);
-  if (!rank_barrier<false>(a, rank, a.epoch, kDevTimeoutStart)) return;
+  if (!batch_begin(b, rank)) return;
 
   Scaler<Acc> sc{scaler_mode(a.op), a.scale};
   constexpr int kN = P::kN;
@@ -124,8 +143,8 @@ __global__ void __launch_bounds__(kMaxThreads) ar_nvls_batch_kernel(const __grid
                                                blockIdx.x, gridDim.x, sc);
     }
   }
-  rank_barrier<true>(a, rank, a.epoch + 1, kDevTimeoutEnd);
-  finish(a, rank);
+  if (!rank_barrier<true>(a, rank, a.epoch + 1, kDevTimeoutEnd)) return;
+  batch_end(b, rank);
 }
 
 }  // namespace dev

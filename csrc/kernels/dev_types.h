@@ -124,10 +124,22 @@ struct CollArgs {
 // src/collectives/include/devcomm.h:66,103-104). `base` gives everything that is per
 // launch (identity, op, epoch, pads, status); its own send/recv/count are unused.
 constexpr int kMaxBatch = 8;
+enum BatchFlags : uint32_t {
+  // Every rank's launch was held back by the host until all ranks' inputs existed and all
+  // outputs could be overwritten, so the kernel needs no barrier before its first load.
+  kBatchSkipStartBarrier = 1u << 0,
+};
 struct BatchArgs {
   CollArgs base;
   int32_t nops;
-  int32_t pad0_;
+  uint32_t flags;                            // BatchFlags
+  // Optional completion word for the caller: the last CTA of this rank to finish stores
+  // `done_value` to `done_ptr` (null = nobody is told from inside the kernel).
+  // `done_counter` is a word in this rank's device memory that counts finished CTAs and
+  // wraps to zero at gridDim.x, so it needs no reset between launches.
+  uint64_t* done_ptr[kMaxRanks];
+  uint64_t done_value[kMaxRanks];
+  uint32_t* done_counter[kMaxRanks];
   uint64_t count[kMaxBatch];                 // elements of each member
   const void* send[kMaxBatch][kMaxRanks];
   void* recv[kMaxBatch][kMaxRanks];

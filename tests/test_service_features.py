@@ -417,7 +417,8 @@ def test_consecutive_allreduces_share_one_launch(tmp_path):
     import mccs_b200 as M
     d = str(tmp_path)
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=-1,
-                       force_host=True, extra="fuse_allreduce = 8")
+                       force_host=True,
+                       extra="fuse_allreduce = 8\nsingle_through_fused = true\nskip_start_barrier = true\nkernel_writes_done = true")
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
     try:
         n = 4
@@ -433,9 +434,10 @@ def test_consecutive_allreduces_share_one_launch(tmp_path):
             assert res["ok"] and res["async_error"] == 0
             assert res["launched"] == 3 * 17 + 4
             fused.append((res["fused_launches"], res["fused_members"]))
-        # every fused launch carries 2..8 members, and the bursts did get fused
+        # every fused launch carries 1..8 members (lone two-shot AllReduces also take the fused
+        # kernel in this configuration), and the bursts did get fused
         launches, members = max(fused)
-        assert launches >= 1 and 2 * launches <= members <= 8 * launches, fused
+        assert launches >= 1 and launches < members <= 8 * launches, fused
     finally:
         sp.stop()
 
