@@ -36,11 +36,18 @@ def default_config(prefix: str, *, transport: str = "auto", nvls: bool = True, c
 
     The size -> (variant, CTAs) table measured on B200 (``configs/tuning_b200.json``,
     written by ``python -m mccs_b200.utils.sweep --tuning``) is loaded when present;
-    pass ``tuning_file=""`` for the built-in defaults.
+    pass ``tuning_file=""`` for the built-in defaults. ``MCCS_B200_EXTRA`` (environment)
+    adds lines to the ``[b200]`` table of every configuration built here, e.g.
+    ``MCCS_B200_EXTRA='fuse_allreduce = 8;skip_start_barrier = true'`` (``;`` separates lines),
+    which is how the benchmark tools are pointed at an experimental setting.
     """
     if tuning_file is None:
         tuning_file = TUNING_FILE if os.path.exists(TUNING_FILE) else ""
     wait_timeout_ms = int(os.environ.get("MCCS_WAIT_TIMEOUT_MS", wait_timeout_ms))
+    env_extra = os.environ.get("MCCS_B200_EXTRA", "")
+    if env_extra:
+        # before `extra`, which may open another table
+        extra = "\n".join([line.strip() for line in env_extra.split(";") if line.strip()] + [extra])
     tuning_line = f'tuning_file = "{tuning_file}"' if tuning_file else ""
     return f"""
 listen_port = {listen_port}
