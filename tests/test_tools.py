@@ -73,3 +73,24 @@ def test_latency_breakdown_tool_on_host_backend():
     st = out["stages"]
     assert st["rendezvous"]["n"] == 200 and st["launch"]["n"] == 200
     assert st["rendezvous"]["median_us"] + st["launch"]["median_us"] < 5 * out["period_us"] + 50
+
+
+def test_report_table_and_svg(tmp_path):
+    """Sweep CSV -> markdown table (service vs NCCL, roofline fraction) and SVG curves."""
+    import xml.dom.minidom
+    csv_path = tmp_path / "s.csv"
+    rows = ["coll,dtype,n,bytes,algo,ctas,ms,algbw_GBps,busbw_GBps"]
+    for i, size in enumerate([1 << 20, 1 << 24, 1 << 28]):
+        rows.append(f"allreduce,bf16,8,{size},nccl,0,{0.03 * 4 ** i},{size / (0.03 * 4 ** i) / 1e6},{size / (0.03 * 4 ** i) / 1e6 * 1.75}")
+        rows.append(f"allreduce,bf16,8,{size},ar_nvls_twoshot,16,{0.04 * 3 ** i},{size / (0.04 * 3 ** i) / 1e6},{size / (0.04 * 3 ** i) / 1e6 * 1.75}")
+        rows.append(f"allreduce,bf16,8,{size},ar_twoshot,32,{0.05 * 4 ** i},{size / (0.05 * 4 ** i) / 1e6},{size / (0.05 * 4 ** i) / 1e6 * 1.75}")
+    csv_path.write_text("\n".join(rows) + "\n")
+    svg = tmp_path / "c.svg"
+    res = subprocess.run([sys.executable, "-m", "mccs_b200.utils.report", str(csv_path), "--svg", str(svg)],
+                         capture_output=True, text=True, cwd=REPO, env=dict(os.environ, PYTHONPATH=REPO), timeout=60)
+    assert res.returncode == 0, res.stderr
+    lines = [l for l in res.stdout.splitlines() if l.startswith("| allreduce")]
+    assert len(lines) == 3 and all("ar_nvls_twoshot" in l for l in lines)
+    assert "| 0.75 |" in lines[0]            # 1 MiB: 0.03 ms NCCL vs 0.04 ms service
+    doc = xml.dom.minidom.parse(str(svg))
+    assert len(doc.getElementsByTagName("polyline")) == 2
