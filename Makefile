@@ -94,6 +94,15 @@ build/san/mccsd_tsan: $(SAN_DAEMON_SRCS) $(HDRS)
 	@mkdir -p build/san
 	$(SAN_CXX) $(SAN_FLAGS) -fsanitize=thread -o $@ $(SAN_DAEMON_SRCS) $(LDLIBS)
 
+# The collective kernels themselves on the CPU: the same .cuh sources, compiled by the host
+# compiler against a SIMT emulator (csrc/tests/sim), every variant checked against plain sums.
+build/sim/kernel_sim_test: csrc/tests/kernel_sim_test.cc $(wildcard csrc/tests/sim/*.h) $(HDRS)
+	@mkdir -p build/sim
+	$(SAN_CXX) -std=c++17 -O1 -g -Wall -Wno-unknown-pragmas -Wno-unused-parameter -pthread -I/usr/local/cuda/include -o $@ csrc/tests/kernel_sim_test.cc
+
+simtest: build/sim/kernel_sim_test
+	build/sim/kernel_sim_test
+
 tsan: build/san/stress_tsan
 	TSAN_OPTIONS="halt_on_error=0 second_deadlock_stack=1 suppressions=csrc/tests/tsan.supp" build/san/stress_tsan 40
 
@@ -149,5 +158,5 @@ eval-latency: all       # where the time of a small collective goes
 clean:
 	rm -rf build $(OUT)/*.so $(OUT)/mccsd $(APP_BINS) $(OUT)/host_tests
 
-.PHONY: all clean tsan asan eval-single eval-tune eval-multi eval-dynamic eval-colocate eval-latency
+.PHONY: all clean simtest tsan asan eval-single eval-tune eval-multi eval-dynamic eval-colocate eval-latency
 .SECONDARY:

@@ -21,6 +21,15 @@
 namespace mccs {
 namespace dev {
 
+#ifdef MCCS_HOST_SIM
+// CPU emulation of the kernels for tests: the PTX wrappers below are replaced by host
+// code with the same names and meaning.
+}  // namespace dev
+}  // namespace mccs
+#include "../tests/sim/sim_prims.h"
+namespace mccs {
+namespace dev {
+#else
 // ----------------------------------------------------------------------------
 // Scalar system-scope flag accesses
 // ----------------------------------------------------------------------------
@@ -161,6 +170,8 @@ __device__ __forceinline__ void multimem_st16(void* mc, Raw<16> v) {
                "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
+
+#endif  // MCCS_HOST_SIM
 
 // ----------------------------------------------------------------------------
 // Bounded waits

@@ -39,3 +39,14 @@ def test_thread_sanitizer_stress():
 
 def test_address_sanitizer_stress():
     _sanitizer_run("asan")
+
+
+def test_kernels_on_the_simt_emulator():
+    """The collective kernels' own source, compiled for the host against the SIMT emulator
+    in csrc/tests/sim: every variant, 2-8 ranks, odd sizes, in place, fused launches,
+    per-rank pipelining, and the bounded-wait error paths."""
+    from helpers import REPO
+    res = subprocess.run(["make", "simtest"], cwd=REPO, capture_output=True, text=True, timeout=900)
+    out = res.stdout + res.stderr
+    assert res.returncode == 0, out[-4000:]
+    assert ", 0 failed" in out
