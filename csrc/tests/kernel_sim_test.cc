@@ -429,6 +429,78 @@ void pipelined_case(int n, int rounds) {
   CHECK(bad == 0);
 }
 
+// The start barrier may be dropped when the host holds every launch back until all
+// clients have arrived. Worst case for that claim: every rank's stream runs the same
+// in-place AllReduce on the same buffer again and again, with no barrier before the first
+// load and nothing but stream order between the launches of one rank; a rank may be in
+// launch k+1 while a peer is still inside launch k. The closing barrier of launch k
+// (which every rank passed before its launch k+1 could start) is what keeps this correct.
+void skip_start_chain_case(int n, int rounds, bool nvls) {
+  World w(n);
+  const size_t count = 2048 + 8;
+  Buffers<float> b(n, count, 0);
+  for (int r = 0; r < n; r++)
+    for (size_t i = 0; i < count; i++) b.send(r)[i] = (float)(1 + (i + (size_t)r) % 3);
+  std::vector<BatchArgs> launches;
+  sim_mc_regions().clear();
+  SimMcRegion ms{0x100000000000ull, count * 4, {}};
+  for (int r = 0; r < n; r++) ms.backing.push_back((char*)b.send(r));
+  sim_mc_regions().push_back(ms);
+  for (int k = 0; k < rounds; k++) {
+    BatchArgs a;
+    memset(&a, 0, sizeof a);
+    a.base = w.base(kFloat32, kSum, nvls ? kArNvlsTwo : kArTwoShot, 0, false);
+    a.nops = 1;
+    a.flags = kBatchSkipStartBarrier;
+    // Odd launches reduce only the first half: their shards cut across the shards of the
+    // even launches, so a rank does read what OTHER ranks wrote one launch earlier.
+    a.count[0] = (k % 2) ? count / 2 : count;
+    for (int r = 0; r < n; r++) { a.send[0][r] = b.send(r); a.recv[0][r] = b.send(r); }
+    a.mc_send[0] = (const void*)ms.base;
+    a.mc_recv[0] = (void*)ms.base;
+    launches.push_back(a);
+  }
+  // every launch multiplies the common value by n (fp32 sums in rank order, as the kernels
+  // do), so a launch that read a peer's buffer one round too early or too late shows up
+  std::vector<float> want(count);
+  for (size_t i = 0; i < count; i++) {
+    float acc = 0;
+    for (int r = 0; r < n; r++) acc += (float)(1 + (i + (size_t)r) % 3);
+    for (int k = 1; k < rounds; k++) {
+      if ((k % 2) && i >= count / 2) continue;
+      float next = acc;
+      for (int r = 1; r < n; r++) next += acc;
+      acc = next;
+    }
+    want[i] = acc;
+  }
+  std::vector<std::thread> streams;
+  for (int r = 0; r < n; r++)
+    streams.emplace_back([&, r] {
+      std::mt19937 rng((unsigned)r * 31u + 7u);
+      for (const BatchArgs& l : launches) {
+        struct timespec ts = {0, (long)(rng() % 200) * 1000};
+        nanosleep(&ts, nullptr);
+        BatchArgs a = l;
+        a.base.rank = r;
+        std::vector<std::thread> pool;
+        sim::Dim3 grid; grid.x = 3;
+        if (nvls) sim::launch(ar_nvls_batch_kernel<float>, grid, 32, a, &pool);
+        else sim::launch(ar_twoshot_batch_kernel<float, OpSum>, grid, 32, a, &pool);
+        sim::join_all(&pool);
+      }
+    });
+  for (auto& t : streams) t.join();
+  int bad = 0;
+  for (int r = 0; r < n; r++) {
+    for (size_t i = 0; i < count; i++)
+      if (b.send(r)[i] != want[i]) { bad++; break; }
+    bad += w.status[(size_t)r]->error != 0;
+  }
+  if (bad) fprintf(stderr, "FAILED skip-start chain (n=%d rounds=%d nvls=%d)\n", n, rounds, (int)nvls);
+  CHECK(bad == 0);
+}
+
 // Random shapes within what the planner would allow: rank count, CTAs, threads, size,
 // start offset (scalar path), placement, in place, variant, element type.
 void random_cases(unsigned seed, int iterations) {
@@ -540,8 +612,16 @@ int main() {
     CHECK(memcmp(b.send(0), b.recv(0), 5000) == 0 && w.status[0]->done_seq == a.seq);
   }
   random_cases(20240611u, 250);
+  // from here on the emulated kernels are perturbed (see sim::chaos_point)
+  sim::g_chaos = true;
+  skip_start_chain_case(2, 30, false);
+  skip_start_chain_case(5, 20, false);
+  skip_start_chain_case(4, 20, true);
+  skip_start_chain_case(8, 12, true);
   pipelined_case(4, 24);
   pipelined_case(8, 12);
+  random_cases(777u, 60);
+  sim::g_chaos = false;
   missing_peer_case();
   printf("kernel_sim_test: %d checks, %d failed\n", g_checks, g_failed);
   return g_failed ? 1 : 0;

@@ -37,12 +37,14 @@ inline void sim_check_aligned(const void* p, int bytes) {
   }
 }
 template <int BYTES> inline Raw<BYTES> ld_data(const void* p) {
+  sim::chaos_point();
   sim_check_aligned(p, BYTES);
   Raw<BYTES> r;
   memcpy(&r, p, BYTES);
   return r;
 }
 template <int BYTES> inline void st_data(void* p, Raw<BYTES> v) {
+  sim::chaos_point();
   sim_check_aligned(p, BYTES);
   memcpy(p, &v, BYTES);
 }
@@ -76,6 +78,7 @@ inline void sim_from_float(float f, __nv_bfloat16* out) { *out = __float2bfloat1
 inline void sim_from_float(float f, __half* out) { *out = __float2half_rn(f); }
 
 template <typename T> Raw<16> SimMultimem<T>::ld_reduce_add(const void* mc) {
+  sim::chaos_point();
   sim_check_aligned(mc, 16);
   size_t off = 0;
   const SimMcRegion& r = sim_mc_find(mc, &off);
@@ -94,6 +97,7 @@ template <typename T> Raw<16> SimMultimem<T>::ld_reduce_add(const void* mc) {
   return raw;
 }
 inline void multimem_st16(void* mc, Raw<16> v) {
+  sim::chaos_point();
   sim_check_aligned(mc, 16);
   size_t off = 0;
   const SimMcRegion& r = sim_mc_find(mc, &off);

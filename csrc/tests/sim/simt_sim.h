@@ -164,6 +164,23 @@ inline void join_all(std::vector<std::thread>* pool) {
   pool->clear();
 }
 
+// Chaos mode: memory accesses of the emulated kernels now and then hand the CPU to another
+// fiber, or put the whole CTA to sleep for a moment, so that ranks and CTAs drift apart
+// and interleavings a quiet machine would never produce do occur. Deterministic per CTA.
+inline bool g_chaos = false;
+inline void chaos_point() {
+  if (!g_chaos || g_cta == nullptr) return;
+  static thread_local uint32_t state = 0;
+  if (state == 0) state = 0x9E3779B9u ^ (g_cta->bid.x * 7919u + g_cta->bid.y * 104729u + 1u);
+  state ^= state << 13; state ^= state >> 17; state ^= state << 5;
+  if ((state & 0x3f) == 0) {
+    spin_yield();
+  } else if ((state & 0x7ff) == 1) {
+    struct timespec ts = {0, (long)(20000 + (state >> 12) % 200000)};
+    nanosleep(&ts, nullptr);
+  }
+}
+
 inline uint64_t now_ns() {
   struct timespec ts;
   clock_gettime(CLOCK_MONOTONIC, &ts);
