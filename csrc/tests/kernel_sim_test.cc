@@ -601,6 +601,29 @@ int main() {
       batch_case<float>(w, false, 1, ctas, threads, emulated, true, true);
     }
   }
+  // empty collectives (only the hand-shakes run), a full-size CTA, and more CTAs than work
+  {
+    World w(4);
+    for (int v : {kArOneShot, kArTwoShot, kArRing, kArNvlsOne, kArNvlsTwo})
+      allreduce_case<float, OpSum>(w, v, kSum, 0, 2, threads, false, 0, false, "empty all-reduce");
+    for (int v : {kAgPull, kAgPush, kAgRing, kAgNvls}) allgather_case(w, v, 0, 2, threads, true, 0, false, "empty all-gather");
+    allreduce_case<__nv_bfloat16, OpSum>(w, kArTwoShot, kSum, 20011, 2, 512, true, 0, false, "twoshot bf16, 512 threads");
+    allreduce_case<float, OpSum>(w, kArRing, kSum, 9000, 4, 512, false, 0, true, "ring f32, 512 threads");
+    allreduce_case<float, OpSum>(w, kArTwoShot, kSum, 5, 16, threads, false, 0, false, "twoshot, 16 CTAs for 5 elements");
+    allgather_case(w, kAgPush, 48, 12, threads, false, 0, false, "ag push, 12 CTAs for 48 bytes");
+    batch_case<float>(w, false, 8, 16, threads, false, false, true);
+  }
+  // a variant the planner must never pick for these arguments reports that instead of
+  // touching memory: NVLS all-gather of a size that is not a multiple of 16 bytes
+  {
+    World w(2);
+    Buffers<uint8_t> b(2, 40, 0, 2);
+    CollArgs a = w.base(kUint8, kSum, kAgNvls, 40, false);
+    for (int r = 0; r < 2; r++) { a.send[r] = b.send(r); a.recv[r] = b.recv(r); }
+    a.mc_recv = (void*)0x200000000000ull;   // never dereferenced
+    run_all(ag_direct_kernel<kAgModeNvls>, a, 2, 1, threads, false);
+    CHECK(w.status[0]->error == kDevBadArgs && w.status[1]->error == kDevBadArgs);
+  }
   // single-rank copy
   {
     World w(1);
