@@ -33,9 +33,15 @@ __device__ __forceinline__ void batch_end(const BatchArgs& b, int rank) {
   if (b.done_ptr[rank] == nullptr) return;
   __syncthreads();
   if (threadIdx.x == 0) {
+    // Release pattern on the way in (everything this CTA observed and wrote is ordered
+    // before its count), acquire pattern for the CTA that sees the full count, so that the
+    // completion word is ordered after what ALL CTAs of this rank observed.
     fence_sys();
     const unsigned last = gridDim.x - 1;
-    if (atomicInc(b.done_counter[rank], last) == last) st_release_sys_u64(b.done_ptr[rank], b.done_value[rank]);
+    if (atomicInc(b.done_counter[rank], last) == last) {
+      fence_sys();
+      st_release_sys_u64(b.done_ptr[rank], b.done_value[rank]);
+    }
   }
 }
 
