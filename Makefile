@@ -18,6 +18,8 @@ HOST_SRCS := csrc/common/value.cc csrc/common/log.cc csrc/ipc/uds.cc csrc/device
              csrc/daemon/config.cc csrc/daemon/planner.cc csrc/daemon/qos.cc csrc/daemon/trace.cc \
              csrc/daemon/runtime.cc csrc/daemon/daemon.cc csrc/daemon/proxy.cc csrc/daemon/admin.cc
 HOST_OBJS := $(patsubst csrc/%.cc,$(OBJ)/%.o,$(HOST_SRCS))
+# the kernels compiled for the host against the SIMT emulator (used by the host backend on request)
+EMU_OBJ   := $(OBJ)/device/emulated_kernels.o
 CUDA_OBJS := $(OBJ)/device/cuda_backend.o $(OBJ)/kernels/launch.o $(OBJ)/kernels/untyped.o $(OBJ)/kernels/noalloc.o $(TYPE_OBJS)
 SHIM_SRCS := csrc/shim/libmccs.cc csrc/common/value.cc csrc/common/log.cc csrc/ipc/uds.cc
 SHIM_OBJS := $(patsubst csrc/%.cc,$(OBJ)/%.o,$(SHIM_SRCS))
@@ -31,6 +33,10 @@ all: $(OUT)/libmccs_daemon.so $(OUT)/libmccs.so $(OUT)/mccsd $(OUT)/libmccs_prel
 $(OBJ)/%.o: csrc/%.cc $(HDRS)
 	@mkdir -p $(dir $@)
 	$(CXX) $(CXXFLAGS) -c $< -o $@
+
+$(EMU_OBJ): csrc/device/emulated_kernels.cc $(wildcard csrc/tests/sim/*.h) $(HDRS)
+	@mkdir -p $(dir $@)
+	$(CXX) $(CXXFLAGS) -O1 -Wno-unknown-pragmas -Wno-sign-compare -Wno-maybe-uninitialized -c $< -o $@
 
 $(OBJ)/device/cuda_backend.o: csrc/device/cuda_backend.cu $(HDRS)
 	@mkdir -p $(dir $@)
@@ -50,9 +56,9 @@ $(OBJ)/batch_$(1).o: csrc/kernels/inst_batch.cu $(HDRS)
 endef
 $(foreach t,$(TYPES),$(eval $(call TYPE_RULE,$(word 1,$(subst :, ,$(t))),$(word 2,$(subst :, ,$(t))))))
 
-$(OUT)/libmccs_daemon.so: $(HOST_OBJS) $(CUDA_OBJS) csrc/exports.map
+$(OUT)/libmccs_daemon.so: $(HOST_OBJS) $(EMU_OBJ) $(CUDA_OBJS) csrc/exports.map
 	@mkdir -p $(OUT)
-	$(NVCC) $(ARCH) -shared -cudart static -Xlinker --version-script=csrc/exports.map -o $@ $(HOST_OBJS) $(CUDA_OBJS) $(LDLIBS)
+	$(NVCC) $(ARCH) -shared -cudart static -Xlinker --version-script=csrc/exports.map -o $@ $(HOST_OBJS) $(EMU_OBJ) $(CUDA_OBJS) $(LDLIBS)
 
 $(OUT)/libmccs.so: $(SHIM_OBJS) csrc/exports.map
 	@mkdir -p $(OUT)

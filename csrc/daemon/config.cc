@@ -98,6 +98,7 @@ Config Config::from_value(const Value& root) {
     const Value& q = root["qos"];
     c.qos_cta_budget = (int)q["cta_budget"].as_int(c.qos_cta_budget);
     c.qos_max_outstanding_bytes = (uint64_t)q["max_outstanding_bytes"].as_int((int64_t)c.qos_max_outstanding_bytes);
+    c.qos_active_window_us = (uint64_t)q["active_window_us"].as_int((int64_t)c.qos_active_window_us);
     for (const auto& kv : q["tenants"].fields()) {
       QosTenantConfig t;
       t.weight = kv.second["weight"].as_double(1.0);
@@ -113,7 +114,7 @@ Config Config::from_value(const Value& root) {
     check_keys(b,
                {"transport", "nvls", "vmm", "sync", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
                 "host_devices", "force_host_backend", "idle_sleep_us", "idle_spin_us", "pin_threads", "init_timeout_ms", "fuse_allreduce",
-                "single_through_fused", "skip_start_barrier", "kernel_writes_done"},
+                "single_through_fused", "skip_start_barrier", "kernel_writes_done", "host_kernels"},
                "[b200]");
     c.transport = b["transport"].as_string(c.transport);
     if (c.transport != "auto" && c.transport != "nvlink" && c.transport != "host_staged")
@@ -129,6 +130,9 @@ Config Config::from_value(const Value& root) {
     c.trace_file = b["trace_file"].as_string();
     c.host_devices = (int)b["host_devices"].as_int(c.host_devices);
     c.force_host_backend = b["force_host_backend"].as_bool(c.force_host_backend);
+    c.host_kernels = b["host_kernels"].as_string(c.host_kernels);
+    if (c.host_kernels != "loops" && c.host_kernels != "emulated")
+      throw std::runtime_error("b200.host_kernels must be loops or emulated");
     c.idle_sleep_us = (int)b["idle_sleep_us"].as_int(c.idle_sleep_us);
     c.idle_spin_us = (int)b["idle_spin_us"].as_int(c.idle_spin_us);
     c.pin_threads = b["pin_threads"].as_bool(c.pin_threads);

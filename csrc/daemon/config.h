@@ -66,6 +66,7 @@ struct Config {
   std::map<uint32_t, QosTenantConfig> qos_tenants;
   int qos_cta_budget = 64;       // CTAs shared by contending tenants on one GPU
   uint64_t qos_max_outstanding_bytes = 64ull << 20;  // per tenant, only under contention
+  uint64_t qos_active_window_us = 5000;  // a tenant counts as a contender this long after its last request
   // [[comm_patterns_override]]
   std::vector<CommPattern> overrides;
   // [b200]
@@ -79,6 +80,7 @@ struct Config {
   std::string trace_file;
   int host_devices = 8;
   bool force_host_backend = false;
+  std::string host_kernels = "loops";  // host backend: "loops" (plain CPU collectives) | "emulated" (the kernels on the SIMT emulator)
   int idle_sleep_us = 50;           // sleep between polls once a proxy has been idle for idle_spin_us
   int idle_spin_us = 200000;        // how long an idle proxy keeps busy-polling
   bool pin_threads = true;

@@ -48,6 +48,7 @@ int Daemon::start(const Config& cfg, std::string* err) {
   bo.allow_nvls = cfg.nvls;
   bo.force_host = cfg.force_host_backend;
   bo.allow_memops = cfg.sync != "events";
+  bo.emulate_kernels = cfg.host_kernels == "emulated";
   backend_.reset(make_backend(bo));
   if (!backend_) { if (err) *err = "no backend"; return proto::kErrInternal; }
   LOG_INFO("daemon backend: %s", backend_->describe().c_str());

@@ -13,6 +13,7 @@ void QosArbiter::configure(const Config& cfg) {
   schedule_ = cfg.qos_schedule;
   cta_budget_ = cfg.qos_cta_budget > 0 ? cfg.qos_cta_budget : 64;
   max_outstanding_ = cfg.qos_max_outstanding_bytes;
+  active_window_us_ = cfg.qos_active_window_us;
   for (const auto& kv : cfg.qos_tenants) tenants_[kv.first].cfg = kv.second;
 }
 

@@ -59,6 +59,7 @@ struct BackendOptions {
   bool allow_nvls = true;
   bool force_host = false;
   bool allow_memops = true;
+  bool emulate_kernels = false; // host backend: run the real kernels on the SIMT emulator instead of plain loops
 };
 
 class Backend {

@@ -17,6 +17,7 @@
 #include "../common/log.h"
 #include "../ipc/uds.h"
 #include "backend.h"
+#include "emulated_kernels.h"
 
 namespace mccs {
 namespace {
@@ -154,12 +155,15 @@ void cpu_allgather(const CollArgs& a) {
 
 class HostBackend : public Backend {
  public:
-  explicit HostBackend(const BackendOptions& opt) : ndev_(opt.host_devices > 0 ? opt.host_devices : 1) {}
+  explicit HostBackend(const BackendOptions& opt)
+      : ndev_(opt.host_devices > 0 ? opt.host_devices : 1), emulate_(opt.emulate_kernels) {}
   uint32_t kind() const override { return proto::kBackendHost; }
   int device_count() const override { return ndev_; }
   bool nvls_supported() const override { return false; }
   bool peer_access(int, int) const override { return true; }
-  std::string describe() const override { return "host backend (" + std::to_string(ndev_) + " emulated devices)"; }
+  std::string describe() const override {
+    return "host backend (" + std::to_string(ndev_) + " emulated devices" + (emulate_ ? ", kernels on the SIMT emulator)" : ")");
+  }
   std::string cpu_affinity(int) const override { return ""; }
   int set_device(int dev) override { return dev >= 0 && dev < ndev_ ? proto::kOk : proto::kErrInvalidArgument; }
 
@@ -226,6 +230,7 @@ class HostBackend : public Backend {
   int max_group_batch_ctas(int, int, int, int, int) const override { return kMaxCtas; }
   int launch_batch(int dev, const BatchArgs& b, LaunchDims dims, void* stream) override {
     if (b.nops < 1 || b.nops > kMaxBatch) return proto::kErrInvalidArgument;
+    if (emulate_) return emulated_launch_batch(b, dims) ? proto::kOk : proto::kErrUnsupported;
     for (int k = 0; k < b.nops; k++) {
       CollArgs a = b.base;
       a.count = b.count[k];
@@ -236,8 +241,10 @@ class HostBackend : public Backend {
     return proto::kOk;
   }
 
-  int launch(int, int kind, const CollArgs& a, LaunchDims, void*) override {
+  int launch(int, int kind, const CollArgs& a, LaunchDims dims_, void*) override {
     if (!a.emulated && a.nranks > 1) return proto::kErrUnsupported;
+    // The real kernels on the SIMT emulator: they do their own abort and status handling.
+    if (emulate_) return emulated_launch(kind, a, dims_) ? proto::kOk : proto::kErrUnsupported;
     if (a.status[0] && __atomic_load_n(&a.status[0]->abort, __ATOMIC_ACQUIRE)) {
       for (int r = 0; r < a.nranks; r++) if (a.status[r]) __atomic_store_n(&a.status[r]->error, (uint32_t)kDevAborted, __ATOMIC_RELEASE);
       return proto::kOk;
@@ -266,6 +273,7 @@ class HostBackend : public Backend {
 
  private:
   int ndev_;
+  bool emulate_;
   std::atomic<uint64_t> next_handle_{0x1000};
 };
 

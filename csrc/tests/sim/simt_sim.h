@@ -18,6 +18,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <math.h>
 #include <sched.h>
 #include <stdint.h>
 #include <stdio.h>

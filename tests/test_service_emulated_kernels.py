@@ -1,0 +1,185 @@
+"""The whole service on a machine without a GPU, with the REAL kernels: the daemon's host
+backend runs the kernels' own sources on the SIMT emulator (`[b200] host_kernels =
+"emulated"`) instead of its plain loops. What this adds over the other host tests is the
+daemon's side of the device contract: barrier epochs and tickets handed out per collective
+and per slice, ring step counters and FIFO placement across collectives, ring orders
+frozen at plan time, live reconfiguration between kernels, fused launches and the
+host-staged transport's FIFO ring."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+from helpers import REPO, write_config
+
+CLIENT = r"""
+import os, sys, json, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"]); port = int(os.environ["ADMIN_PORT"])
+torch.manual_seed(1234)                     # every rank can compute every rank's input
+DT = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16, "i32": torch.int32, "i64": torch.int64, "f64": torch.float64}
+def inputs(dt, count, salt):
+    g = torch.Generator().manual_seed(1000 * salt + count)
+    return [torch.randint(-4, 5, (count,), generator=g).to(dt) for _ in range(n)]
+send = M.Buffer(1 << 20, rank); recv = M.Buffer(1 << 21, rank)
+comm = M.Communicator(6100, rank, n, device=rank)
+bad = []
+seen = set()
+salt = 0
+def allreduce(algo, dname, count, op="sum", in_place=False):
+    global salt
+    salt += 1
+    dt = DT[dname]
+    xs = inputs(dt, count, salt)
+    s = send.tensor(dt, count); s.copy_(xs[rank])
+    d = s if in_place else recv.tensor(dt, count)
+    comm.all_reduce(s, None if in_place else d, op=op, algo=algo)
+    acc = torch.stack([x.double() for x in xs])
+    want = {"sum": acc.sum(0), "max": acc.max(0).values, "min": acc.min(0).values, "avg": acc.sum(0) / n, "prod": acc.prod(0)}[op]
+    tol = {"bf16": 0.05 * n, "f16": 0.01 * n}.get(dname, 1e-6)
+    if not torch.allclose(d.double(), want, rtol=0, atol=tol):
+        bad.append(("allreduce", algo, dname, count, op, in_place))
+    seen.add(comm.last_plan()[0])
+def allgather(algo, nbytes, in_place=False):
+    global salt
+    salt += 1
+    xs = [((torch.arange(nbytes) * (r + 3) + salt) % 251).to(torch.uint8) for r in range(n)]
+    out = recv.tensor(torch.uint8, nbytes * n)
+    s = out[rank * nbytes:(rank + 1) * nbytes] if in_place else send.tensor(torch.uint8, nbytes)
+    s.copy_(xs[rank])
+    comm.all_gather(s, out, algo=algo)
+    if not torch.equal(out, torch.cat(xs)):
+        bad.append(("allgather", algo, nbytes, in_place))
+    seen.add(comm.last_plan()[0])
+
+for algo in ("ar_oneshot", "ar_twoshot", "ar_ring", "auto"):
+    for dname, count in (("f32", 1), ("f32", 4099), ("bf16", 3001), ("i32", 257), ("f64", 100), ("i64", 33), ("f16", 2048)):
+        allreduce(algo, dname, count)
+    allreduce(algo, "f32", 1000, op="avg")
+    allreduce(algo, "i32", 500, op="max")
+    if algo != "ar_oneshot":
+        allreduce(algo, "f32", 5000, in_place=True)
+for algo in ("ag_pull", "ag_push", "ag_ring", "auto"):
+    for nbytes in (16, 1000, 40000):
+        allgather(algo, nbytes)
+    allgather(algo, 4096, in_place=True)
+# many FIFO loops through the ring, then a live change of the ring order and channel count,
+# then the ring again: step counters and FIFO slots carry over between the launches
+allreduce("ar_ring", "f32", 150000)
+if rank == 0:
+    ring = list(reversed(range(n)))
+    rep = M.reconfigure(port, [{"communicator_id": 6100, "channels": [{"channel_id": 0, "ring": ring}, {"channel_id": 1, "ring": list(range(n))}, {"channel_id": 2, "ring": ring}]}])
+    assert rep.get("status") == "ok", rep
+for _ in range(3):
+    allreduce("ar_ring", "f32", 70000)
+    allgather("ag_ring", 30000)
+# a burst: 8 independent all-reduces in one group (fused launches are on in this daemon)
+bufs = [M.Buffer(8192, rank) for _ in range(8)]
+ts = [b.tensor(torch.float32, 100 + 37 * i) for i, b in enumerate(bufs)]
+for i, t in enumerate(ts):
+    t.fill_(float(rank + i))
+with M.group():
+    for t in ts:
+        comm.all_reduce(t, algo="ar_twoshot")
+for i, t in enumerate(ts):
+    if not bool(torch.all(t == float(sum(range(n)) + n * i))):
+        bad.append(("group", i))
+q = comm.query()
+st = M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"]["6100"]
+comm.destroy()
+print("RESULT", json.dumps({"bad": bad, "seen": sorted(seen), "async_error": q["async_error"], "device_error": q["device_error"],
+                            "fused_members": st["fused_members"], "epoch": st["config_epoch"]}), flush=True)
+"""
+
+
+def _run(tmp_path, n, extra, **kw):
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=n, listen_port=-1, force_host=True,
+                       wait_timeout_ms=20000, extra='host_kernels = "emulated"\nfuse_allreduce = 8\n' + extra, **kw)
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        assert "SIMT emulator" in json.dumps(__import__("mccs_b200").admin_request(sp.admin_port, {"cmd": "stats"}))
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), MCCS_LOG="error",
+                   ADMIN_PORT=str(sp.admin_port), MCCS_WC_TIMEOUT_MS="60000")
+        procs = [subprocess.Popen([sys.executable, "-c", CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                                  stderr=subprocess.PIPE, text=True) for r in range(n)]
+        results = []
+        for p in procs:
+            out, err = p.communicate(timeout=600)
+            assert p.returncode == 0, err[-3000:]
+            results.append(json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:]))
+        return results
+    finally:
+        sp.stop()
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_service_with_the_real_kernels_on_the_emulator(tmp_path, n):
+    for res in _run(tmp_path, n, ""):
+        assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
+        # every emulated variant really ran
+        assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
+        assert res["epoch"] == 1 and res["fused_members"] >= 2
+
+
+def test_host_staged_transport_with_the_real_ring_kernels(tmp_path):
+    """`transport = "host_staged"`: only the FIFO ring variants are legal, whatever is asked for."""
+    for res in _run(tmp_path, 3, "", transport="host_staged"):
+        assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
+        assert set(res["seen"]) <= {"ar_ring", "ag_ring"}
+
+
+SLICE_CLIENT = r"""
+import os, sys, json, time, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); cid = int(os.environ["COMM"]); n = 2
+count = 1 << 20                                         # 4 MiB of fp32: above the 1 MiB slice size of this daemon
+buf = M.Buffer(count * 4, rank); out = M.Buffer(count * 4, rank)
+comm = M.Communicator(cid, rank, n, device=rank)
+x = buf.tensor(torch.float32, count); y = out.tensor(torch.float32, count)
+ok = True
+# start together with the other tenant: wait until both communicators exist
+port = int(os.environ["ADMIN_PORT"])
+for _ in range(600):
+    if {"6201", "6202"} <= set(M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"]):
+        break
+    time.sleep(0.05)
+for it in range(12):
+    x.copy_(torch.arange(count, dtype=torch.float32) % 97 + rank + it + cid)
+    comm.all_reduce(x, y, algo="ar_twoshot")
+    want = (torch.arange(count, dtype=torch.float32) % 97) * 2 + 1 + 2 * (it + cid)
+    ok &= bool(torch.equal(y, want))
+q = comm.query()
+comm.destroy()
+print("RESULT", json.dumps({"ok": ok, "async_error": q["async_error"], "device_error": q["device_error"]}), flush=True)
+"""
+
+
+def test_time_sliced_allreduce_with_the_real_kernels(tmp_path):
+    """Two tenants on the same two devices: large all-reduces are cut into slices (each its
+    own launch with its own barrier epochs and ticket) and still give the right sums."""
+    import mccs_b200 as M
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=2, listen_port=-1, force_host=True,
+                       wait_timeout_ms=20000, trace=True, extra='host_kernels = "emulated"')
+    with open(cfg, "a") as f:
+        f.write("\n[qos]\nmax_outstanding_bytes = 2097152\nactive_window_us = 3000000\n[qos.tenants.6201]\nweight = 2.0\n[qos.tenants.6202]\nweight = 1.0\n")
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, MCCS_LOG="error", MCCS_WC_TIMEOUT_MS="60000",
+                   ADMIN_PORT=str(sp.admin_port))
+        procs = [subprocess.Popen([sys.executable, "-c", SLICE_CLIENT], env=dict(env, RANK=str(r), COMM=str(c)),
+                                  stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for c in (6201, 6202) for r in range(2)]
+        for p in procs:
+            out, err = p.communicate(timeout=600)
+            assert p.returncode == 0, err[-3000:]
+            res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+            assert res["ok"] and res["async_error"] == 0 and res["device_error"] == 0
+        events = M.admin_request(sp.admin_port, {"cmd": "trace", "enabled": False, "inline": True})["trace"]["traceEvents"]
+        assert max(e.get("args", {}).get("slices", 1) for e in events) > 1, "no collective was sliced"
+    finally:
+        sp.stop()
