@@ -111,6 +111,8 @@ bool ProxyEngine::intake(RankState& rs) {
       int err = rs.comm->async_error.load();
       wc.status = err ? err : proto::kErrPeerLost;
       wc.user_seq = rs.pending_wr.user_seq;
+      LOG_WARN("comm %u rank %d: request %llu arrived after the communicator stopped taking work (status %d)", rs.comm->id,
+               rs.rank, (unsigned long long)wc.user_seq, wc.status);
       if (rs.pending_wr.sync_slot && rs.dp_status) {
         signal_done(rs, rs.pending_wr.user_seq);
         if (rs.dp_status->first_error == 0) rs.dp_status->first_error = wc.status;
@@ -790,13 +792,21 @@ bool ProxyEngine::advance(RankState& rs) {
     }
     const uint64_t seq = rs.next_launch_seq;
     CollSlot& s = c.slot(seq);
+    // The communicator's state is read BEFORE the slot's: a peer only closes its handle
+    // after every collective it took part in has been collected, so a slot that still
+    // shows "collecting" after the close was observed can never complete. (Read the other
+    // way round, a proxy thread that is descheduled between the two loads would fail a
+    // collective that completed for everybody else in the meantime.)
+    const bool comm_stopped = c.state.load(std::memory_order_acquire) == kCommError;
     int st = s.state.load(std::memory_order_acquire);
-    if (c.state.load(std::memory_order_acquire) == kCommError) {
+    if (comm_stopped) {
       // A failed communicator never launches again; what was posted completes in error.
       // A communicator that is merely being closed (a peer destroyed its handle, no
       // error recorded) still finishes collectives every rank had already joined.
       const int err = c.async_error.load();
       if (err != 0 || st == kSlotCollecting) {
+        LOG_WARN("comm %u rank %d: collective %llu ends with status %d (%d of %d ranks had joined it)", c.id, rs.rank,
+                 (unsigned long long)seq, err ? err : proto::kErrPeerLost, s.arrived.load(), c.nranks);
         if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq);
         complete_request(rs, s, seq, err ? err : proto::kErrPeerLost);
         rs.next_launch_seq++;

@@ -74,7 +74,12 @@ void run_rank(const App& app, int rank) {
       EXPECT(mccsGroupStart() == mccsSuccess);
       for (int k = 0; k < 4; k++)
         EXPECT(mccsAllReduce(comm, multi[k], multi[k], 64 + 16 * (size_t)k, mccsFloat32, mccsSum, nullptr) == mccsSuccess);
-      EXPECT(mccsGroupEnd() == mccsSuccess);
+      {
+        const mccsResult_t ge = mccsGroupEnd();
+        if (ge != mccsSuccess) fprintf(stderr, "comm %u rank %d iteration %d: group of independent buffers ended with %d (%s)\n",
+                                       app.comm_id, rank, it, (int)ge, mccsGetErrorString(ge));
+        EXPECT(ge == mccsSuccess);
+      }
       for (int k = 0; k < 4; k++) {
         const int last = 64 + 16 * k - 1;
         EXPECT(multi[k][last] == (float)(n * (n - 1) / 2) + (float)n * (float)(k + last % 3));
