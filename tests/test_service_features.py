@@ -493,3 +493,70 @@ def test_preload_hook_routes_large_allocations_to_the_service(private_daemon, tm
     assert "big_ours=1" in res.stdout and "small_ours=0" in res.stdout and "big_after_free=0" in res.stdout
     size = int(res.stdout.split("size=")[1].split()[0])
     assert size >= 2 << 20
+
+
+CHAOS_CLIENT = r"""
+import os, sys, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"]); cid = int(os.environ["COMM"])
+buf = M.Buffer(1 << 16, rank)
+t = buf.tensor(torch.float32, 4096); t.fill_(1.0)
+try:
+    c = M.Communicator(cid, rank, n, device=rank)
+except Exception as e:
+    print("INIT_ERROR", getattr(e, "code", None), flush=True); sys.exit(0)
+print("READY", flush=True)
+try:
+    for i in range(10 ** 7):
+        t.fill_(1.0)
+        if i % 7 == 3:
+            with M.group():
+                for _ in range(4):
+                    c.all_reduce(t, op="max")
+        else:
+            c.all_reduce(t)
+        if float(t[0]) not in (1.0, float(n)):
+            print("BAD", float(t[0]), flush=True); sys.exit(3)
+except Exception as e:
+    print("ERROR", getattr(e, "code", None), flush=True)
+"""
+
+
+def test_clients_killed_at_random_leave_the_daemon_clean(tmp_path):
+    """Three rounds of: a few ranks hammer a communicator, one of them is killed without
+    warning at a random moment; the others get an error (never a wrong value, never a
+    hang), the same communicator id is usable again in the next round, and at the end the
+    daemon holds no client, communicator or allocation."""
+    import random
+    import signal
+    import time
+    import mccs_b200 as M
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=-1, force_host=True,
+                       wait_timeout_ms=3000, extra="init_timeout_ms = 3000\nfuse_allreduce = 4")
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "error"})
+    rng = random.Random(11)
+    try:
+        for rnd in range(3):
+            n = rng.choice([2, 3, 4])
+            env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), COMM="8000", MCCS_LOG="error",
+                       MCCS_WC_TIMEOUT_MS="8000")
+            procs = [subprocess.Popen([sys.executable, "-c", CHAOS_CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True) for r in range(n)]
+            # wait until every rank is in its loop, then strike at a random moment
+            for p in procs:
+                assert p.stdout.readline().startswith("READY")
+            time.sleep(rng.uniform(0.05, 0.8))
+            victim = rng.randrange(n)
+            procs[victim].send_signal(signal.SIGKILL)
+            for r, p in enumerate(procs):
+                out, err = p.communicate(timeout=30)
+                assert "BAD" not in out
+                if r != victim:
+                    assert "ERROR" in out, (rnd, r, out, err[-500:])
+            assert sp.proc.poll() is None, "the daemon died"
+        st = M.admin_request(sp.admin_port, {"cmd": "stats"})["stats"]
+        assert st["clients"] == 0 and st["communicators"] == {} and st["allocations"] == 0
+    finally:
+        sp.stop()
