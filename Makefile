@@ -111,6 +111,7 @@ simtest: build/sim/kernel_sim_test
 
 tsan: build/san/stress_tsan
 	TSAN_OPTIONS="halt_on_error=0 second_deadlock_stack=1 suppressions=csrc/tests/tsan.supp" build/san/stress_tsan 40
+	TSAN_OPTIONS="halt_on_error=0 second_deadlock_stack=1 suppressions=csrc/tests/tsan.supp" build/san/stress_tsan 40 memops
 
 build/san/fuzz_value: csrc/tests/fuzz_value.cc csrc/common/value.cc csrc/common/log.cc csrc/daemon/config.cc $(HDRS)
 	@mkdir -p build/san
@@ -123,6 +124,7 @@ build/san/fuzz_protocol: $(SAN_FUZZP_SRCS) $(HDRS)
 
 asan: build/san/stress_asan build/san/fuzz_value build/san/fuzz_protocol
 	ASAN_OPTIONS="detect_leaks=1" build/san/stress_asan 40
+	ASAN_OPTIONS="detect_leaks=1" build/san/stress_asan 40 memops
 	build/san/fuzz_value 40000
 	ASAN_OPTIONS="detect_leaks=1" build/san/fuzz_protocol 3000
 

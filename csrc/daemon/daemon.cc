@@ -49,6 +49,7 @@ int Daemon::start(const Config& cfg, std::string* err) {
   bo.force_host = cfg.force_host_backend;
   bo.allow_memops = cfg.sync != "events";
   bo.emulate_kernels = cfg.host_kernels == "emulated";
+  bo.host_memops = cfg.sync == "memops";   // on the host backend only on request ("auto" keeps events there)
   backend_.reset(make_backend(bo));
   if (!backend_) { if (err) *err = "no backend"; return proto::kErrInternal; }
   LOG_INFO("daemon backend: %s", backend_->describe().c_str());
@@ -612,7 +613,8 @@ int Daemon::finalize_communicator(Communicator& c) {
     // "wait for done" blocking the client's stream could then hold up the very backend
     // stream that has to produce "done". Such clients use ordinary events, which are
     // cheap inside one process.
-    if (memops_ && !rs.same_process) {
+    // (The host backend has no hardware queues: there every client may use the page.)
+    if (memops_ && (!rs.same_process || host)) {
       if ((rc = backend_->sync_page_create(rs.device, &rs.sync)) != proto::kOk) return rc;
     }
     if ((rc = backend_->stream_create(rs.device, prio, &rs.stream)) != proto::kOk) return rc;
@@ -637,9 +639,11 @@ int Daemon::finalize_communicator(Communicator& c) {
   qos_.tenant_register(c.id, devs);
   c.state.store(kCommActive);
   for (int r = 0; r < c.nranks; r++) proxies_[(size_t)c.ranks[(size_t)r]->device]->add_rank(c.ranks[(size_t)r].get());
-  LOG_INFO("comm %u ready: %d ranks, %s%s, %d ring channel(s)", c.id, c.nranks,
+  int sem_ranks = 0;
+  for (auto& r : c.ranks) sem_ranks += r->sync.host != nullptr;
+  LOG_INFO("comm %u ready: %d ranks, %s%s, %d ring channel(s), %d rank(s) ordered by semaphores, %d by events", c.id, c.nranks,
            c.host_staged ? "host-staged" : "nvlink peer memory", c.emulated ? " (single-device emulation)" : "",
-           c.channel_count);
+           c.channel_count, sem_ranks, c.nranks - sem_ranks);
   return proto::kOk;
 }
 

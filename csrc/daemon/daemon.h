@@ -219,7 +219,7 @@ class ProxyEngine : public Engine {
   bool admit_slice(Communicator& c, CollSlot& s, int slice);
   void fill_args(Communicator& c, CollSlot& s, int rank, int slice, CollArgs* a);
   bool complete_request(RankState& rs, CollSlot& s, uint64_t seq, int status);
-  void signal_done(RankState& rs, uint64_t user_seq);
+  void signal_done(RankState& rs, uint64_t user_seq, int status);
   void order_after_client(RankState& rs, const CollOp& op, void* stream);
   bool clients_ready(Communicator& c, CollSlot& s, int self_rank);
   void finish_slot(Communicator& c, CollSlot& s, uint64_t seq);

@@ -114,7 +114,7 @@ bool ProxyEngine::intake(RankState& rs) {
       LOG_WARN("comm %u rank %d: request %llu arrived after the communicator stopped taking work (status %d)", rs.comm->id,
                rs.rank, (unsigned long long)wc.user_seq, wc.status);
       if (rs.pending_wr.sync_slot && rs.dp_status) {
-        signal_done(rs, rs.pending_wr.user_seq);
+        signal_done(rs, rs.pending_wr.user_seq, wc.status);
         if (rs.dp_status->first_error == 0) rs.dp_status->first_error = wc.status;
         __atomic_store_n(&rs.dp_status->completed, rs.dp_status->completed + 1, __ATOMIC_RELEASE);
       } else if (!rs.cq.try_push(&wc)) { rs.pending_wc = wc; rs.have_pending_wc = true; }
@@ -669,8 +669,12 @@ void ProxyEngine::order_after_client(RankState& rs, const CollOp& op, void* stre
 
 // A request that ends without a launch must still release the client's stream, which
 // (in mem-op mode) already waits for this request's "done" value.
-void ProxyEngine::signal_done(RankState& rs, uint64_t user_seq) {
+void ProxyEngine::signal_done(RankState& rs, uint64_t user_seq, int status) {
   if (!rs.sync.host) return;
+  // The error is published before the stream is released, so that a caller who waited for
+  // this request finds it.
+  if (status != proto::kOk && rs.dp_status && rs.dp_status->first_error == 0)
+    __atomic_store_n(&rs.dp_status->first_error, status, __ATOMIC_RELEASE);
   Communicator& c = *rs.comm;
   void* stream = c.group_stream ? c.group_stream : rs.stream;
   daemon_->backend()->stream_write_value64(rs.device, stream, rs.sync.dev_addr + 8 * proto::kSyncDoneSlot, user_seq);
@@ -807,7 +811,7 @@ bool ProxyEngine::advance(RankState& rs) {
       if (err != 0 || st == kSlotCollecting) {
         LOG_WARN("comm %u rank %d: collective %llu ends with status %d (%d of %d ranks had joined it)", c.id, rs.rank,
                  (unsigned long long)seq, err ? err : proto::kErrPeerLost, s.arrived.load(), c.nranks);
-        if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq);
+        if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq, err ? err : proto::kErrPeerLost);
         complete_request(rs, s, seq, err ? err : proto::kErrPeerLost);
         rs.next_launch_seq++;
         rs.next_slice = 0;
@@ -846,7 +850,7 @@ bool ProxyEngine::advance(RankState& rs) {
     const uint64_t t_go_us = daemon_->tracer().enabled() ? monotonic_us() : 0;
     if (st == kSlotFailed) {
       status = s.status;
-      if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq);
+      if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq, status);
     } else if (follower) {
       if (c.state.load() == kCommError) status = c.async_error.load();
     } else if (group) {

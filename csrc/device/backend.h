@@ -59,6 +59,7 @@ struct BackendOptions {
   bool allow_nvls = true;
   bool force_host = false;
   bool allow_memops = true;
+  bool host_memops = false;     // host backend: offer semaphore pages, "stream memory operations" done by the CPU
   bool emulate_kernels = false; // host backend: run the real kernels on the SIMT emulator instead of plain loops
 };
 

@@ -16,6 +16,8 @@
 
 #include "../common/log.h"
 #include "../ipc/uds.h"
+#include <sched.h>
+
 #include "backend.h"
 #include "emulated_kernels.h"
 
@@ -156,7 +158,7 @@ void cpu_allgather(const CollArgs& a) {
 class HostBackend : public Backend {
  public:
   explicit HostBackend(const BackendOptions& opt)
-      : ndev_(opt.host_devices > 0 ? opt.host_devices : 1), emulate_(opt.emulate_kernels) {}
+      : ndev_(opt.host_devices > 0 ? opt.host_devices : 1), emulate_(opt.emulate_kernels), memops_(opt.host_memops) {}
   uint32_t kind() const override { return proto::kBackendHost; }
   int device_count() const override { return ndev_; }
   bool nvls_supported() const override { return false; }
@@ -214,12 +216,41 @@ class HostBackend : public Backend {
   int event_destroy(int, void*) override { return proto::kOk; }
   int stream_wait_event(int, void*, void*) override { return proto::kOk; }
   int event_record(int, void*, void*) override { return proto::kOk; }
-  bool memops_supported() const override { return false; }
-  int stream_wait_value64(int, void*, uint64_t, uint64_t) override { return proto::kOk; }
-  int stream_write_value64(int, void*, uint64_t, uint64_t) override { return proto::kOk; }
+  // Stream memory operations, done by the CPU at once (a host "stream" has nothing queued
+  // when a call returns): the mem-op protocol between client library and proxies runs
+  // unchanged, which is what lets it be tested without a GPU.
+  bool memops_supported() const override { return memops_; }
+  int stream_wait_value64(int, void*, uint64_t addr, uint64_t value) override {
+    while ((int64_t)(__atomic_load_n((uint64_t*)addr, __ATOMIC_ACQUIRE) - value) < 0) sched_yield();
+    return proto::kOk;
+  }
+  int stream_write_value64(int, void*, uint64_t addr, uint64_t value) override {
+    __atomic_store_n((uint64_t*)addr, value, __ATOMIC_RELEASE);
+    return proto::kOk;
+  }
   int zero_memory(int, uint64_t addr, size_t bytes) override { memset((void*)addr, 0, bytes); return proto::kOk; }
-  int sync_page_create(int, SyncPage*) override { return proto::kErrUnsupported; }
-  int sync_page_destroy(int, SyncPage*) override { return proto::kOk; }
+  int sync_page_create(int, SyncPage* out) override {
+    if (!memops_) return proto::kErrUnsupported;
+    const size_t bytes = 4096;
+    int fd = ipc::memfd_make("mccs-sync", bytes);
+    if (fd < 0) return proto::kErrOutOfMemory;
+    void* p = ipc::map_shared(fd, bytes);
+    if (!p) { close(fd); return proto::kErrOutOfMemory; }
+    memset(p, 0, bytes);
+    out->fd = fd;
+    out->host = p;
+    out->dev_addr = (uint64_t)p;
+    out->bytes = bytes;
+    return proto::kOk;
+  }
+  int sync_page_destroy(int, SyncPage* p) override {
+    if (!p->host) return proto::kOk;
+    ipc::unmap_shared(p->host, p->bytes);
+    close(p->fd);
+    p->host = nullptr;
+    p->fd = -1;
+    return proto::kOk;
+  }
   int mc_create(const std::vector<const Allocation*>&, McRegion*) override { return proto::kErrUnsupported; }
   int mc_destroy(McRegion*) override { return proto::kOk; }
 
@@ -274,6 +305,7 @@ class HostBackend : public Backend {
  private:
   int ndev_;
   bool emulate_;
+  bool memops_;
   std::atomic<uint64_t> next_handle_{0x1000};
 };
 

@@ -129,6 +129,7 @@ struct CtxScope {
   bool switched = false;
   bool ok = false;
   explicit CtxScope(int device) {
+    if (device < 0) { ok = true; return; }   // nothing to make current (host backend)
     if (!load_driver()) return;
     CUcontext cur = nullptr;
     g_drv.cuCtxGetCurrent_(&cur);
@@ -220,6 +221,7 @@ struct mccsComm {
   void* sync_host = nullptr;
   size_t sync_bytes = 0;
   uint64_t sync_base = 0;     // device address of the page for stream memory operations
+  bool sync_emulated = false; // host backend: the CPU writes and awaits the semaphores itself
   std::map<uint64_t, uint32_t> stream_slot;            // stream handle -> semaphore index
   uint64_t slot_value[proto::kSyncMaxStreams] = {0};   // last value written per semaphore
 };
@@ -509,6 +511,42 @@ void reap_completions(mccsComm* comm) {
   }
 }
 
+// The two stream memory operations of the mem-op mode. On the host backend there is no
+// stream: the write happens now and the wait blocks the caller (host collectives are
+// complete when a call returns anyway), which keeps the protocol with the daemon the same.
+mccsResult_t sem_write(mccsComm* comm, mccsStream_t stream, uint64_t addr, uint64_t value) {
+  if (comm->sync_emulated) {
+    __atomic_store_n((uint64_t*)addr, value, __ATOMIC_RELEASE);
+    return mccsSuccess;
+  }
+  CUresult r = g_drv.cuStreamWriteValue64_((CUstream)stream, (CUdeviceptr)addr, value, CU_STREAM_WRITE_VALUE_DEFAULT);
+  if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWriteValue64: %s", cu_err(r)); return mccsDeviceError; }
+  return mccsSuccess;
+}
+
+mccsResult_t sem_wait_geq(mccsComm* comm, mccsStream_t stream, uint64_t addr, uint64_t value) {
+  if (comm->sync_emulated) {
+    struct timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    uint64_t spins = 0;
+    while ((int64_t)(__atomic_load_n((uint64_t*)addr, __ATOMIC_ACQUIRE) - value) < 0) {
+      if ((++spins & 0xfff) == 0) {
+        struct timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        uint64_t ms = (uint64_t)(t1.tv_sec - t0.tv_sec) * 1000 + (uint64_t)((t1.tv_nsec - t0.tv_nsec) / 1000000);
+        if (ms > g_ctx.wc_timeout_ms) return mccsTimeout;
+        struct pollfd pf = {g_ctx.fd, 0, 0};
+        if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+        if (spins > (1u << 20)) usleep(50);
+      }
+    }
+    return mccsSuccess;
+  }
+  CUresult r = g_drv.cuStreamWaitValue64_((CUstream)stream, (CUdeviceptr)addr, value, CU_STREAM_WAIT_VALUE_GEQ);
+  if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitValue64: %s", cu_err(r)); return mccsDeviceError; }
+  return mccsSuccess;
+}
+
 // Mem-op mode: nothing blocks. The caller's stream publishes "submitted", the request
 // is posted, and the stream is told to wait for the request's "done" value, which the
 // daemon's stream writes after the kernel. Errors surface on a later call.
@@ -522,7 +560,7 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
     // rank's "submitted" mark would sit behind the first rank's "wait until done".
     std::unique_lock<std::mutex> g(g_ctx.mu);   // stream tables are only changed under this lock
     for (mccsComm* other : g_ctx.comms)
-      if (other != comm && other->id == comm->id && other->stream_slot.count((uint64_t)stream)) {
+      if (!comm->sync_emulated && other != comm && other->id == comm->id && other->stream_slot.count((uint64_t)stream)) {
         LOG_ERROR("communicator %u: ranks %d and %d of this process use the same CUDA stream; give each rank "
                   "its own stream (or run the daemon with [b200] sync = \"events\")", comm->id, other->rank, comm->rank);
         return mccsInvalidArgument;
@@ -537,11 +575,10 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
   wr.user_seq = comm->next_user_seq++;
   wr.sync_slot = slot + 1;
   wr.sync_value = ++comm->slot_value[slot];
-  CtxScope scope(comm->device);
+  CtxScope scope(comm->sync_emulated ? -1 : comm->device);
   if (!scope.ok) return mccsDeviceError;
-  CUresult r = g_drv.cuStreamWriteValue64_((CUstream)stream, (CUdeviceptr)(comm->sync_base + 8 * (proto::kSyncFirstStreamSlot + slot)),
-                                           wr.sync_value, CU_STREAM_WRITE_VALUE_DEFAULT);
-  if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWriteValue64: %s", cu_err(r)); return mccsDeviceError; }
+  mccsResult_t sr = sem_write(comm, stream, comm->sync_base + 8 * (proto::kSyncFirstStreamSlot + slot), wr.sync_value);
+  if (sr != mccsSuccess) return sr;
   uint64_t spins = 0;
   while (!comm->wq.try_push(&wr)) {
     reap_completions(comm);
@@ -560,9 +597,13 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
     g_group_items.push_back({comm, stream});
     return mccsSuccess;
   }
-  r = g_drv.cuStreamWaitValue64_((CUstream)stream, (CUdeviceptr)(comm->sync_base + 8 * proto::kSyncDoneSlot), wr.user_seq,
-                                 CU_STREAM_WAIT_VALUE_GEQ);
-  if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitValue64: %s", cu_err(r)); return mccsDeviceError; }
+  sr = sem_wait_geq(comm, stream, comm->sync_base + 8 * proto::kSyncDoneSlot, wr.user_seq);
+  if (sr != mccsSuccess) return sr;
+  if (comm->sync_emulated) {
+    // the call is synchronous here: report this request's own error, as the event mode does
+    reap_completions(comm);
+    if (comm->sticky_error) return (mccsResult_t)comm->sticky_error;
+  }
   return mccsSuccess;
 }
 
@@ -826,6 +867,16 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
       }
     }
   }
+  if (g_ctx.backend == proto::kBackendHost && m.comm_init_reply.sync_size && fds.size() > 1) {
+    const size_t bytes = m.comm_init_reply.sync_size;
+    void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[1], 0);
+    if (p != MAP_FAILED) {
+      c->sync_host = p;
+      c->sync_bytes = bytes;
+      c->sync_base = (uint64_t)p;
+      c->sync_emulated = true;
+    }
+  }
   for (int f : fds) close(f);
   fds.clear();
   if (g_ctx.backend == proto::kBackendCuda) {
@@ -898,8 +949,10 @@ mccsResult_t mccsCommDestroy(mccsComm_t comm) {
     if (g_ctx.comms[i] == comm) { g_ctx.comms.erase(g_ctx.comms.begin() + (long)i); break; }
   if (comm->dp_mem) munmap(comm->dp_mem, comm->dp_bytes);
   if (comm->sync_host) {
-    CtxScope scope(comm->device);
-    if (scope.ok) g_drv.cuMemHostUnregister_(comm->sync_host);
+    if (!comm->sync_emulated) {
+      CtxScope scope(comm->device);
+      if (scope.ok) g_drv.cuMemHostUnregister_(comm->sync_host);
+    }
     munmap(comm->sync_host, comm->sync_bytes);
   }
   delete comm;
@@ -970,16 +1023,20 @@ mccsResult_t mccsCommSetDeferredWait(mccsComm_t comm, int on) {
 
 mccsResult_t mccsCommWait(mccsComm_t comm, mccsStream_t stream) {
   if (!comm) return mccsInvalidArgument;
+  if (comm->sync_emulated) {
+    if (!comm->last_posted_seq) return mccsSuccess;
+    mccsResult_t r = sem_wait_geq(comm, stream, comm->sync_base + 8 * proto::kSyncDoneSlot, comm->last_posted_seq);
+    if (r != mccsSuccess) return r;
+    reap_completions(comm);
+    return (mccsResult_t)comm->sticky_error;
+  }
   if (g_ctx.backend != proto::kBackendCuda) return mccsSuccess;
   if (comm->sync_base) {
     if (!comm->last_posted_seq) return mccsSuccess;
     CtxScope scope(comm->device);
     if (!scope.ok) return mccsDeviceError;
     // "done" only grows and is written in submission order: the newest value covers all.
-    CUresult r = g_drv.cuStreamWaitValue64_((CUstream)stream, (CUdeviceptr)(comm->sync_base + 8 * proto::kSyncDoneSlot),
-                                            comm->last_posted_seq, CU_STREAM_WAIT_VALUE_GEQ);
-    if (r != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitValue64: %s", cu_err(r)); return mccsDeviceError; }
-    return mccsSuccess;
+    return sem_wait_geq(comm, stream, comm->sync_base + 8 * proto::kSyncDoneSlot, comm->last_posted_seq);
   }
   return finish_on_stream(comm, stream);
 }

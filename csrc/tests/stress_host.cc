@@ -135,11 +135,15 @@ void operator_thread(const std::vector<App>& apps, std::atomic<bool>* stop) {
 
 int main(int argc, char** argv) {
   const int iters = argc > 1 ? atoi(argv[1]) : 60;
+  // "memops": the stream-memory-operation protocol (semaphore page, counted completions,
+  // launches gated on every rank's semaphore) instead of events and completion messages
+  const bool memops = argc > 2 && std::string(argv[2]) == "memops";
   const std::string prefix = "/tmp/mccs-stress-" + std::to_string((long)getpid());
   const std::string cfg =
       "listen_port = -1\nmccs_daemon_prefix = \"" + prefix + "\"\n[control]\nprefix = \"" + prefix +
       "\"\npath = \"control.sock\"\n[comm_default_config]\nbuffer_sizes = [65536]\nchannel_count = 2\n"
-      "[b200]\nforce_host_backend = true\nhost_devices = 4\nwait_timeout_ms = 20000\nfuse_allreduce = 4\n"
+      "[b200]\nforce_host_backend = true\nhost_devices = 4\nwait_timeout_ms = 20000\nfuse_allreduce = 4\n" +
+      std::string(memops ? "sync = \"memops\"\n" : "") +
       "[qos.tenants.7001]\nweight = 2.0\n[qos.tenants.7002]\nweight = 1.0\n";
   if (mccs::mccsd_start(cfg.c_str()) != 0) {
     fprintf(stderr, "daemon did not start\n");
@@ -163,6 +167,6 @@ int main(int argc, char** argv) {
   mccsFinalize();
   mccs::mccsd_stop();
   const int f = g_failures.load();
-  printf("stress_host: %d failure(s)\n", f);
+  printf("stress_host%s: %d failure(s)\n", memops ? " (memops)" : "", f);
   return f ? 1 : 0;
 }

@@ -116,9 +116,13 @@ def _run(tmp_path, n, extra, **kw):
         sp.stop()
 
 
-@pytest.mark.parametrize("n", [2, 4])
-def test_service_with_the_real_kernels_on_the_emulator(tmp_path, n):
-    for res in _run(tmp_path, n, ""):
+@pytest.mark.parametrize("n,sync", [(2, "auto"), (4, "auto"), (3, "memops")])
+def test_service_with_the_real_kernels_on_the_emulator(tmp_path, n, sync):
+    """`sync = "memops"`: the same, with the semaphore protocol instead of events (and with
+    it the fused kernels' start-barrier skip and in-kernel completion word, which only
+    apply to semaphore-ordered ranks)."""
+    extra = "single_through_fused = true\nskip_start_barrier = true\nkernel_writes_done = true" if sync == "memops" else ""
+    for res in _run(tmp_path, n, extra, sync=sync):
         assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
         # every emulated variant really ran
         assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
