@@ -81,12 +81,14 @@ def _free_port() -> int:
     return p
 
 
-@pytest.fixture()
-def standalone_daemon():
+@pytest.fixture(params=["events", "memops"])
+def standalone_daemon(request):
+    """Both ways of ordering collectives against the caller: events with completion
+    messages, and the semaphore protocol (done by the CPU on the host backend)."""
     from mccs_b200 import daemon
     d = tempfile.mkdtemp(prefix="mccs-pg-")
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=0,
-                       force_host=True)
+                       force_host=True, sync=request.param)
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
     yield sp
     sp.stop()
