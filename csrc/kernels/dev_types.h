@@ -100,7 +100,7 @@ struct CollArgs {
   uint32_t epoch;          // first barrier value this launch may use (uses epoch, epoch+1)
   uint64_t timeout_ns;     // bound for every device-side wait
   int32_t trace;           // 1: record globaltimer start/end into the status block
-  int32_t unroll_hint;     // tuning knob, kernels clamp it
+  int32_t unroll_hint;     // reserved (keeps the layout); the kernels choose their unrolling from the rank count
   // --- buffers (unicast addresses valid on every GPU of the communicator) -----
   const void* send[kMaxRanks];
   void* recv[kMaxRanks];

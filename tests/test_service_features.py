@@ -525,7 +525,7 @@ except Exception as e:
 def test_clients_killed_at_random_leave_the_daemon_clean(tmp_path):
     """Three rounds of: a few ranks hammer a communicator, one of them is killed without
     warning at a random moment; the others get an error (never a wrong value, never a
-    hang), the same communicator id is usable again in the next round, and at the end the
+    hang), the same communicator id is usable again right afterwards, and at the end the
     daemon holds no client, communicator or allocation."""
     import random
     import signal

@@ -93,7 +93,7 @@ def test_allgather(service, nranks):
         full = out.tensor(torch.float32, per * nranks)
         full.zero_()
         mine = full[r * per:(r + 1) * per]
-        mine.copy_(torch.arange(per, dtype=torch.float32) + r * 1e6)   # values of BASELINE config 1
+        mine.copy_(torch.arange(per, dtype=torch.float32) + r * 1e6)   # rank * 1e6 + index: every element names its origin
         c = M.Communicator(cid, r, nranks, device=r)
         c.all_gather(mine, full)        # in place: send = recv + rank*bytes
         c.destroy()
@@ -106,7 +106,7 @@ def test_allgather(service, nranks):
 
 
 def test_config1_two_rank_reference_shapes(service):
-    """BASELINE configuration 1: 2 ranks, AllReduce sum fp32 count=262144 of N(0,1)
+    """The smallest end-to-end configuration: 2 ranks, AllReduce sum fp32 count=262144 of N(0,1)
     (seed 0) and AllGather fp32 of 65536 per rank with rank*1e6+index."""
     M = service
     if M.backend() != "host":
