@@ -94,3 +94,25 @@ def test_report_table_and_svg(tmp_path):
     assert "| 0.75 |" in lines[0]            # 1 MiB: 0.03 ms NCCL vs 0.04 ms service
     doc = xml.dom.minidom.parse(str(svg))
     assert len(doc.getElementsByTagName("polyline")) == 2
+
+
+import pytest
+
+
+@pytest.mark.parametrize("sync", ["events", "memops"])
+def test_multi_tenant_tool_on_host_backend(sync):
+    """Four applications on overlapping devices, QoS weights, a live reconfiguration of one
+    of them in the middle: every rank finishes without error and the reconfigured
+    application reports the new configuration epoch."""
+    import json
+    res = subprocess.run([sys.executable, "-m", "mccs_b200.utils.multi_tenant", "--iters", "30", "--reconfig-at", "15",
+                          "--bytes", "65536", "--batch", "4", "--host-devices", "4", "--timeout", "200", "--sync", sync],
+                         capture_output=True, text=True, cwd=REPO, env=dict(os.environ, PYTHONPATH=REPO, MCCS_LOG="error"),
+                         timeout=400)
+    assert res.returncode == 0, res.stderr[-3000:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert set(out["apps"]) == {"A", "B", "C", "D"}
+    for name, app in out["apps"].items():
+        assert app["finite"] and app["async_error"] == 0, (name, app)
+    assert out["apps"]["C"]["config_epoch"] == 1 and out["apps"]["A"]["config_epoch"] == 0
+    assert all(t["admitted"] == 35 * 4 for t in out["qos_stats"].values())
