@@ -116,3 +116,41 @@ def test_multi_tenant_tool_on_host_backend(sync):
         assert app["finite"] and app["async_error"] == 0, (name, app)
     assert out["apps"]["C"]["config_epoch"] == 1 and out["apps"]["A"]["config_epoch"] == 0
     assert all(t["admitted"] == 35 * 4 for t in out["qos_stats"].values())
+
+
+def test_bench_script_contract_on_cpu():
+    """bench.py runs end to end without a GPU (host backend, reduced size) and prints the
+    one JSON line with every key of the benchmark contract; the reference arm prints
+    either its result or the reason it is unavailable."""
+    import json
+    import socket
+    env = dict(os.environ, PYTHONPATH=REPO, MCCS_LOG="error")
+    one = subprocess.run([sys.executable, "bench.py", "--steps", "2", "--warmup", "1"], capture_output=True, text=True,
+                         cwd=REPO, env=env, timeout=300)
+    assert one.returncode == 0, one.stderr[-2000:]
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    two = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                          "127.0.0.1", "--master-port", str(port), "bench.py", "--gpus", "2", "--steps", "2", "--warmup", "1"],
+                         capture_output=True, text=True, cwd=REPO, env=env, timeout=300)
+    assert two.returncode == 0, two.stderr[-2000:]
+    for res, n in ((one, 1), (two, 2)):
+        lines = [l for l in res.stdout.splitlines() if l.startswith("{")]
+        assert len(lines) == 1                      # rank 0 prints ONE line
+        out = json.loads(lines[0])
+        for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                    "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches"):
+            assert key in out, key
+        assert out["n_gpus"] == n and out["steps"] == 2 and out["warmup"] >= 3 and out["higher_is_better"] is True
+        assert out["metric"] == "allreduce_algbw_GBps" and out["dtype"] == "bf16" and out["data"] == "synthetic"
+        assert {"model", "global_batch", "seq_len", "parallelism"} <= set(out["config"])
+        assert out["config"]["parallelism"] == f"dp{n}" and out["config"]["verified"] is True
+        assert {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"} <= set(out["e2e"])
+        assert out["e2e"]["h2d_bytes_per_step"] > 0 and out["e2e"]["d2h_bytes_per_step"] > 0
+        assert out["gpu_launches"] == 2 * n
+    ref = subprocess.run([sys.executable, "bench.py", "--impl", "reference", "--steps", "2", "--warmup", "1"],
+                         capture_output=True, text=True, cwd=REPO, env=env, timeout=300)
+    assert ref.returncode == 0
+    r = json.loads([l for l in ref.stdout.splitlines() if l.startswith("{")][-1])
+    assert r["impl"] == "reference" and ("value" in r or "unavailable" in r)
