@@ -70,10 +70,17 @@ def main() -> int:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     n = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
+    # Without a GPU the same script runs over gloo against the host backend (timing on the
+    # host clock; the "nccl" column is then gloo): useful to check the tool, not the numbers.
+    cuda = torch.cuda.is_available()
     dev = local_rank
+    tdev = f"cuda:{dev}" if cuda else "cpu"
+    if cuda:
+        torch.cuda.set_device(local_rank)
     if n > 1:
-        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{dev}"))
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl" if cuda else "gloo", device_id=torch.device(tdev) if cuda else None)
 
     def barrier():
         if n > 1:
@@ -82,7 +89,7 @@ def main() -> int:
     def max_over_ranks(x: float) -> float:
         if n == 1:
             return x
-        t = torch.tensor([x], dtype=torch.float64, device=f"cuda:{dev}")
+        t = torch.tensor([x], dtype=torch.float64, device=tdev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
@@ -114,7 +121,7 @@ def main() -> int:
         nvls = "nvls=on" in stats["backend"]
         print(f"# {describe}: {stats['backend']}", flush=True)
     if n > 1:
-        flag = torch.tensor([1 if nvls else 0], device=f"cuda:{dev}")
+        flag = torch.tensor([1 if nvls else 0], device=tdev)
         dist.broadcast(flag, 0)
         nvls = bool(flag.item())
 
@@ -144,6 +151,13 @@ def main() -> int:
     def time_ms(fn) -> float:
         for _ in range(warm):
             fn()
+        if not cuda:
+            import time
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(iters):
+                fn()
+            return max_over_ranks((time.perf_counter() - t0) * 1e3 / iters)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         stream = torch.cuda.current_stream()
         barrier()
@@ -184,8 +198,8 @@ def main() -> int:
                 else:
                     recv = recv_buf.tensor(tdtype, count * n)
                 if tdtype.is_floating_point:
-                    g = torch.Generator(device=f"cuda:{dev}").manual_seed(rank)
-                    send.copy_((torch.rand(min(count, 1 << 22), generator=g, device=f"cuda:{dev}") * 2 - 1)
+                    g = torch.Generator(device=tdev).manual_seed(rank)
+                    send.copy_((torch.rand(min(count, 1 << 22), generator=g, device=tdev) * 2 - 1)
                                .to(tdtype).repeat((count + (1 << 22) - 1) // (1 << 22))[:count])
                 if n > 1 and not args.no_nccl:
                     src = send
@@ -195,7 +209,7 @@ def main() -> int:
                         def nccl_fn():
                             dist.all_reduce(dst)
                     else:
-                        dst = torch.empty(count * n, dtype=tdtype, device=f"cuda:{dev}")
+                        dst = torch.empty(count * n, dtype=tdtype, device=tdev)
 
                         def nccl_fn():
                             dist.all_gather_into_tensor(dst, src)

@@ -154,3 +154,34 @@ def test_bench_script_contract_on_cpu():
     assert ref.returncode == 0
     r = json.loads([l for l in ref.stdout.splitlines() if l.startswith("{")][-1])
     assert r["impl"] == "reference" and ("value" in r or "unavailable" in r)
+
+
+def test_sweep_tuner_and_report_pipeline_on_cpu(tmp_path, service):
+    """The sweep tool end to end without a GPU (two gloo ranks, host backend): every
+    variant x CTA count is measured through the live-reconfiguration path, the tuning
+    table it writes is accepted by a planner, and the report tool digests its CSV."""
+    import json
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    csv_path, tuning = str(tmp_path / "sweep.csv"), str(tmp_path / "tuning.json")
+    env = dict(os.environ, PYTHONPATH=REPO, MCCS_LOG="error")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                          "127.0.0.1", "--master-port", str(port), "-m", "mccs_b200.utils.sweep", "--mode", "tune", "--dtypes", "bf16",
+                          "--min-bytes", "32K", "--max-bytes", "128K", "--ctas", "2,4", "--iters", "3", "--warmup", "1",
+                          "--out", csv_path, "--tuning", tuning], capture_output=True, text=True, cwd=REPO, env=env, timeout=600)
+    assert res.returncode == 0, res.stderr[-3000:]
+    table = json.load(open(tuning))
+    assert [r[0] for r in table["allreduce"]["2"]] == [32768, 65536, -1]
+    assert all(r[1].startswith("ar_") for r in table["allreduce"]["2"]) and all(r[1].startswith("ag_") for r in table["allgather"]["2"])
+    M = service
+    admin = M.daemon.embedded_admin_port()
+    before = M.admin_request(admin, {"cmd": "tuning_get"})["tuning"]
+    try:
+        assert M.admin_request(admin, {"cmd": "tuning_set", "tuning": table})["status"] == "ok"
+    finally:
+        M.admin_request(admin, {"cmd": "tuning_set", "tuning": before})
+    rep = subprocess.run([sys.executable, "-m", "mccs_b200.utils.report", csv_path], capture_output=True, text=True, cwd=REPO,
+                         env=env, timeout=60)
+    assert rep.returncode == 0 and rep.stdout.count("| allreduce | bf16 | 2 |") == 3 and rep.stdout.count("| allgather |") == 3
