@@ -99,6 +99,7 @@ Config Config::from_value(const Value& root) {
     c.qos_cta_budget = (int)q["cta_budget"].as_int(c.qos_cta_budget);
     c.qos_max_outstanding_bytes = (uint64_t)q["max_outstanding_bytes"].as_int((int64_t)c.qos_max_outstanding_bytes);
     c.qos_active_window_us = (uint64_t)q["active_window_us"].as_int((int64_t)c.qos_active_window_us);
+    c.qos_sm_limit = (int)q["sm_limit"].as_int(c.qos_sm_limit);
     for (const auto& kv : q["tenants"].fields()) {
       QosTenantConfig t;
       t.weight = kv.second["weight"].as_double(1.0);

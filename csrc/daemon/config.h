@@ -66,6 +66,7 @@ struct Config {
   std::map<uint32_t, QosTenantConfig> qos_tenants;
   int qos_cta_budget = 64;       // CTAs shared by contending tenants on one GPU
   uint64_t qos_max_outstanding_bytes = 64ull << 20;  // per tenant, only under contention
+  int qos_sm_limit = 148;          // CTAs of kernels that wait on each other allowed in flight per GPU; 0 = unchecked
   uint64_t qos_active_window_us = 5000;  // a tenant counts as a contender this long after its last request
   // [[comm_patterns_override]]
   std::vector<CommPattern> overrides;

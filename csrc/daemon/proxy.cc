@@ -534,7 +534,9 @@ bool ProxyEngine::admit_slice(Communicator& c, CollSlot& s, int slice) {
   std::lock_guard<std::mutex> g(c.admit_mu);
   if (s.admitted_slices.load(std::memory_order_acquire) > slice) return true;
   const uint64_t bytes = s.batch_len > 1 ? s.batch_bytes : s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
-  QosDecision d = daemon_->qos().admit(c.id, bytes, monotonic_us(), wall_us());
+  // CTAs per GPU: one launch per rank and GPU, or every rank's CTAs on the one GPU.
+  const int ctas = s.plan.dims.ctas * (c.emulated ? c.nranks : 1);
+  QosDecision d = daemon_->qos().admit(c.id, bytes, monotonic_us(), wall_us(), ctas);
   if (d != kQosAdmit) return false;
   s.admitted_slices.store(slice + 1, std::memory_order_release);
   return true;

@@ -14,6 +14,7 @@ void QosArbiter::configure(const Config& cfg) {
   cta_budget_ = cfg.qos_cta_budget > 0 ? cfg.qos_cta_budget : 64;
   max_outstanding_ = cfg.qos_max_outstanding_bytes;
   active_window_us_ = cfg.qos_active_window_us;
+  sm_limit_ = cfg.qos_sm_limit;
   for (const auto& kv : cfg.qos_tenants) tenants_[kv.first].cfg = kv.second;
 }
 
@@ -48,6 +49,7 @@ void QosArbiter::tenant_unregister(uint32_t id) {
   if (it == tenants_.end()) return;
   it->second.registered = false;
   it->second.outstanding_bytes = 0;
+  it->second.inflight_ctas = 0;
   it->second.waiting_since_us = 0;
   it->second.devices.clear();
 }
@@ -124,14 +126,29 @@ void QosArbiter::note_waiting(uint32_t id, uint64_t now_us) {
   if (!t.waiting_since_us) t.waiting_since_us = now_us ? now_us : 1;
 }
 
-QosDecision QosArbiter::admit(uint32_t id, uint64_t bytes, uint64_t now_us, uint64_t wall_us) {
+QosDecision QosArbiter::admit(uint32_t id, uint64_t bytes, uint64_t now_us, uint64_t wall_us, int ctas) {
   std::lock_guard<std::mutex> g(mu_);
   Tenant& me = tenant(id);
   me.last_active_us = now_us;
   if (!me.waiting_since_us) me.waiting_since_us = now_us ? now_us : 1;
+  // Residency comes first and holds even with the arbiter switched off: it is what keeps
+  // kernels that wait for each other from starving each other of SMs.
+  if (sm_limit_ > 0 && ctas > 0) {
+    int resident = 0;
+    for (const auto& kv : tenants_)
+      if (kv.first != id && kv.second.outstanding_bytes > 0 && shares_device(me, kv.second)) resident += kv.second.inflight_ctas;
+    // Launches of one tenant run one after another: only a launch that needs more CTAs
+    // than the tenant already has in flight adds to what must be resident.
+    const bool grows = me.outstanding_bytes == 0 || ctas > me.inflight_ctas;
+    if (grows && resident > 0 && resident + ctas > sm_limit_) {
+      me.deferred_residency++;
+      return kQosDeferResidency;
+    }
+  }
   auto grant = [&]() {
     me.vtime += (double)bytes / me.cfg.weight;
     me.outstanding_bytes += bytes;
+    me.inflight_ctas = std::max(me.inflight_ctas, ctas);
     me.waiting_since_us = 0;
     me.round++;
     me.admitted++;
@@ -181,6 +198,7 @@ void QosArbiter::complete(uint32_t id, uint64_t bytes) {
   std::lock_guard<std::mutex> g(mu_);
   Tenant& t = tenant(id);
   t.outstanding_bytes = t.outstanding_bytes > bytes ? t.outstanding_bytes - bytes : 0;
+  if (t.outstanding_bytes == 0) t.inflight_ctas = 0;
 }
 
 Value QosArbiter::stats() {
@@ -201,6 +219,8 @@ Value QosArbiter::stats() {
     v.set("deferred_window", (int64_t)t.deferred_window);
     v.set("deferred_backlog", (int64_t)t.deferred_backlog);
     v.set("deferred_fairness", (int64_t)t.deferred_fair);
+    v.set("deferred_residency", (int64_t)t.deferred_residency);
+    v.set("inflight_ctas", t.inflight_ctas);
     v.set("outstanding_bytes", (int64_t)t.outstanding_bytes);
     v.set("vtime", t.vtime);
     ts.set(std::to_string(kv.first), v);

@@ -17,7 +17,12 @@
 //     one, so a waiting tenant gets the links between slices;
 //   * windows: the Allow/Deny interval schedule of the reference, evaluated on the
 //     same `now % epoch` clock;
-//   * stream priority for tenants marked high priority.
+//   * stream priority for tenants marked high priority;
+//   * residency: the kernels of one collective wait for each other across GPUs, so all
+//     their CTAs must get an SM. A launch is held back while its CTAs plus those of the
+//     other tenants' kernels in flight on a shared GPU exceed the SM count: otherwise two
+//     tenants whose kernels reached two GPUs in opposite order could each hold the SMs
+//     the other one's missing CTAs need, until the device-side bound ends both.
 // All decisions are host-side and take the clock as an argument (testable).
 #pragma once
 #include <stdint.h>
@@ -32,7 +37,7 @@
 
 namespace mccs {
 
-enum QosDecision { kQosAdmit = 0, kQosDeferWindow = 1, kQosDeferBacklog = 2, kQosDeferFairness = 3 };
+enum QosDecision { kQosAdmit = 0, kQosDeferWindow = 1, kQosDeferBacklog = 2, kQosDeferFairness = 3, kQosDeferResidency = 4 };
 
 class QosArbiter {
  public:
@@ -55,7 +60,8 @@ class QosArbiter {
 
   // A planned collective (or slice) asks to launch. `wall_us` is the Unix clock used
   // for the window schedule, `now_us` a monotonic clock.
-  QosDecision admit(uint32_t id, uint64_t bytes, uint64_t now_us, uint64_t wall_us);
+  // `ctas`: CTAs the launch puts on each of the tenant's GPUs (0 = unknown, not counted).
+  QosDecision admit(uint32_t id, uint64_t bytes, uint64_t now_us, uint64_t wall_us, int ctas = 0);
   // Registers that a collective of `id` is planned and waiting for admission.
   void note_waiting(uint32_t id, uint64_t now_us);
   void complete(uint32_t id, uint64_t bytes);
@@ -70,6 +76,8 @@ class QosArbiter {
     bool registered = false;
     double vtime = 0;
     uint64_t outstanding_bytes = 0;
+    int inflight_ctas = 0;           // most CTAs any launch in flight uses per GPU (a tenant's launches run one after another)
+    uint64_t deferred_residency = 0;
     uint64_t last_active_us = 0;
     uint64_t waiting_since_us = 0;   // 0: nothing waiting
     uint64_t round = 0;
@@ -88,6 +96,7 @@ class QosArbiter {
   int cta_budget_ = 64;
   uint64_t max_outstanding_ = 64ull << 20;
   uint64_t active_window_us_ = 5000;   // a tenant counts as active this long after its last request
+  int sm_limit_ = 148;                 // CTAs of waiting-on-each-other kernels that may be in flight per GPU (0 = unchecked)
 };
 
 }  // namespace mccs

@@ -329,6 +329,26 @@ static void test_qos() {
   r.set_enabled(false);
   CHECK(r.admit(1, 1024, 12, 5000) == kQosAdmit);
   CHECK(r.stats()["tenants"]["1"]["deferred_window"].as_int() == 1);
+  // Residency: kernels that wait on each other must all get an SM. Tenants 1 and 2 share
+  // GPU 0, tenant 3 sits on other GPUs; the limit is 148 CTAs per GPU.
+  QosArbiter s;
+  s.configure(cfg);
+  s.set_enabled(false);                       // the rule holds with the arbiter switched off, too
+  s.tenant_register(1, {0, 1});
+  s.tenant_register(2, {0, 2});
+  s.tenant_register(3, {4, 5});
+  CHECK(s.admit(1, 1 << 20, 1, 0, 128) == kQosAdmit);
+  CHECK(s.admit(2, 1 << 20, 1, 0, 64) == kQosDeferResidency);    // 128 + 64 > 148
+  CHECK(s.admit(2, 1 << 20, 1, 0, 20) == kQosAdmit);             // 128 + 20 fits
+  CHECK(s.admit(3, 1 << 20, 1, 0, 128) == kQosAdmit);            // no GPU in common with anybody
+  CHECK(s.admit(1, 1 << 20, 2, 0, 128) == kQosAdmit);            // same size as what tenant 1 already has in flight
+  CHECK(s.admit(2, 1 << 20, 2, 0, 21) == kQosDeferResidency);    // growing to 21 would make 149
+  s.complete(1, 2 << 20);
+  CHECK(s.admit(2, 1 << 20, 3, 0, 128) == kQosAdmit);            // tenant 1 has nothing in flight any more
+  CHECK(s.admit(1, 1 << 20, 3, 0, 64) == kQosDeferResidency);
+  s.complete(2, 2 << 20);
+  CHECK(s.admit(1, 1 << 20, 4, 0, 200) == kQosAdmit);            // alone, even more CTAs than SMs are its own business
+  CHECK(s.stats()["tenants"]["2"]["deferred_residency"].as_int() == 2);
 }
 
 static void test_misc() {
