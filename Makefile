@@ -36,7 +36,7 @@ $(OBJ)/%.o: csrc/%.cc $(HDRS)
 
 $(EMU_OBJ): csrc/device/emulated_kernels.cc $(wildcard csrc/tests/sim/*.h) $(HDRS)
 	@mkdir -p $(dir $@)
-	$(CXX) $(CXXFLAGS) -O1 -Wno-unknown-pragmas -Wno-sign-compare -Wno-maybe-uninitialized -c $< -o $@
+	$(CXX) $(CXXFLAGS) -O1 -g0 -Wno-unknown-pragmas -Wno-sign-compare -Wno-maybe-uninitialized -c $< -o $@
 
 $(OBJ)/device/cuda_backend.o: csrc/device/cuda_backend.cu $(HDRS)
 	@mkdir -p $(dir $@)
