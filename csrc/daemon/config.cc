@@ -115,7 +115,8 @@ Config Config::from_value(const Value& root) {
     check_keys(b,
                {"transport", "nvls", "vmm", "sync", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
                 "host_devices", "force_host_backend", "idle_sleep_us", "idle_spin_us", "pin_threads", "init_timeout_ms", "fuse_allreduce",
-                "single_through_fused", "skip_start_barrier", "kernel_writes_done", "host_kernels"},
+                "single_through_fused", "skip_start_barrier", "kernel_writes_done", "host_kernels",
+                "hybrid_nvls_permille", "hybrid_nvls_ctas"},
                "[b200]");
     c.transport = b["transport"].as_string(c.transport);
     if (c.transport != "auto" && c.transport != "nvlink" && c.transport != "host_staged")
@@ -138,6 +139,10 @@ Config Config::from_value(const Value& root) {
     c.idle_spin_us = (int)b["idle_spin_us"].as_int(c.idle_spin_us);
     c.pin_threads = b["pin_threads"].as_bool(c.pin_threads);
     c.init_timeout_ms = (uint64_t)b["init_timeout_ms"].as_int((int64_t)c.init_timeout_ms);
+    c.hybrid_nvls_permille = (int)b["hybrid_nvls_permille"].as_int(c.hybrid_nvls_permille);
+    c.hybrid_nvls_ctas = (int)b["hybrid_nvls_ctas"].as_int(c.hybrid_nvls_ctas);
+    if (c.hybrid_nvls_permille < 0 || c.hybrid_nvls_permille > 1000 || c.hybrid_nvls_ctas < 0 || c.hybrid_nvls_ctas > kMaxCtas)
+      throw std::runtime_error("b200.hybrid_nvls_permille must be 0..1000 and hybrid_nvls_ctas 0..128");
     c.single_through_fused = b["single_through_fused"].as_bool(c.single_through_fused);
     c.skip_start_barrier = b["skip_start_barrier"].as_bool(c.skip_start_barrier);
     c.kernel_writes_done = b["kernel_writes_done"].as_bool(c.kernel_writes_done);

@@ -91,6 +91,8 @@ struct Config {
   int fuse_allreduce = 1;
   // Experiments on the per-call floor; they act on launches that go through the fused
   // kernels only (kernels/batch.cuh) and are all off by default.
+  int hybrid_nvls_permille = 750;     // ar_hybrid: share of the message that goes through the switch (1/1000)
+  int hybrid_nvls_ctas = 8;           // ar_hybrid: CTAs that feed the switch; the others exchange the rest by peer copies
   bool single_through_fused = false;  // a lone two-shot AllReduce also uses the fused kernel (one member)
   bool skip_start_barrier = false;    // no barrier before the first load when the host has gated every rank
   bool kernel_writes_done = false;    // the kernel's last CTA releases the caller's stream itself

@@ -144,7 +144,7 @@ std::string Planner::infeasible(int variant, const PlanInput& in) {
   switch (variant) {
     case kLocalCopy:
       return in.nranks == 1 ? "" : "local copy needs a single-rank communicator";
-    case kArOneShot: case kArTwoShot: case kArRing: case kArNvlsOne: case kArNvlsTwo:
+    case kArOneShot: case kArTwoShot: case kArRing: case kArNvlsOne: case kArNvlsTwo: case kArHybrid:
       if (!is_ar) return "all-reduce variant requested for an all-gather";
       break;
     case kAgPull: case kAgPush: case kAgNvls: case kAgRing:
@@ -172,6 +172,7 @@ std::string Planner::infeasible(int variant, const PlanInput& in) {
 }
 
 Plan Planner::plan(const PlanInput& in) const {
+  constexpr uint64_t MB_ = 1024 * 1024;
   Plan p;
   p.bytes = message_bytes(in);
   if (in.nranks < 1 || in.nranks > kMaxRanks) { p.status = proto::kErrInvalidArgument; return p; }
@@ -211,6 +212,9 @@ Plan Planner::plan(const PlanInput& in) const {
     const uint64_t MB = 1024 * 1024;
     ctas = p.bytes <= 256 * 1024 ? 4 : p.bytes <= 4 * MB ? 16 : p.bytes <= 64 * MB ? 32 : 64;
   }
+  // The hybrid kernel runs two data paths side by side: the peer-copy part wants as many
+  // CTAs as the plain two-shot exchange on top of the few that feed the switch.
+  if (chosen == kArHybrid && !(e && e->variant == chosen)) ctas = p.bytes <= 4 * MB_ ? 24 : 72;
   if (variant_is_ring(chosen)) {
     ctas = in.ring_channels > 0 ? in.ring_channels : 1;
     // Small messages do not fill several channels: drop to one, then shrink the CTA,
@@ -229,8 +233,8 @@ Plan Planner::plan(const PlanInput& in) const {
   if (!variant_is_ring(chosen) && (uint64_t)ctas > packs) ctas = (int)packs;
   p.dims.ctas = ctas;
   p.dims.threads = threads;
-  p.needs_mc_send = chosen == kArNvlsOne || chosen == kArNvlsTwo;
-  p.needs_mc_recv = chosen == kArNvlsTwo || chosen == kAgNvls;
+  p.needs_mc_send = chosen == kArNvlsOne || chosen == kArNvlsTwo || chosen == kArHybrid;
+  p.needs_mc_recv = chosen == kArNvlsTwo || chosen == kAgNvls || chosen == kArHybrid;
   return p;
 }
 

@@ -578,6 +578,11 @@ void ProxyEngine::fill_args(Communicator& c, CollSlot& s, int rank, int slice, C
   }
   if (s.plan.needs_mc_send) a.mc_send = (const void*)(s.mc_send[rank] + s.ops[rank].send_off + off);
   if (s.plan.needs_mc_recv) a.mc_recv = (void*)(s.mc_recv[rank] + s.ops[rank].recv_off + off);
+  if (s.plan.variant == kArHybrid) {
+    const Config& cfg = daemon_->config();
+    const int nvls_ctas = std::min(cfg.hybrid_nvls_ctas, std::max(s.plan.dims.ctas - 1, 0));
+    a.unroll_hint = (int32_t)(((uint32_t)nvls_ctas << 16) | (uint32_t)cfg.hybrid_nvls_permille);
+  }
   a.fifo_slot_bytes = c.fifo_slot_bytes;
   memcpy(a.ring, s.ring, sizeof a.ring);
   for (int ch = 0; ch < kMaxRingChannels; ch++) a.ring_step_base[ch] = s.ring_step_base[ch];

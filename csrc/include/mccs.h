@@ -79,7 +79,8 @@ typedef enum {
 typedef enum {
   mccsAlgoAuto = 0, mccsAlgoArOneShot = 1, mccsAlgoArTwoShot = 2, mccsAlgoArNvlsOneShot = 3,
   mccsAlgoArNvlsTwoShot = 4, mccsAlgoArRing = 5, mccsAlgoAgPull = 6, mccsAlgoAgPush = 7,
-  mccsAlgoAgNvls = 8, mccsAlgoAgRing = 9
+  mccsAlgoAgNvls = 8, mccsAlgoAgRing = 9, mccsAlgoLocalCopy = 10,
+  mccsAlgoArHybrid = 11   /* part through the switch, part by peer copies, in one kernel */
 } mccsAlgo_t;
 
 /* Connects to the daemon. Optional: every other call connects on first use with

@@ -46,7 +46,8 @@ enum Variant : int32_t {
   kAgNvls = 8,       // multimem.st of the own shard
   kAgRing = 9,       // FIFO-staged ring
   kLocalCopy = 10,   // single-rank communicator: device copy (or nothing in place)
-  kNumVariants = 11
+  kArHybrid = 11,    // head of the buffer through the switch (multimem), rest by peer loads/stores, in one kernel
+  kNumVariants = 12
 };
 
 // Error codes written by kernels into the per-rank status word.
@@ -100,7 +101,7 @@ struct CollArgs {
   uint32_t epoch;          // first barrier value this launch may use (uses epoch, epoch+1)
   uint64_t timeout_ns;     // bound for every device-side wait
   int32_t trace;           // 1: record globaltimer start/end into the status block
-  int32_t unroll_hint;     // reserved (keeps the layout); the kernels choose their unrolling from the rank count
+  int32_t unroll_hint;     // ar_hybrid only: low 16 bits = share of the message for the multimem part (1/1000), high 16 bits = its CTAs
   // --- buffers (unicast addresses valid on every GPU of the communicator) -----
   const void* send[kMaxRanks];
   void* recv[kMaxRanks];
@@ -175,11 +176,12 @@ inline const char* variant_name(int v) {
     case kAgNvls: return "ag_nvls";
     case kAgRing: return "ag_ring";
     case kLocalCopy: return "local_copy";
+    case kArHybrid: return "ar_hybrid";
   }
   return "?";
 }
 
-inline bool variant_is_nvls(int v) { return v == kArNvlsOne || v == kArNvlsTwo || v == kAgNvls; }
+inline bool variant_is_nvls(int v) { return v == kArNvlsOne || v == kArNvlsTwo || v == kAgNvls || v == kArHybrid; }
 inline bool variant_is_ring(int v) { return v == kArRing || v == kAgRing; }
 
 // Number of ring steps one channel consumes for a collective. Every rank and every

@@ -2,6 +2,7 @@
 // scheme as inst_dtype.cu): instantiates the fused AllReduce kernels and exports their
 // lookup function.
 #include "batch.cuh"
+#include "hybrid.cuh"
 
 namespace mccs {
 namespace dev {
@@ -11,6 +12,10 @@ namespace dev {
 
 extern "C" const void* MCCS_CAT(mccs_kfn_batch_, MCCS_TNAME)(int variant, int op) {
 #ifdef MCCS_NVLS
+  if (variant == kArHybrid) {
+    if (op != kSum && op != kSumPostDiv) return nullptr;
+    return (const void*)&ar_hybrid_kernel<MCCS_T>;
+  }
   if (variant == kArNvlsTwo) {
     if (op != kSum && op != kSumPostDiv) return nullptr;
     return (const void*)&ar_nvls_batch_kernel<MCCS_T>;

@@ -28,7 +28,10 @@ const void* mccs_kfn_batch_bf16(int, int);
 
 namespace mccs {
 
+const void* batch_kernel_function(int variant, int dtype, int op);
+
 const void* kernel_function(int variant, int dtype, int op) {
+  if (variant == kArHybrid) return batch_kernel_function(variant, dtype, op);   // lives with the newer kernels
   switch (variant) {
     case kAgPull: case kAgPush: case kAgNvls: case kAgRing: case kLocalCopy:
       return mccs_kfn_untyped(variant);

@@ -200,6 +200,16 @@ static void test_planner() {
   pl = p.plan(in);
   CHECK(pl.variant != kAgPull && !pl.note.empty());
   in.requested_variant = kAuto;
+  // the hybrid variant is only ever taken on request, needs both multicast mappings, and
+  // falls back (with a note) where the switch path is not available
+  in.count = 64u << 20; in.nvls_possible = true; in.requested_variant = kArHybrid;
+  pl = p.plan(in);
+  CHECK(pl.status == 0 && pl.variant == kArHybrid && pl.needs_mc_send && pl.needs_mc_recv && pl.dims.ctas == 72);
+  in.nvls_possible = false;
+  pl = p.plan(in);
+  CHECK(pl.variant == kArTwoShot && !pl.note.empty());
+  in.nvls_possible = true; in.requested_variant = kAuto;
+  CHECK(Planner::variant_from_name("ar_hybrid") == kArHybrid);
   // QoS cap and override
   in.count = 256u << 20; in.cta_cap = 5;
   CHECK(p.plan(in).dims.ctas == 5);

@@ -21,6 +21,7 @@
 
 #define MCCS_UNTYPED_KERNELS 1
 #include "../kernels/batch.cuh"
+#include "../kernels/hybrid.cuh"
 
 using namespace mccs;
 using namespace mccs::dev;
@@ -257,6 +258,45 @@ void allgather_case(World& w, int variant, size_t bytes, int ctas, int threads, 
   }
   if (bad) fprintf(stderr, "FAILED %s (n=%d bytes=%zu ctas=%d emulated=%d offset=%zu in_place=%d)\n", what, n, bytes, ctas,
                    (int)emulated, offset, (int)in_place);
+  CHECK(bad == 0);
+}
+
+// The hybrid kernel: `permille` of the message through the (emulated) switch on the first
+// `nvls_ctas` CTAs, the rest by peer loads/stores on the others.
+template <typename T>
+void hybrid_case(World& w, size_t count, int ctas, int nvls_ctas, int permille, int threads, bool emulated, bool in_place, int op) {
+  const int n = w.n;
+  Buffers<T> b(n, count, 0);
+  std::vector<std::vector<double>> in((size_t)n, std::vector<double>(count));
+  for (int r = 0; r < n; r++)
+    for (size_t i = 0; i < count; i++) {
+      b.send(r)[i] = Dt<T>::to((double)((int)((i * 5 + (size_t)r * 7) % 13) - 6));
+      in[(size_t)r][i] = Dt<T>::from(b.send(r)[i]);
+    }
+  CollArgs a = w.base(Dt<T>::id, op, kArHybrid, count, emulated);
+  a.unroll_hint = (int32_t)(((uint32_t)nvls_ctas << 16) | (uint32_t)permille);
+  for (int r = 0; r < n; r++) { a.send[r] = b.send(r); a.recv[r] = in_place ? (void*)b.send(r) : (void*)b.recv(r); }
+  sim_mc_regions().clear();
+  SimMcRegion ms{0x100000000000ull, (count * sizeof(T) + 15) / 16 * 16, {}}, mr{0x200000000000ull, (count * sizeof(T) + 15) / 16 * 16, {}};
+  for (int r = 0; r < n; r++) { ms.backing.push_back((char*)a.send[r]); mr.backing.push_back((char*)a.recv[r]); }
+  sim_mc_regions().push_back(ms);
+  sim_mc_regions().push_back(mr);
+  a.mc_send = (const void*)ms.base;
+  a.mc_recv = (void*)mr.base;
+  run_all(ar_hybrid_kernel<T>, a, n, ctas, threads, emulated);
+  int bad = 0;
+  const double tol = tolerance<T>(n);
+  for (size_t i = 0; i < count && bad < 4; i++) {
+    double want = 0;
+    for (int r = 0; r < n; r++) want += in[(size_t)r][i];
+    if (op == kSumPostDiv) want /= n;
+    for (int r = 0; r < n; r++)
+      if (fabs(Dt<T>::from(((T*)a.recv[r])[i]) - want) > tol + (tol > 0 ? 1e-3 * fabs(want) : 0)) bad++;
+  }
+  for (int r = 1; r < n; r++) bad += memcmp(a.recv[0], a.recv[r], count * sizeof(T)) != 0;
+  for (int r = 0; r < n; r++) bad += w.status[(size_t)r]->error != 0 || w.status[(size_t)r]->done_seq != a.seq;
+  if (bad) fprintf(stderr, "FAILED hybrid (n=%d count=%zu ctas=%d nvls_ctas=%d permille=%d emulated=%d in_place=%d)\n", n, count, ctas,
+                   nvls_ctas, permille, (int)emulated, (int)in_place);
   CHECK(bad == 0);
 }
 
@@ -592,6 +632,15 @@ int main() {
       allgather_case(w, kAgPull, 333, ctas, threads, emulated, 5, false, "ag pull unaligned");
       allgather_case(w, kAgPush, 333, ctas, threads, emulated, 5, false, "ag push unaligned");
       allgather_case(w, kAgRing, 60000, ctas, threads, emulated, 0, false, "ag ring, many loops");
+      // --- hybrid: part through the switch, part around it ----------------------------------------
+      for (int permille : {0, 250, 750, 1000}) {
+        hybrid_case<float>(w, 4099, 4, 1, permille, threads, emulated, false, kSum);
+        hybrid_case<__nv_bfloat16>(w, 10007, 4, 2, permille, threads, emulated, true, kSum);
+      }
+      hybrid_case<float>(w, 3, 3, 1, 750, threads, emulated, false, kSum);            // less than one pack
+      hybrid_case<float>(w, 2048, 4, 0, 750, threads, emulated, false, kSumPostDiv);  // no CTA feeds the switch
+      hybrid_case<float>(w, 2048, 2, 2, 750, threads, emulated, true, kSumPostDiv);   // every CTA feeds the switch
+      hybrid_case<__half>(w, 8191, 5, 2, 600, threads, emulated, false, kSum);
       // --- fused launches --------------------------------------------------------------------
       batch_case<float>(w, false, 5, ctas, threads, emulated, false, false);
       batch_case<float>(w, false, 8, ctas, threads, emulated, true, true);

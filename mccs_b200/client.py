@@ -32,7 +32,7 @@ OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "premulsum": 4, "avg": 5, "sumpo
 
 ALGOS = {
     "auto": 0, "ar_oneshot": 1, "ar_twoshot": 2, "ar_nvls_oneshot": 3, "ar_nvls_twoshot": 4,
-    "ar_ring": 5, "ag_pull": 6, "ag_push": 7, "ag_nvls": 8, "ag_ring": 9, "local_copy": 10,
+    "ar_ring": 5, "ag_pull": 6, "ag_push": 7, "ag_nvls": 8, "ag_ring": 9, "local_copy": 10, "ar_hybrid": 11,
 }
 ALGO_NAMES = {v: k for k, v in ALGOS.items()}
 

@@ -31,7 +31,7 @@ import torch.distributed as dist
 import mccs_b200 as M
 from mccs_b200.utils.timing import bus_factor
 
-AR_ALGOS = ["ar_oneshot", "ar_twoshot", "ar_nvls_oneshot", "ar_nvls_twoshot", "ar_ring"]
+AR_ALGOS = ["ar_oneshot", "ar_twoshot", "ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid", "ar_ring"]
 AG_ALGOS = ["ag_pull", "ag_push", "ag_nvls", "ag_ring"]
 DTYPES = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
 
@@ -173,7 +173,7 @@ def main() -> int:
     best: Dict[Tuple[str, int], Tuple[float, str, int]] = {}
     for coll in colls:
         is_ar = coll == "allreduce"
-        algos = [a for a in (AR_ALGOS if is_ar else AG_ALGOS) if nvls or "nvls" not in a]
+        algos = [a for a in (AR_ALGOS if is_ar else AG_ALGOS) if nvls or ("nvls" not in a and a != "ar_hybrid")]
         if args.algos:
             algos = [a for a in algos if a in args.algos.split(",")]
         if args.mode == "final":
