@@ -1,0 +1,91 @@
+"""Collective operations on tensors, functional form.
+
+``all_reduce`` / ``all_gather`` are the stream-ordered collectives of a
+:class:`mccs_b200.Communicator` (the reference's ``libmccs::all_reduce`` /
+``all_gather``, src/libmccs/src/collectives.rs:15-138) written as plain functions, with
+the kernel variant as a keyword: what runs is one of the hand-written sm_100a kernels of
+``csrc/kernels`` (``VARIANTS``), launched by the daemon.
+
+``local_all_reduce_no_alloc`` calls the kernels directly, without daemon or communicator:
+the allocation-free single-GPU AllReduce of ``csrc/include/mccs_noalloc.h``.
+
+On a machine with a GPU these functions never fall back to PyTorch code: a missing
+native library is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from .. import _lib
+from ..client import ALGOS, DTYPES, Communicator
+
+VARIANTS = {
+    "auto": "the planner's choice from the measured size -> (variant, CTAs) table",
+    "ar_oneshot": "AllReduce: every rank loads all peers' data over NVLink, reduces in fp32, stores locally (small messages, out of place)",
+    "ar_twoshot": "AllReduce: rank r reduces shard r from all peers (loads) and stores it into every rank's output",
+    "ar_nvls_oneshot": "AllReduce: multimem.ld_reduce of the whole buffer on every rank (sum in the NVSwitch)",
+    "ar_nvls_twoshot": "AllReduce: multimem.ld_reduce of the own shard + multimem.st broadcast",
+    "ar_hybrid": "AllReduce: head of the buffer through the switch, the rest by peer loads/stores, in one kernel",
+    "ar_ring": "AllReduce: FIFO-staged ring with a configurable order per channel (also the host-staged transport)",
+    "ag_pull": "AllGather: every rank loads its peers' shards",
+    "ag_push": "AllGather: every rank stores its shard into every peer",
+    "ag_nvls": "AllGather: multimem.st of the own shard",
+    "ag_ring": "AllGather: FIFO-staged ring",
+    "local_copy": "single-rank communicator: device copy",
+}
+assert set(VARIANTS) == set(ALGOS)
+
+
+def all_reduce(comm: Communicator, send: torch.Tensor, recv: Optional[torch.Tensor] = None, *, op: str = "sum",
+               scale: float = 1.0, algo: str = "auto", stream=None) -> torch.Tensor:
+    """AllReduce of ``send`` into ``recv`` (in place when ``recv`` is None) over ``comm``;
+    both tensors live in service memory (:class:`mccs_b200.Buffer`). Returns the output
+    tensor; like a kernel launch, the call returns before the result exists."""
+    comm.all_reduce(send, recv, op=op, scale=scale, algo=algo, stream=stream)
+    return send if recv is None else recv
+
+
+def all_gather(comm: Communicator, send: torch.Tensor, recv: torch.Tensor, *, algo: str = "auto", stream=None) -> torch.Tensor:
+    """AllGather: rank r's ``send`` lands at ``recv[r * send.numel():]`` on every rank."""
+    comm.all_gather(send, recv, algo=algo, stream=stream)
+    return recv
+
+
+def local_all_reduce_no_alloc(inputs: Sequence[torch.Tensor], outputs: Optional[Sequence[torch.Tensor]] = None,
+                              stream=None) -> Sequence[torch.Tensor]:
+    """Sum of up to 8 equally shaped f32 / f16 / bf16 tensors on the CURRENT CUDA device,
+    written to every output (in place when ``outputs`` is None), by the two-shot kernel in
+    one cooperative launch. Allocates nothing, neither here nor in the native code: usable
+    while a memory pool is frozen. Overlapping calls on one device race (they share one
+    scratch array); make the first call on a device outside stream capture."""
+    if not inputs:
+        raise ValueError("no tensors")
+    outs = list(inputs) if outputs is None else list(outputs)
+    first = inputs[0]
+    if len(outs) != len(inputs) or len(inputs) > 8:
+        raise ValueError("need as many outputs as inputs, at most 8")
+    for t in list(inputs) + outs:
+        if not t.is_cuda or t.device != first.device or t.dtype != first.dtype or t.numel() != first.numel() or not t.is_contiguous():
+            raise ValueError("tensors must be contiguous CUDA tensors of one device, dtype and size")
+    if first.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError("float32, float16 or bfloat16 only")
+    lib = _lib.daemon_lib()          # raises when the native library is missing: no silent fallback
+    fn = lib.mccsLocalAllReduceNoAlloc
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_size_t,
+                   ctypes.c_int, ctypes.c_void_p]
+    n = len(inputs)
+    ins = (ctypes.c_void_p * n)(*[t.data_ptr() for t in inputs])
+    ous = (ctypes.c_void_p * n)(*[t.data_ptr() for t in outs])
+    s = torch.cuda.current_stream(first.device) if stream is None else stream
+    with torch.cuda.device(first.device):
+        rc = fn(ins, ous, n, first.numel(), DTYPES[first.dtype], ctypes.c_void_p(s.cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"mccsLocalAllReduceNoAlloc failed with CUDA error {rc}")
+    return outs
+
+
+__all__ = ["VARIANTS", "all_reduce", "all_gather", "local_all_reduce_no_alloc"]

@@ -198,3 +198,31 @@ def test_buffer_must_come_from_the_service(service):
     with pytest.raises(M.client._lib.MccsError):
         c.all_reduce(t)
     c.destroy()
+
+
+def test_functional_ops_over_a_communicator(service):
+    """`mccs_b200.ops`: the collectives as plain functions, every variant described."""
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    from mccs_b200 import ops
+    assert set(ops.VARIANTS) == set(M.client.ALGOS)
+    n, cid = 3, fresh_comm_id()
+
+    def rank_fn(r):
+        a, b, d = M.Buffer(4096, r), M.Buffer(4096, r), M.Buffer(4096, r)
+        x = a.tensor(torch.float32, 1000)
+        x.fill_(float(r + 1))
+        c = M.Communicator(cid, r, n, device=r)
+        y = ops.all_reduce(c, x, b.tensor(torch.float32, 1000), algo="ar_twoshot")
+        z = ops.all_reduce(c, x, op="max")                       # in place: returns the input tensor
+        assert z is x
+        g = ops.all_gather(c, x[:16], d.tensor(torch.float32, 16 * n), algo="ag_pull")
+        out = (y.clone(), x.clone(), g.clone())
+        c.destroy()
+        return out
+
+    for y, x, g in run_ranks(n, rank_fn):
+        assert torch.all(y == 6.0) and torch.all(x == 3.0) and torch.all(g == 3.0)
+    with pytest.raises(ValueError):
+        ops.local_all_reduce_no_alloc([torch.zeros(8)])          # CPU tensors are refused, not silently summed

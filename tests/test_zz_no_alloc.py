@@ -84,3 +84,21 @@ def test_no_alloc_entry_rejects_what_it_cannot_do(service):
     assert fn(one, one, 0, 16, 7, None) != 0
     assert fn(one, one, 1, 16, 7, None) == 0          # single buffer in place: nothing to do, still valid
     torch.cuda.synchronize()
+
+
+def test_ops_binding_of_the_no_alloc_entry(service):
+    """The same entry point through `mccs_b200.ops`, in place, and its argument checks."""
+    from mccs_b200 import ops
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(5)
+    xs = [(torch.rand(70001, generator=g) * 2 - 1).cuda() for _ in range(3)]
+    ref = torch.stack([x.double() for x in xs]).sum(0)
+    outs = ops.local_all_reduce_no_alloc(xs)
+    torch.cuda.synchronize()
+    assert all(o is x for o, x in zip(outs, xs))
+    for x in xs:
+        assert torch.allclose(x.double(), ref, rtol=1e-5, atol=1e-5)
+    with pytest.raises(ValueError):
+        ops.local_all_reduce_no_alloc([torch.zeros(4, device="cuda", dtype=torch.int32)])
+    with pytest.raises(ValueError):
+        ops.local_all_reduce_no_alloc([torch.zeros(4, device="cuda"), torch.zeros(5, device="cuda")])
