@@ -60,9 +60,9 @@ $(OUT)/libmccs_daemon.so: $(HOST_OBJS) $(EMU_OBJ) $(CUDA_OBJS) csrc/exports.map
 	@mkdir -p $(OUT)
 	$(NVCC) $(ARCH) -shared -cudart static -Xlinker --version-script=csrc/exports.map -o $@ $(HOST_OBJS) $(EMU_OBJ) $(CUDA_OBJS) $(LDLIBS)
 
-$(OUT)/libmccs.so: $(SHIM_OBJS) csrc/exports.map
+$(OUT)/libmccs.so: $(SHIM_OBJS) $(EMU_OBJ) csrc/exports.map
 	@mkdir -p $(OUT)
-	$(CXX) -shared -Wl,--version-script=csrc/exports.map -o $@ $(SHIM_OBJS) $(LDLIBS)
+	$(CXX) -shared -Wl,--version-script=csrc/exports.map -o $@ $(SHIM_OBJS) $(EMU_OBJ) $(LDLIBS)
 
 $(OUT)/libmccs_preload.so: $(OBJ)/shim/preload.o $(OUT)/libmccs.so
 	$(CXX) -shared -Wl,--version-script=csrc/exports_preload.map -o $@ $(OBJ)/shim/preload.o -L$(OUT) -lmccs -Wl,-rpath,'$$ORIGIN' $(LDLIBS)

@@ -17,7 +17,7 @@ namespace mccs {
 namespace proto {
 
 constexpr uint32_t kMagic = 0x5343434du;  // "MCCS"
-constexpr uint32_t kVersion = 5;
+constexpr uint32_t kVersion = 6;
 constexpr uint32_t kWqDepth = 64;
 constexpr uint32_t kCqDepth = 64;
 constexpr uint32_t kWrBytes = 128;
@@ -33,6 +33,9 @@ enum MsgType : uint32_t {
   kRegisterStream = 11, kRegisterStreamReply = 12,
   kCommQuery = 13, kCommQueryReply = 14,
   kGoodbye = 15,
+  // client-side launch: a member of a communicator maps what its kernels must address
+  kMapScratch = 16, kMapScratchReply = 17,   // a rank's signal pad / status block / FIFOs
+  kMapMem = 18, kMapMemReply = 19,           // a peer's allocation named in a plan
 };
 
 enum Status : int32_t {
@@ -143,6 +146,8 @@ struct CommInitReply {
   uint64_t sync_size;                     // 0: no sync page, events are used
   uint64_t sync_daemon_va;
   uint8_t sync_ipc_handle[kIpcHandleBytes];
+  uint32_t launch_mode;                   // LaunchMode
+  uint32_t fifo_slot_bytes;               // client-side launch: geometry of the ring FIFOs
 };
 
 struct CommDestroyReq { Header h; uint64_t comm_handle; };
@@ -157,6 +162,19 @@ struct RegisterStreamReq {
   uint64_t event_raw;
 };
 struct RegisterStreamReply { Header h; uint64_t stream_id; };
+
+// Who launches the kernels of a communicator. The reference's service always does
+// (src/mccs/src/proxy/plan.rs:637-669). With kLaunchClient the daemon still collects the
+// ranks' requests, plans, admits and hands out barrier epochs and tickets, but gives the
+// finished plan back to each rank's client library, which launches the kernel on the
+// caller's own stream: no hand-over between two processes' streams per collective.
+enum LaunchMode : uint32_t { kLaunchDaemon = 0, kLaunchClient = 1 };
+
+enum ScratchKind : uint32_t { kScratchPad = 0, kScratchStatus = 1, kScratchFifo = 2 };
+struct MapScratchReq { Header h; uint64_t comm_handle; int32_t rank; uint32_t kind; };   // ScratchKind
+struct MapScratchReply { Header h; uint64_t bytes; uint32_t share_kind; uint32_t reserved; };   // + 1 fd
+struct MapMemReq { Header h; uint64_t comm_handle; uint64_t mem_id; };
+struct MapMemReply { Header h; uint64_t bytes; uint32_t share_kind; int32_t device; };         // + 1 fd
 
 struct CommQueryReq { Header h; uint64_t comm_handle; };
 struct CommQueryReply {
@@ -179,6 +197,8 @@ union AnyMsg {
   CommDestroyReq comm_destroy; CommDestroyReply comm_destroy_reply;
   RegisterStreamReq reg_stream; RegisterStreamReply reg_stream_reply;
   CommQueryReq comm_query; CommQueryReply comm_query_reply;
+  MapScratchReq map_scratch; MapScratchReply map_scratch_reply;
+  MapMemReq map_mem; MapMemReply map_mem_reply;
   uint8_t raw[256];
 };
 
@@ -188,6 +208,30 @@ union AnyMsg {
 enum WrFlags : uint32_t {
   kWrGroupMore = 1u << 0,   // further requests of the same group follow
 };
+
+// Client-side launch: what a rank's proxy hands back for one collective, through the
+// plan ring of the data-path segment. Addresses are (allocation, offset) pairs; the
+// client library turns them into its own mappings.
+constexpr uint32_t kPqDepth = 16;
+constexpr uint32_t kPlanBytes = 1024;
+struct alignas(64) PlanMsg {
+  uint64_t user_seq;
+  int32_t status;          // Status; anything but kOk: nothing to launch
+  int32_t kind;            // CollKind
+  int32_t variant, ctas, threads;
+  int32_t dtype, op;
+  int32_t nranks;
+  float scale;
+  uint32_t epoch;          // first barrier value of this launch
+  uint64_t ticket;         // device-visible sequence number
+  uint64_t count;
+  uint64_t timeout_ns;
+  struct { uint64_t send_mem, send_off, recv_mem, recv_off; } rank[8];
+  int8_t ring[32][8];
+  uint64_t ring_step_base[32];
+  uint8_t reserved[184];
+};
+static_assert(sizeof(PlanMsg) == kPlanBytes, "a plan must fill one slot of the plan ring");
 
 struct alignas(64) WorkRequest {
   uint32_t kind;        // CollKind
@@ -235,7 +279,9 @@ static_assert(sizeof(DpStatus) == 64, "DpStatus layout is part of the ABI");
 
 inline size_t dp_wq_bytes() { return ((sizeof(uint64_t) * 24 + (size_t)kWqDepth * kWrBytes) + 63) / 64 * 64; }
 inline size_t dp_cq_bytes() { return ((sizeof(uint64_t) * 24 + (size_t)kCqDepth * kWcBytes) + 63) / 64 * 64; }
-inline size_t dp_segment_bytes() { return dp_wq_bytes() + dp_cq_bytes() + sizeof(DpStatus); }
+inline size_t dp_pq_bytes() { return ((sizeof(uint64_t) * 24 + (size_t)kPqDepth * kPlanBytes) + 63) / 64 * 64; }
+inline size_t dp_pq_offset() { return dp_wq_bytes() + dp_cq_bytes() + sizeof(DpStatus); }
+inline size_t dp_segment_bytes() { return dp_pq_offset() + dp_pq_bytes(); }
 
 inline uint64_t make_comm_handle(uint32_t comm_id, int rank) { return ((uint64_t)comm_id << 32) + (uint32_t)rank; }
 inline uint32_t handle_comm_id(uint64_t h) { return (uint32_t)(h >> 32); }

@@ -180,6 +180,7 @@ Value Daemon::stats() {
       // Placement fields are written while the communicator is being set up, outside
       // the registry lock; they are final once its state has left "init".
       const bool ready = c.state.load(std::memory_order_acquire) != kCommInit;
+      v.set("client_launch", ready && c.client_launch);
       v.set("emulated", ready && c.emulated);
       v.set("host_staged", ready && c.host_staged);
       v.set("paused", c.paused.load());

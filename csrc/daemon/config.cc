@@ -116,7 +116,7 @@ Config Config::from_value(const Value& root) {
                {"transport", "nvls", "vmm", "sync", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
                 "host_devices", "force_host_backend", "idle_sleep_us", "idle_spin_us", "pin_threads", "init_timeout_ms", "fuse_allreduce",
                 "single_through_fused", "skip_start_barrier", "kernel_writes_done", "host_kernels",
-                "hybrid_nvls_permille", "hybrid_nvls_ctas"},
+                "hybrid_nvls_permille", "hybrid_nvls_ctas", "launch"},
                "[b200]");
     c.transport = b["transport"].as_string(c.transport);
     if (c.transport != "auto" && c.transport != "nvlink" && c.transport != "host_staged")
@@ -126,6 +126,8 @@ Config Config::from_value(const Value& root) {
     c.sync = b["sync"].as_string(c.sync);
     if (c.sync != "auto" && c.sync != "events" && c.sync != "memops")
       throw std::runtime_error("b200.sync must be auto, events or memops");
+    c.launch = b["launch"].as_string(c.launch);
+    if (c.launch != "daemon" && c.launch != "client") throw std::runtime_error("b200.launch must be daemon or client");
     c.wait_timeout_ms = (uint64_t)b["wait_timeout_ms"].as_int((int64_t)c.wait_timeout_ms);
     c.tuning_file = b["tuning_file"].as_string();
     c.trace = b["trace"].as_bool(c.trace);

@@ -75,6 +75,7 @@ struct Config {
   bool nvls = true;
   bool vmm = true;
   std::string sync = "auto";        // auto | events | memops (see proto::SyncMode)
+  std::string launch = "daemon";    // daemon | client (see proto::LaunchMode): who launches the kernels
   uint64_t wait_timeout_ms = 10000; // bound of every device-side wait
   std::string tuning_file;
   bool trace = false;

@@ -56,6 +56,11 @@ int Daemon::start(const Config& cfg, std::string* err) {
   memops_ = backend_->memops_supported() && cfg.sync != "events";
   if (cfg.sync == "memops" && !memops_) LOG_WARN("b200.sync=memops requested but stream memory operations are unavailable; using events");
 
+  client_launch_ = cfg.launch == "client";
+  if (client_launch_ && backend_->kind() != proto::kBackendHost) {
+    LOG_WARN("b200.launch=client is only available on the host backend so far; the daemon launches");
+    client_launch_ = false;
+  }
   planner_.load_defaults(backend_->nvls_supported() && cfg.nvls);
   if (!cfg.tuning_file.empty()) {
     std::string terr;
@@ -240,6 +245,8 @@ void Daemon::handle_session(Session& s) {
     case proto::kCommDestroy: need = sizeof(proto::CommDestroyReq); break;
     case proto::kRegisterStream: need = sizeof(proto::RegisterStreamReq); break;
     case proto::kCommQuery: need = sizeof(proto::CommQueryReq); break;
+    case proto::kMapScratch: need = sizeof(proto::MapScratchReq); break;
+    case proto::kMapMem: need = sizeof(proto::MapMemReq); break;
     default: break;
   }
   if ((size_t)n < need) m.h.type = 0;   // falls into the protocol-error reply below
@@ -250,6 +257,8 @@ void Daemon::handle_session(Session& s) {
     case proto::kCommDestroy: on_comm_destroy(s, m.comm_destroy); break;
     case proto::kRegisterStream: on_register_stream(s, m.reg_stream); break;
     case proto::kCommQuery: on_comm_query(s, m.comm_query); break;
+    case proto::kMapScratch: on_map_scratch(s, m.map_scratch); break;
+    case proto::kMapMem: on_map_mem(s, m.map_mem); break;
     case proto::kGoodbye: drop_session(s.id, "client said goodbye"); break;
     default: {
       proto::AnyMsg r;
@@ -531,6 +540,8 @@ void Daemon::on_comm_init(Session& s, const proto::CommInitReq& m) {
       memcpy(r.comm_init_reply.event_handle, rs.event_handle, sizeof rs.event_handle);
       r.comm_init_reply.event_raw = ps->same_process ? (uint64_t)rs.backend_event : 0;
       r.comm_init_reply.dp_bytes = (uint32_t)rs.dp_bytes;
+      r.comm_init_reply.launch_mode = cptr->client_launch ? proto::kLaunchClient : proto::kLaunchDaemon;
+      r.comm_init_reply.fifo_slot_bytes = (uint32_t)cptr->fifo_slot_bytes;
       int fds[2] = {rs.dp_fd, -1};
       int nfds = 1;
       if (rs.sync.host) {
@@ -561,6 +572,7 @@ int Daemon::finalize_communicator(Communicator& c) {
     return proto::kErrUnsupported;
   }
   c.emulated = !host && c.nranks > 1 && all_same;
+  c.client_launch = client_launch_;
   bool p2p = true;
   for (int a = 0; a < c.nranks; a++)
     for (int b = 0; b < c.nranks; b++)
@@ -614,7 +626,7 @@ int Daemon::finalize_communicator(Communicator& c) {
     // stream that has to produce "done". Such clients use ordinary events, which are
     // cheap inside one process.
     // (The host backend has no hardware queues: there every client may use the page.)
-    if (memops_ && (!rs.same_process || host)) {
+    if (memops_ && (!rs.same_process || host) && !c.client_launch) {
       if ((rc = backend_->sync_page_create(rs.device, &rs.sync)) != proto::kOk) return rc;
     }
     if ((rc = backend_->stream_create(rs.device, prio, &rs.stream)) != proto::kOk) return rc;
@@ -630,6 +642,7 @@ int Daemon::finalize_communicator(Communicator& c) {
     memset(rs.dp_status, 0, sizeof(proto::DpStatus));
     rs.wq.init(rs.dp_mem, proto::kWqDepth, proto::kWrBytes);
     rs.cq.init((char*)rs.dp_mem + wq_bytes, proto::kCqDepth, proto::kWcBytes);
+    rs.pq.init((char*)rs.dp_mem + proto::dp_pq_offset(), proto::kPqDepth, proto::kPlanBytes);
   }
   if (c.emulated || host) {
     int rc = backend_->stream_create(c.ranks[0]->device, prio, &c.group_stream);
@@ -782,6 +795,71 @@ void Daemon::on_comm_destroy(Session& s, const proto::CommDestroyReq& m) {
   }
   if (last) destroy_communicator(id);
   reply(s, r, sizeof(proto::CommDestroyReply));
+}
+
+// Client-side launch: a member of a communicator maps another member's signal pad, status
+// block or FIFOs (its kernels address all of them).
+void Daemon::on_map_scratch(Session& s, const proto::MapScratchReq& m) {
+  proto::AnyMsg r;
+  memset(&r, 0, sizeof r);
+  r.h.type = proto::kMapScratchReply;
+  r.h.req_id = m.h.req_id;
+  const uint32_t id = proto::handle_comm_id(m.comm_handle);
+  const auto me = std::make_pair(id, proto::handle_rank(m.comm_handle));
+  int fd = -1;
+  size_t bytes = 0;
+  int status = proto::kErrNotFound;
+  if (std::find(s.comm_ranks.begin(), s.comm_ranks.end(), me) != s.comm_ranks.end()) {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = comms_.find(id);
+    if (it != comms_.end() && it->second->client_launch && m.rank >= 0 && m.rank < it->second->nranks &&
+        it->second->ranks[(size_t)m.rank]) {
+      RankState& rs = *it->second->ranks[(size_t)m.rank];
+      void* p = m.kind == proto::kScratchPad ? (void*)rs.pad : m.kind == proto::kScratchStatus ? (void*)rs.status
+                : m.kind == proto::kScratchFifo ? (void*)rs.fifo : nullptr;
+      status = p ? backend_->scratch_export(p, &fd, &bytes) : proto::kErrNotFound;
+    }
+  }
+  r.h.status = status;
+  r.map_scratch_reply.bytes = bytes;
+  r.map_scratch_reply.share_kind = proto::kShareHostFd;
+  if (status == proto::kOk) reply(s, r, sizeof(proto::MapScratchReply), &fd, 1);
+  else reply(s, r, sizeof(proto::MapScratchReply));
+}
+
+// Client-side launch: an allocation named in a plan. Only allocations of sessions that
+// hold a rank of the same communicator as the requester can be mapped.
+void Daemon::on_map_mem(Session& s, const proto::MapMemReq& m) {
+  proto::AnyMsg r;
+  memset(&r, 0, sizeof r);
+  r.h.type = proto::kMapMemReply;
+  r.h.req_id = m.h.req_id;
+  const uint32_t id = proto::handle_comm_id(m.comm_handle);
+  const auto me = std::make_pair(id, proto::handle_rank(m.comm_handle));
+  int status = proto::kErrNotFound;
+  int fd = -1;
+  if (std::find(s.comm_ranks.begin(), s.comm_ranks.end(), me) != s.comm_ranks.end()) {
+    std::set<uint64_t> members;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      auto it = comms_.find(id);
+      if (it != comms_.end() && it->second->client_launch)
+        for (auto& rr : it->second->ranks)
+          if (rr) members.insert(rr->session_id);
+    }
+    std::shared_lock<std::shared_mutex> al(alloc_mu_);
+    auto it = allocs_.find(m.mem_id);
+    if (it != allocs_.end() && members.count(it->second.owner_session) && it->second.share_fd >= 0) {
+      status = proto::kOk;
+      fd = it->second.share_fd;
+      r.map_mem_reply.bytes = it->second.size;
+      r.map_mem_reply.share_kind = it->second.share_kind;
+      r.map_mem_reply.device = it->second.device;
+    }
+  }
+  r.h.status = status;
+  if (status == proto::kOk) reply(s, r, sizeof(proto::MapMemReply), &fd, 1);
+  else reply(s, r, sizeof(proto::MapMemReply));
 }
 
 void Daemon::on_comm_query(Session& s, const proto::CommQueryReq& m) {

@@ -121,6 +121,7 @@ struct RankState {
   void* dp_mem = nullptr;
   size_t dp_bytes = 0;
   ipc::Ring wq, cq;
+  ipc::Ring pq;                        // plans handed back to the client (client-side launch)
   proto::DpStatus* dp_status = nullptr;
   // device resources
   void* stream = nullptr;
@@ -132,6 +133,8 @@ struct RankState {
   size_t fifo_bytes = 0;
   SyncPage sync;                       // semaphore page shared with the client (mem-op mode)
   // proxy-owned progress state
+  int pending_plan_error = 0;          // client-side launch: an error answer that did not fit the plan ring yet
+  uint64_t pending_plan_seq = 0;
   uint64_t next_post_seq = 0;
   uint64_t next_launch_seq = 0;
   int next_slice = 0;
@@ -155,6 +158,7 @@ class Communicator {
   int nranks = 0;
   bool emulated = false;       // all ranks on one device: one launch covers every rank
   bool host_staged = false;
+  bool client_launch = false;  // the ranks' client libraries launch the kernels; the daemon plans and admits
   std::vector<int> devices;    // device of each rank
   std::vector<std::unique_ptr<RankState>> ranks;
   std::atomic<int> state{kCommInit};
@@ -220,6 +224,8 @@ class ProxyEngine : public Engine {
   void fill_args(Communicator& c, CollSlot& s, int rank, int slice, CollArgs* a);
   bool complete_request(RankState& rs, CollSlot& s, uint64_t seq, int status);
   void signal_done(RankState& rs, uint64_t user_seq, int status);
+  bool publish_plan(RankState& rs, CollSlot& s, uint64_t seq);
+  bool publish_plan_error(RankState& rs, uint64_t user_seq, int status);
   void order_after_client(RankState& rs, const CollOp& op, void* stream);
   bool clients_ready(Communicator& c, CollSlot& s, int self_rank);
   void finish_slot(Communicator& c, CollSlot& s, uint64_t seq);
@@ -292,6 +298,8 @@ class Daemon {
   void on_comm_destroy(Session& s, const proto::CommDestroyReq& m);
   void on_register_stream(Session& s, const proto::RegisterStreamReq& m);
   void on_comm_query(Session& s, const proto::CommQueryReq& m);
+  void on_map_scratch(Session& s, const proto::MapScratchReq& m);
+  void on_map_mem(Session& s, const proto::MapMemReq& m);
   int finalize_communicator(Communicator& c);
   void fail_pending_inits(Communicator& c, int status);
   void check_init_timeouts();
@@ -319,6 +327,7 @@ class Daemon {
   std::thread admin_thread_;
   std::atomic<bool> running_{false};
   bool memops_ = false;
+  bool client_launch_ = false;
   std::atomic<bool> stop_{false};
 
   std::mutex mu_;   // sessions_, comms_, pending_inits_

@@ -113,7 +113,9 @@ bool ProxyEngine::intake(RankState& rs) {
       wc.user_seq = rs.pending_wr.user_seq;
       LOG_WARN("comm %u rank %d: request %llu arrived after the communicator stopped taking work (status %d)", rs.comm->id,
                rs.rank, (unsigned long long)wc.user_seq, wc.status);
-      if (rs.pending_wr.sync_slot && rs.dp_status) {
+      if (rs.comm->client_launch) {
+        if (!publish_plan_error(rs, wc.user_seq, wc.status)) break;
+      } else if (rs.pending_wr.sync_slot && rs.dp_status) {
         signal_done(rs, rs.pending_wr.user_seq, wc.status);
         if (rs.dp_status->first_error == 0) rs.dp_status->first_error = wc.status;
         __atomic_store_n(&rs.dp_status->completed, rs.dp_status->completed + 1, __ATOMIC_RELEASE);
@@ -263,7 +265,7 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   for (int a = 0; a < c.nranks && in.p2p_possible; a++)
     for (int b = 0; b < c.nranks; b++)
       if (!be->peer_access(c.devices[a], c.devices[b])) { in.p2p_possible = false; break; }
-  in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged &&
+  in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged && !c.client_launch &&
                      all_vmm && same_recv_off && (same_send_off || o0.kind == kAllGather) && c.nranks >= 2;
   {
     std::lock_guard<std::mutex> g(c.cfg_mu);
@@ -322,7 +324,7 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   s.slice_count = o0.count;
   const uint64_t slice_bytes = daemon_->qos().slice_bytes(c.id, now);
   if (slice_bytes && o0.kind == kAllReduce && !variant_is_ring(plan.variant) && plan.bytes > slice_bytes &&
-      plan.variant != kLocalCopy) {
+      plan.variant != kLocalCopy && !c.client_launch) {   // a plan handed to a client is one launch
     const uint64_t esz = (uint64_t)dtype_size(o0.dtype);
     uint64_t n = std::min<uint64_t>((plan.bytes + slice_bytes - 1) / slice_bytes, 64);
     uint64_t per = (o0.count + n - 1) / n;
@@ -426,7 +428,7 @@ bool ProxyEngine::plan_member(Communicator& c, CollSlot& head, CollSlot& m, cons
 void ProxyEngine::extend_batch(Communicator& c, CollSlot& head, uint64_t seq, const PlanInput& head_in, uint64_t now) {
   const int limit = std::min(daemon_->config().fuse_allreduce, kMaxBatch);
   const bool single = daemon_->config().single_through_fused;
-  if (limit <= 1 && !single) return;
+  if ((limit <= 1 && !single) || c.client_launch) return;
   Backend* be = daemon_->backend();
   const CollOp& h0 = head.ops[0];
   if (h0.kind != kAllReduce || head.nslices != 1) return;
@@ -753,8 +755,60 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
 // ---------------------------------------------------------------------------
 // (6): completion
 // ---------------------------------------------------------------------------
+// Client-side launch: the plan ring carries the answer to every request, the plan itself
+// or the reason there is none. The client has one request outstanding at a time, so the
+// ring cannot be full; should it ever be, the caller retries.
+bool ProxyEngine::publish_plan_error(RankState& rs, uint64_t user_seq, int status) {
+  proto::PlanMsg m;
+  memset(&m, 0, sizeof m);
+  m.user_seq = user_seq;
+  m.status = status;
+  return rs.pq.try_push(&m);
+}
+
+bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
+  Communicator& c = *rs.comm;
+  if (!admit_slice(c, s, 0)) return false;
+  const CollOp& o0 = s.ops[0];
+  proto::PlanMsg m;
+  memset(&m, 0, sizeof m);
+  m.user_seq = s.ops[rs.rank].user_seq;
+  m.status = proto::kOk;
+  m.kind = o0.kind;
+  m.variant = s.plan.variant;
+  m.ctas = s.plan.dims.ctas;
+  m.threads = s.plan.dims.threads;
+  m.dtype = o0.kind == kAllReduce ? o0.dtype : kUint8;
+  m.op = o0.kind == kAllReduce ? o0.op : kSum;
+  m.nranks = c.nranks;
+  m.scale = o0.op == kSumPostDiv ? 1.0f / (float)c.nranks : o0.scale;
+  m.epoch = s.epoch_base;
+  m.ticket = s.ticket_base;
+  m.count = o0.count;
+  m.timeout_ns = daemon_->timeout_ns();
+  for (int r = 0; r < c.nranks; r++) {
+    m.rank[r].send_mem = s.ops[r].send_mem; m.rank[r].send_off = s.ops[r].send_off;
+    m.rank[r].recv_mem = s.ops[r].recv_mem; m.rank[r].recv_off = s.ops[r].recv_off;
+  }
+  memcpy(m.ring, s.ring, sizeof m.ring);
+  for (int ch = 0; ch < kMaxRingChannels; ch++) m.ring_step_base[ch] = s.ring_step_base[ch];
+  if (!rs.pq.try_push(&m)) return false;
+  if (rs.rank == 0) rs.inflight.push_back({s.ticket_base, s.plan.bytes});
+  rs.last_ticket.store(s.ticket_base, std::memory_order_relaxed);
+  (void)seq;
+  return true;
+}
+
 bool ProxyEngine::complete_request(RankState& rs, CollSlot& s, uint64_t seq, int status) {
   const CollOp& op = s.ops[rs.rank];
+  if (rs.comm->client_launch) {
+    // a published plan is the answer; only failures still need one
+    if (status != proto::kOk && !publish_plan_error(rs, op.user_seq, status)) {
+      rs.pending_plan_error = status;
+      rs.pending_plan_seq = op.user_seq;
+    }
+    return true;
+  }
   if (op.sync_slot && rs.dp_status) {
     // Mem-op request: counted, not answered (see proto::DpStatus).
     proto::DpStatus* d = rs.dp_status;
@@ -794,9 +848,13 @@ void ProxyEngine::finish_slot(Communicator& c, CollSlot& s, uint64_t seq) {
 bool ProxyEngine::advance(RankState& rs) {
   Communicator& c = *rs.comm;
   Backend* be = daemon_->backend();
-  const bool group = c.emulated || be->kind() == proto::kBackendHost;
+  const bool group = (c.emulated || be->kind() == proto::kBackendHost) && !c.client_launch;
   bool any = false;
   while (rs.next_launch_seq < rs.next_post_seq) {
+    if (rs.pending_plan_error) {
+      if (!publish_plan_error(rs, rs.pending_plan_seq, rs.pending_plan_error)) break;
+      rs.pending_plan_error = 0;
+    }
     if (rs.have_pending_wc) {
       if (!rs.cq.try_push(&rs.pending_wc)) break;
       rs.have_pending_wc = false;
@@ -860,6 +918,8 @@ bool ProxyEngine::advance(RankState& rs) {
       if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq, status);
     } else if (follower) {
       if (c.state.load() == kCommError) status = c.async_error.load();
+    } else if (c.client_launch) {
+      if (!publish_plan(rs, s, seq)) break;   // the rank's own library launches the kernel
     } else if (group) {
       if (s.group_launch.load(std::memory_order_acquire) != 2) {
         if (rs.rank != 0) break;

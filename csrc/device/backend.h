@@ -90,6 +90,10 @@ class Backend {
   // Host-visible memory the device writes (status blocks).
   virtual int hostmem_alloc(size_t bytes, void** out) = 0;
   virtual int hostmem_free(void* p) = 0;
+  // Client-side launch: a file descriptor through which another process can map a
+  // scratch or host-memory block of this backend (the daemon keeps it open).
+  // kErrUnsupported where such blocks cannot be shared.
+  virtual int scratch_export(void* p, int* fd, size_t* bytes) = 0;
 
   virtual int stream_create(int dev, int priority, void** stream) = 0;
   virtual int stream_destroy(int dev, void* stream) = 0;

@@ -516,6 +516,10 @@ class CudaBackend : public Backend {
     return max_cooperative_ctas(variant, dtype, op, threads, nranks);
   }
 
+  // Scratch of this backend is not exported to clients yet (client-side launch is
+  // offered by the host backend only).
+  int scratch_export(void*, int*, size_t*) override { return proto::kErrUnsupported; }
+
   bool batch_supported(int variant, int dtype, int op) const override {
     if (variant_is_nvls(variant) && !nvls_) return false;
     return batch_kernel_function(variant, dtype, op) != nullptr;

@@ -22,12 +22,17 @@ namespace {
 
 using namespace mccs::dev;
 
+// When set, a launch covers one rank only (grid.y = 1, the rank comes with the
+// arguments): the other ranks' kernels run elsewhere, in other threads or processes, and
+// meet this one through the shared signal pads. Used by client-side launch.
+thread_local bool g_single_rank = false;
+
 template <typename Kernel, typename Args>
 void run_grid(Kernel kernel, const Args& a, int nranks, int ctas, int threads) {
   std::vector<std::thread> pool;
   sim::Dim3 grid;
   grid.x = (unsigned)ctas;
-  grid.y = (unsigned)nranks;   // one launch carries every rank, as on a single GPU
+  grid.y = g_single_rank ? 1u : (unsigned)nranks;   // else one launch carries every rank, as on a single GPU
   sim::launch(kernel, grid, (unsigned)threads, a, &pool);
   sim::join_all(&pool);
 }
@@ -92,9 +97,16 @@ void clamp(int* ctas, int* threads, bool ring) {
 
 }  // namespace
 
+bool emulated_launch_rank(int kind, const CollArgs& args, LaunchDims dims) {
+  g_single_rank = true;
+  const bool ok = emulated_launch(kind, args, dims);
+  g_single_rank = false;
+  return ok;
+}
+
 bool emulated_launch(int kind, const CollArgs& args, LaunchDims dims) {
   CollArgs a = args;
-  a.emulated = 1;
+  a.emulated = g_single_rank ? 0 : 1;
   int ctas = dims.ctas, threads = dims.threads;
   clamp(&ctas, &threads, variant_is_ring(a.variant));
   if (a.variant == kLocalCopy) {

@@ -8,4 +8,7 @@
 namespace mccs {
 bool emulated_launch(int kind, const CollArgs& args, LaunchDims dims);
 bool emulated_launch_batch(const BatchArgs& args, LaunchDims dims);
+// One rank's part of a collective (args.rank), to completion; the other ranks' parts run
+// concurrently elsewhere and are met through the shared signal pads.
+bool emulated_launch_rank(int kind, const CollArgs& args, LaunchDims dims);
 }  // namespace mccs

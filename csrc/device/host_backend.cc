@@ -17,6 +17,8 @@
 #include "../common/log.h"
 #include "../ipc/uds.h"
 #include <sched.h>
+#include <mutex>
+#include <map>
 
 #include "backend.h"
 #include "emulated_kernels.h"
@@ -192,16 +194,46 @@ class HostBackend : public Backend {
     a->va = 0; a->share_fd = -1;
     return proto::kOk;
   }
+  // Scratch lives in anonymous shared memory so that a client process can map it too
+  // (client-side launch: its kernels address every rank's pads, status blocks and FIFOs).
   int scratch_alloc(int, size_t bytes, bool, void** out) override {
-    void* p = nullptr;
-    if (posix_memalign(&p, 256, bytes) != 0) return proto::kErrOutOfMemory;
-    memset(p, 0, bytes);
+    const size_t page = (size_t)sysconf(_SC_PAGESIZE);
+    const size_t size = (bytes + page - 1) / page * page;
+    int fd = ipc::memfd_make("mccs-scratch", size);
+    if (fd < 0) return proto::kErrOutOfMemory;
+    void* p = ipc::map_shared(fd, size);
+    if (!p) { close(fd); return proto::kErrOutOfMemory; }
+    memset(p, 0, size);
+    {
+      std::lock_guard<std::mutex> g(scratch_mu_);
+      scratch_[p] = {fd, size};
+    }
     *out = p;
     return proto::kOk;
   }
-  int scratch_free(int, void* p, size_t, bool) override { free(p); return proto::kOk; }
+  int scratch_free(int, void* p, size_t, bool) override {
+    std::pair<int, size_t> e{-1, 0};
+    {
+      std::lock_guard<std::mutex> g(scratch_mu_);
+      auto it = scratch_.find(p);
+      if (it == scratch_.end()) return proto::kErrNotFound;
+      e = it->second;
+      scratch_.erase(it);
+    }
+    ipc::unmap_shared(p, e.second);
+    close(e.first);
+    return proto::kOk;
+  }
   int hostmem_alloc(size_t bytes, void** out) override { return scratch_alloc(0, bytes, true, out); }
-  int hostmem_free(void* p) override { free(p); return proto::kOk; }
+  int hostmem_free(void* p) override { return scratch_free(0, p, 0, true); }
+  int scratch_export(void* p, int* fd, size_t* bytes) override {
+    std::lock_guard<std::mutex> g(scratch_mu_);
+    auto it = scratch_.find(p);
+    if (it == scratch_.end()) return proto::kErrNotFound;
+    *fd = it->second.first;
+    *bytes = it->second.second;
+    return proto::kOk;
+  }
 
   int stream_create(int, int, void** s) override { *s = (void*)(uintptr_t)(++next_handle_); return proto::kOk; }
   int stream_destroy(int, void*) override { return proto::kOk; }
@@ -303,6 +335,8 @@ class HostBackend : public Backend {
   }
 
  private:
+  std::mutex scratch_mu_;
+  std::map<void*, std::pair<int, size_t>> scratch_;
   int ndev_;
   bool emulate_;
   bool memops_;

@@ -35,6 +35,7 @@
 #include "../common/value.h"
 #include "../ipc/shm_ring.h"
 #include "../ipc/uds.h"
+#include "../device/emulated_kernels.h"
 #include "../kernels/dev_types.h"
 
 using namespace mccs;
@@ -224,6 +225,17 @@ struct mccsComm {
   bool sync_emulated = false; // host backend: the CPU writes and awaits the semaphores itself
   std::map<uint64_t, uint32_t> stream_slot;            // stream handle -> semaphore index
   uint64_t slot_value[proto::kSyncMaxStreams] = {0};   // last value written per semaphore
+  // client-side launch (proto::kLaunchClient): plans come back through `pq`, the kernels
+  // are launched here and address every rank's pads, status blocks, FIFOs and buffers
+  bool client_launch = false;
+  ipc::Ring pq;
+  SignalPad* pads[kMaxRanks] = {nullptr};
+  StatusBlock* status[kMaxRanks] = {nullptr};
+  char* fifo[kMaxRanks] = {nullptr};
+  size_t pad_bytes[kMaxRanks] = {0}, status_bytes[kMaxRanks] = {0}, fifo_bytes[kMaxRanks] = {0};
+  uint64_t fifo_slot_bytes = 0;
+  struct PeerMem { uint64_t base; size_t size; };
+  std::map<uint64_t, PeerMem> peer_mem;                // allocations of other ranks, mapped on first use
 };
 
 namespace {
@@ -607,6 +619,111 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
   return mccsSuccess;
 }
 
+// Address, in this process, of byte `off` of allocation `mem_id`: one of the caller's own
+// allocations, or a peer's, mapped on first use (client-side launch only).
+mccsResult_t resolve_mem(mccsComm* comm, uint64_t mem_id, uint64_t off, uint64_t* out) {
+  std::unique_lock<std::mutex> g(g_ctx.mu);
+  for (const auto& kv : g_ctx.mem)
+    if (kv.second.mem_id == mem_id) { *out = kv.second.base + off; return mccsSuccess; }
+  auto it = comm->peer_mem.find(mem_id);
+  if (it == comm->peer_mem.end()) {
+    proto::AnyMsg m;
+    memset(&m, 0, sizeof m);
+    m.h.type = proto::kMapMem;
+    m.map_mem.comm_handle = comm->handle;
+    m.map_mem.mem_id = mem_id;
+    std::vector<int> fds;
+    mccsResult_t r = roundtrip(g, m, sizeof(proto::MapMemReq), proto::kMapMemReply, &fds, 30000);
+    if (r != mccsSuccess) return r;
+    if (fds.empty() || m.map_mem_reply.share_kind != proto::kShareHostFd) {
+      for (int f : fds) close(f);
+      return mccsUnsupported;
+    }
+    void* p = mmap(nullptr, m.map_mem_reply.bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
+    for (int f : fds) close(f);
+    if (p == MAP_FAILED) return mccsOutOfMemory;
+    it = comm->peer_mem.emplace(mem_id, mccsComm::PeerMem{(uint64_t)p, (size_t)m.map_mem_reply.bytes}).first;
+  }
+  if (off > it->second.size) return mccsInvalidArgument;
+  *out = it->second.base + off;
+  return mccsSuccess;
+}
+
+// Client-side launch: post the request, wait for the plan the daemon makes for all ranks
+// (variant, launch shape, barrier epoch, ticket, ring order, everybody's buffers), and
+// launch this rank's kernel here. The daemon never touches a stream for this collective.
+mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr) {
+  if (comm->sticky_error) return (mccsResult_t)comm->sticky_error;
+  wr.comm_handle = comm->handle;
+  wr.user_seq = comm->next_user_seq++;
+  uint64_t spins = 0;
+  while (!comm->wq.try_push(&wr)) {
+    if ((++spins & 0xffff) == 0) {
+      struct pollfd pf = {g_ctx.fd, 0, 0};
+      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+    }
+  }
+  comm->last_posted_seq = wr.user_seq;
+  proto::PlanMsg plan;
+  struct timespec t0;
+  clock_gettime(CLOCK_MONOTONIC, &t0);
+  spins = 0;
+  while (!comm->pq.try_pop(&plan)) {
+    if ((++spins & 0xfff) == 0) {
+      struct timespec t1;
+      clock_gettime(CLOCK_MONOTONIC, &t1);
+      uint64_t ms = (uint64_t)(t1.tv_sec - t0.tv_sec) * 1000 + (uint64_t)((t1.tv_nsec - t0.tv_nsec) / 1000000);
+      if (ms > g_ctx.wc_timeout_ms) return mccsTimeout;
+      struct pollfd pf = {g_ctx.fd, 0, 0};
+      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+      if (spins > (1u << 20)) usleep(50);
+    }
+  }
+  if (plan.user_seq != wr.user_seq) return mccsProtocolError;
+  if (plan.status != 0) {
+    if (comm->sticky_error == 0) comm->sticky_error = plan.status;
+    return (mccsResult_t)plan.status;
+  }
+  comm->last_variant = (uint32_t)plan.variant;
+  comm->last_ctas = (uint32_t)plan.ctas;
+  if (plan.nranks != comm->nranks) return mccsProtocolError;
+  CollArgs a;
+  memset(&a, 0, sizeof a);
+  a.rank = comm->rank;
+  a.nranks = comm->nranks;
+  a.dtype = plan.dtype;
+  a.op = plan.op;
+  a.variant = plan.variant;
+  a.count = plan.count;
+  a.seq = plan.ticket;
+  a.scale = plan.scale;
+  a.epoch = plan.epoch;
+  a.timeout_ns = plan.timeout_ns;
+  for (int r = 0; r < comm->nranks; r++) {
+    uint64_t s = 0, d = 0;
+    mccsResult_t rr = resolve_mem(comm, plan.rank[r].send_mem, plan.rank[r].send_off, &s);
+    if (rr == mccsSuccess) rr = resolve_mem(comm, plan.rank[r].recv_mem, plan.rank[r].recv_off, &d);
+    if (rr != mccsSuccess) return rr;
+    a.send[r] = (const void*)s;
+    a.recv[r] = (void*)d;
+    a.pad[r] = comm->pads[r];
+    a.status[r] = comm->status[r];
+    a.fifo[r] = comm->fifo[r];
+  }
+  a.fifo_slot_bytes = comm->fifo_slot_bytes;
+  memcpy(a.ring, plan.ring, sizeof a.ring);
+  for (int ch = 0; ch < kMaxRingChannels; ch++) a.ring_step_base[ch] = plan.ring_step_base[ch];
+  LaunchDims dims{plan.ctas, plan.threads};
+  if (g_ctx.backend != proto::kBackendHost) return mccsUnsupported;   // the GPU form loads the kernels into the caller's context
+  if (!emulated_launch_rank(plan.kind, a, dims)) return mccsUnsupported;
+  const uint32_t err = __atomic_load_n(&comm->status[comm->rank]->error, __ATOMIC_ACQUIRE);
+  if (err != 0) {
+    comm->sticky_error = err == kDevAborted ? mccsAborted : mccsTimeout;
+    return (mccsResult_t)comm->sticky_error;
+  }
+  return mccsSuccess;
+}
+
 mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, void* recv, uint64_t send_bytes,
                     uint64_t recv_bytes, mccsStream_t stream) {
   if (!comm) return mccsInvalidArgument;
@@ -623,11 +740,12 @@ mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, vo
     wr.send_mem = sm->mem_id; wr.send_off = (uint64_t)send - sm->base;
     wr.recv_mem = rm->mem_id; wr.recv_off = (uint64_t)recv - rm->base;
     if (wr.send_off + send_bytes > sm->size || wr.recv_off + recv_bytes > rm->size) return mccsInvalidArgument;
-    if (!comm->sync_base) {
+    if (!comm->sync_base && !comm->client_launch) {
       mccsResult_t r = register_stream_locked(g, comm->device, stream, &srec);
       if (r != mccsSuccess) return r;
     }
   }
+  if (comm->client_launch) return submit_client_launch(comm, wr);
   if (comm->sync_base) return submit_memops(comm, wr, stream);
   wr.comm_handle = comm->handle;
   wr.stream_id = srec->stream_id;
@@ -867,6 +985,9 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
       }
     }
   }
+  if (c->dp_bytes >= proto::dp_segment_bytes()) c->pq.attach((char*)c->dp_mem + proto::dp_pq_offset());
+  c->client_launch = m.comm_init_reply.launch_mode == proto::kLaunchClient;
+  c->fifo_slot_bytes = m.comm_init_reply.fifo_slot_bytes;
   if (g_ctx.backend == proto::kBackendHost && m.comm_init_reply.sync_size && fds.size() > 1) {
     const size_t bytes = m.comm_init_reply.sync_size;
     void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[1], 0);
@@ -895,6 +1016,37 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
         return mccsDeviceError;
       }
       c->event_owned = true;
+    }
+  }
+  if (c->client_launch) {
+    // Everything this rank's kernels address besides the buffers: every rank's signal pad
+    // and status block, and (for the ring variants) every rank's FIFOs.
+    for (int r = 0; r < nranks; r++) {
+      for (uint32_t kind : {(uint32_t)proto::kScratchPad, (uint32_t)proto::kScratchStatus, (uint32_t)proto::kScratchFifo}) {
+        if (kind == proto::kScratchFifo && nranks == 1) continue;
+        proto::AnyMsg q;
+        memset(&q, 0, sizeof q);
+        q.h.type = proto::kMapScratch;
+        q.map_scratch.comm_handle = c->handle;
+        q.map_scratch.rank = r;
+        q.map_scratch.kind = kind;
+        std::vector<int> sfds;
+        mccsResult_t mr = roundtrip(g, q, sizeof(proto::MapScratchReq), proto::kMapScratchReply, &sfds, 30000);
+        void* p = MAP_FAILED;
+        if (mr == mccsSuccess && !sfds.empty())
+          p = mmap(nullptr, q.map_scratch_reply.bytes, PROT_READ | PROT_WRITE, MAP_SHARED, sfds[0], 0);
+        for (int f : sfds) close(f);
+        if (p == MAP_FAILED) {
+          LOG_ERROR("cannot map rank %d's %s of communicator %u", r, kind == proto::kScratchPad ? "signal pad" : kind == proto::kScratchStatus ? "status block" : "FIFOs", c->id);
+          g_ctx.comms.push_back(c);      // mccsCommDestroy below undoes what exists so far
+          g.unlock();
+          mccsCommDestroy(c);
+          return mr != mccsSuccess ? mr : mccsOutOfMemory;
+        }
+        if (kind == proto::kScratchPad) { c->pads[r] = (SignalPad*)p; c->pad_bytes[r] = q.map_scratch_reply.bytes; }
+        else if (kind == proto::kScratchStatus) { c->status[r] = (StatusBlock*)p; c->status_bytes[r] = q.map_scratch_reply.bytes; }
+        else { c->fifo[r] = (char*)p; c->fifo_bytes[r] = q.map_scratch_reply.bytes; }
+      }
     }
   }
   g_ctx.comms.push_back(c);
@@ -948,6 +1100,12 @@ mccsResult_t mccsCommDestroy(mccsComm_t comm) {
   for (size_t i = 0; i < g_ctx.comms.size(); i++)
     if (g_ctx.comms[i] == comm) { g_ctx.comms.erase(g_ctx.comms.begin() + (long)i); break; }
   if (comm->dp_mem) munmap(comm->dp_mem, comm->dp_bytes);
+  for (int r = 0; r < kMaxRanks; r++) {
+    if (comm->pads[r]) munmap(comm->pads[r], comm->pad_bytes[r]);
+    if (comm->status[r]) munmap(comm->status[r], comm->status_bytes[r]);
+    if (comm->fifo[r]) munmap(comm->fifo[r], comm->fifo_bytes[r]);
+  }
+  for (auto& kv : comm->peer_mem) munmap((void*)kv.second.base, kv.second.size);
   if (comm->sync_host) {
     if (!comm->sync_emulated) {
       CtxScope scope(comm->device);

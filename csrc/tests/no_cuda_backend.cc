@@ -13,4 +13,5 @@ Backend* make_cuda_backend(const BackendOptions&, std::string* why) {
 // sanitizer builds run the host backend's plain loops only.
 bool emulated_launch(int, const CollArgs&, LaunchDims) { return false; }
 bool emulated_launch_batch(const BatchArgs&, LaunchDims) { return false; }
+bool emulated_launch_rank(int, const CollArgs&, LaunchDims) { return false; }
 }  // namespace mccs

@@ -90,7 +90,8 @@ q = comm.query()
 st = M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"]["6100"]
 comm.destroy()
 print("RESULT", json.dumps({"bad": bad, "seen": sorted(seen), "async_error": q["async_error"], "device_error": q["device_error"],
-                            "fused_members": st["fused_members"], "epoch": st["config_epoch"]}), flush=True)
+                            "fused_members": st["fused_members"], "epoch": st["config_epoch"],
+                            "client_launch": st["client_launch"], "completed": st["completed"]}), flush=True)
 """
 
 
@@ -126,7 +127,7 @@ def test_service_with_the_real_kernels_on_the_emulator(tmp_path, n, sync):
         assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
         # every emulated variant really ran
         assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
-        assert res["epoch"] == 1 and res["fused_members"] >= 2
+        assert res["epoch"] == 1 and res["fused_members"] >= 2 and res["client_launch"] is False
 
 
 def test_host_staged_transport_with_the_real_ring_kernels(tmp_path):
@@ -187,3 +188,16 @@ def test_time_sliced_allreduce_with_the_real_kernels(tmp_path):
         assert max(e.get("args", {}).get("slices", 1) for e in events) > 1, "no collective was sliced"
     finally:
         sp.stop()
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_client_side_launch(tmp_path, n):
+    """`[b200] launch = "client"`: the daemon collects the ranks' requests, plans, admits and
+    hands out epochs and tickets as always, but gives the plan back to each rank's client
+    library, which maps its peers' buffers, pads, status blocks and FIFOs and runs its
+    rank's kernel itself (here on the emulator, one process per rank meeting through
+    shared memory). Same scenario as above: every variant, ring reconfiguration, groups."""
+    for res in _run(tmp_path, n, 'launch = "client"'):
+        assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
+        assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
+        assert res["epoch"] == 1 and res["client_launch"] is True and res["completed"] > 50

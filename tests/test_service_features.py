@@ -522,7 +522,8 @@ except Exception as e:
 """
 
 
-def test_clients_killed_at_random_leave_the_daemon_clean(tmp_path):
+@pytest.mark.parametrize("launch", ["daemon", "client"])
+def test_clients_killed_at_random_leave_the_daemon_clean(tmp_path, launch):
     """Three rounds of: a few ranks hammer a communicator, one of them is killed without
     warning at a random moment; the others get an error (never a wrong value, never a
     hang), the same communicator id is usable again right afterwards, and at the end the
@@ -534,7 +535,7 @@ def test_clients_killed_at_random_leave_the_daemon_clean(tmp_path):
     from mccs_b200 import daemon
     d = str(tmp_path)
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=-1, force_host=True,
-                       wait_timeout_ms=3000, extra="init_timeout_ms = 3000\nfuse_allreduce = 4")
+                       wait_timeout_ms=3000, extra=f"init_timeout_ms = 3000\nfuse_allreduce = 4\nlaunch = \"{launch}\"")
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "error"})
     rng = random.Random(11)
     try:
@@ -556,7 +557,14 @@ def test_clients_killed_at_random_leave_the_daemon_clean(tmp_path):
                 if r != victim:
                     assert "ERROR" in out, (rnd, r, out, err[-500:])
             assert sp.proc.poll() is None, "the daemon died"
-        st = M.admin_request(sp.admin_port, {"cmd": "stats"})["stats"]
+        # A session leaves the client count first and gives its memory back last, after the
+        # streams that may still touch it have drained: allow that a moment.
+        deadline = time.time() + 10
+        while True:
+            st = M.admin_request(sp.admin_port, {"cmd": "stats"})["stats"]
+            if (st["clients"], st["communicators"], st["allocations"]) == (0, {}, 0) or time.time() > deadline:
+                break
+            time.sleep(0.1)
         assert st["clients"] == 0 and st["communicators"] == {} and st["allocations"] == 0
     finally:
         sp.stop()
