@@ -28,7 +28,7 @@ HDRS := $(wildcard csrc/*/*.h csrc/*/*.cuh)
 APPS := allreduce_bench allgather_bench allreduce_proto allgather_proto traffic_gen ring_config mccs_hello
 APP_BINS := $(addprefix $(OUT)/,$(APPS))
 
-all: $(OUT)/libmccs_daemon.so $(OUT)/libmccs.so $(OUT)/mccsd $(OUT)/libmccs_preload.so $(APP_BINS) $(OUT)/host_tests
+all: $(OUT)/libmccs_daemon.so $(OUT)/libmccs.so $(OUT)/libmccs_kernels.so $(OUT)/mccsd $(OUT)/libmccs_preload.so $(APP_BINS) $(OUT)/host_tests
 
 $(OBJ)/%.o: csrc/%.cc $(HDRS)
 	@mkdir -p $(dir $@)
@@ -59,6 +59,12 @@ $(foreach t,$(TYPES),$(eval $(call TYPE_RULE,$(word 1,$(subst :, ,$(t))),$(word 
 $(OUT)/libmccs_daemon.so: $(HOST_OBJS) $(EMU_OBJ) $(CUDA_OBJS) csrc/exports.map
 	@mkdir -p $(OUT)
 	$(NVCC) $(ARCH) -shared -cudart static -Xlinker --version-script=csrc/exports.map -o $@ $(HOST_OBJS) $(EMU_OBJ) $(CUDA_OBJS) $(LDLIBS)
+
+# The kernels alone, for clients that launch them themselves ([b200] launch = "client").
+KLIB_OBJS := $(OBJ)/kernels/client_entry.o $(OBJ)/kernels/launch.o $(OBJ)/kernels/untyped.o $(TYPE_OBJS)
+$(OUT)/libmccs_kernels.so: $(KLIB_OBJS) csrc/exports_kernels.map
+	@mkdir -p $(OUT)
+	$(NVCC) $(ARCH) -shared -cudart static -Xlinker --version-script=csrc/exports_kernels.map -o $@ $(KLIB_OBJS) $(LDLIBS)
 
 $(OUT)/libmccs.so: $(SHIM_OBJS) $(EMU_OBJ) csrc/exports.map
 	@mkdir -p $(OUT)

@@ -17,7 +17,7 @@ namespace mccs {
 namespace proto {
 
 constexpr uint32_t kMagic = 0x5343434du;  // "MCCS"
-constexpr uint32_t kVersion = 6;
+constexpr uint32_t kVersion = 7;
 constexpr uint32_t kWqDepth = 64;
 constexpr uint32_t kCqDepth = 64;
 constexpr uint32_t kWrBytes = 128;
@@ -172,9 +172,10 @@ enum LaunchMode : uint32_t { kLaunchDaemon = 0, kLaunchClient = 1 };
 
 enum ScratchKind : uint32_t { kScratchPad = 0, kScratchStatus = 1, kScratchFifo = 2 };
 struct MapScratchReq { Header h; uint64_t comm_handle; int32_t rank; uint32_t kind; };   // ScratchKind
-struct MapScratchReply { Header h; uint64_t bytes; uint32_t share_kind; uint32_t reserved; };   // + 1 fd
+// share_kind kShareSameProcess (a client inside the daemon's process on a GPU): no descriptor, use daemon_va
+struct MapScratchReply { Header h; uint64_t bytes; uint32_t share_kind; uint32_t reserved; uint64_t daemon_va; };   // + 1 fd
 struct MapMemReq { Header h; uint64_t comm_handle; uint64_t mem_id; };
-struct MapMemReply { Header h; uint64_t bytes; uint32_t share_kind; int32_t device; };         // + 1 fd
+struct MapMemReply { Header h; uint64_t bytes; uint32_t share_kind; int32_t device; uint64_t daemon_va; };   // + 1 fd
 
 struct CommQueryReq { Header h; uint64_t comm_handle; };
 struct CommQueryReply {

@@ -57,8 +57,8 @@ int Daemon::start(const Config& cfg, std::string* err) {
   if (cfg.sync == "memops" && !memops_) LOG_WARN("b200.sync=memops requested but stream memory operations are unavailable; using events");
 
   client_launch_ = cfg.launch == "client";
-  if (client_launch_ && backend_->kind() != proto::kBackendHost) {
-    LOG_WARN("b200.launch=client is only available on the host backend so far; the daemon launches");
+  if (client_launch_ && !backend_->client_launch_supported()) {
+    LOG_WARN("b200.launch=client needs exportable device memory and registered host memory addressable by its host pointer; the daemon launches");
     client_launch_ = false;
   }
   planner_.load_defaults(backend_->nvls_supported() && cfg.nvls);
@@ -572,12 +572,18 @@ int Daemon::finalize_communicator(Communicator& c) {
     return proto::kErrUnsupported;
   }
   c.emulated = !host && c.nranks > 1 && all_same;
-  c.client_launch = client_launch_;
   bool p2p = true;
   for (int a = 0; a < c.nranks; a++)
     for (int b = 0; b < c.nranks; b++)
       p2p &= backend_->peer_access(c.devices[(size_t)a], c.devices[(size_t)b]);
   c.host_staged = cfg_.transport == "host_staged" || (cfg_.transport == "auto" && !p2p);
+  // Kernels that clients launch themselves: not when several ranks share a GPU (their
+  // kernels would be separate launches that wait on one another on one device), and on a
+  // GPU not with the pads in pinned host memory (that memory is not exported).
+  c.client_launch = client_launch_ && (host || (!c.emulated && !c.host_staged));
+  if (client_launch_ && !c.client_launch)
+    LOG_WARN("comm %u: launched by the daemon although b200.launch=client (%s)", c.id,
+             c.emulated ? "several ranks on one GPU" : "host-staged transport");
   if (cfg_.transport == "nvlink" && !p2p) {
     LOG_ERROR("comm %u: transport=nvlink but the devices have no peer access", c.id);
     return proto::kErrUnsupported;
@@ -610,14 +616,14 @@ int Daemon::finalize_communicator(Communicator& c) {
     RankState& rs = *c.ranks[(size_t)r];
     int rc;
     void* p = nullptr;
-    if ((rc = backend_->scratch_alloc(rs.device, sizeof(SignalPad), c.host_staged, &p)) != proto::kOk) return rc;
+    if ((rc = backend_->scratch_alloc(rs.device, sizeof(SignalPad), c.host_staged, c.client_launch, &p)) != proto::kOk) return rc;
     rs.pad = (SignalPad*)p;
     if (c.nranks > 1) {
-      if ((rc = backend_->scratch_alloc(rs.device, fifo_bytes, c.host_staged, &p)) != proto::kOk) return rc;
+      if ((rc = backend_->scratch_alloc(rs.device, fifo_bytes, c.host_staged, c.client_launch, &p)) != proto::kOk) return rc;
       rs.fifo = (char*)p;
       rs.fifo_bytes = fifo_bytes;
     }
-    if ((rc = backend_->hostmem_alloc(sizeof(StatusBlock), &p)) != proto::kOk) return rc;
+    if ((rc = backend_->hostmem_alloc(sizeof(StatusBlock), c.client_launch, &p)) != proto::kOk) return rc;
     rs.status = (StatusBlock*)p;
     // Stream-memory-operation ordering only for clients in other processes. A client
     // that lives in the daemon's own process has its stream in the same CUDA context
@@ -808,6 +814,7 @@ void Daemon::on_map_scratch(Session& s, const proto::MapScratchReq& m) {
   const auto me = std::make_pair(id, proto::handle_rank(m.comm_handle));
   int fd = -1;
   size_t bytes = 0;
+  uint32_t share_kind = proto::kShareHostFd;
   int status = proto::kErrNotFound;
   if (std::find(s.comm_ranks.begin(), s.comm_ranks.end(), me) != s.comm_ranks.end()) {
     std::lock_guard<std::mutex> g(mu_);
@@ -817,13 +824,18 @@ void Daemon::on_map_scratch(Session& s, const proto::MapScratchReq& m) {
       RankState& rs = *it->second->ranks[(size_t)m.rank];
       void* p = m.kind == proto::kScratchPad ? (void*)rs.pad : m.kind == proto::kScratchStatus ? (void*)rs.status
                 : m.kind == proto::kScratchFifo ? (void*)rs.fifo : nullptr;
-      status = p ? backend_->scratch_export(p, &fd, &bytes) : proto::kErrNotFound;
+      status = p ? backend_->scratch_export(p, &fd, &bytes, &share_kind) : proto::kErrNotFound;
+      r.map_scratch_reply.daemon_va = (uint64_t)p;
     }
   }
+  // A client inside this process on a GPU uses the daemon's own mappings.
+  const bool direct = s.same_process && backend_->kind() == proto::kBackendCuda;
   r.h.status = status;
   r.map_scratch_reply.bytes = bytes;
-  r.map_scratch_reply.share_kind = proto::kShareHostFd;
-  if (status == proto::kOk) reply(s, r, sizeof(proto::MapScratchReply), &fd, 1);
+  r.map_scratch_reply.share_kind = direct ? (uint32_t)proto::kShareSameProcess : share_kind;
+  if (!direct) r.map_scratch_reply.daemon_va = 0;
+  if (status == proto::kOk && direct) reply(s, r, sizeof(proto::MapScratchReply));
+  else if (status == proto::kOk) reply(s, r, sizeof(proto::MapScratchReply), &fd, 1);
   else reply(s, r, sizeof(proto::MapScratchReply));
 }
 
@@ -849,16 +861,19 @@ void Daemon::on_map_mem(Session& s, const proto::MapMemReq& m) {
     }
     std::shared_lock<std::shared_mutex> al(alloc_mu_);
     auto it = allocs_.find(m.mem_id);
-    if (it != allocs_.end() && members.count(it->second.owner_session) && it->second.share_fd >= 0) {
+    const bool direct = s.same_process && backend_->kind() == proto::kBackendCuda;
+    if (it != allocs_.end() && members.count(it->second.owner_session) && (direct || it->second.share_fd >= 0)) {
       status = proto::kOk;
-      fd = it->second.share_fd;
+      fd = direct ? -1 : it->second.share_fd;
       r.map_mem_reply.bytes = it->second.size;
-      r.map_mem_reply.share_kind = it->second.share_kind;
+      r.map_mem_reply.share_kind = direct ? (uint32_t)proto::kShareSameProcess : it->second.share_kind;
       r.map_mem_reply.device = it->second.device;
+      r.map_mem_reply.daemon_va = direct ? it->second.va : 0;
     }
   }
   r.h.status = status;
-  if (status == proto::kOk) reply(s, r, sizeof(proto::MapMemReply), &fd, 1);
+  if (status == proto::kOk && fd < 0) reply(s, r, sizeof(proto::MapMemReply));
+  else if (status == proto::kOk) reply(s, r, sizeof(proto::MapMemReply), &fd, 1);
   else reply(s, r, sizeof(proto::MapMemReply));
 }
 

@@ -84,16 +84,18 @@ class Backend {
   virtual int release(Allocation* a) = 0;
 
   // Zero-filled scratch readable and writable from every device. host_staged places
-  // it in pinned host memory (the host-staged transport).
-  virtual int scratch_alloc(int dev, size_t bytes, bool host_staged, void** out) = 0;
+  // it in pinned host memory (the host-staged transport). `shareable` asks for a block
+  // that scratch_export can hand to another process (client-side launch).
+  virtual int scratch_alloc(int dev, size_t bytes, bool host_staged, bool shareable, void** out) = 0;
   virtual int scratch_free(int dev, void* p, size_t bytes, bool host_staged) = 0;
   // Host-visible memory the device writes (status blocks).
-  virtual int hostmem_alloc(size_t bytes, void** out) = 0;
+  virtual int hostmem_alloc(size_t bytes, bool shareable, void** out) = 0;
   virtual int hostmem_free(void* p) = 0;
-  // Client-side launch: a file descriptor through which another process can map a
-  // scratch or host-memory block of this backend (the daemon keeps it open).
-  // kErrUnsupported where such blocks cannot be shared.
-  virtual int scratch_export(void* p, int* fd, size_t* bytes) = 0;
+  // Client-side launch: whether blocks made with `shareable` can be mapped by the
+  // clients' processes at all, and a file descriptor plus its proto::ShareKind through
+  // which one is mapped (the backend keeps the descriptor open until the block is freed).
+  virtual bool client_launch_supported() const = 0;
+  virtual int scratch_export(void* p, int* fd, size_t* bytes, uint32_t* share_kind) = 0;
 
   virtual int stream_create(int dev, int priority, void** stream) = 0;
   virtual int stream_destroy(int dev, void* stream) = 0;

@@ -136,6 +136,12 @@ class CudaBackend : public Backend {
       drv_.cuDeviceGetAttribute_(&ok64, CU_DEVICE_ATTRIBUTE_CAN_USE_64_BIT_STREAM_MEM_OPS, dev);
       if (!ok64) memops_ = false;
     }
+    host_ptr_is_dev_ptr_ = true;
+    for (int d = 0; d < ndev_; d++) {
+      int same = 0;
+      if (cudaDeviceGetAttribute(&same, cudaDevAttrCanUseHostPointerForRegisteredMem, d) != cudaSuccess) { cudaGetLastError(); same = 0; }
+      if (!same) host_ptr_is_dev_ptr_ = false;
+    }
     cudaSetDevice(0);
     LOG_INFO("%s", describe().c_str());
     return true;
@@ -235,8 +241,9 @@ class CudaBackend : public Backend {
     return proto::kOk;
   }
 
-  int scratch_alloc(int dev, size_t bytes, bool host_staged, void** out) override {
+  int scratch_alloc(int dev, size_t bytes, bool host_staged, bool shareable, void** out) override {
     DeviceGuard guard;
+    if (shareable && (host_staged || !vmm_)) return proto::kErrUnsupported;
     if (host_staged) {
       void* p = nullptr;
       RT_CHECK(cudaHostAlloc(&p, bytes, cudaHostAllocPortable | cudaHostAllocMapped), proto::kErrOutOfMemory);
@@ -249,12 +256,29 @@ class CudaBackend : public Backend {
       size_t size = (bytes + gran_ - 1) / gran_ * gran_;
       CUmemGenericAllocationHandle h = 0;
       CUdeviceptr va = 0;
-      int rc = vmm_create_mapped(dev, size, false, &h, &va);
+      int rc = vmm_create_mapped(dev, size, shareable, &h, &va);
       if (rc != proto::kOk) return rc;
-      RT_CHECK(cudaMemset((void*)va, 0, size), proto::kErrDevice);
-      RT_CHECK(cudaDeviceSynchronize(), proto::kErrDevice);
+      int fd = -1;
+      if (shareable) {
+        // Exported once; every client that maps the block gets a duplicate of this descriptor.
+        CUresult r = drv_.cuMemExportToShareableHandle_(&fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+        if (r != CUDA_SUCCESS) {
+          log_cu("cuMemExportToShareableHandle(scratch)", r);
+          vmm_destroy(h, va, size);
+          return proto::kErrDevice;
+        }
+      }
+      cudaError_t e = cudaMemset((void*)va, 0, size);
+      if (e == cudaSuccess) e = cudaDeviceSynchronize();
+      if (e != cudaSuccess) {
+        LOG_ERROR("clearing scratch memory failed: %s", cudaGetErrorString(e));
+        cudaGetLastError();
+        if (fd >= 0) close(fd);
+        vmm_destroy(h, va, size);
+        return proto::kErrDevice;
+      }
       std::lock_guard<std::mutex> g(mu_);
-      scratch_.push_back({(uint64_t)va, (uint64_t)h, size});
+      scratch_.push_back({(uint64_t)va, (uint64_t)h, size, fd});
       *out = (void*)va;
       return proto::kOk;
     }
@@ -274,6 +298,7 @@ class CudaBackend : public Backend {
       for (size_t i = 0; i < scratch_.size(); i++) {
         if (scratch_[i].va == (uint64_t)p) {
           vmm_destroy((CUmemGenericAllocationHandle)scratch_[i].handle, (CUdeviceptr)scratch_[i].va, scratch_[i].size);
+          if (scratch_[i].fd >= 0) close(scratch_[i].fd);
           scratch_.erase(scratch_.begin() + (long)i);
           return proto::kOk;
         }
@@ -284,14 +309,58 @@ class CudaBackend : public Backend {
     cudaFree(p);
     return proto::kOk;
   }
-  int hostmem_alloc(size_t bytes, void** out) override {
+  int hostmem_alloc(size_t bytes, bool shareable, void** out) override {
     void* p = nullptr;
+    if (shareable) {
+      // Shared host memory that this process and the clients both register with CUDA, the
+      // way the semaphore pages are made. Kernels get the host address, which is only a
+      // valid device address where the platform says so.
+      if (!host_ptr_is_dev_ptr_) return proto::kErrUnsupported;
+      const size_t page = (size_t)sysconf(_SC_PAGESIZE);
+      const size_t size = (bytes + page - 1) / page * page;
+      int fd = ipc::memfd_make("mccs-status", size);
+      if (fd < 0) return proto::kErrOutOfMemory;
+      p = ipc::map_shared(fd, size);
+      if (!p) { close(fd); return proto::kErrOutOfMemory; }
+      memset(p, 0, size);
+      cudaError_t e = cudaHostRegister(p, size, cudaHostRegisterPortable | cudaHostRegisterMapped);
+      void* d = nullptr;
+      if (e == cudaSuccess) e = cudaHostGetDevicePointer(&d, p, 0);
+      if (e != cudaSuccess || d != p) {
+        LOG_ERROR("registering a shared status block failed: %s", e != cudaSuccess ? cudaGetErrorString(e) : "device address differs from host address");
+        if (e == cudaSuccess) cudaHostUnregister(p);
+        cudaGetLastError();
+        ipc::unmap_shared(p, size);
+        close(fd);
+        return proto::kErrDevice;
+      }
+      std::lock_guard<std::mutex> g(mu_);
+      shared_host_.push_back({p, size, fd});
+      *out = p;
+      return proto::kOk;
+    }
     RT_CHECK(cudaHostAlloc(&p, bytes, cudaHostAllocPortable | cudaHostAllocMapped), proto::kErrOutOfMemory);
     memset(p, 0, bytes);
     *out = p;
     return proto::kOk;
   }
-  int hostmem_free(void* p) override { if (p) cudaFreeHost(p); return proto::kOk; }
+  int hostmem_free(void* p) override {
+    if (!p) return proto::kOk;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      for (size_t i = 0; i < shared_host_.size(); i++) {
+        if (shared_host_[i].p != p) continue;
+        cudaHostUnregister(p);
+        cudaGetLastError();
+        ipc::unmap_shared(p, shared_host_[i].size);
+        close(shared_host_[i].fd);
+        shared_host_.erase(shared_host_.begin() + (long)i);
+        return proto::kOk;
+      }
+    }
+    cudaFreeHost(p);
+    return proto::kOk;
+  }
 
   // ------------------------------------------------------------ streams and events
   int stream_create(int dev, int priority, void** stream) override {
@@ -516,9 +585,23 @@ class CudaBackend : public Backend {
     return max_cooperative_ctas(variant, dtype, op, threads, nranks);
   }
 
-  // Scratch of this backend is not exported to clients yet (client-side launch is
-  // offered by the host backend only).
-  int scratch_export(void*, int*, size_t*) override { return proto::kErrUnsupported; }
+  // Client-side launch needs pads and FIFOs that other processes can import (VMM with
+  // descriptor export) and status blocks whose host address is also their device address.
+  bool client_launch_supported() const override { return vmm_ && host_ptr_is_dev_ptr_; }
+  int scratch_export(void* p, int* fd, size_t* bytes, uint32_t* share_kind) override {
+    std::lock_guard<std::mutex> g(mu_);
+    for (const Scratch& sc : scratch_)
+      if (sc.va == (uint64_t)p && sc.fd >= 0) {
+        *fd = sc.fd; *bytes = sc.size; *share_kind = proto::kShareVmmFd;
+        return proto::kOk;
+      }
+    for (const SharedHost& sh : shared_host_)
+      if (sh.p == p) {
+        *fd = sh.fd; *bytes = sh.size; *share_kind = proto::kShareHostFd;
+        return proto::kOk;
+      }
+    return proto::kErrNotFound;
+  }
 
   bool batch_supported(int variant, int dtype, int op) const override {
     if (variant_is_nvls(variant) && !nvls_) return false;
@@ -550,7 +633,8 @@ class CudaBackend : public Backend {
   }
 
  private:
-  struct Scratch { uint64_t va, handle; size_t size; };
+  struct Scratch { uint64_t va, handle; size_t size; int fd; };   // fd: exported handle, -1 when not shareable
+  struct SharedHost { void* p; size_t size; int fd; };
 
   void log_cu(const char* what, CUresult r) {
     const char* s = nullptr;
@@ -686,6 +770,8 @@ class CudaBackend : public Backend {
   Driver drv_;
   std::mutex mu_;
   std::vector<Scratch> scratch_;
+  std::vector<SharedHost> shared_host_;
+  bool host_ptr_is_dev_ptr_ = false;
 };
 
 }  // namespace

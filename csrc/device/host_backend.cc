@@ -196,7 +196,7 @@ class HostBackend : public Backend {
   }
   // Scratch lives in anonymous shared memory so that a client process can map it too
   // (client-side launch: its kernels address every rank's pads, status blocks and FIFOs).
-  int scratch_alloc(int, size_t bytes, bool, void** out) override {
+  int scratch_alloc(int, size_t bytes, bool, bool, void** out) override {
     const size_t page = (size_t)sysconf(_SC_PAGESIZE);
     const size_t size = (bytes + page - 1) / page * page;
     int fd = ipc::memfd_make("mccs-scratch", size);
@@ -224,14 +224,16 @@ class HostBackend : public Backend {
     close(e.first);
     return proto::kOk;
   }
-  int hostmem_alloc(size_t bytes, void** out) override { return scratch_alloc(0, bytes, true, out); }
+  int hostmem_alloc(size_t bytes, bool, void** out) override { return scratch_alloc(0, bytes, true, true, out); }
   int hostmem_free(void* p) override { return scratch_free(0, p, 0, true); }
-  int scratch_export(void* p, int* fd, size_t* bytes) override {
+  bool client_launch_supported() const override { return true; }
+  int scratch_export(void* p, int* fd, size_t* bytes, uint32_t* share_kind) override {
     std::lock_guard<std::mutex> g(scratch_mu_);
     auto it = scratch_.find(p);
     if (it == scratch_.end()) return proto::kErrNotFound;
     *fd = it->second.first;
     *bytes = it->second.second;
+    *share_kind = proto::kShareHostFd;
     return proto::kOk;
   }
 

@@ -74,6 +74,7 @@ struct Driver {
   DRV_FN(cuMemHostRegister);
   DRV_FN(cuMemHostUnregister);
   DRV_FN(cuMemHostGetDevicePointer);
+  DRV_FN(cuCtxSynchronize);
   bool memops = false;
 };
 Driver g_drv;
@@ -112,6 +113,7 @@ bool load_driver() {
                  sym(l, "cuMemHostRegister_v2", &g_drv.cuMemHostRegister_) &&
                  sym(l, "cuMemHostUnregister", &g_drv.cuMemHostUnregister_) &&
                  sym(l, "cuMemHostGetDevicePointer_v2", &g_drv.cuMemHostGetDevicePointer_);
+  sym(l, "cuCtxSynchronize", &g_drv.cuCtxSynchronize_);
   if (g_drv.ok && g_drv.cuInit_(0) != CUDA_SUCCESS) g_drv.ok = false;
   return g_drv.ok;
 }
@@ -158,6 +160,17 @@ struct MemRec {
   int device = 0;
   uint32_t share_kind = 0;
   uint64_t vmm_handle = 0;
+};
+
+// A block of another owner (a peer's buffer, a rank's signal pad, status block or FIFOs)
+// mapped into this process for client-side launch.
+struct Mapped {
+  uint64_t addr = 0;        // the address kernels launched here use
+  void* host = nullptr;     // CPU-readable address, null for device memory
+  size_t bytes = 0;
+  uint32_t share_kind = 0;
+  uint64_t vmm_handle = 0;
+  bool registered = false;  // host memory registered with CUDA here
 };
 
 struct StreamRec {
@@ -229,13 +242,10 @@ struct mccsComm {
   // are launched here and address every rank's pads, status blocks, FIFOs and buffers
   bool client_launch = false;
   ipc::Ring pq;
-  SignalPad* pads[kMaxRanks] = {nullptr};
-  StatusBlock* status[kMaxRanks] = {nullptr};
-  char* fifo[kMaxRanks] = {nullptr};
-  size_t pad_bytes[kMaxRanks] = {0}, status_bytes[kMaxRanks] = {0}, fifo_bytes[kMaxRanks] = {0};
+  Mapped pad_map[kMaxRanks], status_map[kMaxRanks], fifo_map[kMaxRanks];
   uint64_t fifo_slot_bytes = 0;
-  struct PeerMem { uint64_t base; size_t size; };
-  std::map<uint64_t, PeerMem> peer_mem;                // allocations of other ranks, mapped on first use
+  std::map<uint64_t, Mapped> peer_mem;                 // allocations of other ranks, mapped on first use
+  bool launched_here = false;                          // a kernel of this communicator may still be running on a caller's stream
 };
 
 namespace {
@@ -471,6 +481,109 @@ void unmap_allocation(const MemRec& rec) {
   }
 }
 
+// The collective kernels for client-side launch on a GPU live in a library of their own
+// next to this one (it carries the device code and a static CUDA runtime), loaded when the
+// first communicator in that mode is created.
+typedef unsigned long long (*KernelsAbiFn)(void);
+typedef int (*KernelsLaunchFn)(int, const CollArgs*, int, int, void*, const char**);
+struct KernelsLib {
+  bool tried = false;
+  void* lib = nullptr;
+  KernelsLaunchFn launch = nullptr;
+};
+KernelsLib g_klib;
+
+bool load_kernels_lib() {   // g_ctx.mu held
+  if (g_klib.tried) return g_klib.launch != nullptr;
+  g_klib.tried = true;
+  std::string path = "libmccs_kernels.so";
+  Dl_info info;
+  if (dladdr((void*)&load_kernels_lib, &info) && info.dli_fname) {
+    std::string self = info.dli_fname;
+    size_t slash = self.rfind('/');
+    if (slash != std::string::npos) path = self.substr(0, slash + 1) + path;
+  }
+  const char* over = getenv("MCCS_KERNELS_LIB");
+  if (over && over[0]) path = over;
+  g_klib.lib = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL);
+  if (!g_klib.lib) { LOG_ERROR("client-side launch: cannot load %s: %s", path.c_str(), dlerror()); return false; }
+  KernelsAbiFn abi = (KernelsAbiFn)dlsym(g_klib.lib, "mccs_kernels_abi");
+  KernelsLaunchFn fn = (KernelsLaunchFn)dlsym(g_klib.lib, "mccs_kernels_launch");
+  if (!abi || !fn || abi() != sizeof(CollArgs)) {
+    LOG_ERROR("client-side launch: %s does not match this library", path.c_str());
+    return false;
+  }
+  g_klib.launch = fn;
+  return true;
+}
+
+// Client-side launch: maps a block described by a kMapScratch / kMapMem reply for the
+// kernels this process launches on `device` (-1: host backend). The descriptor stays the
+// caller's to close.
+mccsResult_t map_block(int fd, size_t bytes, uint32_t share_kind, uint64_t daemon_va, int device, Mapped* out) {
+  *out = Mapped();
+  out->bytes = bytes;
+  out->share_kind = share_kind;
+  if (share_kind == proto::kShareSameProcess) {
+    out->addr = daemon_va;
+    return daemon_va ? mccsSuccess : mccsProtocolError;
+  }
+  if (share_kind == proto::kShareVmmFd) {
+    // Device memory of any GPU of the box: imported and made accessible to `device`.
+    MemRec rec;
+    rec.size = bytes;
+    rec.device = device;
+    rec.share_kind = share_kind;
+    mccsResult_t r = map_allocation(rec, fd, nullptr, 0);
+    if (r != mccsSuccess) return r;
+    out->addr = rec.base;
+    out->vmm_handle = rec.vmm_handle;
+    return mccsSuccess;
+  }
+  if (share_kind != proto::kShareHostFd || fd < 0) return mccsUnsupported;
+  void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  if (p == MAP_FAILED) return mccsOutOfMemory;
+  out->host = p;
+  out->addr = (uint64_t)p;
+  if (device >= 0) {
+    // Shared host memory that kernels address: pinned and mapped into the device's
+    // address space here, as the daemon did on its side.
+    CtxScope scope(device);
+    if (!scope.ok || !g_drv.memops) { munmap(p, bytes); return mccsDeviceError; }
+    CUresult cr = g_drv.cuMemHostRegister_(p, bytes, CU_MEMHOSTREGISTER_PORTABLE | CU_MEMHOSTREGISTER_DEVICEMAP);
+    CUdeviceptr d = 0;
+    if (cr == CUDA_SUCCESS) {
+      out->registered = true;
+      cr = g_drv.cuMemHostGetDevicePointer_(&d, p, 0);
+    }
+    if (cr != CUDA_SUCCESS) {
+      LOG_ERROR("registering shared host memory for client-side launch: %s", cu_err(cr));
+      if (out->registered) g_drv.cuMemHostUnregister_(p);
+      munmap(p, bytes);
+      *out = Mapped();
+      return mccsDeviceError;
+    }
+    out->addr = (uint64_t)d;
+  }
+  return mccsSuccess;
+}
+
+void unmap_block(Mapped& m, int device) {
+  if (!m.addr) return;
+  if (m.share_kind == proto::kShareVmmFd) {
+    MemRec rec;
+    rec.base = m.addr; rec.size = m.bytes; rec.device = device; rec.share_kind = m.share_kind; rec.vmm_handle = m.vmm_handle;
+    unmap_allocation(rec);
+  } else if (m.share_kind == proto::kShareHostFd && m.host) {
+    if (m.registered && g_drv.ok) {
+      CtxScope scope(device);
+      if (scope.ok) g_drv.cuMemHostUnregister_(m.host);
+    }
+    munmap(m.host, m.bytes);
+  }
+  m = Mapped();
+}
+
 // Spins for the completion of the oldest outstanding request of `comm`.
 mccsResult_t wait_completion(mccsComm* comm, proto::WorkCompletion* wc) {
   struct timespec t0;
@@ -635,24 +748,22 @@ mccsResult_t resolve_mem(mccsComm* comm, uint64_t mem_id, uint64_t off, uint64_t
     std::vector<int> fds;
     mccsResult_t r = roundtrip(g, m, sizeof(proto::MapMemReq), proto::kMapMemReply, &fds, 30000);
     if (r != mccsSuccess) return r;
-    if (fds.empty() || m.map_mem_reply.share_kind != proto::kShareHostFd) {
-      for (int f : fds) close(f);
-      return mccsUnsupported;
-    }
-    void* p = mmap(nullptr, m.map_mem_reply.bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
+    Mapped mp;
+    r = map_block(fds.empty() ? -1 : fds[0], (size_t)m.map_mem_reply.bytes, m.map_mem_reply.share_kind, m.map_mem_reply.daemon_va,
+                  g_ctx.backend == proto::kBackendCuda ? comm->device : -1, &mp);
     for (int f : fds) close(f);
-    if (p == MAP_FAILED) return mccsOutOfMemory;
-    it = comm->peer_mem.emplace(mem_id, mccsComm::PeerMem{(uint64_t)p, (size_t)m.map_mem_reply.bytes}).first;
+    if (r != mccsSuccess) return r;
+    it = comm->peer_mem.emplace(mem_id, mp).first;
   }
-  if (off > it->second.size) return mccsInvalidArgument;
-  *out = it->second.base + off;
+  if (off > it->second.bytes) return mccsInvalidArgument;
+  *out = it->second.addr + off;
   return mccsSuccess;
 }
 
 // Client-side launch: post the request, wait for the plan the daemon makes for all ranks
 // (variant, launch shape, barrier epoch, ticket, ring order, everybody's buffers), and
 // launch this rank's kernel here. The daemon never touches a stream for this collective.
-mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr) {
+mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t stream) {
   if (comm->sticky_error) return (mccsResult_t)comm->sticky_error;
   wr.comm_handle = comm->handle;
   wr.user_seq = comm->next_user_seq++;
@@ -706,17 +817,39 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr) {
     if (rr != mccsSuccess) return rr;
     a.send[r] = (const void*)s;
     a.recv[r] = (void*)d;
-    a.pad[r] = comm->pads[r];
-    a.status[r] = comm->status[r];
-    a.fifo[r] = comm->fifo[r];
+    a.pad[r] = (SignalPad*)comm->pad_map[r].addr;
+    a.status[r] = (StatusBlock*)comm->status_map[r].addr;
+    a.fifo[r] = (char*)comm->fifo_map[r].addr;
   }
   a.fifo_slot_bytes = comm->fifo_slot_bytes;
   memcpy(a.ring, plan.ring, sizeof a.ring);
   for (int ch = 0; ch < kMaxRingChannels; ch++) a.ring_step_base[ch] = plan.ring_step_base[ch];
   LaunchDims dims{plan.ctas, plan.threads};
-  if (g_ctx.backend != proto::kBackendHost) return mccsUnsupported;   // the GPU form loads the kernels into the caller's context
+  const StatusBlock* mine = (const StatusBlock*)comm->status_map[comm->rank].host;
+  if (g_ctx.backend == proto::kBackendCuda) {
+    // On the caller's stream, in the caller's context: ordered against the caller's other
+    // work like any kernel of its own. An error a previous kernel left behind (a wait that
+    // ran out, an abort raised by the daemon) ends the communicator before the next launch.
+    uint32_t before = __atomic_load_n(&mine->error, __ATOMIC_ACQUIRE);
+    if (before != 0) {
+      comm->sticky_error = before == kDevAborted ? mccsAborted : mccsTimeout;
+      return (mccsResult_t)comm->sticky_error;
+    }
+    if (!g_klib.launch) return mccsUnsupported;
+    CtxScope scope(comm->device);
+    if (!scope.ok) return mccsDeviceError;
+    const char* what = nullptr;
+    int e = g_klib.launch(plan.kind, &a, dims.ctas, dims.threads, (void*)stream, &what);
+    if (e != 0) {
+      LOG_ERROR("client-side launch of %s failed: %s", variant_name(plan.variant), what ? what : "?");
+      comm->sticky_error = mccsDeviceError;
+      return mccsDeviceError;
+    }
+    comm->launched_here = true;
+    return mccsSuccess;
+  }
   if (!emulated_launch_rank(plan.kind, a, dims)) return mccsUnsupported;
-  const uint32_t err = __atomic_load_n(&comm->status[comm->rank]->error, __ATOMIC_ACQUIRE);
+  const uint32_t err = __atomic_load_n(&mine->error, __ATOMIC_ACQUIRE);
   if (err != 0) {
     comm->sticky_error = err == kDevAborted ? mccsAborted : mccsTimeout;
     return (mccsResult_t)comm->sticky_error;
@@ -745,7 +878,7 @@ mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, vo
       if (r != mccsSuccess) return r;
     }
   }
-  if (comm->client_launch) return submit_client_launch(comm, wr);
+  if (comm->client_launch) return submit_client_launch(comm, wr, stream);
   if (comm->sync_base) return submit_memops(comm, wr, stream);
   wr.comm_handle = comm->handle;
   wr.stream_id = srec->stream_id;
@@ -1032,21 +1165,38 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
         q.map_scratch.kind = kind;
         std::vector<int> sfds;
         mccsResult_t mr = roundtrip(g, q, sizeof(proto::MapScratchReq), proto::kMapScratchReply, &sfds, 30000);
-        void* p = MAP_FAILED;
-        if (mr == mccsSuccess && !sfds.empty())
-          p = mmap(nullptr, q.map_scratch_reply.bytes, PROT_READ | PROT_WRITE, MAP_SHARED, sfds[0], 0);
+        Mapped mp;
+        if (mr == mccsSuccess)
+          mr = map_block(sfds.empty() ? -1 : sfds[0], (size_t)q.map_scratch_reply.bytes, q.map_scratch_reply.share_kind,
+                         q.map_scratch_reply.daemon_va, g_ctx.backend == proto::kBackendCuda ? device : -1, &mp);
         for (int f : sfds) close(f);
-        if (p == MAP_FAILED) {
+        if (mr != mccsSuccess) {
           LOG_ERROR("cannot map rank %d's %s of communicator %u", r, kind == proto::kScratchPad ? "signal pad" : kind == proto::kScratchStatus ? "status block" : "FIFOs", c->id);
           g_ctx.comms.push_back(c);      // mccsCommDestroy below undoes what exists so far
           g.unlock();
           mccsCommDestroy(c);
-          return mr != mccsSuccess ? mr : mccsOutOfMemory;
+          return mr;
         }
-        if (kind == proto::kScratchPad) { c->pads[r] = (SignalPad*)p; c->pad_bytes[r] = q.map_scratch_reply.bytes; }
-        else if (kind == proto::kScratchStatus) { c->status[r] = (StatusBlock*)p; c->status_bytes[r] = q.map_scratch_reply.bytes; }
-        else { c->fifo[r] = (char*)p; c->fifo_bytes[r] = q.map_scratch_reply.bytes; }
+        // inside the daemon's process the status block is the daemon's own (registered) host memory
+        if (kind == proto::kScratchStatus && mp.share_kind == proto::kShareSameProcess) mp.host = (void*)mp.addr;
+        if (kind == proto::kScratchPad) c->pad_map[r] = mp;
+        else if (kind == proto::kScratchStatus) c->status_map[r] = mp;
+        else c->fifo_map[r] = mp;
       }
+    }
+    // The status block of this rank is read by the CPU here (device errors, the abort word).
+    if (!c->status_map[rank].host) {
+      LOG_ERROR("communicator %u: this rank's status block is not readable by the CPU", c->id);
+      g_ctx.comms.push_back(c);
+      g.unlock();
+      mccsCommDestroy(c);
+      return mccsProtocolError;
+    }
+    if (g_ctx.backend == proto::kBackendCuda && !load_kernels_lib()) {
+      g_ctx.comms.push_back(c);
+      g.unlock();
+      mccsCommDestroy(c);
+      return mccsUnsupported;
     }
   }
   g_ctx.comms.push_back(c);
@@ -1084,6 +1234,12 @@ mccsResult_t mccsCommFlush(mccsComm_t comm) {
 mccsResult_t mccsCommDestroy(mccsComm_t comm) {
   if (!comm) return mccsSuccess;
   if (g_ctx.connected) mccsCommFlush(comm);   // every posted request has been taken by the daemon
+  if (comm->launched_here && g_ctx.backend == proto::kBackendCuda && g_drv.cuCtxSynchronize_) {
+    // Kernels of this communicator run on the caller's streams: they must be through
+    // before the daemon takes the pads and FIFOs away. Their waits are bounded.
+    CtxScope scope(comm->device);
+    if (scope.ok) g_drv.cuCtxSynchronize_();
+  }
   std::unique_lock<std::mutex> g(g_ctx.mu);
   mccsResult_t r = mccsSuccess;
   if (g_ctx.connected) {
@@ -1100,12 +1256,13 @@ mccsResult_t mccsCommDestroy(mccsComm_t comm) {
   for (size_t i = 0; i < g_ctx.comms.size(); i++)
     if (g_ctx.comms[i] == comm) { g_ctx.comms.erase(g_ctx.comms.begin() + (long)i); break; }
   if (comm->dp_mem) munmap(comm->dp_mem, comm->dp_bytes);
+  const int map_dev = g_ctx.backend == proto::kBackendCuda ? comm->device : -1;
   for (int r = 0; r < kMaxRanks; r++) {
-    if (comm->pads[r]) munmap(comm->pads[r], comm->pad_bytes[r]);
-    if (comm->status[r]) munmap(comm->status[r], comm->status_bytes[r]);
-    if (comm->fifo[r]) munmap(comm->fifo[r], comm->fifo_bytes[r]);
+    unmap_block(comm->pad_map[r], map_dev);
+    unmap_block(comm->status_map[r], map_dev);
+    unmap_block(comm->fifo_map[r], map_dev);
   }
-  for (auto& kv : comm->peer_mem) munmap((void*)kv.second.base, kv.second.size);
+  for (auto& kv : comm->peer_mem) unmap_block(kv.second, map_dev);
   if (comm->sync_host) {
     if (!comm->sync_emulated) {
       CtxScope scope(comm->device);
