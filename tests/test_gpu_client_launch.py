@@ -1,0 +1,114 @@
+"""Client-side launch on GPUs: `[b200] launch = "client"` with the CUDA backend. One client
+process per GPU; each maps its peers' buffers, signal pads, status blocks and FIFOs
+(exported VMM handles, shared registered host memory), loads `libmccs_kernels.so` and
+launches its own rank's kernel on its own stream from the plan the daemon published.
+
+Opt-in (`MCCS_TEST_CLIENT_LAUNCH=1`) until the mode has had its first run on a GPU box: the
+regular GPU suite must not depend on code that was only ever exercised on the CPU emulator
+(`tests/test_service_emulated_kernels.py::test_client_side_launch` covers the protocol and
+the daemon's side there). With one GPU only the single-rank copy can be launched by a
+client; several ranks on one GPU stay with the daemon's cooperative launch by design.
+"""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import REPO, write_config
+
+pytestmark = [
+    pytest.mark.gpu,
+    pytest.mark.skipif(os.environ.get("MCCS_TEST_CLIENT_LAUNCH") != "1", reason="opt-in: MCCS_TEST_CLIENT_LAUNCH=1"),
+]
+
+CLIENT = r"""
+import os, sys, json, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"]); port = int(os.environ["ADMIN_PORT"])
+torch.cuda.set_device(rank)
+DT = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16, "i32": torch.int32}
+def inputs(dt, count, salt):
+    g = torch.Generator().manual_seed(1000 * salt + count)
+    return [torch.randint(-4, 5, (count,), generator=g).to(dt) for _ in range(n)]
+send = M.Buffer(8 << 20, rank); recv = M.Buffer(16 << 20, rank)
+comm = M.Communicator(6300, rank, n, device=rank)
+bad, seen, salt = [], set(), 0
+def allreduce(algo, dname, count, op="sum", in_place=False):
+    global salt
+    salt += 1
+    dt = DT[dname]
+    xs = inputs(dt, count, salt)
+    s = send.tensor(dt, count); s.copy_(xs[rank])
+    d = s if in_place else recv.tensor(dt, count)
+    comm.all_reduce(s, None if in_place else d, op=op, algo=algo)
+    acc = torch.stack([x.double() for x in xs])
+    want = {"sum": acc.sum(0), "max": acc.max(0).values, "avg": acc.sum(0) / n}[op]
+    tol = {"bf16": 0.05 * n, "f16": 0.01 * n}.get(dname, 1e-6)
+    if not torch.allclose(d.double().cpu(), want, rtol=0, atol=tol):
+        bad.append(("allreduce", algo, dname, count, op, in_place))
+    seen.add(comm.last_plan()[0])
+def allgather(algo, nbytes):
+    global salt
+    salt += 1
+    xs = [((torch.arange(nbytes) * (r + 3) + salt) % 251).to(torch.uint8) for r in range(n)]
+    out = recv.tensor(torch.uint8, nbytes * n)
+    s = send.tensor(torch.uint8, nbytes); s.copy_(xs[rank])
+    comm.all_gather(s, out, algo=algo)
+    if not torch.equal(out.cpu(), torch.cat(xs)):
+        bad.append(("allgather", algo, nbytes))
+    seen.add(comm.last_plan()[0])
+ar = ("ar_oneshot", "ar_twoshot", "ar_ring", "auto") if n > 1 else ("auto",)
+ag = ("ag_pull", "ag_push", "ag_ring", "auto") if n > 1 else ("auto",)
+for algo in ar:
+    for dname, count in (("f32", 1), ("f32", 4099), ("bf16", 3001), ("i32", 257), ("f16", 2048), ("bf16", 1 << 20)):
+        allreduce(algo, dname, count)
+    allreduce(algo, "f32", 1000, op="avg")
+    allreduce(algo, "i32", 500, op="max")
+    if algo != "ar_oneshot":
+        allreduce(algo, "f32", 5000, in_place=True)
+for algo in ag:
+    for nbytes in (16, 1000, 40000, 1 << 20):
+        allgather(algo, nbytes)
+# back to back on the stream without looking at the results in between
+t = send.tensor(torch.float32, 1 << 16)
+t.fill_(1.0)
+for _ in range(50):
+    comm.all_reduce(t, op="avg")
+torch.cuda.synchronize()
+if not bool(torch.all(t == 1.0)):
+    bad.append(("chain",))
+q = comm.query()
+st = M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"]["6300"]
+comm.destroy()
+print("RESULT", json.dumps({"bad": bad, "seen": sorted(seen), "async_error": q["async_error"], "device_error": q["device_error"],
+                            "client_launch": st["client_launch"], "completed": st["completed"]}), flush=True)
+"""
+
+
+def test_client_side_launch_on_gpus(tmp_path):
+    from mccs_b200 import daemon
+    n = min(torch.cuda.device_count(), 4)
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, wait_timeout_ms=2000,
+                       extra='launch = "client"')
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn", "NCCL_NVLS_ENABLE": "0"})
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), MCCS_LOG="error",
+                   ADMIN_PORT=str(sp.admin_port), MCCS_WC_TIMEOUT_MS="60000")
+        procs = [subprocess.Popen([sys.executable, "-c", CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                                  stderr=subprocess.PIPE, text=True) for r in range(n)]
+        for p in procs:
+            out, err = p.communicate(timeout=600)
+            assert p.returncode == 0, err[-3000:]
+            res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+            assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
+            assert res["client_launch"] is True
+            if n > 1:
+                assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
+            else:
+                assert set(res["seen"]) == {"local_copy"}
+    finally:
+        sp.stop()
