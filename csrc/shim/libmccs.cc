@@ -246,6 +246,8 @@ struct mccsComm {
   uint64_t fifo_slot_bytes = 0;
   std::map<uint64_t, Mapped> peer_mem;                 // allocations of other ranks, mapped on first use
   bool launched_here = false;                          // a kernel of this communicator may still be running on a caller's stream
+  CUevent launch_event = nullptr;                      // deferred waiting: recorded behind the newest kernel launched here
+  bool launch_event_set = false;
 };
 
 namespace {
@@ -846,6 +848,15 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
       return mccsDeviceError;
     }
     comm->launched_here = true;
+    if (comm->deferred_wait) {
+      // The caller will name the stream that needs the results later (mccsCommWait).
+      if (!comm->launch_event && g_drv.cuEventCreate_(&comm->launch_event, CU_EVENT_DISABLE_TIMING) != CUDA_SUCCESS) {
+        comm->launch_event = nullptr;
+        return mccsDeviceError;
+      }
+      if (g_drv.cuEventRecord_(comm->launch_event, (CUstream)stream) != CUDA_SUCCESS) return mccsDeviceError;
+      comm->launch_event_set = true;
+    }
     return mccsSuccess;
   }
   if (!emulated_launch_rank(plan.kind, a, dims)) return mccsUnsupported;
@@ -1253,6 +1264,10 @@ mccsResult_t mccsCommDestroy(mccsComm_t comm) {
     CtxScope scope(comm->device);
     g_drv.cuEventDestroy_(comm->backend_event);
   }
+  if (comm->launch_event && g_drv.ok) {
+    CtxScope scope(comm->device);
+    g_drv.cuEventDestroy_(comm->launch_event);
+  }
   for (size_t i = 0; i < g_ctx.comms.size(); i++)
     if (g_ctx.comms[i] == comm) { g_ctx.comms.erase(g_ctx.comms.begin() + (long)i); break; }
   if (comm->dp_mem) munmap(comm->dp_mem, comm->dp_bytes);
@@ -1346,6 +1361,17 @@ mccsResult_t mccsCommWait(mccsComm_t comm, mccsStream_t stream) {
     return (mccsResult_t)comm->sticky_error;
   }
   if (g_ctx.backend != proto::kBackendCuda) return mccsSuccess;
+  if (comm->client_launch) {
+    // The kernels ran on the streams the collectives were given; `stream` waits for the
+    // newest of them (launches of one communicator are made in order).
+    if (comm->sticky_error) return (mccsResult_t)comm->sticky_error;
+    if (!comm->launch_event_set) return mccsSuccess;
+    CtxScope scope(comm->device);
+    if (!scope.ok) return mccsDeviceError;
+    CUresult cr = g_drv.cuStreamWaitEvent_((CUstream)stream, comm->launch_event, 0);
+    if (cr != CUDA_SUCCESS) { LOG_ERROR("cuStreamWaitEvent: %s", cu_err(cr)); return mccsDeviceError; }
+    return mccsSuccess;
+  }
   if (comm->sync_base) {
     if (!comm->last_posted_seq) return mccsSuccess;
     CtxScope scope(comm->device);

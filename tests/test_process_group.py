@@ -81,14 +81,17 @@ def _free_port() -> int:
     return p
 
 
-@pytest.fixture(params=["events", "memops"])
+@pytest.fixture(params=["events", "memops", "client"])
 def standalone_daemon(request):
-    """Both ways of ordering collectives against the caller: events with completion
-    messages, and the semaphore protocol (done by the CPU on the host backend)."""
+    """The ways of ordering collectives against the caller: events with completion
+    messages, the semaphore protocol (done by the CPU on the host backend), and kernels
+    launched by the client library itself (the real kernels on the emulator)."""
     from mccs_b200 import daemon
     d = tempfile.mkdtemp(prefix="mccs-pg-")
+    client = request.param == "client"
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=0,
-                       force_host=True, sync=request.param)
+                       force_host=True, sync="events" if client else request.param,
+                       extra='host_kernels = "emulated"\nlaunch = "client"' if client else "")
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
     yield sp
     sp.stop()
