@@ -230,7 +230,8 @@ struct alignas(64) PlanMsg {
   struct { uint64_t send_mem, send_off, recv_mem, recv_off; } rank[8];
   int8_t ring[32][8];
   uint64_t ring_step_base[32];
-  uint8_t reserved[184];
+  int32_t trace;           // 1: the kernel stamps its start and end time into the status block
+  uint8_t reserved[180];
 };
 static_assert(sizeof(PlanMsg) == kPlanBytes, "a plan must fill one slot of the plan ring");
 

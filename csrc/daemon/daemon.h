@@ -188,6 +188,7 @@ class Communicator {
   // --- multicast registrations, keyed by the allocation ids of all ranks ------------
   std::mutex mc_mu;
   std::map<std::vector<uint64_t>, McRegion> mc_cache;
+  uint64_t next_mc_id = 0;   // under mc_mu
   std::mutex admit_mu;
 
   CollSlot& slot(uint64_t seq) { return slots[seq % kCollSlots]; }

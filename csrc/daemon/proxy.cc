@@ -203,13 +203,15 @@ int ProxyEngine::ensure_mc(Communicator& c, CollSlot& s, bool for_recv, uint64_t
       allocs.push_back(a);
     }
     McRegion reg;
-    int rc = daemon_->backend()->mc_create(allocs, &reg);
+    int rc = daemon_->backend()->mc_create(allocs, &reg, c.client_launch);
     if (rc != proto::kOk) {
       // Remember the failure so that it is not retried on every collective.
       McRegion none;
       c.mc_cache[key] = none;
       return rc;
     }
+    reg.id = ++c.next_mc_id;
+    for (int r = 0; r < c.nranks; r++) reg.mems[r] = key[(size_t)r];
     LOG_INFO("comm %u: multicast region of %zu bytes bound for %d ranks", c.id, reg.size, c.nranks);
     it = c.mc_cache.emplace(key, reg).first;
   }
@@ -249,7 +251,7 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   in.host_staged = c.host_staged;
   in.fifo_slot_bytes = c.fifo_slot_bytes;
   uint64_t bits = o0.kind == kAllGather ? o0.count : 0;
-  bool same_send_off = true, same_recv_off = true, all_vmm = !host_backend;
+  bool same_send_off = true, same_recv_off = true, all_vmm = !host_backend || be->nvls_supported();   // the host backend's emulated multicast binds any of its allocations
   int req = o0.variant_req;
   for (int r = 0; r < c.nranks; r++) {
     const CollOp& o = s.ops[r];
@@ -786,6 +788,7 @@ bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
   m.ticket = s.ticket_base;
   m.count = o0.count;
   m.timeout_ns = daemon_->timeout_ns();
+  m.trace = daemon_->tracer().enabled() ? 1 : 0;
   for (int r = 0; r < c.nranks; r++) {
     m.rank[r].send_mem = s.ops[r].send_mem; m.rank[r].send_off = s.ops[r].send_off;
     m.rank[r].recv_mem = s.ops[r].recv_mem; m.rank[r].recv_off = s.ops[r].recv_off;

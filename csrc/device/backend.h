@@ -36,7 +36,11 @@ struct Allocation {
 // One multicast object with the same-offset allocation of every rank bound to it.
 struct McRegion {
   uint64_t handle = 0;
+  uint64_t id = 0;                // name of the region in plans handed to clients
   size_t size = 0;
+  size_t gran = 0;                // alignment a mapping of the object needs
+  int share_fd = -1;              // exported object (client-side launch), kept open until destroyed
+  uint64_t mems[kMaxRanks] = {0}; // the allocation bound per rank
   uint64_t va[kMaxRanks] = {0};   // mapping used by rank r's kernels
   int nranks = 0;
   int devices[kMaxRanks] = {0};
@@ -115,7 +119,8 @@ class Backend {
   virtual int sync_page_create(int dev, SyncPage* out) = 0;
   virtual int sync_page_destroy(int dev, SyncPage* p) = 0;
 
-  virtual int mc_create(const std::vector<const Allocation*>& per_rank, McRegion* out) = 0;
+  // `shareable`: the object can be handed to the clients' processes (client-side launch).
+  virtual int mc_create(const std::vector<const Allocation*>& per_rank, McRegion* out, bool shareable) = 0;
   virtual int mc_destroy(McRegion* r) = 0;
 
   // Launches one collective kernel on `stream` of `dev`. With a.emulated the grid

@@ -488,7 +488,7 @@ class CudaBackend : public Backend {
   }
 
   // ------------------------------------------------------------------- multicast
-  int mc_create(const std::vector<const Allocation*>& per_rank, McRegion* out) override {
+  int mc_create(const std::vector<const Allocation*>& per_rank, McRegion* out, bool shareable) override {
     DeviceGuard guard;
     if (!nvls_) return proto::kErrUnsupported;
     const int n = (int)per_rank.size();
@@ -504,7 +504,7 @@ class CudaBackend : public Backend {
     memset(&prop, 0, sizeof prop);
     prop.numDevices = (unsigned)n;
     prop.size = size;
-    prop.handleTypes = 0;
+    prop.handleTypes = shareable ? CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR : 0;
     size_t mc_gran = 0;
     CUresult r = drv_.cuMulticastGetGranularity_(&mc_gran, &prop, CU_MULTICAST_GRANULARITY_MINIMUM);
     if (r != CUDA_SUCCESS || mc_gran == 0) { log_cu("cuMulticastGetGranularity", r); return proto::kErrDevice; }
@@ -517,7 +517,14 @@ class CudaBackend : public Backend {
     McRegion reg;
     reg.handle = (uint64_t)mc;
     reg.size = size;
+    reg.gran = mc_gran;
     reg.nranks = n;
+    if (shareable) {
+      int fd = -1;
+      r = drv_.cuMemExportToShareableHandle_(&fd, mc, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+      if (r != CUDA_SUCCESS) { log_cu("cuMemExportToShareableHandle(multicast)", r); drv_.cuMemRelease_(mc); return proto::kErrDevice; }
+      reg.share_fd = fd;
+    }
     for (int i = 0; i < n; i++) {
       CUdevice dev;
       drv_.cuDeviceGet_(&dev, per_rank[i]->device);
@@ -571,6 +578,8 @@ class CudaBackend : public Backend {
       }
     }
     drv_.cuMemRelease_((CUmemGenericAllocationHandle)reg->handle);
+    if (reg->share_fd >= 0) close(reg->share_fd);
+    reg->share_fd = -1;
     reg->handle = 0;
     return proto::kOk;
   }

@@ -13,6 +13,7 @@
 #define dev dev_emulated
 #define MCCS_UNTYPED_KERNELS 1
 #include "../kernels/batch.cuh"
+#include "../kernels/hybrid.cuh"
 
 #include "emulated_kernels.h"
 
@@ -48,6 +49,16 @@ bool typed_allreduce(const CollArgs& a, int ctas, int threads) {
     }
     return false;
   };
+  // The in-switch variants: sums of the three floating-point types that multimem reduces.
+  if constexpr (std::is_same<T, float>::value || std::is_same<T, __half>::value || std::is_same<T, __nv_bfloat16>::value) {
+    if (a.op == kSum || a.op == kPreMulSum || a.op == kSumPostDiv) {
+      switch (a.variant) {
+        case kArNvlsOne: run_grid(ar_nvls_kernel<T, false>, a, a.nranks, ctas, threads); return true;
+        case kArNvlsTwo: run_grid(ar_nvls_kernel<T, true>, a, a.nranks, ctas, threads); return true;
+        case kArHybrid: run_grid(ar_hybrid_kernel<T>, a, a.nranks, ctas, threads); return true;
+      }
+    }
+  }
   switch (a.op) {
     case kSum: case kPreMulSum: case kSumPostDiv: return by_op(OpSum{});
     case kProd: return by_op(OpProd{});
@@ -59,8 +70,14 @@ bool typed_allreduce(const CollArgs& a, int ctas, int threads) {
 
 template <typename T>
 bool typed_batch(const BatchArgs& b, int ctas, int threads) {
-  if (b.base.variant != kArTwoShot) return false;
   const int n = b.base.nranks;
+  if constexpr (std::is_same<T, float>::value || std::is_same<T, __half>::value || std::is_same<T, __nv_bfloat16>::value) {
+    if (b.base.variant == kArNvlsTwo && (b.base.op == kSum || b.base.op == kPreMulSum || b.base.op == kSumPostDiv)) {
+      run_grid(ar_nvls_batch_kernel<T>, b, n, ctas, threads);
+      return true;
+    }
+  }
+  if (b.base.variant != kArTwoShot) return false;
   switch (b.base.op) {
     case kSum: case kPreMulSum: case kSumPostDiv: run_grid(ar_twoshot_batch_kernel<T, OpSum>, b, n, ctas, threads); return true;
     case kProd: run_grid(ar_twoshot_batch_kernel<T, OpProd>, b, n, ctas, threads); return true;
@@ -97,6 +114,14 @@ void clamp(int* ctas, int* threads, bool ring) {
 
 }  // namespace
 
+void emulated_mc_add(uint64_t base, size_t size, const std::vector<void*>& backing) {
+  std::vector<char*> b;
+  for (void* p : backing) b.push_back((char*)p);
+  sim_mc_add((uintptr_t)base, size, b);
+}
+
+void emulated_mc_remove(uint64_t base) { sim_mc_remove((uintptr_t)base); }
+
 bool emulated_launch_rank(int kind, const CollArgs& args, LaunchDims dims) {
   g_single_rank = true;
   const bool ok = emulated_launch(kind, args, dims);
@@ -119,6 +144,7 @@ bool emulated_launch(int kind, const CollArgs& args, LaunchDims dims) {
       case kAgPull: run_grid(ag_direct_kernel<kAgModePull>, a, a.nranks, ctas, threads); return true;
       case kAgPush: run_grid(ag_direct_kernel<kAgModePush>, a, a.nranks, ctas, threads); return true;
       case kAgRing: run_grid(ag_ring_kernel, a, a.nranks, ctas, threads); return true;
+      case kAgNvls: run_grid(ag_direct_kernel<kAgModeNvls>, a, a.nranks, ctas, threads); return true;
     }
     return false;
   }

@@ -8,6 +8,7 @@
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/mman.h>
 #include <unistd.h>
 
 #include <atomic>
@@ -163,7 +164,7 @@ class HostBackend : public Backend {
       : ndev_(opt.host_devices > 0 ? opt.host_devices : 1), emulate_(opt.emulate_kernels), memops_(opt.host_memops) {}
   uint32_t kind() const override { return proto::kBackendHost; }
   int device_count() const override { return ndev_; }
-  bool nvls_supported() const override { return false; }
+  bool nvls_supported() const override { return emulate_; }   // emulated multicast regions (see mc_create)
   bool peer_access(int, int) const override { return true; }
   std::string describe() const override {
     return "host backend (" + std::to_string(ndev_) + " emulated devices" + (emulate_ ? ", kernels on the SIMT emulator)" : ")");
@@ -285,13 +286,54 @@ class HostBackend : public Backend {
     p->fd = -1;
     return proto::kOk;
   }
-  int mc_create(const std::vector<const Allocation*>&, McRegion*) override { return proto::kErrUnsupported; }
-  int mc_destroy(McRegion*) override { return proto::kOk; }
+  // With the emulated kernels a multicast region is an address range that is reserved but
+  // never accessible; the emulator turns accesses to it into accesses to every rank's
+  // buffer at the same offset.
+  int mc_create(const std::vector<const Allocation*>& per_rank, McRegion* out, bool) override {
+    if (!emulate_) return proto::kErrUnsupported;
+    const int n = (int)per_rank.size();
+    if (n < 2 || n > kMaxRanks) return proto::kErrInvalidArgument;
+    size_t size = (size_t)-1;
+    std::vector<void*> backing;
+    for (const Allocation* a : per_rank) {
+      if (!a || !a->va) return proto::kErrUnsupported;
+      size = a->size < size ? a->size : size;
+      backing.push_back((void*)a->va);
+    }
+    const size_t page = (size_t)sysconf(_SC_PAGESIZE);
+    size = size / page * page;
+    if (size == 0) return proto::kErrUnsupported;
+    void* base = mmap(nullptr, size, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0);
+    if (base == MAP_FAILED) return proto::kErrOutOfMemory;
+    emulated_mc_add((uint64_t)base, size, backing);
+    McRegion reg;
+    reg.handle = (uint64_t)base;
+    reg.size = size;
+    reg.gran = page;
+    reg.nranks = n;
+    for (int r = 0; r < n; r++) { reg.va[r] = (uint64_t)base; reg.devices[r] = per_rank[r]->device; }
+    *out = reg;
+    return proto::kOk;
+  }
+  int mc_destroy(McRegion* reg) override {
+    if (!reg->handle) return proto::kOk;
+    emulated_mc_remove(reg->handle);
+    munmap((void*)reg->handle, reg->size);
+    reg->handle = 0;
+    return proto::kOk;
+  }
 
-  bool variant_supported(int variant, int, int) const override { return !variant_is_nvls(variant); }
+  bool variant_supported(int variant, int dtype, int op) const override {
+    if (!variant_is_nvls(variant)) return true;
+    if (!emulate_) return false;
+    if (variant == kAgNvls) return true;
+    return (dtype == kFloat32 || dtype == kFloat16 || dtype == kBfloat16) && (op == kSum || op == kPreMulSum || op == kSumPostDiv);
+  }
   int max_group_ctas(int, int, int, int, int) const override { return kMaxCtas; }
 
-  bool batch_supported(int variant, int, int) const override { return variant == kArTwoShot; }
+  bool batch_supported(int variant, int dtype, int op) const override {
+    return variant == kArTwoShot || (variant == kArNvlsTwo && variant_supported(variant, dtype, op));
+  }
   int max_group_batch_ctas(int, int, int, int, int) const override { return kMaxCtas; }
   int launch_batch(int dev, const BatchArgs& b, LaunchDims dims, void* stream) override {
     if (b.nops < 1 || b.nops > kMaxBatch) return proto::kErrInvalidArgument;

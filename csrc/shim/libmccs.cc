@@ -812,6 +812,7 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
   a.scale = plan.scale;
   a.epoch = plan.epoch;
   a.timeout_ns = plan.timeout_ns;
+  a.trace = plan.trace;
   for (int r = 0; r < comm->nranks; r++) {
     uint64_t s = 0, d = 0;
     mccsResult_t rr = resolve_mem(comm, plan.rank[r].send_mem, plan.rank[r].send_off, &s);

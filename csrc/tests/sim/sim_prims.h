@@ -7,6 +7,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <shared_mutex>
 #include <vector>
 
 namespace mccs {
@@ -51,14 +52,28 @@ template <int BYTES> inline void st_data(void* p, Raw<BYTES> v) {
 
 // Emulated multicast regions: [base, base + size) stands for the same offsets of every
 // rank's backing buffer.
+// The table may change while kernels of other communicators run (a service binds and
+// drops regions at any time): every multimem access holds the shared lock while it uses
+// an entry, sim_mc_add / sim_mc_remove take it exclusively.
 struct SimMcRegion { uintptr_t base; size_t size; std::vector<char*> backing; };
 inline std::vector<SimMcRegion>& sim_mc_regions() { static std::vector<SimMcRegion> v; return v; }
-inline const SimMcRegion& sim_mc_find(const void* mc, size_t* off) {
+inline std::shared_mutex& sim_mc_mutex() { static std::shared_mutex m; return m; }
+inline const SimMcRegion& sim_mc_find(const void* mc, size_t* off) {   // shared lock held by the caller
   const uintptr_t a = (uintptr_t)mc;
   for (const SimMcRegion& r : sim_mc_regions())
     if (a >= r.base && a + 16 <= r.base + r.size) { *off = a - r.base; return r; }
   fprintf(stderr, "simulated kernel: multimem access outside every multicast region (%p)\n", mc);
   abort();
+}
+inline void sim_mc_add(uintptr_t base, size_t size, const std::vector<char*>& backing) {
+  std::unique_lock<std::shared_mutex> g(sim_mc_mutex());
+  sim_mc_regions().push_back(SimMcRegion{base, size, backing});
+}
+inline void sim_mc_remove(uintptr_t base) {
+  std::unique_lock<std::shared_mutex> g(sim_mc_mutex());
+  auto& v = sim_mc_regions();
+  for (size_t i = 0; i < v.size(); i++)
+    if (v[i].base == base) { v.erase(v.begin() + (long)i); return; }
 }
 
 template <typename T> struct Multimem;
@@ -81,6 +96,7 @@ template <typename T> Raw<16> SimMultimem<T>::ld_reduce_add(const void* mc) {
   sim::chaos_point();
   sim_check_aligned(mc, 16);
   size_t off = 0;
+  std::shared_lock<std::shared_mutex> mc_guard(sim_mc_mutex());
   const SimMcRegion& r = sim_mc_find(mc, &off);
   constexpr int kN = 16 / (int)sizeof(T);
   float acc[kN];
@@ -100,6 +116,7 @@ inline void multimem_st16(void* mc, Raw<16> v) {
   sim::chaos_point();
   sim_check_aligned(mc, 16);
   size_t off = 0;
+  std::shared_lock<std::shared_mutex> mc_guard(sim_mc_mutex());
   const SimMcRegion& r = sim_mc_find(mc, &off);
   for (char* b : r.backing) memcpy(b + off, &v, 16);
 }

@@ -61,6 +61,17 @@ for algo in ("ar_oneshot", "ar_twoshot", "ar_ring", "auto"):
     allreduce(algo, "i32", 500, op="max")
     if algo != "ar_oneshot":
         allreduce(algo, "f32", 5000, in_place=True)
+if os.environ.get("NVLS") == "1":
+    # the in-switch variants on emulated multicast regions (floating-point sums; anything
+    # else asked of them is answered by a variant that can do it)
+    for algo in ("ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid"):
+        for dname, count in (("f32", 4), ("f32", 4100), ("bf16", 3000), ("f16", 2048), ("f32", 4099), ("i32", 256)):
+            allreduce(algo, dname, count)
+        allreduce(algo, "f32", 1000, op="avg")
+        allreduce(algo, "f32", 8192, in_place=True)
+        allreduce(algo, "f32", 512, op="max")
+    for nbytes in (16, 4096, 40000, 1000):
+        allgather("ag_nvls", nbytes)
 for algo in ("ag_pull", "ag_push", "ag_ring", "auto"):
     for nbytes in (16, 1000, 40000):
         allgather(algo, nbytes)
@@ -95,7 +106,7 @@ print("RESULT", json.dumps({"bad": bad, "seen": sorted(seen), "async_error": q["
 """
 
 
-def _run(tmp_path, n, extra, **kw):
+def _run(tmp_path, n, extra, client_env=None, **kw):
     from mccs_b200 import daemon
     d = str(tmp_path)
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=n, listen_port=-1, force_host=True,
@@ -105,6 +116,7 @@ def _run(tmp_path, n, extra, **kw):
         assert "SIMT emulator" in json.dumps(__import__("mccs_b200").admin_request(sp.admin_port, {"cmd": "stats"}))
         env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), MCCS_LOG="error",
                    ADMIN_PORT=str(sp.admin_port), MCCS_WC_TIMEOUT_MS="60000")
+        env.update(client_env or {})
         procs = [subprocess.Popen([sys.executable, "-c", CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
                                   stderr=subprocess.PIPE, text=True) for r in range(n)]
         results = []
@@ -128,6 +140,17 @@ def test_service_with_the_real_kernels_on_the_emulator(tmp_path, n, sync):
         # every emulated variant really ran
         assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
         assert res["epoch"] == 1 and res["fused_members"] >= 2 and res["client_launch"] is False
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_in_switch_variants_on_emulated_multicast(tmp_path, n):
+    """The NVLS kernels through the whole service without a GPU: the host backend binds
+    emulated multicast regions (an address range that stands for the same offsets of every
+    rank's buffer), so the multicast cache, the feasibility rules and the multicast
+    addresses in the kernels' arguments are exercised as on a GPU."""
+    for res in _run(tmp_path, n, "", client_env={"NVLS": "1"}):
+        assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
+        assert {"ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid", "ag_nvls"} <= set(res["seen"])
 
 
 def test_host_staged_transport_with_the_real_ring_kernels(tmp_path):
