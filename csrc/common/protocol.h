@@ -17,7 +17,7 @@ namespace mccs {
 namespace proto {
 
 constexpr uint32_t kMagic = 0x5343434du;  // "MCCS"
-constexpr uint32_t kVersion = 7;
+constexpr uint32_t kVersion = 8;
 constexpr uint32_t kWqDepth = 64;
 constexpr uint32_t kCqDepth = 64;
 constexpr uint32_t kWrBytes = 128;
@@ -36,6 +36,7 @@ enum MsgType : uint32_t {
   // client-side launch: a member of a communicator maps what its kernels must address
   kMapScratch = 16, kMapScratchReply = 17,   // a rank's signal pad / status block / FIFOs
   kMapMem = 18, kMapMemReply = 19,           // a peer's allocation named in a plan
+  kMapMc = 20, kMapMcReply = 21,             // a multicast region named in a plan
 };
 
 enum Status : int32_t {
@@ -177,6 +178,22 @@ struct MapScratchReply { Header h; uint64_t bytes; uint32_t share_kind; uint32_t
 struct MapMemReq { Header h; uint64_t comm_handle; uint64_t mem_id; };
 struct MapMemReply { Header h; uint64_t bytes; uint32_t share_kind; int32_t device; uint64_t daemon_va; };   // + 1 fd
 
+// A multicast region (the same offsets of every rank's buffer behind one address range).
+// On a GPU the reply brings the exported multicast object (+ 1 fd) to map with alignment
+// `align`; a client inside the daemon's process uses daemon_va; on the host backend with
+// emulated kernels it names the allocation bound per rank and the client builds the
+// emulated region from its own mappings of them.
+struct MapMcReq { Header h; uint64_t comm_handle; uint64_t mc_id; };
+struct MapMcReply {
+  Header h;
+  uint64_t bytes;
+  uint32_t share_kind;
+  uint32_t nranks;
+  uint64_t align;
+  uint64_t daemon_va;
+  uint64_t mems[8];
+};
+
 struct CommQueryReq { Header h; uint64_t comm_handle; };
 struct CommQueryReply {
   Header h;
@@ -200,6 +217,7 @@ union AnyMsg {
   CommQueryReq comm_query; CommQueryReply comm_query_reply;
   MapScratchReq map_scratch; MapScratchReply map_scratch_reply;
   MapMemReq map_mem; MapMemReply map_mem_reply;
+  MapMcReq map_mc; MapMcReply map_mc_reply;
   uint8_t raw[256];
 };
 
@@ -231,7 +249,10 @@ struct alignas(64) PlanMsg {
   int8_t ring[32][8];
   uint64_t ring_step_base[32];
   int32_t trace;           // 1: the kernel stamps its start and end time into the status block
-  uint8_t reserved[180];
+  int32_t variant_hint;    // CollArgs::unroll_hint (ar_hybrid: share and CTAs of the in-switch part)
+  uint64_t mc_send_id, mc_send_off;   // multicast region of the inputs (0: none) and this rank's offset in it
+  uint64_t mc_recv_id, mc_recv_off;
+  uint8_t reserved[144];
 };
 static_assert(sizeof(PlanMsg) == kPlanBytes, "a plan must fill one slot of the plan ring");
 

@@ -114,7 +114,7 @@ Config Config::from_value(const Value& root) {
     const Value& b = root["b200"];
     check_keys(b,
                {"transport", "nvls", "vmm", "sync", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
-                "host_devices", "force_host_backend", "idle_sleep_us", "idle_spin_us", "pin_threads", "init_timeout_ms", "fuse_allreduce",
+                "host_devices", "force_host_backend", "idle_sleep_us", "idle_spin_us", "pin_threads", "init_timeout_ms", "fuse_allreduce", "client_nvls",
                 "single_through_fused", "skip_start_barrier", "kernel_writes_done", "host_kernels",
                 "hybrid_nvls_permille", "hybrid_nvls_ctas", "launch"},
                "[b200]");
@@ -148,6 +148,7 @@ Config Config::from_value(const Value& root) {
     c.single_through_fused = b["single_through_fused"].as_bool(c.single_through_fused);
     c.skip_start_barrier = b["skip_start_barrier"].as_bool(c.skip_start_barrier);
     c.kernel_writes_done = b["kernel_writes_done"].as_bool(c.kernel_writes_done);
+    c.client_nvls = b["client_nvls"].as_bool(c.client_nvls);
     c.fuse_allreduce = (int)b["fuse_allreduce"].as_int(c.fuse_allreduce);
     if (c.fuse_allreduce < 1 || c.fuse_allreduce > kMaxBatch)
       throw std::runtime_error("b200.fuse_allreduce must be between 1 and " + std::to_string(kMaxBatch));

@@ -76,6 +76,7 @@ struct Config {
   bool vmm = true;
   std::string sync = "auto";        // auto | events | memops (see proto::SyncMode)
   std::string launch = "daemon";    // daemon | client (see proto::LaunchMode): who launches the kernels
+  bool client_nvls = false;         // client-side launch: also plan the in-switch variants (clients map the multicast objects)
   uint64_t wait_timeout_ms = 10000; // bound of every device-side wait
   std::string tuning_file;
   bool trace = false;

@@ -247,6 +247,7 @@ void Daemon::handle_session(Session& s) {
     case proto::kCommQuery: need = sizeof(proto::CommQueryReq); break;
     case proto::kMapScratch: need = sizeof(proto::MapScratchReq); break;
     case proto::kMapMem: need = sizeof(proto::MapMemReq); break;
+    case proto::kMapMc: need = sizeof(proto::MapMcReq); break;
     default: break;
   }
   if ((size_t)n < need) m.h.type = 0;   // falls into the protocol-error reply below
@@ -258,6 +259,7 @@ void Daemon::handle_session(Session& s) {
     case proto::kRegisterStream: on_register_stream(s, m.reg_stream); break;
     case proto::kCommQuery: on_comm_query(s, m.comm_query); break;
     case proto::kMapScratch: on_map_scratch(s, m.map_scratch); break;
+    case proto::kMapMc: on_map_mc(s, m.map_mc); break;
     case proto::kMapMem: on_map_mem(s, m.map_mem); break;
     case proto::kGoodbye: drop_session(s.id, "client said goodbye"); break;
     default: {
@@ -875,6 +877,45 @@ void Daemon::on_map_mem(Session& s, const proto::MapMemReq& m) {
   if (status == proto::kOk && fd < 0) reply(s, r, sizeof(proto::MapMemReply));
   else if (status == proto::kOk) reply(s, r, sizeof(proto::MapMemReply), &fd, 1);
   else reply(s, r, sizeof(proto::MapMemReply));
+}
+
+// Client-side launch: a multicast region named in a plan.
+void Daemon::on_map_mc(Session& s, const proto::MapMcReq& m) {
+  proto::AnyMsg r;
+  memset(&r, 0, sizeof r);
+  r.h.type = proto::kMapMcReply;
+  r.h.req_id = m.h.req_id;
+  const uint32_t id = proto::handle_comm_id(m.comm_handle);
+  const int rank = proto::handle_rank(m.comm_handle);
+  int status = proto::kErrNotFound;
+  int fd = -1;
+  if (std::find(s.comm_ranks.begin(), s.comm_ranks.end(), std::make_pair(id, rank)) != s.comm_ranks.end()) {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = comms_.find(id);
+    if (it != comms_.end() && it->second->client_launch && rank >= 0 && rank < it->second->nranks) {
+      Communicator& c = *it->second;
+      std::lock_guard<std::mutex> mg(c.mc_mu);
+      for (const auto& kv : c.mc_cache) {
+        const McRegion& reg = kv.second;
+        if (!reg.handle || reg.id != m.mc_id) continue;
+        const bool host = backend_->kind() == proto::kBackendHost;
+        const bool direct = s.same_process && !host;
+        if (!host && !direct && reg.share_fd < 0) { status = proto::kErrUnsupported; break; }
+        status = proto::kOk;
+        r.map_mc_reply.bytes = reg.size;
+        r.map_mc_reply.align = reg.gran;
+        r.map_mc_reply.nranks = (uint32_t)reg.nranks;
+        r.map_mc_reply.share_kind = host ? (uint32_t)proto::kShareHostFd : direct ? (uint32_t)proto::kShareSameProcess : (uint32_t)proto::kShareVmmFd;
+        if (direct) r.map_mc_reply.daemon_va = reg.va[rank];
+        if (host) for (int q = 0; q < reg.nranks; q++) r.map_mc_reply.mems[q] = reg.mems[q];
+        if (!host && !direct) fd = reg.share_fd;
+        break;
+      }
+    }
+  }
+  r.h.status = status;
+  if (status == proto::kOk && fd >= 0) reply(s, r, sizeof(proto::MapMcReply), &fd, 1);
+  else reply(s, r, sizeof(proto::MapMcReply));
 }
 
 void Daemon::on_comm_query(Session& s, const proto::CommQueryReq& m) {

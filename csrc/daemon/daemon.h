@@ -100,6 +100,7 @@ struct CollSlot {
   uint64_t ring_step_base[kMaxRingChannels];
   uint64_t mc_send[kMaxRanks];
   uint64_t mc_recv[kMaxRanks];
+  uint64_t mc_send_id = 0, mc_recv_id = 0;    // McRegion::id of the two (client-side launch names them in the plan)
   int8_t ring[kMaxRingChannels][kMaxRanks];   // ring order per channel, fixed at plan time
   uint64_t t_ready_us = 0;
   // Fused launches. A head slot carries `batch_len` collectives (itself and the next
@@ -301,6 +302,7 @@ class Daemon {
   void on_comm_query(Session& s, const proto::CommQueryReq& m);
   void on_map_scratch(Session& s, const proto::MapScratchReq& m);
   void on_map_mem(Session& s, const proto::MapMemReq& m);
+  void on_map_mc(Session& s, const proto::MapMcReq& m);
   int finalize_communicator(Communicator& c);
   void fail_pending_inits(Communicator& c, int status);
   void check_init_timeouts();

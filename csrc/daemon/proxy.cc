@@ -219,6 +219,7 @@ int ProxyEngine::ensure_mc(Communicator& c, CollSlot& s, bool for_recv, uint64_t
   if (!reg.handle) return proto::kErrUnsupported;
   if (off + bytes > reg.size) return proto::kErrUnsupported;
   for (int r = 0; r < c.nranks; r++) out_va[r] = reg.va[r];
+  (for_recv ? s.mc_recv_id : s.mc_send_id) = reg.id;
   return proto::kOk;
 }
 
@@ -267,7 +268,8 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   for (int a = 0; a < c.nranks && in.p2p_possible; a++)
     for (int b = 0; b < c.nranks; b++)
       if (!be->peer_access(c.devices[a], c.devices[b])) { in.p2p_possible = false; break; }
-  in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged && !c.client_launch &&
+  in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged &&
+                     (!c.client_launch || daemon_->config().client_nvls) &&
                      all_vmm && same_recv_off && (same_send_off || o0.kind == kAllGather) && c.nranks >= 2;
   {
     std::lock_guard<std::mutex> g(c.cfg_mu);
@@ -789,6 +791,13 @@ bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
   m.count = o0.count;
   m.timeout_ns = daemon_->timeout_ns();
   m.trace = daemon_->tracer().enabled() ? 1 : 0;
+  if (s.plan.variant == kArHybrid) {
+    const Config& cfg = daemon_->config();
+    const int nvls_ctas = std::min(cfg.hybrid_nvls_ctas, std::max(s.plan.dims.ctas - 1, 0));
+    m.variant_hint = (int32_t)(((uint32_t)nvls_ctas << 16) | (uint32_t)cfg.hybrid_nvls_permille);
+  }
+  if (s.plan.needs_mc_send) { m.mc_send_id = s.mc_send_id; m.mc_send_off = s.ops[rs.rank].send_off; }
+  if (s.plan.needs_mc_recv) { m.mc_recv_id = s.mc_recv_id; m.mc_recv_off = s.ops[rs.rank].recv_off; }
   for (int r = 0; r < c.nranks; r++) {
     m.rank[r].send_mem = s.ops[r].send_mem; m.rank[r].send_off = s.ops[r].send_off;
     m.rank[r].recv_mem = s.ops[r].recv_mem; m.rank[r].recv_off = s.ops[r].recv_off;

@@ -171,6 +171,7 @@ struct Mapped {
   uint32_t share_kind = 0;
   uint64_t vmm_handle = 0;
   bool registered = false;  // host memory registered with CUDA here
+  bool emulated_mc = false; // an emulated multicast region (host backend): an inaccessible range known to the emulator
 };
 
 struct StreamRec {
@@ -245,6 +246,7 @@ struct mccsComm {
   Mapped pad_map[kMaxRanks], status_map[kMaxRanks], fifo_map[kMaxRanks];
   uint64_t fifo_slot_bytes = 0;
   std::map<uint64_t, Mapped> peer_mem;                 // allocations of other ranks, mapped on first use
+  std::map<uint64_t, Mapped> mc_map;                   // multicast regions named in plans, mapped on first use
   bool launched_here = false;                          // a kernel of this communicator may still be running on a caller's stream
   CUevent launch_event = nullptr;                      // deferred waiting: recorded behind the newest kernel launched here
   bool launch_event_set = false;
@@ -572,6 +574,12 @@ mccsResult_t map_block(int fd, size_t bytes, uint32_t share_kind, uint64_t daemo
 
 void unmap_block(Mapped& m, int device) {
   if (!m.addr) return;
+  if (m.emulated_mc) {
+    emulated_mc_remove(m.addr);
+    munmap((void*)m.addr, m.bytes);
+    m = Mapped();
+    return;
+  }
   if (m.share_kind == proto::kShareVmmFd) {
     MemRec rec;
     rec.base = m.addr; rec.size = m.bytes; rec.device = device; rec.share_kind = m.share_kind; rec.vmm_handle = m.vmm_handle;
@@ -762,6 +770,89 @@ mccsResult_t resolve_mem(mccsComm* comm, uint64_t mem_id, uint64_t off, uint64_t
   return mccsSuccess;
 }
 
+// Multicast address of byte `off` of region `mc_id` for this rank's kernels; the region is
+// mapped on first use: the exported multicast object on a GPU, an emulated region over this
+// process's own mappings of the ranks' buffers on the host backend.
+mccsResult_t resolve_mc(mccsComm* comm, uint64_t mc_id, uint64_t off, uint64_t* out) {
+  auto it = comm->mc_map.find(mc_id);
+  if (it == comm->mc_map.end()) {
+    proto::AnyMsg m;
+    memset(&m, 0, sizeof m);
+    m.h.type = proto::kMapMc;
+    m.map_mc.comm_handle = comm->handle;
+    m.map_mc.mc_id = mc_id;
+    std::vector<int> fds;
+    {
+      std::unique_lock<std::mutex> g(g_ctx.mu);
+      mccsResult_t r = roundtrip(g, m, sizeof(proto::MapMcReq), proto::kMapMcReply, &fds, 30000);
+      if (r != mccsSuccess) return r;
+    }
+    const proto::MapMcReply& rep = m.map_mc_reply;
+    Mapped mp;
+    mp.bytes = (size_t)rep.bytes;
+    mp.share_kind = rep.share_kind;
+    mccsResult_t r = mccsSuccess;
+    if (rep.share_kind == proto::kShareSameProcess) {
+      mp.addr = rep.daemon_va;
+      if (!mp.addr) r = mccsProtocolError;
+    } else if (rep.share_kind == proto::kShareVmmFd && !fds.empty()) {
+      CtxScope scope(comm->device);
+      CUmemGenericAllocationHandle h = 0;
+      CUdeviceptr va = 0;
+      CUresult cr = scope.ok ? g_drv.cuMemImportFromShareableHandle_(&h, (void*)(uintptr_t)fds[0], CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR)
+                             : CUDA_ERROR_INVALID_CONTEXT;
+      if (cr == CUDA_SUCCESS) {
+        cr = g_drv.cuMemAddressReserve_(&va, mp.bytes, (size_t)rep.align, 0, 0);
+        if (cr == CUDA_SUCCESS) {
+          cr = g_drv.cuMemMap_(va, mp.bytes, 0, h, 0);
+          if (cr == CUDA_SUCCESS) {
+            CUmemAccessDesc desc;
+            memset(&desc, 0, sizeof desc);
+            desc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+            desc.location.id = comm->device;
+            desc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+            cr = g_drv.cuMemSetAccess_(va, mp.bytes, &desc, 1);
+            if (cr != CUDA_SUCCESS) g_drv.cuMemUnmap_(va, mp.bytes);
+          }
+          if (cr != CUDA_SUCCESS) g_drv.cuMemAddressFree_(va, mp.bytes);
+        }
+        if (cr != CUDA_SUCCESS) g_drv.cuMemRelease_(h);
+      }
+      if (cr != CUDA_SUCCESS) {
+        LOG_ERROR("mapping multicast region %llu: %s", (unsigned long long)mc_id, cu_err(cr));
+        r = mccsDeviceError;
+      } else {
+        mp.addr = (uint64_t)va;
+        mp.vmm_handle = (uint64_t)h;
+      }
+    } else if (rep.share_kind == proto::kShareHostFd && g_ctx.backend == proto::kBackendHost) {
+      std::vector<void*> backing;
+      for (uint32_t q = 0; q < rep.nranks && q < 8 && r == mccsSuccess; q++) {
+        uint64_t p = 0;
+        r = resolve_mem(comm, rep.mems[q], 0, &p);
+        backing.push_back((void*)p);
+      }
+      if (r == mccsSuccess) {
+        void* base = mmap(nullptr, mp.bytes, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0);
+        if (base == MAP_FAILED) r = mccsOutOfMemory;
+        else {
+          emulated_mc_add((uint64_t)base, mp.bytes, backing);
+          mp.addr = (uint64_t)base;
+          mp.emulated_mc = true;
+        }
+      }
+    } else {
+      r = mccsUnsupported;
+    }
+    for (int f : fds) close(f);
+    if (r != mccsSuccess) return r;
+    it = comm->mc_map.emplace(mc_id, mp).first;
+  }
+  if (off > it->second.bytes) return mccsInvalidArgument;
+  *out = it->second.addr + off;
+  return mccsSuccess;
+}
+
 // Client-side launch: post the request, wait for the plan the daemon makes for all ranks
 // (variant, launch shape, barrier epoch, ticket, ring order, everybody's buffers), and
 // launch this rank's kernel here. The daemon never touches a stream for this collective.
@@ -813,6 +904,7 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
   a.epoch = plan.epoch;
   a.timeout_ns = plan.timeout_ns;
   a.trace = plan.trace;
+  a.unroll_hint = plan.variant_hint;
   for (int r = 0; r < comm->nranks; r++) {
     uint64_t s = 0, d = 0;
     mccsResult_t rr = resolve_mem(comm, plan.rank[r].send_mem, plan.rank[r].send_off, &s);
@@ -823,6 +915,18 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
     a.pad[r] = (SignalPad*)comm->pad_map[r].addr;
     a.status[r] = (StatusBlock*)comm->status_map[r].addr;
     a.fifo[r] = (char*)comm->fifo_map[r].addr;
+  }
+  if (plan.mc_send_id) {
+    uint64_t p = 0;
+    mccsResult_t rr = resolve_mc(comm, plan.mc_send_id, plan.mc_send_off, &p);
+    if (rr != mccsSuccess) return rr;
+    a.mc_send = (const void*)p;
+  }
+  if (plan.mc_recv_id) {
+    uint64_t p = 0;
+    mccsResult_t rr = resolve_mc(comm, plan.mc_recv_id, plan.mc_recv_off, &p);
+    if (rr != mccsSuccess) return rr;
+    a.mc_recv = (void*)p;
   }
   a.fifo_slot_bytes = comm->fifo_slot_bytes;
   memcpy(a.ring, plan.ring, sizeof a.ring);
@@ -1053,6 +1157,15 @@ mccsResult_t mccsFree(void* ptr) {
     if (g_ctx.connected)
       for (mccsComm* c : mine)
         if (c->outstanding || c->memop_posted) mccsCommFlush(c);
+    // Kernels launched from here (client-side launch) run on the caller's streams: the
+    // daemon cannot wait for them, so this call does, before the memory and the multicast
+    // bindings that name it go away.
+    if (g_ctx.backend == proto::kBackendCuda && g_drv.cuCtxSynchronize_)
+      for (mccsComm* c : mine)
+        if (c->launched_here) {
+          CtxScope scope(c->device);
+          if (scope.ok) g_drv.cuCtxSynchronize_();
+        }
   }
   std::unique_lock<std::mutex> g(g_ctx.mu);
   auto it = g_ctx.mem.find((uint64_t)ptr);
@@ -1278,6 +1391,7 @@ mccsResult_t mccsCommDestroy(mccsComm_t comm) {
     unmap_block(comm->status_map[r], map_dev);
     unmap_block(comm->fifo_map[r], map_dev);
   }
+  for (auto& kv : comm->mc_map) unmap_block(kv.second, map_dev);
   for (auto& kv : comm->peer_mem) unmap_block(kv.second, map_dev);
   if (comm->sync_host) {
     if (!comm->sync_emulated) {

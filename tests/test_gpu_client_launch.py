@@ -19,9 +19,10 @@ import torch
 
 from helpers import REPO, write_config
 
+OPT_IN = os.environ.get("MCCS_TEST_CLIENT_LAUNCH", "")
 pytestmark = [
     pytest.mark.gpu,
-    pytest.mark.skipif(os.environ.get("MCCS_TEST_CLIENT_LAUNCH") != "1", reason="opt-in: MCCS_TEST_CLIENT_LAUNCH=1"),
+    pytest.mark.skipif(OPT_IN not in ("1", "nvls"), reason="opt-in: MCCS_TEST_CLIENT_LAUNCH=1 (or =nvls, after =1 has passed)"),
 ]
 
 CLIENT = r"""
@@ -72,6 +73,14 @@ for algo in ar:
 for algo in ag:
     for nbytes in (16, 1000, 40000, 1 << 20):
         allgather(algo, nbytes)
+if os.environ.get("NVLS") == "1" and n > 1:
+    # the in-switch variants: each client maps the multicast objects the daemon bound
+    for algo in ("ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid"):
+        for dname, count in (("f32", 4), ("f32", 4100), ("bf16", 3000), ("f16", 2048), ("bf16", 1 << 20)):
+            allreduce(algo, dname, count)
+        allreduce(algo, "f32", 8192, in_place=True)
+    for nbytes in (16, 4096, 1 << 20):
+        allgather("ag_nvls", nbytes)
 # back to back on the stream without looking at the results in between
 t = send.tensor(torch.float32, 1 << 16)
 t.fill_(1.0)
@@ -88,16 +97,21 @@ print("RESULT", json.dumps({"bad": bad, "seen": sorted(seen), "async_error": q["
 """
 
 
-def test_client_side_launch_on_gpus(tmp_path):
+@pytest.mark.parametrize("nvls", [False, True])
+def test_client_side_launch_on_gpus(tmp_path, nvls):
     from mccs_b200 import daemon
+    if nvls and OPT_IN != "nvls":
+        pytest.skip("second step: MCCS_TEST_CLIENT_LAUNCH=nvls")
     n = min(torch.cuda.device_count(), 4)
+    if nvls and n < 2:
+        pytest.skip("multicast needs two GPUs")
     d = str(tmp_path)
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, wait_timeout_ms=2000,
-                       extra='launch = "client"')
+                       extra='launch = "client"' + ("\nclient_nvls = true" if nvls else ""))
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn", "NCCL_NVLS_ENABLE": "0"})
     try:
         env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), MCCS_LOG="error",
-                   ADMIN_PORT=str(sp.admin_port), MCCS_WC_TIMEOUT_MS="60000")
+                   ADMIN_PORT=str(sp.admin_port), MCCS_WC_TIMEOUT_MS="60000", NVLS="1" if nvls else "0")
         procs = [subprocess.Popen([sys.executable, "-c", CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
                                   stderr=subprocess.PIPE, text=True) for r in range(n)]
         for p in procs:
@@ -106,6 +120,8 @@ def test_client_side_launch_on_gpus(tmp_path):
             res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
             assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
             assert res["client_launch"] is True
+            if nvls:
+                assert {"ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid", "ag_nvls"} <= set(res["seen"])
             if n > 1:
                 assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
             else:

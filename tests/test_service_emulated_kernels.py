@@ -224,3 +224,13 @@ def test_client_side_launch(tmp_path, n):
         assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
         assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
         assert res["epoch"] == 1 and res["client_launch"] is True and res["completed"] > 50
+
+
+def test_client_side_launch_of_the_in_switch_variants(tmp_path):
+    """`client_nvls = true`: plans name multicast regions; each client maps them (here: builds
+    the emulated region over its own mappings of the ranks' buffers) and launches the NVLS,
+    hybrid and multicast all-gather kernels itself."""
+    for res in _run(tmp_path, 4, 'launch = "client"\nclient_nvls = true', client_env={"NVLS": "1"}):
+        assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
+        assert {"ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid", "ag_nvls"} <= set(res["seen"])
+        assert res["client_launch"] is True
