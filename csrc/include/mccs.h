@@ -16,6 +16,12 @@
  *   - interprocess events (the reference's scheme): the library records "submitted",
  *     waits for the daemon's completion message, then makes the stream wait for the
  *     daemon's "done" event; the call blocks for one round trip and reports errors.
+ * A third arrangement, [b200] launch = "client", keeps planning, admission and
+ * reconfiguration in the daemon but has this library launch the planned kernel on the
+ * caller's stream itself (it maps the peers' buffers for that); a call then blocks until
+ * every rank has made the same call and the plan is back, like a rendezvous.
+ * In every arrangement each call involves the daemon, so collectives cannot be recorded
+ * into a CUDA graph and replayed; keep them outside stream capture.
  *
  * This is the C form of the reference's Rust API (src/libmccs/src/lib.rs:23-27):
  *   cuda_malloc            -> mccsMalloc          (src/libmccs/src/memory.rs:12)
