@@ -1279,14 +1279,14 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
   if (c->client_launch) {
     // Everything this rank's kernels address besides the buffers: every rank's signal pad
     // and status block, and (for the ring variants) every rank's FIFOs.
-    for (int r = 0; r < nranks; r++) {
+    for (int peer = 0; peer < nranks; peer++) {
       for (uint32_t kind : {(uint32_t)proto::kScratchPad, (uint32_t)proto::kScratchStatus, (uint32_t)proto::kScratchFifo}) {
         if (kind == proto::kScratchFifo && nranks == 1) continue;
         proto::AnyMsg q;
         memset(&q, 0, sizeof q);
         q.h.type = proto::kMapScratch;
         q.map_scratch.comm_handle = c->handle;
-        q.map_scratch.rank = r;
+        q.map_scratch.rank = peer;
         q.map_scratch.kind = kind;
         std::vector<int> sfds;
         mccsResult_t mr = roundtrip(g, q, sizeof(proto::MapScratchReq), proto::kMapScratchReply, &sfds, 30000);
@@ -1296,7 +1296,7 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
                          q.map_scratch_reply.daemon_va, g_ctx.backend == proto::kBackendCuda ? device : -1, &mp);
         for (int f : sfds) close(f);
         if (mr != mccsSuccess) {
-          LOG_ERROR("cannot map rank %d's %s of communicator %u", r, kind == proto::kScratchPad ? "signal pad" : kind == proto::kScratchStatus ? "status block" : "FIFOs", c->id);
+          LOG_ERROR("cannot map rank %d's %s of communicator %u", peer, kind == proto::kScratchPad ? "signal pad" : kind == proto::kScratchStatus ? "status block" : "FIFOs", c->id);
           g_ctx.comms.push_back(c);      // mccsCommDestroy below undoes what exists so far
           g.unlock();
           mccsCommDestroy(c);
@@ -1304,9 +1304,9 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
         }
         // inside the daemon's process the status block is the daemon's own (registered) host memory
         if (kind == proto::kScratchStatus && mp.share_kind == proto::kShareSameProcess) mp.host = (void*)mp.addr;
-        if (kind == proto::kScratchPad) c->pad_map[r] = mp;
-        else if (kind == proto::kScratchStatus) c->status_map[r] = mp;
-        else c->fifo_map[r] = mp;
+        if (kind == proto::kScratchPad) c->pad_map[peer] = mp;
+        else if (kind == proto::kScratchStatus) c->status_map[peer] = mp;
+        else c->fifo_map[peer] = mp;
       }
     }
     // The status block of this rank is read by the CPU here (device errors, the abort word).
@@ -1386,10 +1386,10 @@ mccsResult_t mccsCommDestroy(mccsComm_t comm) {
     if (g_ctx.comms[i] == comm) { g_ctx.comms.erase(g_ctx.comms.begin() + (long)i); break; }
   if (comm->dp_mem) munmap(comm->dp_mem, comm->dp_bytes);
   const int map_dev = g_ctx.backend == proto::kBackendCuda ? comm->device : -1;
-  for (int r = 0; r < kMaxRanks; r++) {
-    unmap_block(comm->pad_map[r], map_dev);
-    unmap_block(comm->status_map[r], map_dev);
-    unmap_block(comm->fifo_map[r], map_dev);
+  for (int k = 0; k < kMaxRanks; k++) {
+    unmap_block(comm->pad_map[k], map_dev);
+    unmap_block(comm->status_map[k], map_dev);
+    unmap_block(comm->fifo_map[k], map_dev);
   }
   for (auto& kv : comm->mc_map) unmap_block(kv.second, map_dev);
   for (auto& kv : comm->peer_mem) unmap_block(kv.second, map_dev);
