@@ -133,6 +133,7 @@ asan: build/san/stress_asan build/san/fuzz_value build/san/fuzz_protocol
 	ASAN_OPTIONS="detect_leaks=1" build/san/stress_asan 40 memops
 	build/san/fuzz_value 40000
 	ASAN_OPTIONS="detect_leaks=1" build/san/fuzz_protocol 3000
+	ASAN_OPTIONS="detect_leaks=1" build/san/fuzz_protocol 2000 client
 
 # ---------------------------------------------------------------------------------------
 # Evaluation recipes, one per figure of the reference's justfile (its `four_gpu_*`,

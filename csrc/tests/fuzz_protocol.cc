@@ -6,6 +6,7 @@
 //
 // The reference trusts its clients: most of its error paths are unwrap()/panic!
 // (src/mccs/src/daemon/engine.rs:86-99,263).
+#include <signal.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -21,12 +22,25 @@
 #include "../include/mccs.h"
 #include "../ipc/shm_ring.h"
 #include "../ipc/uds.h"
+#include "../kernels/dev_types.h"
 
 using namespace mccs;
 
 namespace {
 
 std::mt19937_64 rng(987654321);
+
+// Where the run is, for the watchdog: a daemon that stops answering must end the run with
+// its place, not hang it.
+volatile int g_stage = 0;
+volatile long g_step = 0, g_posted = 0, g_answered = 0;
+void on_alarm(int) {
+  char buf[160];
+  int n = snprintf(buf, sizeof buf, "fuzz_protocol: stuck in stage %d at step %ld (posted %ld, answered %ld)\n", g_stage, g_step,
+                   g_posted, g_answered);
+  if (write(2, buf, (size_t)n) < 0) {}
+  _exit(3);
+}
 
 int connect_and_hello(const std::string& path) {
   int fd = ipc::uds_connect(path);
@@ -75,18 +89,27 @@ uint64_t wild_u64() {
 
 int main(int argc, char** argv) {
   const int rounds = argc > 1 ? atoi(argv[1]) : 3000;
+  // "client": the daemon hands plans back instead of launching ([b200] launch = "client");
+  // the hostile tenant then also asks for mappings of scratch memory, foreign allocations
+  // and multicast regions, and reads plans instead of completions.
+  const bool client_mode = argc > 2 && std::string(argv[2]) == "client";
   const std::string prefix = "/tmp/mccs-fuzz-" + std::to_string((long)getpid());
   const std::string cfg = "listen_port = 0\nmccs_daemon_prefix = \"" + prefix + "\"\n[control]\nprefix = \"" + prefix +
                           "\"\npath = \"control.sock\"\n[comm_default_config]\nbuffer_sizes = [65536]\nchannel_count = 2\n"
-                          "[b200]\nforce_host_backend = true\nhost_devices = 2\nwait_timeout_ms = 2000\ninit_timeout_ms = 300\n";
+                          "[b200]\nforce_host_backend = true\nhost_devices = 2\nwait_timeout_ms = 2000\ninit_timeout_ms = 300\n" +
+                          std::string(client_mode ? "launch = \"client\"\nclient_nvls = true\n" : "");
   setenv("MCCS_LOG", "error", 0);
+  signal(SIGALRM, on_alarm);
+  alarm(getenv("FUZZ_ALARM") ? (unsigned)atoi(getenv("FUZZ_ALARM")) : 600u);
   if (mccsd_start(cfg.c_str()) != 0) { fprintf(stderr, "daemon did not start\n"); return 2; }
   const std::string path = mccsd_control_path();
 
   // 1. control messages: every type, random length, random fields
   int fd = connect_and_hello(path);
   if (fd < 0) { fprintf(stderr, "cannot connect\n"); return 2; }
+  g_stage = 1;
   for (int i = 0; i < rounds; i++) {
+    g_step = i;
     proto::AnyMsg m;
     for (size_t k = 0; k < sizeof m.raw; k++) m.raw[k] = (uint8_t)rng();
     m.h.magic = (rng() % 50 == 0) ? (uint32_t)rng() : proto::kMagic;
@@ -101,6 +124,19 @@ int main(int argc, char** argv) {
         m.comm_init.device = (int32_t)(rng() % 5) - 1;
         break;
       case proto::kCommDestroy: m.comm_destroy.comm_handle = ((uint64_t)(9000 + rng() % 4) << 32) + rng() % 3; break;
+      case proto::kMapScratch:
+        m.map_scratch.comm_handle = (rng() % 2) ? wild_u64() : ((uint64_t)(9000 + rng() % 4) << 32) + rng() % 3;
+        m.map_scratch.rank = (int32_t)(rng() % 12) - 2;
+        m.map_scratch.kind = (uint32_t)(rng() % 5);
+        break;
+      case proto::kMapMem:
+        m.map_mem.comm_handle = (rng() % 2) ? wild_u64() : ((uint64_t)(9000 + rng() % 4) << 32) + rng() % 3;
+        m.map_mem.mem_id = rng() % 40;
+        break;
+      case proto::kMapMc:
+        m.map_mc.comm_handle = (rng() % 2) ? wild_u64() : ((uint64_t)(9000 + rng() % 4) << 32) + rng() % 3;
+        m.map_mc.mc_id = rng() % 6;
+        break;
       case proto::kCommQuery: m.comm_query.comm_handle = (rng() % 2) ? wild_u64() : ((uint64_t)(9000 + rng() % 4) << 32) + rng() % 3; break;
       default: break;
     }
@@ -148,11 +184,48 @@ int main(int argc, char** argv) {
   void* dp = mmap(nullptr, dp_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
   for (int f : fds) close(f);
   if (dp == MAP_FAILED) { fprintf(stderr, "cannot map the data-path segment\n"); return 1; }
-  ipc::Ring wq, cq;
+  ipc::Ring wq, cq, pq;
   wq.attach(dp);
   cq.attach((char*)dp + proto::dp_wq_bytes());
+  pq.attach((char*)dp + proto::dp_pq_offset());
+  if (client_mode && rep.comm_init_reply.launch_mode != proto::kLaunchClient) { fprintf(stderr, "the communicator is not in client-launch mode\n"); return 1; }
+  // A client that launches its own kernels also owns their completion: the kernel's last
+  // store is its ticket into the rank's status block, which is what lets the daemon hand out
+  // further plans. The fuzzer runs no kernel, so it writes the ticket itself.
+  StatusBlock* my_status = nullptr;
+  if (client_mode) {
+    memset(&m, 0, sizeof m);
+    m.h.magic = proto::kMagic;
+    m.h.type = proto::kMapScratch;
+    m.map_scratch.comm_handle = rep.comm_init_reply.comm_handle;
+    m.map_scratch.rank = 0;
+    m.map_scratch.kind = proto::kScratchStatus;
+    ipc::uds_send(fd, &m, sizeof(proto::MapScratchReq));
+    proto::AnyMsg sr;
+    memset(&sr, 0, sizeof sr);
+    std::vector<int> sfds;
+    ipc::wait_readable(fd, 2000);
+    ipc::uds_recv(fd, &sr, sizeof sr, &sfds);
+    if (sr.h.status == 0 && !sfds.empty())
+      my_status = (StatusBlock*)mmap(nullptr, sr.map_scratch_reply.bytes, PROT_READ | PROT_WRITE, MAP_SHARED, sfds[0], 0);
+    for (int f : sfds) close(f);
+    if (!my_status || my_status == MAP_FAILED) { fprintf(stderr, "cannot map the status block\n"); return 1; }
+  }
   long posted = 0, answered = 0;
+  // every request is answered exactly once: by a completion, or (client-side launch) by a
+  // plan or the reason there is none
+  auto reap = [&]() {
+    proto::WorkCompletion wc;
+    while (cq.try_pop(&wc)) answered++;
+    proto::PlanMsg plan;
+    while (client_mode && pq.try_pop(&plan)) {
+      answered++;
+      if (plan.status == 0) __atomic_store_n(&my_status->done_seq, plan.ticket, __ATOMIC_RELEASE);
+    }
+  };
+  g_stage = 2;
   for (int i = 0; i < rounds; i++) {
+    g_step = i; g_posted = posted; g_answered = answered;
     proto::WorkRequest wr;
     uint8_t* raw = (uint8_t*)&wr;
     for (size_t k = 0; k < sizeof wr; k++) raw[k] = (uint8_t)rng();
@@ -170,17 +243,16 @@ int main(int argc, char** argv) {
     wr.stream_id = rng() % 3;
     wr.user_seq = (uint64_t)i;
     while (!wq.try_push(&wr)) {
-      proto::WorkCompletion wc;
-      while (cq.try_pop(&wc)) answered++;
+      reap();
       usleep(50);
     }
     posted++;
-    proto::WorkCompletion wc;
-    while (cq.try_pop(&wc)) answered++;
+    reap();
+    // the library keeps one request in flight in this mode (the plan ring is that deep)
+    for (int spin = 0; client_mode && spin < 20000 && answered < posted; spin++) { usleep(50); reap(); }
   }
   for (int spin = 0; spin < 20000 && answered < posted; spin++) {
-    proto::WorkCompletion wc;
-    while (cq.try_pop(&wc)) answered++;
+    reap();
     usleep(100);
   }
   const bool all_answered = answered == posted;
@@ -188,7 +260,9 @@ int main(int argc, char** argv) {
   // both indices) while the proxy keeps polling them. Whatever it makes of the contents,
   // it must stay inside the segment.
   for (int i = 0; i < 200; i++) {
-    ipc::RingHeader* h = (ipc::RingHeader*)((rng() % 2) ? dp : (void*)((char*)dp + proto::dp_wq_bytes()));
+    const int which = (int)(rng() % (client_mode ? 3 : 2));
+    ipc::RingHeader* h = (ipc::RingHeader*)(which == 0 ? dp : which == 1 ? (void*)((char*)dp + proto::dp_wq_bytes())
+                                                                        : (void*)((char*)dp + proto::dp_pq_offset()));
     h->depth = (uint32_t)wild_u64();
     h->slot_bytes = (uint32_t)wild_u64();
     h->tail.store(wild_u64());
@@ -199,6 +273,7 @@ int main(int argc, char** argv) {
   close(fd);   // no goodbye: the daemon cleans up after us
   if (!all_answered) { fprintf(stderr, "only %ld of %ld requests were answered\n", answered, posted); return 1; }
 
+  g_stage = 3;
   // 3. a well-behaved tenant still gets service
   setenv("MCCS_CONTROL", path.c_str(), 1);
   int bad = 0;
@@ -209,7 +284,10 @@ int main(int argc, char** argv) {
   bad += mccsCommInitRank(&comm, 9200, 0, 1, 0, nullptr) != mccsSuccess;
   if (buf && comm) {
     for (int i = 0; i < 1024; i++) buf[i] = (float)i;
-    bad += mccsAllReduce(comm, buf, buf, 1024, mccsFloat32, mccsSum, nullptr) != mccsSuccess;
+    // Sanitizer builds carry no emulated kernels, so in client-launch mode the library
+    // gets its plan and then has nothing to run it with: "unsupported", and nothing worse.
+    const mccsResult_t ar = mccsAllReduce(comm, buf, buf, 1024, mccsFloat32, mccsSum, nullptr);
+    bad += client_mode ? (ar != mccsUnsupported) : (ar != mccsSuccess);
     bad += buf[1023] != 1023.0f;
     bad += mccsCommDestroy(comm) != mccsSuccess;
     bad += mccsFree(buf) != mccsSuccess;
