@@ -281,7 +281,7 @@ def main() -> int:
             "config": {
                 "model": f"{args.coll} sum, {nbytes / 2**20:g} MiB per rank, out of place, through libmccs + daemon",
                 "global_batch": nbytes * n, "seq_len": 1, "parallelism": f"dp{n}",
-                "variant": variant, "ctas": ctas, "backend": backend,
+                "variant": variant, "ctas": ctas, "backend": backend, "launch": comm.launch_mode,
                 "l2": "inputs larger than L2 (no flush)", "timing": "CUDA events, max over ranks",
                 "verified": ok,
             },

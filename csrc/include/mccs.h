@@ -163,6 +163,9 @@ mccsResult_t mccsCommGetAsyncError(mccsComm_t comm, mccsResult_t* async_error);
 mccsResult_t mccsCommFlush(mccsComm_t comm);
 /* Variant and CTA count reported with the last completed request of this rank. */
 mccsResult_t mccsCommLastPlan(mccsComm_t comm, uint32_t* variant, uint32_t* ctas);
+/* Who launches this communicator's kernels: 0 = the daemon, 1 = this library on the
+ * caller's stream ([b200] launch = "client" in the daemon's configuration). */
+int mccsCommLaunchMode(mccsComm_t comm);
 
 const char* mccsGetErrorString(mccsResult_t r);
 const char* mccsAlgoName(int algo);

@@ -1566,6 +1566,8 @@ mccsResult_t mccsCommLastPlan(mccsComm_t comm, uint32_t* variant, uint32_t* ctas
   return mccsSuccess;
 }
 
+int mccsCommLaunchMode(mccsComm_t comm) { return comm && comm->client_launch ? 1 : 0; }
+
 const char* mccsGetErrorString(mccsResult_t r) {
   switch (r) {
     case mccsSuccess: return "success";

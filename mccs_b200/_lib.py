@@ -81,6 +81,8 @@ def shim() -> ctypes.CDLL:
     lib.mccsCommFlush.restype = c_int
     lib.mccsCommLastPlan.argtypes = [c_void_p, POINTER(c_uint32), POINTER(c_uint32)]
     lib.mccsCommLastPlan.restype = c_int
+    lib.mccsCommLaunchMode.argtypes = [c_void_p]
+    lib.mccsCommLaunchMode.restype = c_int
     lib.mccsGetErrorString.argtypes = [c_int]
     lib.mccsGetErrorString.restype = c_char_p
     lib.mccsAlgoName.argtypes = [c_int]

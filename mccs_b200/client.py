@@ -201,6 +201,12 @@ class Communicator:
         _lib.shim().mccsCommLastPlan(self._h, byref(v), byref(c))
         return ALGO_NAMES.get(v.value, str(v.value)), int(c.value)
 
+    @property
+    def launch_mode(self) -> str:
+        """'daemon' (the service launches the kernels) or 'client' (this process does, on the
+        caller's stream, from the plan the service made)."""
+        return "client" if _lib.shim().mccsCommLaunchMode(self._h) == 1 else "daemon"
+
     def destroy(self) -> None:
         if self._h is not None and self._h.value:
             _lib.shim().mccsCommDestroy(self._h)

@@ -160,7 +160,7 @@ def main() -> int:
         rep = M.admin_request(admin_port, {"cmd": "trace", "enabled": False, "inline": True})
         stages = summarise(rep["trace"]["traceEvents"], comm_id, args.warmup)
         out = {"coll": args.coll, "bytes": nbytes, "n": n, "variant": variant, "ctas": ctas,
-               "backend": M.backend(), "period_us": period_us, "stages": stages}
+               "backend": M.backend(), "launch": comm.launch_mode, "period_us": period_us, "stages": stages}
         if args.json:
             print(json.dumps(out))
         else:
