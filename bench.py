@@ -227,6 +227,7 @@ def main() -> int:
 
     ms = timed(step)
     variant, ctas = comm.last_plan()
+    launch_mode = comm.launch_mode
 
     # End to end: input arrives from pinned host memory and the result is read back, every step.
     d2h_elems = min(count, 32768)
@@ -281,7 +282,7 @@ def main() -> int:
             "config": {
                 "model": f"{args.coll} sum, {nbytes / 2**20:g} MiB per rank, out of place, through libmccs + daemon",
                 "global_batch": nbytes * n, "seq_len": 1, "parallelism": f"dp{n}",
-                "variant": variant, "ctas": ctas, "backend": backend, "launch": comm.launch_mode,
+                "variant": variant, "ctas": ctas, "backend": backend, "launch": launch_mode,
                 "l2": "inputs larger than L2 (no flush)", "timing": "CUDA events, max over ranks",
                 "verified": ok,
             },
