@@ -118,6 +118,23 @@ def test_multi_tenant_tool_on_host_backend(sync):
     assert all(t["admitted"] == 35 * 4 for t in out["qos_stats"].values())
 
 
+def test_multi_tenant_tool_with_client_side_launch():
+    """The same four applications with `[b200] launch = "client"`: every rank's library runs
+    its own kernels (on the emulator) while weights, admission and the live reconfiguration
+    stay with the daemon."""
+    import json
+    env = dict(os.environ, PYTHONPATH=REPO, MCCS_LOG="error", MCCS_B200_EXTRA='launch = "client"')
+    res = subprocess.run([sys.executable, "-m", "mccs_b200.utils.multi_tenant", "--iters", "20", "--reconfig-at", "10",
+                          "--bytes", "65536", "--batch", "4", "--host-devices", "4", "--timeout", "300", "--sync", "events"],
+                         capture_output=True, text=True, cwd=REPO, env=env, timeout=500)
+    assert res.returncode == 0, res.stderr[-3000:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    for name, app in out["apps"].items():
+        assert app["finite"] and app["async_error"] == 0, (name, app)
+    assert out["apps"]["C"]["config_epoch"] == 1 and out["apps"]["A"]["config_epoch"] == 0
+    assert all(t["admitted"] == 25 * 4 and t["outstanding_bytes"] == 0 for t in out["qos_stats"].values())
+
+
 def test_bench_script_contract_on_cpu():
     """bench.py runs end to end without a GPU (host backend, reduced size) and prints the
     one JSON line with every key of the benchmark contract; the reference arm prints
