@@ -197,6 +197,7 @@ struct Context {
   uint32_t sync_mode = 0;
   uint32_t next_req = 1;
   std::map<uint64_t, MemRec> mem;                       // base -> record
+  std::map<uint64_t, uint64_t> mem_base_by_id;          // allocation id -> base (plans name allocations by id)
   std::map<std::pair<int, uint64_t>, StreamRec> streams;   // (device, stream) -> record
   uint64_t wc_timeout_ms = 300000;
   // reply demultiplexing (see roundtrip)
@@ -744,10 +745,9 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
 
 // Address, in this process, of byte `off` of allocation `mem_id`: one of the caller's own
 // allocations, or a peer's, mapped on first use (client-side launch only).
-mccsResult_t resolve_mem(mccsComm* comm, uint64_t mem_id, uint64_t off, uint64_t* out) {
-  std::unique_lock<std::mutex> g(g_ctx.mu);
-  for (const auto& kv : g_ctx.mem)
-    if (kv.second.mem_id == mem_id) { *out = kv.second.base + off; return mccsSuccess; }
+mccsResult_t resolve_mem(std::unique_lock<std::mutex>& g, mccsComm* comm, uint64_t mem_id, uint64_t off, uint64_t* out) {
+  auto own = g_ctx.mem_base_by_id.find(mem_id);
+  if (own != g_ctx.mem_base_by_id.end()) { *out = own->second + off; return mccsSuccess; }
   auto it = comm->peer_mem.find(mem_id);
   if (it == comm->peer_mem.end()) {
     proto::AnyMsg m;
@@ -773,7 +773,7 @@ mccsResult_t resolve_mem(mccsComm* comm, uint64_t mem_id, uint64_t off, uint64_t
 // Multicast address of byte `off` of region `mc_id` for this rank's kernels; the region is
 // mapped on first use: the exported multicast object on a GPU, an emulated region over this
 // process's own mappings of the ranks' buffers on the host backend.
-mccsResult_t resolve_mc(mccsComm* comm, uint64_t mc_id, uint64_t off, uint64_t* out) {
+mccsResult_t resolve_mc(std::unique_lock<std::mutex>& g, mccsComm* comm, uint64_t mc_id, uint64_t off, uint64_t* out) {
   auto it = comm->mc_map.find(mc_id);
   if (it == comm->mc_map.end()) {
     proto::AnyMsg m;
@@ -782,11 +782,8 @@ mccsResult_t resolve_mc(mccsComm* comm, uint64_t mc_id, uint64_t off, uint64_t* 
     m.map_mc.comm_handle = comm->handle;
     m.map_mc.mc_id = mc_id;
     std::vector<int> fds;
-    {
-      std::unique_lock<std::mutex> g(g_ctx.mu);
-      mccsResult_t r = roundtrip(g, m, sizeof(proto::MapMcReq), proto::kMapMcReply, &fds, 30000);
-      if (r != mccsSuccess) return r;
-    }
+    mccsResult_t rt = roundtrip(g, m, sizeof(proto::MapMcReq), proto::kMapMcReply, &fds, 30000);
+    if (rt != mccsSuccess) return rt;
     const proto::MapMcReply& rep = m.map_mc_reply;
     Mapped mp;
     mp.bytes = (size_t)rep.bytes;
@@ -829,7 +826,7 @@ mccsResult_t resolve_mc(mccsComm* comm, uint64_t mc_id, uint64_t off, uint64_t* 
       std::vector<void*> backing;
       for (uint32_t q = 0; q < rep.nranks && q < 8 && r == mccsSuccess; q++) {
         uint64_t p = 0;
-        r = resolve_mem(comm, rep.mems[q], 0, &p);
+        r = resolve_mem(g, comm, rep.mems[q], 0, &p);
         backing.push_back((void*)p);
       }
       if (r == mccsSuccess) {
@@ -905,10 +902,13 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
   a.timeout_ns = plan.timeout_ns;
   a.trace = plan.trace;
   a.unroll_hint = plan.variant_hint;
+  // One pass under the library's lock: the caller's own allocations by id, peers' buffers
+  // and multicast regions from this communicator's maps (filled on first use).
+  std::unique_lock<std::mutex> g(g_ctx.mu);
   for (int r = 0; r < comm->nranks; r++) {
     uint64_t s = 0, d = 0;
-    mccsResult_t rr = resolve_mem(comm, plan.rank[r].send_mem, plan.rank[r].send_off, &s);
-    if (rr == mccsSuccess) rr = resolve_mem(comm, plan.rank[r].recv_mem, plan.rank[r].recv_off, &d);
+    mccsResult_t rr = resolve_mem(g, comm, plan.rank[r].send_mem, plan.rank[r].send_off, &s);
+    if (rr == mccsSuccess) rr = resolve_mem(g, comm, plan.rank[r].recv_mem, plan.rank[r].recv_off, &d);
     if (rr != mccsSuccess) return rr;
     a.send[r] = (const void*)s;
     a.recv[r] = (void*)d;
@@ -918,16 +918,17 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
   }
   if (plan.mc_send_id) {
     uint64_t p = 0;
-    mccsResult_t rr = resolve_mc(comm, plan.mc_send_id, plan.mc_send_off, &p);
+    mccsResult_t rr = resolve_mc(g, comm, plan.mc_send_id, plan.mc_send_off, &p);
     if (rr != mccsSuccess) return rr;
     a.mc_send = (const void*)p;
   }
   if (plan.mc_recv_id) {
     uint64_t p = 0;
-    mccsResult_t rr = resolve_mc(comm, plan.mc_recv_id, plan.mc_recv_off, &p);
+    mccsResult_t rr = resolve_mc(g, comm, plan.mc_recv_id, plan.mc_recv_off, &p);
     if (rr != mccsSuccess) return rr;
     a.mc_recv = (void*)p;
   }
+  g.unlock();
   a.fifo_slot_bytes = comm->fifo_slot_bytes;
   memcpy(a.ring, plan.ring, sizeof a.ring);
   for (int ch = 0; ch < kMaxRingChannels; ch++) a.ring_step_base[ch] = plan.ring_step_base[ch];
@@ -1087,6 +1088,7 @@ mccsResult_t mccsFinalize(void) {
   c.connected = false;
   for (auto& kv : c.mem) unmap_allocation(kv.second);
   c.mem.clear();
+  c.mem_base_by_id.clear();
   if (g_drv.ok)
     for (auto& kv : c.streams)
       if (kv.second.event) { CtxScope scope(kv.second.device); g_drv.cuEventDestroy_(kv.second.event); }
@@ -1136,6 +1138,7 @@ mccsResult_t mccsMalloc(void** ptr, int device, size_t size) {
     return fail;
   }
   g_ctx.mem[rec.base] = rec;
+  g_ctx.mem_base_by_id[rec.mem_id] = rec.base;
   *ptr = (void*)rec.base;
   return mccsSuccess;
 }
@@ -1174,6 +1177,7 @@ mccsResult_t mccsFree(void* ptr) {
   // Unmap here first, then let the daemon release the memory.
   unmap_allocation(rec);
   g_ctx.mem.erase(it);
+  g_ctx.mem_base_by_id.erase(rec.mem_id);
   if (!g_ctx.connected) return mccsSuccess;
   proto::AnyMsg m;
   memset(&m, 0, sizeof m);
