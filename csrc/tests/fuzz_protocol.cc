@@ -289,6 +289,53 @@ int main(int argc, char** argv) {
     const mccsResult_t ar = mccsAllReduce(comm, buf, buf, 1024, mccsFloat32, mccsSum, nullptr);
     bad += client_mode ? (ar != mccsUnsupported) : (ar != mccsSuccess);
     bad += buf[1023] != 1023.0f;
+    if (client_mode) {
+      // Isolation: another tenant (own connection, own communicator) asks to map the good
+      // tenant's buffer and status block. Both belong to a communicator it is no part of.
+      uint64_t good_mem = 0;
+      mccsMemInfo(buf, &good_mem, nullptr, nullptr);
+      int fd2 = connect_and_hello(path);
+      proto::AnyMsg q, a;
+      memset(&q, 0, sizeof q);
+      q.h.magic = proto::kMagic;
+      q.h.type = proto::kCommInit;
+      q.comm_init.comm_id = 9300;
+      q.comm_init.nranks = 1;
+      ipc::uds_send(fd2, &q, sizeof(proto::CommInitReq));
+      std::vector<int> got;
+      ipc::wait_readable(fd2, 2000);
+      ipc::uds_recv(fd2, &a, sizeof a, &got);
+      const uint64_t own_handle = a.comm_init_reply.comm_handle;
+      for (int f : got) close(f);
+      got.clear();
+      for (uint64_t handle : {own_handle, (uint64_t)mccsCommHandle(comm)}) {
+        memset(&q, 0, sizeof q);
+        q.h.magic = proto::kMagic;
+        q.h.type = proto::kMapMem;
+        q.map_mem.comm_handle = handle;
+        q.map_mem.mem_id = good_mem;
+        ipc::uds_send(fd2, &q, sizeof(proto::MapMemReq));
+        ipc::wait_readable(fd2, 2000);
+        memset(&a, 0, sizeof a);
+        ipc::uds_recv(fd2, &a, sizeof a, &got);
+        if (a.h.status == 0 || !got.empty()) { fprintf(stderr, "a foreign tenant was handed another tenant's buffer\n"); bad++; }
+        for (int f : got) close(f);
+        got.clear();
+      }
+      memset(&q, 0, sizeof q);
+      q.h.magic = proto::kMagic;
+      q.h.type = proto::kMapScratch;
+      q.map_scratch.comm_handle = mccsCommHandle(comm);
+      q.map_scratch.rank = 0;
+      q.map_scratch.kind = proto::kScratchStatus;
+      ipc::uds_send(fd2, &q, sizeof(proto::MapScratchReq));
+      ipc::wait_readable(fd2, 2000);
+      memset(&a, 0, sizeof a);
+      ipc::uds_recv(fd2, &a, sizeof a, &got);
+      if (a.h.status == 0 || !got.empty()) { fprintf(stderr, "a foreign tenant was handed another tenant's status block\n"); bad++; }
+      for (int f : got) close(f);
+      close(fd2);
+    }
     bad += mccsCommDestroy(comm) != mccsSuccess;
     bad += mccsFree(buf) != mccsSuccess;
   }
