@@ -190,10 +190,17 @@ class ProcessGroupMCCS(dist.ProcessGroup):
         for t in tensors:
             if t.numel() == 0:
                 continue
+            # The service has AllReduce and AllGather (as the reference). A broadcast is the
+            # integer sum of the root's bytes and zeros: exact for every dtype, in place, and
+            # 2(n-1)/n of the message per GPU instead of the n-fold traffic of a gather.
             flat = t.contiguous()
-            gathered = torch.empty((self._size,) + tuple(flat.shape), dtype=flat.dtype, device=flat.device)
-            self._all_gather_flat(gathered, flat)
-            t.copy_(gathered[root])
+            raw = flat.view(torch.uint8).reshape(-1) if flat.dtype != torch.uint8 else flat.reshape(-1)
+            words = raw.view(torch.int32) if raw.numel() % 4 == 0 and raw.data_ptr() % 4 == 0 else raw
+            if self._rank != root:
+                words.zero_()
+            self._all_reduce_flat(words, "sum")
+            if flat.data_ptr() != t.data_ptr():
+                t.copy_(flat)
         return _done(list(tensors))
 
     def allgather(self, output_tensors, input_tensors, opts=AllgatherOptions()):

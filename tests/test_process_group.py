@@ -22,6 +22,16 @@ assert torch.equal(t, sum(torch.arange(10, dtype=torch.float32) + r for r in ran
 h = (torch.arange(7) + rank).to(torch.bfloat16); dist.all_reduce(h, op=dist.ReduceOp.AVG)
 assert torch.allclose(h.float(), torch.arange(7).float() + (n - 1) / 2, atol=0.1)
 b = torch.full((5,), float(rank)); dist.broadcast(b, src=1); assert torch.all(b == 1)
+# bit-exact for every dtype and odd sizes: negative zero, NaN, bool, 3-byte tails, strided views
+nz = torch.tensor([-0.0, float("nan"), float("-inf"), 1.5]) if rank == 0 else torch.ones(4)
+dist.broadcast(nz, src=0); assert nz.view(torch.int32).tolist() == torch.tensor([-0.0, float("nan"), float("-inf"), 1.5]).view(torch.int32).tolist()
+bb = torch.tensor([True, False, True]) if rank == 1 else torch.zeros(3, dtype=torch.bool)
+dist.broadcast(bb, src=1); assert bb.tolist() == [True, False, True]
+h = (torch.arange(7, dtype=torch.float16) - 3) if rank == 0 else torch.zeros(7, dtype=torch.float16)
+dist.broadcast(h, src=0); assert h.tolist() == (torch.arange(7, dtype=torch.float16) - 3).tolist()
+sv = torch.zeros(4, 6); col = sv[:, 1:4]
+if rank == 1: col.copy_(torch.arange(12.).reshape(4, 3))
+dist.broadcast(col, src=1); assert torch.equal(sv[:, 1:4], torch.arange(12.).reshape(4, 3)) and float(sv[:, 0].abs().sum()) == 0
 outs = [torch.empty(3, dtype=torch.int64) for _ in range(n)]
 dist.all_gather(outs, torch.full((3,), rank, dtype=torch.int64))
 assert all(torch.all(o == r) for r, o in enumerate(outs))
