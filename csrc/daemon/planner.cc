@@ -21,8 +21,9 @@ const TuneTable* Planner::find_table(int kind, int nranks) const {
 }
 
 uint64_t Planner::message_bytes(const PlanInput& in) {
-  return in.kind == kAllGather ? in.count * (uint64_t)in.nranks
-                               : in.count * (uint64_t)dtype_size(in.dtype);
+  // The whole message: what an all-gather produces, what a reduce-scatter consumes.
+  if (in.kind == kAllGather) return in.count * (uint64_t)in.nranks;
+  return send_units(in.kind, in.count, in.nranks) * (uint64_t)dtype_size(in.dtype);
 }
 
 int Planner::variant_from_name(const std::string& name) {
@@ -42,13 +43,23 @@ void Planner::load_defaults(bool nvls) {
   for (int n = 1; n <= kMaxRanks; n++) {
     TuneTable& ar = table(kAllReduce, n);
     TuneTable& ag = table(kAllGather, n);
+    TuneTable& rs = table(kReduceScatter, n);
     ar.entries.clear();
     ag.entries.clear();
+    rs.entries.clear();
     if (n == 1) {
       ar.entries = {{1 * MB, kLocalCopy, 8, 512}, {kInf, kLocalCopy, 128, 512}};
       ag.entries = ar.entries;
+      rs.entries = ar.entries;
       continue;
     }
+    // Reduce-scatter has not been tuned on hardware: the rows follow the measured rows of
+    // the kernels it shares its inner loop with (the reducing half of the two-shot exchange,
+    // the in-switch reduction).
+    if (n >= 4 && nvls)
+      rs.entries = {{1 * MB, kRsDirect, 8, 512}, {32 * MB, kRsNvls, 8, 512}, {kInf, kRsNvls, 16, 512}};
+    else
+      rs.entries = {{1 * MB, kRsDirect, 8, 512}, {32 * MB, kRsDirect, 32, 512}, {kInf, kRsDirect, 64, 512}};
     // Rows measured on B200: eight ranks behind an NVSwitch for n >= 4, two ranks for
     // n <= 3, where the in-switch reduction moves no fewer bytes than a direct exchange
     // and measured slower. A tuning file replaces them per rank count.
@@ -74,7 +85,7 @@ void Planner::load_defaults(bool nvls) {
 
 bool Planner::load_json(const Value& root, std::string* err) {
   // {"allreduce": {"8": [[max_bytes, "variant", ctas, threads], ...]}, "allgather": {...}}
-  static const char* kind_names[kNumCollKinds] = {"allreduce", "allgather"};
+  static const char* kind_names[kNumCollKinds] = {"allreduce", "allgather", "reducescatter"};
   for (int k = 0; k < kNumCollKinds; k++) {
     const Value& per_kind = root[kind_names[k]];
     for (const auto& kv : per_kind.fields()) {
@@ -118,7 +129,7 @@ bool Planner::load_file(const std::string& path, std::string* err) {
 
 Value Planner::to_json() const {
   std::shared_lock<std::shared_mutex> g(mu_);
-  static const char* kind_names[kNumCollKinds] = {"allreduce", "allgather"};
+  static const char* kind_names[kNumCollKinds] = {"allreduce", "allgather", "reducescatter"};
   Value root = Value::object();
   for (int k = 0; k < kNumCollKinds; k++) {
     Value per_kind = Value::object();
@@ -140,15 +151,18 @@ Value Planner::to_json() const {
 }
 
 std::string Planner::infeasible(int variant, const PlanInput& in) {
-  const bool is_ar = in.kind == kAllReduce;
+  const bool is_ar = kind_reduces(in.kind);   // carries an element type and an operator
   switch (variant) {
     case kLocalCopy:
       return in.nranks == 1 ? "" : "local copy needs a single-rank communicator";
     case kArOneShot: case kArTwoShot: case kArRing: case kArNvlsOne: case kArNvlsTwo: case kArHybrid:
-      if (!is_ar) return "all-reduce variant requested for an all-gather";
+      if (in.kind != kAllReduce) return "all-reduce variant requested for another collective";
       break;
     case kAgPull: case kAgPush: case kAgNvls: case kAgRing:
-      if (is_ar) return "all-gather variant requested for an all-reduce";
+      if (in.kind != kAllGather) return "all-gather variant requested for another collective";
+      break;
+    case kRsDirect: case kRsNvls:
+      if (in.kind != kReduceScatter) return "reduce-scatter variant requested for another collective";
       break;
     default:
       return "unknown variant";
@@ -177,6 +191,7 @@ Plan Planner::plan(const PlanInput& in) const {
   p.bytes = message_bytes(in);
   if (in.nranks < 1 || in.nranks > kMaxRanks) { p.status = proto::kErrInvalidArgument; return p; }
   const bool is_ar = in.kind == kAllReduce;
+  const bool is_rs = in.kind == kReduceScatter;
   std::shared_lock<std::shared_mutex> g(mu_);
   const TuneTable* t = find_table(in.kind, in.nranks);
   const TuneEntry* e = t ? t->lookup(p.bytes) : nullptr;
@@ -186,7 +201,9 @@ Plan Planner::plan(const PlanInput& in) const {
   if (in.requested_variant > 0) candidates.push_back(in.requested_variant);
   if (e) candidates.push_back(e->variant);
   if (in.nranks == 1) candidates.push_back(kLocalCopy);
-  if (is_ar) {
+  if (is_rs) {
+    candidates.push_back(kRsDirect);
+  } else if (is_ar) {
     if (p.bytes <= 256 * 1024) candidates.push_back(kArOneShot);
     candidates.push_back(kArTwoShot);
     candidates.push_back(kArRing);
@@ -233,7 +250,7 @@ Plan Planner::plan(const PlanInput& in) const {
   if (!variant_is_ring(chosen) && (uint64_t)ctas > packs) ctas = (int)packs;
   p.dims.ctas = ctas;
   p.dims.threads = threads;
-  p.needs_mc_send = chosen == kArNvlsOne || chosen == kArNvlsTwo || chosen == kArHybrid;
+  p.needs_mc_send = chosen == kArNvlsOne || chosen == kArNvlsTwo || chosen == kArHybrid || chosen == kRsNvls;
   p.needs_mc_recv = chosen == kArNvlsTwo || chosen == kAgNvls || chosen == kArHybrid;
   return p;
 }

@@ -152,16 +152,16 @@ bool ProxyEngine::post(RankState& rs, const proto::WorkRequest& wr) {
   op.recv_mem = wr.recv_mem; op.recv_off = wr.recv_off;
   op.t_post_us = monotonic_us();
   int status = proto::kOk;
-  if (op.kind != kAllReduce && op.kind != kAllGather) status = proto::kErrInvalidArgument;
-  else if (op.kind == kAllReduce && (op.dtype < 0 || op.dtype >= kNumDataTypes || op.op < 0 || op.op >= kNumRedOps))
+  if (op.kind < 0 || op.kind >= kNumCollKinds) status = proto::kErrInvalidArgument;
+  else if (kind_reduces(op.kind) && (op.dtype < 0 || op.dtype >= kNumDataTypes || op.op < 0 || op.op >= kNumRedOps))
     status = proto::kErrInvalidArgument;
   else if (op.variant_req < 0 || op.variant_req >= kNumVariants) status = proto::kErrInvalidArgument;
   // Sizes come from another process: keep count * element size * ranks far from wrapping.
   else if (op.count > (1ull << 44)) status = proto::kErrInvalidArgument;
   if (status == proto::kOk) {
-    const uint64_t esz = op.kind == kAllReduce ? (uint64_t)dtype_size(op.dtype) : 1;
-    const uint64_t send_bytes = op.count * esz;
-    const uint64_t recv_bytes = op.kind == kAllReduce ? send_bytes : send_bytes * (uint64_t)c.nranks;
+    const uint64_t esz = kind_reduces(op.kind) ? (uint64_t)dtype_size(op.dtype) : 1;
+    const uint64_t send_bytes = send_units(op.kind, op.count, c.nranks) * esz;
+    const uint64_t recv_bytes = recv_units(op.kind, op.count, c.nranks) * esz;
     int sdev = -1, rdev = -1;
     if (!daemon_->translate(op.send_mem, op.send_off, send_bytes, &op.send_va, &sdev) ||
         !daemon_->translate(op.recv_mem, op.recv_off, recv_bytes, &op.recv_va, &rdev))
@@ -189,9 +189,9 @@ int ProxyEngine::ensure_mc(Communicator& c, CollSlot& s, bool for_recv, uint64_t
   std::vector<uint64_t> key;
   for (int r = 0; r < c.nranks; r++) key.push_back(for_recv ? s.ops[r].recv_mem : s.ops[r].send_mem);
   const uint64_t off = for_recv ? s.ops[0].recv_off : s.ops[0].send_off;
-  const uint64_t esz = s.ops[0].kind == kAllReduce ? (uint64_t)dtype_size(s.ops[0].dtype) : 1;
-  uint64_t bytes = s.ops[0].count * esz;
-  if (for_recv && s.ops[0].kind == kAllGather) bytes *= (uint64_t)c.nranks;
+  const uint64_t esz = kind_reduces(s.ops[0].kind) ? (uint64_t)dtype_size(s.ops[0].dtype) : 1;
+  const uint64_t bytes = (for_recv ? recv_units(s.ops[0].kind, s.ops[0].count, c.nranks)
+                                   : send_units(s.ops[0].kind, s.ops[0].count, c.nranks)) * esz;
   std::lock_guard<std::mutex> g(c.mc_mu);
   auto it = c.mc_cache.find(key);
   if (it == c.mc_cache.end()) {
@@ -237,7 +237,7 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
     if (!s.ops[r].valid) return fail(s.ops[r].status ? s.ops[r].status : proto::kErrInvalidArgument);
   for (int r = 1; r < c.nranks; r++) {
     const CollOp& o = s.ops[r];
-    if (o.kind != o0.kind || o.count != o0.count || (o0.kind == kAllReduce && (o.dtype != o0.dtype || o.op != o0.op)))
+    if (o.kind != o0.kind || o.count != o0.count || (kind_reduces(o0.kind) && (o.dtype != o0.dtype || o.op != o0.op)))
       return fail(proto::kErrMismatch);
   }
   Backend* be = daemon_->backend();
@@ -246,18 +246,20 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   in.kind = o0.kind;
   in.nranks = c.nranks;
   in.count = o0.count;
-  in.dtype = o0.kind == kAllReduce ? o0.dtype : kUint8;
-  in.op = o0.kind == kAllReduce ? o0.op : kSum;
+  in.dtype = kind_reduces(o0.kind) ? o0.dtype : kUint8;
+  in.op = kind_reduces(o0.kind) ? o0.op : kSum;
   in.emulated = c.emulated;
   in.host_staged = c.host_staged;
   in.fifo_slot_bytes = c.fifo_slot_bytes;
-  uint64_t bits = o0.kind == kAllGather ? o0.count : 0;
+  // Every block boundary the kernels compute from the count must be aligned as well.
+  uint64_t bits = o0.kind == kAllGather ? o0.count : o0.kind == kReduceScatter ? o0.count * (uint64_t)dtype_size(o0.dtype) : 0;
   bool same_send_off = true, same_recv_off = true, all_vmm = !host_backend || be->nvls_supported();   // the host backend's emulated multicast binds any of its allocations
   int req = o0.variant_req;
   for (int r = 0; r < c.nranks; r++) {
     const CollOp& o = s.ops[r];
     bits |= o.send_va | o.recv_va;
     if (o0.kind == kAllReduce) in.in_place |= o.send_va == o.recv_va;
+    else if (o0.kind == kReduceScatter) in.in_place |= o.recv_va == o.send_va + (uint64_t)r * o.count * (uint64_t)dtype_size(o.dtype);
     else in.in_place |= o.send_va == o.recv_va + (uint64_t)r * o.count;
     same_send_off &= o.send_off == o0.send_off;
     same_recv_off &= o.recv_off == o0.recv_off;
@@ -270,10 +272,12 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
       if (!be->peer_access(c.devices[a], c.devices[b])) { in.p2p_possible = false; break; }
   in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged &&
                      (!c.client_launch || daemon_->config().client_nvls) &&
-                     all_vmm && same_recv_off && (same_send_off || o0.kind == kAllGather) && c.nranks >= 2;
+                     all_vmm && c.nranks >= 2 &&
+                     (o0.kind == kReduceScatter ? same_send_off   // only the inputs are read through the switch
+                                                : same_recv_off && (same_send_off || o0.kind == kAllGather));
   {
     std::lock_guard<std::mutex> g(c.cfg_mu);
-    const int cfg_variant = o0.kind == kAllReduce ? c.ar_variant : c.ag_variant;
+    const int cfg_variant = o0.kind == kAllReduce ? c.ar_variant : o0.kind == kAllGather ? c.ag_variant : (int)kAuto;
     in.requested_variant = req != kAuto ? req : cfg_variant;
     in.requested_ctas = c.ctas_override;
     in.ring_channels = c.channel_count;
@@ -342,7 +346,7 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   s.ticket_base = c.ticket + 1;
   c.ticket += (uint64_t)s.nslices;
   if (variant_is_ring(plan.variant)) {
-    const int esz = o0.kind == kAllReduce ? dtype_size(o0.dtype) : 1;
+    const int esz = kind_reduces(o0.kind) ? dtype_size(o0.dtype) : 1;
     const uint64_t steps = ring_steps_per_channel(o0.kind, o0.count, esz, c.nranks, plan.dims.ctas, c.fifo_slot_bytes);
     for (int ch = 0; ch < kMaxRingChannels; ch++) s.ring_step_base[ch] = c.ring_steps[ch];
     for (int ch = 0; ch < plan.dims.ctas; ch++) c.ring_steps[ch] += steps;
@@ -559,10 +563,10 @@ void ProxyEngine::fill_args(Communicator& c, CollSlot& s, int rank, int slice, C
   a.rank = rank;
   a.nranks = c.nranks;
   a.emulated = group ? 1 : 0;
-  a.dtype = o0.kind == kAllReduce ? o0.dtype : kUint8;
-  a.op = o0.kind == kAllReduce ? o0.op : kSum;
+  a.dtype = kind_reduces(o0.kind) ? o0.dtype : kUint8;
+  a.op = kind_reduces(o0.kind) ? o0.op : kSum;
   a.variant = s.plan.variant;
-  const uint64_t esz = o0.kind == kAllReduce ? (uint64_t)dtype_size(o0.dtype) : 1;
+  const uint64_t esz = kind_reduces(o0.kind) ? (uint64_t)dtype_size(o0.dtype) : 1;
   uint64_t first = 0, count = o0.count;
   if (s.nslices > 1) {
     first = (uint64_t)slice * s.slice_count;
@@ -782,8 +786,8 @@ bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
   m.variant = s.plan.variant;
   m.ctas = s.plan.dims.ctas;
   m.threads = s.plan.dims.threads;
-  m.dtype = o0.kind == kAllReduce ? o0.dtype : kUint8;
-  m.op = o0.kind == kAllReduce ? o0.op : kSum;
+  m.dtype = kind_reduces(o0.kind) ? o0.dtype : kUint8;
+  m.op = kind_reduces(o0.kind) ? o0.op : kSum;
   m.nranks = c.nranks;
   m.scale = o0.op == kSumPostDiv ? 1.0f / (float)c.nranks : o0.scale;
   m.epoch = s.epoch_base;

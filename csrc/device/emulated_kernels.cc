@@ -14,6 +14,7 @@
 #define MCCS_UNTYPED_KERNELS 1
 #include "../kernels/batch.cuh"
 #include "../kernels/hybrid.cuh"
+#include "../kernels/scatter.cuh"
 
 #include "emulated_kernels.h"
 
@@ -64,6 +65,24 @@ bool typed_allreduce(const CollArgs& a, int ctas, int threads) {
     case kProd: return by_op(OpProd{});
     case kMax: return by_op(OpMax{});
     case kMin: return by_op(OpMin{});
+  }
+  return false;
+}
+
+template <typename T>
+bool typed_reduce_scatter(const CollArgs& a, int ctas, int threads) {
+  if constexpr (std::is_same<T, float>::value || std::is_same<T, __half>::value || std::is_same<T, __nv_bfloat16>::value) {
+    if (a.variant == kRsNvls && (a.op == kSum || a.op == kSumPostDiv)) {
+      run_grid(rs_nvls_kernel<T>, a, a.nranks, ctas, threads);
+      return true;
+    }
+  }
+  if (a.variant != kRsDirect) return false;
+  switch (a.op) {
+    case kSum: case kPreMulSum: case kSumPostDiv: run_grid(rs_direct_kernel<T, OpSum>, a, a.nranks, ctas, threads); return true;
+    case kProd: run_grid(rs_direct_kernel<T, OpProd>, a, a.nranks, ctas, threads); return true;
+    case kMax: run_grid(rs_direct_kernel<T, OpMax>, a, a.nranks, ctas, threads); return true;
+    case kMin: run_grid(rs_direct_kernel<T, OpMin>, a, a.nranks, ctas, threads); return true;
   }
   return false;
 }
@@ -135,7 +154,7 @@ bool emulated_launch(int kind, const CollArgs& args, LaunchDims dims) {
   int ctas = dims.ctas, threads = dims.threads;
   clamp(&ctas, &threads, variant_is_ring(a.variant));
   if (a.variant == kLocalCopy) {
-    if (kind == kAllReduce) a.count = args.count * (uint64_t)dtype_size(args.dtype);
+    if (kind_reduces(kind)) a.count = args.count * (uint64_t)dtype_size(args.dtype);
     run_grid(local_copy_kernel, a, a.nranks, ctas, threads);
     return true;
   }
@@ -148,6 +167,11 @@ bool emulated_launch(int kind, const CollArgs& args, LaunchDims dims) {
     }
     return false;
   }
+  if (kind == kReduceScatter)
+    return by_dtype(a.dtype, [&](auto* tag) {
+      using T = typename std::remove_pointer<decltype(tag)>::type;
+      return typed_reduce_scatter<T>(a, ctas, threads);
+    });
   return by_dtype(a.dtype, [&](auto* tag) {
     using T = typename std::remove_pointer<decltype(tag)>::type;
     return typed_allreduce<T>(a, ctas, threads);

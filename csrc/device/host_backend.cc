@@ -326,7 +326,7 @@ class HostBackend : public Backend {
   bool variant_supported(int variant, int dtype, int op) const override {
     if (!variant_is_nvls(variant)) return true;
     if (!emulate_) return false;
-    if (variant == kAgNvls) return true;
+    if (variant == kAgNvls) return true;   // (kRsNvls reduces: the type rule below applies)
     return (dtype == kFloat32 || dtype == kFloat16 || dtype == kBfloat16) && (op == kSum || op == kPreMulSum || op == kSumPostDiv);
   }
   int max_group_ctas(int, int, int, int, int) const override { return kMaxCtas; }
@@ -358,7 +358,31 @@ class HostBackend : public Backend {
     }
     if (kind == kAllGather) {
       cpu_allgather(a);
+    } else if (kind == kReduceScatter && a.nranks > 1) {
+      // Block q of every rank's input, reduced, is rank q's output: nranks small all-reduces
+      // whose every "rank" stores to the one destination.
+      const uint64_t block = a.count * (uint64_t)dtype_size(a.dtype);
+      for (int q = 0; q < a.nranks; q++) {
+        CollArgs b = a;
+        for (int r = 0; r < a.nranks; r++) {
+          b.send[r] = (const char*)a.send[r] + (uint64_t)q * block;
+          b.recv[r] = a.recv[q];
+        }
+        int rc = launch_allreduce_loops(b);
+        if (rc != proto::kOk) return rc;
+      }
     } else {
+      int rc = launch_allreduce_loops(a);
+      if (rc != proto::kOk) return rc;
+    }
+    for (int r = 0; r < a.nranks; r++)
+      if (a.status[r]) __atomic_store_n(&a.status[r]->done_seq, a.seq, __ATOMIC_RELEASE);
+    return proto::kOk;
+  }
+
+ private:
+  static int launch_allreduce_loops(const CollArgs& a) {
+    {
       switch (a.dtype) {
         case kInt8: cpu_allreduce<int8_t, 1>(a); break;
         case kUint8: cpu_allreduce<uint8_t, 1>(a); break;
@@ -373,12 +397,9 @@ class HostBackend : public Backend {
         default: return proto::kErrInvalidArgument;
       }
     }
-    for (int r = 0; r < a.nranks; r++)
-      if (a.status[r]) __atomic_store_n(&a.status[r]->done_seq, a.seq, __ATOMIC_RELEASE);
     return proto::kOk;
   }
 
- private:
   std::mutex scratch_mu_;
   std::map<void*, std::pair<int, size_t>> scratch_;
   int ndev_;

@@ -86,7 +86,9 @@ typedef enum {
   mccsAlgoAuto = 0, mccsAlgoArOneShot = 1, mccsAlgoArTwoShot = 2, mccsAlgoArNvlsOneShot = 3,
   mccsAlgoArNvlsTwoShot = 4, mccsAlgoArRing = 5, mccsAlgoAgPull = 6, mccsAlgoAgPush = 7,
   mccsAlgoAgNvls = 8, mccsAlgoAgRing = 9, mccsAlgoLocalCopy = 10,
-  mccsAlgoArHybrid = 11   /* part through the switch, part by peer copies, in one kernel */
+  mccsAlgoArHybrid = 11,  /* part through the switch, part by peer copies, in one kernel */
+  mccsAlgoRsDirect = 12,  /* reduce-scatter by peer loads */
+  mccsAlgoRsNvls = 13     /* reduce-scatter in the switch */
 } mccsAlgo_t;
 
 /* Connects to the daemon. Optional: every other call connects on first use with
@@ -127,6 +129,15 @@ mccsResult_t mccsAllGather(mccsComm_t comm, const void* send, void* recv, size_t
                            mccsStream_t stream);
 mccsResult_t mccsAllGatherEx(mccsComm_t comm, const void* send, void* recv, size_t bytes,
                              mccsAlgo_t algo, mccsStream_t stream);
+
+/* Not in the reference: every rank contributes nranks*count elements and receives the
+ * reduction of block `rank` (count elements), at half the traffic of an AllReduce.
+ * In-place when recv == send + rank*count elements. */
+mccsResult_t mccsReduceScatter(mccsComm_t comm, const void* send, void* recv, size_t count,
+                               mccsDataType_t dtype, mccsRedOp_t op, mccsStream_t stream);
+mccsResult_t mccsReduceScatterEx(mccsComm_t comm, const void* send, void* recv, size_t count,
+                                 mccsDataType_t dtype, mccsRedOp_t op, float scale, mccsAlgo_t algo,
+                                 mccsStream_t stream);
 
 /* Deferred waiting. By default every collective call also makes the caller's stream wait
  * for the collective (stream order, like a kernel launch). A caller that issues many

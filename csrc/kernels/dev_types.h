@@ -31,7 +31,13 @@ enum RedOp : int32_t {
   kNumRedOps = 6
 };
 
-enum CollKind : int32_t { kAllReduce = 0, kAllGather = 1, kNumCollKinds = 2 };
+// kReduceScatter: every rank sends nranks * count elements and receives the reduction of
+// block `rank` (count elements).
+enum CollKind : int32_t { kAllReduce = 0, kAllGather = 1, kReduceScatter = 2, kNumCollKinds = 3 };
+inline bool kind_reduces(int kind) { return kind == kAllReduce || kind == kReduceScatter; }
+// Units (elements; bytes for all-gather) one rank sends and receives for CollArgs::count.
+inline uint64_t send_units(int kind, uint64_t count, int nranks) { return kind == kReduceScatter ? count * (uint64_t)nranks : count; }
+inline uint64_t recv_units(int kind, uint64_t count, int nranks) { return kind == kAllGather ? count * (uint64_t)nranks : count; }
 
 // Kernel variants. `kAuto` lets the planner pick from the tuning table.
 enum Variant : int32_t {
@@ -47,7 +53,9 @@ enum Variant : int32_t {
   kAgRing = 9,       // FIFO-staged ring
   kLocalCopy = 10,   // single-rank communicator: device copy (or nothing in place)
   kArHybrid = 11,    // head of the buffer through the switch (multimem), rest by peer loads/stores, in one kernel
-  kNumVariants = 12
+  kRsDirect = 12,    // reduce-scatter: every rank loads its block from all peers and reduces it
+  kRsNvls = 13,      // reduce-scatter: multimem.ld_reduce of the own block
+  kNumVariants = 14
 };
 
 // Error codes written by kernels into the per-rank status word.
@@ -95,7 +103,7 @@ struct CollArgs {
   int32_t dtype;           // DataType
   int32_t op;              // RedOp
   int32_t variant;         // Variant
-  uint64_t count;          // AllReduce: elements. AllGather: bytes per rank.
+  uint64_t count;          // AllReduce: elements. AllGather: bytes per rank. ReduceScatter: elements per block.
   uint64_t seq;            // collective sequence number (for StatusBlock::done_seq)
   float scale;             // PreMulSum multiplier / SumPostDiv divisor reciprocal
   uint32_t epoch;          // first barrier value this launch may use (uses epoch, epoch+1)
@@ -177,11 +185,13 @@ inline const char* variant_name(int v) {
     case kAgRing: return "ag_ring";
     case kLocalCopy: return "local_copy";
     case kArHybrid: return "ar_hybrid";
+    case kRsDirect: return "rs_direct";
+    case kRsNvls: return "rs_nvls";
   }
   return "?";
 }
 
-inline bool variant_is_nvls(int v) { return v == kArNvlsOne || v == kArNvlsTwo || v == kAgNvls || v == kArHybrid; }
+inline bool variant_is_nvls(int v) { return v == kArNvlsOne || v == kArNvlsTwo || v == kAgNvls || v == kArHybrid || v == kRsNvls; }
 inline bool variant_is_ring(int v) { return v == kArRing || v == kAgRing; }
 
 // Number of ring steps one channel consumes for a collective. Every rank and every

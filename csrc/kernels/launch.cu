@@ -31,7 +31,8 @@ namespace mccs {
 const void* batch_kernel_function(int variant, int dtype, int op);
 
 const void* kernel_function(int variant, int dtype, int op) {
-  if (variant == kArHybrid) return batch_kernel_function(variant, dtype, op);   // lives with the newer kernels
+  if (variant == kArHybrid || variant == kRsDirect || variant == kRsNvls)
+    return batch_kernel_function(variant, dtype, op);   // live with the newer kernels
   switch (variant) {
     case kAgPull: case kAgPush: case kAgNvls: case kAgRing: case kLocalCopy:
       return mccs_kfn_untyped(variant);
@@ -108,7 +109,7 @@ int max_cooperative_ctas(int variant, int dtype, int op, int threads, int nranks
 
 cudaError_t launch_collective(int kind, const CollArgs& args, LaunchDims dims, void* stream) {
   CollArgs a = args;
-  if (a.variant == kLocalCopy && kind == kAllReduce) a.count = args.count * (uint64_t)dtype_size(args.dtype);
+  if (a.variant == kLocalCopy && kind_reduces(kind)) a.count = args.count * (uint64_t)dtype_size(args.dtype);
   const void* fn = kernel_function(a.variant, a.dtype, a.op);
   if (!fn) return cudaErrorInvalidDeviceFunction;
   if (dims.ctas < 1 || dims.ctas > kMaxCtas || dims.threads < 32 || dims.threads > 512)

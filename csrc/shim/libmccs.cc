@@ -1447,6 +1447,33 @@ mccsResult_t mccsAllReduce(mccsComm_t comm, const void* send, void* recv, size_t
   return mccsAllReduceEx(comm, send, recv, count, dtype, op, 1.0f, mccsAlgoAuto, stream);
 }
 
+mccsResult_t mccsReduceScatterEx(mccsComm_t comm, const void* send, void* recv, size_t count, mccsDataType_t dtype,
+                                 mccsRedOp_t op, float scale, mccsAlgo_t algo, mccsStream_t stream) {
+  if (!comm || (int)dtype < 0 || (int)dtype >= kNumDataTypes || (int)op < 0 || (int)op >= kNumRedOps)
+    return mccsInvalidArgument;
+  const uint64_t esz = (uint64_t)dtype_size((int)dtype);
+  if ((((uint64_t)send | (uint64_t)recv) & (esz - 1)) != 0 || count > (1ull << 44)) {
+    LOG_ERROR("reduce-scatter buffers must be aligned to the element size (send %p, recv %p, %llu-byte elements)", send, recv,
+              (unsigned long long)esz);
+    return mccsInvalidArgument;
+  }
+  proto::WorkRequest wr;
+  memset(&wr, 0, sizeof wr);
+  wr.kind = kReduceScatter;
+  wr.dtype = (uint32_t)dtype;
+  wr.op = (uint32_t)op;
+  wr.count = count;
+  wr.scale = scale;
+  wr.variant = (uint32_t)algo;
+  const uint64_t bytes = (uint64_t)count * esz;
+  return submit(comm, wr, send, recv, bytes * (uint64_t)comm->nranks, bytes, stream);
+}
+
+mccsResult_t mccsReduceScatter(mccsComm_t comm, const void* send, void* recv, size_t count, mccsDataType_t dtype,
+                               mccsRedOp_t op, mccsStream_t stream) {
+  return mccsReduceScatterEx(comm, send, recv, count, dtype, op, 1.0f, mccsAlgoAuto, stream);
+}
+
 mccsResult_t mccsAllGatherEx(mccsComm_t comm, const void* send, void* recv, size_t bytes, mccsAlgo_t algo,
                              mccsStream_t stream) {
   if (!comm) return mccsInvalidArgument;

@@ -210,6 +210,29 @@ static void test_planner() {
   CHECK(pl.variant == kArTwoShot && !pl.note.empty());
   in.nvls_possible = true; in.requested_variant = kAuto;
   CHECK(Planner::variant_from_name("ar_hybrid") == kArHybrid);
+  // reduce-scatter: its own table; in the switch only for float sums on aligned blocks;
+  // variants of other collectives are refused for it and its variants for them
+  {
+    PlanInput rs = in;
+    rs.kind = kReduceScatter; rs.count = 8u << 20; rs.requested_variant = kAuto; rs.in_place = true;
+    Plan q = p.plan(rs);
+    CHECK(q.status == 0 && q.variant == kRsNvls && q.needs_mc_send && !q.needs_mc_recv);
+    CHECK(q.bytes == (uint64_t)(8u << 20) * (uint64_t)rs.nranks * (uint64_t)dtype_size(rs.dtype));
+    rs.nvls_possible = false;
+    q = p.plan(rs);
+    CHECK(q.status == 0 && q.variant == kRsDirect);
+    rs.nvls_possible = true; rs.dtype = kInt32;
+    CHECK(p.plan(rs).variant == kRsDirect);
+    rs.dtype = in.dtype; rs.requested_variant = kArTwoShot;
+    q = p.plan(rs);
+    CHECK(q.status == 0 && (q.variant == kRsNvls || q.variant == kRsDirect) && !q.note.empty());
+    PlanInput ar = in;
+    ar.requested_variant = kRsDirect;
+    q = p.plan(ar);
+    CHECK(q.status == 0 && q.variant != kRsDirect && !q.note.empty());
+    rs.requested_variant = kAuto; rs.nranks = 1;
+    CHECK(p.plan(rs).variant == kLocalCopy);
+  }
   // QoS cap and override
   in.count = 256u << 20; in.cta_cap = 5;
   CHECK(p.plan(in).dims.ctas == 5);

@@ -67,6 +67,9 @@ def shim() -> ctypes.CDLL:
     lib.mccsAllReduceEx.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_float,
                                     c_int, c_void_p]
     lib.mccsAllReduceEx.restype = c_int
+    lib.mccsReduceScatterEx.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_int, c_float,
+                                        c_int, c_void_p]
+    lib.mccsReduceScatterEx.restype = c_int
     lib.mccsAllGatherEx.argtypes = [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]
     lib.mccsAllGatherEx.restype = c_int
     lib.mccsGroupStart.restype = c_int

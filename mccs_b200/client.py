@@ -33,6 +33,7 @@ OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "premulsum": 4, "avg": 5, "sumpo
 ALGOS = {
     "auto": 0, "ar_oneshot": 1, "ar_twoshot": 2, "ar_nvls_oneshot": 3, "ar_nvls_twoshot": 4,
     "ar_ring": 5, "ag_pull": 6, "ag_push": 7, "ag_nvls": 8, "ag_ring": 9, "local_copy": 10, "ar_hybrid": 11,
+    "rs_direct": 12, "rs_nvls": 13,
 }
 ALGO_NAMES = {v: k for k, v in ALGOS.items()}
 
@@ -173,6 +174,20 @@ class Communicator:
             nbytes = send.numel() * send.element_size()
         check(_lib.shim().mccsAllGatherEx(self._h, c_void_p(_ptr(send)), c_void_p(_ptr(recv)), int(nbytes),
                                           ALGOS[algo], c_void_p(self._stream(stream))), "mccsAllGather")
+
+    def reduce_scatter(self, send, recv, *, count: Optional[int] = None, dtype: Optional[torch.dtype] = None,
+                       op: str = "sum", scale: float = 1.0, algo: str = "auto", stream=None) -> None:
+        """ReduceScatter: ``send`` holds ``nranks * count`` elements, ``recv`` receives the
+        reduction of block ``rank`` (``count`` elements). In place when ``recv`` is the
+        rank's own block of ``send``. The reference has no such call."""
+        if isinstance(recv, torch.Tensor):
+            dtype = dtype or recv.dtype
+            count = recv.numel() if count is None else count
+        if dtype is None or count is None:
+            raise ValueError("dtype and count are needed for raw pointers")
+        check(_lib.shim().mccsReduceScatterEx(self._h, c_void_p(_ptr(send)), c_void_p(_ptr(recv)), int(count),
+                                              DTYPES[dtype], OPS[op.lower()], float(scale), ALGOS[algo],
+                                              c_void_p(self._stream(stream))), "mccsReduceScatter")
 
     def set_deferred_wait(self, on: bool) -> None:
         """With deferred waiting a collective call does not make the caller's stream wait

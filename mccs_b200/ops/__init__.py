@@ -34,6 +34,8 @@ VARIANTS = {
     "ag_push": "AllGather: every rank stores its shard into every peer",
     "ag_nvls": "AllGather: multimem.st of the own shard",
     "ag_ring": "AllGather: FIFO-staged ring",
+    "rs_direct": "ReduceScatter: every rank loads its block from all peers and reduces it (the reducing half of ar_twoshot)",
+    "rs_nvls": "ReduceScatter: multimem.ld_reduce of the own block",
     "local_copy": "single-rank communicator: device copy",
 }
 assert set(VARIANTS) == set(ALGOS)
@@ -51,6 +53,14 @@ def all_reduce(comm: Communicator, send: torch.Tensor, recv: Optional[torch.Tens
 def all_gather(comm: Communicator, send: torch.Tensor, recv: torch.Tensor, *, algo: str = "auto", stream=None) -> torch.Tensor:
     """AllGather: rank r's ``send`` lands at ``recv[r * send.numel():]`` on every rank."""
     comm.all_gather(send, recv, algo=algo, stream=stream)
+    return recv
+
+
+def reduce_scatter(comm: Communicator, send: torch.Tensor, recv: torch.Tensor, *, op: str = "sum", scale: float = 1.0,
+                   algo: str = "auto", stream=None) -> torch.Tensor:
+    """ReduceScatter: ``send`` holds ``nranks`` blocks of ``recv.numel()`` elements; ``recv``
+    receives the reduction of this rank's block (in place when it is that block of ``send``)."""
+    comm.reduce_scatter(send, recv, op=op, scale=scale, algo=algo, stream=stream)
     return recv
 
 
@@ -88,4 +98,4 @@ def local_all_reduce_no_alloc(inputs: Sequence[torch.Tensor], outputs: Optional[
     return outs
 
 
-__all__ = ["VARIANTS", "all_reduce", "all_gather", "local_all_reduce_no_alloc"]
+__all__ = ["VARIANTS", "all_reduce", "all_gather", "reduce_scatter", "local_all_reduce_no_alloc"]

@@ -225,20 +225,35 @@ class ProcessGroupMCCS(dist.ProcessGroup):
             self._allgather_base(o, i, opts)
         return _done(outputs)
 
+    def _reduce_scatter_flat(self, out: torch.Tensor, full: torch.Tensor, op: str) -> None:
+        """full: contiguous, size * out.numel() elements; out receives the reduction of this
+        rank's block. Through the service's own reduce-scatter (half the traffic of the
+        all-reduce this used to be); tensors outside service memory are staged."""
+        n = out.numel()
+        if n == 0:
+            return
+        if self._usable_in_place(full) and self._usable_in_place(out) and out.dtype == full.dtype:
+            self._comm.reduce_scatter(full, out, op=op)
+            return
+        dtype = full.dtype
+        work_dtype = dtype if dtype in client.DTYPES else torch.float32
+        esz = torch.empty((), dtype=work_dtype).element_size()
+        with self._lock:
+            st = self._stage(n * self._size * esz).tensor(work_dtype, n * self._size)
+            st.copy_(full.reshape(-1), non_blocking=True)
+            mine = st[self._rank * n:(self._rank + 1) * n]
+            self._comm.reduce_scatter(st, mine, op=op)           # in place inside the staging buffer
+            out.reshape(-1).copy_(mine, non_blocking=True) if out.is_contiguous() else out.copy_(mine.reshape(out.shape))
+
     def reduce_scatter(self, output_tensors, input_tensors, opts=ReduceScatterOptions()):
-        # The service offers all-reduce and all-gather (as the reference does); a
-        # reduce-scatter is an all-reduce of which each rank keeps its part.
         op = _op_name(opts.reduceOp)
         for out, ins in zip(output_tensors, input_tensors):
             full = torch.stack([i.contiguous() for i in ins])
-            self._all_reduce_flat(full, op)
-            out.copy_(full[self._rank])
+            self._reduce_scatter_flat(out, full, op)
         return _done(output_tensors)
 
     def _reduce_scatter_base(self, output_tensor, input_tensor, opts=ReduceScatterOptions()):
-        full = input_tensor.contiguous().clone()
-        self._all_reduce_flat(full, _op_name(opts.reduceOp))
-        output_tensor.copy_(full.reshape(self._size, -1)[self._rank].reshape(output_tensor.shape))
+        self._reduce_scatter_flat(output_tensor, input_tensor.contiguous(), _op_name(opts.reduceOp))
         return _done(output_tensor)
 
     def barrier(self, opts=BarrierOptions()):

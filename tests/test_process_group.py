@@ -40,6 +40,13 @@ assert torch.equal(big, torch.arange(n).repeat_interleave(4).float())
 m = torch.tensor([float(rank)]); dist.all_reduce(m, op=dist.ReduceOp.MAX); assert m.item() == n - 1
 rs = torch.empty(2); dist.reduce_scatter_tensor(rs, torch.arange(2 * n).float())
 assert torch.equal(rs, torch.arange(2 * n).float().reshape(n, 2)[rank] * n)
+ro = torch.empty(3, dtype=torch.float16)
+dist.reduce_scatter(ro, [torch.full((3,), float(rank + q), dtype=torch.float16) for q in range(n)], op=dist.ReduceOp.AVG)
+assert torch.allclose(ro.float(), torch.full((3,), sum(r + rank for r in range(n)) / n))
+# both tensors in service memory: the service's reduce-scatter runs on them directly
+zf, keep_f = mpg.empty(8 * n, torch.float32, device=rank); zo, keep_o = mpg.empty(8, torch.float32, device=rank)
+zf.copy_(torch.arange(8 * n).float() + rank); dist.reduce_scatter_tensor(zo, zf)
+assert torch.equal(zo, (torch.arange(8 * n).float().reshape(n, 8)[rank]) * n + sum(range(n)))
 # a tensor in service memory is reduced in place, without staging
 z, keep = mpg.empty(1000, torch.float32, device=rank)
 z.fill_(rank + 1.0); assert mpg.in_service_memory(z)

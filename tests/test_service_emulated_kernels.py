@@ -54,6 +54,35 @@ def allgather(algo, nbytes, in_place=False):
         bad.append(("allgather", algo, nbytes, in_place))
     seen.add(comm.last_plan()[0])
 
+def reduce_scatter(algo, dname, count, op="sum", in_place=False):
+    global salt
+    salt += 1
+    dt = DT[dname]
+    xs = inputs(dt, count * n, salt)
+    s = send.tensor(dt, count * n); s.copy_(xs[rank])
+    d = s[rank * count:(rank + 1) * count] if in_place else recv.tensor(dt, count)
+    comm.reduce_scatter(s, d, op=op, algo=algo)
+    acc = torch.stack([x.double() for x in xs])[:, rank * count:(rank + 1) * count]
+    want = {"sum": acc.sum(0), "max": acc.max(0).values, "avg": acc.sum(0) / n}[op]
+    tol = {"bf16": 0.05 * n, "f16": 0.01 * n}.get(dname, 1e-6)
+    if not torch.allclose(d.double(), want, rtol=0, atol=tol):
+        bad.append(("reduce_scatter", algo, dname, count, op, in_place))
+    seen.add(comm.last_plan()[0])
+
+if os.environ.get("HOST_STAGED") == "1":
+    # the host-staged transport has ring kernels only, and reduce-scatter has no ring form
+    try:
+        reduce_scatter("auto", "f32", 64)
+        bad.append(("reduce_scatter accepted on the host-staged transport",))
+    except Exception as e:
+        if getattr(e, "code", None) != -9: bad.append(("reduce_scatter", str(e)))
+    comm.destroy(); comm = M.Communicator(6100, rank, n, device=rank)   # the refusal ended the communicator
+for algo in () if os.environ.get("HOST_STAGED") == "1" else ("rs_direct", "auto") + (("rs_nvls",) if os.environ.get("NVLS") == "1" else ()):
+    for dname, count in (("f32", 1), ("f32", 1028), ("bf16", 3000), ("i32", 257), ("f64", 100), ("f16", 2048), ("f32", 4099)):
+        reduce_scatter(algo, dname, count)
+    reduce_scatter(algo, "f32", 1000, op="avg")
+    reduce_scatter(algo, "i32", 500, op="max")
+    reduce_scatter(algo, "f32", 2048, in_place=True)
 for algo in ("ar_oneshot", "ar_twoshot", "ar_ring", "auto"):
     for dname, count in (("f32", 1), ("f32", 4099), ("bf16", 3001), ("i32", 257), ("f64", 100), ("i64", 33), ("f16", 2048)):
         allreduce(algo, dname, count)
@@ -138,7 +167,7 @@ def test_service_with_the_real_kernels_on_the_emulator(tmp_path, n, sync):
     for res in _run(tmp_path, n, extra, sync=sync):
         assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
         # every emulated variant really ran
-        assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
+        assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring", "rs_direct"} <= set(res["seen"])
         assert res["epoch"] == 1 and res["fused_members"] >= 2 and res["client_launch"] is False
 
 
@@ -150,12 +179,12 @@ def test_in_switch_variants_on_emulated_multicast(tmp_path, n):
     addresses in the kernels' arguments are exercised as on a GPU."""
     for res in _run(tmp_path, n, "", client_env={"NVLS": "1"}):
         assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
-        assert {"ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid", "ag_nvls"} <= set(res["seen"])
+        assert {"ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid", "ag_nvls", "rs_nvls"} <= set(res["seen"])
 
 
 def test_host_staged_transport_with_the_real_ring_kernels(tmp_path):
     """`transport = "host_staged"`: only the FIFO ring variants are legal, whatever is asked for."""
-    for res in _run(tmp_path, 3, "", transport="host_staged"):
+    for res in _run(tmp_path, 3, "", transport="host_staged", client_env={"HOST_STAGED": "1"}):
         assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
         assert set(res["seen"]) <= {"ar_ring", "ag_ring"}
 

@@ -218,6 +218,10 @@ def test_functional_ops_over_a_communicator(service):
         z = ops.all_reduce(c, x, op="max")                       # in place: returns the input tensor
         assert z is x
         g = ops.all_gather(c, x[:16], d.tensor(torch.float32, 16 * n), algo="ag_pull")
+        x[:3 * n] = torch.arange(3 * n).float() + r
+        rs = ops.reduce_scatter(c, x[:3 * n], b.tensor(torch.float32, 3, offset_bytes=4000), op="avg")
+        assert torch.allclose(rs, torch.arange(3 * n).float()[3 * r:3 * r + 3] + 1.0)    # mean of r over 3 ranks = 1
+        x[:3 * n] = 3.0
         out = (y.clone(), x.clone(), g.clone())
         c.destroy()
         return out
