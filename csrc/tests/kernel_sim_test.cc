@@ -22,6 +22,7 @@
 #define MCCS_UNTYPED_KERNELS 1
 #include "../kernels/batch.cuh"
 #include "../kernels/hybrid.cuh"
+#include "../kernels/scatter.cuh"
 
 using namespace mccs;
 using namespace mccs::dev;
@@ -215,6 +216,62 @@ void allreduce_case(World& w, int variant, int op, size_t count, int ctas, int t
   // every rank holds bit-identical results
   for (int r = 1; r < n; r++) bad += memcmp(a.recv[0], a.recv[r], count * sizeof(T)) != 0;
   for (int r = 0; r < n; r++) bad += w.status[(size_t)r]->error != 0;
+  if (bad) fprintf(stderr, "FAILED %s (n=%d count=%zu ctas=%d emulated=%d offset=%zu in_place=%d)\n", what, n, count, ctas,
+                   (int)emulated, offset, (int)in_place);
+  CHECK(bad == 0);
+}
+
+// One ReduceScatter: rank r must end up with the reduction of block r, and nothing else of
+// anybody's buffers may change (apart from the rank's own block when it works in place).
+template <typename T, typename Op>
+void reduce_scatter_case(World& w, int variant, int op, size_t count, int ctas, int threads, bool emulated, size_t offset,
+                         bool in_place, const char* what) {
+  const int n = w.n;
+  Buffers<T> b(n, count * (size_t)n, offset);
+  std::mt19937 rng((unsigned)(count * 13 + (size_t)variant * 5 + (size_t)n));
+  std::vector<std::vector<double>> in((size_t)n, std::vector<double>(count * (size_t)n));
+  for (int r = 0; r < n; r++)
+    for (size_t i = 0; i < count * (size_t)n; i++) {
+      double v = (double)((int)(rng() % 17) - 8);
+      if (std::is_same<T, uint8_t>::value) v = (double)(rng() % 9);   // no wrap-around in the sum
+      b.send(r)[i] = Dt<T>::to(v);
+      in[(size_t)r][i] = Dt<T>::from(b.send(r)[i]);
+    }
+  CollArgs a = w.base(Dt<T>::id, op, variant, count, emulated);
+  for (int r = 0; r < n; r++) {
+    a.send[r] = b.send(r);
+    a.recv[r] = in_place ? (void*)(b.send(r) + (size_t)r * count) : (void*)b.recv(r);
+  }
+  if (variant == kRsNvls) {
+    sim_mc_regions().clear();
+    SimMcRegion ms{0x100000000000ull, (count * (size_t)n * sizeof(T) + 15) / 16 * 16, {}};
+    for (int r = 0; r < n; r++) ms.backing.push_back((char*)a.send[r]);
+    sim_mc_regions().push_back(ms);
+    a.mc_send = (const void*)ms.base;
+  }
+  if (variant == kRsDirect) run_all(rs_direct_kernel<T, Op>, a, n, ctas, threads, emulated);
+  if constexpr (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value || std::is_same<T, __half>::value) {
+    if (variant == kRsNvls) run_all(rs_nvls_kernel<T>, a, n, ctas, threads, emulated);
+  }
+  const double tol = tolerance<T>(n);
+  int bad = 0;
+  for (int r = 0; r < n; r++) {
+    for (size_t i = 0; i < count && bad < 4; i++) {
+      std::vector<double> xs;
+      for (int q = 0; q < n; q++) xs.push_back(in[(size_t)q][(size_t)r * count + i]);
+      const double want = reduce_ref(op, xs, n);
+      const double got = Dt<T>::from(((T*)a.recv[r])[i]);
+      if (fabs(got - want) > tol + 1e-3 * fabs(want) * (tol > 0 ? 1 : 0)) {
+        if (bad++ < 3) fprintf(stderr, "  %s: rank %d elem %zu: got %g want %g\n", what, r, i, got, want);
+      }
+    }
+    // the inputs outside the rank's own block are untouched
+    for (size_t i = 0; i < count * (size_t)n; i++) {
+      if (in_place && i / count == (size_t)r) continue;
+      if (Dt<T>::from(b.send(r)[i]) != in[(size_t)r][i]) { bad++; break; }
+    }
+    bad += w.status[(size_t)r]->error != 0;
+  }
   if (bad) fprintf(stderr, "FAILED %s (n=%d count=%zu ctas=%d emulated=%d offset=%zu in_place=%d)\n", what, n, count, ctas,
                    (int)emulated, offset, (int)in_place);
   CHECK(bad == 0);
@@ -621,6 +678,19 @@ int main() {
       allreduce_case<float, OpSum>(w, kArNvlsTwo, kSumPostDiv, 1000, ctas, threads, emulated, 0, false, "nvls twoshot f32 avg");
       // several FIFO loops per channel (ring slots are 4 KiB here)
       allreduce_case<float, OpSum>(w, kArRing, kSum, 40000, ctas, threads, emulated, 0, false, "ring f32, many loops");
+      // --- ReduceScatter -----------------------------------------------------------------
+      for (size_t count : {(size_t)1, (size_t)37, (size_t)1000, (size_t)4100}) {
+        reduce_scatter_case<float, OpSum>(w, kRsDirect, kSum, count, ctas, threads, emulated, 0, false, "rs direct f32");
+        reduce_scatter_case<float, OpSum>(w, kRsDirect, kSum, count, ctas, threads, emulated, 0, true, "rs direct f32 in place");
+        if (count % 4 == 0) reduce_scatter_case<float, OpSum>(w, kRsNvls, kSum, count, ctas, threads, emulated, 0, false, "rs nvls f32");
+      }
+      reduce_scatter_case<__nv_bfloat16, OpSum>(w, kRsDirect, kSum, 3001, ctas, threads, emulated, 3, false, "rs direct bf16 +6B");
+      reduce_scatter_case<__nv_bfloat16, OpSum>(w, kRsNvls, kSumPostDiv, 2048, ctas, threads, emulated, 0, true, "rs nvls bf16 avg in place");
+      reduce_scatter_case<__half, OpSum>(w, kRsNvls, kSum, 1024, ctas, threads, emulated, 0, false, "rs nvls f16");
+      reduce_scatter_case<int32_t, OpMax>(w, kRsDirect, kMax, 777, ctas, threads, emulated, 1, false, "rs direct i32 max +4B");
+      reduce_scatter_case<double, OpSum>(w, kRsDirect, kSum, 99, ctas, threads, emulated, 0, false, "rs direct f64");
+      reduce_scatter_case<float, OpSum>(w, kRsDirect, kSumPostDiv, 1000, ctas, threads, emulated, 0, false, "rs direct f32 avg");
+      reduce_scatter_case<uint8_t, OpSum>(w, kRsDirect, kSum, 5000, ctas, threads, emulated, 0, true, "rs direct u8 in place");
       // --- AllGather ---------------------------------------------------------------------
       for (size_t bytes : {(size_t)16, (size_t)1000, (size_t)4112}) {
         allgather_case(w, kAgPull, bytes, ctas, threads, emulated, 0, false, "ag pull");
