@@ -61,6 +61,26 @@ def allgather(algo, nbytes):
     if not torch.equal(out.cpu(), torch.cat(xs)):
         bad.append(("allgather", algo, nbytes))
     seen.add(comm.last_plan()[0])
+def reduce_scatter(algo, dname, count, in_place=False):
+    global salt
+    salt += 1
+    dt = DT[dname]
+    xs = inputs(dt, count * n, salt)
+    s = send.tensor(dt, count * n); s.copy_(xs[rank])
+    d = s[rank * count:(rank + 1) * count] if in_place else recv.tensor(dt, count)
+    comm.reduce_scatter(s, d, algo=algo)
+    want = torch.stack([x.double() for x in xs]).sum(0)[rank * count:(rank + 1) * count]
+    tol = {"bf16": 0.05 * n, "f16": 0.01 * n}.get(dname, 1e-6)
+    if not torch.allclose(d.double().cpu(), want, rtol=0, atol=tol):
+        bad.append(("reduce_scatter", algo, dname, count, in_place))
+    seen.add(comm.last_plan()[0])
+if n > 1:
+    for dname, count in (("f32", 1), ("f32", 4096), ("bf16", 3001), ("i32", 257), ("bf16", 1 << 18)):
+        reduce_scatter("rs_direct", dname, count)
+    reduce_scatter("auto", "f32", 8192, in_place=True)
+    if os.environ.get("NVLS") == "1":
+        for dname, count in (("f32", 4096), ("bf16", 1 << 18)):
+            reduce_scatter("rs_nvls", dname, count)
 ar = ("ar_oneshot", "ar_twoshot", "ar_ring", "auto") if n > 1 else ("auto",)
 ag = ("ag_pull", "ag_push", "ag_ring", "auto") if n > 1 else ("auto",)
 for algo in ar:
