@@ -33,6 +33,7 @@ from mccs_b200.utils.timing import bus_factor
 
 AR_ALGOS = ["ar_oneshot", "ar_twoshot", "ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid", "ar_ring"]
 AG_ALGOS = ["ag_pull", "ag_push", "ag_nvls", "ag_ring"]
+RS_ALGOS = ["rs_direct", "rs_nvls"]
 DTYPES = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
 
 
@@ -173,41 +174,51 @@ def main() -> int:
     best: Dict[Tuple[str, int], Tuple[float, str, int]] = {}
     for coll in colls:
         is_ar = coll == "allreduce"
-        algos = [a for a in (AR_ALGOS if is_ar else AG_ALGOS) if nvls or ("nvls" not in a and a != "ar_hybrid")]
+        is_rs = coll == "reducescatter"
+        algos = [a for a in (AR_ALGOS if is_ar else RS_ALGOS if is_rs else AG_ALGOS) if nvls or ("nvls" not in a and a != "ar_hybrid")]
         if args.algos:
             algos = [a for a in algos if a in args.algos.split(",")]
         if args.mode == "final":
             algos = ["auto"] + ([] if args.auto_only else algos)
         if n == 1:
             algos = ["auto"]
-        for dname in (args.dtypes.split(",") if is_ar else ["bytes"]):
+        for dname in (args.dtypes.split(",") if is_ar or is_rs else ["bytes"]):
             tdtype = DTYPES.get(dname, torch.uint8)
             esz = torch.empty((), dtype=tdtype).element_size()
             for size in sizes:
                 # `size` is the message size nccl-tests reports: the reduced buffer for
-                # all-reduce, the total gathered bytes for all-gather.
+                # all-reduce, the total gathered bytes for all-gather, the whole input of a
+                # rank for reduce-scatter.
                 per_rank = size if is_ar else size // n
                 per_rank = per_rank // 16 * 16
                 if per_rank == 0:
                     continue
                 total = per_rank if is_ar else per_rank * n
                 count = per_rank // esz
-                send = send_buf.tensor(tdtype, count)
+                send = send_buf.tensor(tdtype, count * n if is_rs else count)
                 if is_ar:
                     recv = send if args.in_place else recv_buf.tensor(tdtype, count)
+                elif is_rs:
+                    recv = send[rank * count:(rank + 1) * count] if args.in_place else recv_buf.tensor(tdtype, count)
                 else:
                     recv = recv_buf.tensor(tdtype, count * n)
                 if tdtype.is_floating_point:
                     g = torch.Generator(device=tdev).manual_seed(rank)
-                    send.copy_((torch.rand(min(count, 1 << 22), generator=g, device=tdev) * 2 - 1)
-                               .to(tdtype).repeat((count + (1 << 22) - 1) // (1 << 22))[:count])
-                if n > 1 and not args.no_nccl:
+                    ne = send.numel()
+                    send.copy_((torch.rand(min(ne, 1 << 22), generator=g, device=tdev) * 2 - 1)
+                               .to(tdtype).repeat((ne + (1 << 22) - 1) // (1 << 22))[:ne])
+                if n > 1 and not args.no_nccl and (cuda or not is_rs):   # gloo (the CPU dry run) has no reduce-scatter
                     src = send
                     if is_ar:
                         dst = torch.empty_like(src)
 
                         def nccl_fn():
                             dist.all_reduce(dst)
+                    elif is_rs:
+                        dst = torch.empty(count, dtype=tdtype, device=tdev)
+
+                        def nccl_fn():
+                            dist.reduce_scatter_tensor(dst, src)
                     else:
                         dst = torch.empty(count * n, dtype=tdtype, device=tdev)
 
@@ -229,6 +240,8 @@ def main() -> int:
                         def fn():
                             if is_ar:
                                 comm.all_reduce(send, recv, algo=algo)
+                            elif is_rs:
+                                comm.reduce_scatter(send, recv, algo=algo)
                             else:
                                 comm.all_gather(send, recv, algo=algo)
                         try:
@@ -265,7 +278,7 @@ def main() -> int:
             for r in rows:
                 w.writerow(r)
         if args.tuning and args.mode == "tune":
-            table: Dict[str, Dict[str, list]] = {"allreduce": {}, "allgather": {}}
+            table: Dict[str, Dict[str, list]] = {"allreduce": {}, "allgather": {}, "reducescatter": {}}
             for coll in colls:
                 ent = sorted((b, v) for (c, b), v in best.items() if c == coll)
                 table[coll][str(n)] = [[b, v[1], v[2], 512] for b, v in ent]
@@ -274,7 +287,7 @@ def main() -> int:
             with open(args.tuning, "w") as f:
                 json.dump(table, f, indent=1)
             if args.merge_into:
-                merged = {"allreduce": {}, "allgather": {}}
+                merged = {"allreduce": {}, "allgather": {}, "reducescatter": {}}
                 if os.path.exists(args.merge_into):
                     with open(args.merge_into) as f:
                         merged.update(json.load(f))
