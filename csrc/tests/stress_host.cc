@@ -93,6 +93,12 @@ void run_rank(const App& app, int rank) {
     memset(gath + 1024 * (size_t)rank, rank + 1, 1024);
     EXPECT(mccsAllGather(comm, gath + 1024 * (size_t)rank, gath, 1024, nullptr) == mccsSuccess);
     for (int r = 0; r < n; r++) EXPECT(gath[1024 * (size_t)r + 1023] == (uint8_t)(r + 1));
+    // reduce-scatter of the first n * 512 elements: block `rank` of the sum lands in recv
+    if (it % 3 == 0 && (size_t)n * 512 <= count) {
+      EXPECT(mccsReduceScatter(comm, send, recv, 512, mccsFloat32, mccsSum, nullptr) == mccsSuccess);
+      const size_t at = (size_t)rank * 512 + 511;
+      EXPECT(recv[511] == (float)(n * (n + 1) / 2) + (float)n * ((float)(at % 7) + (float)it));
+    }
   }
   mccsCommInfo_t info;
   EXPECT(mccsCommQuery(comm, &info) == mccsSuccess);
