@@ -9,7 +9,8 @@ collectives of one variant, then exit.
 The buffers are larger than the L2 (126 MB) by default, so DRAM counters mean
 something, and stay within a few GB in total. ``--fuse K`` splits the message into K
 independent AllReduces issued as one group with fused launches switched on, which is
-how the fused kernels (``ar_twoshot_batch``) are reached. Rank 0 checks the last result
+how the fused kernels (``ar_twoshot_batch``) are reached; ``--algo rs_direct`` runs a
+ReduceScatter of the ``--mb`` input. Rank 0 checks the last result
 against a plain fp32 sum (or the concatenation) of the ranks' inputs.
 """
 from __future__ import annotations
@@ -44,7 +45,9 @@ def main() -> int:
     nbytes = int(a.mb * 1024 * 1024)
     esz = torch.empty((), dtype=dtype).element_size()
     is_ar = a.algo.startswith("ar_") or a.algo == "auto"
+    is_rs = a.algo.startswith("rs_")      # --mb is then the whole input of a rank; each rank keeps 1/ranks of it
     count = nbytes // esz
+    block = count // n // 64 * 64         # reduce-scatter: elements per block, 128-byte multiples
     errors = []
     ready = threading.Barrier(n)
     inputs = [None] * n
@@ -56,11 +59,11 @@ def main() -> int:
             torch.cuda.set_device(0)
             torch.cuda.set_stream(torch.cuda.Stream())
             send = M.Buffer(nbytes, 0)
-            recv = M.Buffer(nbytes if is_ar else nbytes * n, 0)
+            recv = M.Buffer(nbytes if is_ar or is_rs else nbytes * n, 0)
             s = send.tensor(dtype, count)
             s.copy_(((torch.rand(min(count, 1 << 20)) * 2 - 1).to(dtype)).repeat((count + (1 << 20) - 1) // (1 << 20))[:count])
             inputs[r] = s
-            r_all = recv.tensor(dtype, count if is_ar else count * n)
+            r_all = recv.tensor(dtype, count if is_ar or is_rs else count * n)
             comm = M.Communicator(77, r, n, device=0)
             if a.ctas and r == 0:
                 M.reconfigure(M.daemon.embedded_admin_port(), [{"communicator_id": 77, "ctas": a.ctas}])
@@ -72,6 +75,8 @@ def main() -> int:
                             comm.all_reduce(s[k * part:(k + 1) * part], r_all[k * part:(k + 1) * part], algo=a.algo)
                 elif is_ar:
                     comm.all_reduce(s, r_all, algo=a.algo)
+                elif is_rs:
+                    comm.reduce_scatter(s[:block * n], r_all[:block], algo=a.algo)
                 else:
                     comm.all_gather(s, r_all, algo=a.algo)
             torch.cuda.synchronize()
@@ -79,7 +84,12 @@ def main() -> int:
             if r == 0:
                 print("plan:", comm.last_plan(), flush=True)
                 m = min(part * parts if is_ar else count, 1 << 22)   # compare the head of the buffers
-                if is_ar:
+                if is_rs:
+                    m = min(block, 1 << 22)
+                    want = torch.stack([x[:m].float() for x in inputs]).sum(0)       # rank 0 keeps block 0
+                    tol = 1e-5 if dtype == torch.float32 else 2e-2
+                    good = bool(torch.allclose(r_all[:m].float(), want, rtol=tol, atol=tol * n))
+                elif is_ar:
                     want = torch.stack([x[:m].float() for x in inputs]).sum(0)
                     tol = 1e-5 if dtype == torch.float32 else 2e-2
                     good = bool(torch.allclose(r_all[:m].float(), want, rtol=tol, atol=tol * n))
