@@ -76,7 +76,7 @@ def summarise(events: List[dict], comm_id: int, skip: int) -> Dict[str, dict]:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--bytes", default="64K")
-    ap.add_argument("--coll", default="allreduce", choices=["allreduce", "allgather"])
+    ap.add_argument("--coll", default="allreduce", choices=["allreduce", "allgather", "reducescatter"])
     ap.add_argument("--algo", default="auto")
     ap.add_argument("--iters", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=50)
@@ -116,18 +116,24 @@ def main() -> int:
 
     nbytes = parse_size(args.bytes)
     is_ar = args.coll == "allreduce"
-    count = nbytes // 4 if is_ar else nbytes // n
+    is_rs = args.coll == "reducescatter"     # --bytes is then the whole input of a rank
+    count = nbytes // 4 if is_ar else max(nbytes // 4 // n, 1) if is_rs else nbytes // n
     send = M.Buffer(max(nbytes, 16), dev)
     recv = M.Buffer(max(nbytes, 16), dev)
     comm_id = 0x1A7
     comm = M.Communicator(comm_id, rank, n, device=dev)
-    s = send.tensor(torch.float32, count) if is_ar else send.tensor(torch.uint8, count)
-    r = recv.tensor(torch.float32, count) if is_ar else recv.tensor(torch.uint8, count * n)
+    if is_rs:
+        s, r = send.tensor(torch.float32, count * n), recv.tensor(torch.float32, count)
+    else:
+        s = send.tensor(torch.float32, count) if is_ar else send.tensor(torch.uint8, count)
+        r = recv.tensor(torch.float32, count) if is_ar else recv.tensor(torch.uint8, count * n)
     s.fill_(1)
 
     def call():
         if is_ar:
             comm.all_reduce(s, r, algo=args.algo)
+        elif is_rs:
+            comm.reduce_scatter(s, r, algo=args.algo)
         else:
             comm.all_gather(s, r, algo=args.algo)
 
