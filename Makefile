@@ -25,7 +25,7 @@ SHIM_SRCS := csrc/shim/libmccs.cc csrc/common/value.cc csrc/common/log.cc csrc/i
 SHIM_OBJS := $(patsubst csrc/%.cc,$(OBJ)/%.o,$(SHIM_SRCS))
 HDRS := $(wildcard csrc/*/*.h csrc/*/*.cuh)
 
-APPS := allreduce_bench allgather_bench allreduce_proto allgather_proto traffic_gen ring_config mccs_hello
+APPS := allreduce_bench allgather_bench allreduce_proto allgather_proto reducescatter_proto traffic_gen ring_config mccs_hello
 APP_BINS := $(addprefix $(OUT)/,$(APPS))
 
 all: $(OUT)/libmccs_daemon.so $(OUT)/libmccs.so $(OUT)/libmccs_kernels.so $(OUT)/mccsd $(OUT)/libmccs_preload.so $(APP_BINS) $(OUT)/host_tests

@@ -14,7 +14,7 @@ def pytest_configure(config):
 
 def _native_ready() -> bool:
     d = os.path.join(REPO, "mccs_b200", "_native")
-    return all(os.path.exists(os.path.join(d, f)) for f in ("libmccs.so", "libmccs_daemon.so", "libmccs_kernels.so", "mccsd", "host_tests"))
+    return all(os.path.exists(os.path.join(d, f)) for f in ("libmccs.so", "libmccs_daemon.so", "libmccs_kernels.so", "mccsd", "host_tests", "reducescatter_proto"))
 
 
 @pytest.fixture(scope="session", autouse=True)

@@ -308,6 +308,8 @@ def test_example_apps_end_to_end(private_daemon, tmp_path):
     assert all("passed" in o[0] for o in outs)
     outs = run_ranks_app("allgather_proto", 3, ["--size", "65536", "--communicator", "43"])
     assert all("passed" in o[0] for o in outs)
+    outs = run_ranks_app("reducescatter_proto", 3, ["--size", "49152", "--communicator", "48"])
+    assert all("passed" in o[0] for o in outs)
     outs = run_ranks_app("allreduce_bench", 2, ["--size", "262144", "--communicator", "44", "--round", "5", "--epoch", "2"])
     assert outs[0][0].count("Algorithm bandwidth") == 2 and "Bus bandwidth" in outs[0][0]
     outs = run_ranks_app("allgather_bench", 2, ["--size", "65536", "--communicator", "45", "--round", "5"])
