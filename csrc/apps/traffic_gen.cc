@@ -5,7 +5,8 @@
 // compute_interval in microseconds).
 //   traffic_gen --rank R --config trace.toml [--iters 20] [--save-path times.csv]
 //               [--verbose] [--name tag] [--root-addr A]
-// Each iteration spins for the compute interval, issues the fp16 AllReduce or the
+// Each iteration spins for the compute interval, issues the fp16 AllReduce (or, beyond the
+// reference's trace types, the fp16 ReduceScatter, type "reduce_scatter") or the
 // AllGather of `size` bytes and synchronises the stream; rank 0 prints the total run
 // time (the job completion time of the reference's figure 9) and can save the
 // per-iteration times; the first 20 iterations are dropped from the statistics.
@@ -19,7 +20,7 @@
 #include "../common/value.h"
 #include "app_common.h"
 
-struct Trace { size_t size; bool all_reduce; uint64_t compute_us; };
+struct Trace { size_t size; bool all_reduce; bool reduce_scatter = false; uint64_t compute_us; };
 
 int main(int argc, char** argv) {
   const char* usage = "usage: traffic_gen --rank R --config trace.toml [--iters 20] [--save-path f.csv] [--verbose] [--name X]";
@@ -46,12 +47,13 @@ int main(int argc, char** argv) {
     tr.size = (size_t)(t.has("size") ? t["size"] : t["message_size"]).as_int();
     const std::string type = (t.has("type") ? t["type"] : t["op_type"]).as_string();
     tr.all_reduce = type == "all_reduce" || type == "AllReduce";
+    tr.reduce_scatter = type == "reduce_scatter" || type == "ReduceScatter";   // `size` = the whole input of a rank
     tr.compute_us = (uint64_t)t["compute_interval"].as_int();
     traces.push_back(tr);
   }
   if (traces.empty()) { fprintf(stderr, "no traces in the configuration\n"); return 2; }
   size_t buffer = 0;
-  for (const Trace& t : traces) buffer = std::max(buffer, t.all_reduce ? t.size : t.size * (size_t)n);
+  for (const Trace& t : traces) buffer = std::max(buffer, t.all_reduce || t.reduce_scatter ? t.size : t.size * (size_t)n);
   buffer = (buffer + (size_t)n - 1) / (size_t)n * (size_t)n;
   buffer = (buffer + 255) / 256 * 256;
 
@@ -81,6 +83,10 @@ int main(int argc, char** argv) {
       app::spin_sleep_us(t.compute_us);
       if (t.all_reduce) {
         app::check(mccsAllReduce(comm, buf, buf, t.size / 2, mccsFloat16, mccsSum, nullptr), "mccsAllReduce");
+      } else if (t.reduce_scatter) {
+        const size_t block = t.size / 2 / (size_t)n / 8 * 8;   // fp16 elements per block, 16-byte multiples
+        if (block)
+          app::check(mccsReduceScatter(comm, buf, buf + (size_t)rank * block * 2, block, mccsFloat16, mccsSum, nullptr), "mccsReduceScatter");
       } else {
         const size_t sz = t.size / 16 * 16;
         app::check(mccsAllGather(comm, buf + (size_t)rank * sz, buf, sz, nullptr), "mccsAllGather");

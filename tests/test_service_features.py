@@ -317,7 +317,8 @@ def test_example_apps_end_to_end(private_daemon, tmp_path):
 
     trace = tmp_path / "trace.toml"
     trace.write_text('communicator_id = 200\ncuda_devices = [0, 1]\n[[traces]]\nsize = 65536\ntype = "all_reduce"\n'
-                     'compute_interval = 500\n[[traces]]\nsize = 4096\ntype = "all_gather"\ncompute_interval = 100\n')
+                     'compute_interval = 500\n[[traces]]\nsize = 4096\ntype = "all_gather"\ncompute_interval = 100\n'
+                     '[[traces]]\nsize = 32768\ntype = "reduce_scatter"\ncompute_interval = 100\n')
     csv = tmp_path / "times.csv"
     procs = [subprocess.Popen([os.path.join(NATIVE, "traffic_gen"), "--rank", str(rk), "--config", str(trace), "--iters", "30",
                                "--save-path", str(csv), "--name", "vgg"], env=env, stdout=subprocess.PIPE,
