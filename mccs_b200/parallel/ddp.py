@@ -21,7 +21,7 @@ from ..client import Buffer, Communicator, backend
 
 
 class _Bucket:
-    def __init__(self, params: List[torch.nn.Parameter], dtype: torch.dtype, device: int, cuda: bool):
+    def __init__(self, params: List[torch.nn.Parameter], dtype: torch.dtype, device: int, cuda: bool, multiple: int = 1):
         self.params = params
         self.numel = sum(p.numel() for p in params)
         esz = torch.empty((), dtype=dtype).element_size()
@@ -31,7 +31,7 @@ class _Bucket:
         for p in params:
             self.offsets.append(off)
             off += (p.numel() * esz + 255) // 256 * 256 // esz
-        self.padded = off
+        self.padded = (off + multiple - 1) // multiple * multiple   # sharded subclasses cut the bucket into equal parts
         self.buffer = Buffer(max(self.padded * esz, 256), device)
         self.flat = self.buffer.tensor(dtype, self.padded)
         self.flat.zero_()
@@ -67,13 +67,13 @@ class DataParallel:
         for p in reversed(params):
             nbytes = p.numel() * p.element_size()
             if cur and (cur_bytes + nbytes > limit or p.dtype != cur_dtype):
-                self.buckets.append(_Bucket(cur, cur_dtype, self._device, self._cuda))
+                self.buckets.append(_Bucket(cur, cur_dtype, self._device, self._cuda, self._bucket_multiple()))
                 cur, cur_bytes = [], 0
             cur.append(p)
             cur_bytes += nbytes
             cur_dtype = p.dtype
         if cur:
-            self.buckets.append(_Bucket(cur, cur_dtype, self._device, self._cuda))
+            self.buckets.append(_Bucket(cur, cur_dtype, self._device, self._cuda, self._bucket_multiple()))
         self._launched = 0
         # Bucket reductions are issued from a side stream and only their sum total is
         # awaited, once, at the end of backward: no per-bucket wait is queued anywhere.
@@ -83,6 +83,10 @@ class DataParallel:
                 # same strides as the parameter (channels-last weights keep that layout)
                 p.grad = b.flat[off:off + p.numel()].as_strided(p.shape, p.stride())
                 p.register_post_accumulate_grad_hook(self._make_hook(b))
+
+    def _bucket_multiple(self) -> int:
+        """Element count every bucket is padded to a multiple of."""
+        return 1
 
     # -- parameter broadcast (rank 0's values) through an all-gather ----------------
     def _broadcast(self, params: Iterable[torch.nn.Parameter]) -> None:

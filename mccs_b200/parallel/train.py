@@ -48,6 +48,9 @@ def main() -> int:
                     help="cap the CTAs of this job's collective kernels (a QoS quota set through the admin "
                          "endpoint), leaving the other SMs to backward; 0 = the planner's choice")
     ap.add_argument("--admin-port", type=int, default=0, help="admin port of a daemon that is already running")
+    ap.add_argument("--shard-optimizer", action="store_true",
+                    help="ZeRO stage 1 over the service's ReduceScatter: reduce-scattered gradients, 1/n of the optimizer "
+                         "state per rank, updated parameters all-gathered (mccs backend; not with --save/--resume)")
     ap.add_argument("--save", default="", help="after the run rank 0 writes model + optimizer state here (torch.save)")
     ap.add_argument("--resume", default="", help="load model + optimizer state written by --save before training")
     args = ap.parse_args()
@@ -108,8 +111,14 @@ def main() -> int:
         if args.start_daemon or args.control:
             M.init(prefix + "/control.sock" if not prefix.endswith(".sock") else prefix)
         comm = M.Communicator(args.comm_id, rank, world, device=dev_index if cuda else rank)
-        from mccs_b200.parallel import DataParallel
-        ddp = DataParallel(model, comm, bucket_mb=args.bucket_mb, broadcast_parameters=world > 1)
+        from mccs_b200.parallel import DataParallel, ShardedDataParallel
+        if args.shard_optimizer:
+            if args.save or args.resume:
+                raise SystemExit("--shard-optimizer keeps 1/n of the optimizer state per rank: no --save/--resume")
+            ddp = ShardedDataParallel(model, comm, bucket_mb=args.bucket_mb, broadcast_parameters=world > 1)
+            opt = ddp.make_optimizer(torch.optim.SGD, lr=args.lr, momentum=0.9)
+        else:
+            ddp = DataParallel(model, comm, bucket_mb=args.bucket_mb, broadcast_parameters=world > 1)
         fwd = model
     elif args.backend == "nccl" and world > 1:
         fwd = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev_index] if cuda else None,
@@ -144,7 +153,10 @@ def main() -> int:
         loss.backward()
         if ddp is not None:
             ddp.finish()
-        opt.step()
+        if args.shard_optimizer and ddp is not None:
+            ddp.step(opt)
+        else:
+            opt.step()
         return loss
 
     losses = []

@@ -129,6 +129,57 @@ def _run_workers(code: str, n: int, control: str, extra_env=None):
 def test_process_group_two_processes(standalone_daemon):
     _run_workers(WORKER, 2, standalone_daemon.control)
 
+ZERO_WORKER = r"""
+import os, sys, torch
+import mccs_b200 as M
+from mccs_b200 import models
+from mccs_b200.parallel import ShardedDataParallel
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"])
+torch.manual_seed(0)
+m = models.build("gpt2-tiny")
+total = sum(p.numel() for p in m.parameters())
+comm = M.Communicator(78, rank, n, device=rank)
+ddp = ShardedDataParallel(m, comm, bucket_mb=0.05)
+opt = ddp.make_optimizer(torch.optim.SGD, lr=0.1, momentum=0.9)
+ids = torch.randint(0, 512, (4, 33), generator=torch.Generator().manual_seed(rank))
+for it in range(3):
+    ddp.zero_grad()
+    loss = m(ids[:, :-1], ids[:, 1:])
+    loss.backward()
+    ddp.finish()
+    ddp.step(opt)
+torch.save([p.detach().clone() for p in m.parameters()], os.environ["OUT"] + f".{rank}")
+# the optimizer of this rank holds momentum for about 1/n of the model only
+state = sum(v.numel() for st in opt.state.values() for v in st.values() if torch.is_tensor(v))
+assert len(ddp.buckets) > 3 and state == ddp.optimizer_state_elements() and state < total * (1.0 / n + 0.2)
+assert comm.last_plan()[0] in ("ag_pull", "ag_push", "ag_ring", "ag_nvls")
+ddp.release(); comm.destroy(); M.finalize()
+print("ok", flush=True)
+"""
+
+
+def test_sharded_data_parallel_matches_single_process(standalone_daemon, tmp_path):
+    """ZeRO-1 over the service's ReduceScatter: reduce-scattered gradients, optimizer state for
+    1/n of the model per rank, updated parts all-gathered: same parameters as momentum SGD in
+    one process on the combined batch, on every rank."""
+    import torch
+    from mccs_b200 import models
+    out = str(tmp_path / "params")
+    n = 2
+    _run_workers(ZERO_WORKER, n, standalone_daemon.control, {"OUT": out})
+    torch.manual_seed(0)
+    m = models.build("gpt2-tiny")
+    opt = torch.optim.SGD(m.parameters(), lr=0.1, momentum=0.9)
+    batches = [torch.randint(0, 512, (4, 33), generator=torch.Generator().manual_seed(r)) for r in range(n)]
+    for _ in range(3):
+        opt.zero_grad()
+        (sum(m(b[:, :-1], b[:, 1:]) for b in batches) / n).backward()
+        opt.step()
+    for r in range(n):
+        got = torch.load(out + f".{r}")
+        for a, b in zip(got, m.parameters()):
+            assert torch.allclose(a, b.detach(), rtol=1e-4, atol=1e-5)
+
 
 def test_data_parallel_matches_single_process(standalone_daemon, tmp_path):
     import torch
