@@ -52,6 +52,8 @@ enum Status : int32_t {
   kErrUnsupported = -9,
   kErrPeerLost = -10,       // another rank of the communicator went away
   kErrInternal = -11,
+  kErrNotConnected = -12,   // client side only: the daemon went away
+  kErrBusy = -13,           // memory is still named by a collective that has not been launched
 };
 
 enum Backend : uint32_t { kBackendHost = 0, kBackendCuda = 1 };

@@ -134,6 +134,7 @@ void Daemon::stop() {
     std::unique_lock<std::shared_mutex> al(alloc_mu_);
     for (auto& kv : allocs_) backend_->release(&kv.second);
     allocs_.clear();
+    alloc_use_.clear();
   }
   if (listen_fd_ >= 0) { close(listen_fd_); listen_fd_ = -1; unlink(control_path_.c_str()); }
   if (admin_fd_ >= 0) { close(admin_fd_); admin_fd_ = -1; }
@@ -293,6 +294,7 @@ void Daemon::on_malloc(Session& s, const proto::MallocReq& m) {
     std::unique_lock<std::shared_mutex> al(alloc_mu_);
     a.id = next_mem_id_++;
     allocs_[a.id] = a;
+    alloc_use_[a.id];
   }
   s.allocs.insert(a.id);
   r.malloc_reply.mem_id = a.id;
@@ -351,6 +353,28 @@ void Daemon::on_free(Session& s, const proto::FreeReq& m) {
     reply(s, r, sizeof(proto::FreeReply));
     return;
   }
+  {
+    // A collective that was posted but has not been launched on every rank still carries
+    // this allocation's address (it may be waiting for peers, for admission, behind a
+    // pause or behind the queue bound). Releasing the memory now would turn its launch
+    // into a device fault inside the daemon, so the free is refused instead; the client
+    // library drains its communicators first and never gets here with work in flight.
+    // From here on the id resolves for nobody, so no new request can name it.
+    std::unique_lock<std::shared_mutex> al(alloc_mu_);
+    auto ut = alloc_use_.find(m.mem_id);
+    if (ut != alloc_use_.end()) {
+      if (ut->second.busy.load(std::memory_order_acquire) > 0) {
+        al.unlock();
+        LOG_WARN("client %llu: free of mem %llu refused, a queued collective still names it", (unsigned long long)s.id,
+                 (unsigned long long)m.mem_id);
+        r.h.status = proto::kErrBusy;
+        reply(s, r, sizeof(proto::FreeReply));
+        return;
+      }
+      ut->second.dying = true;
+    }
+  }
+  // Everything that named the allocation is on a stream by now: wait for it.
   quiesce_session_streams(s);
   drop_mc_regions_using(m.mem_id);
   {
@@ -360,6 +384,7 @@ void Daemon::on_free(Session& s, const proto::FreeReq& m) {
       backend_->release(&it->second);
       allocs_.erase(it);
     }
+    alloc_use_.erase(m.mem_id);
   }
   s.allocs.erase(m.mem_id);
   reply(s, r, sizeof(proto::FreeReply));
@@ -370,17 +395,38 @@ const Allocation* Daemon::find_alloc_locked(uint64_t mem_id) const {
   return it == allocs_.end() ? nullptr : &it->second;
 }
 
-bool Daemon::translate(uint64_t mem_id, uint64_t off, uint64_t bytes, uint64_t* va, int* device) {
+bool Daemon::translate(uint64_t session_id, uint64_t mem_id, uint64_t off, uint64_t bytes, uint64_t* va, int* device) {
   std::shared_lock<std::shared_mutex> al(alloc_mu_);
   auto it = allocs_.find(mem_id);
   if (it == allocs_.end()) return false;
   const Allocation& a = it->second;
+  if (a.owner_session != session_id) return false;   // another tenant's memory does not exist for this one
+  auto ut = alloc_use_.find(mem_id);
+  if (ut == alloc_use_.end() || ut->second.dying) return false;
   // Bounds-checked sub-buffer, like MccsDeviceMemoryHandle::add
   // (src/ipc/mccs/src/command.rs:44-56).
   if (off > a.size || bytes > a.size - off) return false;
   *va = a.va + off;
   *device = a.device;
+  ut->second.busy.fetch_add(1, std::memory_order_acq_rel);
   return true;
+}
+
+void Daemon::release_mem_ref(uint64_t mem_id) {
+  std::shared_lock<std::shared_mutex> al(alloc_mu_);
+  auto ut = alloc_use_.find(mem_id);
+  if (ut != alloc_use_.end()) ut->second.busy.fetch_sub(1, std::memory_order_acq_rel);
+}
+
+void Daemon::release_slot_refs(Communicator& c) {
+  for (auto& slot : c.slots)
+    for (int r = 0; r < c.nranks; r++) {
+      CollOp& op = slot.ops[r];
+      if (!op.holds_refs) continue;
+      op.holds_refs = false;
+      release_mem_ref(op.send_mem);
+      release_mem_ref(op.recv_mem);
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -750,6 +796,7 @@ void Daemon::destroy_communicator(uint32_t comm_id) {
     backend_->stream_sync(c->ranks[0]->device, c->group_stream);
     backend_->stream_destroy(c->ranks[0]->device, c->group_stream);
   }
+  release_slot_refs(*c);   // collectives that never completed on every rank
   {
     std::lock_guard<std::mutex> mg(c->mc_mu);
     for (auto& kv : c->mc_cache) backend_->mc_destroy(&kv.second);
@@ -1003,6 +1050,7 @@ void Daemon::drop_session(uint64_t session_id, const char* why) {
     std::unique_lock<std::shared_mutex> al(alloc_mu_);
     auto it = allocs_.find(mem);
     if (it != allocs_.end()) { backend_->release(&it->second); allocs_.erase(it); }
+    alloc_use_.erase(mem);
   }
   {
     std::unique_lock<std::shared_mutex> g(stream_mu_);

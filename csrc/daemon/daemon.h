@@ -79,6 +79,7 @@ struct CollOp {
   uint64_t sync_slot = 0, sync_value = 0;   // mem-op mode (see proto::SyncMode)
   uint64_t user_seq = 0;
   uint64_t t_post_us = 0;
+  bool holds_refs = false;   // send_mem and recv_mem are held busy (Daemon::translate)
 };
 
 enum SlotState : int { kSlotCollecting = 0, kSlotCollected = 1, kSlotPlanning = 2, kSlotPlanned = 3, kSlotFailed = 4 };
@@ -277,7 +278,16 @@ class Daemon {
   bool memops() const { return memops_; }
 
   // Allocation lookup for the data path (shared lock).
-  bool translate(uint64_t mem_id, uint64_t off, uint64_t bytes, uint64_t* va, int* device);
+  // Resolves (mem id, offset, length) of a request posted by `session_id` to a device
+  // address. Fails unless the allocation belongs to that session (ids are guessable, so a
+  // tenant could otherwise name another tenant's memory; the reference resolves ids in a
+  // per-client map, src/mccs/src/daemon/engine.rs:188-209) and is not being freed. On
+  // success the allocation is held busy until release_mem_ref(): a free that arrives
+  // while a posted collective has not been launched on every rank is refused.
+  bool translate(uint64_t session_id, uint64_t mem_id, uint64_t off, uint64_t bytes, uint64_t* va, int* device);
+  void release_mem_ref(uint64_t mem_id);
+  // Drops what the not yet finished collectives of a communicator still hold.
+  void release_slot_refs(Communicator& c);
   const Allocation* find_alloc_locked(uint64_t mem_id) const;   // caller holds alloc_mu_ (shared)
   std::shared_mutex& alloc_mutex() { return alloc_mu_; }
   void* lookup_stream_event(uint64_t session_id, uint64_t stream_id);
@@ -342,6 +352,8 @@ class Daemon {
 
   mutable std::shared_mutex alloc_mu_;
   std::map<uint64_t, Allocation> allocs_;
+  struct AllocUse { std::atomic<int> busy{0}; bool dying = false; };
+  std::map<uint64_t, AllocUse> alloc_use_;   // same keys as allocs_, same lock
   uint64_t next_mem_id_ = 1;
 
   // registrations for the data path's stream lookup

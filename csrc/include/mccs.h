@@ -65,7 +65,8 @@ typedef enum {
   mccsUnsupported = -9,
   mccsPeerLost = -10,
   mccsInternalError = -11,
-  mccsNotConnected = -12
+  mccsNotConnected = -12,
+  mccsBusy = -13            /* mccsFree: a queued collective still names the memory */
 } mccsResult_t;
 
 /* Same numbering as the kernels' element types. The reference API exposes only

@@ -255,6 +255,73 @@ struct mccsComm {
 
 namespace {
 
+// The daemon is gone (its end of the control socket closed). In stream-memory-operation
+// mode a caller's stream may already hold a "wait until done >= n" that only the daemon
+// would have satisfied; left alone, that stream and everything queued behind it would sit
+// there until the process is killed. The semaphore page is host memory mapped in this
+// process too, so the library satisfies every such wait itself with a value above any
+// sequence number (the comparison is cyclic, hence 2^62 and not all ones) and marks the
+// communicators failed: the waits fall through, the results are undefined, and the next
+// call on each communicator reports mccsNotConnected.
+void on_daemon_lost_locked() {
+  Context& c = g_ctx;
+  c.connected = false;
+  for (mccsComm* comm : c.comms) {
+    if (!comm->sticky_error) comm->sticky_error = mccsNotConnected;
+    if (comm->sync_host)
+      __atomic_store_n((uint64_t*)comm->sync_host + proto::kSyncDoneSlot, 1ull << 62, __ATOMIC_RELEASE);
+  }
+  c.reply_cv.notify_all();
+}
+
+// For the places that notice the closed socket themselves, without the lock held.
+mccsResult_t daemon_lost() {
+  std::unique_lock<std::mutex> g(g_ctx.mu);
+  if (g_ctx.connected) on_daemon_lost_locked();
+  return mccsNotConnected;
+}
+
+// Watches the control socket for the daemon's death, because a process whose threads all
+// sit in a stream synchronisation makes no call that would notice it.
+std::atomic<bool> g_watch_stop{false};
+std::atomic<int> g_watch_generation{0};
+struct WatchStopAtExit { ~WatchStopAtExit() { g_watch_stop.store(true); } } g_watch_stop_at_exit;
+
+void* watch_daemon(void* arg) {
+  const int my_generation = (int)(intptr_t)arg;
+  for (;;) {
+    if (g_watch_stop.load() || g_watch_generation.load() != my_generation) return nullptr;
+    int fd;
+    {
+      std::unique_lock<std::mutex> g(g_ctx.mu);
+      if (!g_ctx.connected || g_ctx.fd < 0) return nullptr;
+      fd = g_ctx.fd;
+    }
+    struct pollfd pf = {fd, 0, 0};
+    const int rc = poll(&pf, 1, 100);
+    if (g_watch_stop.load() || g_watch_generation.load() != my_generation) return nullptr;
+    if (rc > 0 && (pf.revents & (POLLHUP | POLLERR | POLLNVAL))) {
+      std::unique_lock<std::mutex> g(g_ctx.mu);
+      if (g_ctx.connected && g_ctx.fd == fd && g_watch_generation.load() == my_generation) {
+        LOG_ERROR("the mccs daemon closed the connection: pending stream waits are released, communicators fail");
+        on_daemon_lost_locked();
+      }
+      return nullptr;
+    }
+  }
+}
+
+void start_daemon_watch() {
+  pthread_t t;
+  pthread_attr_t attr;
+  pthread_attr_init(&attr);
+  pthread_attr_setdetachstate(&attr, PTHREAD_CREATE_DETACHED);
+  const int generation = g_watch_generation.fetch_add(1) + 1;
+  if (pthread_create(&t, &attr, watch_daemon, (void*)(intptr_t)generation) != 0)
+    LOG_WARN("could not start the daemon watch thread: a daemon that dies will only be noticed by the next call");
+  pthread_attr_destroy(&attr);
+}
+
 std::string default_control_path() {
   const char* direct = getenv("MCCS_CONTROL");
   if (direct && direct[0] == '/') return direct;
@@ -309,7 +376,7 @@ mccsResult_t roundtrip(std::unique_lock<std::mutex>& lk, proto::AnyMsg& m, size_
     lk.lock();
     c.reader_active = false;
     if (rc > 0) {
-      if (got <= 0 && got != -EAGAIN) { c.connected = false; c.reply_cv.notify_all(); return mccsNotConnected; }
+      if (got <= 0 && got != -EAGAIN) { on_daemon_lost_locked(); return mccsNotConnected; }
       if (got >= (ssize_t)sizeof(proto::Header) && rep.msg.h.magic == proto::kMagic)
         c.replies[rep.msg.h.req_id] = rep;
     } else if (rc < 0) {
@@ -356,6 +423,7 @@ mccsResult_t ensure_connected_locked(std::unique_lock<std::mutex>& lk, const cha
   const char* to = getenv("MCCS_WC_TIMEOUT_MS");
   if (to) c.wc_timeout_ms = strtoull(to, nullptr, 10);
   c.connected = true;
+  if (!c.same_process) start_daemon_watch();   // an embedded daemon cannot die on its own
   if (c.backend == proto::kBackendCuda && !load_driver()) {
     LOG_ERROR("the daemon runs on CUDA but libcuda.so.1 cannot be loaded here");
     return mccsDeviceError;
@@ -608,7 +676,7 @@ mccsResult_t wait_completion(mccsComm* comm, proto::WorkCompletion* wc) {
       if (ms > g_ctx.wc_timeout_ms) return mccsTimeout;
       // A dead daemon never completes anything: notice the closed control connection.
       struct pollfd pf = {g_ctx.fd, 0, 0};
-      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return daemon_lost();
       if (spins > (1u << 22)) usleep(50);
     }
   }
@@ -672,7 +740,7 @@ mccsResult_t sem_wait_geq(mccsComm* comm, mccsStream_t stream, uint64_t addr, ui
         uint64_t ms = (uint64_t)(t1.tv_sec - t0.tv_sec) * 1000 + (uint64_t)((t1.tv_nsec - t0.tv_nsec) / 1000000);
         if (ms > g_ctx.wc_timeout_ms) return mccsTimeout;
         struct pollfd pf = {g_ctx.fd, 0, 0};
-        if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+        if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return daemon_lost();
         if (spins > (1u << 20)) usleep(50);
       }
     }
@@ -720,7 +788,7 @@ mccsResult_t submit_memops(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t 
     reap_completions(comm);
     if ((++spins & 0xffff) == 0) {
       struct pollfd pf = {g_ctx.fd, 0, 0};
-      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return daemon_lost();
     }
   }
   comm->memop_posted++;
@@ -861,7 +929,7 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
   while (!comm->wq.try_push(&wr)) {
     if ((++spins & 0xffff) == 0) {
       struct pollfd pf = {g_ctx.fd, 0, 0};
-      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return daemon_lost();
     }
   }
   comm->last_posted_seq = wr.user_seq;
@@ -876,7 +944,7 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
       uint64_t ms = (uint64_t)(t1.tv_sec - t0.tv_sec) * 1000 + (uint64_t)((t1.tv_nsec - t0.tv_nsec) / 1000000);
       if (ms > g_ctx.wc_timeout_ms) return mccsTimeout;
       struct pollfd pf = {g_ctx.fd, 0, 0};
-      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return daemon_lost();
       if (spins > (1u << 20)) usleep(50);
     }
   }
@@ -1083,6 +1151,7 @@ mccsResult_t mccsFinalize(void) {
   m.h.magic = proto::kMagic;
   m.h.type = proto::kGoodbye;
   ipc::uds_send(c.fd, &m, sizeof(proto::Header));
+  g_watch_generation.fetch_add(1);   // retires the watch thread of this connection
   close(c.fd);
   c.fd = -1;
   c.connected = false;
@@ -1174,16 +1243,31 @@ mccsResult_t mccsFree(void* ptr) {
   auto it = g_ctx.mem.find((uint64_t)ptr);
   if (it == g_ctx.mem.end()) return mccsNotFound;
   MemRec rec = it->second;
-  // Unmap here first, then let the daemon release the memory.
+  mccsResult_t res = mccsSuccess;
+  if (g_ctx.connected) {
+    // The daemon refuses to release memory that a collective still names which has not
+    // been launched on every rank (a peer's kernel may be about to store into it). After
+    // the flush above that can only be a matter of the other ranks' proxies catching up,
+    // so the request is repeated for a bounded time before the error is handed on.
+    for (int attempt = 0;; attempt++) {
+      proto::AnyMsg m;
+      memset(&m, 0, sizeof m);
+      m.h.type = proto::kFree;
+      m.free_req.mem_id = rec.mem_id;
+      res = roundtrip(g, m, sizeof(proto::FreeReq), proto::kFreeReply, nullptr, 60000);
+      if (res != mccsBusy || attempt >= 2000) break;
+      g.unlock();
+      usleep(1000);
+      g.lock();
+      it = g_ctx.mem.find((uint64_t)ptr);
+      if (it == g_ctx.mem.end()) return mccsNotFound;   // freed by another thread meanwhile
+    }
+    if (res == mccsBusy) return res;   // still mapped and still owned: the caller may retry
+  }
   unmap_allocation(rec);
   g_ctx.mem.erase(it);
   g_ctx.mem_base_by_id.erase(rec.mem_id);
-  if (!g_ctx.connected) return mccsSuccess;
-  proto::AnyMsg m;
-  memset(&m, 0, sizeof m);
-  m.h.type = proto::kFree;
-  m.free_req.mem_id = rec.mem_id;
-  return roundtrip(g, m, sizeof(proto::FreeReq), proto::kFreeReply, nullptr, 60000);
+  return res;
 }
 
 mccsResult_t mccsMemInfo(const void* ptr, uint64_t* mem_id, uint64_t* offset, uint64_t* alloc_size) {
@@ -1351,7 +1435,7 @@ mccsResult_t mccsCommFlush(mccsComm_t comm) {
         uint64_t ms = (uint64_t)(t1.tv_sec - t0.tv_sec) * 1000 + (uint64_t)((t1.tv_nsec - t0.tv_nsec) / 1000000);
         if (ms > g_ctx.wc_timeout_ms) return mccsTimeout;
         struct pollfd pf = {g_ctx.fd, 0, 0};
-        if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return mccsNotConnected;
+        if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return daemon_lost();
         if (spins > (1u << 20)) usleep(50);
       }
     }
@@ -1614,6 +1698,7 @@ const char* mccsGetErrorString(mccsResult_t r) {
     case mccsPeerLost: return "a peer rank went away";
     case mccsInternalError: return "internal error";
     case mccsNotConnected: return "not connected to the daemon";
+    case mccsBusy: return "memory is still named by a queued collective";
   }
   return "unknown error";
 }

@@ -85,6 +85,192 @@ uint64_t wild_u64() {
   }
 }
 
+
+// A tenant that speaks the raw protocol: one connection, its own allocations (mapped here
+// through the descriptor the host backend hands out) and communicators.
+struct RawTenant {
+  int fd = -1;
+  bool open(const std::string& path) { fd = connect_and_hello(path); return fd >= 0; }
+  bool request(proto::AnyMsg& m, size_t len, proto::AnyMsg* rep, std::vector<int>* fds) {
+    m.h.magic = proto::kMagic;
+    if (ipc::uds_send(fd, &m, len) < 0) return false;
+    if (ipc::wait_readable(fd, 5000) <= 0) return false;
+    memset(rep, 0, sizeof *rep);
+    return ipc::uds_recv(fd, rep, sizeof *rep, fds) > 0;
+  }
+  // Allocation of `bytes` on `device`; returns the id and a host mapping of the memory.
+  bool alloc(int device, size_t bytes, uint64_t* mem_id, void** host) {
+    proto::AnyMsg m, rep;
+    memset(&m, 0, sizeof m);
+    m.h.type = proto::kMalloc;
+    m.malloc_req.device = device;
+    m.malloc_req.size = bytes;
+    std::vector<int> fds;
+    if (!request(m, sizeof(proto::MallocReq), &rep, &fds) || rep.h.status != 0) return false;
+    *mem_id = rep.malloc_reply.mem_id;
+    // This test shares the daemon's process, where host-backend memory is addressable as
+    // it is; out of process the reply carries a descriptor to map.
+    if (fds.empty()) *host = (void*)rep.malloc_reply.daemon_va;
+    else *host = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
+    for (int f : fds) close(f);
+    return *host != nullptr && *host != MAP_FAILED;
+  }
+  int free_mem(uint64_t mem_id) {
+    proto::AnyMsg m, rep;
+    memset(&m, 0, sizeof m);
+    m.h.type = proto::kFree;
+    m.free_req.mem_id = mem_id;
+    std::vector<int> fds;
+    if (!request(m, sizeof(proto::FreeReq), &rep, &fds)) return -1000;
+    for (int f : fds) close(f);
+    return rep.h.status;
+  }
+  void send_comm_init(uint32_t id, int nranks, int rank, int device) {
+    proto::AnyMsg m;
+    memset(&m, 0, sizeof m);
+    m.h.magic = proto::kMagic;
+    m.h.type = proto::kCommInit;
+    m.comm_init.comm_id = id;
+    m.comm_init.nranks = nranks;
+    m.comm_init.rank = rank;
+    m.comm_init.device = device;
+    ipc::uds_send(fd, &m, sizeof(proto::CommInitReq));
+  }
+  struct Rings { uint64_t handle = 0; void* dp = nullptr; size_t bytes = 0; ipc::Ring wq, cq; };
+  bool recv_comm_init(Rings* out) {
+    proto::AnyMsg rep;
+    std::vector<int> fds;
+    if (ipc::wait_readable(fd, 5000) <= 0) return false;
+    memset(&rep, 0, sizeof rep);
+    if (ipc::uds_recv(fd, &rep, sizeof rep, &fds) <= 0 || rep.h.status != 0 || fds.empty()) return false;
+    out->handle = rep.comm_init_reply.comm_handle;
+    out->bytes = rep.comm_init_reply.dp_bytes;
+    out->dp = mmap(nullptr, out->bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[0], 0);
+    for (int f : fds) close(f);
+    if (out->dp == MAP_FAILED) return false;
+    out->wq.attach(out->dp);
+    out->cq.attach((char*)out->dp + proto::dp_wq_bytes());
+    return true;
+  }
+};
+
+proto::WorkRequest make_wr(uint64_t handle, int kind, uint64_t send_mem, uint64_t recv_mem, uint64_t count, uint64_t user_seq) {
+  proto::WorkRequest wr;
+  memset(&wr, 0, sizeof wr);
+  wr.kind = (uint32_t)kind;
+  wr.dtype = kFloat32;
+  wr.op = kSum;
+  wr.variant = kAuto;
+  wr.comm_handle = handle;
+  wr.send_mem = send_mem;
+  wr.recv_mem = recv_mem;
+  wr.count = count;
+  wr.user_seq = user_seq;
+  return wr;
+}
+
+bool wait_completion(ipc::Ring& cq, proto::WorkCompletion* wc, int ms) {
+  for (int i = 0; i < ms * 10; i++) {
+    if (cq.try_pop(wc)) return true;
+    usleep(100);
+  }
+  return false;
+}
+
+// Tenant isolation on the data path, and memory that is freed under a queued collective.
+// Returns the number of failed expectations.
+int isolation_and_busy_checks(const std::string& path) {
+  int bad = 0;
+  auto expect = [&](bool ok, const char* what) { if (!ok) { fprintf(stderr, "isolation check failed: %s\n", what); bad++; } };
+  RawTenant victim, thief;
+  if (!victim.open(path) || !thief.open(path)) { fprintf(stderr, "isolation check: cannot connect\n"); return 1; }
+  uint64_t vmem = 0, tmem = 0;
+  float *vhost = nullptr, *thost = nullptr;
+  expect(victim.alloc(0, 4096, &vmem, (void**)&vhost), "victim allocation");
+  expect(thief.alloc(0, 4096 * 2, &tmem, (void**)&thost), "thief allocation");
+  if (bad) return bad;
+  for (int i = 0; i < 1024; i++) { vhost[i] = 1000.0f + (float)i; thost[i] = -1.0f; thost[1024 + i] = -1.0f; }
+  RawTenant::Rings tr;
+  thief.send_comm_init(9400, 1, 0, 0);
+  expect(thief.recv_comm_init(&tr), "thief communicator");
+  if (bad) return bad;
+  // 1. read: AllReduce of the victim's buffer into the thief's own (a single-rank
+  //    communicator turns that into a copy); 2. write: the thief's data over the victim's;
+  // 3. the same two through AllGather. Memory ids are small consecutive numbers, so a
+  //    tenant can guess them: none of the four may be carried out.
+  struct Case { int kind; uint64_t send, recv; const char* what; } cases[] = {
+      {kAllReduce, vmem, tmem, "AllReduce reading a foreign buffer"},
+      {kAllReduce, tmem, vmem, "AllReduce writing a foreign buffer"},
+      {kAllGather, vmem, tmem, "AllGather reading a foreign buffer"},
+      {kAllGather, tmem, vmem, "AllGather writing a foreign buffer"},
+  };
+  uint64_t useq = 0;
+  for (const Case& c : cases) {
+    proto::WorkRequest wr = make_wr(tr.handle, c.kind, c.send, c.recv, c.kind == kAllGather ? 4096 : 1024, useq++);
+    expect(tr.wq.try_push(&wr), "posting");
+    proto::WorkCompletion wc;
+    memset(&wc, 0, sizeof wc);
+    expect(wait_completion(tr.cq, &wc, 5000), "a completion for the foreign request");
+    expect(wc.status != 0, c.what);
+  }
+  bool untouched = true, nothing_leaked = true;
+  for (int i = 0; i < 1024; i++) {
+    if (vhost[i] != 1000.0f + (float)i) untouched = false;
+    if (thost[i] != -1.0f) nothing_leaked = false;
+  }
+  expect(untouched, "the victim's bytes are unchanged");
+  expect(nothing_leaked, "the thief's buffer holds none of the victim's bytes");
+  // A request on its own memory still works for the same tenant.
+  {
+    proto::WorkRequest wr = make_wr(tr.handle, kAllReduce, tmem, tmem, 1024, useq++);
+    wr.recv_off = 4096;
+    tr.wq.try_push(&wr);
+    proto::WorkCompletion wc;
+    memset(&wc, 0, sizeof wc);
+    expect(wait_completion(tr.cq, &wc, 5000) && wc.status == 0, "the tenant's own request is served");
+  }
+
+  // Free under a queued collective: rank 0 of a two-rank communicator posts, rank 1 does not
+  // yet, so the request sits in its rendezvous slot with the buffer's address resolved. A
+  // raw free of that buffer must be refused; once rank 1 has joined and the collective has
+  // gone out on both ranks, the same free succeeds.
+  RawTenant peer;
+  expect(peer.open(path), "second rank connects");
+  uint64_t pmem = 0;
+  float* phost = nullptr;
+  expect(peer.alloc(1, 4096, &pmem, (void**)&phost), "second rank allocation");
+  RawTenant::Rings r0, r1;
+  victim.send_comm_init(9401, 2, 0, 0);
+  peer.send_comm_init(9401, 2, 1, 1);
+  expect(victim.recv_comm_init(&r0) && peer.recv_comm_init(&r1), "two-rank communicator");
+  if (bad) return bad;
+  for (int i = 0; i < 1024; i++) phost[i] = 1.0f;
+  proto::WorkRequest w0 = make_wr(r0.handle, kAllReduce, vmem, vmem, 1024, 0);
+  expect(r0.wq.try_push(&w0), "rank 0 posts");
+  usleep(20000);   // the proxy has taken it by now; rank 1 has not posted
+  expect(victim.free_mem(vmem) == proto::kErrBusy, "free of a buffer named by a queued collective is refused");
+  proto::WorkRequest w1 = make_wr(r1.handle, kAllReduce, pmem, pmem, 1024, 0);
+  expect(r1.wq.try_push(&w1), "rank 1 posts");
+  proto::WorkCompletion wc;
+  memset(&wc, 0, sizeof wc);
+  expect(wait_completion(r0.cq, &wc, 5000) && wc.status == 0, "the collective completes on rank 0");
+  expect(wait_completion(r1.cq, &wc, 5000) && wc.status == 0, "the collective completes on rank 1");
+  expect(vhost[5] == 1005.0f + 1.0f && phost[5] == 1005.0f + 1.0f, "its result is the sum");
+  int st = proto::kErrBusy;
+  for (int i = 0; i < 2000 && st == proto::kErrBusy; i++) { st = victim.free_mem(vmem); if (st == proto::kErrBusy) usleep(1000); }
+  expect(st == 0, "the free succeeds once the collective has been launched everywhere");
+  // a request that names the freed id is refused, not run on a stale address
+  proto::WorkRequest w2 = make_wr(r0.handle, kAllReduce, vmem, vmem, 1024, 1);
+  r0.wq.try_push(&w2);
+  proto::WorkRequest w3 = make_wr(r1.handle, kAllReduce, pmem, pmem, 1024, 1);
+  r1.wq.try_push(&w3);
+  memset(&wc, 0, sizeof wc);
+  expect(wait_completion(r0.cq, &wc, 5000) && wc.status != 0, "a request naming freed memory fails");
+  wait_completion(r1.cq, &wc, 5000);
+  close(victim.fd); close(thief.fd); close(peer.fd);
+  return bad;
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -340,6 +526,10 @@ int main(int argc, char** argv) {
     bad += mccsFree(buf) != mccsSuccess;
   }
   mccsFinalize();
+  if (!client_mode) {
+    g_stage = 4;
+    bad += isolation_and_busy_checks(path);
+  }
   mccsd_stop();
   printf("fuzz_protocol: %d control frames, %ld ring requests answered, good tenant %s\n", rounds, answered,
          bad ? "FAILED" : "served");

@@ -106,3 +106,62 @@ def test_memop_mode_tenants_share_devices(tmp_path):
             assert res["bad"] == [] and res["async_error"] == 0 and res["mismatch"] == -8
     finally:
         sp.stop()
+
+
+WAITER = r"""
+import os, sys, time, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"])
+buf = M.Buffer(1 << 16, rank)
+x = buf.tensor(torch.float32, 4096)
+comm = M.Communicator(6400, rank, 2, device=rank)
+if rank == 1:
+    print("JOINED", flush=True)
+    time.sleep(600)          # never posts: rank 0's request stays queued in the daemon
+comm.set_deferred_wait(True)
+comm.all_reduce(x)           # returns at once; the "wait for done" is what blocks below
+print("POSTED", flush=True)
+t0 = time.time()
+code = 0
+try:
+    comm.wait()              # the daemon dies while this waits for the "done" semaphore
+except Exception as e:
+    code = getattr(e, "code", -999)
+first = time.time() - t0
+later = 0
+try:
+    comm.all_reduce(x)
+except Exception as e:
+    later = getattr(e, "code", -999)
+print("RESULT", code, later, round(first, 2), flush=True)
+"""
+
+
+def test_daemon_death_releases_a_waiter_in_memop_mode(tmp_path):
+    """A caller whose stream already waits for a collective's "done" semaphore must not be
+    left waiting for ever when the daemon is killed: the library notices the closed control
+    socket, satisfies the wait itself and fails the communicator with mccsNotConnected."""
+    import time
+    sp = _spawn_daemon(tmp_path, 2)
+    procs = []
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, MCCS_LOG="fatal", MCCS_WC_TIMEOUT_MS="120000")
+        procs = [subprocess.Popen([sys.executable, "-c", WAITER], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                                  stderr=subprocess.PIPE, text=True) for r in range(2)]
+        assert procs[1].stdout.readline().strip() == "JOINED"
+        assert procs[0].stdout.readline().strip() == "POSTED"
+        time.sleep(0.5)
+        sp.proc.kill()           # no goodbye, no clean-up
+        t0 = time.time()
+        out, err = procs[0].communicate(timeout=60)
+        took = time.time() - t0
+        line = [l for l in out.splitlines() if l.startswith("RESULT ")]
+        assert line, err[-2000:]
+        code, later, _ = line[0].split()[1:]
+        assert int(code) == -12 and int(later) == -12          # mccsNotConnected, now and from then on
+        assert took < 20, f"the waiter needed {took:.1f}s, the 120 s completion timeout must not be what released it"
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        sp.stop()
