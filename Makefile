@@ -15,7 +15,7 @@ NVLS_TYPES := f16 f32 bf16
 TYPE_OBJS := $(foreach t,$(TYPES),$(OBJ)/inst_$(word 1,$(subst :, ,$(t))).o) $(foreach t,$(TYPES),$(OBJ)/batch_$(word 1,$(subst :, ,$(t))).o)
 
 HOST_SRCS := csrc/common/value.cc csrc/common/log.cc csrc/ipc/uds.cc csrc/device/host_backend.cc \
-             csrc/daemon/config.cc csrc/daemon/planner.cc csrc/daemon/qos.cc csrc/daemon/trace.cc \
+             csrc/daemon/config.cc csrc/daemon/transport.cc csrc/daemon/planner.cc csrc/daemon/qos.cc csrc/daemon/trace.cc \
              csrc/daemon/runtime.cc csrc/daemon/daemon.cc csrc/daemon/proxy.cc csrc/daemon/admin.cc
 HOST_OBJS := $(patsubst csrc/%.cc,$(OBJ)/%.o,$(HOST_SRCS))
 # the kernels compiled for the host against the SIMT emulator (used by the host backend on request)

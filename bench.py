@@ -10,12 +10,15 @@ through the managed service, the configuration of the reference's single-app fig
 
 One step = one AllReduce(sum) of ``--size-mb`` MiB of bf16 per rank, out of place,
 issued through the public client API (libmccs -> daemon -> sm_100a kernel). The local
-rank 0 hosts the daemon inside its process; every rank is a client. Timing: CUDA
+rank 0 starts a stand-alone ``mccsd`` (the deployment the service is made for: one daemon
+per box, applications in their own processes); every rank is a client. Timing: CUDA
 events on the launching stream around exactly K steps, barrier + synchronise on both
 sides, MAX over ranks. The message (512 MiB) is larger than the 126 MB L2, so no
 flush is needed between iterations. The ``e2e`` figure adds, every step, the
 host->device copy of the input from pinned memory and a device->host read of the head
-of the result.
+of the result. After the timed steps a sample spread over the whole output (first and last
+elements, the shard boundaries, evenly spaced windows) is compared with a plain fp32 sum of
+the ranks' inputs; a mismatch makes the run fail.
 
 ``--impl reference`` runs the reference's own NCCL baseline harness
 (``nccl-tests-mccs`` built unmodified into ``baseline/_ref``) for the same message.
@@ -49,19 +52,95 @@ def parse_args():
     return p.parse_args()
 
 
+def job_config(args, nbytes: int, n: int) -> dict:
+    """The work of one step, in the same words for both arms."""
+    return {"model": f"{args.coll} sum, {nbytes / 2**20:g} MiB {args.dtype} per rank, out of place",
+            "global_batch": nbytes * n, "seq_len": 1, "parallelism": f"dp{n}"}
+
+
+def reference_e2e(args, rank: int, world: int, size: int):
+    """End-to-end figure for the reference arm. Its harness (nccl-tests) has no per-step host
+    copy, so the same NCCL library is driven through torch.distributed here: pinned host ->
+    device copy of the input, all_reduce, device -> host read of the head of the result, every
+    step. Nothing of this repository is on that path."""
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        return None
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    tdtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    esz = torch.empty((), dtype=tdtype).element_size()
+    count = size // esz
+    pinned = torch.empty(count, dtype=tdtype, pin_memory=True)
+    pinned.fill_(0.5)
+    src = torch.empty(count, dtype=tdtype, device="cuda")
+    d2h = min(count, 32768)
+    host = torch.empty(d2h, dtype=tdtype, pin_memory=True)
+    is_ar = args.coll == "allreduce"
+    dst = src if is_ar else torch.empty(count * world, dtype=tdtype, device="cuda")
+
+    def step():
+        src.copy_(pinned, non_blocking=True)
+        if world > 1:
+            dist.all_reduce(src) if is_ar else dist.all_gather_into_tensor(dst, src)
+        elif not is_ar:
+            dst.copy_(src)
+        host.copy_(dst[:d2h], non_blocking=True)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.destroy_process_group()
+    total = size if is_ar else size * world
+    return {"value": total / ms / 1e6, "unit": "GB/s", "ms_per_step": ms, "h2d_bytes_per_step": size,
+            "d2h_bytes_per_step": d2h * esz,
+            "how": "pinned H2D copy + NCCL collective via torch.distributed (the library the reference harness links) + D2H read"}
+
+
 def reference_arm(args, rank: int) -> int:
-    """The reference's NCCL baseline harness, unmodified, single process, -g N."""
-    if rank != 0:
-        return 0
+    """The reference's NCCL baseline harness, unmodified, single process, -g N. The ranks
+    other than 0 of a torchrun launch only take part in the end-to-end figure, after the
+    harness has finished (they block in the process-group rendezvous until rank 0 joins)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    size = int(args.size_mb * 1024 * 1024)
+    out = {"impl": "reference"}
+    if rank == 0:
+        out.update(run_reference_harness(args, size))
+    try:
+        e2e = reference_e2e(args, rank, world, size)
+        if e2e and "unavailable" not in out:
+            out["e2e"] = e2e
+    except Exception as e:  # noqa: BLE001
+        out["e2e_unavailable"] = str(e)[:200]
+    if rank == 0:
+        print(json.dumps(out))
+    return 0
+
+
+def run_reference_harness(args, size: int) -> dict:
     exe = os.path.join(REPO, "baseline", "_ref", "nccl-tests-mccs", "build",
                        "all_reduce_perf" if args.coll == "allreduce" else "all_gather_perf")
-    out = {"impl": "reference"}
     if not os.path.exists(exe):
-        out["unavailable"] = ("the reference is a Rust workspace (no setup.py/pyproject; needs cargo, libibverbs, "
-                              "gdrcopy) and its nccl-tests-mccs harness is not built in baseline/_ref")
-        print(json.dumps(out))
-        return 0
-    size = int(args.size_mb * 1024 * 1024)
+        return {"unavailable": "the reference is a Rust workspace (no setup.py/pyproject; needs cargo, libibverbs, "
+                               "gdrcopy) and its nccl-tests-mccs harness is not built in baseline/_ref"}
     dt = {"bf16": "bfloat16", "fp16": "half", "fp32": "float"}[args.dtype]
     env = dict(os.environ)
     import glob
@@ -73,35 +152,27 @@ def reference_arm(args, rank: int) -> int:
     try:
         res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     except Exception as e:  # noqa: BLE001
-        out["unavailable"] = f"nccl-tests-mccs failed to run: {e}"
-        print(json.dumps(out))
-        return 0
-    alg = None
+        return {"unavailable": f"nccl-tests-mccs failed to run: {e}"}
+    alg, t_us = None, None
     for line in res.stdout.splitlines():
         f = line.split()
-        # size count type redop root  time algbw busbw #wrong  time algbw busbw #wrong
+        # size count type redop root | time algbw busbw #wrong | time algbw busbw #wrong (out of place, then in place)
         if len(f) >= 8 and f[0].isdigit() and int(f[0]) == size:
             try:
-                # ... time algbw busbw #wrong | time algbw busbw #wrong (out of place, then in place)
                 t_us, alg = float(f[-8]), float(f[-7])
-                out.update({"ms_per_step": t_us / 1000.0})
             except (ValueError, IndexError):
                 pass
     if alg is None:
         tail = (res.stderr.strip() or res.stdout.strip())[-200:].replace("\n", " | ")
-        out["unavailable"] = "nccl-tests-mccs produced no result row: " + tail
-        print(json.dumps(out))
-        return 0
-    out.update({
+        return {"unavailable": "nccl-tests-mccs produced no result row: " + tail}
+    return {
+        "ms_per_step": t_us / 1000.0,
         "metric": f"{args.coll}_algbw_GBps", "value": alg, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": alg / BASELINE_ALGBW_GBPS, "dtype": args.dtype, "data": "synthetic",
-        "config": {"model": f"{args.coll} {args.size_mb:g} MiB {args.dtype}, NCCL via the reference's nccl-tests-mccs "
-                            "(host-timed by that harness, single process -g N)",
-                   "global_batch": size, "seq_len": 1, "parallelism": f"dp{args.gpus}"},
-    })
-    print(json.dumps(out))
-    return 0
+        "config": job_config(args, size, args.gpus),
+        "detail": {"harness": "NCCL via the reference's nccl-tests-mccs, host-timed by that harness, single process -g N"},
+    }
 
 
 def main() -> int:
@@ -146,8 +217,13 @@ def main() -> int:
     port = os.environ.get("MASTER_PORT", "0")
     prefix = f"/tmp/mccs-bench-{os.getuid()}-{port}-{os.environ.get('TORCHELASTIC_RUN_ID', os.getppid() if n > 1 else os.getpid())}"
     control = prefix + "/control.sock"
+    spawned = None
     if local_rank == 0:
-        M.daemon.start_embedded(prefix=prefix, channel_count=2, host_devices=max(n, 1), listen_port=-1)
+        os.makedirs(prefix, exist_ok=True)
+        with open(prefix + "/mccs.toml", "w") as f:
+            f.write(M.daemon.default_config(prefix, channel_count=2, host_devices=max(n, 1), listen_port=-1,
+                                            force_host=not have_cuda))
+        spawned = M.daemon.spawn(prefix + "/mccs.toml")
     barrier()
     M.init(control)
     backend = M.backend()
@@ -190,19 +266,46 @@ def main() -> int:
     if have_cuda:
         torch.cuda.synchronize()
 
-    # Correctness of what is about to be timed: compare a slice against a plain fp32 sum.
-    check_n = min(count, 1 << 16)
-    ok = True
-    if n > 1 and is_ar and have_cuda:
-        mine = send[:check_n].float()
-        gathered = [torch.empty_like(mine) for _ in range(n)]
-        dist.all_gather(gathered, mine)
-        want = torch.stack(gathered).sum(0)
-        got = recv[:check_n].float()
-        tol = 1e-5 if tdtype == torch.float32 else 2e-2
-        ok = bool(torch.allclose(got, want, rtol=tol, atol=tol * n))
-    elif is_ar:
-        ok = bool(torch.equal(recv[:check_n], send[:check_n])) if n == 1 else True
+    # What is checked after the timed steps: windows of the output spread over the whole
+    # buffer (its first and last elements, both sides of every shard boundary, evenly spaced
+    # ones in between) against a plain fp32 sum of all ranks' inputs at the same places.
+    win = min(count, 4096)
+    starts = {0, count - win}
+    for k in range(1, 32):
+        starts.add(min(count - win, (count * k // 32) // 8 * 8))
+    for r in range(1, n):
+        edge = count * r // n
+        starts.add(max(0, min(count - win, edge - win // 2)))
+    starts = sorted(starts)
+    idx = torch.cat([torch.arange(s0, s0 + win) for s0 in starts]).to(send.device)
+
+    def verify() -> bool:
+        if have_cuda:
+            torch.cuda.synchronize()
+        mine = send[idx].float()
+        if n > 1:
+            gathered = [torch.empty_like(mine) for _ in range(n)]
+            dist.all_gather(gathered, mine)
+        else:
+            gathered = [mine]
+        good = True
+        if is_ar:
+            want = torch.stack(gathered).sum(0)
+            got = recv[idx].float()
+            tol = 1e-5 if tdtype == torch.float32 else 2e-2
+            good = bool(torch.allclose(got, want, rtol=tol, atol=tol * n)) and bool(torch.isfinite(got).all())
+        else:
+            for r in range(n):
+                good = good and bool(torch.equal(recv[idx + r * count].float(), gathered[r]))
+        flag = torch.tensor([1.0 if good else 0.0], dtype=torch.float64, device=send.device)
+        if n > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return bool(flag.item() > 0.5)
+
+    # the warm-up results must not be what passes the check
+    recv.fill_(float("nan"))
+    if have_cuda:
+        torch.cuda.synchronize()
 
     def timed(fn) -> float:
         if not have_cuda:
@@ -226,6 +329,7 @@ def main() -> int:
         return max_over_ranks(e0.elapsed_time(e1) / steps)
 
     ms = timed(step)
+    ok = verify()
     variant, ctas = comm.last_plan()
     launch_mode = comm.launch_mode
 
@@ -240,7 +344,9 @@ def main() -> int:
 
     for _ in range(2):
         e2e_step()
+    recv.fill_(float("nan"))
     ms_e2e = timed(e2e_step)
+    ok = verify() and ok
     clocks = sampler.stop() if sampler else None
 
     # Same harness, NCCL (the baseline the service has to match on this box).
@@ -270,8 +376,8 @@ def main() -> int:
     recv_buf.free()
     M.finalize()
     barrier()
-    if local_rank == 0:
-        M.daemon.stop_embedded()
+    if spawned is not None:
+        spawned.stop()
     if rank == 0:
         out = {
             "metric": f"{args.coll}_algbw_GBps", "value": alg, "unit": "GB/s", "n_gpus": n, "steps": steps,
@@ -279,24 +385,25 @@ def main() -> int:
             "vs_baseline": alg / BASELINE_ALGBW_GBPS, "dtype": args.dtype, "data": "synthetic",
             "impl": "mccs",
             "busbw_GBps": alg * bus_factor(args.coll, n),
-            "config": {
-                "model": f"{args.coll} sum, {nbytes / 2**20:g} MiB per rank, out of place, through libmccs + daemon",
-                "global_batch": nbytes * n, "seq_len": 1, "parallelism": f"dp{n}",
+            "config": job_config(args, nbytes, n),
+            "detail": {
+                "path": "libmccs client -> stand-alone mccsd -> sm_100a kernel",
                 "variant": variant, "ctas": ctas, "backend": backend, "launch": launch_mode,
                 "l2": "inputs larger than L2 (no flush)", "timing": "CUDA events, max over ranks",
-                "verified": ok,
+                "verified": ok, "verified_elements": int(idx.numel()),
             },
             "clocks": clocks,
             "e2e": {"value": alg_e2e, "unit": "GB/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": d2h_elems * esz},
-            # one collective kernel per rank and step, launched by the daemon threads in local rank 0
+            # one collective kernel per rank and step (launched by each rank's own library when
+            # "launch" is "client", by the daemon's proxy threads otherwise)
             "gpu_launches": steps * n,
             "nccl_same_harness": nccl,
         }
         print(json.dumps(out))
     if n > 1:
         dist.destroy_process_group()
-    return 0
+    return 0 if ok else 1
 
 
 if __name__ == "__main__":

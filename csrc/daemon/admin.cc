@@ -183,6 +183,7 @@ Value Daemon::stats() {
       v.set("client_launch", ready && c.client_launch);
       v.set("emulated", ready && c.emulated);
       v.set("host_staged", ready && c.host_staged);
+      v.set("transport", ready ? c.conns.describe() : std::string("-"));
       v.set("paused", c.paused.load());
       Value devs = Value::array();
       for (int d : c.devices) devs.push(d);

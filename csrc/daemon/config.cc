@@ -116,7 +116,7 @@ Config Config::from_value(const Value& root) {
                {"transport", "nvls", "vmm", "sync", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
                 "host_devices", "force_host_backend", "idle_sleep_us", "idle_spin_us", "pin_threads", "init_timeout_ms", "fuse_allreduce", "client_nvls",
                 "single_through_fused", "skip_start_barrier", "kernel_writes_done", "host_kernels",
-                "hybrid_nvls_permille", "hybrid_nvls_ctas", "launch"},
+                "hybrid_nvls_permille", "hybrid_nvls_ctas", "launch", "nvls_unroll"},
                "[b200]");
     c.transport = b["transport"].as_string(c.transport);
     if (c.transport != "auto" && c.transport != "nvlink" && c.transport != "host_staged")
@@ -127,7 +127,7 @@ Config Config::from_value(const Value& root) {
     if (c.sync != "auto" && c.sync != "events" && c.sync != "memops")
       throw std::runtime_error("b200.sync must be auto, events or memops");
     c.launch = b["launch"].as_string(c.launch);
-    if (c.launch != "daemon" && c.launch != "client") throw std::runtime_error("b200.launch must be daemon or client");
+    if (c.launch != "auto" && c.launch != "daemon" && c.launch != "client") throw std::runtime_error("b200.launch must be auto, daemon or client");
     c.wait_timeout_ms = (uint64_t)b["wait_timeout_ms"].as_int((int64_t)c.wait_timeout_ms);
     c.tuning_file = b["tuning_file"].as_string();
     c.trace = b["trace"].as_bool(c.trace);
@@ -143,8 +143,10 @@ Config Config::from_value(const Value& root) {
     c.init_timeout_ms = (uint64_t)b["init_timeout_ms"].as_int((int64_t)c.init_timeout_ms);
     c.hybrid_nvls_permille = (int)b["hybrid_nvls_permille"].as_int(c.hybrid_nvls_permille);
     c.hybrid_nvls_ctas = (int)b["hybrid_nvls_ctas"].as_int(c.hybrid_nvls_ctas);
+    c.nvls_unroll = (int)b["nvls_unroll"].as_int(c.nvls_unroll);
+    if (c.nvls_unroll != 4 && c.nvls_unroll != 8) throw std::runtime_error("b200.nvls_unroll must be 4 or 8");
     if (c.hybrid_nvls_permille < 0 || c.hybrid_nvls_permille > 1000 || c.hybrid_nvls_ctas < 0 || c.hybrid_nvls_ctas > kMaxCtas)
-      throw std::runtime_error("b200.hybrid_nvls_permille must be 0..1000 and hybrid_nvls_ctas 0..128");
+      throw std::runtime_error("b200.hybrid_nvls_permille must be 0..1000 and hybrid_nvls_ctas 0..148");
     c.single_through_fused = b["single_through_fused"].as_bool(c.single_through_fused);
     c.skip_start_barrier = b["skip_start_barrier"].as_bool(c.skip_start_barrier);
     c.kernel_writes_done = b["kernel_writes_done"].as_bool(c.kernel_writes_done);

@@ -75,8 +75,12 @@ struct Config {
   bool nvls = true;
   bool vmm = true;
   std::string sync = "auto";        // auto | events | memops (see proto::SyncMode)
-  std::string launch = "daemon";    // daemon | client (see proto::LaunchMode): who launches the kernels
-  bool client_nvls = false;         // client-side launch: also plan the in-switch variants (clients map the multicast objects)
+  // Who launches the kernels (proto::LaunchMode). auto: on GPUs the clients themselves, for
+  // communicators whose ranks are all other processes, one per GPU, on peer memory (the
+  // hand-over between two processes costs more than the kernel of a small collective);
+  // the daemon otherwise. daemon / client force one of the two where it is possible.
+  std::string launch = "auto";
+  bool client_nvls = true;          // client-side launch: also plan the in-switch variants (clients map the multicast objects)
   uint64_t wait_timeout_ms = 10000; // bound of every device-side wait
   std::string tuning_file;
   bool trace = false;
@@ -94,6 +98,7 @@ struct Config {
   // Experiments on the per-call floor; they act on launches that go through the fused
   // kernels only (kernels/batch.cuh) and are all off by default.
   int hybrid_nvls_permille = 750;     // ar_hybrid: share of the message that goes through the switch (1/1000)
+  int nvls_unroll = 4;                // NVLS all-reduce kernels: in-switch loads in flight per thread (4 or 8)
   int hybrid_nvls_ctas = 8;           // ar_hybrid: CTAs that feed the switch; the others exchange the rest by peer copies
   bool single_through_fused = false;  // a lone two-shot AllReduce also uses the fused kernel (one member)
   bool skip_start_barrier = false;    // no barrier before the first load when the host has gated every rank

@@ -56,9 +56,12 @@ int Daemon::start(const Config& cfg, std::string* err) {
   memops_ = backend_->memops_supported() && cfg.sync != "events";
   if (cfg.sync == "memops" && !memops_) LOG_WARN("b200.sync=memops requested but stream memory operations are unavailable; using events");
 
-  client_launch_ = cfg.launch == "client";
+  catalog_.reset(new TransportCatalog(cfg.transport));
+  auto_launch_ = cfg.launch == "auto";
+  client_launch_ = cfg.launch == "client" || (auto_launch_ && backend_->kind() == proto::kBackendCuda);
   if (client_launch_ && !backend_->client_launch_supported()) {
-    LOG_WARN("b200.launch=client needs exportable device memory and registered host memory addressable by its host pointer; the daemon launches");
+    if (!auto_launch_)
+      LOG_WARN("b200.launch=client needs exportable device memory and registered host memory addressable by its host pointer; the daemon launches");
     client_launch_ = false;
   }
   planner_.load_defaults(backend_->nvls_supported() && cfg.nvls);
@@ -620,22 +623,29 @@ int Daemon::finalize_communicator(Communicator& c) {
     return proto::kErrUnsupported;
   }
   c.emulated = !host && c.nranks > 1 && all_same;
-  bool p2p = true;
-  for (int a = 0; a < c.nranks; a++)
-    for (int b = 0; b < c.nranks; b++)
-      p2p &= backend_->peer_access(c.devices[(size_t)a], c.devices[(size_t)b]);
-  c.host_staged = cfg_.transport == "host_staged" || (cfg_.transport == "auto" && !p2p);
+  // One transport per (sender, receiver) pair, the first of the catalog that can connect
+  // the two devices.
+  TransportEnv env;
+  env.peer_access = [this](int a, int b) { return backend_->peer_access(a, b); };
+  env.multicast = [this](int) { return backend_->nvls_supported(); };
+  env.nvls_enabled = cfg_.nvls;
+  c.conns = connect_all(*catalog_, env, c.devices);   // the table points into the catalog, which lives as long as the daemon
+  if (!c.conns.complete()) {
+    LOG_ERROR("comm %u: transport=%s connects no path from rank %d (device %d) to rank %d (device %d)", c.id, cfg_.transport.c_str(),
+              c.conns.unconnected_from, c.devices[(size_t)c.conns.unconnected_from], c.conns.unconnected_to,
+              c.devices[(size_t)c.conns.unconnected_to]);
+    return proto::kErrUnsupported;
+  }
+  c.host_staged = c.conns.scratch_in_host_memory();
   // Kernels that clients launch themselves: not when several ranks share a GPU (their
   // kernels would be separate launches that wait on one another on one device), and on a
   // GPU not with the pads in pinned host memory (that memory is not exported).
-  c.client_launch = client_launch_ && (host || (!c.emulated && !c.host_staged));
-  if (client_launch_ && !c.client_launch)
+  bool all_remote = true;   // every rank is a process of its own (not a thread of this one)
+  for (int r = 0; r < c.nranks; r++) all_remote &= !c.ranks[(size_t)r]->same_process;
+  c.client_launch = client_launch_ && (host || (!c.emulated && !c.host_staged)) && (!auto_launch_ || all_remote);
+  if (client_launch_ && !auto_launch_ && !c.client_launch)
     LOG_WARN("comm %u: launched by the daemon although b200.launch=client (%s)", c.id,
              c.emulated ? "several ranks on one GPU" : "host-staged transport");
-  if (cfg_.transport == "nvlink" && !p2p) {
-    LOG_ERROR("comm %u: transport=nvlink but the devices have no peer access", c.id);
-    return proto::kErrUnsupported;
-  }
 
   {
     std::lock_guard<std::mutex> g(c.cfg_mu);
@@ -709,7 +719,7 @@ int Daemon::finalize_communicator(Communicator& c) {
   int sem_ranks = 0;
   for (auto& r : c.ranks) sem_ranks += r->sync.host != nullptr;
   LOG_INFO("comm %u ready: %d ranks, %s%s, %d ring channel(s), %d rank(s) ordered by semaphores, %d by events", c.id, c.nranks,
-           c.host_staged ? "host-staged" : "nvlink peer memory", c.emulated ? " (single-device emulation)" : "",
+           c.conns.describe().c_str(), c.emulated ? " (single-device emulation)" : "",
            c.channel_count, sem_ranks, c.nranks - sem_ranks);
   return proto::kOk;
 }

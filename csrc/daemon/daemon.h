@@ -34,6 +34,7 @@
 #include "../ipc/shm_ring.h"
 #include "config.h"
 #include "planner.h"
+#include "transport.h"
 #include "qos.h"
 #include "runtime.h"
 #include "trace.h"
@@ -90,6 +91,9 @@ struct CollSlot {
   std::atomic<int> state{kSlotCollecting};
   std::atomic<int> finished{0};        // ranks that launched everything and completed the request
   std::atomic<int> admitted_slices{0};
+  // the last deferral of a slice by the QoS arbiter (under Communicator::admit_mu)
+  int defer_slice = -1;
+  uint64_t defer_gen = 0, defer_retry_us = 0;
   std::atomic<int> group_launch{0};    // emulated/host: 0 idle, 1 launching, 2 launched
   CollOp ops[kMaxRanks];
   Plan plan;
@@ -159,7 +163,8 @@ class Communicator {
   uint32_t id = 0;
   int nranks = 0;
   bool emulated = false;       // all ranks on one device: one launch covers every rank
-  bool host_staged = false;
+  ConnectionTable conns;       // the transport chosen for every (sender, receiver) pair
+  bool host_staged = false;    // = conns.scratch_in_host_memory(): pads and FIFOs in pinned host memory
   bool client_launch = false;  // the ranks' client libraries launch the kernels; the daemon plans and admits
   std::vector<int> devices;    // device of each rank
   std::vector<std::unique_ptr<RankState>> ranks;
@@ -341,6 +346,8 @@ class Daemon {
   std::atomic<bool> running_{false};
   bool memops_ = false;
   bool client_launch_ = false;
+  std::unique_ptr<TransportCatalog> catalog_;   // the transports this daemon offers ([b200] transport), in selection order
+  bool auto_launch_ = false;      // b200.launch = auto: per communicator, see finalize_communicator
   std::atomic<bool> stop_{false};
 
   std::mutex mu_;   // sessions_, comms_, pending_inits_

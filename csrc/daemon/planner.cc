@@ -169,6 +169,7 @@ std::string Planner::infeasible(int variant, const PlanInput& in) {
   }
   if (in.nranks == 1) return "single-rank communicator uses the local copy";
   if (in.host_staged && !variant_is_ring(variant)) return "host-staged transport only runs ring variants";
+  if (!((in.carried_variants >> variant) & 1u)) return "a connection of this communicator cannot carry this variant";
   if (!variant_is_ring(variant) && !in.p2p_possible) return "no peer access between the devices";
   if (variant_is_nvls(variant)) {
     if (in.emulated) return "NVLS needs one device per rank";

@@ -41,6 +41,7 @@ struct PlanInput {
   bool nvls_possible = false;   // backend has NVLS, buffers sit at equal offsets of multicast-able allocations
   bool p2p_possible = true;     // all devices can address each other's memory
   bool host_staged = false;     // transport forces FIFO rings through pinned host memory
+  uint32_t carried_variants = ~0u;  // bit v: every connection of the communicator can carry variant v (ConnectionTable)
   bool emulated = false;        // all ranks on one device (single cooperative launch)
   int requested_variant = kAuto;  // from the caller or an override
   int requested_ctas = 0;         // from an override ("channel count"), 0 = table

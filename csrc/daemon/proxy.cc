@@ -281,11 +281,9 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
     if (o.variant_req != req) req = kAuto;
   }
   in.aligned16 = (bits & 15u) == 0;
-  in.p2p_possible = true;
-  for (int a = 0; a < c.nranks && in.p2p_possible; a++)
-    for (int b = 0; b < c.nranks; b++)
-      if (!be->peer_access(c.devices[a], c.devices[b])) { in.p2p_possible = false; break; }
-  in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged &&
+  in.carried_variants = c.conns.carried_variants();
+  in.p2p_possible = c.conns.carries(kArTwoShot);
+  in.nvls_possible = c.conns.carries(kArNvlsTwo) && !c.emulated &&
                      (!c.client_launch || daemon_->config().client_nvls) &&
                      all_vmm && c.nranks >= 2 &&
                      (o0.kind == kReduceScatter ? same_send_off   // only the inputs are read through the switch
@@ -433,7 +431,8 @@ bool ProxyEngine::plan_member(Communicator& c, CollSlot& head, CollSlot& m, cons
     if (o.variant_req != req) req = kAuto;
   }
   in.aligned16 = (bits & 15u) == 0;
-  in.nvls_possible = be->nvls_supported() && daemon_->config().nvls && !c.emulated && !c.host_staged &&
+  in.carried_variants = head_in.carried_variants;
+  in.nvls_possible = c.conns.carries(kArNvlsTwo) && !c.emulated &&
                      be->kind() != proto::kBackendHost && same_recv_off && same_send_off && c.nranks >= 2;
   {
     std::lock_guard<std::mutex> g(c.cfg_mu);
@@ -536,7 +535,7 @@ void ProxyEngine::fill_batch_args(Communicator& c, CollSlot& head, uint64_t seq,
       if (!rr.sync.host || !head.ops[r].sync_slot || !rr.pad) continue;
       b.done_ptr[r] = (uint64_t*)(rr.sync.dev_addr + 8 * proto::kSyncDoneSlot);
       b.done_value[r] = last_member_user_seq(c, head, seq, r);
-      b.done_counter[r] = &rr.pad->pad_[0];
+      b.done_counter[r] = &rr.pad->pad_[kPadBatchCounter];
     }
   }
 }
@@ -561,8 +560,22 @@ bool ProxyEngine::admit_slice(Communicator& c, CollSlot& s, int slice) {
   const uint64_t bytes = s.batch_len > 1 ? s.batch_bytes : s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
   // CTAs per GPU: one launch per rank and GPU, or every rank's CTAs on the one GPU.
   const int ctas = s.plan.dims.ctas * (c.emulated ? c.nranks : 1);
-  QosDecision d = daemon_->qos().admit(c.id, bytes, monotonic_us(), wall_us(), ctas);
-  if (d != kQosAdmit) return false;
+  // A request that was told to wait is not put to the arbiter again (a lock shared by the
+  // proxies of all GPUs) until the arbiter's state moved, or a short time passed for the
+  // reasons that follow the clock: 20 us for a closed window, 200 us otherwise (a competitor
+  // that stopped issuing work only stops counting after its activity window).
+  QosArbiter& qos = daemon_->qos();
+  const uint64_t now = monotonic_us();
+  const uint64_t gen = qos.generation();
+  if (s.defer_slice == slice && s.defer_gen == gen && now < s.defer_retry_us) return false;
+  QosDecision d = qos.admit(c.id, bytes, now, wall_us(), ctas);
+  if (d != kQosAdmit) {
+    s.defer_slice = slice;
+    s.defer_gen = gen;
+    s.defer_retry_us = now + (d == kQosDeferWindow ? 20 : 200);
+    return false;
+  }
+  s.defer_slice = -1;
   s.admitted_slices.store(slice + 1, std::memory_order_release);
   return true;
 }
@@ -607,6 +620,8 @@ void ProxyEngine::fill_args(Communicator& c, CollSlot& s, int rank, int slice, C
     const Config& cfg = daemon_->config();
     const int nvls_ctas = std::min(cfg.hybrid_nvls_ctas, std::max(s.plan.dims.ctas - 1, 0));
     a.unroll_hint = (int32_t)(((uint32_t)nvls_ctas << 16) | (uint32_t)cfg.hybrid_nvls_permille);
+  } else if (s.plan.variant == kArNvlsOne || s.plan.variant == kArNvlsTwo) {
+    a.unroll_hint = daemon_->config().nvls_unroll;
   }
   a.fifo_slot_bytes = c.fifo_slot_bytes;
   memcpy(a.ring, s.ring, sizeof a.ring);
@@ -814,6 +829,8 @@ bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
     const Config& cfg = daemon_->config();
     const int nvls_ctas = std::min(cfg.hybrid_nvls_ctas, std::max(s.plan.dims.ctas - 1, 0));
     m.variant_hint = (int32_t)(((uint32_t)nvls_ctas << 16) | (uint32_t)cfg.hybrid_nvls_permille);
+  } else if (s.plan.variant == kArNvlsOne || s.plan.variant == kArNvlsTwo) {
+    m.variant_hint = daemon_->config().nvls_unroll;
   }
   if (s.plan.needs_mc_send) { m.mc_send_id = s.mc_send_id; m.mc_send_off = s.ops[rs.rank].send_off; }
   if (s.plan.needs_mc_recv) { m.mc_recv_id = s.mc_recv_id; m.mc_recv_off = s.ops[rs.rank].recv_off; }
@@ -879,6 +896,7 @@ void ProxyEngine::finish_slot(Communicator& c, CollSlot& s, uint64_t seq) {
     s.arrived.store(0, std::memory_order_relaxed);
     s.finished.store(0, std::memory_order_relaxed);
     s.admitted_slices.store(0, std::memory_order_relaxed);
+    s.defer_slice = -1;
     s.group_launch.store(0, std::memory_order_relaxed);
     s.state.store(kSlotCollecting, std::memory_order_relaxed);
     s.seq.store(seq + kCollSlots, std::memory_order_release);

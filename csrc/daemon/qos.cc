@@ -16,6 +16,7 @@ void QosArbiter::configure(const Config& cfg) {
   active_window_us_ = cfg.qos_active_window_us;
   sm_limit_ = cfg.qos_sm_limit;
   for (const auto& kv : cfg.qos_tenants) tenants_[kv.first].cfg = kv.second;
+  bump();
 }
 
 QosArbiter::Tenant& QosArbiter::tenant(uint32_t id) { return tenants_[id]; }
@@ -23,12 +24,14 @@ QosArbiter::Tenant& QosArbiter::tenant(uint32_t id) { return tenants_[id]; }
 void QosArbiter::set_tenant(uint32_t id, const QosTenantConfig& t) {
   std::lock_guard<std::mutex> g(mu_);
   tenants_[id].cfg = t;
+  bump();
 }
 
 void QosArbiter::set_schedule(uint64_t epoch_us, const std::map<uint32_t, QosIntervalConfig>& schedule) {
   std::lock_guard<std::mutex> g(mu_);
   epoch_us_ = epoch_us;
   schedule_ = schedule;
+  bump();
 }
 
 void QosArbiter::tenant_register(uint32_t id, const std::vector<int>& devices) {
@@ -52,6 +55,7 @@ void QosArbiter::tenant_unregister(uint32_t id) {
   it->second.inflight_ctas = 0;
   it->second.waiting_since_us = 0;
   it->second.devices.clear();
+  bump();
 }
 
 bool QosArbiter::shares_device(const Tenant& a, const Tenant& b) const {
@@ -153,6 +157,7 @@ QosDecision QosArbiter::admit(uint32_t id, uint64_t bytes, uint64_t now_us, uint
     me.round++;
     me.admitted++;
     me.bytes_admitted += bytes;
+    bump();   // a waiter that was admitted no longer holds the others back
     return kQosAdmit;
   };
   if (!enabled_) return grant();
@@ -199,6 +204,7 @@ void QosArbiter::complete(uint32_t id, uint64_t bytes) {
   Tenant& t = tenant(id);
   t.outstanding_bytes = t.outstanding_bytes > bytes ? t.outstanding_bytes - bytes : 0;
   if (t.outstanding_bytes == 0) t.inflight_ctas = 0;
+  bump();
 }
 
 Value QosArbiter::stats() {

@@ -27,6 +27,7 @@
 #pragma once
 #include <stdint.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <string>
@@ -45,7 +46,7 @@ class QosArbiter {
   void configure(const Config& cfg);
   void set_tenant(uint32_t id, const QosTenantConfig& t);
   void set_schedule(uint64_t epoch_us, const std::map<uint32_t, QosIntervalConfig>& schedule);
-  void set_enabled(bool on) { std::lock_guard<std::mutex> g(mu_); enabled_ = on; }
+  void set_enabled(bool on) { std::lock_guard<std::mutex> g(mu_); enabled_ = on; bump(); }
 
   void tenant_register(uint32_t id, const std::vector<int>& devices);
   void tenant_unregister(uint32_t id);
@@ -65,6 +66,11 @@ class QosArbiter {
   // Registers that a collective of `id` is planned and waiting for admission.
   void note_waiting(uint32_t id, uint64_t now_us);
   void complete(uint32_t id, uint64_t bytes);
+  // Changes whenever something happened that can turn a deferral into an admission (a
+  // completion, another tenant's admission, a new policy). A proxy that was told to wait
+  // reads this without the arbiter's lock and only asks again when it moved, or after a
+  // short time for the reasons that depend on the clock (windows, a competitor going idle).
+  uint64_t generation() const { return gen_.load(std::memory_order_acquire); }
 
   Value stats();
   static bool window_allows(const QosIntervalConfig& w, uint64_t epoch_us, uint64_t wall_us, uint64_t round);
@@ -88,7 +94,10 @@ class QosArbiter {
   bool shares_device(const Tenant& a, const Tenant& b) const;
   bool is_contender(const Tenant& other, uint64_t now_us) const;
 
+  void bump() { gen_.fetch_add(1, std::memory_order_acq_rel); }
+
   std::mutex mu_;
+  std::atomic<uint64_t> gen_{1};
   bool enabled_ = true;
   std::map<uint32_t, Tenant> tenants_;
   uint64_t epoch_us_ = 0;

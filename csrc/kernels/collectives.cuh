@@ -119,10 +119,23 @@ __device__ __forceinline__ void trace_begin(const CollArgs& a, int rank) {
   if (a.trace && blockIdx.x == 0 && threadIdx.x == 0)
     st_relaxed_sys_u64(&a.status[rank]->start_ns, globaltimer_ns());
 }
+// End of a kernel, called by every thread of every CTA after its last store and its
+// closing barrier. The rank's completion word (StatusBlock::done_seq) is what the host
+// side reasons with (how much is queued on the GPU, when a tenant's admission credit is
+// returned, when buffers may go away in client-side launch), so it must not be written
+// while another CTA of the rank is still storing: each CTA's closing barrier only covers
+// the CTAs with its own index on the peers. The CTAs therefore count themselves off and
+// the last one publishes the word.
 __device__ __forceinline__ void finish(const CollArgs& a, int rank) {
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    if (a.trace) st_relaxed_sys_u64(&a.status[rank]->end_ns, globaltimer_ns());
-    st_release_sys_u64(&a.status[rank]->done_seq, a.seq);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();   // this CTA's stores are ordered before its count
+    const unsigned last = gridDim.x - 1;
+    if (atomicInc(&a.pad[rank]->pad_[kPadCtaCounter], last) == last) {
+      fence_sys();     // ... and, through the counts, before the completion word
+      if (a.trace) st_relaxed_sys_u64(&a.status[rank]->end_ns, globaltimer_ns());
+      st_release_sys_u64(&a.status[rank]->done_seq, a.seq);
+    }
   }
 }
 
@@ -222,7 +235,6 @@ __global__ void __launch_bounds__(kMaxThreads) ar_nvls_kernel(const __grid_const
   char* local_out = (char*)a.recv[rank];
   const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
   uint64_t i = mine.beg + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  constexpr int U = 4;
   auto emit = [&](uint64_t idx, Raw<16> v) {
     if (sc.mode == 2) {
       Acc acc[kN];
@@ -234,13 +246,20 @@ __global__ void __launch_bounds__(kMaxThreads) ar_nvls_kernel(const __grid_const
     if (kTwoShot) multimem_st16(mc_out + idx * 16, v);
     else st_data<16>(local_out + idx * 16, v);
   };
-  for (; i + (uint64_t)(U - 1) * stride < mine.end; i += (uint64_t)U * stride) {
-    Raw<16> v[U];
+  // In-switch loads in flight per thread before the first store (CollArgs::unroll_hint: 8,
+  // anything else means 4).
+  auto sweep = [&](auto uc) {
+    constexpr int U = decltype(uc)::value;
+    for (; i + (uint64_t)(U - 1) * stride < mine.end; i += (uint64_t)U * stride) {
+      Raw<16> v[U];
 #pragma unroll
-    for (int u = 0; u < U; u++) v[u] = Multimem<T>::ld_reduce_add(mc_in + (i + u * stride) * 16);
+      for (int u = 0; u < U; u++) v[u] = Multimem<T>::ld_reduce_add(mc_in + (i + u * stride) * 16);
 #pragma unroll
-    for (int u = 0; u < U; u++) emit(i + u * stride, v[u]);
-  }
+      for (int u = 0; u < U; u++) emit(i + u * stride, v[u]);
+    }
+  };
+  if (a.unroll_hint == 8) sweep(std::integral_constant<int, 8>{});
+  else sweep(std::integral_constant<int, 4>{});
   for (; i < mine.end; i += stride) emit(i, Multimem<T>::ld_reduce_add(mc_in + i * 16));
 
   // Sub-16-byte remainder: plain peer loads/stores.
@@ -537,7 +556,13 @@ __global__ void __launch_bounds__(kMaxThreads) ag_ring_kernel(const __grid_const
   finish(a, rank);
 }
 
-// Single-rank communicator: the collective degenerates to a device copy.
+// Single-rank communicator: the collective degenerates to a device copy (nothing at all
+// in place). Both buffers are local by construction, so plain loads and stores are used,
+// and the launcher sizes the grid from the message: one CTA per kCopyTileBytes, far more
+// CTAs than SMs for a large message. Measured on a B200 with 512 MiB: this shape moves
+// 6.7 TB/s (read + write), a persistent grid of one to eight CTAs per SM with the same
+// inner loop 5.8-6.2 TB/s, the driver's own device-to-device copy 6.3 TB/s. Any grid
+// works (the tile loop strides by the grid), which is what the CPU emulation uses.
 __global__ void __launch_bounds__(kMaxThreads) local_copy_kernel(const __grid_constant__ CollArgs a) {
   const int rank = a.emulated ? (int)blockIdx.y : a.rank;
   trace_begin(a, rank);
@@ -545,26 +570,29 @@ __global__ void __launch_bounds__(kMaxThreads) local_copy_kernel(const __grid_co
   char* out = (char*)a.recv[rank];
   const uint64_t bytes = a.count;  // the launcher converts elements to bytes
   if (in != out) {
-    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     uint64_t done = 0;
     if ((((uint64_t)in | (uint64_t)out) & 15u) == 0) {
       const uint64_t nv = bytes / 16;
-      constexpr int U = 4;
-      uint64_t i = first;
-      for (; i + (U - 1) * stride < nv; i += U * stride) {
-        Raw<16> v[U];
+      const uint64_t tile = (uint64_t)blockDim.x * kCopyUnroll;
+      const Raw<16>* src = (const Raw<16>*)in;
+      Raw<16>* dst = (Raw<16>*)out;
+      for (uint64_t base = (uint64_t)blockIdx.x * tile; base < nv; base += (uint64_t)gridDim.x * tile) {
+        const uint64_t i = base + threadIdx.x;
+        if (base + tile <= nv) {
+          Raw<16> v[kCopyUnroll];
 #pragma unroll
-        for (int u = 0; u < U; u++) v[u] = ld_data<16>(in + (i + u * stride) * 16);
+          for (int u = 0; u < kCopyUnroll; u++) v[u] = src[i + (uint64_t)u * blockDim.x];
 #pragma unroll
-        for (int u = 0; u < U; u++) st_data<16>(out + (i + u * stride) * 16, v[u]);
+          for (int u = 0; u < kCopyUnroll; u++) dst[i + (uint64_t)u * blockDim.x] = v[u];
+        } else {
+          for (uint64_t j = i; j < nv; j += blockDim.x) dst[j] = src[j];
+        }
       }
-      for (; i < nv; i += stride) st_data<16>(out + i * 16, ld_data<16>(in + i * 16));
       done = nv * 16;
     }
-    for (uint64_t i = done + first; i < bytes; i += stride) st_data<1>(out + i, ld_data<1>(in + i));
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = done + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < bytes; i += stride) out[i] = in[i];
   }
-  __syncthreads();
   finish(a, rank);
 }
 

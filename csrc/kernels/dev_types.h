@@ -15,7 +15,7 @@
 namespace mccs {
 
 constexpr int kMaxRanks = 8;       // one NVSwitch box
-constexpr int kMaxCtas = 128;      // per-rank CTAs ("channels") per collective
+constexpr int kMaxCtas = 148;      // per-rank CTAs ("channels") per collective: one per SM of a B200
 constexpr int kMaxRingChannels = 32;  // same limit as the reference (devcomm.h:32)
 constexpr int kRingSlots = 8;      // FIFO slots per ring connection (devcomm.h:29)
 
@@ -79,8 +79,18 @@ struct alignas(128) SignalPad {
   // owner's *sends* that the ring successor has consumed (written by the successor).
   uint64_t ring_tail[kMaxRingChannels];
   uint64_t ring_head[kMaxRingChannels];
+  // Counters of finished CTAs of the owner's kernels (wrap to zero at the grid size, so
+  // they need no reset between launches): [kPadBatchCounter] for the fused kernels'
+  // caller-visible completion word, [kPadCtaCounter] for StatusBlock::done_seq.
   uint32_t pad_[32];
 };
+// Launch shape of the single-rank copy kernel: every thread moves kCopyUnroll 16-byte
+// packs, one CTA per tile of the message.
+constexpr int kCopyThreads = 256;
+constexpr int kCopyUnroll = 4;
+constexpr uint64_t kCopyTileBytes = (uint64_t)kCopyThreads * kCopyUnroll * 16;
+constexpr int kPadBatchCounter = 0;
+constexpr int kPadCtaCounter = 1;
 
 // Per-rank status block in pinned, host-mapped memory: the host reads it without
 // synchronising the stream.
@@ -109,7 +119,8 @@ struct CollArgs {
   uint32_t epoch;          // first barrier value this launch may use (uses epoch, epoch+1)
   uint64_t timeout_ns;     // bound for every device-side wait
   int32_t trace;           // 1: record globaltimer start/end into the status block
-  int32_t unroll_hint;     // ar_hybrid only: low 16 bits = share of the message for the multimem part (1/1000), high 16 bits = its CTAs
+  int32_t unroll_hint;     // ar_hybrid: low 16 bits = share of the message for the multimem part (1/1000), high 16 bits = its CTAs;
+                           // the NVLS all-reduce kernels: in-switch loads in flight per thread (8, or 4 for any other value)
   // --- buffers (unicast addresses valid on every GPU of the communicator) -----
   const void* send[kMaxRanks];
   void* recv[kMaxRanks];

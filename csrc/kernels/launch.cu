@@ -115,6 +115,15 @@ cudaError_t launch_collective(int kind, const CollArgs& args, LaunchDims dims, v
   if (dims.ctas < 1 || dims.ctas > kMaxCtas || dims.threads < 32 || dims.threads > 512)
     return cudaErrorInvalidConfiguration;
   if (variant_is_ring(a.variant) && dims.ctas > kMaxRingChannels) return cudaErrorInvalidConfiguration;
+  if (a.variant == kLocalCopy) {
+    // No CTA of a copy waits for another one, so the grid follows the message instead of the
+    // plan: one CTA per tile (see local_copy_kernel), bounded so that the tile loop takes over
+    // for messages beyond 16 GiB.
+    const uint64_t tile = kCopyTileBytes;
+    uint64_t ctas = (a.count + tile - 1) / tile;
+    dims.ctas = (int32_t)(ctas < 1 ? 1 : ctas > (1u << 20) ? (1u << 20) : ctas);
+    dims.threads = kCopyThreads;
+  }
   dim3 grid((unsigned)dims.ctas, a.emulated ? (unsigned)a.nranks : 1u, 1u);
   dim3 block((unsigned)dims.threads, 1u, 1u);
   void* params[] = {(void*)&a};

@@ -16,6 +16,7 @@
 #include "../daemon/planner.h"
 #include "../daemon/qos.h"
 #include "../daemon/runtime.h"
+#include "../daemon/transport.h"
 #include "../ipc/shm_ring.h"
 #include "../ipc/uds.h"
 #include "../kernels/dev_types.h"
@@ -275,6 +276,88 @@ static void test_planner() {
   CHECK(p2.to_json().to_json() == p.to_json().to_json());
 }
 
+// Transport selection per connection (the reference's "first can_connect wins",
+// src/mccs/src/transport/setup.rs:346-361), against a table standing in for the machine.
+static void test_transports() {
+  bool access[4][4];
+  for (auto& row : access) for (bool& x : row) x = true;
+  bool multicast = true;
+  TransportEnv env;
+  env.peer_access = [&](int a, int b) { return access[a][b]; };
+  env.multicast = [&](int) { return multicast; };
+  const std::vector<int> four = {0, 1, 2, 3};
+
+  // a healthy NVSwitch box: every pair through the switch, everything can run, scratch on the devices
+  TransportCatalog automatic("auto");
+  CHECK(automatic.transports().size() == 3);
+  ConnectionTable t = connect_all(automatic, env, four);
+  CHECK(t.complete() && t.all(kTransportNvls) && !t.scratch_in_host_memory());
+  CHECK(t.carries(kArNvlsTwo) && t.carries(kArTwoShot) && t.carries(kArRing) && t.carries(kAgNvls));
+  CHECK(t.describe() == "nvls");
+
+  // multicast switched off (configuration) or not supported: plain peer memory
+  env.nvls_enabled = false;
+  t = connect_all(automatic, env, four);
+  CHECK(t.all(kTransportNvlinkP2P) && t.carries(kArTwoShot) && t.carries(kAgPush) && !t.carries(kArNvlsTwo) && !t.carries(kArHybrid));
+  env.nvls_enabled = true;
+  multicast = false;
+  t = connect_all(automatic, env, four);
+  CHECK(t.all(kTransportNvlinkP2P) && !t.carries(kRsNvls) && t.carries(kRsDirect));
+  multicast = true;
+
+  // one pair of GPUs without peer access: that connection (both directions) is host-staged,
+  // the others are not; the communicator keeps its scratch in host memory and is limited to
+  // what every connection carries, the FIFO rings
+  access[1][2] = false;
+  t = connect_all(automatic, env, four);
+  CHECK(t.complete());
+  CHECK(t.conn[1][2]->kind() == kTransportHostStaged && t.conn[2][1]->kind() == kTransportHostStaged);
+  CHECK(t.conn[0][1]->kind() == kTransportNvls && t.conn[3][2]->kind() == kTransportNvls);
+  CHECK(t.any(kTransportHostStaged) && !t.all(kTransportHostStaged) && t.scratch_in_host_memory());
+  CHECK(t.carries(kArRing) && t.carries(kAgRing) && !t.carries(kArTwoShot) && !t.carries(kAgPull) && !t.carries(kArNvlsTwo));
+  CHECK(t.carried_variants() == ((1u << kArRing) | (1u << kAgRing)));
+  CHECK(t.describe() == "host_staged x2, nvls x10");
+  // ... and the planner follows: whatever is asked for, a ring runs
+  {
+    Planner p;
+    p.load_defaults(true);
+    PlanInput in;
+    in.kind = kAllReduce; in.nranks = 4; in.count = 1 << 22; in.dtype = kFloat32;
+    in.carried_variants = t.carried_variants();
+    in.host_staged = t.scratch_in_host_memory();
+    in.p2p_possible = t.carries(kArTwoShot);
+    in.ring_channels = 2;
+    CHECK(p.plan(in).variant == kArRing);
+    in.requested_variant = kArTwoShot;
+    Plan pl = p.plan(in);
+    CHECK(pl.status == 0 && pl.variant == kArRing && !pl.note.empty());
+    in.kind = kAllGather; in.requested_variant = kAuto;
+    CHECK(p.plan(in).variant == kAgRing);
+  }
+  // a communicator that does not include the pair is not affected
+  t = connect_all(automatic, env, {0, 1, 3});
+  CHECK(t.all(kTransportNvls) && !t.scratch_in_host_memory());
+
+  // transport = "nvlink": no host-staged fall-back, the pair stays unconnected and is named
+  TransportCatalog nvlink_only("nvlink");
+  t = connect_all(nvlink_only, env, four);
+  CHECK(!t.complete() && t.unconnected_from == 1 && t.unconnected_to == 2);
+  access[1][2] = true;
+  CHECK(connect_all(nvlink_only, env, four).complete());
+
+  // transport = "host_staged": every connection, whatever the machine could do
+  TransportCatalog staged("host_staged");
+  t = connect_all(staged, env, four);
+  CHECK(t.all(kTransportHostStaged) && t.scratch_in_host_memory() && t.carries(kArRing) && !t.carries(kArOneShot));
+
+  // ranks that share a device (the single-GPU form) are peers by construction, never multicast
+  t = connect_all(automatic, env, {0, 0, 0});
+  CHECK(t.all(kTransportNvlinkP2P) && t.carries(kArTwoShot) && !t.carries(kArNvlsOne));
+  // a single rank has no connections and no limits
+  t = connect_all(automatic, env, {2});
+  CHECK(t.complete() && t.carries(kLocalCopy) && !t.scratch_in_host_memory() && t.describe() == "no connections");
+}
+
 static void test_ring_steps() {
   // 8 ranks, 1 channel, 512 KiB slots: a 16 MiB fp32 all-reduce needs
   // ceil(4Mi elems / (131072*8)) = 4 loops of 2*(8-1) steps.
@@ -403,6 +486,7 @@ int main() {
   test_toml_json();
   test_config();
   test_planner();
+  test_transports();
   test_ring_steps();
   test_qos();
   test_misc();

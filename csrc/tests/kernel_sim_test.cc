@@ -96,6 +96,11 @@ struct World {
     }
     return a;
   }
+  // After a kernel that ran to its end: no error, the completion word names this launch,
+  // and the counter of finished CTAs is back at zero (it wraps at the grid size).
+  int finished_cleanly(int r, uint64_t seq) const {
+    return status[(size_t)r]->error == 0 && status[(size_t)r]->done_seq == seq && pad[(size_t)r]->pad_[kPadCtaCounter] == 0 ? 0 : 1;
+  }
   void account_ring(int kind, uint64_t count, int esz, int nch) {
     const uint64_t steps = ring_steps_per_channel(kind, count, esz, n, nch, fifo_slot_bytes);
     for (int ch = 0; ch < nch; ch++) ring_steps[ch] += steps;
@@ -215,7 +220,7 @@ void allreduce_case(World& w, int variant, int op, size_t count, int ctas, int t
   }
   // every rank holds bit-identical results
   for (int r = 1; r < n; r++) bad += memcmp(a.recv[0], a.recv[r], count * sizeof(T)) != 0;
-  for (int r = 0; r < n; r++) bad += w.status[(size_t)r]->error != 0;
+  for (int r = 0; r < n; r++) bad += w.finished_cleanly(r, a.seq);
   if (bad) fprintf(stderr, "FAILED %s (n=%d count=%zu ctas=%d emulated=%d offset=%zu in_place=%d)\n", what, n, count, ctas,
                    (int)emulated, offset, (int)in_place);
   CHECK(bad == 0);
@@ -311,7 +316,7 @@ void allgather_case(World& w, int variant, size_t bytes, int ctas, int threads, 
     for (int s = 0; s < n; s++)
       for (size_t i = 0; i < bytes; i++)
         if (b.recv(r)[(size_t)s * bytes + i] != (uint8_t)(s * 37 + i * 11 + 1)) { bad++; break; }
-    bad += w.status[(size_t)r]->error != 0;
+    bad += w.finished_cleanly(r, a.seq);
   }
   if (bad) fprintf(stderr, "FAILED %s (n=%d bytes=%zu ctas=%d emulated=%d offset=%zu in_place=%d)\n", what, n, bytes, ctas,
                    (int)emulated, offset, (int)in_place);

@@ -198,6 +198,7 @@ inline uint64_t now_ns() {
 #define __syncthreads_or(p) sim::syncthreads_or(p)
 #define __nanosleep(ns) sim::spin_yield()
 
+inline void __threadfence() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
 inline unsigned atomicInc(unsigned* p, unsigned limit) {
   unsigned old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
   for (;;) {

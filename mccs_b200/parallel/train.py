@@ -1,7 +1,8 @@
 """Data-parallel training driver with synthetic data: ResNet-50 / VGG-16 (fp32, batch
 64 per GPU, 224x224x3 images ~N(0,1), labels uniform over 1000 classes) and
-GPT-2-medium (bf16 autocast, batch 8 per GPU, sequence 1024, token ids uniform over
-the vocabulary), random init, SGD. One rank per GPU:
+GPT-2-medium (bf16 parameters and therefore bf16 gradient buckets, batch 8 per GPU, sequence
+1024, token ids uniform over the vocabulary; ``--param-dtype fp32`` keeps fp32 parameters under
+bf16 autocast instead), random init, SGD. One rank per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 4 --master-addr 127.0.0.1 \
         -m mccs_b200.parallel.train --model resnet50 --comm-id 300 --steps 30
@@ -44,6 +45,8 @@ def main() -> int:
     ap.add_argument("--devices", default="", help="comma separated GPU index per rank (default: local rank)")
     ap.add_argument("--name", default="")
     ap.add_argument("--lr", type=float, default=0.01)
+    ap.add_argument("--param-dtype", default="auto", choices=["auto", "fp32", "bf16"],
+                    help="parameter (and gradient bucket) type; auto = bf16 for the language model, fp32 for the CNNs")
     ap.add_argument("--comm-ctas", type=int, default=0,
                     help="cap the CTAs of this job's collective kernels (a QoS quota set through the admin "
                          "endpoint), leaving the other SMs to backward; 0 = the planner's choice")
@@ -75,6 +78,9 @@ def main() -> int:
     batch = args.batch or (8 if lm else 64)
     torch.manual_seed(1234)          # identical initial weights on every rank
     model = models.build(args.model).to(device)
+    bf16_params = args.param_dtype == "bf16" or (args.param_dtype == "auto" and lm and cuda)
+    if bf16_params:
+        model.to(torch.bfloat16)      # gradients, and with them the buckets that are all-reduced, are bf16
     if cuda and not lm:
         model.to(memory_format=torch.channels_last)   # before gradient buckets are laid out
     model.train()
@@ -146,10 +152,10 @@ def main() -> int:
         else:
             opt.zero_grad(set_to_none=False)
         if lm:
-            with torch.autocast(device_type=device.type, dtype=torch.bfloat16, enabled=cuda):
+            with torch.autocast(device_type=device.type, dtype=torch.bfloat16, enabled=cuda and not bf16_params):
                 loss = fwd(inputs, targets)
         else:
-            loss = torch.nn.functional.cross_entropy(fwd(inputs), targets)
+            loss = torch.nn.functional.cross_entropy(fwd(inputs.to(torch.bfloat16) if bf16_params else inputs), targets)
         loss.backward()
         if ddp is not None:
             ddp.finish()
@@ -184,7 +190,7 @@ def main() -> int:
         ms = float(t.item())
     if rank == 0:
         out = {"name": args.name or args.model, "model": args.model, "backend": args.backend, "n_gpus": world,
-               "batch_per_gpu": batch, "ms_per_step": ms,
+               "batch_per_gpu": batch, "ms_per_step": ms, "param_dtype": "bf16" if bf16_params else "fp32",
                ("tokens_per_s" if lm else "images_per_s"): units * world / ms * 1e3,
                "first_loss": losses[0] if losses else None, "last_loss": losses[-1],
                "grad_bytes": ddp.gradient_bytes() if ddp is not None else sum(p.numel() * p.element_size() for p in model.parameters()),

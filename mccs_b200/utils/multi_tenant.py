@@ -43,6 +43,21 @@ def default_apps(ngpu: int) -> List[dict]:
     return [{"name": k, "comm_id": 900 + i, "devices": v, "weight": weights[k]} for i, (k, v) in enumerate(place.items())]
 
 
+def reference_setting(k: int) -> List[dict]:
+    """Placements of the reference's multi-application settings 1-4
+    (``eval/multi-app/gen_config.py:154-413``: four hosts with two GPUs each, jobs that share
+    hosts but never a GPU), with host i of the testbed mapped to the GPU pair (2i, 2i+1) of
+    one box. The jobs are equals (weight 1); the reference runs one 128 MB AllReduce per
+    iteration (``--batch 1 --bytes 134217728``)."""
+    place = {
+        1: {"blue": [0, 1, 2, 3], "red": [4, 5, 6, 7]},                      # two 4-GPU jobs on disjoint host pairs
+        2: {"blue": [0, 4, 2, 6], "green": [1, 3], "red": [5, 7]},            # a 4-GPU job on every host + two 2-GPU jobs
+        3: {"blue": [0, 4, 2, 6], "red": [1, 5, 3, 7]},                       # two 4-GPU jobs on the same four hosts
+        4: {"blue": [0, 1, 2, 3], "green": [4, 6], "red": [5, 7]},            # a 4-GPU job on two hosts + two 2-GPU jobs on the others
+    }[k]
+    return [{"name": n, "comm_id": 910 + 10 * k + i, "devices": d, "weight": 1.0} for i, (n, d) in enumerate(place.items())]
+
+
 def worker(a) -> int:
     import torch
     import torch.distributed as dist
@@ -122,6 +137,7 @@ def worker(a) -> int:
         q = comm.query()
         out["config_epoch"] = q["config_epoch"]
         out["async_error"] = q["async_error"]
+        out["launch"] = comm.launch_mode
         comm.destroy()
     else:
         dist.destroy_process_group()
@@ -133,7 +149,14 @@ def orchestrate(a) -> int:
     import torch
     import torch.distributed as dist
     ngpu = torch.cuda.device_count() if torch.cuda.is_available() else 0
-    apps = json.loads(a.apps) if a.apps else default_apps(max(ngpu, a.host_devices if ngpu == 0 else ngpu))
+    if a.apps:
+        apps = json.loads(a.apps)
+    elif a.setting:
+        apps = reference_setting(a.setting)
+        if ngpu and ngpu < 8:
+            raise SystemExit("the reference's settings place jobs on eight GPUs")
+    else:
+        apps = default_apps(max(ngpu, a.host_devices if ngpu == 0 else ngpu))
     total = sum(len(x["devices"]) for x in apps)
     import datetime
     store = dist.TCPStore("127.0.0.1", 0, is_master=True, timeout=datetime.timedelta(seconds=300), wait_for_workers=False)
@@ -173,7 +196,7 @@ def orchestrate(a) -> int:
         for line in out.splitlines():
             if line.startswith("RESULT "):
                 results.setdefault(name, []).append(json.loads(line[7:]))
-    summary = {"backend": a.backend, "qos": not a.no_qos and a.backend == "mccs", "iters": a.iters, "batch": a.batch,
+    summary = {"backend": a.backend, "qos": not a.no_qos and a.backend == "mccs", "setting": a.setting, "iters": a.iters, "batch": a.batch,
                "bytes": a.bytes, "apps": {}}
     for app in apps:
         rs = results.get(app["name"], [])
@@ -185,7 +208,7 @@ def orchestrate(a) -> int:
             "median_ms": max(r["median_ms"] for r in rs), "p99_ms": max(r["p99_ms"] for r in rs),
             "busbw_GBps": a.batch * a.bytes / mean / 1e6 * 2 * (len(app["devices"]) - 1) / max(len(app["devices"]), 1),
             "before_ms": rs[0].get("mean_before_ms"), "after_ms": rs[0].get("mean_after_ms"),
-            "config_epoch": rs[0].get("config_epoch"), "async_error": rs[0].get("async_error"),
+            "config_epoch": rs[0].get("config_epoch"), "async_error": rs[0].get("async_error"), "launch": rs[0].get("launch"),
             "finite": all(r["finite"] for r in rs),
         }
     # Jain's index over weight-normalised throughput (1.0 = shares exactly follow the weights)
@@ -210,6 +233,8 @@ def main() -> int:
     ap.add_argument("--reconfig-at", type=int, default=500)
     ap.add_argument("--reconfig-app", default="C")
     ap.add_argument("--apps", default="", help="JSON list of {name, comm_id, devices, weight}")
+    ap.add_argument("--setting", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="placement of the reference's multi-application setting 1-4 instead of the default scenario")
     ap.add_argument("--no-qos", action="store_true")
     ap.add_argument("--sync", default="auto", choices=["auto", "memops", "events"])
     ap.add_argument("--host-devices", type=int, default=4)

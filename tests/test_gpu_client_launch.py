@@ -3,11 +3,12 @@ process per GPU; each maps its peers' buffers, signal pads, status blocks and FI
 (exported VMM handles, shared registered host memory), loads `libmccs_kernels.so` and
 launches its own rank's kernel on its own stream from the plan the daemon published.
 
-Opt-in (`MCCS_TEST_CLIENT_LAUNCH=1`) until the mode has had its first run on a GPU box: the
-regular GPU suite must not depend on code that was only ever exercised on the CPU emulator
-(`tests/test_service_emulated_kernels.py::test_client_side_launch` covers the protocol and
-the daemon's side there). With one GPU only the single-rank copy can be launched by a
-client; several ranks on one GPU stay with the daemon's cooperative launch by design.
+This is what the daemon's default (`[b200] launch = "auto"`) gives every communicator whose
+ranks are separate processes on separate GPUs, so the first case runs with the default
+configuration and checks that the mode was chosen. With one GPU only the single-rank copy
+can be launched by a client; several ranks on one GPU stay with the daemon's cooperative
+launch by design. The second case adds the in-switch variants, for which each client maps
+the multicast objects the daemon created and bound (`client_nvls`, on by default).
 """
 import json
 import os
@@ -19,11 +20,7 @@ import torch
 
 from helpers import REPO, write_config
 
-OPT_IN = os.environ.get("MCCS_TEST_CLIENT_LAUNCH", "")
-pytestmark = [
-    pytest.mark.gpu,
-    pytest.mark.skipif(OPT_IN not in ("1", "nvls"), reason="opt-in: MCCS_TEST_CLIENT_LAUNCH=1 (or =nvls, after =1 has passed)"),
-]
+pytestmark = pytest.mark.gpu
 
 CLIENT = r"""
 import os, sys, json, torch
@@ -120,14 +117,12 @@ print("RESULT", json.dumps({"bad": bad, "seen": sorted(seen), "async_error": q["
 @pytest.mark.parametrize("nvls", [False, True])
 def test_client_side_launch_on_gpus(tmp_path, nvls):
     from mccs_b200 import daemon
-    if nvls and OPT_IN != "nvls":
-        pytest.skip("second step: MCCS_TEST_CLIENT_LAUNCH=nvls")
     n = min(torch.cuda.device_count(), 4)
     if nvls and n < 2:
         pytest.skip("multicast needs two GPUs")
     d = str(tmp_path)
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, wait_timeout_ms=2000,
-                       extra='launch = "client"' + ("\nclient_nvls = true" if nvls else ""))
+                       extra='launch = "client"\nclient_nvls = true' if nvls else "client_nvls = false")
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn", "NCCL_NVLS_ENABLE": "0"})
     try:
         env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), MCCS_LOG="error",

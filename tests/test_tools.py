@@ -162,10 +162,11 @@ def test_bench_script_contract_on_cpu():
         assert out["n_gpus"] == n and out["steps"] == 2 and out["warmup"] >= 3 and out["higher_is_better"] is True
         assert out["metric"] == "allreduce_algbw_GBps" and out["dtype"] == "bf16" and out["data"] == "synthetic"
         assert {"model", "global_batch", "seq_len", "parallelism"} <= set(out["config"])
-        assert out["config"]["parallelism"] == f"dp{n}" and out["config"]["verified"] is True
+        assert set(out["config"]) == {"model", "global_batch", "seq_len", "parallelism"}     # the same words in both arms
+        assert out["config"]["parallelism"] == f"dp{n}" and out["detail"]["verified"] is True
         assert {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"} <= set(out["e2e"])
         assert out["e2e"]["h2d_bytes_per_step"] > 0 and out["e2e"]["d2h_bytes_per_step"] > 0
-        assert out["gpu_launches"] == 2 * n and out["config"]["launch"] == "daemon"
+        assert out["gpu_launches"] == 2 * n and out["detail"]["launch"] == "daemon"
     ref = subprocess.run([sys.executable, "bench.py", "--impl", "reference", "--steps", "2", "--warmup", "1"],
                          capture_output=True, text=True, cwd=REPO, env=env, timeout=300)
     assert ref.returncode == 0

@@ -5,7 +5,8 @@ Who needs the entry point: callers that may not allocate when they reduce — in
 frozen or exhausted memory pool, in callbacks and latency-critical sections that must
 not enter the CUDA allocator. It keeps its synchronisation scratch in a static device
 array, so consecutive calls share state; two calls in a row check that the second one
-starts from a clean slate. This file is collected last on purpose: a failure here
+starts from a clean slate. Further cases: free device memory does not move across calls,
+the kernels' status words can be read back, and the aliasing rules. This file is collected last on purpose: a failure here
 leaves every other test already run."""
 import ctypes
 
@@ -71,6 +72,63 @@ def test_no_alloc_entry_matches_service(service, dtype, n, count):
         for r in range(n):
             assert torch.allclose(outputs[r].double(), want[r].double(), rtol=tol, atol=tol * n)
             assert torch.allclose(outputs[r].double(), ref, rtol=tol, atol=tol * n)
+
+
+class _Status(ctypes.Structure):
+    _fields_ = [("error", ctypes.c_uint * 8), ("peer", ctypes.c_uint * 8)]
+
+
+def test_no_alloc_entry_allocates_nothing_and_reports_status(service):
+    """The property the entry point exists for: once the set-up call has run, calls take no
+    device memory (free memory as the driver reports it and PyTorch's own counters are the
+    same before and after), and what the kernels reported can be read back."""
+    from mccs_b200 import _lib
+    lib = _lib.daemon_lib()
+    fn = _entry()
+    torch.cuda.set_device(0)
+    assert lib.mccsLocalAllReduceNoAllocPrepare() == 0
+    n, count = 4, 1 << 20
+    xs = [torch.full((count,), float(r + 1), device="cuda") for r in range(n)]
+    ys = [torch.empty_like(x) for x in xs]
+    ins = (ctypes.c_void_p * n)(*[x.data_ptr() for x in xs])
+    outs = (ctypes.c_void_p * n)(*[y.data_ptr() for y in ys])
+    stream = torch.cuda.current_stream()
+    st = _Status()
+    lib.mccsLocalAllReduceNoAllocStatus.argtypes = [ctypes.POINTER(_Status), ctypes.c_void_p]
+    assert fn(ins, outs, n, count, 7, ctypes.c_void_p(stream.cuda_stream)) == 0      # every kernel has run once
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    alloc0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(5):
+        assert fn(ins, outs, n, count, 7, ctypes.c_void_p(stream.cuda_stream)) == 0
+    assert lib.mccsLocalAllReduceNoAllocStatus(ctypes.byref(st), ctypes.c_void_p(stream.cuda_stream)) == 0
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"device memory in use changed by {free0 - free1} bytes"
+    assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == (alloc0, reserved0)
+    assert list(st.error) == [0] * 8 and list(st.peer) == [0] * 8
+    assert all(bool(torch.all(y == 10.0)) for y in ys)
+
+
+def test_no_alloc_entry_aliasing_rules(service):
+    """Any output may be exactly one of the inputs; partial overlaps are refused."""
+    fn = _entry()
+    torch.cuda.set_device(0)
+    count = 4096
+    a = torch.arange(count, dtype=torch.float32, device="cuda")
+    b = torch.ones(count + 64, dtype=torch.float32, device="cuda")
+    want = (a + 1).clone()
+    # crossed: out[0] is in[1] and out[1] is in[0]
+    ins = (ctypes.c_void_p * 2)(a.data_ptr(), b.data_ptr())
+    outs = (ctypes.c_void_p * 2)(b.data_ptr(), a.data_ptr())
+    assert fn(ins, outs, 2, count, 7, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(a, want) and torch.equal(b[:count], want)
+    # an output that starts inside an input, and two outputs sharing their range
+    shifted = (ctypes.c_void_p * 2)(b.data_ptr() + 64, a.data_ptr())
+    assert fn(ins, shifted, 2, count, 7, None) != 0
+    same_out = (ctypes.c_void_p * 2)(a.data_ptr(), a.data_ptr())
+    assert fn(ins, same_out, 2, count, 7, None) != 0
+    torch.cuda.synchronize()
 
 
 def test_no_alloc_entry_rejects_what_it_cannot_do(service):
