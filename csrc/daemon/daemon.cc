@@ -368,7 +368,7 @@ void Daemon::on_free(Session& s, const proto::FreeReq& m) {
     if (ut != alloc_use_.end()) {
       if (ut->second.busy.load(std::memory_order_acquire) > 0) {
         al.unlock();
-        LOG_WARN("client %llu: free of mem %llu refused, a queued collective still names it", (unsigned long long)s.id,
+        LOG_DEBUG("client %llu: free of mem %llu refused for now, a queued collective still names it", (unsigned long long)s.id,
                  (unsigned long long)m.mem_id);
         r.h.status = proto::kErrBusy;
         reply(s, r, sizeof(proto::FreeReply));

@@ -15,12 +15,13 @@ native library is an error.
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import Optional, Sequence
 
 import torch
 
 from .. import _lib
-from ..client import ALGOS, DTYPES, Communicator
+from ..client import ALGOS, DTYPES, Buffer, Communicator, backend
 
 VARIANTS = {
     "auto": "the planner's choice from the measured size -> (variant, CTAs) table",
@@ -41,26 +42,121 @@ VARIANTS = {
 assert set(VARIANTS) == set(ALGOS)
 
 
+def in_service_memory(t: torch.Tensor) -> bool:
+    """True when the tensor's storage was handed out by the daemon (``Buffer``, the memory
+    pool, the ``LD_PRELOAD`` hook): the kernels can then read and write it where it is."""
+    if t.numel() == 0:
+        return False
+    mem_id, off, size = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+    return _lib.shim().mccsMemInfo(ctypes.c_void_p(t.data_ptr()), ctypes.byref(mem_id), ctypes.byref(off), ctypes.byref(size)) == 0
+
+
+def usable_in_place(t: torch.Tensor) -> bool:
+    return t.is_contiguous() and t.dtype in DTYPES and in_service_memory(t)
+
+
+class _Arena:
+    """Staging memory of one communicator for tensors that do not live in service memory:
+    one service buffer that grows on demand, used under a lock (one staged collective of a
+    communicator at a time; the copies in and out are stream ordered like the collective)."""
+
+    def __init__(self, comm: Communicator):
+        self.comm = comm
+        self.buffer: Optional[Buffer] = None
+        self.lock = threading.Lock()
+
+    def get(self, nbytes: int) -> Buffer:
+        if self.buffer is None or self.buffer.nbytes < nbytes:
+            if self.buffer is not None:
+                if backend() == "cuda":
+                    torch.cuda.current_stream(self.comm.device).synchronize()    # work that still uses the old buffer
+                self.buffer.free()
+            self.buffer = Buffer(max(nbytes, 1 << 20) * 2, self.comm.device)
+        return self.buffer
+
+    def release(self) -> None:
+        if self.buffer is not None:
+            self.buffer.free()
+            self.buffer = None
+
+
+def arena(comm: Communicator) -> _Arena:
+    a = getattr(comm, "_ops_arena", None)
+    if a is None:
+        a = _Arena(comm)
+        comm._ops_arena = a
+    return a
+
+
 def all_reduce(comm: Communicator, send: torch.Tensor, recv: Optional[torch.Tensor] = None, *, op: str = "sum",
                scale: float = 1.0, algo: str = "auto", stream=None) -> torch.Tensor:
-    """AllReduce of ``send`` into ``recv`` (in place when ``recv`` is None) over ``comm``;
-    both tensors live in service memory (:class:`mccs_b200.Buffer`). Returns the output
-    tensor; like a kernel launch, the call returns before the result exists."""
-    comm.all_reduce(send, recv, op=op, scale=scale, algo=algo, stream=stream)
-    return send if recv is None else recv
+    """AllReduce of ``send`` into ``recv`` (in place when ``recv`` is None) over ``comm``.
+    Tensors in service memory (:class:`mccs_b200.Buffer`) are used where they are; any other
+    tensor (ordinary CUDA memory, unsupported element type such as bool, non-contiguous) is
+    staged through the communicator's arena: one copy in, the collective in place, one copy
+    out, all on the caller's stream. Returns the output tensor; like a kernel launch, the call
+    returns before the result exists."""
+    out = send if recv is None else recv
+    if send.numel() == 0:
+        return out
+    if usable_in_place(send) and (recv is None or usable_in_place(recv)):
+        comm.all_reduce(send, recv, op=op, scale=scale, algo=algo, stream=stream)
+        return out
+    work = send.dtype if send.dtype in DTYPES else torch.float32
+    n = send.numel()
+    ar = arena(comm)
+    with ar.lock:
+        st = ar.get(n * torch.empty((), dtype=work).element_size()).tensor(work, n)
+        st.copy_(send.reshape(-1), non_blocking=True)
+        comm.all_reduce(st, op=op, scale=scale, algo=algo, stream=stream)
+        out.copy_(st.view(out.shape) if out.dtype == work else st.to(out.dtype).view(out.shape), non_blocking=True)
+    return out
 
 
 def all_gather(comm: Communicator, send: torch.Tensor, recv: torch.Tensor, *, algo: str = "auto", stream=None) -> torch.Tensor:
-    """AllGather: rank r's ``send`` lands at ``recv[r * send.numel():]`` on every rank."""
-    comm.all_gather(send, recv, algo=algo, stream=stream)
+    """AllGather: rank r's ``send`` lands at ``recv[r * send.numel():]`` on every rank
+    (``recv`` holds ``nranks * send.numel()`` elements of the same type). Staged like
+    :func:`all_reduce` when a tensor is not in service memory."""
+    nb = send.numel() * send.element_size()
+    if nb == 0:
+        return recv
+    if usable_in_place(recv) and send.is_contiguous() and in_service_memory(send):
+        comm.all_gather(send, recv, nbytes=nb, algo=algo, stream=stream)
+        return recv
+    n, r = comm.nranks, comm.rank
+    ar = arena(comm)
+    with ar.lock:
+        full = ar.get(nb * n).bytes_tensor()[:nb * n]
+        mine = full[r * nb:(r + 1) * nb]
+        mine.copy_(send.contiguous().view(torch.uint8).reshape(-1), non_blocking=True)
+        comm.all_gather(mine, full, nbytes=nb, algo=algo, stream=stream)      # in place inside the staging buffer
+        if recv.is_contiguous():
+            recv.view(torch.uint8).reshape(-1).copy_(full, non_blocking=True)
+        else:
+            recv.copy_(full.view(recv.dtype).view(recv.shape), non_blocking=True)
     return recv
 
 
 def reduce_scatter(comm: Communicator, send: torch.Tensor, recv: torch.Tensor, *, op: str = "sum", scale: float = 1.0,
                    algo: str = "auto", stream=None) -> torch.Tensor:
     """ReduceScatter: ``send`` holds ``nranks`` blocks of ``recv.numel()`` elements; ``recv``
-    receives the reduction of this rank's block (in place when it is that block of ``send``)."""
-    comm.reduce_scatter(send, recv, op=op, scale=scale, algo=algo, stream=stream)
+    receives the reduction of this rank's block (in place when it is that block of ``send``).
+    Staged like :func:`all_reduce` when a tensor is not in service memory."""
+    if recv.numel() == 0:
+        return recv
+    if usable_in_place(send) and usable_in_place(recv):
+        comm.reduce_scatter(send, recv, op=op, scale=scale, algo=algo, stream=stream)
+        return recv
+    work = send.dtype if send.dtype in DTYPES else torch.float32
+    n, blk = comm.nranks, recv.numel()
+    esz = torch.empty((), dtype=work).element_size()
+    ar = arena(comm)
+    with ar.lock:
+        st = ar.get(n * blk * esz).tensor(work, n * blk)
+        st.copy_(send.reshape(-1), non_blocking=True)
+        mine = st[comm.rank * blk:(comm.rank + 1) * blk]
+        comm.reduce_scatter(st, mine, op=op, scale=scale, algo=algo, stream=stream)     # in place in the staging buffer
+        recv.copy_(mine.view(recv.shape) if recv.dtype == work else mine.to(recv.dtype).view(recv.shape), non_blocking=True)
     return recv
 
 
@@ -98,4 +194,5 @@ def local_all_reduce_no_alloc(inputs: Sequence[torch.Tensor], outputs: Optional[
     return outs
 
 
-__all__ = ["VARIANTS", "all_reduce", "all_gather", "reduce_scatter", "local_all_reduce_no_alloc"]
+__all__ = ["VARIANTS", "all_reduce", "all_gather", "reduce_scatter", "in_service_memory", "usable_in_place", "arena",
+           "local_all_reduce_no_alloc"]

@@ -53,7 +53,9 @@ class DataParallel:
         self.algo = algo
         self._cuda = backend() == "cuda"
         self._device = comm.device
-        self._stream = torch.cuda.Stream(device=self._device) if self._cuda else None
+        # High priority: the CTAs of a bucket's kernel wait for their peers on the other GPUs, so
+        # they should get SMs as soon as backward's kernels release some, not after its queue.
+        self._stream = torch.cuda.Stream(device=self._device, priority=-1) if self._cuda else None
         params = [p for p in module.parameters() if p.requires_grad]
         if broadcast_parameters and comm.nranks > 1:
             self._broadcast(params)

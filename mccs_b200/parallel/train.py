@@ -54,6 +54,9 @@ def main() -> int:
     ap.add_argument("--shard-optimizer", action="store_true",
                     help="ZeRO stage 1 over the service's ReduceScatter: reduce-scattered gradients, 1/n of the optimizer "
                          "state per rank, updated parameters all-gathered (mccs backend; not with --save/--resume)")
+    ap.add_argument("--sync-dir", default="", help="co-located jobs: directory in which every job drops '<name>.ready' after its "
+                    "warm-up; the timed steps start when --sync-jobs such files exist, so that the jobs' timed regions overlap")
+    ap.add_argument("--sync-jobs", type=int, default=0)
     ap.add_argument("--save", default="", help="after the run rank 0 writes model + optimizer state here (torch.save)")
     ap.add_argument("--resume", default="", help="load model + optimizer state written by --save before training")
     args = ap.parse_args()
@@ -171,6 +174,14 @@ def main() -> int:
     if cuda:
         torch.cuda.synchronize()
     barrier()
+    if args.sync_dir and args.sync_jobs > 1:
+        os.makedirs(args.sync_dir, exist_ok=True)
+        if rank == 0:
+            open(os.path.join(args.sync_dir, (args.name or args.model) + ".ready"), "w").close()
+        deadline = time.time() + 300
+        while len([f for f in os.listdir(args.sync_dir) if f.endswith(".ready")]) < args.sync_jobs and time.time() < deadline:
+            time.sleep(0.005)
+        barrier()
     t0 = time.perf_counter()
     if cuda:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

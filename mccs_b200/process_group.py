@@ -55,12 +55,8 @@ def _done(result) -> "dist.Work":
     return _create_work_from_future(fut)
 
 
-def in_service_memory(t: torch.Tensor) -> bool:
-    """True when the tensor's storage was allocated by the daemon."""
-    if t.numel() == 0:
-        return False
-    mem_id, off, size = c_uint64(), c_uint64(), c_uint64()
-    return _lib.shim().mccsMemInfo(c_void_p(t.data_ptr()), byref(mem_id), byref(off), byref(size)) == 0
+from .ops import all_gather as _ops_all_gather, all_reduce as _ops_all_reduce, arena as _arena, in_service_memory  # noqa: E402
+from .ops import reduce_scatter as _ops_reduce_scatter  # noqa: E402
 
 
 def empty(numel: int, dtype: torch.dtype, device: int = 0):
@@ -108,56 +104,21 @@ class ProcessGroupMCCS(dist.ProcessGroup):
                 comm_id = int(store.get("mccs_comm_id").decode())
         self.comm_id = comm_id
         self._comm = Communicator(comm_id, rank, size, device=self._device)
-        self._staging: Optional[Buffer] = None
         self._lock = threading.Lock()
 
-    # -- helpers -------------------------------------------------------------------
-    def _stage(self, nbytes: int) -> Buffer:
-        if self._staging is None or self._staging.nbytes < nbytes:
-            if self._staging is not None:
-                self._sync()
-                self._staging.free()
-            self._staging = Buffer(max(nbytes, 1 << 20) * 2, self._device)
-        return self._staging
-
+    # -- helpers: the functional collectives of mccs_b200.ops do the work, in place for tensors
+    # in service memory, through the communicator's staging arena otherwise -------------------
     def _sync(self) -> None:
         if self._cuda:
             torch.cuda.current_stream(self._device).synchronize()
 
-    def _usable_in_place(self, t: torch.Tensor) -> bool:
-        return t.is_contiguous() and in_service_memory(t) and t.dtype in client.DTYPES
-
     def _all_reduce_flat(self, t: torch.Tensor, op: str) -> None:
-        """t: contiguous tensor; reduced in place (through staging when needed)."""
-        if t.numel() == 0:
-            return
-        if self._usable_in_place(t):
-            self._comm.all_reduce(t, op=op)
-            return
-        dtype = t.dtype
-        work_dtype = dtype if dtype in client.DTYPES else torch.float32
-        nbytes = t.numel() * torch.empty((), dtype=work_dtype).element_size()
-        with self._lock:
-            st = self._stage(nbytes).tensor(work_dtype, t.numel())
-            st.copy_(t.reshape(-1), non_blocking=True)
-            self._comm.all_reduce(st, op=op)
-            t.reshape(-1).copy_(st, non_blocking=True)
+        """t: contiguous tensor, reduced in place."""
+        _ops_all_reduce(self._comm, t, op=op)
 
     def _all_gather_flat(self, out: torch.Tensor, inp: torch.Tensor) -> None:
         """out: contiguous, size * inp.numel() elements of the same dtype."""
-        nb = inp.numel() * inp.element_size()
-        if nb == 0:
-            return
-        if self._usable_in_place(out) and inp.is_contiguous() and in_service_memory(inp):
-            self._comm.all_gather(inp, out, nbytes=nb)
-            return
-        with self._lock:
-            stage = self._stage(nb * self._size)
-            full = stage.bytes_tensor()[:nb * self._size]
-            mine = full[self._rank * nb:(self._rank + 1) * nb]
-            mine.copy_(inp.contiguous().view(torch.uint8).reshape(-1), non_blocking=True)
-            self._comm.all_gather(mine, full, nbytes=nb)      # in place inside the staging buffer
-            out.view(torch.uint8).reshape(-1).copy_(full, non_blocking=True)
+        _ops_all_gather(self._comm, inp, out)
 
     # -- c10d interface --------------------------------------------------------------
     def getBackendName(self) -> str:
@@ -226,24 +187,8 @@ class ProcessGroupMCCS(dist.ProcessGroup):
         return _done(outputs)
 
     def _reduce_scatter_flat(self, out: torch.Tensor, full: torch.Tensor, op: str) -> None:
-        """full: contiguous, size * out.numel() elements; out receives the reduction of this
-        rank's block. Through the service's own reduce-scatter (half the traffic of the
-        all-reduce this used to be); tensors outside service memory are staged."""
-        n = out.numel()
-        if n == 0:
-            return
-        if self._usable_in_place(full) and self._usable_in_place(out) and out.dtype == full.dtype:
-            self._comm.reduce_scatter(full, out, op=op)
-            return
-        dtype = full.dtype
-        work_dtype = dtype if dtype in client.DTYPES else torch.float32
-        esz = torch.empty((), dtype=work_dtype).element_size()
-        with self._lock:
-            st = self._stage(n * self._size * esz).tensor(work_dtype, n * self._size)
-            st.copy_(full.reshape(-1), non_blocking=True)
-            mine = st[self._rank * n:(self._rank + 1) * n]
-            self._comm.reduce_scatter(st, mine, op=op)           # in place inside the staging buffer
-            out.reshape(-1).copy_(mine, non_blocking=True) if out.is_contiguous() else out.copy_(mine.reshape(out.shape))
+        """full: contiguous, size blocks of out.numel() elements; out receives this rank's block."""
+        _ops_reduce_scatter(self._comm, full, out, op=op)
 
     def reduce_scatter(self, output_tensors, input_tensors, opts=ReduceScatterOptions()):
         op = _op_name(opts.reduceOp)
@@ -270,9 +215,7 @@ class ProcessGroupMCCS(dist.ProcessGroup):
 
     def shutdown(self) -> None:
         self._sync()
-        if self._staging is not None:
-            self._staging.free()
-            self._staging = None
+        _arena(self._comm).release()
         self._comm.destroy()
 
     def __repr__(self) -> str:

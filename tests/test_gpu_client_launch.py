@@ -98,6 +98,29 @@ if os.environ.get("NVLS") == "1" and n > 1:
         allreduce(algo, "f32", 8192, in_place=True)
     for nbytes in (16, 4096, 1 << 20):
         allgather("ag_nvls", nbytes)
+# 200 collectives back to back on poisoned outputs, checked on the device after every one
+# (the ordering stress of tests/test_gpu_collectives.py, here with kernels launched by the
+# clients and, in the second case, through the multicast mappings each client made itself)
+if n > 1:
+    cnt = 300000
+    bad_count = torch.zeros((), dtype=torch.int64, device="cuda")
+    sa = send.tensor(torch.float32, cnt); da = recv.tensor(torch.float32, cnt)
+    stress = ("ar_nvls_twoshot", "ar_twoshot") if os.environ.get("NVLS") == "1" else ("ar_twoshot",)
+    for algo in stress:
+        for it in range(200):
+            sa.fill_(float(rank + 1) + 0.25 * it); da.fill_(float("nan"))
+            comm.all_reduce(sa, da, algo=algo)
+            bad_count += (da != float(n * (n + 1) // 2) + 0.25 * it * n).sum()
+    sg = send.tensor(torch.uint8, cnt); dg = recv.tensor(torch.uint8, cnt * n)
+    for algo in (("ag_nvls", "ag_push") if os.environ.get("NVLS") == "1" else ("ag_push",)):
+        for it in range(200):
+            sg.fill_((rank * 31 + it) % 251); dg.fill_(255)
+            comm.all_gather(sg, dg, algo=algo)
+            for q in range(n):
+                bad_count += (dg[q * cnt:(q + 1) * cnt] != (q * 31 + it) % 251).sum()
+    torch.cuda.synchronize()
+    if int(bad_count.item()) != 0:
+        bad.append(("stress", int(bad_count.item())))
 # back to back on the stream without looking at the results in between
 t = send.tensor(torch.float32, 1 << 16)
 t.fill_(1.0)

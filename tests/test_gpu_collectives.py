@@ -264,3 +264,53 @@ def test_allgather_multi_gpu(svc, algo):
     for nbytes in (4096, 1 << 20, 8 << 20):
         _allgather_case(svc, n, nbytes, algo, list(range(n)), in_place=False)
     _allgather_case(svc, n, 1 << 20, algo, list(range(n)), in_place=True)
+
+
+@multi
+@pytest.mark.parametrize("algo", ["ar_nvls_twoshot", "ar_twoshot", "ag_nvls", "ag_push"])
+def test_back_to_back_on_poisoned_buffers_multi_gpu(svc, algo):
+    """200 collectives back to back on each rank's stream with no host synchronisation in
+    between: before every call the output is poisoned (NaN / 0xFF) and the input changes, after
+    every call a kernel on the same stream counts the elements that differ from what that
+    iteration must produce. This is the ordering stress for the kernels whose last remote
+    stores are followed only by the closing barrier's flag (multimem.st, then a unicast
+    release store): a store that could still be in flight when the peer passes the barrier
+    shows up as a poisoned or stale element in some iteration."""
+    n = min(_ngpu(), 8)
+    nvls = "nvls=on" in svc.daemon.describe_embedded()
+    if "nvls" in algo and not nvls:
+        pytest.skip("this box has no NVLS multicast")
+    cid = fresh_comm_id()
+    is_ar = algo.startswith("ar_")
+    count = 300000            # fp32 elements (AllReduce) / bytes per rank (AllGather): 16-byte multiples, several CTAs
+
+    def rank_fn(r):
+        _own_stream(r)
+        if is_ar:
+            a, b = svc.Buffer(count * 4, r), svc.Buffer(count * 4, r)
+            s, d = a.tensor(torch.float32, count), b.tensor(torch.float32, count)
+        else:
+            a, b = svc.Buffer(count, r), svc.Buffer(count * n, r)
+            s, d = a.tensor(torch.uint8, count), b.tensor(torch.uint8, count * n)
+        comm = svc.Communicator(cid, r, n, device=r)
+        bad = torch.zeros((), dtype=torch.int64, device=f"cuda:{r}")
+        for it in range(200):
+            if is_ar:
+                s.fill_(float(r + 1) + 0.25 * it)
+                d.fill_(float("nan"))
+                comm.all_reduce(s, d, algo=algo)
+                want = float(n * (n + 1) // 2) + 0.25 * it * n
+                bad += (d != want).sum()
+            else:
+                s.fill_((r * 31 + it) % 251)
+                d.fill_(255)
+                comm.all_gather(s, d, algo=algo)
+                for q in range(n):
+                    bad += (d[q * count:(q + 1) * count] != (q * 31 + it) % 251).sum()
+        torch.cuda.synchronize()
+        q = comm.query()
+        comm.destroy()
+        return int(bad.item()), q["async_error"], q["device_error"]
+
+    for bad, async_error, device_error in run_ranks(n, rank_fn, timeout=300.0):
+        assert bad == 0 and async_error == 0 and device_error == 0
