@@ -155,17 +155,28 @@ eval-tune: all          # measures a tuning table and merges it into configs/tun
 	$(TORCHRUN) --master-port 29602 -m mccs_b200.utils.sweep --mode tune --dtypes bf16 --out $(OUT_DIR)/tune_$(NGPU).csv \
 	    --tuning $(OUT_DIR)/tuning_$(NGPU).json --merge-into configs/tuning_b200.json
 
-eval-multi: all         # four co-located tenants under QoS weights, then the same as independent NCCL groups
+eval-multi: all         # four co-located tenants under QoS weights, without the arbiter, and as independent NCCL groups; the reference's settings 1-4
 	@mkdir -p $(OUT_DIR)
 	$(PY) -m mccs_b200.utils.multi_tenant --iters 1000 > $(OUT_DIR)/multi_mccs.json
+	$(PY) -m mccs_b200.utils.multi_tenant --iters 1000 --reconfig-at -1 --no-qos > $(OUT_DIR)/multi_mccs_noqos.json
 	$(PY) -m mccs_b200.utils.multi_tenant --iters 1000 --backend nccl > $(OUT_DIR)/multi_nccl.json
+	for s in 1 2 3 4; do \
+	  $(PY) -m mccs_b200.utils.multi_tenant --setting $$s --batch 1 --bytes 134217728 --iters 300 --reconfig-at -1 > $(OUT_DIR)/setting$${s}_mccs.json; \
+	  $(PY) -m mccs_b200.utils.multi_tenant --setting $$s --batch 1 --bytes 134217728 --iters 300 --backend nccl > $(OUT_DIR)/setting$${s}_nccl.json; \
+	done
 
 eval-dynamic: all       # a running job whose ring is reversed by the admin tool
 	$(PY) -m mccs_b200.utils.launcher --benchmark configs/launch/reconfig.toml --output-dir $(OUT_DIR)
 
-eval-colocate: all      # ResNet-50 and VGG-16 data-parallel jobs side by side; GPT-2-medium with a ResNet-50 neighbour
-	$(PY) -m mccs_b200.utils.launcher --benchmark configs/launch/colocate_cnn.toml --output-dir $(OUT_DIR)
-	$(PY) -m mccs_b200.utils.launcher --benchmark configs/launch/gpt2_with_resnet.toml --output-dir $(OUT_DIR)
+eval-traces: all        # the VGG + 2 x GPT traces side by side under fair / qosv1 / qosv2: job completion times
+	@mkdir -p $(OUT_DIR)
+	$(PY) -m mccs_b200.utils.colocate_traces --scale 1.0 --out $(OUT_DIR)/jct.json
+
+eval-colocate: all      # ResNet-50 next to VGG-16; GPT-2-medium alone and with a ResNet-50 neighbour; service and NCCL
+	@mkdir -p $(OUT_DIR)
+	for sc in cnn gpt gpt-with-resnet; do for be in mccs nccl; do \
+	  $(PY) -m mccs_b200.utils.colocate_train --scenario $$sc --backend $$be > $(OUT_DIR)/colocate_$${sc}_$$be.json; \
+	done; done
 
 eval-latency: all       # where the time of a small collective goes
 	$(TORCHRUN) --master-port 29603 -m mccs_b200.utils.latency --bytes 64K
@@ -173,5 +184,5 @@ eval-latency: all       # where the time of a small collective goes
 clean:
 	rm -rf build $(OUT)/*.so $(OUT)/mccsd $(APP_BINS) $(OUT)/host_tests
 
-.PHONY: all clean simtest tsan asan eval-single eval-tune eval-multi eval-dynamic eval-colocate eval-latency
+.PHONY: all clean simtest tsan asan eval-single eval-tune eval-multi eval-dynamic eval-traces eval-colocate eval-latency
 .SECONDARY:

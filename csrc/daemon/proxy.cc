@@ -254,6 +254,10 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
     const CollOp& o = s.ops[r];
     if (o.kind != o0.kind || o.count != o0.count || (kind_reduces(o0.kind) && (o.dtype != o0.dtype || o.op != o0.op)))
       return fail(proto::kErrMismatch);
+    // The multiplier of PreMulSum / SumPostDiv is one per collective (the kernels apply the
+    // same factor to every source): ranks that pass different factors disagree.
+    if (kind_reduces(o0.kind) && (o0.op == kPreMulSum || o0.op == kSumPostDiv) && o.scale != o0.scale)
+      return fail(proto::kErrMismatch);
   }
   Backend* be = daemon_->backend();
   const bool host_backend = be->kind() == proto::kBackendHost;

@@ -465,6 +465,29 @@ static void test_qos() {
   s.complete(2, 2 << 20);
   CHECK(s.admit(1, 1 << 20, 4, 0, 200) == kQosAdmit);            // alone, even more CTAs than SMs are its own business
   CHECK(s.stats()["tenants"]["2"]["deferred_residency"].as_int() == 2);
+  // Generation: moves on what can turn a deferral into an admission (a completion, another
+  // tenant's admission, a policy change), so that a deferred request need not poll the lock.
+  {
+    QosArbiter q2;
+    Config c2 = Config::from_string("[qos]\nmax_outstanding_bytes = 1048576\n");
+    q2.configure(c2);
+    q2.tenant_register(1, {0});
+    q2.tenant_register(2, {0});
+    const uint64_t g0 = q2.generation();
+    CHECK(q2.admit(1, 1 << 20, 1000, 0, 8) == kQosAdmit);
+    const uint64_t g1 = q2.generation();
+    CHECK(g1 != g0);                                         // an admission
+    q2.note_waiting(2, 1001);
+    CHECK(q2.admit(1, 1 << 20, 1002, 0, 8) == kQosDeferBacklog);
+    CHECK(q2.generation() == g1);                            // a deferral changes nothing
+    q2.complete(1, 1 << 20);
+    CHECK(q2.generation() != g1);                            // a completion
+    const uint64_t g2 = q2.generation();
+    QosTenantConfig tc;
+    tc.weight = 3.0;
+    q2.set_tenant(2, tc);
+    CHECK(q2.generation() != g2);                            // a policy change
+  }
 }
 
 static void test_misc() {

@@ -189,6 +189,37 @@ def test_mismatch_is_an_error_not_a_hang(service):
     assert codes == [-8, -8]      # mccsMismatch on both ranks
 
 
+def test_ranks_must_agree_on_the_scale_factor(service):
+    """PreMulSum's multiplier is one per collective (every source gets the same factor): ranks
+    that pass different factors get mccsMismatch instead of rank 0's factor silently."""
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    cid = fresh_comm_id()
+
+    def rank_fn(r):
+        buf = M.Buffer(4096, r)
+        t = buf.tensor(torch.float32, 1024)
+        t.fill_(1.0)
+        c = M.Communicator(cid, r, 2, device=r)
+        try:
+            c.all_reduce(t, op="premulsum", scale=0.5)
+            agreed = float(t[0])
+            c2 = None
+        except M.client._lib.MccsError as e:
+            c.destroy()
+            return ("first", e.code)
+        try:
+            c.all_reduce(t, op="premulsum", scale=0.5 if r == 0 else 0.25)
+            return ("none", agreed)
+        except M.client._lib.MccsError as e:
+            return (agreed, e.code)
+        finally:
+            c.destroy()
+
+    assert run_ranks(2, rank_fn) == [(1.0, -8), (1.0, -8)]
+
+
 def test_buffer_must_come_from_the_service(service):
     M = service
     if M.backend() != "host":
