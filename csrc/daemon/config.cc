@@ -116,7 +116,7 @@ Config Config::from_value(const Value& root) {
                {"transport", "nvls", "vmm", "sync", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
                 "host_devices", "force_host_backend", "idle_sleep_us", "idle_spin_us", "pin_threads", "init_timeout_ms", "fuse_allreduce", "client_nvls",
                 "single_through_fused", "skip_start_barrier", "kernel_writes_done", "host_kernels",
-                "hybrid_nvls_permille", "hybrid_nvls_ctas", "launch", "nvls_unroll"},
+                "hybrid_nvls_permille", "hybrid_nvls_ctas", "launch", "nvls_unroll", "pack_bytes"},
                "[b200]");
     c.transport = b["transport"].as_string(c.transport);
     if (c.transport != "auto" && c.transport != "nvlink" && c.transport != "host_staged")
@@ -145,6 +145,8 @@ Config Config::from_value(const Value& root) {
     c.hybrid_nvls_ctas = (int)b["hybrid_nvls_ctas"].as_int(c.hybrid_nvls_ctas);
     c.nvls_unroll = (int)b["nvls_unroll"].as_int(c.nvls_unroll);
     if (c.nvls_unroll != 4 && c.nvls_unroll != 8) throw std::runtime_error("b200.nvls_unroll must be 4 or 8");
+    c.pack_bytes = (int)b["pack_bytes"].as_int(c.pack_bytes);
+    if (c.pack_bytes != 16 && c.pack_bytes != 32) throw std::runtime_error("b200.pack_bytes must be 16 or 32");
     if (c.hybrid_nvls_permille < 0 || c.hybrid_nvls_permille > 1000 || c.hybrid_nvls_ctas < 0 || c.hybrid_nvls_ctas > kMaxCtas)
       throw std::runtime_error("b200.hybrid_nvls_permille must be 0..1000 and hybrid_nvls_ctas 0..148");
     c.single_through_fused = b["single_through_fused"].as_bool(c.single_through_fused);

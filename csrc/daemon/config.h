@@ -98,6 +98,7 @@ struct Config {
   // Experiments on the per-call floor; they act on launches that go through the fused
   // kernels only (kernels/batch.cuh) and are all off by default.
   int hybrid_nvls_permille = 750;     // ar_hybrid: share of the message that goes through the switch (1/1000)
+  int pack_bytes = 16;             // two-shot AllReduce and AllGather pull/push kernels: bytes per load/store instruction (16, or 32 = sm_100's 256-bit form)
   int nvls_unroll = 4;                // NVLS all-reduce kernels: in-switch loads in flight per thread (4 or 8)
   int hybrid_nvls_ctas = 8;           // ar_hybrid: CTAs that feed the switch; the others exchange the rest by peer copies
   bool single_through_fused = false;  // a lone two-shot AllReduce also uses the fused kernel (one member)

@@ -626,6 +626,8 @@ void ProxyEngine::fill_args(Communicator& c, CollSlot& s, int rank, int slice, C
     a.unroll_hint = (int32_t)(((uint32_t)nvls_ctas << 16) | (uint32_t)cfg.hybrid_nvls_permille);
   } else if (s.plan.variant == kArNvlsOne || s.plan.variant == kArNvlsTwo) {
     a.unroll_hint = daemon_->config().nvls_unroll;
+  } else if (s.plan.variant == kAgPull || s.plan.variant == kAgPush || s.plan.variant == kArTwoShot) {
+    a.unroll_hint = daemon_->config().pack_bytes;
   }
   a.fifo_slot_bytes = c.fifo_slot_bytes;
   memcpy(a.ring, s.ring, sizeof a.ring);
@@ -835,6 +837,8 @@ bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
     m.variant_hint = (int32_t)(((uint32_t)nvls_ctas << 16) | (uint32_t)cfg.hybrid_nvls_permille);
   } else if (s.plan.variant == kArNvlsOne || s.plan.variant == kArNvlsTwo) {
     m.variant_hint = daemon_->config().nvls_unroll;
+  } else if (s.plan.variant == kAgPull || s.plan.variant == kAgPush || s.plan.variant == kArTwoShot) {
+    m.variant_hint = daemon_->config().pack_bytes;
   }
   if (s.plan.needs_mc_send) { m.mc_send_id = s.mc_send_id; m.mc_send_off = s.ops[rs.rank].send_off; }
   if (s.plan.needs_mc_recv) { m.mc_recv_id = s.mc_recv_id; m.mc_recv_off = s.ops[rs.rank].recv_off; }

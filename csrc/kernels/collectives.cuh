@@ -115,6 +115,12 @@ __device__ __forceinline__ bool all_aligned16(const CollArgs& a, uint64_t extra 
   return (bits & 15u) == 0;
 }
 
+__device__ __forceinline__ bool all_aligned32(const CollArgs& a) {
+  uint64_t bits = 0;
+  for (int r = 0; r < a.nranks; r++) bits |= (uint64_t)a.send[r] | (uint64_t)a.recv[r];
+  return (bits & 31u) == 0;
+}
+
 __device__ __forceinline__ void trace_begin(const CollArgs& a, int rank) {
   if (a.trace && blockIdx.x == 0 && threadIdx.x == 0)
     st_relaxed_sys_u64(&a.status[rank]->start_ns, globaltimer_ns());
@@ -189,7 +195,17 @@ __global__ void __launch_bounds__(kMaxThreads) ar_twoshot_kernel(const __grid_co
   Scaler<typename AccOf<T>::type> sc{scaler_mode(a.op), a.scale};
   constexpr int kN = 16 / (int)sizeof(T);
   uint64_t done = 0;
-  if (all_aligned16(a)) {
+  if (a.unroll_hint == 32 && all_aligned32(a)) {
+    // 256-bit packs (the daemon's `pack_bytes = 32`): 1 KiB per warp and instruction.
+    constexpr int kN32 = 32 / (int)sizeof(T);
+    const uint64_t nv = a.count / kN32;
+    Range mine = split_range(nv, a.nranks, rank);
+    if (a.nranks > 4)
+      reduce_store<T, Op, 32, 1, kMaxRanks>(s_src, a.nranks, s_dst, a.nranks, mine.beg, mine.end, blockIdx.x, gridDim.x, sc);
+    else
+      reduce_store<T, Op, 32, 2, 4>(s_src, a.nranks, s_dst, a.nranks, mine.beg, mine.end, blockIdx.x, gridDim.x, sc);
+    done = nv * kN32;
+  } else if (all_aligned16(a)) {
     const uint64_t nv = a.count / kN;
     Range mine = split_range(nv, a.nranks, rank);
     reduce_store_auto<T, Op, 16>(s_src, a.nranks, s_dst, a.nranks, mine.beg, mine.end,
@@ -467,6 +483,11 @@ __global__ void __launch_bounds__(kMaxThreads) ag_direct_kernel(const __grid_con
 
   const bool in_place = (const char*)a.send[rank] == (const char*)a.recv[rank] + (uint64_t)rank * a.count;
   const bool aligned = all_aligned16(a, a.count);
+  // 256-bit packs (CollArgs::unroll_hint == 32, set by the daemon's `pack_bytes`): half as
+  // many instructions and 1 KiB per warp and store, for buffers and sizes that allow it.
+  uint64_t bits32 = a.count;
+  for (int r = 0; r < n; r++) bits32 |= (uint64_t)a.send[r] | (uint64_t)a.recv[r];
+  const bool wide = MODE != kAgModeNvls && a.unroll_hint == 32 && (bits32 & 31u) == 0;
   const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
   const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
 
@@ -484,7 +505,7 @@ __global__ void __launch_bounds__(kMaxThreads) ag_direct_kernel(const __grid_con
           if (s < n && !(in_place && s == rank)) st_data<B>(s_dst[s] + i * B, v[s]);
       }
     } else {
-      constexpr int U = B == 16 ? 4 : 1;
+      constexpr int U = B == 16 ? 4 : B == 32 ? 2 : 1;
       uint64_t i = first;
       auto emit = [&](uint64_t idx, Raw<B> v) {
         if (MODE == kAgModeNvls) {
@@ -507,7 +528,8 @@ __global__ void __launch_bounds__(kMaxThreads) ag_direct_kernel(const __grid_con
     }
   };
   // The planner only selects the NVLS mode for 16-byte aligned buffers and sizes.
-  if (aligned) run(std::integral_constant<int, 16>{});
+  if (wide) run(std::integral_constant<int, 32>{});
+  else if (aligned) run(std::integral_constant<int, 16>{});
   else if (MODE != kAgModeNvls) run(std::integral_constant<int, 1>{});
   else if (threadIdx.x == 0) report_error(a.status[rank], kDevBadArgs, 0);
 

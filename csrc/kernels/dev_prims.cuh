@@ -77,6 +77,7 @@ template <> struct Raw<2> { uint16_t x; };
 template <> struct Raw<4> { uint32_t x; };
 template <> struct Raw<8> { uint64_t x; };
 template <> struct alignas(16) Raw<16> { uint32_t x, y, z, w; };
+template <> struct alignas(32) Raw<32> { uint32_t a[8]; };   // sm_100 has 256-bit global loads and stores
 
 template <int BYTES> __device__ __forceinline__ Raw<BYTES> ld_data(const void* p);
 template <int BYTES> __device__ __forceinline__ void st_data(void* p, Raw<BYTES> v);
@@ -107,6 +108,17 @@ template <> __device__ __forceinline__ Raw<16> ld_data<16>(const void* p) {
                : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                : "l"(p));
   return r;
+}
+template <> __device__ __forceinline__ Raw<32> ld_data<32>(const void* p) {
+  Raw<32> r;
+  asm volatile("ld.relaxed.sys.global.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r.a[0]), "=r"(r.a[1]), "=r"(r.a[2]), "=r"(r.a[3]), "=r"(r.a[4]), "=r"(r.a[5]), "=r"(r.a[6]), "=r"(r.a[7])
+               : "l"(p));
+  return r;
+}
+template <> __device__ __forceinline__ void st_data<32>(void* p, Raw<32> v) {
+  asm volatile("st.relaxed.sys.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.a[0]), "r"(v.a[1]),
+               "r"(v.a[2]), "r"(v.a[3]), "r"(v.a[4]), "r"(v.a[5]), "r"(v.a[6]), "r"(v.a[7]));
 }
 template <> __device__ __forceinline__ void st_data<1>(void* p, Raw<1> v) {
   asm volatile("st.relaxed.sys.global.u8 [%0], %1;" ::"l"(p), "r"((uint32_t)v.x));

@@ -120,7 +120,8 @@ struct CollArgs {
   uint64_t timeout_ns;     // bound for every device-side wait
   int32_t trace;           // 1: record globaltimer start/end into the status block
   int32_t unroll_hint;     // ar_hybrid: low 16 bits = share of the message for the multimem part (1/1000), high 16 bits = its CTAs;
-                           // the NVLS all-reduce kernels: in-switch loads in flight per thread (8, or 4 for any other value)
+                           // the NVLS all-reduce kernels: in-switch loads in flight per thread (8, or 4 for any other value);
+                           // all-gather pull/push: 32 = 256-bit loads and stores where buffers and size allow
   // --- buffers (unicast addresses valid on every GPU of the communicator) -----
   const void* send[kMaxRanks];
   void* recv[kMaxRanks];

@@ -55,6 +55,10 @@ template <> struct Dt<__half> {
 
 // What one communicator owns: pads, status blocks, FIFOs, and the running counters the
 // daemon keeps (barrier epoch, tickets, ring steps).
+// CollArgs::unroll_hint for the cases that follow (0 = the kernels' default paths; 32 = 256-bit
+// packs in two-shot and pull/push; 8 = deeper unroll of the in-switch kernels).
+static int g_unroll_hint = 0;
+
 struct World {
   int n;
   std::vector<SignalPad*> pad;
@@ -88,6 +92,7 @@ struct World {
     a.epoch = epoch;
     epoch += 2;
     a.timeout_ns = 20ull * 1000 * 1000 * 1000;
+    a.unroll_hint = g_unroll_hint;
     for (int r = 0; r < n; r++) { a.pad[r] = pad[(size_t)r]; a.status[r] = status[(size_t)r]; a.fifo[r] = fifo[(size_t)r]; }
     a.fifo_slot_bytes = fifo_slot_bytes;
     for (int ch = 0; ch < kMaxRingChannels; ch++) {
@@ -654,6 +659,31 @@ void random_cases(unsigned seed, int iterations) {
 }  // namespace
 
 int main() {
+
+  // The wide-pack and deep-unroll forms of the kernels: 256-bit loads and stores in two-shot,
+  // pull and push (sizes that are and are not multiples of 32 bytes, in place, every rank
+  // count), eight in-switch loads in flight in the NVLS kernels.
+  for (int hint : {32, 8}) {
+    g_unroll_hint = hint;
+    for (int n : {2, 3, 4, 8})
+      for (bool emulated : {true, false}) {
+        World w(n);
+        for (size_t count : {(size_t)8, (size_t)1000, (size_t)4099, (size_t)65536 + 24}) {
+          if (hint == 32) {
+            allreduce_case<float, OpSum>(w, kArTwoShot, kSum, count, 3, 64, emulated, 0, false, "twoshot f32 wide");
+            allreduce_case<__nv_bfloat16, OpSum>(w, kArTwoShot, kSumPostDiv, count, 2, 96, emulated, 0, true, "twoshot bf16 wide in place avg");
+            allreduce_case<int32_t, OpMax>(w, kArTwoShot, kMax, count, 4, 32, emulated, 0, false, "twoshot i32 wide max");
+            allgather_case(w, kAgPush, count * 4, 3, 64, emulated, 0, false, "ag push wide");
+            allgather_case(w, kAgPull, count * 4, 2, 64, emulated, 0, true, "ag pull wide in place");
+            allgather_case(w, kAgPush, count * 4 + 16, 2, 64, emulated, 0, false, "ag push, 16-byte multiple only");
+          } else {
+            allreduce_case<float, OpSum>(w, kArNvlsTwo, kSum, count, 2, 64, emulated, 0, false, "nvls twoshot f32 unroll 8");
+            allreduce_case<__nv_bfloat16, OpSum>(w, kArNvlsOne, kSum, count, 3, 32, emulated, 0, false, "nvls oneshot bf16 unroll 8");
+          }
+        }
+      }
+  }
+  g_unroll_hint = 0;
   const int threads = 32;
   // --- AllReduce: every variant, several rank counts, both placements ------------------
   for (int n : {2, 3, 4, 8}) {

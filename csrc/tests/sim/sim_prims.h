@@ -29,6 +29,7 @@ template <> struct Raw<2> { uint16_t x; };
 template <> struct Raw<4> { uint32_t x; };
 template <> struct Raw<8> { uint64_t x; };
 template <> struct alignas(16) Raw<16> { uint32_t x, y, z, w; };
+template <> struct alignas(32) Raw<32> { uint32_t a[8]; };
 
 // A misaligned access is a fault on the GPU; here it ends the test.
 inline void sim_check_aligned(const void* p, int bytes) {
