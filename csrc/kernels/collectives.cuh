@@ -195,15 +195,18 @@ __global__ void __launch_bounds__(kMaxThreads) ar_twoshot_kernel(const __grid_co
   Scaler<typename AccOf<T>::type> sc{scaler_mode(a.op), a.scale};
   constexpr int kN = 16 / (int)sizeof(T);
   uint64_t done = 0;
-  if (a.unroll_hint == 32 && all_aligned32(a)) {
-    // 256-bit packs (the daemon's `pack_bytes = 32`): 1 KiB per warp and instruction.
-    constexpr int kN32 = 32 / (int)sizeof(T);
+  // 256-bit packs (the daemon's `pack_bytes = 32`): 1 KiB per warp and instruction. Not for
+  // 8-bit elements, whose 32 accumulators per pack would not fit the register budget.
+  if (sizeof(T) >= 2 && a.unroll_hint == 32 && all_aligned32(a)) {
+    constexpr int kN32 = sizeof(T) >= 2 ? 32 / (int)sizeof(T) : 16;
     const uint64_t nv = a.count / kN32;
     Range mine = split_range(nv, a.nranks, rank);
-    if (a.nranks > 4)
-      reduce_store<T, Op, 32, 1, kMaxRanks>(s_src, a.nranks, s_dst, a.nranks, mine.beg, mine.end, blockIdx.x, gridDim.x, sc);
-    else
-      reduce_store<T, Op, 32, 2, 4>(s_src, a.nranks, s_dst, a.nranks, mine.beg, mine.end, blockIdx.x, gridDim.x, sc);
+    if constexpr (sizeof(T) >= 2) {
+      if (a.nranks > 4)
+        reduce_store<T, Op, 32, 1, kMaxRanks>(s_src, a.nranks, s_dst, a.nranks, mine.beg, mine.end, blockIdx.x, gridDim.x, sc);
+      else
+        reduce_store<T, Op, 32, 2, 4>(s_src, a.nranks, s_dst, a.nranks, mine.beg, mine.end, blockIdx.x, gridDim.x, sc);
+    }
     done = nv * kN32;
   } else if (all_aligned16(a)) {
     const uint64_t nv = a.count / kN;

@@ -8,6 +8,9 @@ real training loops of :mod:`mccs_b200.parallel.train` run):
     gpt-with-resnet  GPT-2-medium on all 8 GPUs, high priority and weight 4, sharing GPUs 0-3
                      with a ResNet-50 job
 
+On a box with four to seven GPUs the same scenarios run at half the width (ResNet-50 on 0-1 next
+to VGG-16 on 2-3; GPT-2-medium on 0-3 sharing 0-1 with ResNet-50).
+
     python -m mccs_b200.utils.colocate_train --scenario cnn --backend mccs
     python -m mccs_b200.utils.colocate_train --scenario cnn --backend nccl
 
@@ -60,7 +63,13 @@ def main() -> int:
     ap.add_argument("--comm-ctas", type=int, default=0)
     ap.add_argument("--timeout", type=float, default=600.0)
     a = ap.parse_args()
-    jobs = SCENARIOS[a.scenario]
+    jobs = [dict(j) for j in SCENARIOS[a.scenario]]
+    import torch
+    ngpu = torch.cuda.device_count() if torch.cuda.is_available() else 8
+    if 4 <= ngpu < 8:
+        # a four-GPU box: the same scenarios at half the width (jobs of 2 and 4 GPUs)
+        for j in jobs:
+            j["devices"] = sorted({d // 2 for d in j["devices"]})
     out = {"scenario": a.scenario, "backend": a.backend, "jobs": {}}
     with tempfile.TemporaryDirectory(prefix="mccs-cotrain-") as work:
         env = dict(os.environ, PYTHONPATH=REPO + os.pathsep + os.environ.get("PYTHONPATH", ""))

@@ -132,6 +132,7 @@ def main() -> int:
     while s <= hi:
         sizes.append(s)
         s *= 2
+    # final mode: 20 warm-up and 100 timed calls per point (the median of five groups of 20, see time_ms)
     warm = args.warmup or (20 if args.mode == "final" else 5)
     iters = args.iters or (100 if args.mode == "final" else 20)
     cta_list = [int(x) for x in args.ctas.split(",")] if args.mode == "tune" else [0]
@@ -159,16 +160,24 @@ def main() -> int:
             for _ in range(iters):
                 fn()
             return max_over_ranks((time.perf_counter() - t0) * 1e3 / iters)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # The timed calls run back to back in `batches` groups, each bracketed by its own pair of
+        # events; the figure is the median group (MAX over ranks per group). One mean over all
+        # calls lets a single multi-millisecond stall of a shared host (seen for the service and
+        # for NCCL alike) pass for the cost of a collective.
+        batches = 5 if iters >= 50 else 1
+        per = iters // batches
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(batches + 1)]
         stream = torch.cuda.current_stream()
         barrier()
         torch.cuda.synchronize()
-        e0.record(stream)
-        for _ in range(iters):
-            fn()
-        e1.record(stream)
+        evs[0].record(stream)
+        for b in range(batches):
+            for _ in range(per):
+                fn()
+            evs[b + 1].record(stream)
         torch.cuda.synchronize()
-        return max_over_ranks(e0.elapsed_time(e1) / iters)
+        means = sorted(max_over_ranks(evs[b].elapsed_time(evs[b + 1]) / per) for b in range(batches))
+        return means[len(means) // 2]
 
     rows: List[dict] = []
     best: Dict[Tuple[str, int], Tuple[float, str, int]] = {}
