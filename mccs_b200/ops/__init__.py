@@ -1,10 +1,13 @@
 """Collective operations on tensors, functional form.
 
-``all_reduce`` / ``all_gather`` are the stream-ordered collectives of a
+``all_reduce`` / ``all_gather`` / ``reduce_scatter`` are the stream-ordered collectives of a
 :class:`mccs_b200.Communicator` (the reference's ``libmccs::all_reduce`` /
 ``all_gather``, src/libmccs/src/collectives.rs:15-138) written as plain functions, with
 the kernel variant as a keyword: what runs is one of the hand-written sm_100a kernels of
-``csrc/kernels`` (``VARIANTS``), launched by the daemon.
+``csrc/kernels`` (``VARIANTS``), planned by the daemon and launched by the client library or
+the daemon. Unlike the communicator's methods they take any tensor: one that lives in service
+memory is used where it is, anything else is staged through a per-communicator arena (which is
+what the ``torch.distributed`` backend builds on).
 
 ``local_all_reduce_no_alloc`` calls the kernels directly, without daemon or communicator:
 the allocation-free single-GPU AllReduce of ``csrc/include/mccs_noalloc.h``.

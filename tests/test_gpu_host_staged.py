@@ -144,3 +144,57 @@ def test_preload_hook_under_a_cuda_program(tmp_path):
         assert "big_ours=1 small_ours=0 same=1 freed=1 gone=1" in res.stdout, res.stdout + res.stderr
     finally:
         sp.stop()
+
+
+FUSED_CLIENT = r"""
+import os, sys, json, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"]); dev = int(os.environ["DEV"]); port = int(os.environ["ADMIN_PORT"])
+torch.cuda.set_device(dev)
+bufs = [M.Buffer((1 << 20) + 4096 * k, dev) for k in range(6)]
+ts = [b.tensor(torch.float32, (1 << 18) + 1024 * k) for k, b in enumerate(bufs)]     # six members of different sizes
+comm = M.Communicator(7300, rank, n, device=dev)
+bad = []
+for rnd in range(4):
+    for k, t in enumerate(ts):
+        t.fill_(float(rank + 1 + k + rnd))
+    with M.group():                       # queued together: the daemon may carry them in one launch
+        for t in ts:
+            comm.all_reduce(t, algo="ar_twoshot")
+    torch.cuda.synchronize()
+    for k, t in enumerate(ts):
+        want = float(sum(r + 1 + k + rnd for r in range(n)))
+        if not bool(torch.all(t == want)):
+            bad.append((rnd, k, float(t[0]), want))
+q = comm.query()
+st = M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"]["7300"]
+comm.destroy()
+print("RESULT", json.dumps({"bad": bad[:4], "async_error": q["async_error"], "device_error": q["device_error"],
+                            "fused_launches": st["fused_launches"], "fused_members": st["fused_members"], "launch": comm.launch_mode}), flush=True)
+"""
+
+
+def test_fused_launches_on_a_gpu(tmp_path):
+    """`[b200] fuse_allreduce = 4` with daemon launches: AllReduces queued together in a group
+    go out as fused kernels (one pair of cross-rank barriers for up to four of them), and every
+    member's result is right. Two ranks; on one GPU both sit on cuda:0 (cooperative launch)."""
+    from mccs_b200 import daemon
+    ngpu = torch.cuda.device_count()
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, wait_timeout_ms=5000,
+                       extra='launch = "daemon"\nfuse_allreduce = 4')
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE="2", MCCS_LOG="error", MCCS_WC_TIMEOUT_MS="30000",
+                   ADMIN_PORT=str(sp.admin_port))
+        procs = [subprocess.Popen([sys.executable, "-c", FUSED_CLIENT], env=dict(env, RANK=str(r), DEV=str(r if ngpu >= 2 else 0)),
+                                  stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+        for p in procs:
+            out, err = p.communicate(timeout=240)
+            assert p.returncode == 0, err[-3000:]
+            res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+            assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
+            assert res["launch"] == "daemon"
+            assert res["fused_launches"] > 0 and res["fused_members"] >= res["fused_launches"]
+    finally:
+        sp.stop()
