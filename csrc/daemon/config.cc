@@ -116,7 +116,7 @@ Config Config::from_value(const Value& root) {
                {"transport", "nvls", "vmm", "sync", "wait_timeout_ms", "tuning_file", "trace", "trace_file",
                 "host_devices", "force_host_backend", "idle_sleep_us", "idle_spin_us", "pin_threads", "init_timeout_ms", "fuse_allreduce", "client_nvls",
                 "single_through_fused", "skip_start_barrier", "kernel_writes_done", "host_kernels",
-                "hybrid_nvls_permille", "hybrid_nvls_ctas", "launch", "nvls_unroll", "pack_bytes"},
+                "hybrid_nvls_permille", "hybrid_nvls_ctas", "launch", "nvls_unroll", "pack_bytes", "host_no_peer_access"},
                "[b200]");
     c.transport = b["transport"].as_string(c.transport);
     if (c.transport != "auto" && c.transport != "nvlink" && c.transport != "host_staged")
@@ -133,6 +133,11 @@ Config Config::from_value(const Value& root) {
     c.trace = b["trace"].as_bool(c.trace);
     c.trace_file = b["trace_file"].as_string();
     c.host_devices = (int)b["host_devices"].as_int(c.host_devices);
+    if (b.has("host_no_peer_access"))
+      for (const Value& pr : b["host_no_peer_access"].items()) {
+        if (pr.size() != 2) throw std::runtime_error("b200.host_no_peer_access must be a list of [a, b] device pairs");
+        c.host_no_peer_access.push_back({(int)pr.at(0).as_int(), (int)pr.at(1).as_int()});
+      }
     c.force_host_backend = b["force_host_backend"].as_bool(c.force_host_backend);
     c.host_kernels = b["host_kernels"].as_string(c.host_kernels);
     if (c.host_kernels != "loops" && c.host_kernels != "emulated")

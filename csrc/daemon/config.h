@@ -86,6 +86,7 @@ struct Config {
   bool trace = false;
   std::string trace_file;
   int host_devices = 8;
+  std::vector<std::pair<int, int>> host_no_peer_access;   // host backend: [[a, b], ...] device pairs without peer access
   bool force_host_backend = false;
   std::string host_kernels = "loops";  // host backend: "loops" (plain CPU collectives) | "emulated" (the kernels on the SIMT emulator)
   int idle_sleep_us = 50;           // sleep between polls once a proxy has been idle for idle_spin_us

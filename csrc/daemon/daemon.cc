@@ -44,6 +44,7 @@ int Daemon::start(const Config& cfg, std::string* err) {
   cfg_ = cfg;
   BackendOptions bo;
   bo.host_devices = cfg.host_devices;
+  bo.host_no_peer_access = cfg.host_no_peer_access;
   bo.allow_vmm = cfg.vmm;
   bo.allow_nvls = cfg.nvls;
   bo.force_host = cfg.force_host_backend;

@@ -65,6 +65,7 @@ struct BackendOptions {
   bool allow_memops = true;
   bool host_memops = false;     // host backend: offer semaphore pages, "stream memory operations" done by the CPU
   bool emulate_kernels = false; // host backend: run the real kernels on the SIMT emulator instead of plain loops
+  std::vector<std::pair<int, int>> host_no_peer_access;   // host backend: device pairs that report no peer access (to exercise transport selection)
 };
 
 class Backend {

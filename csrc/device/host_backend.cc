@@ -161,11 +161,16 @@ void cpu_allgather(const CollArgs& a) {
 class HostBackend : public Backend {
  public:
   explicit HostBackend(const BackendOptions& opt)
-      : ndev_(opt.host_devices > 0 ? opt.host_devices : 1), emulate_(opt.emulate_kernels), memops_(opt.host_memops) {}
+      : ndev_(opt.host_devices > 0 ? opt.host_devices : 1), emulate_(opt.emulate_kernels), memops_(opt.host_memops),
+        no_peer_(opt.host_no_peer_access) {}
   uint32_t kind() const override { return proto::kBackendHost; }
   int device_count() const override { return ndev_; }
   bool nvls_supported() const override { return emulate_; }   // emulated multicast regions (see mc_create)
-  bool peer_access(int, int) const override { return true; }
+  bool peer_access(int a, int b) const override {
+    for (const auto& p : no_peer_)
+      if ((p.first == a && p.second == b) || (p.first == b && p.second == a)) return false;
+    return true;
+  }
   std::string describe() const override {
     return "host backend (" + std::to_string(ndev_) + " emulated devices" + (emulate_ ? ", kernels on the SIMT emulator)" : ")");
   }
@@ -405,6 +410,7 @@ class HostBackend : public Backend {
   int ndev_;
   bool emulate_;
   bool memops_;
+  std::vector<std::pair<int, int>> no_peer_;
   std::atomic<uint64_t> next_handle_{0x1000};
 };
 

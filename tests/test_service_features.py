@@ -571,3 +571,59 @@ def test_clients_killed_at_random_leave_the_daemon_clean(tmp_path, launch):
         assert st["clients"] == 0 and st["communicators"] == {} and st["allocations"] == 0
     finally:
         sp.stop()
+
+
+TRANSPORT_CLIENT = r"""
+import os, sys, json, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); devs = json.loads(os.environ["DEVS"]); cid = int(os.environ["COMM"]); port = int(os.environ["ADMIN_PORT"])
+n = len(devs); dev = devs[rank]
+a, b = M.Buffer(1 << 20, dev), M.Buffer(1 << 20, dev)
+s, d = a.tensor(torch.float32, 100000), b.tensor(torch.float32, 100000)
+s.fill_(float(rank + 1))
+comm = M.Communicator(cid, rank, n, device=dev)
+comm.all_reduce(s, d)
+ar_plan = comm.last_plan()[0]
+comm.all_reduce(s, d, algo="ar_twoshot")            # a request the connections may not be able to carry
+asked_plan = comm.last_plan()[0]
+ok = bool(torch.all(d == float(n * (n + 1) // 2)))
+g = b.tensor(torch.uint8, 4096 * n)               # reuses the output buffer
+comm.all_gather(a.tensor(torch.uint8, 4096), g)
+ag_plan = comm.last_plan()[0]
+st = M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"][str(cid)]
+comm.destroy()
+print("RESULT", json.dumps({"ok": ok, "ar": ar_plan, "asked": asked_plan, "ag": ag_plan, "transport": st["transport"],
+                            "host_staged": st["host_staged"]}), flush=True)
+"""
+
+
+def test_transport_is_chosen_per_connection(tmp_path):
+    """A box on which one pair of GPUs has no peer access (host backend, `host_no_peer_access`):
+    a communicator that contains the pair gets host-staged connections for it and peer-memory
+    connections for the rest, keeps its scratch in host memory and runs the FIFO rings whatever
+    is asked for; a communicator without the pair is untouched. (The reference picks a
+    transporter per connection the same way, src/mccs/src/transport/setup.rs:346-361.)"""
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=-1, force_host=True,
+                       extra="host_no_peer_access = [[1, 2]]")
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        for cid, devs, want in ((8101, [0, 1, 2, 3], "mixed"), (8102, [0, 1, 3], "peer")):
+            env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, MCCS_LOG="error", DEVS=json.dumps(devs), COMM=str(cid),
+                       ADMIN_PORT=str(sp.admin_port))
+            procs = [subprocess.Popen([sys.executable, "-c", TRANSPORT_CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True) for r in range(len(devs))]
+            for p in procs:
+                out, err = p.communicate(timeout=120)
+                assert p.returncode == 0, err[-2000:]
+                res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+                assert res["ok"]
+                if want == "mixed":
+                    assert res["transport"] == "host_staged x2, nvlink_p2p x10" and res["host_staged"] is True
+                    assert res["ar"] == "ar_ring" and res["asked"] == "ar_ring" and res["ag"] == "ag_ring"
+                else:
+                    assert res["transport"] == "nvlink_p2p" and res["host_staged"] is False
+                    assert res["asked"] == "ar_twoshot" and "ring" not in res["ar"] and "ring" not in res["ag"]
+    finally:
+        sp.stop()
