@@ -17,7 +17,7 @@ namespace mccs {
 namespace proto {
 
 constexpr uint32_t kMagic = 0x5343434du;  // "MCCS"
-constexpr uint32_t kVersion = 8;
+constexpr uint32_t kVersion = 9;
 constexpr uint32_t kWqDepth = 64;
 constexpr uint32_t kCqDepth = 64;
 constexpr uint32_t kWrBytes = 128;
@@ -254,7 +254,11 @@ struct alignas(64) PlanMsg {
   int32_t variant_hint;    // CollArgs::unroll_hint (ar_hybrid: share and CTAs of the in-switch part)
   uint64_t mc_send_id, mc_send_off;   // multicast region of the inputs (0: none) and this rank's offset in it
   uint64_t mc_recv_id, mc_recv_off;
-  uint8_t reserved[144];
+  // Time slices: a large AllReduce of a tenant with competitors is cut into `nslices`
+  // independent collectives over sub-ranges, each admitted (and handed out) on its own; this
+  // message describes slice `slice` (count and offsets are the slice's). 1 / 0 otherwise.
+  int32_t nslices, slice;
+  uint8_t reserved[136];
 };
 static_assert(sizeof(PlanMsg) == kPlanBytes, "a plan must fill one slot of the plan ring");
 

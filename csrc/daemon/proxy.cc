@@ -349,7 +349,7 @@ bool ProxyEngine::plan_slot(Communicator& c, CollSlot& s, uint64_t seq) {
   s.slice_count = o0.count;
   const uint64_t slice_bytes = daemon_->qos().slice_bytes(c.id, now);
   if (slice_bytes && o0.kind == kAllReduce && !variant_is_ring(plan.variant) && plan.bytes > slice_bytes &&
-      plan.variant != kLocalCopy && !c.client_launch) {   // a plan handed to a client is one launch
+      plan.variant != kLocalCopy) {
     const uint64_t esz = (uint64_t)dtype_size(o0.dtype);
     uint64_t n = std::min<uint64_t>((plan.bytes + slice_bytes - 1) / slice_bytes, 64);
     uint64_t per = (o0.count + n - 1) / n;
@@ -812,45 +812,64 @@ bool ProxyEngine::publish_plan_error(RankState& rs, uint64_t user_seq, int statu
 
 bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
   Communicator& c = *rs.comm;
-  if (!admit_slice(c, s, 0)) return false;
   const CollOp& o0 = s.ops[0];
-  proto::PlanMsg m;
-  memset(&m, 0, sizeof m);
-  m.user_seq = s.ops[rs.rank].user_seq;
-  m.status = proto::kOk;
-  m.kind = o0.kind;
-  m.variant = s.plan.variant;
-  m.ctas = s.plan.dims.ctas;
-  m.threads = s.plan.dims.threads;
-  m.dtype = kind_reduces(o0.kind) ? o0.dtype : kUint8;
-  m.op = kind_reduces(o0.kind) ? o0.op : kSum;
-  m.nranks = c.nranks;
-  m.scale = o0.op == kSumPostDiv ? 1.0f / (float)c.nranks : o0.scale;
-  m.epoch = s.epoch_base;
-  m.ticket = s.ticket_base;
-  m.count = o0.count;
-  m.timeout_ns = daemon_->timeout_ns();
-  m.trace = daemon_->tracer().enabled() ? 1 : 0;
-  if (s.plan.variant == kArHybrid) {
-    const Config& cfg = daemon_->config();
-    const int nvls_ctas = std::min(cfg.hybrid_nvls_ctas, std::max(s.plan.dims.ctas - 1, 0));
-    m.variant_hint = (int32_t)(((uint32_t)nvls_ctas << 16) | (uint32_t)cfg.hybrid_nvls_permille);
-  } else if (s.plan.variant == kArNvlsOne || s.plan.variant == kArNvlsTwo) {
-    m.variant_hint = daemon_->config().nvls_unroll;
-  } else if (s.plan.variant == kAgPull || s.plan.variant == kAgPush || s.plan.variant == kArTwoShot) {
-    m.variant_hint = daemon_->config().pack_bytes;
+  const uint64_t esz = kind_reduces(o0.kind) ? (uint64_t)dtype_size(o0.dtype) : 1;
+  // One plan per time slice, each handed out once that slice is admitted: the client launches
+  // them one after another on the caller's stream (a collective that is not sliced is its
+  // only slice).
+  while (rs.next_slice < s.nslices) {
+    const int slice = rs.next_slice;
+    if (!admit_slice(c, s, slice)) return false;
+    uint64_t first = 0, count = o0.count;
+    if (s.nslices > 1) {
+      first = (uint64_t)slice * s.slice_count;
+      count = std::min<uint64_t>(s.slice_count, o0.count - first);
+    }
+    const uint64_t off = first * esz;
+    proto::PlanMsg m;
+    memset(&m, 0, sizeof m);
+    m.user_seq = s.ops[rs.rank].user_seq;
+    m.status = proto::kOk;
+    m.kind = o0.kind;
+    m.variant = s.plan.variant;
+    m.ctas = s.plan.dims.ctas;
+    m.threads = s.plan.dims.threads;
+    m.dtype = kind_reduces(o0.kind) ? o0.dtype : kUint8;
+    m.op = kind_reduces(o0.kind) ? o0.op : kSum;
+    m.nranks = c.nranks;
+    m.scale = o0.op == kSumPostDiv ? 1.0f / (float)c.nranks : o0.scale;
+    m.epoch = s.epoch_base + 2u * (uint32_t)slice;
+    m.ticket = s.ticket_base + (uint64_t)slice;
+    m.count = count;
+    m.nslices = s.nslices;
+    m.slice = slice;
+    m.timeout_ns = daemon_->timeout_ns();
+    m.trace = daemon_->tracer().enabled() ? 1 : 0;
+    if (s.plan.variant == kArHybrid) {
+      const Config& cfg = daemon_->config();
+      const int nvls_ctas = std::min(cfg.hybrid_nvls_ctas, std::max(s.plan.dims.ctas - 1, 0));
+      m.variant_hint = (int32_t)(((uint32_t)nvls_ctas << 16) | (uint32_t)cfg.hybrid_nvls_permille);
+    } else if (s.plan.variant == kArNvlsOne || s.plan.variant == kArNvlsTwo) {
+      m.variant_hint = daemon_->config().nvls_unroll;
+    } else if (s.plan.variant == kAgPull || s.plan.variant == kAgPush || s.plan.variant == kArTwoShot) {
+      m.variant_hint = daemon_->config().pack_bytes;
+    }
+    if (s.plan.needs_mc_send) { m.mc_send_id = s.mc_send_id; m.mc_send_off = s.ops[rs.rank].send_off + off; }
+    if (s.plan.needs_mc_recv) { m.mc_recv_id = s.mc_recv_id; m.mc_recv_off = s.ops[rs.rank].recv_off + off; }
+    for (int r = 0; r < c.nranks; r++) {
+      m.rank[r].send_mem = s.ops[r].send_mem; m.rank[r].send_off = s.ops[r].send_off + off;
+      m.rank[r].recv_mem = s.ops[r].recv_mem; m.rank[r].recv_off = s.ops[r].recv_off + off;
+    }
+    memcpy(m.ring, s.ring, sizeof m.ring);
+    for (int ch = 0; ch < kMaxRingChannels; ch++) m.ring_step_base[ch] = s.ring_step_base[ch];
+    if (!rs.pq.try_push(&m)) return false;   // the client has not taken the previous slices yet: come back
+    if (rs.rank == 0) {
+      const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
+      rs.inflight.push_back({m.ticket, bytes});
+    }
+    rs.last_ticket.store(m.ticket, std::memory_order_relaxed);
+    rs.next_slice++;
   }
-  if (s.plan.needs_mc_send) { m.mc_send_id = s.mc_send_id; m.mc_send_off = s.ops[rs.rank].send_off; }
-  if (s.plan.needs_mc_recv) { m.mc_recv_id = s.mc_recv_id; m.mc_recv_off = s.ops[rs.rank].recv_off; }
-  for (int r = 0; r < c.nranks; r++) {
-    m.rank[r].send_mem = s.ops[r].send_mem; m.rank[r].send_off = s.ops[r].send_off;
-    m.rank[r].recv_mem = s.ops[r].recv_mem; m.rank[r].recv_off = s.ops[r].recv_off;
-  }
-  memcpy(m.ring, s.ring, sizeof m.ring);
-  for (int ch = 0; ch < kMaxRingChannels; ch++) m.ring_step_base[ch] = s.ring_step_base[ch];
-  if (!rs.pq.try_push(&m)) return false;
-  if (rs.rank == 0) rs.inflight.push_back({s.ticket_base, s.plan.bytes});
-  rs.last_ticket.store(s.ticket_base, std::memory_order_relaxed);
   (void)seq;
   return true;
 }

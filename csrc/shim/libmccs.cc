@@ -918,25 +918,12 @@ mccsResult_t resolve_mc(std::unique_lock<std::mutex>& g, mccsComm* comm, uint64_
   return mccsSuccess;
 }
 
-// Client-side launch: post the request, wait for the plan the daemon makes for all ranks
-// (variant, launch shape, barrier epoch, ticket, ring order, everybody's buffers), and
-// launch this rank's kernel here. The daemon never touches a stream for this collective.
-mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t stream) {
-  if (comm->sticky_error) return (mccsResult_t)comm->sticky_error;
-  wr.comm_handle = comm->handle;
-  wr.user_seq = comm->next_user_seq++;
+// Waits for the next plan of request `wr` and launches the kernel it describes on `stream`.
+mccsResult_t launch_planned_slice(mccsComm* comm, const proto::WorkRequest& wr, mccsStream_t stream, int* nslices, int* slice) {
   uint64_t spins = 0;
-  while (!comm->wq.try_push(&wr)) {
-    if ((++spins & 0xffff) == 0) {
-      struct pollfd pf = {g_ctx.fd, 0, 0};
-      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return daemon_lost();
-    }
-  }
-  comm->last_posted_seq = wr.user_seq;
   proto::PlanMsg plan;
   struct timespec t0;
   clock_gettime(CLOCK_MONOTONIC, &t0);
-  spins = 0;
   while (!comm->pq.try_pop(&plan)) {
     if ((++spins & 0xfff) == 0) {
       struct timespec t1;
@@ -953,6 +940,8 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
     if (comm->sticky_error == 0) comm->sticky_error = plan.status;
     return (mccsResult_t)plan.status;
   }
+  *nslices = plan.nslices > 0 ? plan.nslices : 1;
+  *slice = plan.slice;
   comm->last_variant = (uint32_t)plan.variant;
   comm->last_ctas = (uint32_t)plan.ctas;
   if (plan.nranks != comm->nranks) return mccsProtocolError;
@@ -1040,6 +1029,31 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
     return (mccsResult_t)comm->sticky_error;
   }
   return mccsSuccess;
+}
+
+// Client-side launch: post the request, wait for the plan the daemon makes for all ranks
+// (variant, launch shape, barrier epoch, ticket, ring order, everybody's buffers), and
+// launch this rank's kernel here. The daemon never touches a stream for this collective.
+mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsStream_t stream) {
+  if (comm->sticky_error) return (mccsResult_t)comm->sticky_error;
+  wr.comm_handle = comm->handle;
+  wr.user_seq = comm->next_user_seq++;
+  uint64_t spins = 0;
+  while (!comm->wq.try_push(&wr)) {
+    if ((++spins & 0xffff) == 0) {
+      struct pollfd pf = {g_ctx.fd, 0, 0};
+      if (poll(&pf, 1, 0) > 0 && (pf.revents & (POLLHUP | POLLERR))) return daemon_lost();
+    }
+  }
+  comm->last_posted_seq = wr.user_seq;
+  // One plan per time slice (a collective that is not sliced is its only slice): each is waited
+  // for (the daemon hands it out once the slice is admitted) and launched in turn.
+  for (;;) {
+    int nslices = 1, slice = 0;
+    mccsResult_t r = launch_planned_slice(comm, wr, stream, &nslices, &slice);
+    if (r != mccsSuccess) return r;
+    if (slice + 1 >= nslices) return mccsSuccess;
+  }
 }
 
 mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, void* recv, uint64_t send_bytes,

@@ -166,3 +166,61 @@ def test_client_side_launch_on_gpus(tmp_path, nvls):
                 assert set(res["seen"]) == {"local_copy"}
     finally:
         sp.stop()
+
+
+SLICE_CLIENT = r"""
+import os, sys, json, time, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); cid = int(os.environ["COMM"]); n = 2
+torch.cuda.set_device(rank)
+count = 8 << 20                                         # 32 MiB of fp32: eight slices of 4 MiB under this daemon's policy
+buf = M.Buffer(count * 4, rank); out = M.Buffer(count * 4, rank)
+comm = M.Communicator(cid, rank, n, device=rank)
+x = buf.tensor(torch.float32, count); y = out.tensor(torch.float32, count)
+base = (torch.arange(count, dtype=torch.float32, device="cuda") % 97)
+port = int(os.environ["ADMIN_PORT"])
+for _ in range(600):                                    # start together with the other tenant
+    if {"6201", "6202"} <= set(M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"]):
+        break
+    time.sleep(0.05)
+bad = torch.zeros((), dtype=torch.int64, device="cuda")
+for it in range(40):
+    x.copy_(base + float(rank + it + cid % 7))
+    y.fill_(float("nan"))
+    comm.all_reduce(x, y, algo="ar_twoshot")
+    bad += (y != base * 2 + float(1 + 2 * (it + cid % 7))).sum()
+torch.cuda.synchronize()
+q = comm.query()
+mode = comm.launch_mode
+comm.destroy()
+print("RESULT", json.dumps({"bad": int(bad.item()), "async_error": q["async_error"], "device_error": q["device_error"], "launch": mode}), flush=True)
+"""
+
+
+def test_time_slices_under_client_launch_on_gpus(tmp_path):
+    """Two tenants on the same two GPUs, kernels launched by the clients: large AllReduces are
+    cut into time slices, the daemon hands out one plan per admitted slice, and every result is
+    exact although the two tenants' slices interleave on the links."""
+    import mccs_b200 as M
+    from mccs_b200 import daemon
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, wait_timeout_ms=5000, trace=True)
+    with open(cfg, "a") as f:
+        f.write("\n[qos]\nmax_outstanding_bytes = 8388608\nactive_window_us = 3000000\n[qos.tenants.6201]\nweight = 2.0\n[qos.tenants.6202]\nweight = 1.0\n")
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, MCCS_LOG="error", MCCS_WC_TIMEOUT_MS="60000",
+                   ADMIN_PORT=str(sp.admin_port))
+        procs = [subprocess.Popen([sys.executable, "-c", SLICE_CLIENT], env=dict(env, RANK=str(r), COMM=str(c)),
+                                  stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for c in (6201, 6202) for r in range(2)]
+        for p in procs:
+            out, err = p.communicate(timeout=300)
+            assert p.returncode == 0, err[-3000:]
+            res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+            assert res["bad"] == 0 and res["async_error"] == 0 and res["device_error"] == 0 and res["launch"] == "client"
+        events = M.admin_request(sp.admin_port, {"cmd": "trace", "enabled": False, "inline": True})["trace"]["traceEvents"]
+        assert max(e.get("args", {}).get("slices", 1) for e in events) > 1, "no collective was sliced"
+    finally:
+        sp.stop()

@@ -215,14 +215,17 @@ print("RESULT", json.dumps({"ok": ok, "async_error": q["async_error"], "device_e
 """
 
 
-def test_time_sliced_allreduce_with_the_real_kernels(tmp_path):
+@pytest.mark.parametrize("launch", ["daemon", "client"])
+def test_time_sliced_allreduce_with_the_real_kernels(tmp_path, launch):
     """Two tenants on the same two devices: large all-reduces are cut into slices (each its
-    own launch with its own barrier epochs and ticket) and still give the right sums."""
+    own launch with its own barrier epochs and ticket) and still give the right sums. With
+    client-side launch the daemon hands out one plan per admitted slice and the client
+    library launches them one after another."""
     import mccs_b200 as M
     from mccs_b200 import daemon
     d = str(tmp_path)
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=2, listen_port=-1, force_host=True,
-                       wait_timeout_ms=20000, trace=True, extra='host_kernels = "emulated"')
+                       wait_timeout_ms=20000, trace=True, extra=f'host_kernels = "emulated"\nlaunch = "{launch}"')
     with open(cfg, "a") as f:
         f.write("\n[qos]\nmax_outstanding_bytes = 2097152\nactive_window_us = 3000000\n[qos.tenants.6201]\nweight = 2.0\n[qos.tenants.6202]\nweight = 1.0\n")
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
