@@ -17,7 +17,7 @@ namespace mccs {
 namespace proto {
 
 constexpr uint32_t kMagic = 0x5343434du;  // "MCCS"
-constexpr uint32_t kVersion = 9;
+constexpr uint32_t kVersion = 10;
 constexpr uint32_t kWqDepth = 64;
 constexpr uint32_t kCqDepth = 64;
 constexpr uint32_t kWrBytes = 128;
@@ -151,6 +151,8 @@ struct CommInitReply {
   uint8_t sync_ipc_handle[kIpcHandleBytes];
   uint32_t launch_mode;                   // LaunchMode
   uint32_t fifo_slot_bytes;               // client-side launch: geometry of the ring FIFOs
+  uint32_t group_defer;                   // client-side launch: inside a group the library only posts and takes the plans at the end (fused launches are on)
+  uint32_t pad_;
 };
 
 struct CommDestroyReq { Header h; uint64_t comm_handle; };
@@ -258,7 +260,13 @@ struct alignas(64) PlanMsg {
   // independent collectives over sub-ranges, each admitted (and handed out) on its own; this
   // message describes slice `slice` (count and offsets are the slice's). 1 / 0 otherwise.
   int32_t nslices, slice;
-  uint8_t reserved[136];
+  // Fused launches: >= 2 in the answer to the first request of a fused launch (that many
+  // consecutive requests of the communicator run in ONE kernel, launched with this plan's
+  // shape, epoch and ticket); -1 in the answers to the others, which only describe their
+  // buffers; 0 for a request that runs on its own.
+  int32_t batch_len;
+  int32_t pad1_;
+  uint8_t reserved[128];
 };
 static_assert(sizeof(PlanMsg) == kPlanBytes, "a plan must fill one slot of the plan ring");
 

@@ -594,6 +594,7 @@ void Daemon::on_comm_init(Session& s, const proto::CommInitReq& m) {
       r.comm_init_reply.dp_bytes = (uint32_t)rs.dp_bytes;
       r.comm_init_reply.launch_mode = cptr->client_launch ? proto::kLaunchClient : proto::kLaunchDaemon;
       r.comm_init_reply.fifo_slot_bytes = (uint32_t)cptr->fifo_slot_bytes;
+      r.comm_init_reply.group_defer = cptr->client_launch && cfg_.fuse_allreduce > 1 ? 1u : 0u;
       int fds[2] = {rs.dp_fd, -1};
       int nfds = 1;
       if (rs.sync.host) {

@@ -108,6 +108,7 @@ struct CollSlot {
   uint64_t mc_send_id = 0, mc_recv_id = 0;    // McRegion::id of the two (client-side launch names them in the plan)
   int8_t ring[kMaxRingChannels][kMaxRanks];   // ring order per channel, fixed at plan time
   uint64_t t_ready_us = 0;
+  std::atomic<uint64_t> t_collected_us{0};   // when the last rank's request arrived
   // Fused launches. A head slot carries `batch_len` collectives (itself and the next
   // batch_len - 1 slots) in one kernel; a follower slot has batch_len == 0 and launches
   // nothing of its own. Written by the planning proxy before the slot becomes "planned".
@@ -233,6 +234,8 @@ class ProxyEngine : public Engine {
   bool complete_request(RankState& rs, CollSlot& s, uint64_t seq, int status);
   void signal_done(RankState& rs, uint64_t user_seq, int status);
   bool publish_plan(RankState& rs, CollSlot& s, uint64_t seq);
+  bool publish_follower_plan(RankState& rs, CollSlot& s);
+  bool followers_still_arriving(Communicator& c, CollSlot& s, uint64_t seq);
   bool publish_plan_error(RankState& rs, uint64_t user_seq, int status);
   void order_after_client(RankState& rs, const CollOp& op, void* stream);
   bool clients_ready(Communicator& c, CollSlot& s, int self_rank);

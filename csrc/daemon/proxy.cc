@@ -188,9 +188,30 @@ bool ProxyEngine::post(RankState& rs, const proto::WorkRequest& wr) {
   op.status = status;
   op.valid = status == proto::kOk;
   rs.next_post_seq++;
-  if (s.arrived.fetch_add(1, std::memory_order_acq_rel) + 1 == c.nranks)
+  if (s.arrived.fetch_add(1, std::memory_order_acq_rel) + 1 == c.nranks) {
+    s.t_collected_us.store(op.t_post_us, std::memory_order_relaxed);
     s.state.store(kSlotCollected, std::memory_order_release);
+  }
   return true;
+}
+
+// Fused launches: a collective whose followers are still arriving (some rank has posted the
+// next request, not all have) is worth a short wait, because only requests that every rank has
+// posted can join its launch. Ranks post the members of a group microseconds apart; the wait
+// ends as soon as the next slots are complete or untouched, and after 50 us in any case.
+bool ProxyEngine::followers_still_arriving(Communicator& c, CollSlot& s, uint64_t seq) {
+  const Config& cfg = daemon_->config();
+  if (cfg.fuse_allreduce <= 1 || s.ops[0].kind != kAllReduce) return false;
+  if (monotonic_us() - s.t_collected_us.load(std::memory_order_relaxed) > 50) return false;
+  const int limit = std::min(cfg.fuse_allreduce, kMaxBatch);
+  for (int k = 1; k < limit; k++) {
+    CollSlot& m = c.slot(seq + (uint64_t)k);
+    if (m.seq.load(std::memory_order_acquire) != seq + (uint64_t)k) return false;   // still serving an older collective
+    const int arrived = m.arrived.load(std::memory_order_acquire);
+    if (arrived == 0) return false;              // nobody has posted a follower: nothing to wait for
+    if (arrived < c.nranks) return true;         // some have, not all: wait for the rest
+  }
+  return false;
 }
 
 // ---------------------------------------------------------------------------
@@ -454,7 +475,7 @@ bool ProxyEngine::plan_member(Communicator& c, CollSlot& head, CollSlot& m, cons
 void ProxyEngine::extend_batch(Communicator& c, CollSlot& head, uint64_t seq, const PlanInput& head_in, uint64_t now) {
   const int limit = std::min(daemon_->config().fuse_allreduce, kMaxBatch);
   const bool single = daemon_->config().single_through_fused;
-  if ((limit <= 1 && !single) || c.client_launch) return;
+  if (limit <= 1 && !(single && !c.client_launch)) return;   // a lone collective through the fused kernel is a daemon-launch experiment
   Backend* be = daemon_->backend();
   const CollOp& h0 = head.ops[0];
   if (h0.kind != kAllReduce || head.nslices != 1) return;
@@ -843,6 +864,7 @@ bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
     m.count = count;
     m.nslices = s.nslices;
     m.slice = slice;
+    m.batch_len = s.fused_kernel && s.batch_len >= 2 ? s.batch_len : 0;   // the head of a fused launch
     m.timeout_ns = daemon_->timeout_ns();
     m.trace = daemon_->tracer().enabled() ? 1 : 0;
     if (s.plan.variant == kArHybrid) {
@@ -864,7 +886,7 @@ bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
     for (int ch = 0; ch < kMaxRingChannels; ch++) m.ring_step_base[ch] = s.ring_step_base[ch];
     if (!rs.pq.try_push(&m)) return false;   // the client has not taken the previous slices yet: come back
     if (rs.rank == 0) {
-      const uint64_t bytes = s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
+      const uint64_t bytes = s.batch_len > 1 ? s.batch_bytes : s.nslices == 1 ? s.plan.bytes : s.plan.bytes / (uint64_t)s.nslices;
       rs.inflight.push_back({m.ticket, bytes});
     }
     rs.last_ticket.store(m.ticket, std::memory_order_relaxed);
@@ -872,6 +894,32 @@ bool ProxyEngine::publish_plan(RankState& rs, CollSlot& s, uint64_t seq) {
   }
   (void)seq;
   return true;
+}
+
+// The answer to a request that runs inside the fused launch of an earlier one: only its
+// buffers (and multicast regions); the head's plan carries everything else.
+bool ProxyEngine::publish_follower_plan(RankState& rs, CollSlot& s) {
+  Communicator& c = *rs.comm;
+  const CollOp& o0 = s.ops[0];
+  proto::PlanMsg m;
+  memset(&m, 0, sizeof m);
+  m.user_seq = s.ops[rs.rank].user_seq;
+  m.status = proto::kOk;
+  m.kind = o0.kind;
+  m.variant = s.plan.variant;
+  m.dtype = o0.dtype;
+  m.op = o0.op;
+  m.nranks = c.nranks;
+  m.count = o0.count;
+  m.nslices = 1;
+  m.batch_len = -1;
+  if (s.plan.needs_mc_send) { m.mc_send_id = s.mc_send_id; m.mc_send_off = s.ops[rs.rank].send_off; }
+  if (s.plan.needs_mc_recv) { m.mc_recv_id = s.mc_recv_id; m.mc_recv_off = s.ops[rs.rank].recv_off; }
+  for (int r = 0; r < c.nranks; r++) {
+    m.rank[r].send_mem = s.ops[r].send_mem; m.rank[r].send_off = s.ops[r].send_off;
+    m.rank[r].recv_mem = s.ops[r].recv_mem; m.rank[r].recv_off = s.ops[r].recv_off;
+  }
+  return rs.pq.try_push(&m);
 }
 
 bool ProxyEngine::complete_request(RankState& rs, CollSlot& s, uint64_t seq, int status) {
@@ -972,6 +1020,7 @@ bool ProxyEngine::advance(RankState& rs) {
     if (st == kSlotCollecting) break;
     if (st == kSlotCollected) {
       if (c.paused.load(std::memory_order_acquire)) break;
+      if (followers_still_arriving(c, s, seq)) break;
       int expect = kSlotCollected;
       if (!s.state.compare_exchange_strong(expect, kSlotPlanning, std::memory_order_acq_rel)) break;
       {
@@ -1002,6 +1051,7 @@ bool ProxyEngine::advance(RankState& rs) {
       status = s.status;
       if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq, status);
     } else if (follower) {
+      if (c.client_launch && !publish_follower_plan(rs, s)) break;
       if (c.state.load() == kCommError) status = c.async_error.load();
     } else if (c.client_launch) {
       if (!publish_plan(rs, s, seq)) break;   // the rank's own library launches the kernel

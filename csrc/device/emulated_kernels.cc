@@ -178,9 +178,16 @@ bool emulated_launch(int kind, const CollArgs& args, LaunchDims dims) {
   });
 }
 
+bool emulated_launch_batch_rank(const BatchArgs& args, LaunchDims dims) {
+  g_single_rank = true;
+  const bool ok = emulated_launch_batch(args, dims);
+  g_single_rank = false;
+  return ok;
+}
+
 bool emulated_launch_batch(const BatchArgs& args, LaunchDims dims) {
   BatchArgs b = args;
-  b.base.emulated = 1;
+  b.base.emulated = g_single_rank ? 0 : 1;
   int ctas = dims.ctas, threads = dims.threads;
   clamp(&ctas, &threads, false);
   return by_dtype(b.base.dtype, [&](auto* tag) {

@@ -16,6 +16,7 @@ bool emulated_launch_batch(const BatchArgs& args, LaunchDims dims);
 // One rank's part of a collective (args.rank), to completion; the other ranks' parts run
 // concurrently elsewhere and are met through the shared signal pads.
 bool emulated_launch_rank(int kind, const CollArgs& args, LaunchDims dims);
+bool emulated_launch_batch_rank(const BatchArgs& args, LaunchDims dims);
 // [base, base + size) becomes a multicast address range over `backing` (one pointer per
 // rank); the range itself is never dereferenced, only looked up.
 void emulated_mc_add(uint64_t base, size_t size, const std::vector<void*>& backing);

@@ -14,7 +14,9 @@ extern "C" {
 
 // Layout check between the two libraries: both must have been built from the same
 // dev_types.h.
-unsigned long long mccs_kernels_abi(void) { return (unsigned long long)sizeof(mccs::CollArgs); }
+unsigned long long mccs_kernels_abi(void) {
+  return (unsigned long long)sizeof(mccs::CollArgs) | ((unsigned long long)sizeof(mccs::BatchArgs) << 32);
+}
 
 // Launches one rank's kernel of the collective described by `args` on `stream` of the
 // current context. Returns 0 or a cudaError_t; `*err` then points to its static text.
@@ -28,6 +30,24 @@ int mccs_kernels_launch(int kind, const mccs::CollArgs* args, int ctas, int thre
   dims.ctas = ctas;
   dims.threads = threads;
   cudaError_t e = mccs::launch_collective(kind, *args, dims, stream);
+  if (e != cudaSuccess) {
+    if (err) *err = cudaGetErrorString(e);
+    cudaGetLastError();
+  }
+  return (int)e;
+}
+
+// Same for a fused launch of several AllReduces (kernels/batch.cuh).
+int mccs_kernels_launch_batch(const mccs::BatchArgs* args, int ctas, int threads, void* stream, const char** err) {
+  if (err) *err = nullptr;
+  if (!args || args->base.emulated) {
+    if (err) *err = "invalid arguments";
+    return (int)cudaErrorInvalidValue;
+  }
+  mccs::LaunchDims dims;
+  dims.ctas = ctas;
+  dims.threads = threads;
+  cudaError_t e = mccs::launch_batch(*args, dims, stream);
   if (e != cudaSuccess) {
     if (err) *err = cudaGetErrorString(e);
     cudaGetLastError();

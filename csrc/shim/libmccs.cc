@@ -243,6 +243,7 @@ struct mccsComm {
   // client-side launch (proto::kLaunchClient): plans come back through `pq`, the kernels
   // are launched here and address every rank's pads, status blocks, FIFOs and buffers
   bool client_launch = false;
+  bool group_defer = false;      // inside a group, requests are only posted; the plans are taken at the end (fused launches)
   ipc::Ring pq;
   Mapped pad_map[kMaxRanks], status_map[kMaxRanks], fifo_map[kMaxRanks];
   uint64_t fifo_slot_bytes = 0;
@@ -559,10 +560,12 @@ void unmap_allocation(const MemRec& rec) {
 // first communicator in that mode is created.
 typedef unsigned long long (*KernelsAbiFn)(void);
 typedef int (*KernelsLaunchFn)(int, const CollArgs*, int, int, void*, const char**);
+typedef int (*KernelsLaunchBatchFn)(const BatchArgs*, int, int, void*, const char**);
 struct KernelsLib {
   bool tried = false;
   void* lib = nullptr;
   KernelsLaunchFn launch = nullptr;
+  KernelsLaunchBatchFn launch_batch = nullptr;
 };
 KernelsLib g_klib;
 
@@ -582,7 +585,8 @@ bool load_kernels_lib() {   // g_ctx.mu held
   if (!g_klib.lib) { LOG_ERROR("client-side launch: cannot load %s: %s", path.c_str(), dlerror()); return false; }
   KernelsAbiFn abi = (KernelsAbiFn)dlsym(g_klib.lib, "mccs_kernels_abi");
   KernelsLaunchFn fn = (KernelsLaunchFn)dlsym(g_klib.lib, "mccs_kernels_launch");
-  if (!abi || !fn || abi() != sizeof(CollArgs)) {
+  g_klib.launch_batch = (KernelsLaunchBatchFn)dlsym(g_klib.lib, "mccs_kernels_launch_batch");
+  if (!abi || !fn || abi() != (sizeof(CollArgs) | ((unsigned long long)sizeof(BatchArgs) << 32))) {
     LOG_ERROR("client-side launch: %s does not match this library", path.c_str());
     return false;
   }
@@ -918,13 +922,12 @@ mccsResult_t resolve_mc(std::unique_lock<std::mutex>& g, mccsComm* comm, uint64_
   return mccsSuccess;
 }
 
-// Waits for the next plan of request `wr` and launches the kernel it describes on `stream`.
-mccsResult_t launch_planned_slice(mccsComm* comm, const proto::WorkRequest& wr, mccsStream_t stream, int* nslices, int* slice) {
+// Waits for the next message of the plan ring, which must answer request `user_seq`.
+mccsResult_t wait_plan(mccsComm* comm, uint64_t user_seq, proto::PlanMsg* plan) {
   uint64_t spins = 0;
-  proto::PlanMsg plan;
   struct timespec t0;
   clock_gettime(CLOCK_MONOTONIC, &t0);
-  while (!comm->pq.try_pop(&plan)) {
+  while (!comm->pq.try_pop(plan)) {
     if ((++spins & 0xfff) == 0) {
       struct timespec t1;
       clock_gettime(CLOCK_MONOTONIC, &t1);
@@ -935,17 +938,20 @@ mccsResult_t launch_planned_slice(mccsComm* comm, const proto::WorkRequest& wr, 
       if (spins > (1u << 20)) usleep(50);
     }
   }
-  if (plan.user_seq != wr.user_seq) return mccsProtocolError;
-  if (plan.status != 0) {
-    if (comm->sticky_error == 0) comm->sticky_error = plan.status;
-    return (mccsResult_t)plan.status;
+  if (plan->user_seq != user_seq) return mccsProtocolError;
+  if (plan->status != 0) {
+    if (comm->sticky_error == 0) comm->sticky_error = plan->status;
+    return (mccsResult_t)plan->status;
   }
-  *nslices = plan.nslices > 0 ? plan.nslices : 1;
-  *slice = plan.slice;
-  comm->last_variant = (uint32_t)plan.variant;
-  comm->last_ctas = (uint32_t)plan.ctas;
-  if (plan.nranks != comm->nranks) return mccsProtocolError;
-  CollArgs a;
+  if (plan->nranks != comm->nranks) return mccsProtocolError;
+  return mccsSuccess;
+}
+
+// The kernel arguments a plan describes, with every address resolved in this process: the
+// caller's own allocations by id, peers' buffers and multicast regions from this
+// communicator's maps (filled on first use).
+mccsResult_t args_from_plan(mccsComm* comm, const proto::PlanMsg& plan, CollArgs* out) {
+  CollArgs& a = *out;
   memset(&a, 0, sizeof a);
   a.rank = comm->rank;
   a.nranks = comm->nranks;
@@ -959,8 +965,6 @@ mccsResult_t launch_planned_slice(mccsComm* comm, const proto::WorkRequest& wr, 
   a.timeout_ns = plan.timeout_ns;
   a.trace = plan.trace;
   a.unroll_hint = plan.variant_hint;
-  // One pass under the library's lock: the caller's own allocations by id, peers' buffers
-  // and multicast regions from this communicator's maps (filled on first use).
   std::unique_lock<std::mutex> g(g_ctx.mu);
   for (int r = 0; r < comm->nranks; r++) {
     uint64_t s = 0, d = 0;
@@ -989,24 +993,29 @@ mccsResult_t launch_planned_slice(mccsComm* comm, const proto::WorkRequest& wr, 
   a.fifo_slot_bytes = comm->fifo_slot_bytes;
   memcpy(a.ring, plan.ring, sizeof a.ring);
   for (int ch = 0; ch < kMaxRingChannels; ch++) a.ring_step_base[ch] = plan.ring_step_base[ch];
-  LaunchDims dims{plan.ctas, plan.threads};
+  return mccsSuccess;
+}
+
+// Launches one kernel of this rank on `stream`: a single collective (`batch` null) or a fused
+// launch of several. On the caller's stream, in the caller's context: ordered against the
+// caller's other work like any kernel of its own. An error a previous kernel left behind (a
+// wait that ran out, an abort raised by the daemon) ends the communicator before the launch.
+mccsResult_t launch_here(mccsComm* comm, int kind, const CollArgs& a, const BatchArgs* batch, LaunchDims dims, mccsStream_t stream) {
   const StatusBlock* mine = (const StatusBlock*)comm->status_map[comm->rank].host;
   if (g_ctx.backend == proto::kBackendCuda) {
-    // On the caller's stream, in the caller's context: ordered against the caller's other
-    // work like any kernel of its own. An error a previous kernel left behind (a wait that
-    // ran out, an abort raised by the daemon) ends the communicator before the next launch.
     uint32_t before = __atomic_load_n(&mine->error, __ATOMIC_ACQUIRE);
     if (before != 0) {
       comm->sticky_error = before == kDevAborted ? mccsAborted : mccsTimeout;
       return (mccsResult_t)comm->sticky_error;
     }
-    if (!g_klib.launch) return mccsUnsupported;
+    if (!g_klib.launch || (batch && !g_klib.launch_batch)) return mccsUnsupported;
     CtxScope scope(comm->device);
     if (!scope.ok) return mccsDeviceError;
     const char* what = nullptr;
-    int e = g_klib.launch(plan.kind, &a, dims.ctas, dims.threads, (void*)stream, &what);
+    int e = batch ? g_klib.launch_batch(batch, dims.ctas, dims.threads, (void*)stream, &what)
+                  : g_klib.launch(kind, &a, dims.ctas, dims.threads, (void*)stream, &what);
     if (e != 0) {
-      LOG_ERROR("client-side launch of %s failed: %s", variant_name(plan.variant), what ? what : "?");
+      LOG_ERROR("client-side launch of %s failed: %s", variant_name(a.variant), what ? what : "?");
       comm->sticky_error = mccsDeviceError;
       return mccsDeviceError;
     }
@@ -1022,13 +1031,83 @@ mccsResult_t launch_planned_slice(mccsComm* comm, const proto::WorkRequest& wr, 
     }
     return mccsSuccess;
   }
-  if (!emulated_launch_rank(plan.kind, a, dims)) return mccsUnsupported;
+  if (!(batch ? emulated_launch_batch_rank(*batch, dims) : emulated_launch_rank(kind, a, dims))) return mccsUnsupported;
   const uint32_t err = __atomic_load_n(&mine->error, __ATOMIC_ACQUIRE);
   if (err != 0) {
     comm->sticky_error = err == kDevAborted ? mccsAborted : mccsTimeout;
     return (mccsResult_t)comm->sticky_error;
   }
   return mccsSuccess;
+}
+
+// Takes the answer(s) to request `user_seq` from the plan ring and launches what they
+// describe: one kernel, or one kernel per time slice (the daemon hands each slice's plan out
+// once that slice is admitted). `plan` is the first answer, already taken.
+mccsResult_t run_planned(mccsComm* comm, uint64_t user_seq, proto::PlanMsg& plan, mccsStream_t stream) {
+  for (;;) {
+    comm->last_variant = (uint32_t)plan.variant;
+    comm->last_ctas = (uint32_t)plan.ctas;
+    CollArgs a;
+    mccsResult_t r = args_from_plan(comm, plan, &a);
+    if (r != mccsSuccess) return r;
+    r = launch_here(comm, plan.kind, a, nullptr, LaunchDims{plan.ctas, plan.threads}, stream);
+    if (r != mccsSuccess) return r;
+    if (plan.slice + 1 >= (plan.nslices > 0 ? plan.nslices : 1)) return mccsSuccess;
+    r = wait_plan(comm, user_seq, &plan);
+    if (r != mccsSuccess) return r;
+  }
+}
+
+// Requests posted inside a group whose plans have not been taken yet (client-side launch with
+// fused launches enabled in the daemon): posting all of them before the first plan is read
+// is what lets the daemon see them together and carry several in one kernel.
+struct DeferredLaunch { mccsComm* comm; uint64_t user_seq; mccsStream_t stream; };
+thread_local std::vector<DeferredLaunch> g_deferred;
+
+mccsResult_t flush_deferred() {
+  std::vector<DeferredLaunch> items;
+  items.swap(g_deferred);
+  mccsResult_t result = mccsSuccess;
+  for (size_t i = 0; i < items.size(); i++) {
+    mccsComm* comm = items[i].comm;
+    proto::PlanMsg plan;
+    mccsResult_t r = wait_plan(comm, items[i].user_seq, &plan);
+    if (r == mccsSuccess && plan.batch_len >= 2) {
+      // A fused launch: this plan is the head (launch shape, barrier epoch, ticket), the
+      // answers to the next batch_len - 1 requests of this communicator are its members.
+      const int len = plan.batch_len;
+      comm->last_variant = (uint32_t)plan.variant;
+      comm->last_ctas = (uint32_t)plan.ctas;
+      BatchArgs b;
+      memset(&b, 0, sizeof b);
+      r = len <= kMaxBatch && i + (size_t)len <= items.size() ? args_from_plan(comm, plan, &b.base) : mccsProtocolError;
+      b.nops = len;
+      for (int k = 0; k < len && r == mccsSuccess; k++) {
+        proto::PlanMsg member = plan;
+        if (k > 0) {
+          if (items[i + (size_t)k].comm != comm) { r = mccsProtocolError; break; }
+          r = wait_plan(comm, items[i + (size_t)k].user_seq, &member);
+          if (r == mccsSuccess && member.batch_len != -1) r = mccsProtocolError;
+        }
+        CollArgs ma;
+        if (r == mccsSuccess) r = args_from_plan(comm, member, &ma);
+        if (r != mccsSuccess) break;
+        b.count[k] = member.count;
+        for (int q = 0; q < comm->nranks; q++) { b.send[k][q] = ma.send[q]; b.recv[k][q] = ma.recv[q]; }
+        b.mc_send[k] = ma.mc_send;
+        b.mc_recv[k] = ma.mc_recv;
+      }
+      if (r == mccsSuccess) r = launch_here(comm, kAllReduce, b.base, &b, LaunchDims{plan.ctas, plan.threads}, items[i].stream);
+      i += (size_t)len - 1;
+    } else if (r == mccsSuccess) {
+      r = run_planned(comm, items[i].user_seq, plan, items[i].stream);
+    }
+    if (r != mccsSuccess) {
+      if (result == mccsSuccess) result = r;
+      if (r == mccsTimeout || r == mccsNotConnected || r == mccsProtocolError) return r;   // the ring is out of step: stop here
+    }
+  }
+  return result;
 }
 
 // Client-side launch: post the request, wait for the plan the daemon makes for all ranks
@@ -1046,14 +1125,17 @@ mccsResult_t submit_client_launch(mccsComm* comm, proto::WorkRequest& wr, mccsSt
     }
   }
   comm->last_posted_seq = wr.user_seq;
-  // One plan per time slice (a collective that is not sliced is its only slice): each is waited
-  // for (the daemon hands it out once the slice is admitted) and launched in turn.
-  for (;;) {
-    int nslices = 1, slice = 0;
-    mccsResult_t r = launch_planned_slice(comm, wr, stream, &nslices, &slice);
-    if (r != mccsSuccess) return r;
-    if (slice + 1 >= nslices) return mccsSuccess;
+  if (g_group_depth > 0 && comm->group_defer) {
+    // Inside a group: only posted here; mccsGroupEnd (or a group that outgrows the plan
+    // ring) takes the plans and launches.
+    g_deferred.push_back({comm, wr.user_seq, stream});
+    if (g_deferred.size() >= proto::kPqDepth - 1) return flush_deferred();
+    return mccsSuccess;
   }
+  proto::PlanMsg plan;
+  mccsResult_t r = wait_plan(comm, wr.user_seq, &plan);
+  if (r != mccsSuccess) return r;
+  return run_planned(comm, wr.user_seq, plan, stream);
 }
 
 mccsResult_t submit(mccsComm* comm, proto::WorkRequest& wr, const void* send, void* recv, uint64_t send_bytes,
@@ -1347,6 +1429,7 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
   }
   if (c->dp_bytes >= proto::dp_segment_bytes()) c->pq.attach((char*)c->dp_mem + proto::dp_pq_offset());
   c->client_launch = m.comm_init_reply.launch_mode == proto::kLaunchClient;
+  c->group_defer = c->client_launch && m.comm_init_reply.group_defer != 0;
   c->fifo_slot_bytes = m.comm_init_reply.fifo_slot_bytes;
   if (g_ctx.backend == proto::kBackendHost && m.comm_init_reply.sync_size && fds.size() > 1) {
     const size_t bytes = m.comm_init_reply.sync_size;
@@ -1631,7 +1714,7 @@ mccsResult_t mccsGroupStart(void) { g_group_depth++; return mccsSuccess; }
 mccsResult_t mccsGroupEnd(void) {
   if (g_group_depth <= 0) return mccsInvalidArgument;
   if (--g_group_depth > 0) return mccsSuccess;
-  mccsResult_t result = mccsSuccess;
+  mccsResult_t result = g_deferred.empty() ? mccsSuccess : flush_deferred();
   std::vector<GroupItem> items;
   items.swap(g_group_items);
   // Collect every completion, then order each (communicator, stream) pair once.

@@ -14,6 +14,7 @@ Backend* make_cuda_backend(const BackendOptions&, std::string* why) {
 bool emulated_launch(int, const CollArgs&, LaunchDims) { return false; }
 bool emulated_launch_batch(const BatchArgs&, LaunchDims) { return false; }
 bool emulated_launch_rank(int, const CollArgs&, LaunchDims) { return false; }
+bool emulated_launch_batch_rank(const BatchArgs&, LaunchDims) { return false; }
 void emulated_mc_add(uint64_t, size_t, const std::vector<void*>&) {}
 void emulated_mc_remove(uint64_t) {}
 }  // namespace mccs

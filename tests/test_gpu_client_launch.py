@@ -224,3 +224,65 @@ def test_time_slices_under_client_launch_on_gpus(tmp_path):
         assert max(e.get("args", {}).get("slices", 1) for e in events) > 1, "no collective was sliced"
     finally:
         sp.stop()
+
+
+FUSED_CLIENT = r"""
+import os, sys, json, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"]); port = int(os.environ["ADMIN_PORT"])
+torch.cuda.set_device(rank)
+bufs = [M.Buffer((4 << 20) + 4096 * k, rank) for k in range(12)]
+ts = [b.tensor(torch.float32, (1 << 20) + 1024 * k) for k, b in enumerate(bufs)]     # twelve members of different sizes
+comm = M.Communicator(7400, rank, n, device=rank)
+bad = []
+for rnd in range(6):
+    for k, t in enumerate(ts):
+        t.fill_(float(rank + 1 + k + rnd))
+    with M.group():                       # posted together; the plans are taken at the end of the group
+        for t in ts:
+            comm.all_reduce(t, algo="ar_twoshot")
+    torch.cuda.synchronize()
+    for k, t in enumerate(ts):
+        want = float(sum(r + 1 + k + rnd for r in range(n)))
+        if not bool(torch.all(t == want)):
+            bad.append((rnd, k, float(t[0]), want))
+# a single call outside a group still works as before
+ts[0].fill_(1.0)
+comm.all_reduce(ts[0])
+torch.cuda.synchronize()
+if not bool(torch.all(ts[0] == float(n))):
+    bad.append(("single",))
+q = comm.query()
+st = M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"]["7400"]
+mode = comm.launch_mode
+comm.destroy()
+print("RESULT", json.dumps({"bad": bad[:4], "async_error": q["async_error"], "device_error": q["device_error"],
+                            "fused_launches": st["fused_launches"], "fused_members": st["fused_members"], "launch": mode}), flush=True)
+"""
+
+
+def test_fused_launches_under_client_launch_on_gpus(tmp_path):
+    """`fuse_allreduce = 8` with kernels launched by the clients: the AllReduces of a group are
+    posted together, the daemon carries up to eight of them in one plan (a head and its
+    followers), and each client builds and launches the fused kernel itself."""
+    from mccs_b200 import daemon
+    n = min(torch.cuda.device_count(), 4)
+    if n < 2:
+        pytest.skip("needs two GPUs")
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, wait_timeout_ms=5000,
+                       extra="fuse_allreduce = 8")
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), MCCS_LOG="error", MCCS_WC_TIMEOUT_MS="30000",
+                   ADMIN_PORT=str(sp.admin_port))
+        procs = [subprocess.Popen([sys.executable, "-c", FUSED_CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                                  stderr=subprocess.PIPE, text=True) for r in range(n)]
+        for p in procs:
+            out, err = p.communicate(timeout=240)
+            assert p.returncode == 0, err[-3000:]
+            res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+            assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0 and res["launch"] == "client"
+            assert res["fused_launches"] > 0 and res["fused_members"] > res["fused_launches"]
+    finally:
+        sp.stop()

@@ -256,6 +256,9 @@ def test_client_side_launch(tmp_path, n):
         assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
         assert {"ar_oneshot", "ar_twoshot", "ar_ring", "ag_pull", "ag_push", "ag_ring"} <= set(res["seen"])
         assert res["epoch"] == 1 and res["client_launch"] is True and res["completed"] > 50
+        # the burst of eight grouped all-reduces went out as fused launches, built by each
+        # client from the head's plan and its followers' buffers
+        assert res["fused_members"] >= 2
 
 
 def test_client_side_launch_of_the_in_switch_variants(tmp_path):
