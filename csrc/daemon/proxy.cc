@@ -171,13 +171,13 @@ bool ProxyEngine::post(RankState& rs, const proto::WorkRequest& wr) {
     } else {
       op.holds_refs = true;
     }
-    if (status != proto::kOk) {}
-    else if (sdev != rs.device || rdev != rs.device)
-      status = proto::kErrInvalidArgument;
-    // Elements must be naturally aligned: the kernels load and store whole elements, and
-    // a misaligned access is a device fault, not an error code.
-    else if (((op.send_va | op.recv_va) & (esz - 1)) != 0)
-      status = proto::kErrInvalidArgument;
+    if (status == proto::kOk) {
+      // Both buffers on the rank's own device, and elements naturally aligned: the kernels
+      // load and store whole elements, and a misaligned access is a device fault, not an
+      // error code.
+      if (sdev != rs.device || rdev != rs.device) status = proto::kErrInvalidArgument;
+      else if (((op.send_va | op.recv_va) & (esz - 1)) != 0) status = proto::kErrInvalidArgument;
+    }
   }
   if (status != proto::kOk && op.holds_refs) {
     op.holds_refs = false;
