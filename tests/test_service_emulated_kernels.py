@@ -269,3 +269,75 @@ def test_client_side_launch_of_the_in_switch_variants(tmp_path):
         assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
         assert {"ar_nvls_oneshot", "ar_nvls_twoshot", "ar_hybrid", "ag_nvls"} <= set(res["seen"])
         assert res["client_launch"] is True
+
+
+GROUP_CLIENT = r"""
+import os, sys, json, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"]); port = int(os.environ["ADMIN_PORT"])
+comm = M.Communicator(6500, rank, n, device=rank)
+bufs = [M.Buffer(4096, rank) for _ in range(40)]
+ts = [b.tensor(torch.float32, 64 + 8 * (i % 5)) for i, b in enumerate(bufs)]
+gat_buf = M.Buffer(256 * n, rank)           # the object owns the memory: it must outlive its tensors
+gat = gat_buf.tensor(torch.uint8, 256 * n)
+bad = []
+for rnd in range(3):
+    for i, t in enumerate(ts):
+        t.fill_(float(rank + i + rnd))
+    gat[rank * 256:(rank + 1) * 256] = rank + 1 + rnd
+    with M.group():
+        # more members than the plan ring holds (the library takes plans as it goes), an
+        # all-gather in the middle (never fused), a max in between sums (ends a fused run)
+        for i, t in enumerate(ts[:25]):
+            comm.all_reduce(t, algo="ar_twoshot")
+        comm.all_gather(gat[rank * 256:(rank + 1) * 256], gat)
+        comm.all_reduce(ts[25], op="max", algo="ar_twoshot")
+        for t in ts[26:]:
+            comm.all_reduce(t, algo="ar_twoshot")
+    for i, t in enumerate(ts):
+        want = float(n - 1 + i + rnd) if i == 25 else float(sum(range(n)) + n * (i + rnd))
+        if not bool(torch.all(t == want)):
+            bad.append((rnd, i, float(t[0]), want))
+    if [int(gat[r * 256]) for r in range(n)] != [r + 1 + rnd for r in range(n)]:
+        bad.append((rnd, "gather"))
+# dependent members must not share a launch: out of one is the input of the next
+a, b, c = ts[0], ts[1], ts[2]
+a.fill_(1.0)
+with M.group():
+    comm.all_reduce(a, a, algo="ar_twoshot")          # a = n
+    comm.all_reduce(a, a, algo="ar_twoshot")          # a = n * n
+if not bool(torch.all(a == float(n * n))):
+    bad.append(("dependent", float(a[0])))
+q = comm.query()
+st = M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"]["6500"]
+comm.destroy()
+print("RESULT", json.dumps({"bad": bad[:5], "async_error": q["async_error"], "device_error": q["device_error"],
+                            "fused_launches": st["fused_launches"], "fused_members": st["fused_members"],
+                            "client_launch": st["client_launch"], "completed": st["completed"]}), flush=True)
+"""
+
+
+@pytest.mark.parametrize("launch", ["client", "daemon"])
+def test_large_and_mixed_groups_with_fused_launches(tmp_path, launch):
+    """Groups that are larger than the plan ring, contain collectives that cannot be fused and
+    members that depend on each other: fused where allowed, right everywhere."""
+    from mccs_b200 import daemon
+    n = 3
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=n, listen_port=-1, force_host=True,
+                       wait_timeout_ms=20000, extra=f'host_kernels = "emulated"\nfuse_allreduce = 8\nlaunch = "{launch}"')
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), MCCS_LOG="error",
+                   ADMIN_PORT=str(sp.admin_port), MCCS_WC_TIMEOUT_MS="60000")
+        procs = [subprocess.Popen([sys.executable, "-c", GROUP_CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                                  stderr=subprocess.PIPE, text=True) for r in range(n)]
+        for p in procs:
+            out, err = p.communicate(timeout=600)
+            assert p.returncode == 0, err[-3000:]
+            res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+            assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
+            assert res["client_launch"] is (launch == "client")
+            assert res["fused_launches"] > 0 and res["completed"] > 0
+    finally:
+        sp.stop()
