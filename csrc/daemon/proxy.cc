@@ -821,8 +821,9 @@ bool ProxyEngine::launch_group(Communicator& c, CollSlot& s, uint64_t seq) {
 // (6): completion
 // ---------------------------------------------------------------------------
 // Client-side launch: the plan ring carries the answer to every request, the plan itself
-// or the reason there is none. The client has one request outstanding at a time, so the
-// ring cannot be full; should it ever be, the caller retries.
+// or the reason there is none. A client keeps fewer requests outstanding than the ring has
+// places (one outside a group; inside a group it takes the answers before the ring fills),
+// so a push only fails while the client is behind; the caller then comes back.
 bool ProxyEngine::publish_plan_error(RankState& rs, uint64_t user_seq, int status) {
   proto::PlanMsg m;
   memset(&m, 0, sizeof m);
@@ -1051,8 +1052,9 @@ bool ProxyEngine::advance(RankState& rs) {
       status = s.status;
       if (s.ops[rs.rank].sync_slot) signal_done(rs, s.ops[rs.rank].user_seq, status);
     } else if (follower) {
-      if (c.client_launch && !publish_follower_plan(rs, s)) break;
+      // One answer per request: the error, or the member's buffers.
       if (c.state.load() == kCommError) status = c.async_error.load();
+      if (status == proto::kOk && c.client_launch && !publish_follower_plan(rs, s)) break;
     } else if (c.client_launch) {
       if (!publish_plan(rs, s, seq)) break;   // the rank's own library launches the kernel
     } else if (group) {

@@ -1064,6 +1064,54 @@ mccsResult_t run_planned(mccsComm* comm, uint64_t user_seq, proto::PlanMsg& plan
 struct DeferredLaunch { mccsComm* comm; uint64_t user_seq; mccsStream_t stream; };
 thread_local std::vector<DeferredLaunch> g_deferred;
 
+bool names_deferred(const mccsComm* comm) {
+  for (const DeferredLaunch& d : g_deferred)
+    if (d.comm == comm) return true;
+  return false;
+}
+
+bool ring_out_of_step(mccsResult_t r) { return r == mccsTimeout || r == mccsNotConnected || r == mccsProtocolError; }
+
+// A fused launch: `head` (the answer to items[i]) carries the launch shape, the barrier epoch
+// and the ticket; the answers to the next batch_len - 1 requests of the same communicator
+// carry the other members' buffers. Every answer is taken off the ring even when one member
+// cannot run here (the launch then does not happen), so the ring stays in step.
+mccsResult_t launch_fused(const std::vector<DeferredLaunch>& items, size_t i, const proto::PlanMsg& head) {
+  mccsComm* comm = items[i].comm;
+  const int len = head.batch_len;
+  if (len > kMaxBatch || i + (size_t)len > items.size()) return mccsProtocolError;
+  for (int k = 1; k < len; k++)
+    if (items[i + (size_t)k].comm != comm) return mccsProtocolError;
+  comm->last_variant = (uint32_t)head.variant;
+  comm->last_ctas = (uint32_t)head.ctas;
+  BatchArgs b;
+  memset(&b, 0, sizeof b);
+  b.nops = len;
+  mccsResult_t result = args_from_plan(comm, head, &b.base);
+  for (int k = 0; k < len; k++) {
+    proto::PlanMsg member = head;
+    if (k > 0) {
+      mccsResult_t r = wait_plan(comm, items[i + (size_t)k].user_seq, &member);
+      if (ring_out_of_step(r)) return r;
+      if (r == mccsSuccess && member.batch_len != -1) return mccsProtocolError;
+      if (r != mccsSuccess) {
+        if (result == mccsSuccess) result = r;
+        continue;
+      }
+    }
+    if (result != mccsSuccess) continue;
+    CollArgs ma;
+    result = args_from_plan(comm, member, &ma);
+    if (result != mccsSuccess) continue;
+    b.count[k] = member.count;
+    for (int q = 0; q < comm->nranks; q++) { b.send[k][q] = ma.send[q]; b.recv[k][q] = ma.recv[q]; }
+    b.mc_send[k] = ma.mc_send;
+    b.mc_recv[k] = ma.mc_recv;
+  }
+  if (result != mccsSuccess) return result;
+  return launch_here(comm, kAllReduce, b.base, &b, LaunchDims{head.ctas, head.threads}, items[i].stream);
+}
+
 mccsResult_t flush_deferred() {
   std::vector<DeferredLaunch> items;
   items.swap(g_deferred);
@@ -1073,38 +1121,14 @@ mccsResult_t flush_deferred() {
     proto::PlanMsg plan;
     mccsResult_t r = wait_plan(comm, items[i].user_seq, &plan);
     if (r == mccsSuccess && plan.batch_len >= 2) {
-      // A fused launch: this plan is the head (launch shape, barrier epoch, ticket), the
-      // answers to the next batch_len - 1 requests of this communicator are its members.
-      const int len = plan.batch_len;
-      comm->last_variant = (uint32_t)plan.variant;
-      comm->last_ctas = (uint32_t)plan.ctas;
-      BatchArgs b;
-      memset(&b, 0, sizeof b);
-      r = len <= kMaxBatch && i + (size_t)len <= items.size() ? args_from_plan(comm, plan, &b.base) : mccsProtocolError;
-      b.nops = len;
-      for (int k = 0; k < len && r == mccsSuccess; k++) {
-        proto::PlanMsg member = plan;
-        if (k > 0) {
-          if (items[i + (size_t)k].comm != comm) { r = mccsProtocolError; break; }
-          r = wait_plan(comm, items[i + (size_t)k].user_seq, &member);
-          if (r == mccsSuccess && member.batch_len != -1) r = mccsProtocolError;
-        }
-        CollArgs ma;
-        if (r == mccsSuccess) r = args_from_plan(comm, member, &ma);
-        if (r != mccsSuccess) break;
-        b.count[k] = member.count;
-        for (int q = 0; q < comm->nranks; q++) { b.send[k][q] = ma.send[q]; b.recv[k][q] = ma.recv[q]; }
-        b.mc_send[k] = ma.mc_send;
-        b.mc_recv[k] = ma.mc_recv;
-      }
-      if (r == mccsSuccess) r = launch_here(comm, kAllReduce, b.base, &b, LaunchDims{plan.ctas, plan.threads}, items[i].stream);
-      i += (size_t)len - 1;
+      r = launch_fused(items, i, plan);
+      i += (size_t)plan.batch_len - 1;
     } else if (r == mccsSuccess) {
       r = run_planned(comm, items[i].user_seq, plan, items[i].stream);
     }
     if (r != mccsSuccess) {
       if (result == mccsSuccess) result = r;
-      if (r == mccsTimeout || r == mccsNotConnected || r == mccsProtocolError) return r;   // the ring is out of step: stop here
+      if (ring_out_of_step(r)) return r;
     }
   }
   return result;
@@ -1324,7 +1348,7 @@ mccsResult_t mccsFree(void* ptr) {
     }
     if (g_ctx.connected)
       for (mccsComm* c : mine)
-        if (c->outstanding || c->memop_posted) mccsCommFlush(c);
+        if (c->outstanding || c->memop_posted || names_deferred(c)) mccsCommFlush(c);
     // Kernels launched from here (client-side launch) run on the caller's streams: the
     // daemon cannot wait for them, so this call does, before the memory and the multicast
     // bindings that name it go away.
@@ -1516,6 +1540,13 @@ mccsResult_t mccsCommInitRank(mccsComm_t* comm, uint32_t unique_id, int rank, in
 
 mccsResult_t mccsCommFlush(mccsComm_t comm) {
   if (!comm) return mccsInvalidArgument;
+  // Requests of an open group whose plans have not been taken yet are launched now: nothing
+  // that the caller does after a flush (free, destroy, reading the last plan) may find them
+  // half way.
+  if (names_deferred(comm)) {
+    mccsResult_t r = flush_deferred();
+    if (r == mccsTimeout || r == mccsNotConnected) return r;
+  }
   proto::WorkCompletion wc;
   while (comm->outstanding > 0) {
     mccsResult_t r = wait_completion(comm, &wc);
@@ -1544,6 +1575,11 @@ mccsResult_t mccsCommFlush(mccsComm_t comm) {
 mccsResult_t mccsCommDestroy(mccsComm_t comm) {
   if (!comm) return mccsSuccess;
   if (g_ctx.connected) mccsCommFlush(comm);   // every posted request has been taken by the daemon
+  // A handle destroyed inside an open group must not be looked at again when the group ends.
+  for (size_t i = g_group_items.size(); i-- > 0;)
+    if (g_group_items[i].comm == comm) g_group_items.erase(g_group_items.begin() + (long)i);
+  for (size_t i = g_deferred.size(); i-- > 0;)
+    if (g_deferred[i].comm == comm) g_deferred.erase(g_deferred.begin() + (long)i);
   if (comm->launched_here && g_ctx.backend == proto::kBackendCuda && g_drv.cuCtxSynchronize_) {
     // Kernels of this communicator run on the caller's streams: they must be through
     // before the daemon takes the pads and FIFOs away. Their waits are bounded.

@@ -24,7 +24,8 @@ def inputs(dt, count, salt):
     g = torch.Generator().manual_seed(1000 * salt + count)
     return [torch.randint(-4, 5, (count,), generator=g).to(dt) for _ in range(n)]
 send = M.Buffer(1 << 20, rank); recv = M.Buffer(1 << 21, rank)
-comm = M.Communicator(6100, rank, n, device=rank)
+CID = 6100
+comm = M.Communicator(CID, rank, n, device=rank)
 bad = []
 seen = set()
 salt = 0
@@ -76,7 +77,9 @@ if os.environ.get("HOST_STAGED") == "1":
         bad.append(("reduce_scatter accepted on the host-staged transport",))
     except Exception as e:
         if getattr(e, "code", None) != -9: bad.append(("reduce_scatter", str(e)))
-    comm.destroy(); comm = M.Communicator(6100, rank, n, device=rank)   # the refusal ended the communicator
+    # the refusal ended the communicator; a new one takes a new id (the old id stays taken until
+    # every rank has let go of it)
+    comm.destroy(); CID = 6101; comm = M.Communicator(CID, rank, n, device=rank)
 for algo in () if os.environ.get("HOST_STAGED") == "1" else ("rs_direct", "auto") + (("rs_nvls",) if os.environ.get("NVLS") == "1" else ()):
     for dname, count in (("f32", 1), ("f32", 1028), ("bf16", 3000), ("i32", 257), ("f64", 100), ("f16", 2048), ("f32", 4099)):
         reduce_scatter(algo, dname, count)
@@ -110,7 +113,7 @@ for algo in ("ag_pull", "ag_push", "ag_ring", "auto"):
 allreduce("ar_ring", "f32", 150000)
 if rank == 0:
     ring = list(reversed(range(n)))
-    rep = M.reconfigure(port, [{"communicator_id": 6100, "channels": [{"channel_id": 0, "ring": ring}, {"channel_id": 1, "ring": list(range(n))}, {"channel_id": 2, "ring": ring}]}])
+    rep = M.reconfigure(port, [{"communicator_id": CID, "channels": [{"channel_id": 0, "ring": ring}, {"channel_id": 1, "ring": list(range(n))}, {"channel_id": 2, "ring": ring}]}])
     assert rep.get("status") == "ok", rep
 for _ in range(3):
     allreduce("ar_ring", "f32", 70000)
@@ -127,7 +130,7 @@ for i, t in enumerate(ts):
     if not bool(torch.all(t == float(sum(range(n)) + n * i))):
         bad.append(("group", i))
 q = comm.query()
-st = M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"]["6100"]
+st = M.admin_request(port, {"cmd": "stats"})["stats"]["communicators"][str(CID)]
 comm.destroy()
 print("RESULT", json.dumps({"bad": bad, "seen": sorted(seen), "async_error": q["async_error"], "device_error": q["device_error"],
                             "fused_members": st["fused_members"], "epoch": st["config_epoch"],
@@ -339,5 +342,69 @@ def test_large_and_mixed_groups_with_fused_launches(tmp_path, launch):
             assert res["bad"] == [] and res["async_error"] == 0 and res["device_error"] == 0
             assert res["client_launch"] is (launch == "client")
             assert res["fused_launches"] > 0 and res["completed"] > 0
+    finally:
+        sp.stop()
+
+
+OPEN_GROUP_CLIENT = r"""
+import os, sys, json, torch
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"])
+comm = M.Communicator(6600, rank, n, device=rank)
+other = M.Communicator(6601, rank, n, device=rank)
+bufs = [M.Buffer(4096, rank) for _ in range(6)]
+ts = [b.tensor(torch.float32, 128) for b in bufs]
+res = {}
+for i, t in enumerate(ts):
+    t.fill_(float(rank + i))
+M.client._lib.shim().mccsGroupStart()
+for t in ts[:3]:
+    comm.all_reduce(t, algo="ar_twoshot")
+res["plan_inside"] = comm.last_plan()[0]          # flushes: the three run now, inside the open group
+res["inside_ok"] = all(bool(torch.all(t == float(sum(range(n)) + n * i))) for i, t in enumerate(ts[:3]))
+comm.all_reduce(ts[3], algo="ar_twoshot")
+ts[3] = None
+bufs[3].free()                                     # a free inside the group settles what names the memory first
+other.all_reduce(ts[4], algo="ar_twoshot")
+other.destroy()                                    # so does destroying a communicator with requests pending
+comm.all_reduce(ts[5], algo="ar_twoshot")
+res["group_end"] = int(M.client._lib.shim().mccsGroupEnd())
+res["after_ok"] = all(bool(torch.all(ts[i] == float(sum(range(n)) + n * i))) for i in (4, 5))
+# ranks that disagree inside a fused group: every rank gets the error when the group ends, the
+# requests before the bad one have run, nothing waits for ever
+a, b, c = ts[0], ts[1], ts[2]
+a.fill_(1.0); b.fill_(1.0); c.fill_(1.0)
+M.client._lib.shim().mccsGroupStart()
+comm.all_reduce(a, algo="ar_twoshot")
+comm.all_reduce(b, count=64 if rank == 1 else 128, algo="ar_twoshot")
+comm.all_reduce(c, algo="ar_twoshot")
+res["mismatch_rc"] = int(M.client._lib.shim().mccsGroupEnd())
+res["first_ran"] = bool(torch.all(a == float(n)))
+comm.destroy()
+print("RESULT", json.dumps(res), flush=True)
+"""
+
+
+def test_open_groups_settle_before_free_destroy_and_queries(tmp_path):
+    """Client-side launch with fused launches on: requests of an open group are only posted.
+    Reading the last plan, freeing a buffer and destroying a communicator inside the group each
+    launch what is pending first; a group whose ranks disagree ends with an error on every rank."""
+    from mccs_b200 import daemon
+    n = 2
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=n, listen_port=-1, force_host=True,
+                       wait_timeout_ms=5000, extra='host_kernels = "emulated"\nfuse_allreduce = 8\nlaunch = "client"')
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "error"})
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, WORLD_SIZE=str(n), MCCS_LOG="off", MCCS_WC_TIMEOUT_MS="30000")
+        procs = [subprocess.Popen([sys.executable, "-c", OPEN_GROUP_CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                                  stderr=subprocess.PIPE, text=True) for r in range(n)]
+        for p in procs:
+            out, err = p.communicate(timeout=300)
+            assert p.returncode == 0, err[-3000:]
+            res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+            assert res["plan_inside"] == "ar_twoshot" and res["inside_ok"]
+            assert res["group_end"] == 0 and res["after_ok"]
+            assert res["mismatch_rc"] != 0 and res["first_ran"]
     finally:
         sp.stop()
