@@ -49,22 +49,23 @@ REFERENCE_JCT_MS = {   # eval/plot/real_workload/jct.csv, means of 10 runs on th
 }
 
 
-def policy_config(policy: str, vgg_comm_us: int, gpt_comm_us: int) -> str:
+def policy_config(policy: str, vgg_comm_us: int, gpt_comm_us: int, time_scale: float = 1.0) -> str:
     if policy == "fair":
         return ""
     text = f"[qos.tenants.{JOBS['vgg'][0]}]\nweight = 4.0\npriority = 1\n"
     if policy == "qosv2":
-        premium, victim, epoch = calculate_intervals(JOBS["vgg"][2], vgg_comm_us, JOBS["gpt_1"][2], gpt_comm_us,
-                                                     epoch=JOBS["vgg"][2] + vgg_comm_us)
+        vgg_compute = max(int(JOBS["vgg"][2] * time_scale), 1)
+        gpt_compute = max(int(JOBS["gpt_1"][2] * time_scale), 1)
+        premium, victim, epoch = calculate_intervals(vgg_compute, vgg_comm_us, gpt_compute, gpt_comm_us, epoch=vgg_compute + vgg_comm_us)
         text += to_toml(epoch, {JOBS["vgg"][0]: premium, JOBS["gpt_1"][0]: victim, JOBS["gpt_2"][0]: victim})
     return text
 
 
 def run_policy(policy: str, place: Dict[str, List[int]], scale: float, work: str, host: bool, vgg_comm_us: int,
-               gpt_comm_us: int, timeout: float) -> dict:
+               gpt_comm_us: int, timeout: float, size_scale: float = 1.0, time_scale: float = 1.0) -> dict:
     prefix = os.path.join(work, policy)
     os.makedirs(prefix, exist_ok=True)
-    cfg = daemon.default_config(prefix, listen_port=-1, host_devices=8, force_host=host) + policy_config(policy, vgg_comm_us, gpt_comm_us)
+    cfg = daemon.default_config(prefix, listen_port=-1, host_devices=8, force_host=host) + policy_config(policy, vgg_comm_us, gpt_comm_us, time_scale)
     with open(prefix + "/mccs.toml", "w") as f:
         f.write(cfg)
     sp = daemon.spawn(prefix + "/mccs.toml", env={"MCCS_LOG": "warn"})
@@ -73,6 +74,8 @@ def run_policy(policy: str, place: Dict[str, List[int]], scale: float, work: str
         env = dict(os.environ, MCCS_CONTROL=sp.control, MCCS_LOG="error")
         for name, (cid, size, compute, iters) in JOBS.items():
             trace = f"{prefix}/{name}.toml"
+            size = max(int(size * size_scale) // 16 * 16, 16)
+            compute = max(int(compute * time_scale), 1)
             with open(trace, "w") as f:
                 f.write(f"communicator_id = {cid}\ncuda_devices = {place[name]}\n[[traces]]\nsize = {size}\ntype = \"all_reduce\"\n"
                         f"compute_interval = {compute}\n")
@@ -112,14 +115,18 @@ def main() -> int:
     ap.add_argument("--vgg-comm-us", type=int, default=2000, help="VGG's AllReduce time alone, for the window schedule")
     ap.add_argument("--gpt-comm-us", type=int, default=400, help="a GPT job's AllReduce time alone")
     ap.add_argument("--host", action="store_true", help="host backend (a dry run of the tool without GPUs)")
+    ap.add_argument("--size-scale", type=float, default=1.0, help="multiplies the message sizes (dry runs)")
+    ap.add_argument("--time-scale", type=float, default=1.0, help="multiplies the compute intervals (dry runs)")
     ap.add_argument("--timeout", type=float, default=900.0)
     ap.add_argument("--out", default="")
     a = ap.parse_args()
     place = PLACEMENT[a.placement]
-    res = {"placement": a.placement, "devices": place, "scale": a.scale, "policies": {}}
+    res = {"placement": a.placement, "devices": place, "scale": a.scale, "size_scale": a.size_scale, "time_scale": a.time_scale,
+           "policies": {}}
     with tempfile.TemporaryDirectory(prefix="mccs-colocate-") as work:
         for policy in a.policies.split(","):
-            res["policies"][policy] = run_policy(policy, place, a.scale, work, a.host, a.vgg_comm_us, a.gpt_comm_us, a.timeout)
+            res["policies"][policy] = run_policy(policy, place, a.scale, work, a.host, a.vgg_comm_us, a.gpt_comm_us, a.timeout,
+                                                 a.size_scale, a.time_scale)
     text = json.dumps(res, indent=1)
     if a.out:
         with open(a.out, "w") as f:

@@ -203,3 +203,20 @@ def test_sweep_tuner_and_report_pipeline_on_cpu(tmp_path, service):
     rep = subprocess.run([sys.executable, "-m", "mccs_b200.utils.report", csv_path], capture_output=True, text=True, cwd=REPO,
                          env=env, timeout=60)
     assert rep.returncode == 0 and rep.stdout.count("| allreduce | bf16 | 2 |") == 3 and rep.stdout.count("| allgather |") == 3
+
+
+def test_trace_colocation_tool_on_host_backend():
+    """The real-workload co-location experiment as a dry run: the three traces side by side
+    under the three policies (none, weight + priority, weight + priority + time windows),
+    sizes and compute intervals scaled down; every job of every policy reports its times."""
+    import json
+    res = subprocess.run([sys.executable, "-m", "mccs_b200.utils.colocate_traces", "--host", "--scale", "0.001", "--size-scale", "0.0005",
+                          "--time-scale", "0.02", "--vgg-comm-us", "400", "--gpt-comm-us", "100", "--timeout", "120"],
+                         capture_output=True, text=True, cwd=REPO, env=dict(os.environ, PYTHONPATH=REPO, MCCS_LOG="error"), timeout=400)
+    assert res.returncode == 0, res.stderr[-3000:]
+    out = json.loads(res.stdout[res.stdout.index("{"):])
+    assert set(out["policies"]) == {"fair", "qosv1", "qosv2"}
+    for policy, jobs in out["policies"].items():
+        assert set(jobs) == {"vgg", "gpt_1", "gpt_2"}
+        for name, job in jobs.items():
+            assert job["iterations"] == 22 and job["jct_ms"] is not None and job["mean_iter_ms"] > 0, (policy, name, job)
