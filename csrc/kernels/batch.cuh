@@ -51,27 +51,12 @@ __device__ __forceinline__ bool batch_aligned16(const BatchArgs& b, int k) {
   return (bits & 15u) == 0;
 }
 
-// One member of a batch: the two-shot exchange of `count` elements. The 16-byte path is
-// always the "eight sources, unroll 2" form: with the member loop's bookkeeping live as
-// well, the "four sources, unroll 4" form of the single kernel no longer fits 128
-// registers and spills.
-template <typename T, typename Op>
-__device__ __forceinline__ void twoshot_member(const char* const* src, char* const* dst, uint64_t count,
-                                            bool aligned, int rank, int nranks, int op, float scale) {
-  Scaler<typename AccOf<T>::type> sc{scaler_mode(op), scale};
-  constexpr int kN = 16 / (int)sizeof(T);
-  uint64_t done = 0;
-  if (aligned) {
-    const uint64_t nv = count / kN;
-    Range mine = split_range(nv, nranks, rank);
-    reduce_store<T, Op, 16, 2, kMaxRanks>(src, nranks, dst, nranks, mine.beg, mine.end, blockIdx.x, gridDim.x, sc);
-    done = nv * kN;
-  }
-  Range mine = split_range(count - done, nranks, rank);
-  reduce_store<T, Op, sizeof(T), 1, kMaxRanks>(src, nranks, dst, nranks, done + mine.beg, done + mine.end,
-                                               blockIdx.x, gridDim.x, sc);
-}
-
+// The members are walked twice: first the whole 16-byte packs of every member whose buffers
+// are 16-byte aligned, then what is left of each member (less than a pack, or all of it when a
+// buffer is not aligned) element by element. One walk doing both per member kept the second
+// part's operands live across the pack loop, beyond 128 registers. The pack loop is the "eight
+// sources, unroll 2" form: the "four sources, unroll 4" form of the single kernel does not
+// fit next to the member loop either.
 template <typename T, typename Op>
 __global__ void __launch_bounds__(kMaxThreads) ar_twoshot_batch_kernel(const __grid_constant__ BatchArgs b) {
   const CollArgs& a = b.base;
@@ -79,16 +64,36 @@ __global__ void __launch_bounds__(kMaxThreads) ar_twoshot_batch_kernel(const __g
   __shared__ const char* s_src[kMaxRanks];
   __shared__ char* s_dst[kMaxRanks];
   if (!batch_begin(b, rank)) return;
+  constexpr uint64_t kN = 16 / sizeof(T);
 
 #pragma unroll 1
   for (int k = 0; k < b.nops; k++) {
+    if (!batch_aligned16(b, k) || b.count[k] < kN) continue;   // the same answer in every thread
     __syncthreads();   // the previous member's users of s_src / s_dst are done
     if (threadIdx.x < a.nranks) {
       s_src[threadIdx.x] = (const char*)b.send[k][threadIdx.x];
       s_dst[threadIdx.x] = (char*)b.recv[k][threadIdx.x];
     }
     __syncthreads();
-    twoshot_member<T, Op>(s_src, s_dst, b.count[k], batch_aligned16(b, k), rank, a.nranks, a.op, a.scale);
+    Scaler<typename AccOf<T>::type> sc{scaler_mode(a.op), a.scale};
+    const Range mine = split_range(b.count[k] / kN, a.nranks, rank);
+    reduce_store<T, Op, 16, 2, kMaxRanks>(s_src, a.nranks, s_dst, a.nranks, mine.beg, mine.end, blockIdx.x, gridDim.x, sc);
+  }
+#pragma unroll 1
+  for (int k = 0; k < b.nops; k++) {
+    const uint64_t count = b.count[k];
+    const uint64_t done = batch_aligned16(b, k) ? count / kN * kN : 0;
+    if (done == count) continue;
+    __syncthreads();
+    if (threadIdx.x < a.nranks) {
+      s_src[threadIdx.x] = (const char*)b.send[k][threadIdx.x];
+      s_dst[threadIdx.x] = (char*)b.recv[k][threadIdx.x];
+    }
+    __syncthreads();
+    Scaler<typename AccOf<T>::type> sc{scaler_mode(a.op), a.scale};
+    const Range mine = split_range(count - done, a.nranks, rank);
+    reduce_store<T, Op, sizeof(T), 1, kMaxRanks>(s_src, a.nranks, s_dst, a.nranks, done + mine.beg, done + mine.end,
+                                                 blockIdx.x, gridDim.x, sc);
   }
   if (!rank_barrier<true>(a, rank, a.epoch + 1, kDevTimeoutEnd)) return;
   batch_end(b, rank);

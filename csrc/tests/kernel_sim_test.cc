@@ -390,7 +390,7 @@ void batch_case(World& w, bool nvls, int nops, int ctas, int threads, bool emula
   for (int k = 0; k < nops; k++) {
     size_t count = counts[k];
     if (nvls) count = (count + 7) / 8 * 8 + (k == 2 ? 3 : 0);   // one member with a sub-16-byte tail
-    bufs.emplace_back(new Buffers<T>(n, count, 0));
+    bufs.emplace_back(new Buffers<T>(n, count, !nvls && k == 4 ? 1 : 0));   // one member that is not 16-byte aligned
     b.count[k] = count;
     for (int r = 0; r < n; r++) {
       for (size_t i = 0; i < count; i++) bufs.back()->send(r)[i] = Dt<T>::to((double)((int)((i * 7 + (size_t)r * 3 + (size_t)k) % 9) - 4));
