@@ -543,7 +543,17 @@ void Daemon::on_comm_init(Session& s, const proto::CommInitReq& m) {
     }
     Communicator& c = *it->second;
     if (c.state.load() != kCommInit || c.nranks != m.nranks || c.ranks[(size_t)m.rank]) {
-      // The id is in use (or the ranks disagree on the size).
+      // The id is in use (or the ranks disagree on the size). If the communicator that holds it
+      // is on its way out (a rank has left already: the others are about to, or will be told),
+      // the request waits for the id instead of failing; a rank that destroys a communicator and
+      // creates its successor under the same id is simply ahead of its peers.
+      bool closing = false;
+      if (c.state.load() != kCommInit)
+        for (auto& r : c.ranks) closing |= r && r->gone.load();
+      if (closing) {
+        parked_inits_.push_back({s.id, m, monotonic_us() + cfg_.init_timeout_ms * 1000});
+        return;
+      }
       return fail(proto::kErrInvalidArgument);
     }
     auto rs = std::make_unique<RankState>();
@@ -726,7 +736,41 @@ int Daemon::finalize_communicator(Communicator& c) {
   return proto::kOk;
 }
 
+// Second (third, ...) pass for requests that wait for their id: through on_comm_init again
+// once the old communicator is gone, answered with an error when their time is up.
+void Daemon::retry_parked_inits() {
+  if (parked_inits_.empty()) return;
+  std::vector<ParkedInit> parked;
+  parked.swap(parked_inits_);
+  const uint64_t now = monotonic_us();
+  for (ParkedInit& pi : parked) {
+    Session* ps = nullptr;
+    bool id_taken = false;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      auto it = sessions_.find(pi.session_id);
+      if (it != sessions_.end()) ps = it->second.get();
+      auto cit = comms_.find(pi.req.comm_id);
+      id_taken = cit != comms_.end() && cit->second->state.load() != kCommInit;
+    }
+    if (!ps) continue;   // the client went away while it waited
+    if (!id_taken) {
+      on_comm_init(*ps, pi.req);
+    } else if (now > pi.deadline_us) {
+      proto::AnyMsg r;
+      memset(&r, 0, sizeof r);
+      r.h.type = proto::kCommInitReply;
+      r.h.req_id = pi.req.h.req_id;
+      r.h.status = proto::kErrInvalidArgument;
+      reply(*ps, r, sizeof(proto::CommInitReply));
+    } else {
+      parked_inits_.push_back(pi);
+    }
+  }
+}
+
 void Daemon::check_init_timeouts() {
+  retry_parked_inits();
   const uint64_t now = monotonic_us();
   std::vector<PendingInit> expired;
   {

@@ -358,6 +358,11 @@ class Daemon {
   std::map<uint32_t, std::unique_ptr<Communicator>> comms_;
   struct PendingInit { uint64_t session_id; uint32_t req_id; uint32_t comm_id; int rank; uint64_t deadline_us; };
   std::vector<PendingInit> pending_inits_;
+  // Requests for an id whose previous communicator is still being let go of by its other
+  // ranks: answered (by a second pass through on_comm_init) once the id is free.
+  struct ParkedInit { uint64_t session_id; proto::CommInitReq req; uint64_t deadline_us; };
+  std::vector<ParkedInit> parked_inits_;   // control thread only
+  void retry_parked_inits();
   uint64_t next_session_id_ = 1;
 
   mutable std::shared_mutex alloc_mu_;

@@ -261,3 +261,43 @@ def test_functional_ops_over_a_communicator(service):
         assert torch.all(y == 6.0) and torch.all(x == 3.0) and torch.all(g == 3.0)
     with pytest.raises(ValueError):
         ops.local_all_reduce_no_alloc([torch.zeros(8)])          # CPU tensors are refused, not silently summed
+
+
+def test_an_id_can_be_taken_again_while_peers_still_let_go(service):
+    """A rank that destroys its communicator and creates the next one under the same id is
+    only ahead of its peers: the request waits until the old communicator is gone. An id held
+    by an intact communicator is refused at once."""
+    import time
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    cid = fresh_comm_id()
+
+    def rank_fn(r):
+        buf = M.Buffer(4096, r)
+        t = buf.tensor(torch.float32, 256)
+        c = M.Communicator(cid, r, 2, device=r)
+        t.fill_(float(r + 1))
+        c.all_reduce(t)
+        first = float(t[0])
+        refused, took = None, 0.0
+        if r == 0:
+            t0 = time.time()
+            try:
+                M.Communicator(cid, 0, 2, device=0)       # nobody has left: the id is simply in use
+            except Exception as e:
+                refused = getattr(e, "code", None)
+            took = time.time() - t0
+        else:
+            time.sleep(0.5)       # rank 0 is back for the id long before rank 1 lets go of it
+        c.destroy()
+        c = M.Communicator(cid, r, 2, device=r)
+        t.fill_(float(r + 3))
+        c.all_reduce(t)
+        second = float(t[0])
+        c.destroy()
+        return first, second, refused, took
+
+    outs = run_ranks(2, rank_fn)
+    assert [o[0] for o in outs] == [3.0, 3.0] and [o[1] for o in outs] == [7.0, 7.0]
+    assert outs[0][2] == -1 and outs[0][3] < 1.0
