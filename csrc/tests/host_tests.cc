@@ -8,6 +8,7 @@
 #include <sys/wait.h>
 #include <unistd.h>
 
+#include <atomic>
 #include <thread>
 
 #include "../common/protocol.h"
@@ -16,6 +17,7 @@
 #include "../daemon/planner.h"
 #include "../daemon/qos.h"
 #include "../daemon/runtime.h"
+#include "../daemon/trace.h"
 #include "../daemon/transport.h"
 #include "../ipc/shm_ring.h"
 #include "../ipc/uds.h"
@@ -490,6 +492,72 @@ static void test_qos() {
   }
 }
 
+// Forty tenants on one GPU, asked for by eight threads the way the proxies do it: a request
+// that was told to wait asks again only when the arbiter's generation moved or a short time
+// went by. Everybody is served, shares follow the weights, and the arbiter's lock is not
+// hammered: the number of questions stays within a small multiple of the admissions.
+static void test_qos_many_tenants() {
+  constexpr int kTenants = 40, kThreads = 8, kPerThread = kTenants / kThreads;
+  Config cfg;
+  for (int t = 0; t < kTenants; t++) cfg.qos_tenants[(uint32_t)(100 + t)].weight = (double)(1 << (t % 3));   // 1, 2, 4
+  cfg.qos_max_outstanding_bytes = 8u << 20;
+  QosArbiter q;
+  q.configure(cfg);
+  for (int t = 0; t < kTenants; t++) q.tenant_register((uint32_t)(100 + t), {0});
+  std::atomic<uint64_t> asks{0}, admissions{0};
+  std::vector<uint64_t> bytes((size_t)kTenants, 0);
+  const uint64_t sz = 1 << 20;
+  const uint64_t t_end = monotonic_us() + 1500000;
+  std::vector<std::thread> threads;
+  for (int w = 0; w < kThreads; w++)
+    threads.emplace_back([&, w]() {
+      struct Mine { uint32_t id; bool deferred = false; uint64_t gen = 0, retry_us = 0; int inflight = 0; };
+      Mine mine[kPerThread];
+      for (int k = 0; k < kPerThread; k++) mine[k].id = (uint32_t)(100 + w * kPerThread + k);
+      while (monotonic_us() < t_end) {
+        for (Mine& m : mine) {
+          const uint64_t now = monotonic_us();
+          if (m.inflight) {               // the "kernel" of the previous admission is through
+            q.complete(m.id, sz);
+            m.inflight = 0;
+          }
+          if (m.deferred && q.generation() == m.gen && now < m.retry_us) continue;
+          m.gen = q.generation();
+          q.note_waiting(m.id, now);
+          asks.fetch_add(1, std::memory_order_relaxed);
+          if (q.admit(m.id, sz, now, 0, 4) == kQosAdmit) {
+            m.deferred = false;
+            m.inflight = 1;
+            bytes[(size_t)(m.id - 100)] += sz;
+            admissions.fetch_add(1, std::memory_order_relaxed);
+          } else {
+            m.deferred = true;
+            m.retry_us = now + 200;
+          }
+        }
+      }
+      for (Mine& m : mine)
+        if (m.inflight) q.complete(m.id, sz);
+    });
+  for (auto& t : threads) t.join();
+  double by_weight[3] = {0, 0, 0};
+  bool all_served = true;
+  for (int t = 0; t < kTenants; t++) {
+    all_served &= bytes[(size_t)t] > 0;
+    by_weight[t % 3] += (double)bytes[(size_t)t];
+  }
+  CHECK(all_served);
+  CHECK(admissions.load() > 2000);
+  // classes 0, 1, 2 hold 14, 13 and 13 tenants of weight 1, 2 and 4
+  const double per1 = by_weight[0] / 14, per2 = by_weight[1] / 13, per4 = by_weight[2] / 13;
+  CHECK(per2 / per1 > 1.5 && per2 / per1 < 2.6);
+  CHECK(per4 / per1 > 3.0 && per4 / per1 < 5.2);
+  CHECK(asks.load() < 40 * admissions.load());
+  if (getenv("MCCS_TEST_VERBOSE"))
+    printf("qos, 40 tenants: %llu admissions, %llu questions, shares 1 : %.2f : %.2f\n", (unsigned long long)admissions.load(),
+           (unsigned long long)asks.load(), per2 / per1, per4 / per1);
+}
+
 static void test_misc() {
   std::vector<int> c = parse_cpu_list("0-3,8,10-11");
   CHECK(c.size() == 7 && c[4] == 8 && c[6] == 11);
@@ -512,6 +580,7 @@ int main() {
   test_transports();
   test_ring_steps();
   test_qos();
+  test_qos_many_tenants();
   test_misc();
   printf("%d checks, %d failed\n", g_checks, g_failed);
   return g_failed;
