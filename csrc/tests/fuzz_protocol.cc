@@ -441,6 +441,24 @@ int main(int argc, char** argv) {
     reap();
     usleep(100);
   }
+  if (client_mode) {
+    // A tenant that posts far ahead of the answers it takes (a group that never ends): the
+    // request ring and the plan ring fill up and the daemon has to sit on answers it cannot
+    // deliver. Nothing may be lost or answered twice once the tenant reads again.
+    g_stage = 25;
+    long burst = 0;
+    for (int i = 0; i < 400; i++) {
+      proto::WorkRequest wr = make_wr(rep.comm_init_reply.comm_handle, kAllReduce, mem_id, mem_id, 16, (uint64_t)(rounds + i));
+      wr.flags = proto::kWrGroupMore;
+      if (!wq.try_push(&wr)) break;
+      burst++;
+    }
+    posted += burst;
+    usleep(100000);
+    for (int spin = 0; spin < 40000 && answered < posted; spin++) { reap(); usleep(50); }
+    usleep(20000);
+    reap();   // a second answer to any of them would show up here
+  }
   const bool all_answered = answered == posted;
   // The segment is writable by the tenant: scribble over the ring headers (geometry and
   // both indices) while the proxy keeps polling them. Whatever it makes of the contents,
