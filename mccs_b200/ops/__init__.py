@@ -112,7 +112,8 @@ def all_reduce(comm: Communicator, send: torch.Tensor, recv: Optional[torch.Tens
         st = ar.get(n * torch.empty((), dtype=work).element_size()).tensor(work, n)
         st.copy_(send.reshape(-1), non_blocking=True)
         comm.all_reduce(st, op=op, scale=scale, algo=algo, stream=stream)
-        out.copy_(st.view(out.shape) if out.dtype == work else st.to(out.dtype).view(out.shape), non_blocking=True)
+        # (a copy to ordinary host memory is left blocking: the caller may read it at once)
+        out.copy_(st.view(out.shape) if out.dtype == work else st.to(out.dtype).view(out.shape), non_blocking=out.is_cuda)
     return out
 
 
@@ -134,9 +135,9 @@ def all_gather(comm: Communicator, send: torch.Tensor, recv: torch.Tensor, *, al
         mine.copy_(send.contiguous().view(torch.uint8).reshape(-1), non_blocking=True)
         comm.all_gather(mine, full, nbytes=nb, algo=algo, stream=stream)      # in place inside the staging buffer
         if recv.is_contiguous():
-            recv.view(torch.uint8).reshape(-1).copy_(full, non_blocking=True)
+            recv.view(torch.uint8).reshape(-1).copy_(full, non_blocking=recv.is_cuda)
         else:
-            recv.copy_(full.view(recv.dtype).view(recv.shape), non_blocking=True)
+            recv.copy_(full.view(recv.dtype).view(recv.shape), non_blocking=recv.is_cuda)
     return recv
 
 
@@ -159,7 +160,7 @@ def reduce_scatter(comm: Communicator, send: torch.Tensor, recv: torch.Tensor, *
         st.copy_(send.reshape(-1), non_blocking=True)
         mine = st[comm.rank * blk:(comm.rank + 1) * blk]
         comm.reduce_scatter(st, mine, op=op, scale=scale, algo=algo, stream=stream)     # in place in the staging buffer
-        recv.copy_(mine.view(recv.shape) if recv.dtype == work else mine.to(recv.dtype).view(recv.shape), non_blocking=True)
+        recv.copy_(mine.view(recv.shape) if recv.dtype == work else mine.to(recv.dtype).view(recv.shape), non_blocking=recv.is_cuda)
     return recv
 
 

@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import os
 import threading
+import weakref
 from ctypes import byref, c_uint64, c_void_p
 from typing import List, Optional
 
@@ -83,6 +84,17 @@ def mem_pool():
     return torch.cuda.MemPool(_pool_allocator.allocator())
 
 
+_groups: "weakref.WeakSet[ProcessGroupMCCS]" = weakref.WeakSet()
+
+
+def shutdown() -> None:
+    """Shuts down every process group of this backend that is still alive in this process
+    (``dist.destroy_process_group()`` drops the group object without telling a backend written
+    in Python): call it before the process ends, while its CUDA context is still there."""
+    for g in list(_groups):
+        g.shutdown()
+
+
 class ProcessGroupMCCS(dist.ProcessGroup):
     """One rank of a process group whose collectives run in the mccs daemon."""
 
@@ -105,6 +117,8 @@ class ProcessGroupMCCS(dist.ProcessGroup):
         self.comm_id = comm_id
         self._comm = Communicator(comm_id, rank, size, device=self._device)
         self._lock = threading.Lock()
+        self._closed = False
+        _groups.add(self)
 
     # -- helpers: the functional collectives of mccs_b200.ops do the work, in place for tensors
     # in service memory, through the communicator's staging arena otherwise -------------------
@@ -214,6 +228,11 @@ class ProcessGroupMCCS(dist.ProcessGroup):
         return self._comm
 
     def shutdown(self) -> None:
+        """Waits for this rank's collectives, then gives the staging memory and the
+        communicator back to the service. Safe to call more than once."""
+        if self._closed:
+            return
+        self._closed = True
         self._sync()
         _arena(self._comm).release()
         self._comm.destroy()
@@ -228,4 +247,4 @@ def _create(store, rank, size, timeout):
 
 dist.Backend.register_backend("mccs", _create, devices=["cpu", "cuda"])
 
-__all__ = ["ProcessGroupMCCS", "empty", "mem_pool", "in_service_memory"]
+__all__ = ["ProcessGroupMCCS", "empty", "mem_pool", "in_service_memory", "shutdown"]
