@@ -54,9 +54,11 @@ void run_rank(const App& app, int rank) {
   for (int k = 0; k < 4; k++) EXPECT(mccsMalloc((void**)&multi[k], dev, (64 + 16 * (size_t)k) * sizeof(float)) == mccsSuccess);
   // Several lives of the communicator: creation and teardown race with the operator's
   // statistics and reconfiguration requests and with the other tenants' traffic.
-  for (int life = 0; life < 3; life++) {
+  // The last life takes the id of the one before it: ranks that are ahead of their peers ask
+  // for the id while the old communicator is still being let go of, and wait for it.
+  for (int life = 0; life < 4; life++) {
   mccsComm_t comm = nullptr;
-  EXPECT(mccsCommInitRank(&comm, app.comm_id + 100u * (uint32_t)life, rank, n, dev, nullptr) == mccsSuccess);
+  EXPECT(mccsCommInitRank(&comm, app.comm_id + 100u * (uint32_t)(life < 3 ? life : 2), rank, n, dev, nullptr) == mccsSuccess);
   if (!comm) return;
   for (int it = 0; it < app.iters; it++) {
     for (size_t i = 0; i < count; i++) send[i] = (float)(rank + 1) + (float)(i % 7) + (float)it;
