@@ -1,10 +1,11 @@
 // mccsd: the per-host service daemon.
-//   mccsd [--config mccs.toml] [--host <index>]
+//   mccsd [--config mccs.toml] [--host <index>] [--check]
 // Same command line as the reference binary (src/mccs/src/main.rs:16-24): the
 // configuration defaults to ./mccs.toml when that file exists; --host selects this
 // machine's entry of `addrs` and is only informational inside a single box. SIGINT
 // and SIGTERM end the control loop (main.rs:26-31,67-73); clients then see their
-// control connection close.
+// control connection close. --check reads the configuration, prints what it understood
+// and exits without starting anything (0 = the file is acceptable).
 #include <signal.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -22,11 +23,13 @@ static void on_signal(int) {
 int main(int argc, char** argv) {
   std::string config_path;
   int host = 0;
+  bool check_only = false;
   for (int i = 1; i < argc; i++) {
     if ((!strcmp(argv[i], "--config") || !strcmp(argv[i], "-c")) && i + 1 < argc) config_path = argv[++i];
     else if ((!strcmp(argv[i], "--host") || !strcmp(argv[i], "-h")) && i + 1 < argc) host = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--check")) check_only = true;
     else if (!strcmp(argv[i], "--help")) {
-      printf("usage: mccsd [--config mccs.toml] [--host <index>]\n");
+      printf("usage: mccsd [--config mccs.toml] [--host <index>] [--check]\n");
       return 0;
     } else {
       fprintf(stderr, "mccsd: unknown argument '%s'\n", argv[i]);
@@ -41,6 +44,14 @@ int main(int argc, char** argv) {
   } catch (const std::exception& e) {
     fprintf(stderr, "mccsd: %s\n", e.what());
     return 2;
+  }
+  if (check_only) {
+    printf("configuration ok: control %s/%s, admin port %d, %d ring channel(s), buffers of %llu bytes, transport %s, launch %s, "
+           "%zu tenant policies, %zu communicator overrides, %zu window schedules\n",
+           cfg.control_prefix.c_str(), cfg.control_path.c_str(), cfg.listen_port, cfg.channel_count,
+           (unsigned long long)cfg.buffer_sizes[0], cfg.transport.c_str(), cfg.launch.c_str(), cfg.qos_tenants.size(),
+           cfg.overrides.size(), cfg.qos_schedule.size());
+    return 0;
   }
   LOG_INFO("mccsd starting (host index %d)", host);
   mccs::Daemon daemon;

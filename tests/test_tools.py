@@ -220,3 +220,44 @@ def test_trace_colocation_tool_on_host_backend():
         assert set(jobs) == {"vgg", "gpt_1", "gpt_2"}
         for name, job in jobs.items():
             assert job["iterations"] == 22 and job["jct_ms"] is not None and job["mean_iter_ms"] > 0, (policy, name, job)
+
+
+def test_shipped_configurations_are_consistent():
+    """Every file under configs/: the daemon accepts its configurations (`mccsd --check`), a
+    malformed file is refused, every worker of a launch description names a program, a module
+    and files that exist, every trace names devices and well-formed steps."""
+    import glob
+    import importlib.util
+    import shlex
+    import tomllib
+    from helpers import NATIVE
+    mccsd = os.path.join(NATIVE, "mccsd")
+    for cfg in ("configs/mccs.toml", "configs/mccs_qos.toml"):
+        res = subprocess.run([mccsd, "--config", os.path.join(REPO, cfg), "--check"], capture_output=True, text=True, timeout=60)
+        assert res.returncode == 0 and "configuration ok" in res.stdout, res.stdout + res.stderr
+    assert "2 tenant policies" in res.stdout
+    bad = subprocess.run([mccsd, "--config", os.path.join(REPO, "Makefile"), "--check"], capture_output=True, text=True, timeout=60)
+    assert bad.returncode == 2
+    launches = [f for f in glob.glob(os.path.join(REPO, "configs/launch/*.toml")) if "worker" in tomllib.load(open(f, "rb"))]
+    assert len(launches) >= 3
+    for path in launches:
+        spec = tomllib.load(open(path, "rb"))
+        workers = spec["worker"]
+        for i, w in enumerate(workers):
+            assert w["bin"] == "python" or os.path.exists(os.path.join(NATIVE, "mccsd" if w["bin"] in ("mccs", "mccsd") else w["bin"])), (path, w["bin"])
+            assert all(0 <= d < len(workers) and d != i for d in w.get("dependencies", [])), (path, i)
+            words = shlex.split(w.get("args", ""))
+            for k, word in enumerate(words):
+                if word.startswith("configs/"):
+                    assert os.path.exists(os.path.join(REPO, word)), (path, word)
+                if word == "-m" and k + 1 < len(words):
+                    assert importlib.util.find_spec(words[k + 1]) is not None, (path, words[k + 1])
+    traces = glob.glob(os.path.join(REPO, "configs/workloads/*.toml"))
+    assert len(traces) >= 4
+    for path in traces:
+        t = tomllib.load(open(path, "rb"))
+        assert isinstance(t["communicator_id"], int) and len(t["cuda_devices"]) >= 1, path
+        for step in t["traces"]:
+            assert step["size"] > 0 and step["type"] in ("all_reduce", "all_gather", "reduce_scatter") and step["compute_interval"] >= 0, (path, step)
+    patch = tomllib.load(open(os.path.join(REPO, "configs/launch/reconfig-patch.toml"), "rb"))
+    assert patch["comm_patterns_reconfig"][0]["channels"][0]["ring"]
