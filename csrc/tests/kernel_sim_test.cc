@@ -800,6 +800,14 @@ int main() {
   random_cases(777u, 60);
   sim::g_chaos = false;
   missing_peer_case();
+  // MCCS_SIM_SOAK=N: N more seeds of random shapes, every second one perturbed (a longer soak
+  // than the default run, for changes to the kernels).
+  if (const char* soak = getenv("MCCS_SIM_SOAK"))
+    for (int i = 0; i < atoi(soak); i++) {
+      sim::g_chaos = i % 2 == 1;
+      random_cases(1000u + (unsigned)i, 100);
+    }
+  sim::g_chaos = false;
   printf("kernel_sim_test: %d checks, %d failed\n", g_checks, g_failed);
   return g_failed ? 1 : 0;
 }
