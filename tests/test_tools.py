@@ -261,3 +261,35 @@ def test_shipped_configurations_are_consistent():
             assert step["size"] > 0 and step["type"] in ("all_reduce", "all_gather", "reduce_scatter") and step["compute_interval"] >= 0, (path, step)
     patch = tomllib.load(open(os.path.join(REPO, "configs/launch/reconfig-patch.toml"), "rb"))
     assert patch["comm_patterns_reconfig"][0]["channels"][0]["ring"]
+
+
+def test_clock_sampler_reads_clocks_and_throttle_reasons(tmp_path, monkeypatch):
+    """The sampler that runs beside every timed region, against a stand-in `nvidia-smi`:
+    median and maximum clocks, peak power, and the throttle reasons that were active."""
+    import stat
+    import time
+    from mccs_b200.utils.timing import ClockSampler, bus_factor
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/sh\n"
+                    "echo '0, 1965, 1965, 250.1, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active'\n"
+                    "echo '0, 1800, 1965, 990.5, 0x0000000000000004, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '0, 1700, 1965, 1001.0, 0x0000000000000004, Not Active, Active, Not Active, Active'\n"
+                    "echo 'garbage line'\n"
+                    "sleep 30\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(tmp_path) + os.pathsep + os.environ["PATH"])
+    s = ClockSampler(gpu_index=0)
+    s.start()
+    for _ in range(100):
+        if len(s.lines) >= 4:
+            break
+        time.sleep(0.05)
+    out = s.stop()
+    assert out["samples"] == 3 and out["sm_mhz"] == 1800 and out["sm_max_mhz"] == 1965 and out["power_w_max"] == 1001.0
+    assert out["reasons"] == ["hw_thermal_slowdown", "sw_power_cap"]
+    assert bus_factor("allreduce", 8) == 1.75 and bus_factor("allgather", 8) == 0.875 and bus_factor("allreduce", 1) == 1.0
+    # no nvidia-smi at all: an empty record, not an error
+    monkeypatch.setenv("PATH", str(tmp_path / "nowhere"))
+    s2 = ClockSampler()
+    s2.start()
+    assert s2.stop()["samples"] == 0
