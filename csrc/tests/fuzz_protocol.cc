@@ -285,6 +285,7 @@ int main(int argc, char** argv) {
                           "[b200]\nforce_host_backend = true\nhost_devices = 2\nwait_timeout_ms = 2000\ninit_timeout_ms = 300\n" +
                           std::string(client_mode ? "launch = \"client\"\nclient_nvls = true\n" : "");
   setenv("MCCS_LOG", "error", 0);
+  if (getenv("FUZZ_SEED")) rng.seed(strtoull(getenv("FUZZ_SEED"), nullptr, 0));   // another run of the same length, other contents
   signal(SIGALRM, on_alarm);
   alarm(getenv("FUZZ_ALARM") ? (unsigned)atoi(getenv("FUZZ_ALARM")) : 600u);
   if (mccsd_start(cfg.c_str()) != 0) { fprintf(stderr, "daemon did not start\n"); return 2; }
