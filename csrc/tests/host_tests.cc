@@ -492,70 +492,102 @@ static void test_qos() {
   }
 }
 
-// Forty tenants on one GPU, asked for by eight threads the way the proxies do it: a request
-// that was told to wait asks again only when the arbiter's generation moved or a short time
-// went by. Everybody is served, shares follow the weights, and the arbiter's lock is not
-// hammered: the number of questions stays within a small multiple of the admissions.
+// Forty tenants on one GPU, asked for the way the proxies do it: a request that was told to
+// wait asks again only when the arbiter's generation moved or a short time went by. First on a
+// simulated clock, in one thread (the figures are then exact: everybody is served, shares
+// follow the weights, the number of questions stays within a small multiple of the
+// admissions), then by eight threads on the real clock for the locking (shares then depend on
+// how the machine schedules the threads and are not asked for).
 static void test_qos_many_tenants() {
   constexpr int kTenants = 40, kThreads = 8, kPerThread = kTenants / kThreads;
   Config cfg;
   for (int t = 0; t < kTenants; t++) cfg.qos_tenants[(uint32_t)(100 + t)].weight = (double)(1 << (t % 3));   // 1, 2, 4
   cfg.qos_max_outstanding_bytes = 8u << 20;
+  const uint64_t sz = 1 << 20;
+  struct Asker { uint32_t id; bool deferred = false; uint64_t gen = 0, retry_us = 0; int inflight = 0; uint64_t bytes = 0; };
+  auto ask = [&](QosArbiter& q, Asker& m, uint64_t now, uint64_t* asks, uint64_t* admissions) {
+    if (m.inflight) {               // the "kernel" of the previous admission is through
+      q.complete(m.id, sz);
+      m.inflight = 0;
+    }
+    if (m.deferred && q.generation() == m.gen && now < m.retry_us) return;
+    m.gen = q.generation();
+    q.note_waiting(m.id, now);
+    (*asks)++;
+    if (q.admit(m.id, sz, now, 0, 4) == kQosAdmit) {
+      m.deferred = false;
+      m.inflight = 1;
+      m.bytes += sz;
+      (*admissions)++;
+    } else {
+      m.deferred = true;
+      m.retry_us = now + 200;
+    }
+  };
+  {
+    QosArbiter q;
+    q.configure(cfg);
+    std::vector<Asker> all((size_t)kTenants);
+    for (int t = 0; t < kTenants; t++) { all[(size_t)t].id = (uint32_t)(100 + t); q.tenant_register(all[(size_t)t].id, {0}); }
+    // One round = what concurrent proxies do in one stretch of time: the transfers admitted
+    // in the round before complete, every tenant has its next request waiting, and the
+    // requests are put to the arbiter one after the other (starting with another tenant each
+    // round).
+    uint64_t asks = 0, admissions = 0, now = 1000;
+    for (int round = 0; round < 20000; round++) {
+      now += 10;
+      for (Asker& m : all)
+        if (m.inflight) { q.complete(m.id, sz); m.inflight = 0; }
+      for (Asker& m : all) q.note_waiting(m.id, now);
+      for (int k = 0; k < kTenants; k++) ask(q, all[(size_t)((round + k) % kTenants)], now, &asks, &admissions);
+    }
+    double by_weight[3] = {0, 0, 0};
+    bool all_served = true;
+    for (int t = 0; t < kTenants; t++) {
+      all_served &= all[(size_t)t].bytes > 0;
+      by_weight[t % 3] += (double)all[(size_t)t].bytes;
+    }
+    // classes 0, 1, 2 hold 14, 13 and 13 tenants of weight 1, 2 and 4
+    const double per1 = by_weight[0] / 14, per2 = by_weight[1] / 13, per4 = by_weight[2] / 13;
+    CHECK(all_served && admissions > 2000);
+    CHECK(per2 / per1 > 1.8 && per2 / per1 < 2.2);
+    CHECK(per4 / per1 > 3.6 && per4 / per1 < 4.4);
+    CHECK(asks < 40 * admissions);
+    if (getenv("MCCS_TEST_VERBOSE"))
+      printf("qos, 40 tenants, simulated clock: %llu admissions, %llu questions, shares 1 : %.2f : %.2f\n",
+             (unsigned long long)admissions, (unsigned long long)asks, per2 / per1, per4 / per1);
+  }
   QosArbiter q;
   q.configure(cfg);
   for (int t = 0; t < kTenants; t++) q.tenant_register((uint32_t)(100 + t), {0});
   std::atomic<uint64_t> asks{0}, admissions{0};
   std::vector<uint64_t> bytes((size_t)kTenants, 0);
-  const uint64_t sz = 1 << 20;
-  const uint64_t t_end = monotonic_us() + 1500000;
+  const uint64_t t_end = monotonic_us() + 500000;
   std::vector<std::thread> threads;
   for (int w = 0; w < kThreads; w++)
     threads.emplace_back([&, w]() {
-      struct Mine { uint32_t id; bool deferred = false; uint64_t gen = 0, retry_us = 0; int inflight = 0; };
-      Mine mine[kPerThread];
+      Asker mine[kPerThread];
       for (int k = 0; k < kPerThread; k++) mine[k].id = (uint32_t)(100 + w * kPerThread + k);
-      while (monotonic_us() < t_end) {
-        for (Mine& m : mine) {
-          const uint64_t now = monotonic_us();
-          if (m.inflight) {               // the "kernel" of the previous admission is through
-            q.complete(m.id, sz);
-            m.inflight = 0;
-          }
-          if (m.deferred && q.generation() == m.gen && now < m.retry_us) continue;
-          m.gen = q.generation();
-          q.note_waiting(m.id, now);
-          asks.fetch_add(1, std::memory_order_relaxed);
-          if (q.admit(m.id, sz, now, 0, 4) == kQosAdmit) {
-            m.deferred = false;
-            m.inflight = 1;
-            bytes[(size_t)(m.id - 100)] += sz;
-            admissions.fetch_add(1, std::memory_order_relaxed);
-          } else {
-            m.deferred = true;
-            m.retry_us = now + 200;
-          }
-        }
-      }
-      for (Mine& m : mine)
+      uint64_t my_asks = 0, my_admissions = 0;
+      while (monotonic_us() < t_end)
+        for (Asker& m : mine) ask(q, m, monotonic_us(), &my_asks, &my_admissions);
+      for (Asker& m : mine) {
         if (m.inflight) q.complete(m.id, sz);
+        bytes[(size_t)(m.id - 100)] = m.bytes;
+      }
+      asks.fetch_add(my_asks);
+      admissions.fetch_add(my_admissions);
     });
   for (auto& t : threads) t.join();
-  double by_weight[3] = {0, 0, 0};
   bool all_served = true;
-  for (int t = 0; t < kTenants; t++) {
-    all_served &= bytes[(size_t)t] > 0;
-    by_weight[t % 3] += (double)bytes[(size_t)t];
-  }
+  for (int t = 0; t < kTenants; t++) all_served &= bytes[(size_t)t] > 0;
   CHECK(all_served);
-  CHECK(admissions.load() > 2000);
-  // classes 0, 1, 2 hold 14, 13 and 13 tenants of weight 1, 2 and 4
-  const double per1 = by_weight[0] / 14, per2 = by_weight[1] / 13, per4 = by_weight[2] / 13;
-  CHECK(per2 / per1 > 1.5 && per2 / per1 < 2.6);
-  CHECK(per4 / per1 > 3.0 && per4 / per1 < 5.2);
-  CHECK(asks.load() < 40 * admissions.load());
+  CHECK(admissions.load() >= (uint64_t)kTenants && asks.load() >= admissions.load());
+  Value st = q.stats();
+  CHECK(st["tenants"]["100"]["outstanding_bytes"].as_int() == 0 && st["tenants"]["139"]["outstanding_bytes"].as_int() == 0);
   if (getenv("MCCS_TEST_VERBOSE"))
-    printf("qos, 40 tenants: %llu admissions, %llu questions, shares 1 : %.2f : %.2f\n", (unsigned long long)admissions.load(),
-           (unsigned long long)asks.load(), per2 / per1, per4 / per1);
+    printf("qos, 40 tenants, 8 threads: %llu admissions, %llu questions\n", (unsigned long long)admissions.load(),
+           (unsigned long long)asks.load());
 }
 
 static void test_misc() {
