@@ -226,7 +226,7 @@ def private_daemon():
     from mccs_b200 import daemon
     d = tempfile.mkdtemp(prefix="mccs-ft-")
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=-1,
-                       force_host=True, extra="init_timeout_ms = 1500")
+                       force_host=True, extra="init_timeout_ms = 6000")   # well above the start-up skew of two client processes on a busy machine
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
     yield sp
     sp.stop()
