@@ -130,6 +130,14 @@ def _stream_handle(stream) -> Optional[int]:
     return int(stream.cuda_stream)
 
 
+def _refuse_capture() -> None:
+    """A collective takes its barrier epoch and its ticket from the daemon at the call: a CUDA
+    graph that captured one would replay stale values. Refused here, loudly, instead of giving
+    wrong results at replay."""
+    if torch.cuda.is_current_stream_capturing():
+        raise _lib.MccsError(-9, "a collective inside CUDA graph capture")
+
+
 class Communicator:
     """One rank of a communicator (``init_communicator_rank`` in the reference)."""
 
@@ -146,6 +154,8 @@ class Communicator:
         return int(_lib.shim().mccsCommHandle(self._h))
 
     def _stream(self, stream) -> Optional[int]:
+        if self._is_cuda:
+            _refuse_capture()
         if stream is not None:
             return _stream_handle(stream)
         if self._is_cuda:

@@ -301,3 +301,26 @@ def test_an_id_can_be_taken_again_while_peers_still_let_go(service):
     outs = run_ranks(2, rank_fn)
     assert [o[0] for o in outs] == [3.0, 3.0] and [o[1] for o in outs] == [7.0, 7.0]
     assert outs[0][2] == -1 and outs[0][3] < 1.0
+
+
+def test_collectives_refuse_cuda_graph_capture(service, monkeypatch):
+    """Every collective asks the daemon for its barrier epoch and ticket when it is called, so
+    one that was captured into a CUDA graph would replay stale values: the call is refused
+    (checked here with a stand-in for torch's capture query; the check itself only runs for
+    CUDA communicators)."""
+    from mccs_b200 import client
+    M = service
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: True)
+    with pytest.raises(M.MccsError if hasattr(M, "MccsError") else RuntimeError) as e:
+        client._refuse_capture()
+    assert getattr(e.value, "code", None) == -9
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
+    client._refuse_capture()          # not capturing: nothing happens
+    # a host communicator never asks
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: True)
+    if M.backend() == "host":
+        cid = fresh_comm_id()
+        buf = M.Buffer(64, 0)
+        c = M.Communicator(cid, 0, 1, device=0)
+        c.all_reduce(buf.tensor(torch.float32, 16))
+        c.destroy()
