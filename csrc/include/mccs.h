@@ -2,24 +2,29 @@
  *
  * An application links against (or dlopens) libmccs.so and talks to the per-host
  * daemon `mccsd`. The daemon owns the GPUs' communication: it allocates the device
- * buffers (the application maps them), keeps the communicators, and launches the
- * collective kernels on its own streams. A collective call is stream ordered like a
- * kernel launch: it returns once the work is queued and the caller's stream will not
- * run anything issued later until the collective has finished. Two mechanisms, chosen
- * by the daemon ([b200] sync in its configuration):
- *   - stream memory operations (default on GPUs that support them): the library
- *     queues "write submitted" and "wait done" on the caller's stream, on two 64-bit
- *     semaphores in a pinned host page it shares with the daemon, and returns at
- *     once; the daemon polls "submitted" and launches when every rank got there;
- *     errors of a request show up on a later call or in mccsCommFlush. One stream may
- *     carry only one rank of a given communicator.
- *   - interprocess events (the reference's scheme): the library records "submitted",
- *     waits for the daemon's completion message, then makes the stream wait for the
- *     daemon's "done" event; the call blocks for one round trip and reports errors.
- * A third arrangement, [b200] launch = "client", keeps planning, admission and
- * reconfiguration in the daemon but has this library launch the planned kernel on the
- * caller's stream itself (it maps the peers' buffers for that); a call then blocks until
- * every rank has made the same call and the plan is back, like a rendezvous.
+ * buffers (the application maps them), keeps the communicators, plans and admits every
+ * collective (variant, launch shape, ring order, tenant arbitration) and can change
+ * all of that while applications run. A collective call is stream ordered like a
+ * kernel launch: the caller's stream will not run anything issued later until the
+ * collective has finished. Who launches the kernel is the daemon's choice
+ * ([b200] launch in its configuration):
+ *   - this library (the default on GPUs for communicators whose ranks are separate
+ *     processes on separate GPUs): it maps the peers' buffers, signal pads and
+ *     multicast objects and launches its rank's kernel on the caller's stream from the
+ *     plan the daemon made; a call blocks until every rank has made the same call and
+ *     the plan is back, like a rendezvous;
+ *   - the daemon, on its own streams (ranks that share a GPU, clients inside the
+ *     daemon's process, the host-staged transport, the host backend), ordered against
+ *     the caller's stream in one of two ways ([b200] sync):
+ *       stream memory operations (default on GPUs that support them): the library
+ *       queues "write submitted" and "wait done" on the caller's stream, on two 64-bit
+ *       semaphores in a pinned host page it shares with the daemon, and returns at
+ *       once; the daemon polls "submitted" and launches when every rank got there;
+ *       errors of a request show up on a later call or in mccsCommFlush. One stream may
+ *       carry only one rank of a given communicator;
+ *       interprocess events (the reference's scheme): the library records "submitted",
+ *       waits for the daemon's completion message, then makes the stream wait for the
+ *       daemon's "done" event; the call blocks for one round trip and reports errors.
  * In every arrangement each call involves the daemon, so collectives cannot be recorded
  * into a CUDA graph and replayed; keep them outside stream capture.
  *
