@@ -18,7 +18,7 @@ Options::Options(int argc, char** argv, const std::vector<std::string>& flags) {
     std::string key = a.substr(2);
     size_t eq = key.find('=');
     if (eq != std::string::npos) { kv_[key.substr(0, eq)] = key.substr(eq + 1); continue; }
-    if (std::find(flags.begin(), flags.end(), key) != flags.end()) { kv_[key] = "1"; continue; }
+    if (key == "help" || std::find(flags.begin(), flags.end(), key) != flags.end()) { kv_[key] = "1"; continue; }
     if (i + 1 >= argc) { fprintf(stderr, "option --%s needs a value\n", key.c_str()); exit(2); }
     kv_[key] = argv[++i];
   }
@@ -36,6 +36,7 @@ double Options::real(const std::string& key, double dflt) const {
   return it == kv_.end() ? dflt : strtod(it->second.c_str(), nullptr);
 }
 void Options::require(const std::vector<std::string>& keys, const char* usage) const {
+  if (has("help")) { printf("%s\n", usage); exit(0); }
   for (const auto& k : keys)
     if (!has(k)) { fprintf(stderr, "missing --%s\n%s\n", k.c_str(), usage); exit(2); }
 }

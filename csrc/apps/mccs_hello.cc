@@ -8,6 +8,7 @@
 
 int main(int argc, char** argv) {
   app::Options o(argc, argv);
+  o.require({}, "usage: mccs_hello [--cuda-device-idx 0]");
   const int dev = (int)o.num("cuda-device-idx", 0);
   app::check(mccsInit(nullptr), "mccsInit");
   printf("backend: %s, %d device(s)\n", mccsBackendKind() == 1 ? "cuda" : "host", mccsDeviceCount());

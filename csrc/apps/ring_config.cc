@@ -17,6 +17,7 @@
 
 int main(int argc, char** argv) {
   app::Options o(argc, argv, {"stats", "hwinfo"});
+  o.require({}, "usage: ring_config --config patch.toml [--port P] [--addr A] | --stats | --hwinfo");
   std::vector<std::string> addrs;
   int port = (int)o.num("port", 5000);
   mccs::Value body = mccs::Value::object();

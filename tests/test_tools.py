@@ -293,3 +293,21 @@ def test_clock_sampler_reads_clocks_and_throttle_reasons(tmp_path, monkeypatch):
     s2 = ClockSampler()
     s2.start()
     assert s2.stop()["samples"] == 0
+
+
+def test_every_tool_starts_and_describes_itself():
+    """`--help` of every command-line tool of the package, of the training driver and of the
+    benchmark script: imports resolve and the argument parsers build."""
+    env = dict(os.environ, PYTHONPATH=REPO)
+    mods = ["mccs_b200.utils." + m for m in ("sweep", "report", "multi_tenant", "qos_intervals", "latency", "profile_case",
+                                             "launcher", "colocate_traces", "colocate_train")] + ["mccs_b200.parallel.train"]
+    procs = [subprocess.Popen([sys.executable, "-m", m, "--help"], cwd=REPO, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+             for m in mods]
+    procs.append(subprocess.Popen([sys.executable, "bench.py", "--help"], cwd=REPO, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    for name, p in zip(mods + ["bench.py"], procs):
+        out, err = p.communicate(timeout=300)
+        assert p.returncode == 0 and "usage" in out.lower(), (name, err[-1000:])
+    from helpers import NATIVE
+    for app in ("mccsd", "allreduce_bench", "allgather_bench", "traffic_gen", "ring_config", "mccs_hello"):
+        res = subprocess.run([os.path.join(NATIVE, app), "--help"], capture_output=True, text=True, timeout=60)
+        assert "usage" in (res.stdout + res.stderr).lower(), (app, res.stdout + res.stderr)
