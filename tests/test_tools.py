@@ -300,7 +300,7 @@ def test_every_tool_starts_and_describes_itself():
     benchmark script: imports resolve and the argument parsers build."""
     env = dict(os.environ, PYTHONPATH=REPO)
     mods = ["mccs_b200.utils." + m for m in ("sweep", "report", "multi_tenant", "qos_intervals", "latency", "profile_case",
-                                             "launcher", "colocate_traces", "colocate_train")] + ["mccs_b200.parallel.train"]
+                                             "launcher", "colocate_traces", "colocate_train", "metrics")] + ["mccs_b200.parallel.train"]
     procs = [subprocess.Popen([sys.executable, "-m", m, "--help"], cwd=REPO, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
              for m in mods]
     procs.append(subprocess.Popen([sys.executable, "bench.py", "--help"], cwd=REPO, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
@@ -311,3 +311,50 @@ def test_every_tool_starts_and_describes_itself():
     for app in ("mccsd", "allreduce_bench", "allgather_bench", "traffic_gen", "ring_config", "mccs_hello"):
         res = subprocess.run([os.path.join(NATIVE, app), "--help"], capture_output=True, text=True, timeout=60)
         assert "usage" in (res.stdout + res.stderr).lower(), (app, res.stdout + res.stderr)
+
+
+def test_metrics_exporter_serves_the_daemons_counters(service):
+    """`mccs_b200.utils.metrics`: the statistics of a live daemon as Prometheus text, through
+    the render function and through the HTTP endpoint a scraper would ask."""
+    import threading
+    import urllib.request
+    import torch
+    from helpers import fresh_comm_id, run_ranks
+    from mccs_b200.utils import metrics
+    M = service
+    if M.backend() != "host":
+        pytest.skip("host-backend test")
+    cid = fresh_comm_id()
+
+    def rank_fn(r):
+        buf = M.Buffer(4096, r)
+        c = M.Communicator(cid, r, 2, device=r)
+        for _ in range(3):
+            c.all_reduce(buf.tensor(torch.float32, 256))
+        c.flush()
+        text = metrics.scrape(M.daemon.embedded_admin_port()) if r == 0 else ""
+        import time
+        time.sleep(0.2)          # rank 1 keeps the communicator alive while rank 0 reads
+        c.destroy()
+        return text
+
+    text = run_ranks(2, rank_fn)[0]
+    assert f'mccs_comm_planned_total{{comm="{cid}"}} 3' in text
+    assert f'mccs_tenant_admitted_total{{comm="{cid}"}} 3' in text
+    assert f'mccs_tenant_deferred_total{{comm="{cid}",reason="window"}} 0' in text
+    assert f'mccs_comm_info{{comm="{cid}",variant="' in text and "# TYPE mccs_comm_completed_total counter" in text
+    for line in text.splitlines():        # every sample line is `name{labels} number`
+        if line and not line.startswith("#"):
+            float(line.rsplit(" ", 1)[1])
+    srv = metrics.serve(M.daemon.embedded_admin_port(), 0)
+    t = threading.Thread(target=srv.serve_forever, daemon=True)
+    t.start()
+    try:
+        port = srv.server_address[1]
+        body = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10).read().decode()
+        assert "mccs_clients " in body and "mccs_allocated_bytes " in body
+        with pytest.raises(Exception):
+            urllib.request.urlopen(f"http://127.0.0.1:{port}/other", timeout=10)
+    finally:
+        srv.shutdown()
+        srv.server_close()
