@@ -27,8 +27,9 @@ from typing import List, Optional
 
 import torch
 import torch.distributed as dist
-from torch._C._distributed_c10d import (AllgatherOptions, AllreduceOptions, BarrierOptions, BroadcastOptions,
-                                        ReduceOp, ReduceScatterOptions, _create_work_from_future)
+from torch._C._distributed_c10d import (AllgatherOptions, AllreduceOptions, AllToAllOptions, BarrierOptions, BroadcastOptions,
+                                        GatherOptions, ReduceOp, ReduceOptions, ReduceScatterOptions, ScatterOptions,
+                                        _create_work_from_future)
 from torch.futures import Future
 
 from . import _lib, client
@@ -48,6 +49,12 @@ def _op_name(op) -> str:
         if op == k:
             return v
     raise NotImplementedError(f"reduce op {op} is not supported by the mccs backend")
+
+
+def _allreduce_options(op) -> AllreduceOptions:
+    o = AllreduceOptions()
+    o.reduceOp = op
+    return o
 
 
 def _done(result) -> "dist.Work":
@@ -214,6 +221,66 @@ class ProcessGroupMCCS(dist.ProcessGroup):
     def _reduce_scatter_base(self, output_tensor, input_tensor, opts=ReduceScatterOptions()):
         self._reduce_scatter_flat(output_tensor, input_tensor.contiguous(), _op_name(opts.reduceOp))
         return _done(output_tensor)
+
+    # The rooted and the personalised collectives are composed from the service's three (the
+    # reference has AllReduce and AllGather only): every rank moves what the un-rooted
+    # collective moves, which is n times what a native gather / scatter / all-to-all would.
+    # They are here so that code written against torch.distributed runs; the hot paths of
+    # data-parallel training do not use them.
+    def reduce(self, tensors, opts=ReduceOptions()):
+        tensors = tensors if isinstance(tensors, (list, tuple)) else [tensors]
+        op = _op_name(opts.reduceOp)
+        for t in tensors:
+            if self._rank == opts.rootRank:
+                self.allreduce([t], _allreduce_options(opts.reduceOp))
+            else:
+                self._all_reduce_flat(t.contiguous().clone(), op)     # takes part; its own tensor stays as it is
+        return _done(list(tensors))
+
+    def gather(self, output_tensors, input_tensors, opts=GatherOptions()):
+        for i, inp in enumerate(input_tensors):
+            flat = torch.empty((self._size,) + tuple(inp.shape), dtype=inp.dtype, device=inp.device)
+            self._all_gather_flat(flat, inp.contiguous())
+            if self._rank == opts.rootRank:
+                for r, o in enumerate(output_tensors[i]):
+                    o.copy_(flat[r])
+        return _done(output_tensors)
+
+    def scatter(self, output_tensors, input_tensors, opts=ScatterOptions()):
+        for i, out in enumerate(output_tensors):
+            if self._rank == opts.rootRank:
+                full = torch.stack([t.contiguous() for t in input_tensors[i]])
+            else:
+                full = torch.empty((self._size,) + tuple(out.shape), dtype=out.dtype, device=out.device)
+            b = BroadcastOptions()
+            b.rootRank = opts.rootRank
+            self.broadcast([full], b)
+            out.copy_(full[self._rank])
+        return _done(output_tensors)
+
+    def alltoall_base(self, output, input, output_split_sizes, input_split_sizes, opts=AllToAllOptions()):
+        if output_split_sizes or input_split_sizes:
+            raise NotImplementedError("all_to_all_single with unequal splits is not supported by the mccs backend")
+        n = self._size
+        if input.numel() % n or output.numel() != input.numel():
+            raise ValueError("all_to_all_single needs equal splits: numel divisible by the group size, output as large as input")
+        k = input.numel() // n
+        everything = torch.empty((n, n, k), dtype=input.dtype, device=input.device)      # [source rank][destination][k]
+        self._all_gather_flat(everything, input.contiguous())
+        res = everything[:, self._rank, :].reshape(output.shape)
+        output.copy_(res)
+        return _done(output)
+
+    def alltoall(self, output_tensors, input_tensors, opts=AllToAllOptions()):
+        shapes = {tuple(t.shape) for t in list(output_tensors) + list(input_tensors)}
+        if len(shapes) != 1:
+            raise NotImplementedError("all_to_all with tensors of different shapes is not supported by the mccs backend")
+        inp = torch.stack([t.contiguous() for t in input_tensors]).reshape(-1)
+        out = torch.empty_like(inp)
+        self.alltoall_base(out, inp, [], [], opts)
+        for r, o in enumerate(output_tensors):
+            o.copy_(out.reshape((self._size,) + tuple(o.shape))[r])
+        return _done(output_tensors)
 
     def barrier(self, opts=BarrierOptions()):
         dev = f"cuda:{self._device}" if self._cuda else "cpu"

@@ -51,6 +51,20 @@ assert torch.equal(zo, (torch.arange(8 * n).float().reshape(n, 8)[rank]) * n + s
 z, keep = mpg.empty(1000, torch.float32, device=rank)
 z.fill_(rank + 1.0); assert mpg.in_service_memory(z)
 dist.all_reduce(z); assert torch.all(z == n * (n + 1) / 2)
+# rooted and personalised collectives, composed from the three the service has
+rd = torch.full((6,), float(rank + 1)); dist.reduce(rd, dst=1)
+assert torch.all(rd == (n * (n + 1) / 2 if rank == 1 else rank + 1)), rd
+gl = [torch.empty(3) for _ in range(n)] if rank == 0 else None
+dist.gather(torch.full((3,), float(rank * 10)), gl, dst=0)
+if rank == 0: assert all(torch.all(g == 10.0 * r) for r, g in enumerate(gl))
+so = torch.empty(4, dtype=torch.int64)
+dist.scatter(so, [torch.full((4,), 100 + r, dtype=torch.int64) for r in range(n)] if rank == 1 else None, src=1)
+assert torch.all(so == 100 + rank), so
+a2a = torch.empty(n * 2); dist.all_to_all_single(a2a, torch.arange(n * 2).float() + 100 * rank)
+assert torch.equal(a2a, torch.cat([torch.arange(2).float() + 2 * rank + 100 * r for r in range(n)])), a2a
+lo = [torch.empty(2, 2) for _ in range(n)]
+dist.all_to_all(lo, [torch.full((2, 2), float(10 * rank + q)) for q in range(n)])
+assert all(torch.all(o == 10.0 * r + rank) for r, o in enumerate(lo)), lo
 dist.barrier()
 # torch's own DistributedDataParallel on top of the backend
 torch.manual_seed(0)
