@@ -143,6 +143,44 @@ def _run_workers(code: str, n: int, control: str, extra_env=None):
 def test_process_group_two_processes(standalone_daemon):
     _run_workers(WORKER, 2, standalone_daemon.control)
 
+SUBGROUP_WORKER = r"""
+import os, torch, torch.distributed as dist
+import mccs_b200.process_group as mpg
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"])
+dist.init_process_group("mccs", init_method=f"tcp://127.0.0.1:{os.environ['PORT']}", rank=rank, world_size=n)
+sub = dist.new_group([0, 2])              # every rank calls new_group, members get a communicator of their own
+t = torch.full((5,), float(rank + 1))
+if rank in (0, 2):
+    dist.all_reduce(t, group=sub)
+    assert torch.all(t == 4.0), t
+dist.all_reduce(t)
+assert torch.all(t == 10.0), t
+sub2 = dist.new_group([1, 2])
+u = torch.full((3,), float(rank))
+if rank in (1, 2):
+    dist.broadcast(u, src=2, group=sub2)
+    assert torch.all(u == 2.0), u
+dist.barrier()
+print(f"rank {rank} ok", flush=True)
+mpg.shutdown()
+dist.destroy_process_group()
+"""
+
+
+def test_process_subgroups(tmp_path):
+    """`dist.new_group`: every subgroup is a communicator of its own in the daemon, next to the
+    world's; three processes, two overlapping pairs."""
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=-1, force_host=True)
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        outs = _run_workers(SUBGROUP_WORKER, 3, sp.control)
+        assert all(f"rank {r} ok" in o for r, (o, _) in enumerate(outs))
+    finally:
+        sp.stop()
+
+
 ZERO_WORKER = r"""
 import os, sys, torch
 import mccs_b200 as M
