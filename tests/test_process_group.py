@@ -181,6 +181,56 @@ def test_process_subgroups(tmp_path):
         sp.stop()
 
 
+FSDP_WORKER = r"""
+import os, torch, torch.distributed as dist
+import mccs_b200.process_group as mpg
+from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"])
+dist.init_process_group("mccs", init_method=f"tcp://127.0.0.1:{os.environ['PORT']}", rank=rank, world_size=n)
+torch.manual_seed(0)
+model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+ref = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+ref.load_state_dict(model.state_dict())
+f = FSDP(model, device_id=torch.device("cpu"))
+opt = torch.optim.SGD(f.parameters(), lr=0.1)
+x = torch.randn(8, 16, generator=torch.Generator().manual_seed(rank))
+f(x).sum().backward()
+opt.step()
+# reference: mean gradient over ranks, plain SGD
+ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
+tot = None
+for r in range(n):
+    ref.zero_grad()
+    ref(torch.randn(8, 16, generator=torch.Generator().manual_seed(r))).sum().backward()
+    g = [p.grad.clone() for p in ref.parameters()]
+    tot = g if tot is None else [a + b for a, b in zip(tot, g)]
+for p, g in zip(ref.parameters(), tot): p.grad = g / n
+ropt.step()
+with FSDP.summon_full_params(f):
+    got = [p.detach().clone() for p in f.parameters()]
+want = [p.detach() for p in ref.parameters()]
+ok = all(torch.allclose(a.reshape(-1), b.reshape(-1), atol=1e-5) for a, b in zip(got, want))
+assert ok
+print(f"rank {rank} ok", flush=True)
+dist.barrier(); mpg.shutdown(); dist.destroy_process_group()
+"""
+
+
+def test_torch_fsdp_over_the_backend(tmp_path):
+    """torch's FullyShardedDataParallel on the backend (all_gather_into_tensor for the
+    parameters, reduce_scatter_tensor for the gradients): one SGD step equals the step of a
+    plain replica with the mean gradient."""
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=2, listen_port=-1, force_host=True)
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        outs = _run_workers(FSDP_WORKER, 2, sp.control)
+        assert all(f"rank {r} ok" in o for r, (o, _) in enumerate(outs))
+    finally:
+        sp.stop()
+
+
 ZERO_WORKER = r"""
 import os, sys, torch
 import mccs_b200 as M
