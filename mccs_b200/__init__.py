@@ -9,8 +9,9 @@ package's object API (:mod:`mccs_b200.client`), a ``torch.distributed`` backend
 """
 from .client import (ALGOS, Buffer, Communicator, admin_request, backend, device_count, finalize, group, init,
                      reconfigure)
+from ._lib import MccsError
 from . import daemon
 
-__all__ = ["ALGOS", "Buffer", "Communicator", "admin_request", "backend", "device_count", "finalize", "group",
+__all__ = ["ALGOS", "Buffer", "Communicator", "MccsError", "admin_request", "backend", "device_count", "finalize", "group",
            "init", "reconfigure", "daemon"]
 __version__ = "0.1.0"

@@ -311,7 +311,7 @@ def test_collectives_refuse_cuda_graph_capture(service, monkeypatch):
     from mccs_b200 import client
     M = service
     monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: True)
-    with pytest.raises(M.MccsError if hasattr(M, "MccsError") else RuntimeError) as e:
+    with pytest.raises(M.MccsError) as e:
         client._refuse_capture()
     assert getattr(e.value, "code", None) == -9
     monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
