@@ -358,3 +358,18 @@ def test_metrics_exporter_serves_the_daemons_counters(service):
     finally:
         srv.shutdown()
         srv.server_close()
+
+
+def test_multi_tenant_tool_with_a_reference_placement():
+    """`--setting 2`: the placement of the reference's second multi-application experiment (a
+    four-GPU job across all host pairs next to two two-GPU jobs), on eight host devices."""
+    import json
+    res = subprocess.run([sys.executable, "-m", "mccs_b200.utils.multi_tenant", "--setting", "2", "--iters", "12", "--reconfig-at", "0",
+                          "--bytes", "65536", "--batch", "1", "--host-devices", "8", "--timeout", "200"],
+                         capture_output=True, text=True, cwd=REPO, env=dict(os.environ, PYTHONPATH=REPO, MCCS_LOG="error"), timeout=400)
+    assert res.returncode == 0, res.stderr[-3000:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["setting"] == 2 and set(out["apps"]) == {"blue", "green", "red"}
+    assert out["apps"]["blue"]["devices"] == [0, 4, 2, 6] and out["apps"]["green"]["devices"] == [1, 3]
+    for name, app in out["apps"].items():
+        assert app["finite"] and app["async_error"] == 0, (name, app)
