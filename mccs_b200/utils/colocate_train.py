@@ -62,6 +62,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--comm-ctas", type=int, default=0)
     ap.add_argument("--timeout", type=float, default=600.0)
+    ap.add_argument("--dry-run-model", default="", help="every job trains this model instead of its own, with a small batch "
+                    "(e.g. gpt2-tiny): a run of the tool itself, on a machine without GPUs too")
     a = ap.parse_args()
     jobs = [dict(j) for j in SCENARIOS[a.scenario]]
     import torch
@@ -87,6 +89,9 @@ def main() -> int:
                        "--model", j["model"], "--backend", a.backend, "--comm-id", str(j["comm_id"]),
                        "--devices", ",".join(map(str, j["devices"])), "--steps", str(max(int(j["steps"] * a.steps_scale), 2)),
                        "--warmup", str(a.warmup), "--name", j["name"], "--sync-dir", work + "/sync", "--sync-jobs", str(len(jobs))]
+                if a.dry_run_model:
+                    cmd[cmd.index("--model") + 1] = a.dry_run_model
+                    cmd += ["--batch", "2", "--seq", "32", "--bucket-mb", "0.05"]
                 if a.backend == "mccs":
                     cmd += ["--control", sp.control]
                     if a.comm_ctas > 0:

@@ -373,3 +373,20 @@ def test_multi_tenant_tool_with_a_reference_placement():
     assert out["apps"]["blue"]["devices"] == [0, 4, 2, 6] and out["apps"]["green"]["devices"] == [1, 3]
     for name, app in out["apps"].items():
         assert app["finite"] and app["async_error"] == 0, (name, app)
+
+
+def test_colocated_training_tool_dry_run():
+    """`colocate_train --scenario gpt-with-resnet` as a dry run on the host backend: an
+    eight-rank job and a four-rank job that shares its devices, both tenants of one daemon
+    (weights and priority from the scenario), warm up apart, start their timed steps
+    together and report their rates."""
+    import json
+    res = subprocess.run([sys.executable, "-m", "mccs_b200.utils.colocate_train", "--scenario", "gpt-with-resnet", "--steps-scale", "0.1",
+                          "--warmup", "1", "--dry-run-model", "gpt2-tiny", "--timeout", "300"],
+                         capture_output=True, text=True, cwd=REPO, env=dict(os.environ, PYTHONPATH=REPO, MCCS_LOG="error"), timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    jobs = out["jobs"]
+    assert set(jobs) == {"gpt2-medium", "resnet50"} and jobs["gpt2-medium"]["n_gpus"] == 8 and jobs["resnet50"]["n_gpus"] == 4
+    for j in jobs.values():
+        assert "error" not in j and j["backend"] == "mccs" and j["ms_per_step"] > 0 and j["last_loss"] < j["first_loss"] + 0.5
