@@ -13,6 +13,7 @@ into the collective kernel (``SumPostDiv``), so no elementwise kernel follows it
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Iterable, List, Optional
 
 import torch
@@ -77,6 +78,7 @@ class DataParallel:
         if cur:
             self.buckets.append(_Bucket(cur, cur_dtype, self._device, self._cuda, self._bucket_multiple()))
         self._launched = 0
+        self._sync = True
         # Bucket reductions are issued from a side stream and only their sum total is
         # awaited, once, at the end of backward: no per-bucket wait is queued anywhere.
         self.comm.set_deferred_wait(True)
@@ -116,7 +118,7 @@ class DataParallel:
 
     def _reduce(self, bucket: _Bucket) -> None:
         self._launched += 1
-        if self.comm.nranks == 1:
+        if self.comm.nranks == 1 or not self._sync:
             return
         if self._cuda:
             # The side stream picks up after the gradients written so far.
@@ -134,9 +136,22 @@ class DataParallel:
                 # forward pass): reduce it now so that all ranks issue the same collectives.
                 self._reduce(b)
             b.pending = len(b.params)
-        if self.comm.nranks > 1:
+        if self.comm.nranks > 1 and self._sync:
             self.comm.wait()          # the compute stream waits for all bucket reductions of this step
         self._launched = 0
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Gradient accumulation, as torch DDP's ``no_sync``: backward passes inside the block
+        only add to the gradient buckets, nothing is reduced; the first backward after the
+        block reduces the accumulated sums. Call :meth:`finish` after every backward, inside
+        the block too (it then only re-arms the buckets), and :meth:`zero_grad` once per
+        optimizer step."""
+        self._sync = False
+        try:
+            yield self
+        finally:
+            self._sync = True
 
     def zero_grad(self) -> None:
         """Zero the gradient buckets (keeps ``.grad`` views in place)."""

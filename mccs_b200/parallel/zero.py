@@ -63,7 +63,7 @@ class ShardedDataParallel(DataParallel):
 
     def _reduce(self, bucket: _Bucket) -> None:
         self._launched += 1
-        if self.comm.nranks == 1:
+        if self.comm.nranks == 1 or not self._sync:
             return
         i = self.buckets.index(bucket)
         mine = self._part_of(bucket.flat, i)
@@ -99,12 +99,12 @@ class ShardedDataParallel(DataParallel):
         return sum(self._part)
 
     def release(self) -> None:
-        super().release()
         # hand the parameters back as ordinary tensors before the buckets go away
         with torch.no_grad():
             for b in self.buckets:
                 for p in b.params:
                     p.data = p.data.clone()
+        super().release()
         for buf in self._param_buffers:
             buf.free()
         self._param_buffers = []

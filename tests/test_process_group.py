@@ -181,6 +181,59 @@ def test_process_subgroups(tmp_path):
         sp.stop()
 
 
+ACCUM_WORKER = r"""
+import os, sys, torch
+import mccs_b200 as M
+from mccs_b200 import models
+from mccs_b200.parallel import DataParallel, ShardedDataParallel
+rank = int(os.environ["RANK"]); n = int(os.environ["WORLD_SIZE"])
+def batch(r, k):
+    return torch.randint(0, 512, (2, 17), generator=torch.Generator().manual_seed(100 * r + k))
+torch.manual_seed(0)
+m = models.build("gpt2-tiny")
+torch.manual_seed(0)
+ref = models.build("gpt2-tiny")
+comm = M.Communicator(79, rank, n, device=rank)
+ddp = DataParallel(m, comm, bucket_mb=0.05)
+ddp.zero_grad()
+at_start = comm.query()["launched"]       # the parameter broadcast of the constructor
+with ddp.no_sync():                       # first micro-batch: accumulate only
+    ids = batch(rank, 0); m(ids[:, :-1], ids[:, 1:]).backward(); ddp.finish()
+before = comm.query()["launched"]
+ids = batch(rank, 1); m(ids[:, :-1], ids[:, 1:]).backward(); ddp.finish()     # second: reduce the sums
+assert before == at_start and comm.query()["launched"] - before == len(ddp.buckets), (at_start, before, comm.query()["launched"])
+# reference: mean over ranks of the sum over micro-batches
+for r in range(n):
+    for k in range(2):
+        ids = batch(r, k); ref(ids[:, :-1], ids[:, 1:]).backward()
+worst = max(float((p.grad - q.grad / n).abs().max()) for p, q in zip(m.parameters(), ref.parameters()))
+assert worst < 1e-5, worst
+ddp.release(); comm.destroy()
+# the sharded form releases cleanly: parameters are ordinary tensors again and still usable
+comm = M.Communicator(80, rank, n, device=rank)
+z = ShardedDataParallel(m, comm, bucket_mb=0.05)
+z.release(); comm.destroy(); M.finalize()
+ids = batch(rank, 2); assert torch.isfinite(m(ids[:, :-1], ids[:, 1:]))
+print(f"rank {rank} ok", flush=True)
+"""
+
+
+def test_gradient_accumulation_and_release(tmp_path):
+    """`DataParallel.no_sync()`: micro-batches inside the block only accumulate, the next
+    backward reduces the sums (one AllReduce per bucket for the whole step) and the result is the
+    mean over ranks of the summed gradients. `ShardedDataParallel.release()` hands the parameters
+    back as ordinary tensors before their buckets are freed."""
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=2, listen_port=-1, force_host=True)
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "warn"})
+    try:
+        outs = _run_workers(ACCUM_WORKER, 2, sp.control)
+        assert all(f"rank {r} ok" in o for r, (o, _) in enumerate(outs))
+    finally:
+        sp.stop()
+
+
 FSDP_WORKER = r"""
 import os, torch, torch.distributed as dist
 import mccs_b200.process_group as mpg
