@@ -72,7 +72,7 @@ class _Arena:
         if self.buffer is None or self.buffer.nbytes < nbytes:
             if self.buffer is not None:
                 if backend() == "cuda":
-                    torch.cuda.current_stream(self.comm.device).synchronize()    # work that still uses the old buffer
+                    torch.cuda.synchronize(self.comm.device)    # work that still uses the old buffer, on whichever stream
                 self.buffer.free()
             self.buffer = Buffer(max(nbytes, 1 << 20) * 2, self.comm.device)
         return self.buffer
