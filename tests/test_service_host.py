@@ -254,6 +254,18 @@ def test_functional_ops_over_a_communicator(service):
         assert torch.allclose(rs, torch.arange(3 * n).float()[3 * r:3 * r + 3] + 1.0)    # mean of r over 3 ranks = 1
         x[:3 * n] = 3.0
         out = (y.clone(), x.clone(), g.clone())
+        # ordinary tensors are staged through the communicator's arena, which grows on demand
+        small = torch.full((1000,), float(r))
+        ops.all_reduce(c, small)
+        first_arena = ops.arena(c).buffer.nbytes
+        big = torch.full((700000,), float(r + 1))
+        ops.all_reduce(c, big, op="avg")
+        assert ops.arena(c).buffer.nbytes > first_arena
+        assert torch.all(small == 3.0) and torch.all(big == 2.0)
+        flags = torch.tensor([r == 0, True, False])               # an element type the kernels do not have: staged as fp32
+        ops.all_reduce(c, flags, op="max")
+        assert flags.tolist() == [True, True, False]
+        ops.arena(c).release()
         c.destroy()
         return out
 
