@@ -134,7 +134,11 @@ def _refuse_capture() -> None:
     """A collective takes its barrier epoch and its ticket from the daemon at the call: a CUDA
     graph that captured one would replay stale values. Refused here, loudly, instead of giving
     wrong results at replay."""
-    if torch.cuda.is_current_stream_capturing():
+    try:
+        capturing = torch.cuda.is_current_stream_capturing()
+    except Exception:      # no usable CUDA runtime in this process: nothing can be capturing
+        capturing = False
+    if capturing:
         raise _lib.MccsError(-9, "a collective inside CUDA graph capture")
 
 

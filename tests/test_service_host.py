@@ -328,6 +328,11 @@ def test_collectives_refuse_cuda_graph_capture(service, monkeypatch):
     assert getattr(e.value, "code", None) == -9
     monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
     client._refuse_capture()          # not capturing: nothing happens
+
+    def broken():
+        raise RuntimeError("no CUDA runtime")
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", broken)
+    client._refuse_capture()          # the query itself fails: treated as not capturing
     # a host communicator never asks
     monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: True)
     if M.backend() == "host":
