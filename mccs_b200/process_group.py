@@ -14,8 +14,10 @@ Tensors that live in service memory (allocated with :func:`empty` / :class:`Buff
 through :func:`mem_pool`) are used in place: the kernel reads and writes them directly.
 Other tensors are staged through a service buffer on the caller's stream (one copy in,
 one copy out). Collectives are stream ordered: when a call returns, the work is
-enqueued and the caller's current stream waits for it, so the returned ``Work`` is
-already complete in the sense PyTorch's stream semantics need.
+enqueued on the caller's current stream. The returned ``Work`` wraps a future that is
+completed at once and, for CUDA tensors, knows their devices: it carries an event recorded
+behind the collective, so ``work.wait()`` (or a callback chained to the future) on any
+stream waits for the collective the way it would for the ``nccl`` backend.
 """
 from __future__ import annotations
 
@@ -57,8 +59,31 @@ def _allreduce_options(op) -> AllreduceOptions:
     return o
 
 
+def _cuda_devices(result) -> list:
+    found = set()
+
+    def visit(x) -> None:
+        if isinstance(x, torch.Tensor):
+            if x.is_cuda:
+                found.add(x.device)
+        elif isinstance(x, (list, tuple)):
+            for y in x:
+                visit(y)
+
+    visit(result)
+    return sorted(found, key=lambda d: d.index or 0)
+
+
 def _done(result) -> "dist.Work":
-    fut: Future = Future()
+    """A finished ``Work`` for a collective that has been enqueued on the caller's current
+    stream. For CUDA results the future is told their devices: completing it then records an
+    event on those devices' current streams, and whoever waits for it (on any stream) waits
+    for that event, that is for the collective."""
+    devices = _cuda_devices(result)
+    try:
+        fut: Future = Future(devices=devices) if devices else Future()
+    except Exception:          # a torch build whose futures take no devices: stream order alone then
+        fut = Future()
     fut.set_result(result)
     return _create_work_from_future(fut)
 
