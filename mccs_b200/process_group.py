@@ -24,8 +24,7 @@ from __future__ import annotations
 import os
 import threading
 import weakref
-from ctypes import byref, c_uint64, c_void_p
-from typing import List, Optional
+from typing import Optional
 
 import torch
 import torch.distributed as dist
