@@ -538,7 +538,7 @@ def test_clients_killed_at_random_leave_the_daemon_clean(tmp_path, launch):
     from mccs_b200 import daemon
     d = str(tmp_path)
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), host_devices=4, listen_port=-1, force_host=True,
-                       wait_timeout_ms=3000, extra=f"init_timeout_ms = 3000\nfuse_allreduce = 4\nlaunch = \"{launch}\"")
+                       wait_timeout_ms=3000, extra=f"init_timeout_ms = 15000\nfuse_allreduce = 4\nlaunch = \"{launch}\"")
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "error"})
     rng = random.Random(11)
     try:
