@@ -39,7 +39,7 @@ dependencies = []
 bin = "python"
 args = "-c \\"open(r'{marker}', 'a').write('job1\\\\n'); print('hello from job1')\\""
 dependencies = [0]
-delay = 0.3
+delay = 4.0
 [[worker]]
 bin = "python"
 args = "-c \\"open(r'{marker}', 'a').write('job2\\\\n')\\""
