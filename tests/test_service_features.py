@@ -627,3 +627,65 @@ def test_transport_is_chosen_per_connection(tmp_path):
                     assert res["asked"] == "ar_twoshot" and "ring" not in res["ar"] and "ring" not in res["ag"]
     finally:
         sp.stop()
+
+
+@pytest.mark.parametrize("launch", ["daemon", "client"])
+def test_daemon_holds_nothing_after_many_client_lifetimes(tmp_path, launch):
+    """A service runs for months: after hundreds of client lifetimes (connect, allocate, create a
+    communicator, run, destroy, leave; some of them killed in the middle of their traffic) the
+    daemon has as many open descriptors and memory mappings as before, and no more memory."""
+    import signal
+    import time
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, host_devices=2, force_host=True,
+                       extra=f'launch = "{launch}"')     # client: pads, status blocks and peers' buffers are handed out as descriptors too
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "error"})
+    pid = sp.proc.pid
+
+    def snapshot():
+        fds = len(os.listdir(f"/proc/{pid}/fd"))
+        rss = int([l for l in open(f"/proc/{pid}/status") if l.startswith("VmRSS")][0].split()[1])
+        maps = sum(1 for _ in open(f"/proc/{pid}/maps"))
+        return fds, rss, maps
+
+    env = dict(os.environ, MCCS_CONTROL=sp.control, MCCS_LOG="error")
+
+    def polite(k):
+        ps = [subprocess.Popen([os.path.join(NATIVE, "allreduce_proto"), "--rank", str(r), "--num-ranks", "2", "--cuda-device-idx", str(r),
+                                "--communicator", str(4000 + k % 7), "--size", "65536"], env=env, stdout=subprocess.DEVNULL,
+                               stderr=subprocess.DEVNULL) for r in range(2)]
+        return [p.wait(timeout=60) for p in ps]
+
+    def killed(k):
+        trace = os.path.join(d, "t.toml")
+        with open(trace, "w") as f:
+            f.write('communicator_id = 4100\ncuda_devices = [0, 1]\n[[traces]]\nsize = 262144\ntype = "all_reduce"\ncompute_interval = 50\n')
+        ps = [subprocess.Popen([os.path.join(NATIVE, "traffic_gen"), "--rank", str(r), "--config", trace, "--iters", "1000000"], env=env,
+                               stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL) for r in range(2)]
+        time.sleep(0.15)
+        ps[k % 2].send_signal(signal.SIGKILL)      # no goodbye; its peer ends with an error
+        for p in ps:
+            p.wait(timeout=60)
+
+    try:
+        for k in range(10):
+            assert polite(k) == [0, 0]
+        killed(0)
+        time.sleep(0.5)
+        before = snapshot()
+        for k in range(120):
+            assert polite(k) == [0, 0]
+        for k in range(12):
+            killed(k)
+        deadline = time.time() + 10
+        while time.time() < deadline:
+            after = snapshot()
+            if after[0] == before[0] and after[2] == before[2]:
+                break
+            time.sleep(0.2)
+        assert after[0] == before[0] and after[2] == before[2], (before, after)
+        assert after[1] <= before[1] + 2048, (before, after)          # kB
+        assert sp.proc.poll() is None
+    finally:
+        sp.stop()
