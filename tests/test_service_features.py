@@ -689,3 +689,53 @@ def test_daemon_holds_nothing_after_many_client_lifetimes(tmp_path, launch):
         assert sp.proc.poll() is None
     finally:
         sp.stop()
+
+
+LIFETIMES_CLIENT = r"""
+import os, torch, gc
+import mccs_b200 as M
+rank = int(os.environ["RANK"]); n = 2
+def snap():
+    return len(os.listdir("/proc/self/fd")), sum(1 for _ in open("/proc/self/maps")), int([l for l in open("/proc/self/status") if l.startswith("VmRSS")][0].split()[1])
+def life(k):
+    buf = M.Buffer(1 << 16, rank); t = buf.tensor(torch.float32, 4096); t.fill_(1.0)
+    c = M.Communicator(5000 + k, rank, n, device=rank)
+    for _ in range(3): c.all_reduce(t)
+    with M.group():
+        c.all_reduce(t); c.all_reduce(t)
+    g = M.Buffer(1 << 12, rank)
+    c.all_gather(g.tensor(torch.uint8, 1024)[:512] if False else g.tensor(torch.uint8, 2048)[rank * 1024:(rank + 1) * 1024], g.tensor(torch.uint8, 2048))
+    c.destroy(); del t; buf.free(); g.free()
+for k in range(20): life(k)
+gc.collect(); a = snap()
+for k in range(20, 170): life(k)
+gc.collect(); b = snap()
+import json; print("RESULT", json.dumps({"before": a, "after": b}), flush=True)
+M.finalize()
+"""
+
+
+@pytest.mark.parametrize("launch", ["daemon", "client"])
+def test_client_library_holds_nothing_after_many_communicator_lifetimes(tmp_path, launch):
+    """The other side of the same question: a long-lived application that creates and destroys
+    communicators and buffers (150 times here, with collectives and groups in between) ends
+    with the descriptors and mappings it started with; with client launches that includes
+    the peers' buffers, pads and status blocks mapped per communicator."""
+    import json
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, host_devices=2, force_host=True,
+                       extra=f'launch = "{launch}"')
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "error"})
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, MCCS_LOG="error", LAUNCH=launch)
+        procs = [subprocess.Popen([sys.executable, "-c", LIFETIMES_CLIENT], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                                  stderr=subprocess.PIPE, text=True) for r in range(2)]
+        for p in procs:
+            out, err = p.communicate(timeout=300)
+            assert p.returncode == 0, err[-3000:]
+            res = json.loads([l for l in out.splitlines() if l.startswith("RESULT ")][0][7:])
+            assert res["after"][0] == res["before"][0] and res["after"][1] <= res["before"][1] + 2, res     # descriptors, mappings
+            assert res["after"][2] <= res["before"][2] + 8192, res                                         # resident kB
+    finally:
+        sp.stop()
