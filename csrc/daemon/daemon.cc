@@ -550,7 +550,11 @@ void Daemon::on_comm_init(Session& s, const proto::CommInitReq& m) {
       bool closing = false;
       if (c.state.load() != kCommInit)
         for (auto& r : c.ranks) closing |= r && r->gone.load();
-      if (closing) {
+      // (A client waits for the answer before it asks again; one that does not is not given
+      // an unbounded list.)
+      size_t mine = 0;
+      for (const ParkedInit& pi : parked_inits_) mine += pi.session_id == s.id;
+      if (closing && mine < 8 && parked_inits_.size() < 1024) {
         parked_inits_.push_back({s.id, m, monotonic_us() + cfg_.init_timeout_ms * 1000});
         return;
       }
