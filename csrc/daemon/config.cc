@@ -56,7 +56,7 @@ Config Config::from_value(const Value& root) {
   check_keys(root,
              {"control", "comm_default_config", "comm_global_config", "addrs", "listen_port",
               "mccs_daemon_basename", "mccs_daemon_prefix", "qos_schedule", "qos",
-              "comm_patterns_override", "b200"},
+              "comm_patterns_override", "b200", "limits"},
              "the top level");
   if (root.has("control")) {
     const Value& t = root["control"];
@@ -110,6 +110,16 @@ Config Config::from_value(const Value& root) {
     }
   }
   for (const Value& p : root["comm_patterns_override"].items()) c.overrides.push_back(parse_pattern(p));
+  if (root.has("limits")) {
+    const Value& l = root["limits"];
+    check_keys(l, {"max_clients", "max_allocations_per_client", "max_bytes_per_client", "max_communicators_per_client"}, "[limits]");
+    c.max_clients = (int)l["max_clients"].as_int(c.max_clients);
+    c.max_allocations_per_client = (int)l["max_allocations_per_client"].as_int(c.max_allocations_per_client);
+    c.max_bytes_per_client = (uint64_t)l["max_bytes_per_client"].as_int((int64_t)c.max_bytes_per_client);
+    c.max_communicators_per_client = (int)l["max_communicators_per_client"].as_int(c.max_communicators_per_client);
+    if (c.max_clients < 0 || c.max_allocations_per_client < 0 || c.max_communicators_per_client < 0)
+      throw std::runtime_error("[limits] values must not be negative");
+  }
   if (root.has("b200")) {
     const Value& b = root["b200"];
     check_keys(b,

@@ -95,6 +95,13 @@ struct Config {
   uint64_t init_timeout_ms = 60000; // how long a communicator waits for all its ranks
   // Fused launches: up to this many consecutive AllReduces of a communicator (same type and
   // operator, all queued when the first is planned) share one kernel; 1 = off.
+  // What one client (one connection to the control socket) may hold. A tenant is another
+  // user's process: without bounds one of them can take the daemon's memory or every byte of
+  // a GPU. 0 = no limit.
+  int max_clients = 1024;
+  int max_allocations_per_client = 65536;
+  uint64_t max_bytes_per_client = 0;
+  int max_communicators_per_client = 1024;
   int fuse_allreduce = 1;
   // Experiments on the per-call floor; they act on launches that go through the fused
   // kernels only (kernels/batch.cuh) and are all off by default.

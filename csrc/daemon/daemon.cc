@@ -192,6 +192,14 @@ void Daemon::accept_clients() {
       close(fd);
       continue;
     }
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      if (cfg_.max_clients > 0 && (int)sessions_.size() >= cfg_.max_clients) {
+        LOG_WARN("rejecting client: %zu clients are connected ([limits] max_clients)", sessions_.size());
+        close(fd);
+        continue;
+      }
+    }
     ipc::PeerCred cred{0, 0, 0};
     ipc::uds_peer_cred(fd, &cred);
     auto s = std::make_unique<Session>();
@@ -287,13 +295,18 @@ void Daemon::on_malloc(Session& s, const proto::MallocReq& m) {
   r.h.type = proto::kMallocReply;
   r.h.req_id = m.h.req_id;
   Allocation a;
-  int rc = backend_->alloc(m.device, m.size, &a);
+  const bool over = (cfg_.max_allocations_per_client > 0 && (int)s.allocs.size() >= cfg_.max_allocations_per_client) ||
+                    (cfg_.max_bytes_per_client > 0 && (m.size > cfg_.max_bytes_per_client || s.alloc_bytes > cfg_.max_bytes_per_client - m.size));
+  int rc = over ? proto::kErrOutOfMemory : backend_->alloc(m.device, m.size, &a);
   if (rc != proto::kOk) {
+    if (over) LOG_WARN("client %llu (%s): allocation of %llu bytes refused by [limits]", (unsigned long long)s.id, s.app.c_str(),
+                       (unsigned long long)m.size);
     r.h.status = rc;
     reply(s, r, sizeof(proto::MallocReply));
     return;
   }
   a.owner_session = s.id;
+  s.alloc_bytes += a.size;
   {
     std::unique_lock<std::shared_mutex> al(alloc_mu_);
     a.id = next_mem_id_++;
@@ -385,6 +398,7 @@ void Daemon::on_free(Session& s, const proto::FreeReq& m) {
     std::unique_lock<std::shared_mutex> al(alloc_mu_);
     auto it = allocs_.find(m.mem_id);
     if (it != allocs_.end()) {
+      s.alloc_bytes -= std::min<uint64_t>(s.alloc_bytes, it->second.size);
       backend_->release(&it->second);
       allocs_.erase(it);
     }
@@ -526,6 +540,10 @@ void Daemon::on_comm_init(Session& s, const proto::CommInitReq& m) {
   if (m.nranks < 1 || m.nranks > kMaxRanks || m.rank < 0 || m.rank >= m.nranks || m.device < 0 ||
       m.device >= backend_->device_count())
     return fail(proto::kErrInvalidArgument);
+  if (cfg_.max_communicators_per_client > 0 && (int)s.comm_ranks.size() >= cfg_.max_communicators_per_client) {
+    LOG_WARN("client %llu (%s): communicator %u refused by [limits]", (unsigned long long)s.id, s.app.c_str(), m.comm_id);
+    return fail(proto::kErrOutOfMemory);
+  }
   Communicator* cptr = nullptr;
   bool complete = false;
   {

@@ -61,6 +61,7 @@ struct Session {
   std::string app;
   int device_affinity = -1;
   std::set<uint64_t> allocs;
+  uint64_t alloc_bytes = 0;                // sum of their sizes (for the per-client limit)
   std::map<uint64_t, StreamReg> streams;   // stream_id -> registration
   uint64_t next_stream_id = 1;
   std::vector<std::pair<uint32_t, int>> comm_ranks;

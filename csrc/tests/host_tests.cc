@@ -160,6 +160,12 @@ static void test_config() {
   bool threw = false;
   try { Config::from_string("bogus_key = 1\n"); } catch (const std::exception&) { threw = true; }
   CHECK(threw);   // unknown top-level keys are rejected
+  Config lim = Config::from_string("[limits]\nmax_clients = 3\nmax_bytes_per_client = 1073741824\n");
+  CHECK(lim.max_clients == 3 && lim.max_bytes_per_client == (1ull << 30) && lim.max_allocations_per_client == 65536 &&
+        lim.max_communicators_per_client == 1024);
+  bool refused = false;
+  try { Config::from_string("[limits]\nmax_clients = -1\n"); } catch (const std::exception&) { refused = true; }
+  CHECK(refused);
   Config d = Config::from_string("[b200]\ntransport = \"host_staged\"\nwait_timeout_ms = 500\n[qos.tenants.7]\nweight = 2.0\npriority = 1\n");
   CHECK(d.transport == "host_staged" && d.wait_timeout_ms == 500);
   CHECK(d.qos_tenants[7].weight == 2.0 && d.qos_tenants[7].priority == 1);

@@ -739,3 +739,61 @@ def test_client_library_holds_nothing_after_many_communicator_lifetimes(tmp_path
             assert res["after"][2] <= res["before"][2] + 8192, res                                         # resident kB
     finally:
         sp.stop()
+
+
+def test_per_client_limits(tmp_path):
+    """`[limits]`: what one client may hold. Beyond the bounds an allocation answers out of
+    memory and a communicator is refused, what the client already holds keeps working, freeing
+    makes room again, and a connection beyond `max_clients` is turned away."""
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, host_devices=2, force_host=True,
+                       extra="[limits]\nmax_clients = 2\nmax_allocations_per_client = 3\nmax_bytes_per_client = 1048576\n"
+                             "max_communicators_per_client = 2")
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "error"})
+    code = r"""
+import os, sys, torch, json
+import mccs_b200 as M
+res = {}
+a = M.Buffer(400000, 0); b = M.Buffer(400000, 0)
+try:
+    M.Buffer(400000, 0); res["bytes"] = "allowed"
+except M.MccsError as e:
+    res["bytes"] = e.code                       # 1.2 MB > max_bytes_per_client
+c = M.Buffer(1000, 0)
+try:
+    M.Buffer(1000, 0); res["count"] = "allowed"
+except M.MccsError as e:
+    res["count"] = e.code                       # a fourth allocation
+c.free()
+d = M.Buffer(1000, 0); res["after_free"] = "ok"  # freeing made room
+c1 = M.Communicator(1, 0, 1, device=0); c2 = M.Communicator(2, 0, 1, device=0)
+try:
+    M.Communicator(3, 0, 1, device=0); res["comms"] = "allowed"
+except M.MccsError as e:
+    res["comms"] = e.code
+t = a.tensor(torch.float32, 1000); t.fill_(3.0); c1.all_reduce(t, b.tensor(torch.float32, 1000))
+res["still_works"] = float(b.tensor(torch.float32, 1000)[7])
+c2.destroy(); c3 = M.Communicator(3, 0, 1, device=0); res["after_destroy"] = "ok"
+print("RESULT", json.dumps(res), flush=True)
+import time; time.sleep(float(os.environ.get("LINGER", "0")))
+"""
+    try:
+        env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, MCCS_LOG="off")
+        first = subprocess.Popen([sys.executable, "-c", code], env=dict(env, LINGER="6"), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        line = first.stdout.readline()
+        res = json.loads(line[7:])
+        assert res == {"bytes": -2, "count": -2, "after_free": "ok", "comms": -2, "still_works": 3.0, "after_destroy": "ok"}, res
+        # the first client is still connected; a second fits, a third does not
+        hello = os.path.join(NATIVE, "mccs_hello")
+        second = subprocess.Popen([sys.executable, "-c", "import mccs_b200 as M, time; M.init(); print('IN', flush=True); time.sleep(4)"],
+                                  env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        assert second.stdout.readline().startswith("IN")
+        third = subprocess.run([hello], env=env, capture_output=True, text=True, timeout=60)
+        assert third.returncode != 0
+        second.wait(timeout=30)
+        first.wait(timeout=30)
+        fourth = subprocess.run([hello], env=env, capture_output=True, text=True, timeout=60)      # room again
+        assert fourth.returncode == 0, fourth.stdout + fourth.stderr
+    finally:
+        sp.stop()
