@@ -344,6 +344,29 @@ void Daemon::quiesce_session_streams(Session& s) {
   for (auto& ds : streams) backend_->stream_sync(ds.first, ds.second);
 }
 
+// Waits until every proxy thread has finished what it was doing when this was called. A proxy
+// decides on a launch (the communicator is fine, every rank has posted) and then carries it out;
+// a communicator that is failed in between is only seen at the proxy's next look. So whoever
+// fails a communicator and then takes away memory its collectives name waits here first: after
+// it no launch decided on earlier is still being carried out (on the host backend the "kernel"
+// runs inside that call; on a GPU it is on a stream by then, which the caller synchronises next).
+void Daemon::proxy_grace_period() {
+  std::vector<std::pair<ProxyEngine*, uint64_t>> seen;
+  for (auto& p : proxies_)
+    if (p && p->running()) seen.push_back({p.get(), p->passes()});
+  const uint64_t t_end = monotonic_us() + 30ull * 1000 * 1000;
+  for (auto& ps : seen) {
+    while (ps.first->passes() < ps.second + 2) {
+      if (stop_.load(std::memory_order_relaxed) || monotonic_us() > t_end) {
+        if (!stop_.load(std::memory_order_relaxed)) LOG_WARN("a proxy thread has not come round within 30 s; going on");
+        return;
+      }
+      struct timespec ts = {0, 50000};
+      nanosleep(&ts, nullptr);
+    }
+  }
+}
+
 void Daemon::drop_mc_regions_using(uint64_t mem_id) {
   std::lock_guard<std::mutex> g(mu_);
   for (auto& kv : comms_) {
@@ -1120,9 +1143,15 @@ void Daemon::drop_session(uint64_t session_id, const char* why) {
     for (auto& rr : c->ranks) if (rr && !rr->gone.load()) last = false;
     if (last) to_destroy.push_back(cr.first);
   }
+  // The communicators this client was part of are failed now, but a proxy of a surviving rank
+  // may be in the middle of a launch it decided on just before, and its kernels may be reading
+  // this client's buffers: let those launches end, then wait for the streams of every rank of
+  // those communicators. Only then can the memory go.
+  if (!s->allocs.empty() && !s->comm_ranks.empty()) {
+    proxy_grace_period();
+    quiesce_session_streams(*s);
+  }
   for (uint32_t id : to_destroy) destroy_communicator(id);
-  // Streams of surviving communicators that may still read this client's memory
-  // were synchronised in detach_rank; now the memory can go.
   for (uint64_t mem : s->allocs) {
     drop_mc_regions_using(mem);
     std::unique_lock<std::shared_mutex> al(alloc_mu_);

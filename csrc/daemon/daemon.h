@@ -217,6 +217,9 @@ class ProxyEngine : public Engine {
   // Removes the rank and returns once the proxy thread no longer touches it.
   void remove_rank(RankState* rs);
   bool running() const { return started_.load(); }
+  // Passes through progress() so far. Two more than a value read earlier means: whatever the
+  // proxy thread was doing at that moment (a launch it had already decided on) is over.
+  uint64_t passes() const { return passes_.load(std::memory_order_acquire); }
 
  private:
   bool intake(RankState& rs);
@@ -251,6 +254,7 @@ class ProxyEngine : public Engine {
   std::vector<RankState*> ranks_;        // guarded by mu_
   std::atomic<uint64_t> version_{0};
   std::atomic<uint64_t> seen_version_{0};
+  std::atomic<uint64_t> passes_{0};
   std::vector<RankState*> local_;        // proxy thread's copy
   std::atomic<bool> started_{false};
   uint64_t spins_ = 0;
@@ -328,6 +332,7 @@ class Daemon {
   void detach_rank(Communicator& c, int rank, int status);
   void destroy_communicator(uint32_t comm_id);
   void quiesce_session_streams(Session& s);
+  void proxy_grace_period();
   void drop_mc_regions_using(uint64_t mem_id);
   void admin_loop();
   void handle_admin_connection(int fd);

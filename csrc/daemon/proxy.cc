@@ -69,6 +69,7 @@ void ProxyEngine::remove_rank(RankState* rs) {
 }
 
 Progress ProxyEngine::progress() {
+  passes_.fetch_add(1, std::memory_order_acq_rel);
   if (seen_version_.load(std::memory_order_relaxed) != version_.load(std::memory_order_acquire)) {
     std::lock_guard<std::mutex> g(mu_);
     local_ = ranks_;

@@ -797,3 +797,42 @@ import time; time.sleep(float(os.environ.get("LINGER", "0")))
         assert fourth.returncode == 0, fourth.stdout + fourth.stderr
     finally:
         sp.stop()
+
+
+@pytest.mark.parametrize("launch", ["daemon", "client"])
+def test_clients_killed_on_a_busy_machine_do_not_take_the_daemon_down(tmp_path, launch):
+    """A client that dies takes its memory with it while a surviving rank's proxy may be in the
+    middle of a launch that reads it (it had looked at the communicator a moment before it was
+    failed). The daemon lets such launches end and waits for every rank's stream before it
+    releases the memory. Forty kills at varying moments with the machine's cores kept busy,
+    which is what it took to hit the window."""
+    import signal
+    import time
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, host_devices=2, force_host=True,
+                       extra=f'launch = "{launch}"')
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "off"})
+    env = dict(os.environ, MCCS_CONTROL=sp.control, MCCS_LOG="off")
+    trace = os.path.join(d, "t.toml")
+    with open(trace, "w") as f:
+        f.write('communicator_id = 4100\ncuda_devices = [0, 1]\n[[traces]]\nsize = 262144\ntype = "all_reduce"\ncompute_interval = 50\n')
+    burners = [subprocess.Popen([sys.executable, "-c", "import time\nt = time.time()\nwhile time.time() - t < 60: pass"]) for _ in range(6)]
+    try:
+        for k in range(40):
+            ps = [subprocess.Popen([os.path.join(NATIVE, "traffic_gen"), "--rank", str(r), "--config", trace, "--iters", "1000000"], env=env,
+                                   stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL) for r in range(2)]
+            time.sleep(0.05 + (k % 5) * 0.04)
+            ps[k % 2].send_signal(signal.SIGKILL)
+            for p in ps:
+                p.wait(timeout=60)
+            assert sp.proc.poll() is None, f"the daemon died after {k + 1} kills"
+        # and it still serves
+        ok = [subprocess.Popen([os.path.join(NATIVE, "allreduce_proto"), "--rank", str(r), "--num-ranks", "2", "--cuda-device-idx", str(r),
+                                "--communicator", "4101", "--size", "65536"], env=env, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+              for r in range(2)]
+        assert [p.wait(timeout=60) for p in ok] == [0, 0]
+    finally:
+        for b in burners:
+            b.kill()
+        sp.stop()
