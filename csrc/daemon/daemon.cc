@@ -1150,6 +1150,29 @@ void Daemon::drop_session(uint64_t session_id, const char* why) {
   if (!s->allocs.empty() && !s->comm_ranks.empty()) {
     proxy_grace_period();
     quiesce_session_streams(*s);
+    // Kernels that surviving clients launched themselves run on their streams, out of the
+    // daemon's reach. They have been told to give up (abort word); give them a moment to do
+    // so before multicast bindings of the dead client's memory are taken apart under them:
+    // every surviving rank is through its last ticket or has reported an error. Bounded: a
+    // client that got a plan and never launched must not hold the daemon up.
+    const uint64_t t_end = monotonic_us() + 2ull * 1000 * 1000;
+    for (auto& cr : s->comm_ranks) {
+      Communicator* c = nullptr;
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        auto cit = comms_.find(cr.first);
+        if (cit != comms_.end()) c = cit->second.get();
+      }
+      if (!c || c->state.load() == kCommInit || !c->client_launch) continue;
+      for (auto& r : c->ranks) {
+        if (!r || r->gone.load() || !r->status) continue;
+        while (__atomic_load_n(&r->status->done_seq, __ATOMIC_ACQUIRE) < r->last_ticket.load(std::memory_order_relaxed) &&
+               __atomic_load_n(&r->status->error, __ATOMIC_ACQUIRE) == kDevOk && monotonic_us() < t_end) {
+          struct timespec ts = {0, 50000};
+          nanosleep(&ts, nullptr);
+        }
+      }
+    }
   }
   for (uint32_t id : to_destroy) destroy_communicator(id);
   for (uint64_t mem : s->allocs) {
