@@ -357,8 +357,8 @@ void Daemon::proxy_grace_period() {
   const uint64_t t_end = monotonic_us() + 30ull * 1000 * 1000;
   for (auto& ps : seen) {
     while (ps.first->passes() < ps.second + 2) {
-      if (stop_.load(std::memory_order_relaxed) || monotonic_us() > t_end) {
-        if (!stop_.load(std::memory_order_relaxed)) LOG_WARN("a proxy thread has not come round within 30 s; going on");
+      if (monotonic_us() > t_end) {
+        LOG_WARN("a proxy thread has not come round within 30 s; going on");
         return;
       }
       struct timespec ts = {0, 50000};
