@@ -836,3 +836,48 @@ def test_clients_killed_on_a_busy_machine_do_not_take_the_daemon_down(tmp_path, 
         for b in burners:
             b.kill()
         sp.stop()
+
+
+@pytest.mark.parametrize("launch", ["daemon", "client"])
+def test_ranks_killed_anywhere_in_their_lifetime(tmp_path, launch):
+    """Sixty short jobs of two to four ranks; in each, one or two ranks are killed at a random
+    moment between their start and their end: while connecting, allocating, joining the
+    communicator, in a collective, in their clean-up. The daemon stays up, gives every
+    descriptor back and serves the next job."""
+    import random
+    import signal
+    import time
+    from mccs_b200 import daemon
+    d = str(tmp_path)
+    cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, host_devices=4, force_host=True,
+                       extra=f'launch = "{launch}"\ninit_timeout_ms = 2000')
+    sp = daemon.spawn(cfg, env={"MCCS_LOG": "off"})
+    env = dict(os.environ, MCCS_CONTROL=sp.control, MCCS_LOG="off", MCCS_WC_TIMEOUT_MS="5000")
+    rng = random.Random(5)
+
+    def job(n, comm, size):
+        return [subprocess.Popen([os.path.join(NATIVE, "allreduce_proto"), "--rank", str(r), "--num-ranks", str(n), "--cuda-device-idx", str(r),
+                                  "--communicator", str(comm), "--size", str(size)], env=env, stdout=subprocess.DEVNULL,
+                                 stderr=subprocess.DEVNULL) for r in range(n)]
+
+    try:
+        fds_before = None
+        for k in range(60):
+            n = rng.choice([2, 3, 4])
+            ps = job(n, 6000 + k % 3, 1048576)
+            time.sleep(rng.uniform(0.0, 0.08))
+            for victim in rng.sample(range(n), rng.choice([1, 1, 2])):
+                ps[victim].send_signal(signal.SIGKILL)
+            for p in ps:
+                p.wait(timeout=60)
+            assert sp.proc.poll() is None, f"the daemon died in round {k}"
+            if k == 10:
+                time.sleep(0.5)
+                fds_before = len(os.listdir(f"/proc/{sp.proc.pid}/fd"))
+        deadline = time.time() + 10
+        while time.time() < deadline and len(os.listdir(f"/proc/{sp.proc.pid}/fd")) != fds_before:
+            time.sleep(0.2)
+        assert len(os.listdir(f"/proc/{sp.proc.pid}/fd")) == fds_before
+        assert [p.wait(timeout=60) for p in job(2, 6100, 65536)] == [0, 0]
+    finally:
+        sp.stop()
