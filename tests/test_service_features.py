@@ -708,7 +708,7 @@ def life(k):
     c.destroy(); del t; buf.free(); g.free()
 for k in range(20): life(k)
 gc.collect(); a = snap()
-for k in range(20, 170): life(k)
+for k in range(20, 120): life(k)
 gc.collect(); b = snap()
 import json; print("RESULT", json.dumps({"before": a, "after": b}), flush=True)
 M.finalize()
@@ -718,7 +718,7 @@ M.finalize()
 @pytest.mark.parametrize("launch", ["daemon", "client"])
 def test_client_library_holds_nothing_after_many_communicator_lifetimes(tmp_path, launch):
     """The other side of the same question: a long-lived application that creates and destroys
-    communicators and buffers (150 times here, with collectives and groups in between) ends
+    communicators and buffers (100 times here, with collectives and groups in between) ends
     with the descriptors and mappings it started with; with client launches that includes
     the peers' buffers, pads and status blocks mapped per communicator."""
     import json
@@ -780,13 +780,13 @@ import time; time.sleep(float(os.environ.get("LINGER", "0")))
 """
     try:
         env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, MCCS_LOG="off")
-        first = subprocess.Popen([sys.executable, "-c", code], env=dict(env, LINGER="6"), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        first = subprocess.Popen([sys.executable, "-c", code], env=dict(env, LINGER="4"), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
         line = first.stdout.readline()
         res = json.loads(line[7:])
         assert res == {"bytes": -2, "count": -2, "after_free": "ok", "comms": -2, "still_works": 3.0, "after_destroy": "ok"}, res
         # the first client is still connected; a second fits, a third does not
         hello = os.path.join(NATIVE, "mccs_hello")
-        second = subprocess.Popen([sys.executable, "-c", "import mccs_b200 as M, time; M.init(); print('IN', flush=True); time.sleep(4)"],
+        second = subprocess.Popen([sys.executable, "-c", "import mccs_b200 as M, time; M.init(); print('IN', flush=True); time.sleep(2.5)"],
                                   env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
         assert second.stdout.readline().startswith("IN")
         third = subprocess.run([hello], env=env, capture_output=True, text=True, timeout=60)
@@ -840,7 +840,7 @@ def test_clients_killed_on_a_busy_machine_do_not_take_the_daemon_down(tmp_path, 
 
 @pytest.mark.parametrize("launch", ["daemon", "client"])
 def test_ranks_killed_anywhere_in_their_lifetime(tmp_path, launch):
-    """Sixty short jobs of two to four ranks; in each, one or two ranks are killed at a random
+    """Forty short jobs of two to four ranks; in each, one or two ranks are killed at a random
     moment between their start and their end: while connecting, allocating, joining the
     communicator, in a collective, in their clean-up. The daemon stays up, gives every
     descriptor back and serves the next job."""
@@ -862,7 +862,7 @@ def test_ranks_killed_anywhere_in_their_lifetime(tmp_path, launch):
 
     try:
         fds_before = None
-        for k in range(60):
+        for k in range(40):
             n = rng.choice([2, 3, 4])
             ps = job(n, 6000 + k % 3, 1048576)
             time.sleep(rng.uniform(0.0, 0.08))
