@@ -164,6 +164,20 @@ Value Daemon::stats() {
   {
     std::lock_guard<std::mutex> g(mu_);
     out.set("clients", (int64_t)sessions_.size());
+    // what every client holds (the quantities the [limits] table bounds)
+    Value holders = Value::array();
+    for (auto& kv : sessions_) {
+      const Session& s = *kv.second;
+      Value h = Value::object();
+      h.set("id", (int64_t)s.id);
+      h.set("pid", s.pid);
+      h.set("app", s.app);
+      h.set("allocations", s.stat_allocs.load(std::memory_order_relaxed));
+      h.set("allocated_bytes", (int64_t)s.stat_bytes.load(std::memory_order_relaxed));
+      h.set("communicators", s.stat_comms.load(std::memory_order_relaxed));
+      holders.push(h);
+    }
+    out.set("client_list", holders);
     for (auto& kv : comms_) {
       Communicator& c = *kv.second;
       Value v = Value::object();

@@ -289,6 +289,12 @@ void Daemon::handle_session(Session& s) {
 // ---------------------------------------------------------------------------
 // Memory
 // ---------------------------------------------------------------------------
+static void refresh_stats(Session& s) {
+  s.stat_bytes.store(s.alloc_bytes, std::memory_order_relaxed);
+  s.stat_allocs.store((int)s.allocs.size(), std::memory_order_relaxed);
+  s.stat_comms.store((int)s.comm_ranks.size(), std::memory_order_relaxed);
+}
+
 void Daemon::on_malloc(Session& s, const proto::MallocReq& m) {
   proto::AnyMsg r;
   memset(&r, 0, sizeof r);
@@ -314,6 +320,7 @@ void Daemon::on_malloc(Session& s, const proto::MallocReq& m) {
     alloc_use_[a.id];
   }
   s.allocs.insert(a.id);
+  refresh_stats(s);
   r.malloc_reply.mem_id = a.id;
   r.malloc_reply.size = a.size;
   r.malloc_reply.daemon_va = a.va;
@@ -428,6 +435,7 @@ void Daemon::on_free(Session& s, const proto::FreeReq& m) {
     alloc_use_.erase(m.mem_id);
   }
   s.allocs.erase(m.mem_id);
+  refresh_stats(s);
   reply(s, r, sizeof(proto::FreeReply));
 }
 
@@ -611,6 +619,7 @@ void Daemon::on_comm_init(Session& s, const proto::CommInitReq& m) {
     c.devices[(size_t)m.rank] = m.device;
     c.ranks[(size_t)m.rank] = std::move(rs);
     s.comm_ranks.push_back({m.comm_id, m.rank});
+    refresh_stats(s);
     pending_inits_.push_back({s.id, m.h.req_id, m.comm_id, m.rank, monotonic_us() + cfg_.init_timeout_ms * 1000});
     int joined = 0;
     for (auto& r : c.ranks) if (r) joined++;
@@ -841,6 +850,7 @@ void Daemon::check_init_timeouts() {
       reply(*ps, r, sizeof(proto::CommInitReply));
       auto& v = ps->comm_ranks;
       v.erase(std::remove(v.begin(), v.end(), std::make_pair(pi.comm_id, pi.rank)), v.end());
+      refresh_stats(*ps);
     }
     bool empty = false;
     {
@@ -932,6 +942,7 @@ void Daemon::on_comm_destroy(Session& s, const proto::CommDestroyReq& m) {
     return;
   }
   s.comm_ranks.erase(it);
+  refresh_stats(s);
   Communicator* c = nullptr;
   {
     std::lock_guard<std::mutex> g(mu_);
@@ -1134,6 +1145,7 @@ void Daemon::drop_session(uint64_t session_id, const char* why) {
         reply(*sit->second, r, sizeof(proto::CommInitReply));
         auto& v = sit->second->comm_ranks;
         v.erase(std::remove(v.begin(), v.end(), std::make_pair(pi.comm_id, pi.rank)), v.end());
+        refresh_stats(*sit->second);
       }
       to_destroy.push_back(cr.first);
       continue;

@@ -62,6 +62,9 @@ struct Session {
   int device_affinity = -1;
   std::set<uint64_t> allocs;
   uint64_t alloc_bytes = 0;                // sum of their sizes (for the per-client limit)
+  // Copies of the three counts for the statistics, which another thread reads.
+  std::atomic<uint64_t> stat_bytes{0};
+  std::atomic<int> stat_allocs{0}, stat_comms{0};
   std::map<uint64_t, StreamReg> streams;   // stream_id -> registration
   uint64_t next_stream_id = 1;
   std::vector<std::pair<uint32_t, int>> comm_ranks;

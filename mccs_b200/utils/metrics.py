@@ -10,6 +10,8 @@ it over HTTP:
 
 Metrics (``comm`` = communicator id, which is also the tenant id of the arbiter):
 ``mccs_clients``, ``mccs_allocations``, ``mccs_allocated_bytes``;
+``mccs_client_allocations{client, pid, app}``, ``mccs_client_allocated_bytes``, ``mccs_client_communicators``
+(what each client holds: the quantities the ``[limits]`` table bounds);
 ``mccs_comm_planned_total``, ``mccs_comm_completed_total`` (kernel launches: a fused launch
 counts once), ``mccs_comm_fused_launches_total``, ``mccs_comm_fused_members_total``,
 ``mccs_comm_config_epoch``, ``mccs_comm_paused``, ``mccs_comm_async_error``,
@@ -51,6 +53,12 @@ def render(stats: dict) -> str:
     family("mccs_allocations", "gauge", "device allocations handed out", [_line("mccs_allocations", {}, int(stats.get("allocations", 0)))])
     family("mccs_allocated_bytes", "gauge", "bytes of device memory handed out",
            [_line("mccs_allocated_bytes", {}, int(stats.get("allocated_bytes", 0)))])
+    holders = stats.get("client_list", [])
+    for name, key, help_ in (("mccs_client_allocations", "allocations", "allocations a client holds"),
+                             ("mccs_client_allocated_bytes", "allocated_bytes", "bytes of device memory a client holds"),
+                             ("mccs_client_communicators", "communicators", "communicator ranks a client holds")):
+        family(name, "gauge", help_, [_line(name, {"client": h.get("id", 0), "pid": h.get("pid", 0), "app": h.get("app", "")}, int(h.get(key, 0)))
+                                      for h in holders])
     comms = stats.get("communicators", {})
     per_comm = [
         ("mccs_comm_planned_total", "counter", "collectives planned", "planned"),

@@ -343,6 +343,7 @@ def test_metrics_exporter_serves_the_daemons_counters(service):
     assert f'mccs_tenant_admitted_total{{comm="{cid}"}} 3' in text
     assert f'mccs_tenant_deferred_total{{comm="{cid}",reason="window"}} 0' in text
     assert f'mccs_comm_info{{comm="{cid}",variant="' in text and "# TYPE mccs_comm_completed_total counter" in text
+    assert "mccs_client_allocated_bytes{client=" in text and "mccs_client_communicators{client=" in text
     for line in text.splitlines():        # every sample line is `name{labels} number`
         if line and not line.startswith("#"):
             float(line.rsplit(" ", 1)[1])
