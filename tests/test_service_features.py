@@ -639,7 +639,7 @@ def test_daemon_holds_nothing_after_many_client_lifetimes(tmp_path, launch):
     from mccs_b200 import daemon
     d = str(tmp_path)
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, host_devices=2, force_host=True,
-                       extra=f'launch = "{launch}"')     # client: pads, status blocks and peers' buffers are handed out as descriptors too
+                       extra=f'launch = "{launch}"\ninit_timeout_ms = 3000')     # client: pads, status blocks and peers' buffers are handed out as descriptors too
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "error"})
     pid = sp.proc.pid
 
@@ -776,24 +776,30 @@ t = a.tensor(torch.float32, 1000); t.fill_(3.0); c1.all_reduce(t, b.tensor(torch
 res["still_works"] = float(b.tensor(torch.float32, 1000)[7])
 c2.destroy(); c3 = M.Communicator(3, 0, 1, device=0); res["after_destroy"] = "ok"
 print("RESULT", json.dumps(res), flush=True)
-import time; time.sleep(float(os.environ.get("LINGER", "0")))
+sys.stdin.readline()          # stays connected until the test lets it go
 """
     try:
         env = dict(os.environ, PYTHONPATH=REPO, MCCS_CONTROL=sp.control, MCCS_LOG="off")
-        first = subprocess.Popen([sys.executable, "-c", code], env=dict(env, LINGER="4"), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        first = subprocess.Popen([sys.executable, "-c", code], env=env, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
         line = first.stdout.readline()
         res = json.loads(line[7:])
         assert res == {"bytes": -2, "count": -2, "after_free": "ok", "comms": -2, "still_works": 3.0, "after_destroy": "ok"}, res
         # the first client is still connected; a second fits, a third does not
         hello = os.path.join(NATIVE, "mccs_hello")
-        second = subprocess.Popen([sys.executable, "-c", "import mccs_b200 as M, time; M.init(); print('IN', flush=True); time.sleep(2.5)"],
-                                  env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        second = subprocess.Popen([sys.executable, "-c", "import sys, mccs_b200 as M; M.init(); print('IN', flush=True); sys.stdin.readline()"],
+                                  env=env, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
         assert second.stdout.readline().startswith("IN")
         third = subprocess.run([hello], env=env, capture_output=True, text=True, timeout=60)
         assert third.returncode != 0
-        second.wait(timeout=30)
-        first.wait(timeout=30)
-        fourth = subprocess.run([hello], env=env, capture_output=True, text=True, timeout=60)      # room again
+        for p in (second, first):
+            p.stdin.close()
+            p.wait(timeout=30)
+        deadline = time.time() + 15          # the daemon notices the closed connections at its next look
+        while True:
+            fourth = subprocess.run([hello], env=env, capture_output=True, text=True, timeout=60)      # room again
+            if fourth.returncode == 0 or time.time() > deadline:
+                break
+            time.sleep(0.2)
         assert fourth.returncode == 0, fourth.stdout + fourth.stderr
     finally:
         sp.stop()
@@ -810,8 +816,9 @@ def test_clients_killed_on_a_busy_machine_do_not_take_the_daemon_down(tmp_path, 
     import time
     from mccs_b200 import daemon
     d = str(tmp_path)
+    # (a victim that is killed before it has joined leaves its peer waiting for the init timeout)
     cfg = write_config(os.path.join(d, "mccs.toml"), os.path.join(d, "sock"), listen_port=-1, host_devices=2, force_host=True,
-                       extra=f'launch = "{launch}"')
+                       extra=f'launch = "{launch}"\ninit_timeout_ms = 3000')
     sp = daemon.spawn(cfg, env={"MCCS_LOG": "off"})
     env = dict(os.environ, MCCS_CONTROL=sp.control, MCCS_LOG="off")
     trace = os.path.join(d, "t.toml")
